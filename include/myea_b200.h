@@ -1,0 +1,232 @@
+/*
+ * myea_b200.h — C ABI of the B200 (sm_100a) implementation of the MyEA training step.
+ *
+ * One handle = one `class Neural_Network` of the reference (Header_Files/Neural_Network/Data.hpp:760-3293)
+ * living on one GPU.  The entry points are one-to-one with the member functions the reference's training
+ * loop calls (Source_Files/Neural_Network/Dataset.cpp:637-691, 7654-7690); each declaration cites the member
+ * it replaces.  Plain pointers and sizes only; host memory is owned by the caller, device memory by the
+ * library.  Every function returns 0 on success or a negative MYEA_E_* status and never aborts or traps;
+ * myea_b200_last_error() gives the message.  One host thread per handle; calls are asynchronous on the
+ * handle's stream, download / compute_error results synchronise.
+ *
+ * Enumerator values are the reference's own (Common_Library/include/Enums/ *.hpp) so that a host class can
+ * pass its enums through unchanged.
+ */
+#ifndef MYEA_B200_H
+#define MYEA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MYEA_MAX_LAYERS 64
+
+/* status codes */
+#define MYEA_OK 0
+#define MYEA_E_INVALID (-1)     /* bad argument / unsupported topology            */
+#define MYEA_E_CUDA (-2)        /* a CUDA runtime / driver call failed            */
+#define MYEA_E_KERNEL (-3)      /* a kernel reported a bounded-wait timeout       */
+#define MYEA_E_UNSUPPORTED (-4) /* valid in the reference, not built here         */
+#define MYEA_E_COMM (-5)        /* NCCL failure                                   */
+
+/* ENUM_TYPE_LAYER (Enum_Type_Layer.hpp:25) */
+#define MYEA_LAYER_FULLY_CONNECTED 4u
+#define MYEA_LAYER_LSTM 8u
+#define MYEA_LAYER_RESIDUAL 10u
+/* ENUM_TYPE_NETWORKS (Enum_Type_Networks.hpp:25) */
+#define MYEA_NETWORK_FEEDFORWARD 3u
+#define MYEA_NETWORK_RECURRENT 4u
+/* ENUM_TYPE_ACTIVATION_FUNCTION (Enum_Type_Activation_Functions.hpp:25) */
+#define MYEA_AF_ELU 3u
+#define MYEA_AF_LINEAR 11u
+#define MYEA_AF_LEAKY_RELU 14u
+#define MYEA_AF_RELU 16u
+#define MYEA_AF_SELU 17u
+#define MYEA_AF_SIGMOID 18u
+#define MYEA_AF_SOFTMAX 22u
+#define MYEA_AF_TANH 23u
+/* ENUM_TYPE_LAYER_NORMALIZATION (Enum_Type_Layer_Normalization.hpp) */
+#define MYEA_NORM_NONE 0u
+#define MYEA_NORM_BATCH_NORMALIZATION 1u
+#define MYEA_NORM_BATCH_RENORMALIZATION 2u
+/* ENUM_TYPE_LAYER_DROPOUT (Enum_Type_Layer_Dropout.hpp:25) */
+#define MYEA_DROPOUT_NONE 0u
+#define MYEA_DROPOUT_BERNOULLI 2u
+#define MYEA_DROPOUT_BERNOULLI_INVERTED 3u
+#define MYEA_DROPOUT_SHAKEDROP 5u
+#define MYEA_DROPOUT_ZONEOUT 7u
+/* ENUM_TYPE_LOSS_FUNCTIONS / ENUM_TYPE_ACCURACY_FUNCTIONS (Enum_Type_Loss_Functions.hpp:25,58) */
+#define MYEA_LOSS_CROSS_ENTROPY 2u
+#define MYEA_LOSS_MSE 10u
+#define MYEA_ACCURACY_NONE 0u
+#define MYEA_ACCURACY_CROSS_ENTROPY 1u
+#define MYEA_ACCURACY_DISTANCE 3u
+/* ENUM_TYPE_OPTIMIZER_FUNCTIONS (Enum_Type_Optimizer_Functions.hpp) */
+#define MYEA_OPT_ADABOUND 1u
+#define MYEA_OPT_ADAM 2u
+#define MYEA_OPT_AMSBOUND 4u
+#define MYEA_OPT_AMSGRAD 5u
+#define MYEA_OPT_GD 6u
+
+/* One layer, as `struct Layer_Parameters` (Data.hpp:56-80) plus the per-layer Set__* state. */
+typedef struct myea_layer_desc {
+  uint32_t type_layer;        /* MYEA_LAYER_*                                                     */
+  uint32_t use_bidirectional; /* Layer_Parameters::use_bidirectional (LSTM only)                  */
+  uint64_t unit_parameters[5];/* [0] FC: neurons, LSTM: blocks, RESIDUAL: block depth; [1] LSTM: cells per block */
+  uint32_t type_activation_function; /* Set__Layer_Activation_Function (Data.hpp:2749)           */
+  uint32_t type_normalization;       /* Set__Layer_Normalization       (Data.hpp:2697)           */
+  uint32_t use_layer_normalization_before_activation; /* reference default: 1                    */
+  uint32_t type_dropout;             /* Set__Dropout                   (Data.hpp:2667)           */
+  float dropout_values[3];    /* Bernoulli: retention probability; ShakeDrop: drop probability; Zoneout: cell, hidden */
+  uint32_t reserved;
+} myea_layer_desc;
+
+/* Whole network: the arguments of Neural_Network::Compile (Data.hpp:2531) plus network-level Set__* state. */
+typedef struct myea_net_desc {
+  uint32_t number_layers;        /* including the input layer (layer 0, an FC desc holding the input width) */
+  uint32_t type_network;         /* MYEA_NETWORK_*                                              */
+  uint64_t number_recurrent_depth; /* T; 1 for feed-forward                                      */
+  uint64_t number_time_delays;   /* Set__Number_Time_Delays (Data.hpp:2666)                      */
+  uint64_t batch_size;           /* rows the activation buffers are carved for (Update__Batch_Size, Data.hpp:2559) */
+  uint32_t type_loss_function;   /* Set__Loss_Function     (Data.hpp:832)                        */
+  uint32_t type_accuracy_function; /* Set__Accuracy_Function (Data.hpp:833)                      */
+  float accuracy_variance;       /* DISTANCE accuracy tolerance                                  */
+  float normalization_momentum_average; /* Data.hpp:2966 */
+  float normalization_epsilon;   /* Data.hpp:2967                                                */
+  float batch_renormalization_r_correction_maximum; /* Data.hpp:2746                             */
+  float batch_renormalization_d_correction_maximum; /* Data.hpp:2747                             */
+  uint32_t reserved;
+  myea_layer_desc layers[MYEA_MAX_LAYERS];
+} myea_net_desc;
+
+/* Optimizer state of the reference object read by Update_Parameter (Data.hpp:2940-2957). */
+typedef struct myea_opt_desc {
+  uint32_t type_optimizer_function; /* MYEA_OPT_*                                               */
+  uint32_t use_adam_bias_correction;
+  float learning_rate;        /* GD learning rate                                                */
+  float learning_momentum;    /* GD momentum (0 = plain GD)                                      */
+  uint32_t use_nesterov;
+  float adam_learning_rate, adam_beta1, adam_beta2, adam_epsilon;
+  float learning_rate_final, learning_gamma; /* AdaBound / AMSBound                              */
+  float regularization__weight_decay;
+  uint32_t use_normalized_weight_decay;
+  uint32_t use_clip_gradient; /* Set__Clip_Gradient(bool)  (Data.hpp:837)                        */
+  float clip_gradient;        /* Set__Clip_Gradient(T_)    (Data.hpp:2718)                       */
+  float epoch_time_step;      /* divisor of the normalized weight decay (Train.cpp:284-286)      */
+} myea_opt_desc;
+
+/* Where one layer's parameters sit in the flat [P] buffer: the index map that
+ * Prepare__Connections__FC/LSTM and Prepare__Bias__FC/LSTM (Neural_Network__Prepare_Connections.cpp:20-252)
+ * and Allocate__Normalized_Unit (Neural_Network__Allocate.cpp:2378-2460) build.  Bit-exact with the reference. */
+typedef struct myea_layer_index {
+  uint64_t first_connection_index, last_connection_index;
+  uint64_t first_bias_connection_index, last_bias_connection_index; /* LSTM: already shifted by the cell count, as the reference does */
+  uint64_t scale_index, shift_index; /* gamma / beta of this layer's first unit; valid once any layer is normalized */
+  uint64_t number_inputs, number_outputs;
+  uint64_t block_stride;      /* LSTM: floats per block = 4*in + 4*cells + 3*cells_per_block     */
+  uint64_t number_units_norm; /* units of this layer counted in the normalized-unit run          */
+} myea_layer_index;
+
+typedef struct myea_b200_net *myea_handle;
+
+/* buffer selectors for upload / download */
+#define MYEA_BUF_PARAMETERS 0     /* ptr_array_parameters                         (Data.hpp:3017 block) */
+#define MYEA_BUF_DERIVATIVES 1    /* ptr_array_derivatives_parameters, merged [P]                       */
+#define MYEA_BUF_FIRST_MOMENT 2   /* ptr_array_previous_biased_first_moment                             */
+#define MYEA_BUF_SECOND_MOMENT 3  /* ptr_array_previous_biased_second_moment                            */
+#define MYEA_BUF_SECOND_MOMENT_HAT 4 /* ptr_array_previous_biased_second_moment_hat (AMSGrad)           */
+#define MYEA_BUF_MASK_REGULARIZED 5  /* ptr_array_mask_regularized_parameters                           */
+#define MYEA_BUF_NORM_MEAN_AVERAGE 6     /* normalized_batch_units.ptr_mean_average, all units          */
+#define MYEA_BUF_NORM_VARIANCE_AVERAGE 7 /* normalized_batch_units.ptr_variance_average, all units      */
+#define MYEA_BUF_PREVIOUS_DELTA 8 /* ptr_array_previous_delta_parameters (GD momentum)                  */
+
+/* Neural_Network::Compile + Set__* + Update__Batch_Size (Neural_Network__Compile.cpp:426-785,
+ * Neural_Network__Update.cpp:187-231): builds the index map, carves device buffers for batch_size rows. */
+int myea_b200_create(myea_handle *out, const myea_net_desc *desc, int device);
+/* Neural_Network::Deallocate (Neural_Network__Deallocate.cpp) */
+void myea_b200_destroy(myea_handle h);
+const char *myea_b200_last_error(myea_handle h);
+
+/* total_parameters / total_weights / total_bias (Data.hpp:2925-2935) and the per-layer index map. */
+int myea_b200_sizes(myea_handle h, uint64_t *total_parameters, uint64_t *total_weights, uint64_t *total_bias,
+                    uint64_t *total_normalized_units);
+int myea_b200_layer_index(myea_handle h, uint32_t layer, myea_layer_index *out);
+
+/* Copy__Parameters__Host_To_Device / …Device_To_Host, Copy__Optimizer_Paramaters__Device_To_Host,
+ * Copy__Batch_Normalization_Neurons__Device_To_Host (Data.hpp:3112-3195): `count` floats from `offset`. */
+int myea_b200_upload(myea_handle h, int which, const float *host, uint64_t offset, uint64_t count);
+int myea_b200_download(myea_handle h, int which, float *host, uint64_t offset, uint64_t count);
+
+/* Layer::ptr_array__mask__dropout__bernoulli (Data.hpp:611): bool[T][units] of layer `layer`, true = keep. */
+int myea_b200_set_mask_bernoulli(myea_handle h, uint32_t layer, const uint8_t *mask, uint64_t count);
+/* Cell_unit::ptr_mask_dropout_zoneout_state / _output (Data.hpp:484-485), gathered as bool[T][cells]
+ * (both directions: [T][2*cells]); true = compute, false = keep the previous value. */
+int myea_b200_set_mask_zoneout(myea_handle h, uint32_t layer, const uint8_t *mask_state, const uint8_t *mask_output,
+                               uint64_t count);
+/* ShakeDrop draws of one residual block made explicit: mask bool[B] (Layer::ptr_array__mask__dropout__shakedrop,
+ * Data.hpp:612), forward coefficients alpha[B][units] and backward coefficients beta[B][units]
+ * (Neural_Network__Forward_Pass__OpenMP.cpp:5021-5056, Neural_Network__Backward_Pass__OpenMP.cpp:1009-1042). */
+int myea_b200_set_shakedrop(myea_handle h, uint32_t layer, const uint8_t *mask, const float *alpha, const float *beta,
+                            uint64_t batch);
+
+/* void Forward_Pass(size_t B, T_ const *const *X, …) (Data.hpp:2896). X is the packed [T][B][inputs] block the
+ * host class gathers from the reference's row pointers; host memory. training: type_state_propagation (Data.hpp:3048). */
+int myea_b200_forward(myea_handle h, uint64_t batch, const float *inputs_TBI, int training);
+/* same, inputs already resident on this handle's GPU */
+int myea_b200_forward_device(myea_handle h, uint64_t batch, const float *device_inputs_TBI, int training);
+/* void Compute__Error(size_t B, T_ const *const *Y) (Data.hpp:1033). Y packed [T][B][outputs]. The loss sum, the
+ * number of loss terms and the accuracy count are ACCUMULATED into the handle (ptr_array_loss_values,
+ * ptr_array_number_loss, ptr_array_accuracy_values) and read with myea_b200_get_loss. */
+int myea_b200_compute_error(myea_handle h, uint64_t batch, const float *desired_TBO);
+int myea_b200_compute_error_device(myea_handle h, uint64_t batch, const float *device_desired_TBO);
+/* Reset__Loss (Data.hpp:823) / the accumulators behind Get__Loss (Data.hpp:2913). */
+int myea_b200_reset_loss(myea_handle h);
+int myea_b200_get_loss(myea_handle h, double *loss_sum, uint64_t *number_loss, double *accuracy_sum);
+/* void Backward_Pass(size_t B) (Data.hpp:1709) */
+int myea_b200_backward(myea_handle h, uint64_t batch);
+/* void Update_Derivative_Weight(size_t B, Layer *first, Layer const *end) (Data.hpp:2199), over all layers */
+int myea_b200_update_derivative_weight(myea_handle h, uint64_t batch);
+/* void Update_Parameter(size_t B, size_t N_train) (Data.hpp:849): merge (all-reduce when a communicator is
+ * attached), clip, optimizer, zero the derivatives. */
+int myea_b200_update_parameter(myea_handle h, uint64_t batch, uint64_t training_size, const myea_opt_desc *opt);
+/* Clear_Training_Arrays (Data.hpp:2438): zero derivatives and optimizer moments, optimizer_time_step = 0. */
+int myea_b200_clear_training_arrays(myea_handle h);
+/* Layer outputs of the last forward pass, [T][B][outputs] (Get__Outputs, Data.hpp:2903), to host memory. */
+int myea_b200_get_outputs(myea_handle h, uint32_t layer, float *host, uint64_t count);
+/* Layer errors (Neuron_unit::ptr_array_errors / cell delta of an LSTM) of the last backward pass. */
+int myea_b200_get_errors(myea_handle h, uint32_t layer, float *host, uint64_t count);
+
+/* Merge_Derivatives_Parameters (Neural_Network__Merge.cpp:20-50) across GPUs: attach this handle to an NCCL
+ * communicator of `world` ranks. `unique_id` is the 128-byte ncclUniqueId made by rank 0
+ * (myea_b200_comm_unique_id) and carried to the other ranks by the caller. */
+int myea_b200_comm_unique_id(uint8_t id_out[128]);
+int myea_b200_comm_init(myea_handle h, int world, int rank, const uint8_t unique_id[128]);
+
+/* Blocks until the handle's stream is idle; returns MYEA_E_KERNEL if any kernel flagged a timeout. */
+int myea_b200_synchronize(myea_handle h);
+/* The handle's cudaStream_t (for event timing by the caller) and counters. */
+void *myea_b200_stream(myea_handle h);
+uint64_t myea_b200_kernel_launches(myea_handle h);
+
+/* Stand-alone dense contraction used by the step, exposed for kernel-level tests and roofline timing:
+ * C[M,N] (+)= A[M,K] · B[N,K]^T, fp32 in HOST memory, computed on tcgen05 with 3xTF32 split precision
+ * (engine 0) or with the FP32 FMA kernel (engine 1). Replaces the triple loops
+ * Forward_Pass__FC / Backward_Pass__FC / Update_Derivative_Weight__FC
+ * (Neural_Network__Forward_Pass__OpenMP.cpp:4517, …Backward_Pass__OpenMP.cpp:1044, …Update_Derivative_Weight__OpenMP.cpp:178). */
+int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N, uint64_t K, const float *A, const float *B,
+                      float *C, int accumulate, float *elapsed_ms, int repeats);
+
+/* Per-kernel-class device time of the handle since the last call with reset!=0 (CUDA events on the handle's
+ * stream); classes: 0 gemm, 1 split/pack, 2 normalization, 3 elementwise, 4 optimizer, 5 recurrent cell. */
+#define MYEA_TIMER_CLASSES 8
+int myea_b200_profile(myea_handle h, int enable);
+int myea_b200_profile_read(myea_handle h, double ms[MYEA_TIMER_CLASSES], uint64_t launches[MYEA_TIMER_CLASSES],
+                           double gemm_flops[1], int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MYEA_B200_H */

@@ -1,0 +1,160 @@
+"""Test infrastructure, not product code.
+
+numpy-friendly wrapper over oracle/_ref/libmyea_ref.so: the reference's own CPU implementation of the training
+step, compiled unmodified by oracle/build_ref.sh and driven through oracle/ref_harness.cpp.  Method names mirror
+myea_b200.net.Net so that a parity test can run the same script against both.
+Only tests/, __graft_entry__.smoke() and the CPU-baseline leg of bench.py may import this module.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+from myea_b200 import capi
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "_ref", "libmyea_ref.so")
+_LIB = None
+
+
+def available():
+    return os.path.exists(LIB_PATH)
+
+
+def _lib():
+    global _LIB
+    if _LIB is None:
+        lib = C.CDLL(LIB_PATH)
+        lib.ref_create.restype = C.c_void_p
+        lib.ref_create.argtypes = [C.POINTER(capi.NetDesc), C.POINTER(capi.OptDesc), C.c_int]
+        lib.ref_destroy.argtypes = [C.c_void_p]
+        lib.ref_threads.argtypes = [C.c_void_p]
+        lib.ref_sizes.argtypes = [C.c_void_p] + [C.POINTER(C.c_uint64)] * 4
+        lib.ref_layer_index.argtypes = [C.c_void_p, C.c_uint32, C.POINTER(capi.LayerIndex)]
+        lib.ref_buffer.restype = C.POINTER(C.c_float)
+        lib.ref_buffer.argtypes = [C.c_void_p, C.c_int]
+        lib.ref_set_mask_bernoulli.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64]
+        lib.ref_set_mask_zoneout.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint64]
+        lib.ref_set_training.argtypes = [C.c_void_p, C.c_int]
+        lib.ref_load_batch.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]
+        lib.ref_run.argtypes = [C.c_void_p, C.c_uint64, C.c_int]
+        lib.ref_merge_derivatives.argtypes = [C.c_void_p]
+        lib.ref_update_parameter.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(capi.OptDesc)]
+        lib.ref_reset_loss.argtypes = [C.c_void_p]
+        lib.ref_get_loss.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_double)]
+        lib.ref_get_outputs.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p]
+        lib.ref_get_errors.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p]
+        lib.ref_time_steps.restype = C.c_double
+        lib.ref_time_steps.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int, C.c_int]
+        _LIB = lib
+    return _LIB
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class RefNet:
+    def __init__(self, desc, opt, threads=1):
+        self.lib = _lib()
+        self.desc, self.opt = desc, opt
+        self.h = self.lib.ref_create(C.byref(desc), C.byref(opt), threads)
+        if not self.h:
+            raise RuntimeError("reference Compile / Set__* failed for this descriptor")
+        self.T = int(desc.number_recurrent_depth)
+        self.B = int(desc.batch_size)
+        self.P, self.W, self.n_bias, self.n_norm = self.sizes()
+        self.threads = self.lib.ref_threads(self.h)
+
+    def close(self):
+        if self.h:
+            self.lib.ref_destroy(self.h)
+            self.h = None
+
+    def sizes(self):
+        v = [C.c_uint64() for _ in range(4)]
+        self.lib.ref_sizes(self.h, *[C.byref(x) for x in v])
+        return tuple(int(x.value) for x in v)
+
+    def layer_index(self, layer):
+        li = capi.LayerIndex()
+        if self.lib.ref_layer_index(self.h, layer, C.byref(li)) != 0:
+            raise RuntimeError("bad layer")
+        return li
+
+    def _buf(self, which, count):
+        p = self.lib.ref_buffer(self.h, which)
+        if not p:
+            raise RuntimeError("reference buffer %d is not allocated" % which)
+        return np.ctypeslib.as_array(p, shape=(count,))
+
+    def _count(self, which):
+        return self.n_norm * self.T if which in (capi.BUF_NORM_MEAN_AVERAGE, capi.BUF_NORM_VARIANCE_AVERAGE) else self.P
+
+    def get(self, which):
+        return self._buf(which, self._count(which)).copy()
+
+    def set(self, which, arr):
+        a = _f32(arr).ravel()
+        self._buf(which, a.size)[:] = a
+
+    def set_mask_bernoulli(self, layer, mask):
+        m = np.ascontiguousarray(mask, dtype=np.uint8).ravel()
+        if self.lib.ref_set_mask_bernoulli(self.h, layer, m.ctypes.data, m.size) != 0:
+            raise RuntimeError("layer %d has no Bernoulli mask" % layer)
+
+    def set_mask_zoneout(self, layer, state, output):
+        s = np.ascontiguousarray(state, dtype=np.uint8).ravel()
+        o = np.ascontiguousarray(output, dtype=np.uint8).ravel()
+        if self.lib.ref_set_mask_zoneout(self.h, layer, s.ctypes.data, o.ctypes.data, s.size) != 0:
+            raise RuntimeError("layer %d has no zoneout mask" % layer)
+
+    def forward(self, X, training=True):
+        X = _f32(X)
+        self.lib.ref_set_training(self.h, 1 if training else 0)
+        self.lib.ref_load_batch(self.h, self.B, X.ctypes.data, None)
+        self.lib.ref_run(self.h, self.B, 1)
+
+    def compute_error(self, Y):
+        Y = _f32(Y)
+        self.lib.ref_load_batch(self.h, self.B, None, Y.ctypes.data)
+        self.lib.ref_run(self.h, self.B, 2)
+
+    def backward(self):
+        self.lib.ref_run(self.h, self.B, 4)
+
+    def update_derivative_weight(self):
+        self.lib.ref_run(self.h, self.B, 8)
+        self.lib.ref_merge_derivatives(self.h)
+
+    def update_parameter(self, training_size=None, opt=None):
+        o = opt or self.opt
+        self.lib.ref_update_parameter(self.h, self.B, training_size or self.B, C.byref(o))
+
+    def reset_loss(self):
+        self.lib.ref_reset_loss(self.h)
+
+    def loss(self):
+        s, n, a = C.c_double(), C.c_uint64(), C.c_double()
+        self.lib.ref_get_loss(self.h, C.byref(s), C.byref(n), C.byref(a))
+        return s.value, int(n.value), a.value
+
+    def outputs(self, layer):
+        w = int(self.layer_index(layer).number_outputs)
+        out = np.empty((self.T, self.B, w), np.float32)
+        self.lib.ref_get_outputs(self.h, layer, self.B, out.ctypes.data)
+        return out
+
+    def errors(self, layer):
+        w = int(self.layer_index(layer).number_outputs)
+        out = np.empty((self.T, self.B, w), np.float32)
+        if self.lib.ref_get_errors(self.h, layer, self.B, out.ctypes.data) != 0:
+            raise RuntimeError("layer %d has no error buffer" % layer)
+        return out
+
+    def time_steps(self, X, Y, warmup, steps, training_size=None):
+        """milliseconds for `steps` whole training steps on (X, Y)"""
+        X, Y = _f32(X), _f32(Y)
+        self.lib.ref_set_training(self.h, 1)
+        self.lib.ref_load_batch(self.h, self.B, X.ctypes.data, Y.ctypes.data)
+        return self.lib.ref_time_steps(self.h, self.B, training_size or self.B, warmup, steps)
