@@ -1,0 +1,161 @@
+// Shared declarations of the sm_100a training-step library: status handling, launch bookkeeping, the
+// activation functions of the reference (Header_Files/Neural_Network/Activation_Functions.hpp:34-183) as device
+// functions, and the interfaces between the translation units.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "myea_b200.h"
+
+namespace myea {
+
+// ---------------------------------------------------------------------------------------------------------
+// Execution context of one handle: stream, error slot written by kernels whose bounded waits ran out,
+// launch counter and optional per-class event timing.
+// ---------------------------------------------------------------------------------------------------------
+enum TimerClass { TC_GEMM = 0, TC_SPLIT = 1, TC_NORM = 2, TC_ELEMENTWISE = 3, TC_OPTIMIZER = 4, TC_RECURRENT = 5, TC_COMM = 6, TC_OTHER = 7 };
+
+struct Context {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  int *d_error_flag = nullptr;  // device int: 0 = fine, otherwise the code of the first kernel that gave up waiting
+  uint64_t launches = 0;
+  bool profiling = false;
+  double class_ms[MYEA_TIMER_CLASSES] = {0};
+  uint64_t class_launches[MYEA_TIMER_CLASSES] = {0};
+  double gemm_flops = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  std::string error;
+  int gemm_engine = 0;  // 0 = tcgen05 3xTF32, 1 = FP32 FMA
+  int gemm_bn = 0;      // forced N tile of the tcgen05 kernel (0 = heuristic)
+
+  void begin(TimerClass) {
+    if (profiling) cudaEventRecord(ev0, stream);
+  }
+  void end(TimerClass c, int n_launch = 1) {
+    launches += n_launch;
+    class_launches[c] += n_launch;
+    if (profiling) {
+      cudaEventRecord(ev1, stream);
+      cudaEventSynchronize(ev1);
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, ev0, ev1);
+      class_ms[c] += ms;
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------------------------------
+// Activation functions, value and derivative, exactly as the reference codes them (steepness 1):
+// tanh is 2/(1+e^-2z)-1 (Activation_Functions.hpp:45), sigmoid 1/(1+e^-z) (:40); the ELU derivative below zero is
+// alpha*y with y = e^z-1 (:93-94), not alpha*e^z; the softmax derivative is 1 (cross-entropy pairing).
+// ---------------------------------------------------------------------------------------------------------
+__host__ __device__ inline float af_fire(uint32_t af, float z) {
+  switch (af) {
+    case MYEA_AF_TANH: return 2.0f / (1.0f + expf(-2.0f * z)) - 1.0f;
+    case MYEA_AF_SIGMOID: return 1.0f / (1.0f + expf(-z));
+    case MYEA_AF_RELU: return z < 0.0f ? 0.0f : z;
+    case MYEA_AF_LEAKY_RELU: return z < 0.0f ? 0.01f * z : z;
+    case MYEA_AF_ELU: return z < 0.0f ? (expf(z) - 1.0f) : z;
+    case MYEA_AF_SELU: return 1.0507009873554804934193349852946f * (z <= 0.0f ? 1.6732632423543772848170429916717f * expf(z) - 1.6732632423543772848170429916717f : z);
+    default: return z;  // linear
+  }
+}
+
+__host__ __device__ inline float af_derive(uint32_t af, float z, float y) {
+  switch (af) {
+    case MYEA_AF_TANH: return 1.0f - y * y;
+    case MYEA_AF_SIGMOID: return y * (1.0f - y);
+    case MYEA_AF_RELU: return z < 0.0f ? 0.0f : 1.0f;
+    case MYEA_AF_LEAKY_RELU: return z < 0.0f ? 0.01f : 1.0f;
+    case MYEA_AF_ELU: return z < 0.0f ? y : 1.0f;
+    case MYEA_AF_SELU: return 1.0507009873554804934193349852946f * (z <= 0.0f ? (y + 1.6732632423543772848170429916717f) : 1.0f);
+    default: return 1.0f;  // linear, softmax
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Dense contraction  C[M,N] (+)= A[M,K] * B[N,K]^T  with a fused epilogue.
+// ---------------------------------------------------------------------------------------------------------
+struct Epilogue {
+  float *C = nullptr;
+  long long ldc = 0;
+  int accumulate = 0;            // C += acc instead of C = acc
+  const float *bias = nullptr;   // [N], added to every row
+  uint32_t deriv_af = 0;         // != 0: result *= f'(pre, y) of this activation
+  const float *aux_pre = nullptr;  // [M,N] pre-activation source (may be null when f' only needs y)
+  const float *aux_y = nullptr;    // [M,N] activation output
+  long long ld_aux = 0;
+  const float *col_scale = nullptr;  // pre = aux_pre * col_scale[n] + col_shift[n] when non-null (normalization folded in)
+  const float *col_shift = nullptr;
+};
+
+// A fp32 matrix operand given by strides: element (r, k) at ptr[r * stride_r + k * stride_k]; one of the two
+// strides is 1.
+struct Operand {
+  const float *ptr = nullptr;
+  long long rows = 0, k = 0;
+  long long stride_r = 0, stride_k = 0;
+};
+
+struct GemmScratch {   // hi/lo K-major panels of both operands, reused by every contraction of a handle
+  float *base = nullptr;
+  size_t floats = 0;
+};
+
+size_t gemm_scratch_floats(long long M, long long N, long long K);
+// Launches split kernels + the tensor-core kernel (engine 0) or the FP32 FMA kernel (engine 1) on ctx.stream.
+int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &epi, const GemmScratch &scratch);
+
+// ---------------------------------------------------------------------------------------------------------
+// Bandwidth-bound kernels (kernels_elementwise.cu, optimizer.cu)
+// ---------------------------------------------------------------------------------------------------------
+struct NormParams {        // one normalized layer
+  uint32_t type = 0;       // MYEA_NORM_*
+  float momentum = 0.999f, epsilon = 1e-5f, r_max = 1.f, d_max = 0.f;
+  const float *gamma = nullptr, *beta = nullptr;   // in the flat parameter buffer
+  float *d_gamma = nullptr, *d_beta = nullptr;     // in the flat derivative buffer
+  float *mean = nullptr, *sigma = nullptr, *r = nullptr, *d = nullptr;  // [H] batch statistics of the last forward
+  float *mean_avg = nullptr, *sigma_avg = nullptr;                      // [H] running averages
+  float *col_scale = nullptr, *col_shift = nullptr;                     // [H] y = z*col_scale + col_shift
+  float *partial = nullptr;  // [2][chunks][H] workspace of the column reductions
+  int chunks = 0;
+};
+
+// z [rows,H] -> batch statistics (training) or running statistics (inference) -> col_scale / col_shift
+int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H, const NormParams &np, int training);
+// out = dropout(f(z*col_scale+col_shift)) ; col_scale null = no normalization. mask: uint8[H] or null; keep_scale = 1/p for inverted dropout
+int activation_forward(Context &ctx, const float *z, float *out, long long rows, long long H, uint32_t af,
+                       const float *col_scale, const float *col_shift, const uint8_t *mask, float keep_scale);
+int softmax_forward(Context &ctx, const float *z, float *out, long long rows, long long H);
+// delta_af [rows,H] (error after the activation derivative) -> error before the normalization, plus d_gamma / d_beta
+int norm_backward(Context &ctx, const float *z, const float *delta_af, float *delta_out, long long rows, long long H,
+                  const NormParams &np);
+// delta = f'(pre,y) * (y - desired); loss / accuracy accumulators (double[2] + uint64) on the device
+int output_error(Context &ctx, const float *pre, const float *y, const float *desired, float *delta, long long rows,
+                 long long H, uint32_t af, uint32_t loss, uint32_t accuracy, float accuracy_variance, double *d_acc,
+                 unsigned long long *d_count);
+// out[j] (+)= sum_rows in[r][j]
+int column_sum(Context &ctx, const float *in, long long rows, long long H, float *out, int accumulate, float *partial,
+               int chunks);
+int fill_zero(Context &ctx, float *p, size_t n);
+
+struct OptLaunch {
+  uint32_t type = 0;
+  float lr_t = 0, beta1 = 0, beta2 = 0, epsilon = 0, weight_decay = 0, lower = 0, upper = 0;
+  float gd_lr = 0, momentum = 0;
+  int nesterov = 0;
+  const float *clip_scale = nullptr;  // device float: multiply the gradient by it first (global-norm clip), may be null
+};
+int optimizer_update(Context &ctx, const OptLaunch &o, float *w, float *g, float *m, float *v, float *vhat,
+                     float *prev_delta, const float *mask, size_t n);
+// d_out[0] = sum g^2 (double)
+int sum_squares(Context &ctx, const float *g, size_t n, double *d_out);
+// clip_scale[0] = norm >= clip ? clip / norm : 1
+int clip_scale_from_norm(Context &ctx, const double *d_sumsq, float clip, float *d_scale);
+
+}  // namespace myea

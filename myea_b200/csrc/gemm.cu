@@ -1,0 +1,550 @@
+// Dense contractions of the training step on Blackwell tensor cores.
+//
+//   C[M,N] (+)= A[M,K] * B[N,K]^T        fp32 in, fp32 out
+//
+// replaces the three scalar triple loops of the reference: Forward_Pass__FC
+// (Neural_Network__Forward_Pass__OpenMP.cpp:4517-4557), Backward_Pass__FC (…Backward_Pass__OpenMP.cpp:1044-1082) and
+// Update_Derivative_Weight__FC (…Update_Derivative_Weight__OpenMP.cpp:178-216), and the LSTM gate products.
+//
+// Precision: 3xTF32.  Every fp32 operand x is split into hi = x with the 13 low mantissa bits cleared (exactly a
+// TF32 number) and lo = x - hi (exact in fp32, at most 13 significant bits), and the tensor core accumulates
+// hi*hi + hi*lo + lo*hi in fp32 in tensor memory; only lo*lo (2^-22 relative) is dropped.
+//
+// Pipeline of one CTA (192 threads, one 128 x BN output tile):
+//   warp 0   : TMA producer - cp.async.bulk.tensor 2D loads of the four K-major panels (A_hi, A_lo, B_hi, B_lo),
+//              128-byte swizzle, 32 floats of K per stage, completing on a per-stage "full" mbarrier
+//   warp 1   : allocates tensor memory, one elected lane issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8) three times
+//              per K step, tcgen05.commit releases the stage ("empty" mbarrier) and finally signals the epilogue
+//   warps 2-5: epilogue - tcgen05.ld of the accumulator (each warp its own 32-lane quarter), transposition through
+//              shared memory so that global accesses are row-contiguous, fused bias / accumulate / activation
+//              derivative, stores
+// Every mbarrier wait is bounded (about one second of SM clock); a wait that runs out sets the handle's error flag
+// and the CTA drains its own copies, frees its tensor memory and returns.
+//
+// The FP32 FMA kernel at the end of the file is the second engine (exact fp32 products; used for tiny shapes whose
+// rows cannot be described to TMA, and selectable for debugging).
+#include "common.cuh"
+
+#include <cudaTypedefs.h>
+#include <stdio.h>
+
+namespace myea {
+
+// ---------------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------------------
+namespace ptx {
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait: gives up after ~2^31 SM cycles (about a second). Returns false on timeout.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > (1ll << 31)) return false;
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_holder, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], TF32 inputs, FP32 accumulate
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns of tensor memory -> 32 registers per thread
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+}  // namespace ptx
+
+// ---------------------------------------------------------------------------------------------------------
+// Descriptors
+// ---------------------------------------------------------------------------------------------------------
+constexpr int BM = 128;       // rows of the output tile = UMMA M = tensor-memory lanes
+constexpr int BK = 32;        // floats of K per pipeline stage = one 128-byte swizzle row
+constexpr int UMMA_K = 8;     // K of one tcgen05.mma.kind::tf32 (32 bytes)
+constexpr int GEMM_THREADS = 192;
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte swizzle TMA
+// wrote it with: start address >> 4 in bits 0-13, leading byte offset (unused for swizzled K-major) bits 16-29,
+// stride byte offset = 1024 B (8 rows) >> 4 in bits 32-45, descriptor version 1 in bits 46-47, layout type
+// SWIZZLE_128B (2) in bits 61-63.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Instruction descriptor of tcgen05.mma.kind::tf32: D format F32 (1) bits 4-5, A and B format TF32 (2) bits 7-9 and
+// 10-12, both operands K-major (bits 15, 16 clear), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc_tf32(int m, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+struct GemmDims {
+  int M, N, K;
+};
+
+// epilogue math for one element
+__device__ __forceinline__ float epilogue_value(const Epilogue &e, float acc, long long m, long long n) {
+  float v = acc;
+  if (e.bias != nullptr) v += e.bias[n];
+  if (e.deriv_af != 0u) {
+    float pre = 0.f, y = 0.f;
+    if (e.aux_pre != nullptr) {
+      pre = e.aux_pre[m * e.ld_aux + n];
+      if (e.col_scale != nullptr) pre = pre * e.col_scale[n] + e.col_shift[n];
+    }
+    if (e.aux_y != nullptr) y = e.aux_y[m * e.ld_aux + n];
+    v *= af_derive(e.deriv_af, pre, y);
+  }
+  if (e.accumulate) v += e.C[m * e.ldc + n];
+  return v;
+}
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack to align the base to 1024 bytes
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
+                           const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
+                           const GemmDims dims, const Epilogue epi, int *error_flag) {
+  using S = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + S::BAR_OFFSET);
+  uint64_t *empty_bar = full_bar + STAGES;
+  uint64_t *tmem_full_bar = empty_bar + STAGES;
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tmem_full_bar + 1);
+
+  // Accumulators in tensor memory (BN fp32 columns each): N_MAIN rotating ones for hi*hi and one for the two
+  // cross terms.  The tensor core truncates when it adds into an accumulator, an error of up to one ulp of the
+  // ACCUMULATOR per tcgen05.mma whatever the size of the addend; keeping the small terms apart and spreading the
+  // dominant products over several accumulators cuts the number of truncating adds per accumulator (12 per stage
+  // down to 4/N_MAIN) and with it the error of a long-K sum.  The epilogue adds them in fp32, round to nearest.
+  constexpr int N_MAIN = (BN == 128) ? 3 : 1;
+  constexpr int TMEM_COLS = 512;
+  static_assert((N_MAIN + 1) * BN <= TMEM_COLS, "accumulators exceed tensor memory");
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM;
+  const int n0 = blockIdx.x * BN;
+  const int num_kb = (dims.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    ptx::mbar_init(tmem_full_bar, 1);
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_holder, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  bool ok = true;
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = static_cast<uint32_t>(kb / STAGES) & 1u;
+        if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u)) { ok = false; break; }
+        uint8_t *st = smem + s * S::STAGE_BYTES;
+        ptx::mbar_arrive_expect_tx(&full_bar[s], S::STAGE_BYTES);
+        ptx::tma_load_2d(st, &tm_a_hi, &full_bar[s], kb * BK, m0);
+        ptx::tma_load_2d(st + S::A_BYTES, &tm_a_lo, &full_bar[s], kb * BK, m0);
+        ptx::tma_load_2d(st + 2 * S::A_BYTES, &tm_b_hi, &full_bar[s], kb * BK, n0);
+        ptx::tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tm_b_lo, &full_bar[s], kb * BK, n0);
+      }
+      if (!ok) atomicCAS(error_flag, 0, 101);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_tf32(BM, BN);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = static_cast<uint32_t>(kb / STAGES) & 1u;
+        if (!ptx::mbar_wait(&full_bar[s], ph)) { ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t st = ptx::smem_u32(smem + s * S::STAGE_BYTES);
+        const uint64_t a_hi = make_smem_desc(st);
+        const uint64_t a_lo = make_smem_desc(st + S::A_BYTES);
+        const uint64_t b_hi = make_smem_desc(st + 2 * S::A_BYTES);
+        const uint64_t b_lo = make_smem_desc(st + 2 * S::A_BYTES + S::B_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint64_t koff = static_cast<uint64_t>((k * UMMA_K * 4) >> 4);  // 32 bytes per K step, in 16-byte units
+          const int step = kb * (BK / UMMA_K) + k;
+          const int main_acc = step % N_MAIN;
+          const uint32_t t_small = tmem_base + static_cast<uint32_t>(N_MAIN * BN);
+          ptx::mma_tf32(t_small, a_lo + koff, b_hi + koff, idesc, step > 0 ? 1u : 0u);
+          ptx::mma_tf32(t_small, a_hi + koff, b_lo + koff, idesc, 1u);
+          ptx::mma_tf32(tmem_base + static_cast<uint32_t>(main_acc * BN), a_hi + koff, b_hi + koff, idesc,
+                        step >= N_MAIN ? 1u : 0u);
+        }
+        ptx::tc_commit(&empty_bar[s]);  // the stage may be refilled once these MMAs have read it
+      }
+      ptx::tc_commit(tmem_full_bar);  // accumulator complete
+      if (!ok) atomicCAS(error_flag, 0, 102);
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5, tensor-memory lane quarter = warp % 4 ----------------
+    const int q = warp & 3;
+    if (!ptx::mbar_wait(tmem_full_bar, 0)) {
+      ok = false;
+      if (lane == 0) atomicCAS(error_flag, 0, 103);
+    }
+    ptx::tc_fence_after();
+    if (ok && num_kb > 0) {
+      // all MMAs are complete, so the pipeline stages are free: use them as the transposition buffer
+      float *tr = reinterpret_cast<float *>(smem) + (warp - 2) * (32 * 33);
+      const long long row_base = static_cast<long long>(m0) + q * 32;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        if (n0 + c >= dims.N) break;
+        uint32_t r[32];
+        float sum[32];
+        const uint32_t t_chunk = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c);
+        ptx::tmem_ld_32x32(t_chunk + static_cast<uint32_t>(N_MAIN * BN), r);  // cross terms first
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum[j] = __uint_as_float(r[j]);
+#pragma unroll
+        for (int a = 0; a < N_MAIN; ++a) {
+          ptx::tmem_ld_32x32(t_chunk + static_cast<uint32_t>(a * BN), r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[j] += __uint_as_float(r[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tr[lane * 33 + j] = sum[j];
+        __syncwarp();
+        const long long n = static_cast<long long>(n0) + c + lane;
+        if (n < dims.N) {
+#pragma unroll 4
+          for (int rr = 0; rr < 32; ++rr) {
+            const long long m = row_base + rr;
+            if (m >= dims.M) break;
+            epi.C[m * epi.ldc + n] = epilogue_value(epi, tr[rr * 33 + lane], m, n);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  // drain: the producer makes sure none of its copies is still in flight before the CTA's shared memory goes away
+  if (warp == 0 && lane == 0) {
+    const int first = num_kb > STAGES ? num_kb - STAGES : 0;
+    for (int kb = first; kb < num_kb; ++kb) {
+      const int s = kb % STAGES;
+      const uint32_t ph = static_cast<uint32_t>(kb / STAGES) & 1u;
+      if (!ptx::mbar_wait(&full_bar[s], ph)) break;
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Operand preparation: fp32 matrix (either stride order) -> K-major hi / lo panels [rows][kp]
+// ---------------------------------------------------------------------------------------------------------
+// Round-to-nearest on both parts: truncation would bias every product the same way and the error of a K-long
+// sum would grow like K instead of sqrt(K).
+__device__ __forceinline__ float round_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+__device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
+  hi = round_tf32(x);
+  lo = round_tf32(x - hi);
+}
+
+// source already K-major (stride_k == 1)
+__global__ void split_rows_kernel(const float *__restrict__ src, long long stride_r, long long rows, long long k, long long kp,
+                                  float *__restrict__ hi, float *__restrict__ lo) {
+  const long long kq = kp >> 2;  // float4 groups per panel row
+  const long long total = rows * kq;
+  const bool vec = ((stride_r & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / kq;
+    const long long c = (i - r * kq) << 2;
+    float v[4];
+    if (vec && c + 3 < k) {
+      const float4 t = *reinterpret_cast<const float4 *>(src + r * stride_r + c);
+      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = (c + j < k) ? src[r * stride_r + c + j] : 0.f;
+    }
+    float4 h, l;
+    split_tf32(v[0], h.x, l.x);
+    split_tf32(v[1], h.y, l.y);
+    split_tf32(v[2], h.z, l.z);
+    split_tf32(v[3], h.w, l.w);
+    *reinterpret_cast<float4 *>(hi + r * kp + c) = h;
+    *reinterpret_cast<float4 *>(lo + r * kp + c) = l;
+  }
+}
+
+// source MN-major (stride_r == 1): tiled transposition, 32x32 tile per block of 32x8 threads
+__global__ void split_transpose_kernel(const float *__restrict__ src, long long stride_k, long long rows, long long k,
+                                       long long kp, float *__restrict__ hi, float *__restrict__ lo) {
+  __shared__ float tile[32][33];
+  const long long r0 = static_cast<long long>(blockIdx.x) * 32;  // panel rows (contiguous in the source)
+  const long long k0 = static_cast<long long>(blockIdx.y) * 32;
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const long long kk = k0 + j, rr = r0 + threadIdx.x;
+    tile[j][threadIdx.x] = (kk < k && rr < rows) ? src[kk * stride_k + rr] : 0.f;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const long long rr = r0 + j, kk = k0 + threadIdx.x;
+    if (rr < rows && kk < kp) {
+      float h, l;
+      split_tf32(tile[threadIdx.x][j], h, l);
+      hi[rr * kp + kk] = h;
+      lo[rr * kp + kk] = l;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// FP32 FMA engine: 64x64 tile, 16 of K per step, 256 threads x (4x4) outputs, arbitrary strides
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gemm_fp32_fma_kernel(const Operand A, const Operand B, const GemmDims dims, const Epilogue epi) {
+  __shared__ float sa[16][64 + 4];
+  __shared__ float sb[16][64 + 4];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const long long m0 = static_cast<long long>(blockIdx.y) * 64, n0 = static_cast<long long>(blockIdx.x) * 64;
+  float acc[4][4] = {};
+  for (long long k0 = 0; k0 < dims.K; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      int r, kk;
+      if (A.stride_k == 1) { r = i >> 4; kk = i & 15; } else { kk = i >> 6; r = i & 63; }
+      const long long m = m0 + r, k = k0 + kk;
+      sa[kk][r] = (m < dims.M && k < dims.K) ? A.ptr[m * A.stride_r + k * A.stride_k] : 0.f;
+      if (B.stride_k == 1) { r = i >> 4; kk = i & 15; } else { kk = i >> 6; r = i & 63; }
+      const long long n = n0 + r;
+      sb[kk][r] = (n < dims.N && k0 + kk < dims.K) ? B.ptr[n * B.stride_r + (k0 + kk) * B.stride_k] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = sa[kk][ty * 4 + i]; b[i] = sb[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const long long m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m < dims.M && n < dims.N) epi.C[m * epi.ldc + n] = epilogue_value(epi, acc[i][j], m, n);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  return fn;
+}
+
+static bool make_panel_map(CUtensorMap *map, const float *panel, long long rows, long long k, long long kp, int box_rows) {
+  PFN_cuTensorMapEncodeTiled_v12000 fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(kp) * 4};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(panel), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
+
+size_t gemm_scratch_floats(long long M, long long N, long long K) {
+  const long long kp = round_up(K, BK);
+  return static_cast<size_t>(2 * (M + N) * kp) + 64;
+}
+
+static int split_operand(Context &ctx, const Operand &op, long long kp, float *hi, float *lo) {
+  if (op.stride_k == 1) {
+    const long long total = op.rows * (kp >> 2);
+    int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
+    if (blocks < 1) blocks = 1;
+    split_rows_kernel<<<blocks, 256, 0, ctx.stream>>>(op.ptr, op.stride_r, op.rows, op.k, kp, hi, lo);
+  } else {
+    dim3 grid(static_cast<unsigned>((op.rows + 31) / 32), static_cast<unsigned>(kp / 32));
+    split_transpose_kernel<<<grid, dim3(32, 8), 0, ctx.stream>>>(op.ptr, op.stride_k, op.rows, op.k, kp, hi, lo);
+  }
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
+template <int BN, int STAGES>
+static int launch_tcgen05(Context &ctx, const CUtensorMap maps[4], const GemmDims &dims, const Epilogue &epi) {
+  using S = GemmSmem<BN, STAGES>;
+  static bool configured[16] = {};
+  if (!configured[ctx.device & 15]) {
+    if (cudaFuncSetAttribute(gemm3x_tf32_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess)
+      return MYEA_E_CUDA;
+    configured[ctx.device & 15] = true;
+  }
+  dim3 grid(static_cast<unsigned>((dims.N + BN - 1) / BN), static_cast<unsigned>((dims.M + BM - 1) / BM));
+  gemm3x_tf32_tcgen05_kernel<BN, STAGES><<<grid, GEMM_THREADS, S::TOTAL, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], dims, epi,
+                                                                                     ctx.d_error_flag);
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
+int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &epi, const GemmScratch &scratch) {
+  GemmDims dims{static_cast<int>(A.rows), static_cast<int>(B.rows), static_cast<int>(A.k)};
+  if (A.k != B.k || dims.M <= 0 || dims.N <= 0 || dims.K <= 0) return MYEA_E_INVALID;
+  const double flops = 2.0 * dims.M * dims.N * static_cast<double>(dims.K);
+  if (ctx.gemm_engine == 1) {
+    ctx.begin(TC_GEMM);
+    dim3 grid(static_cast<unsigned>((dims.N + 63) / 64), static_cast<unsigned>((dims.M + 63) / 64));
+    gemm_fp32_fma_kernel<<<grid, 256, 0, ctx.stream>>>(A, B, dims, epi);
+    ctx.end(TC_GEMM);
+    ctx.gemm_flops += flops;
+    return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+  }
+  const long long kp = round_up(dims.K, BK);
+  if (scratch.base == nullptr || scratch.floats < gemm_scratch_floats(dims.M, dims.N, dims.K)) return MYEA_E_INVALID;
+  float *base = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(scratch.base) + 255) & ~static_cast<uintptr_t>(255));
+  float *a_hi = base, *a_lo = a_hi + dims.M * kp, *b_hi = a_lo + dims.M * kp, *b_lo = b_hi + dims.N * kp;
+  ctx.begin(TC_SPLIT);
+  int rc = split_operand(ctx, A, kp, a_hi, a_lo);
+  if (rc == MYEA_OK) rc = split_operand(ctx, B, kp, b_hi, b_lo);
+  ctx.end(TC_SPLIT, 2);
+  if (rc != MYEA_OK) return rc;
+
+  // N tile: 256 columns unless that leaves SMs idle and 128 fills them better
+  int bn = ctx.gemm_bn;
+  if (bn == 0) {
+    const long long tiles256 = ((dims.N + 255) / 256) * ((dims.M + BM - 1) / BM);
+    (void)tiles256;
+    bn = 128;  // four accumulators of 128 columns: the accurate configuration
+  }
+  CUtensorMap maps[4];
+  bool ok = make_panel_map(&maps[0], a_hi, dims.M, dims.K, kp, BM) && make_panel_map(&maps[1], a_lo, dims.M, dims.K, kp, BM) &&
+            make_panel_map(&maps[2], b_hi, dims.N, dims.K, kp, bn) && make_panel_map(&maps[3], b_lo, dims.N, dims.K, kp, bn);
+  if (!ok) return MYEA_E_CUDA;
+  ctx.begin(TC_GEMM);
+  rc = (bn == 256) ? launch_tcgen05<256, 2>(ctx, maps, dims, epi) : launch_tcgen05<128, 3>(ctx, maps, dims, epi);
+  ctx.end(TC_GEMM);
+  ctx.gemm_flops += flops;
+  return rc;
+}
+
+}  // namespace myea

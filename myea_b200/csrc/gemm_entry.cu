@@ -1,0 +1,70 @@
+// Stand-alone entry point of the dense contraction (host buffers in, host buffers out): used by kernel-level
+// parity tests and by roofline timing of the GEMM alone.
+#include "common.cuh"
+
+#include <stdlib.h>
+#include <vector>
+
+using namespace myea;
+
+extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N, uint64_t K, const float *A, const float *B,
+                                 float *C, int accumulate, float *elapsed_ms, int repeats) {
+  if (A == nullptr || B == nullptr || C == nullptr || M == 0 || N == 0 || K == 0) return MYEA_E_INVALID;
+  if (cudaSetDevice(device) != cudaSuccess) return MYEA_E_CUDA;
+  Context ctx;
+  ctx.device = device;
+  ctx.gemm_engine = engine & 1;
+  ctx.gemm_bn = (engine >> 8) & 0x1FF;  // bits 8..16: forced N tile (0 = heuristic), for tile-shape experiments
+  int rc = MYEA_OK;
+  float *dA = nullptr, *dB = nullptr, *dC = nullptr, *dS = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  const size_t scratch = gemm_scratch_floats(M, N, K);
+  if (cudaStreamCreate(&ctx.stream) != cudaSuccess) return MYEA_E_CUDA;
+  if (cudaMalloc(&dA, M * K * 4) != cudaSuccess || cudaMalloc(&dB, N * K * 4) != cudaSuccess ||
+      cudaMalloc(&dC, M * N * 4) != cudaSuccess || cudaMalloc(&dS, scratch * 4) != cudaSuccess ||
+      cudaMalloc(&ctx.d_error_flag, sizeof(int)) != cudaSuccess) {
+    rc = MYEA_E_CUDA;
+  }
+  if (rc == MYEA_OK) {
+    cudaMemsetAsync(ctx.d_error_flag, 0, sizeof(int), ctx.stream);
+    cudaMemcpyAsync(dA, A, M * K * 4, cudaMemcpyHostToDevice, ctx.stream);
+    cudaMemcpyAsync(dB, B, N * K * 4, cudaMemcpyHostToDevice, ctx.stream);
+    cudaMemcpyAsync(dC, C, M * N * 4, cudaMemcpyHostToDevice, ctx.stream);
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    Operand oa{dA, (long long)M, (long long)K, (long long)K, 1};
+    Operand ob{dB, (long long)N, (long long)K, (long long)K, 1};
+    Epilogue epi;
+    epi.C = dC;
+    epi.ldc = (long long)N;
+    epi.accumulate = accumulate;
+    GemmScratch gs{dS, scratch};
+    rc = gemm_nt(ctx, oa, ob, epi, gs);  // the call whose result is returned
+    if (rc == MYEA_OK && repeats > 0 && elapsed_ms != nullptr) {
+      // timing passes write a second output buffer so that `accumulate` does not pile up in C
+      float *dC2 = nullptr;
+      if (cudaMalloc(&dC2, M * N * 4) == cudaSuccess) {
+        epi.C = dC2;
+        epi.accumulate = 0;
+        gemm_nt(ctx, oa, ob, epi, gs);
+        cudaEventRecord(e0, ctx.stream);
+        for (int i = 0; i < repeats && rc == MYEA_OK; ++i) rc = gemm_nt(ctx, oa, ob, epi, gs);
+        cudaEventRecord(e1, ctx.stream);
+        cudaEventSynchronize(e1);
+        cudaEventElapsedTime(elapsed_ms, e0, e1);
+        *elapsed_ms /= (float)repeats;
+        cudaFree(dC2);
+      }
+    }
+    if (cudaMemcpyAsync(C, dC, M * N * 4, cudaMemcpyDeviceToHost, ctx.stream) != cudaSuccess) rc = MYEA_E_CUDA;
+    int flag = 0;
+    cudaMemcpyAsync(&flag, ctx.d_error_flag, sizeof(int), cudaMemcpyDeviceToHost, ctx.stream);
+    if (cudaStreamSynchronize(ctx.stream) != cudaSuccess) rc = MYEA_E_CUDA;
+    if (rc == MYEA_OK && flag != 0) rc = MYEA_E_KERNEL;
+  }
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  cudaFree(dA); cudaFree(dB); cudaFree(dC); cudaFree(dS); cudaFree(ctx.d_error_flag);
+  cudaStreamDestroy(ctx.stream);
+  return rc;
+}

@@ -1,0 +1,781 @@
+// C ABI of the training step: network construction (index map + device buffers) and the five step functions,
+// one per member function of the reference's `class Neural_Network` that its training loop calls
+// (Dataset.cpp:637-691: Forward_Pass, Compute__Error, Backward_Pass, Update_Derivative_Weight; :7654-7690 Update_Parameter).
+#include "net.cuh"
+
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+
+using namespace myea;
+
+namespace myea {
+// lstm.cu
+int lstm_create(myea_b200_net *net, LayerPlan &L);
+void lstm_destroy(LayerPlan &L);
+int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long n_in);
+int lstm_backward(myea_b200_net *net, LayerPlan &L);
+int lstm_backward_to_input(myea_b200_net *net, LayerPlan &L, float *prev_deriv, const LayerPlan &prev);
+int lstm_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float *input, long long n_in);
+int lstm_set_zoneout(myea_b200_net *net, LayerPlan &L, const uint8_t *state, const uint8_t *output, uint64_t count);
+float *lstm_output_errors(LayerPlan &L);
+// residual.cu
+int residual_forward(myea_b200_net *net, int layer);
+int residual_backward(myea_b200_net *net, int layer);
+// comm.cu
+int comm_all_reduce_sum(myea_b200_net *net, float *buf, size_t n);
+int comm_all_reduce_sum_f64(myea_b200_net *net, double *buf, size_t n);
+void comm_destroy(myea_b200_net *net);
+}  // namespace myea
+
+#define CK(expr)                                                              \
+  do {                                                                        \
+    cudaError_t e__ = (expr);                                                 \
+    if (e__ != cudaSuccess) {                                                 \
+      net->ctx.error = std::string(#expr) + ": " + cudaGetErrorString(e__);   \
+      return MYEA_E_CUDA;                                                     \
+    }                                                                         \
+  } while (0)
+#define RC(expr)                 \
+  do {                           \
+    int rc__ = (expr);           \
+    if (rc__ != MYEA_OK) return rc__; \
+  } while (0)
+
+static int fail(myea_b200_net *net, int code, const char *msg) {
+  net->ctx.error = msg;
+  return code;
+}
+
+template <typename T>
+static int dev_alloc(myea_b200_net *net, T **p, size_t count, bool zero = true) {
+  void *q = nullptr;
+  const size_t bytes = std::max<size_t>(count, 1) * sizeof(T);
+  if (cudaMalloc(&q, bytes) != cudaSuccess) {
+    net->ctx.error = "cudaMalloc failed";
+    return MYEA_E_CUDA;
+  }
+  net->allocations.push_back(q);
+  if (zero && cudaMemsetAsync(q, 0, bytes, net->ctx.stream) != cudaSuccess) return MYEA_E_CUDA;
+  *p = static_cast<T *>(q);
+  return MYEA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Index map: Compile (Neural_Network__Compile.cpp:426-785) -> Prepare__Connections__FC/LSTM, Prepare__Bias__FC/LSTM
+// (Neural_Network__Prepare_Connections.cpp:20-252); normalized-unit slots as Allocate__Normalized_Unit lays them out
+// (Neural_Network__Allocate.cpp:2378-2460): once ANY layer is normalized, gamma for every unit of every layer (input,
+// residual and output layers included) is appended after the biases, then beta for every unit.
+// ---------------------------------------------------------------------------------------------------------
+static int build_index_map(myea_b200_net *net) {
+  const myea_net_desc &d = net->desc;
+  const uint32_t n = d.number_layers;
+  net->layers.assign(n, LayerPlan());
+  // widths
+  for (uint32_t l = 0; l < n; ++l) {
+    LayerPlan &L = net->layers[l];
+    L.desc = d.layers[l];
+    L.type = d.layers[l].type_layer;
+    memset(&L.idx, 0, sizeof(L.idx));
+    switch (L.type) {
+      case MYEA_LAYER_FULLY_CONNECTED: L.n_out = static_cast<long long>(d.layers[l].unit_parameters[0]); break;
+      case MYEA_LAYER_LSTM: {
+        const long long blocks = static_cast<long long>(d.layers[l].unit_parameters[0]);
+        const long long cpb = std::max<long long>(1, static_cast<long long>(d.layers[l].unit_parameters[1]));
+        L.n_out = blocks * cpb;  // per direction; the reference keeps number_outputs at this width even when bidirectional
+        break;
+      }
+      case MYEA_LAYER_RESIDUAL: L.block_depth = static_cast<int>(d.layers[l].unit_parameters[0]); break;
+      default: return fail(net, MYEA_E_UNSUPPORTED, "layer type not built (only fully connected, LSTM, residual)");
+    }
+    if (L.type != MYEA_LAYER_RESIDUAL && L.n_out <= 0) return fail(net, MYEA_E_INVALID, "layer with zero units");
+  }
+  if (net->layers[0].type != MYEA_LAYER_FULLY_CONNECTED || net->layers[n - 1].type != MYEA_LAYER_FULLY_CONNECTED)
+    return fail(net, MYEA_E_INVALID, "input and output layers must be fully connected");
+  // a residual layer's width is the width of the last layer of its block (Assign__Post__Layers, Compile.cpp:222-424)
+  for (uint32_t l = 1; l < n; ++l) {
+    LayerPlan &L = net->layers[l];
+    if (L.type == MYEA_LAYER_RESIDUAL) {
+      if (L.block_depth < 1 || l + L.block_depth >= n) return fail(net, MYEA_E_INVALID, "residual block runs past the output layer");
+      for (int k = 1; k <= L.block_depth; ++k)
+        if (net->layers[l + k].type != MYEA_LAYER_FULLY_CONNECTED) return fail(net, MYEA_E_UNSUPPORTED, "residual blocks of fully connected layers only");
+      L.n_out = net->layers[l + L.block_depth].n_out;
+    }
+  }
+  // inputs: a layer reads the layer before it; the first layer of a residual block reads the layer before the
+  // residual layer, and the layer after a block reads the block's output (held by the residual layer)
+  for (uint32_t l = 1; l < n; ++l) {
+    net->layers[l].input_layer = static_cast<int>(l) - 1;
+    net->layers[l].n_in = net->layers[l - 1].n_out;
+  }
+  for (uint32_t l = 1; l < n; ++l) {
+    LayerPlan &L = net->layers[l];
+    if (L.type != MYEA_LAYER_RESIDUAL) continue;
+    if (net->layers[l - 1].type == MYEA_LAYER_RESIDUAL && false) return fail(net, MYEA_E_INVALID, "unreachable");
+    net->layers[l + 1].input_layer = static_cast<int>(l) - 1;
+    net->layers[l + 1].n_in = net->layers[l - 1].n_out;
+    const uint32_t after = l + L.block_depth + 1;
+    if (after < n) { net->layers[after].input_layer = static_cast<int>(l); net->layers[after].n_in = L.n_out; }
+  }
+  // weights
+  uint64_t tw = 0;
+  for (uint32_t l = 1; l < n; ++l) {
+    LayerPlan &L = net->layers[l];
+    L.idx.number_inputs = L.n_in;
+    L.idx.number_outputs = L.n_out;
+    if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
+      L.idx.first_connection_index = tw;
+      tw += static_cast<uint64_t>(L.n_out) * L.n_in;
+      L.idx.last_connection_index = tw;
+    } else if (L.type == MYEA_LAYER_LSTM) {
+      const uint64_t blocks = L.desc.unit_parameters[0] << (L.desc.use_bidirectional ? 1 : 0);
+      const uint64_t cpb = std::max<uint64_t>(1, L.desc.unit_parameters[1]);
+      const uint64_t cells_dir = L.desc.unit_parameters[0] * cpb;
+      // per block: per cell [W_z,in (in) | W_z,rec (cells)], then W_i,in W_f,in W_o,in (in each), W_i,rec W_f,rec W_o,rec
+      // (cells each), then peepholes p_i p_f p_o (cells per block each)
+      L.idx.block_stride = cpb * (L.n_in + cells_dir) + 3 * L.n_in + 3 * cells_dir + 3 * cpb;
+      L.idx.first_connection_index = tw;
+      tw += blocks * L.idx.block_stride;
+      L.idx.last_connection_index = tw;
+    }
+  }
+  net->layers[0].idx.number_outputs = net->layers[0].n_out;
+  net->total_weights = tw;
+  // biases
+  uint64_t tb = 0;
+  for (uint32_t l = 1; l < n; ++l) {
+    LayerPlan &L = net->layers[l];
+    if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
+      L.idx.first_bias_connection_index = tw + tb;
+      tb += L.n_out;
+      L.idx.last_bias_connection_index = tw + tb;
+    } else if (L.type == MYEA_LAYER_LSTM) {
+      const uint64_t dirs = L.desc.use_bidirectional ? 2 : 1;
+      const uint64_t cells = L.n_out * dirs, blocks = L.desc.unit_parameters[0] * dirs;
+      // Prepare__Bias__LSTM overwrites first_bias_connection_index with (base + cells): the stored range is
+      // [base + cells, base + cells + 3*blocks) although cells + 3*blocks slots are counted.
+      L.idx.first_bias_connection_index = tw + tb + cells;
+      tb += cells + 3 * blocks;
+      L.idx.last_bias_connection_index = tw + tb;
+    }
+  }
+  net->total_bias = tb;
+  net->total_parameters = tw + tb;
+  // normalized units
+  net->any_norm = false;
+  for (uint32_t l = 1; l < n; ++l) net->any_norm = net->any_norm || d.layers[l].type_normalization != MYEA_NORM_NONE;
+  net->total_norm_units = 0;
+  if (net->any_norm) {
+    uint64_t units = 0;
+    for (uint32_t l = 0; l < n; ++l) {
+      net->layers[l].norm_unit_offset = static_cast<long long>(units);
+      if (net->layers[l].type == MYEA_LAYER_LSTM) return fail(net, MYEA_E_UNSUPPORTED, "normalization in a network with LSTM layers is not built");
+      units += net->layers[l].n_out;
+    }
+    net->total_norm_units = units;
+    for (uint32_t l = 0; l < n; ++l) {
+      LayerPlan &L = net->layers[l];
+      L.idx.scale_index = net->total_parameters + L.norm_unit_offset;
+      L.idx.shift_index = net->total_parameters + units + L.norm_unit_offset;
+      L.idx.number_units_norm = L.n_out;
+    }
+    net->total_parameters += 2 * units;
+  }
+  return MYEA_OK;
+}
+
+static bool layer_in_block(const myea_b200_net *net, int l, int *block_layer) {
+  for (int r = 1; r < static_cast<int>(net->layers.size()); ++r)
+    if (net->layers[r].type == MYEA_LAYER_RESIDUAL && l > r && l <= r + net->layers[r].block_depth) {
+      if (block_layer) *block_layer = r;
+      return true;
+    }
+  return false;
+}
+
+static int allocate_buffers(myea_b200_net *net) {
+  const size_t P = net->total_parameters;
+  const long long rows = net->T * net->B;
+  RC(dev_alloc(net, &net->params, P + 4));
+  RC(dev_alloc(net, &net->grads, P + 4));
+  RC(dev_alloc(net, &net->m1, P + 4));
+  RC(dev_alloc(net, &net->m2, P + 4));
+  RC(dev_alloc(net, &net->m2hat, P + 4));
+  RC(dev_alloc(net, &net->prev_delta, P + 4));
+  RC(dev_alloc(net, &net->mask_reg, P + 4));
+  RC(dev_alloc(net, &net->d_loss_acc, 2));
+  RC(dev_alloc(net, &net->d_loss_count, 1));
+  RC(dev_alloc(net, &net->d_sumsq, 1));
+  RC(dev_alloc(net, &net->d_clip_scale, 1));
+  RC(dev_alloc(net, &net->ctx.d_error_flag, 1));
+  RC(dev_alloc(net, &net->d_input, rows * net->layers[0].n_out));
+  RC(dev_alloc(net, &net->d_desired, rows * net->layers.back().n_out));
+  long long max_h = 1;
+  size_t scratch = 0;
+  for (size_t l = 1; l < net->layers.size(); ++l) {
+    LayerPlan &L = net->layers[l];
+    max_h = std::max(max_h, std::max(L.n_out, L.n_in));
+    L.is_output = (l + 1 == net->layers.size());
+    if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
+      L.has_norm = L.desc.type_normalization != MYEA_NORM_NONE;
+      L.use_bias = !L.has_norm;
+      if (L.has_norm && !L.desc.use_layer_normalization_before_activation && !layer_in_block(net, static_cast<int>(l), nullptr))
+        return fail(net, MYEA_E_UNSUPPORTED, "normalization after the activation is not built");
+      RC(dev_alloc(net, &L.summations, rows * L.n_out));
+      RC(dev_alloc(net, &L.values, rows * L.n_out));
+      RC(dev_alloc(net, &L.deriv, rows * L.n_out));
+      if (L.has_norm) RC(dev_alloc(net, &L.errors, rows * L.n_out));
+      else L.errors = L.deriv;
+      scratch = std::max(scratch, gemm_scratch_floats(rows, L.n_out, L.n_in));   // forward
+      scratch = std::max(scratch, gemm_scratch_floats(rows, L.n_in, L.n_out));   // backward data
+      scratch = std::max(scratch, gemm_scratch_floats(L.n_out, L.n_in, rows));   // backward weight
+      if (L.desc.type_dropout == MYEA_DROPOUT_BERNOULLI || L.desc.type_dropout == MYEA_DROPOUT_BERNOULLI_INVERTED) {
+        const float p = L.desc.dropout_values[0];
+        if (!(p > 0.f && p <= 1.f)) return fail(net, MYEA_E_INVALID, "retention probability must be in (0, 1]");
+        RC(dev_alloc(net, &L.mask_bernoulli, net->T * L.n_out));
+        CK(cudaMemsetAsync(L.mask_bernoulli, 1, net->T * L.n_out, net->ctx.stream));
+        // inverted: kept units are scaled by 1/p while training, nothing at inference; plain Bernoulli: no scaling
+        // while training, every unit times p at inference (…Forward_Pass__OpenMP.cpp:4907-4990)
+        L.keep_scale = L.desc.type_dropout == MYEA_DROPOUT_BERNOULLI_INVERTED ? 1.0f / p : 1.0f;
+        L.infer_scale = L.desc.type_dropout == MYEA_DROPOUT_BERNOULLI ? p : 1.0f;
+      }
+    } else if (L.type == MYEA_LAYER_LSTM) {
+      RC(lstm_create(net, L));
+    } else if (L.type == MYEA_LAYER_RESIDUAL) {
+      RC(dev_alloc(net, &L.values, rows * L.n_out));
+      RC(dev_alloc(net, &L.deriv, rows * L.n_out));
+      L.errors = L.deriv;
+      if (L.desc.type_dropout == MYEA_DROPOUT_SHAKEDROP) {
+        RC(dev_alloc(net, &L.shake_mask, net->B));
+        RC(dev_alloc(net, &L.shake_alpha, net->B * L.n_out));
+        RC(dev_alloc(net, &L.shake_beta, net->B * L.n_out));
+      }
+    }
+  }
+  net->layers[0].values = net->d_input;
+  // normalization state
+  if (net->any_norm) {
+    const size_t U = net->total_norm_units;
+    RC(dev_alloc(net, &net->norm_mean_avg, U));
+    RC(dev_alloc(net, &net->norm_sigma_avg, U));
+    RC(dev_alloc(net, &net->norm_stats, U * 6));
+    RC(dev_alloc(net, &net->norm_partial, static_cast<size_t>(2 * net->reduce_chunks + 3) * max_h));
+    for (size_t l = 1; l < net->layers.size(); ++l) {
+      LayerPlan &L = net->layers[l];
+      if (!L.has_norm) continue;
+      NormParams &np = L.norm;
+      np.type = L.desc.type_normalization;
+      np.momentum = net->desc.normalization_momentum_average > 0.f ? net->desc.normalization_momentum_average : 0.999f;
+      np.epsilon = net->desc.normalization_epsilon > 0.f ? net->desc.normalization_epsilon : 1e-5f;
+      np.r_max = net->desc.batch_renormalization_r_correction_maximum > 0.f ? net->desc.batch_renormalization_r_correction_maximum : 1.f;
+      np.d_max = net->desc.batch_renormalization_d_correction_maximum > 0.f ? net->desc.batch_renormalization_d_correction_maximum : 0.f;
+      np.gamma = net->params + L.idx.scale_index;
+      np.beta = net->params + L.idx.shift_index;
+      np.d_gamma = net->grads + L.idx.scale_index;
+      np.d_beta = net->grads + L.idx.shift_index;
+      const size_t o = L.norm_unit_offset;
+      np.mean_avg = net->norm_mean_avg + o;
+      np.sigma_avg = net->norm_sigma_avg + o;
+      np.mean = net->norm_stats + 0 * U + o;
+      np.sigma = net->norm_stats + 1 * U + o;
+      np.r = net->norm_stats + 2 * U + o;
+      np.d = net->norm_stats + 3 * U + o;
+      np.col_scale = net->norm_stats + 4 * U + o;
+      np.col_shift = net->norm_stats + 5 * U + o;
+      np.partial = net->norm_partial;
+      np.chunks = net->reduce_chunks;
+    }
+  }
+  RC(dev_alloc(net, &net->reduce_partial, static_cast<size_t>(net->reduce_chunks) * max_h));
+  net->scratch.floats = scratch + 64;
+  RC(dev_alloc(net, &net->scratch.base, net->scratch.floats, false));
+  return MYEA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// create / destroy / queries
+// ---------------------------------------------------------------------------------------------------------
+extern "C" int myea_b200_create(myea_handle *out, const myea_net_desc *desc, int device) {
+  if (out == nullptr || desc == nullptr) return MYEA_E_INVALID;
+  *out = nullptr;
+  if (desc->number_layers < 2 || desc->number_layers > MYEA_MAX_LAYERS || desc->batch_size == 0 || desc->number_recurrent_depth == 0)
+    return MYEA_E_INVALID;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) return MYEA_E_CUDA;  // no GPU: fail loudly, there is no CPU path
+  if (device < 0 || device >= count) return MYEA_E_INVALID;
+  if (cudaSetDevice(device) != cudaSuccess) return MYEA_E_CUDA;
+  myea_b200_net *net = new (std::nothrow) myea_b200_net();
+  if (net == nullptr) return MYEA_E_INVALID;
+  net->desc = *desc;
+  net->ctx.device = device;
+  net->T = static_cast<long long>(desc->number_recurrent_depth);
+  net->B = static_cast<long long>(desc->batch_size);
+  const char *eng = getenv("MYEA_B200_GEMM_ENGINE");
+  if (eng != nullptr && eng[0] == '1') net->ctx.gemm_engine = 1;
+  *out = net;  // returned even on failure so that the caller can read last_error, then destroy
+  if (cudaStreamCreateWithFlags(&net->ctx.stream, cudaStreamNonBlocking) != cudaSuccess) return fail(net, MYEA_E_CUDA, "cudaStreamCreate failed");
+  cudaEventCreate(&net->ctx.ev0);
+  cudaEventCreate(&net->ctx.ev1);
+  RC(build_index_map(net));
+  RC(allocate_buffers(net));
+  CK(cudaStreamSynchronize(net->ctx.stream));
+  return MYEA_OK;
+}
+
+extern "C" void myea_b200_destroy(myea_handle net) {
+  if (net == nullptr) return;
+  cudaSetDevice(net->ctx.device);
+  if (net->ctx.stream) cudaStreamSynchronize(net->ctx.stream);
+  comm_destroy(net);
+  for (auto &L : net->layers) lstm_destroy(L);
+  for (void *p : net->allocations) cudaFree(p);
+  if (net->ctx.ev0) cudaEventDestroy(net->ctx.ev0);
+  if (net->ctx.ev1) cudaEventDestroy(net->ctx.ev1);
+  if (net->ctx.stream) cudaStreamDestroy(net->ctx.stream);
+  delete net;
+}
+
+extern "C" const char *myea_b200_last_error(myea_handle net) { return net ? net->ctx.error.c_str() : "null handle"; }
+
+extern "C" int myea_b200_sizes(myea_handle net, uint64_t *P, uint64_t *W, uint64_t *bias, uint64_t *norm_units) {
+  if (net == nullptr) return MYEA_E_INVALID;
+  if (P) *P = net->total_parameters;
+  if (W) *W = net->total_weights;
+  if (bias) *bias = net->total_bias;
+  if (norm_units) *norm_units = net->total_norm_units;
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_layer_index(myea_handle net, uint32_t layer, myea_layer_index *out) {
+  if (net == nullptr || out == nullptr || layer >= net->layers.size()) return MYEA_E_INVALID;
+  *out = net->layers[layer].idx;
+  return MYEA_OK;
+}
+
+static float *select_buffer(myea_b200_net *net, int which, size_t *count) {
+  *count = net->total_parameters;
+  switch (which) {
+    case MYEA_BUF_PARAMETERS: return net->params;
+    case MYEA_BUF_DERIVATIVES: return net->grads;
+    case MYEA_BUF_FIRST_MOMENT: return net->m1;
+    case MYEA_BUF_SECOND_MOMENT: return net->m2;
+    case MYEA_BUF_SECOND_MOMENT_HAT: return net->m2hat;
+    case MYEA_BUF_MASK_REGULARIZED: return net->mask_reg;
+    case MYEA_BUF_PREVIOUS_DELTA: return net->prev_delta;
+    case MYEA_BUF_NORM_MEAN_AVERAGE: *count = net->total_norm_units; return net->norm_mean_avg;
+    case MYEA_BUF_NORM_VARIANCE_AVERAGE: *count = net->total_norm_units; return net->norm_sigma_avg;
+    default: *count = 0; return nullptr;
+  }
+}
+
+extern "C" int myea_b200_upload(myea_handle net, int which, const float *host, uint64_t offset, uint64_t count) {
+  if (net == nullptr || host == nullptr) return MYEA_E_INVALID;
+  size_t n = 0;
+  float *dst = select_buffer(net, which, &n);
+  if (dst == nullptr || offset + count > n) return fail(net, MYEA_E_INVALID, "upload: buffer selector or range out of bounds");
+  CK(cudaSetDevice(net->ctx.device));
+  CK(cudaMemcpyAsync(dst + offset, host, count * sizeof(float), cudaMemcpyHostToDevice, net->ctx.stream));
+  CK(cudaStreamSynchronize(net->ctx.stream));
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_download(myea_handle net, int which, float *host, uint64_t offset, uint64_t count) {
+  if (net == nullptr || host == nullptr) return MYEA_E_INVALID;
+  size_t n = 0;
+  float *src = select_buffer(net, which, &n);
+  if (src == nullptr || offset + count > n) return fail(net, MYEA_E_INVALID, "download: buffer selector or range out of bounds");
+  CK(cudaSetDevice(net->ctx.device));
+  CK(cudaMemcpyAsync(host, src + offset, count * sizeof(float), cudaMemcpyDeviceToHost, net->ctx.stream));
+  CK(cudaStreamSynchronize(net->ctx.stream));
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_set_mask_bernoulli(myea_handle net, uint32_t layer, const uint8_t *mask, uint64_t count) {
+  if (net == nullptr || mask == nullptr || layer >= net->layers.size()) return MYEA_E_INVALID;
+  LayerPlan &L = net->layers[layer];
+  if (L.mask_bernoulli == nullptr || count != static_cast<uint64_t>(net->T * L.n_out)) return fail(net, MYEA_E_INVALID, "layer has no Bernoulli mask of that size");
+  CK(cudaMemcpyAsync(L.mask_bernoulli, mask, count, cudaMemcpyHostToDevice, net->ctx.stream));
+  CK(cudaStreamSynchronize(net->ctx.stream));
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_set_mask_zoneout(myea_handle net, uint32_t layer, const uint8_t *mask_state, const uint8_t *mask_output,
+                                          uint64_t count) {
+  if (net == nullptr || mask_state == nullptr || mask_output == nullptr || layer >= net->layers.size()) return MYEA_E_INVALID;
+  LayerPlan &L = net->layers[layer];
+  if (L.type != MYEA_LAYER_LSTM) return fail(net, MYEA_E_INVALID, "zoneout masks belong to LSTM layers");
+  return lstm_set_zoneout(net, L, mask_state, mask_output, count);
+}
+
+extern "C" int myea_b200_set_shakedrop(myea_handle net, uint32_t layer, const uint8_t *mask, const float *alpha, const float *beta,
+                                       uint64_t batch) {
+  if (net == nullptr || mask == nullptr || alpha == nullptr || beta == nullptr || layer >= net->layers.size()) return MYEA_E_INVALID;
+  LayerPlan &L = net->layers[layer];
+  if (L.shake_mask == nullptr || batch != static_cast<uint64_t>(net->B)) return fail(net, MYEA_E_INVALID, "layer has no ShakeDrop state of that batch size");
+  CK(cudaMemcpyAsync(L.shake_mask, mask, batch, cudaMemcpyHostToDevice, net->ctx.stream));
+  CK(cudaMemcpyAsync(L.shake_alpha, alpha, batch * L.n_out * sizeof(float), cudaMemcpyHostToDevice, net->ctx.stream));
+  CK(cudaMemcpyAsync(L.shake_beta, beta, batch * L.n_out * sizeof(float), cudaMemcpyHostToDevice, net->ctx.stream));
+  CK(cudaStreamSynchronize(net->ctx.stream));
+  return MYEA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Forward pass
+// ---------------------------------------------------------------------------------------------------------
+namespace myea {
+
+// One fully connected layer on `rows` rows: z = x W^T (+ b); normalization statistics; activation; dropout.
+// Forward_Pass__FC (Neural_Network__Forward_Pass__Loop.cpp:350-790 is the per-layer driver).
+int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long rows) {
+  Operand a{input, rows, L.n_in, L.n_in, 1};
+  Operand b{net->params + L.idx.first_connection_index, L.n_out, L.n_in, L.n_in, 1};
+  Epilogue e;
+  e.C = L.summations;
+  e.ldc = L.n_out;
+  e.bias = L.use_bias ? net->params + L.idx.first_bias_connection_index : nullptr;
+  RC(gemm_nt(net->ctx, a, b, e, net->scratch));
+  const float *cs = nullptr, *ch = nullptr;
+  if (L.has_norm) {
+    RC(norm_forward_stats(net->ctx, L.summations, rows, L.n_out, L.norm, net->training ? 1 : 0));
+    cs = L.norm.col_scale;
+    ch = L.norm.col_shift;
+  }
+  if (L.desc.type_activation_function == MYEA_AF_SOFTMAX) {
+    if (L.has_norm) return MYEA_E_UNSUPPORTED;
+    return softmax_forward(net->ctx, L.summations, L.values, rows, L.n_out);
+  }
+  const uint8_t *mask = (net->training && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
+  float scale = net->training ? L.keep_scale : L.infer_scale;
+  if (!net->training && L.mask_bernoulli != nullptr && L.infer_scale != 1.f) {
+    // plain Bernoulli at inference: every unit times the retention probability; expressed as an all-ones mask
+    mask = nullptr;
+  }
+  RC(activation_forward(net->ctx, L.summations, L.values, rows, L.n_out, L.desc.type_activation_function, cs, ch, mask, scale));
+  return MYEA_OK;
+}
+
+}  // namespace myea
+
+static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cudaMemcpyKind kind, int training) {
+  if (net == nullptr || src == nullptr) return MYEA_E_INVALID;
+  if (static_cast<long long>(batch) != net->B) return fail(net, MYEA_E_INVALID, "batch must equal the batch size the network was created for");
+  CK(cudaSetDevice(net->ctx.device));
+  net->training = training != 0;
+  const long long rows = net->T * net->B;
+  CK(cudaMemcpyAsync(net->d_input, src, rows * net->layers[0].n_out * sizeof(float), kind, net->ctx.stream));
+  const int n = static_cast<int>(net->layers.size());
+  for (int l = 1; l < n;) {
+    LayerPlan &L = net->layers[l];
+    const LayerPlan &in = net->layers[L.input_layer];
+    if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
+      if (net->T > 1 && L.mask_bernoulli != nullptr) return fail(net, MYEA_E_UNSUPPORTED, "Bernoulli dropout on a recurrent network is not built");
+      RC(fc_forward(net, L, in.values, rows));
+      ++l;
+    } else if (L.type == MYEA_LAYER_LSTM) {
+      RC(lstm_forward(net, L, in.values, L.n_in));
+      ++l;
+    } else {  // residual block: consumes layers l+1 .. l+depth
+      RC(residual_forward(net, l));
+      l += L.block_depth + 1;
+    }
+  }
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_forward(myea_handle net, uint64_t batch, const float *inputs, int training) {
+  return forward_impl(net, batch, inputs, cudaMemcpyHostToDevice, training);
+}
+extern "C" int myea_b200_forward_device(myea_handle net, uint64_t batch, const float *inputs, int training) {
+  return forward_impl(net, batch, inputs, cudaMemcpyDeviceToDevice, training);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Output error
+// ---------------------------------------------------------------------------------------------------------
+static int compute_error_impl(myea_b200_net *net, uint64_t batch, const float *src, cudaMemcpyKind kind) {
+  if (net == nullptr || src == nullptr) return MYEA_E_INVALID;
+  if (static_cast<long long>(batch) != net->B) return fail(net, MYEA_E_INVALID, "batch must equal the batch size the network was created for");
+  CK(cudaSetDevice(net->ctx.device));
+  LayerPlan &L = net->layers.back();
+  const long long rows = net->T * net->B;
+  CK(cudaMemcpyAsync(net->d_desired, src, rows * L.n_out * sizeof(float), kind, net->ctx.stream));
+  // Recurrent networks only score the steps t >= number_time_delays; earlier steps get a zero error
+  // (RNN__Compute__Error, Neural_Network__Recurrent_Compute__Error__OpenMP.cpp:22-159).
+  const long long t0 = net->T > 1 ? std::min<long long>(static_cast<long long>(net->desc.number_time_delays), net->T) : 0;
+  const long long skip = t0 * net->B;
+  if (skip > 0) RC(fill_zero(net->ctx, L.errors, skip * L.n_out));
+  if (rows > skip) {
+    const size_t off = static_cast<size_t>(skip) * L.n_out;
+    RC(output_error(net->ctx, L.summations + off, L.values + off, net->d_desired + off, L.errors + off, rows - skip, L.n_out,
+                    L.desc.type_activation_function, net->desc.type_loss_function, net->desc.type_accuracy_function,
+                    net->desc.accuracy_variance > 0.f ? net->desc.accuracy_variance : 0.49f, net->d_loss_acc, net->d_loss_count));
+  }
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_compute_error(myea_handle net, uint64_t batch, const float *desired) {
+  return compute_error_impl(net, batch, desired, cudaMemcpyHostToDevice);
+}
+extern "C" int myea_b200_compute_error_device(myea_handle net, uint64_t batch, const float *desired) {
+  return compute_error_impl(net, batch, desired, cudaMemcpyDeviceToDevice);
+}
+
+extern "C" int myea_b200_reset_loss(myea_handle net) {
+  if (net == nullptr) return MYEA_E_INVALID;
+  CK(cudaMemsetAsync(net->d_loss_acc, 0, 2 * sizeof(double), net->ctx.stream));
+  CK(cudaMemsetAsync(net->d_loss_count, 0, sizeof(unsigned long long), net->ctx.stream));
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_get_loss(myea_handle net, double *loss_sum, uint64_t *number_loss, double *accuracy_sum) {
+  if (net == nullptr) return MYEA_E_INVALID;
+  double acc[2] = {0, 0};
+  unsigned long long cnt = 0;
+  CK(cudaMemcpyAsync(acc, net->d_loss_acc, sizeof(acc), cudaMemcpyDeviceToHost, net->ctx.stream));
+  CK(cudaMemcpyAsync(&cnt, net->d_loss_count, sizeof(cnt), cudaMemcpyDeviceToHost, net->ctx.stream));
+  CK(cudaStreamSynchronize(net->ctx.stream));
+  if (loss_sum) *loss_sum = acc[0];
+  if (accuracy_sum) *accuracy_sum = acc[1];
+  if (number_loss) *number_loss = cnt;
+  return MYEA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Backward pass: error propagation, last hidden layer -> first hidden layer
+// FF__Backward_Pass_Batch (Neural_Network__Backward_Pass__OpenMP.cpp:24-155), RNN__ (…Recurrent_Backward_Pass__OpenMP.cpp:24-181)
+// ---------------------------------------------------------------------------------------------------------
+namespace myea {
+
+// error arriving on layer `L`'s outputs from the fully connected layer `next`:  D = delta_next * W_next, with the
+// activation derivative of L fused into the epilogue when L is fully connected (Backward_Pass__FC :1044-1082 followed
+// by Backward_Pass__FC__DF :1225-1263), then the normalization backward (:1346-1709).
+int fc_backward_from_fc(myea_b200_net *net, LayerPlan &L, const LayerPlan &next, const float *next_errors, long long rows,
+                        float *dst, bool fuse_derivative) {
+  Operand a{next_errors, rows, next.n_out, next.n_out, 1};
+  Operand b{net->params + next.idx.first_connection_index, next.n_in, next.n_out, 1, next.n_in};  // W[out,in] read as [in rows, K=out]
+  Epilogue e;
+  e.C = dst;
+  e.ldc = next.n_in;
+  if (fuse_derivative) {
+    e.deriv_af = L.desc.type_activation_function;
+    e.aux_pre = L.summations;
+    e.aux_y = L.values;
+    e.ld_aux = L.n_out;
+    if (L.has_norm) { e.col_scale = L.norm.col_scale; e.col_shift = L.norm.col_shift; }
+  }
+  return gemm_nt(net->ctx, a, b, e, net->scratch);
+}
+
+int fc_finish_backward(myea_b200_net *net, LayerPlan &L, long long rows) {
+  if (L.has_norm) return norm_backward(net->ctx, L.summations, L.deriv, L.errors, rows, L.n_out, L.norm);
+  return MYEA_OK;
+}
+
+}  // namespace myea
+
+extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
+  if (net == nullptr) return MYEA_E_INVALID;
+  if (static_cast<long long>(batch) != net->B) return fail(net, MYEA_E_INVALID, "batch must equal the batch size the network was created for");
+  if (!net->training) return fail(net, MYEA_E_INVALID, "can not back propagate in inference mode");
+  CK(cudaSetDevice(net->ctx.device));
+  const long long rows = net->T * net->B;
+  const int n = static_cast<int>(net->layers.size());
+  // walk the consumers: `l` is the layer whose error is known, `p` the layer feeding it
+  int l = n - 1;
+  while (l > 1) {
+    LayerPlan &N = net->layers[l];
+    const int p = N.input_layer;
+    if (p < 1) break;
+    LayerPlan &P = net->layers[p];
+    if (N.type != MYEA_LAYER_FULLY_CONNECTED && N.type != MYEA_LAYER_LSTM) return fail(net, MYEA_E_INVALID, "unexpected consumer layer");
+    if (P.type == MYEA_LAYER_FULLY_CONNECTED) {
+      if (N.type == MYEA_LAYER_FULLY_CONNECTED) RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, true));
+      else return fail(net, MYEA_E_UNSUPPORTED, "a fully connected hidden layer below an LSTM layer is not built");
+      RC(fc_finish_backward(net, P, rows));
+      l = p;
+    } else if (P.type == MYEA_LAYER_LSTM) {
+      float *dh = lstm_output_errors(P);
+      if (N.type == MYEA_LAYER_FULLY_CONNECTED) RC(fc_backward_from_fc(net, P, N, N.errors, rows, dh, false));
+      else RC(lstm_backward_to_input(net, N, dh, P));
+      RC(lstm_backward(net, P));
+      l = p;
+    } else {  // residual block feeding N
+      if (N.type != MYEA_LAYER_FULLY_CONNECTED) return fail(net, MYEA_E_UNSUPPORTED, "residual block below an LSTM layer is not built");
+      RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, false));
+      RC(residual_backward(net, p));
+      l = p;  // the residual layer now stands for its block; its input layer is the one before the block
+      // error for the layer feeding the block has been written by residual_backward; continue from that layer
+      l = P.input_layer + 0;
+      if (l >= 1 && net->layers[l].type == MYEA_LAYER_RESIDUAL) continue;
+      // a fully connected layer feeding the block: its error is final after residual_backward
+    }
+  }
+  return MYEA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Derivative-weight accumulation
+// Update_Derivative_Weight__FC (Neural_Network__Update_Derivative_Weight__OpenMP.cpp:178-216) + bias (:218-242)
+// ---------------------------------------------------------------------------------------------------------
+namespace myea {
+int fc_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float *input, long long rows) {
+  Operand a{L.errors, L.n_out, rows, 1, L.n_out};  // delta^T: [out rows, K = batch]
+  Operand b{input, L.n_in, rows, 1, L.n_in};       // input^T: [in rows, K = batch]
+  Epilogue e;
+  e.C = net->grads + L.idx.first_connection_index;
+  e.ldc = L.n_in;
+  e.accumulate = 1;
+  RC(gemm_nt(net->ctx, a, b, e, net->scratch));
+  if (L.use_bias)
+    RC(column_sum(net->ctx, L.errors, rows, L.n_out, net->grads + L.idx.first_bias_connection_index, 1, net->reduce_partial, net->reduce_chunks));
+  return MYEA_OK;
+}
+}  // namespace myea
+
+extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batch) {
+  if (net == nullptr) return MYEA_E_INVALID;
+  if (static_cast<long long>(batch) != net->B) return fail(net, MYEA_E_INVALID, "batch must equal the batch size the network was created for");
+  CK(cudaSetDevice(net->ctx.device));
+  const long long rows = net->T * net->B;
+  // last layer first: its bucket is ready first when a communicator overlaps the reduction
+  for (int l = static_cast<int>(net->layers.size()) - 1; l >= 1; --l) {
+    LayerPlan &L = net->layers[l];
+    if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
+      const float *input = net->layers[L.input_layer].values;
+      int blk = 0;
+      if (layer_in_block(net, l, &blk)) {
+        // inside a residual block the layer's input is the normalized / activated copy kept by the block
+        // (Layer::ptr_array_pre_summations): residual.cu stores it in the previous slot's `deriv`-independent buffer
+        input = net->layers[l].block_out_errors != nullptr ? reinterpret_cast<const float *>(net->layers[l].block_out_errors) : input;
+      }
+      RC(fc_update_derivative_weight(net, L, input, rows));
+    } else if (L.type == MYEA_LAYER_LSTM) {
+      RC(lstm_update_derivative_weight(net, L, net->layers[L.input_layer].values, L.n_in));
+    }
+  }
+  return MYEA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Parameter update: merge across GPUs, clip, optimizer, zero the derivatives
+// Update_Parameter (Neural_Network.cpp:4719-4900)
+// ---------------------------------------------------------------------------------------------------------
+extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint64_t training_size, const myea_opt_desc *opt) {
+  if (net == nullptr || opt == nullptr || training_size == 0) return MYEA_E_INVALID;
+  CK(cudaSetDevice(net->ctx.device));
+  const size_t P = net->total_parameters;
+  if (net->comm != nullptr) RC(comm_all_reduce_sum(net, net->grads, P));
+  OptLaunch o;
+  o.type = opt->type_optimizer_function;
+  if (opt->use_clip_gradient) {
+    RC(sum_squares(net->ctx, net->grads, P, net->d_sumsq));
+    RC(clip_scale_from_norm(net->ctx, net->d_sumsq, opt->clip_gradient, net->d_clip_scale));
+    o.clip_scale = net->d_clip_scale;
+  }
+  net->optimizer_time_step += 1.f;
+  const float t = net->optimizer_time_step;
+  // decoupled weight decay, "normalized" by default (Train.cpp:284-286); fp32 arithmetic as the reference
+  float wd = opt->regularization__weight_decay;
+  if (wd != 0.f && opt->use_normalized_weight_decay)
+    wd = wd * sqrtf(static_cast<float>(batch) / (static_cast<float>(training_size) * (opt->epoch_time_step > 0.f ? opt->epoch_time_step : 1.f)));
+  o.weight_decay = wd;
+  switch (o.type) {
+    case MYEA_OPT_ADAM:
+    case MYEA_OPT_AMSGRAD:
+    case MYEA_OPT_ADABOUND:
+    case MYEA_OPT_AMSBOUND: {
+      o.beta1 = opt->adam_beta1;
+      o.beta2 = opt->adam_beta2;
+      o.epsilon = opt->adam_epsilon;
+      const float lr = opt->adam_learning_rate;
+      o.lr_t = opt->use_adam_bias_correction ? lr * sqrtf(1.f - powf(o.beta2, t)) / (1.f - powf(o.beta1, t)) : lr;
+      o.lower = opt->learning_rate_final * (1.f - 1.f / (opt->learning_gamma * t + 1.f));
+      o.upper = opt->learning_rate_final * (1.f + 1.f / (opt->learning_gamma * t));
+      break;
+    }
+    case MYEA_OPT_GD:
+      o.gd_lr = opt->learning_rate;
+      o.momentum = opt->learning_momentum;
+      o.nesterov = opt->use_nesterov != 0;
+      break;
+    default: return fail(net, MYEA_E_UNSUPPORTED, "optimizer not built (Adam, AMSGrad, AdaBound, AMSBound, gradient descent / momentum / Nesterov)");
+  }
+  RC(optimizer_update(net->ctx, o, net->params, net->grads, net->m1, net->m2, net->m2hat, net->prev_delta, net->mask_reg, P));
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_clear_training_arrays(myea_handle net) {
+  if (net == nullptr) return MYEA_E_INVALID;
+  const size_t bytes = (net->total_parameters + 4) * sizeof(float);
+  CK(cudaMemsetAsync(net->grads, 0, bytes, net->ctx.stream));
+  CK(cudaMemsetAsync(net->m1, 0, bytes, net->ctx.stream));
+  CK(cudaMemsetAsync(net->m2, 0, bytes, net->ctx.stream));
+  CK(cudaMemsetAsync(net->m2hat, 0, bytes, net->ctx.stream));
+  CK(cudaMemsetAsync(net->prev_delta, 0, bytes, net->ctx.stream));
+  net->optimizer_time_step = 0.f;
+  return MYEA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Read-back helpers, synchronisation, profiling
+// ---------------------------------------------------------------------------------------------------------
+static int copy_out(myea_b200_net *net, const float *src, size_t have, float *host, uint64_t count) {
+  if (src == nullptr || count > have) return fail(net, MYEA_E_INVALID, "layer has no such buffer, or count too large");
+  CK(cudaMemcpyAsync(host, src, count * sizeof(float), cudaMemcpyDeviceToHost, net->ctx.stream));
+  CK(cudaStreamSynchronize(net->ctx.stream));
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_get_outputs(myea_handle net, uint32_t layer, float *host, uint64_t count) {
+  if (net == nullptr || host == nullptr || layer >= net->layers.size()) return MYEA_E_INVALID;
+  LayerPlan &L = net->layers[layer];
+  return copy_out(net, L.values, static_cast<size_t>(net->T * net->B * L.n_out), host, count);
+}
+
+extern "C" int myea_b200_get_errors(myea_handle net, uint32_t layer, float *host, uint64_t count) {
+  if (net == nullptr || host == nullptr || layer >= net->layers.size() || layer == 0) return MYEA_E_INVALID;
+  LayerPlan &L = net->layers[layer];
+  const float *src = L.type == MYEA_LAYER_LSTM ? lstm_output_errors(L) : L.errors;
+  return copy_out(net, src, static_cast<size_t>(net->T * net->B * L.n_out), host, count);
+}
+
+extern "C" int myea_b200_synchronize(myea_handle net) {
+  if (net == nullptr) return MYEA_E_INVALID;
+  CK(cudaSetDevice(net->ctx.device));
+  int flag = 0;
+  CK(cudaMemcpyAsync(&flag, net->ctx.d_error_flag, sizeof(int), cudaMemcpyDeviceToHost, net->ctx.stream));
+  CK(cudaStreamSynchronize(net->ctx.stream));
+  if (flag != 0) {
+    char msg[96];
+    snprintf(msg, sizeof(msg), "a kernel gave up a bounded wait (code %d)", flag);
+    return fail(net, MYEA_E_KERNEL, msg);
+  }
+  return MYEA_OK;
+}
+
+extern "C" void *myea_b200_stream(myea_handle net) { return net ? net->ctx.stream : nullptr; }
+extern "C" uint64_t myea_b200_kernel_launches(myea_handle net) { return net ? net->ctx.launches : 0; }
+
+extern "C" int myea_b200_profile(myea_handle net, int enable) {
+  if (net == nullptr) return MYEA_E_INVALID;
+  net->ctx.profiling = enable != 0;
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_profile_read(myea_handle net, double ms[MYEA_TIMER_CLASSES], uint64_t launches[MYEA_TIMER_CLASSES],
+                                      double gemm_flops[1], int reset) {
+  if (net == nullptr) return MYEA_E_INVALID;
+  for (int i = 0; i < MYEA_TIMER_CLASSES; ++i) {
+    if (ms) ms[i] = net->ctx.class_ms[i];
+    if (launches) launches[i] = net->ctx.class_launches[i];
+  }
+  if (gemm_flops) gemm_flops[0] = net->ctx.gemm_flops;
+  if (reset) {
+    for (int i = 0; i < MYEA_TIMER_CLASSES; ++i) { net->ctx.class_ms[i] = 0; net->ctx.class_launches[i] = 0; }
+    net->ctx.gemm_flops = 0;
+  }
+  return MYEA_OK;
+}

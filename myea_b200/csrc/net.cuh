@@ -1,0 +1,69 @@
+// The device-side network object behind a myea_handle: the reference's flat buffers and index map, the
+// per-layer activation / error buffers, and the step functions.
+#pragma once
+
+#include <vector>
+
+#include "common.cuh"
+
+namespace myea {
+
+struct LstmPlan;   // lstm.cu
+struct CommState;  // comm.cu
+
+struct LayerPlan {
+  myea_layer_desc desc;
+  myea_layer_index idx;
+  uint32_t type = 0;
+  long long n_in = 0, n_out = 0;  // widths per time step
+  int input_layer = -1;            // layer whose outputs feed this one
+  bool use_bias = false;           // FC: false under normalization (Layer::Use__Bias, Data.hpp:736)
+  bool is_output = false;
+  // [T*B, n_out] each
+  float *summations = nullptr;  // z = W x (+ b)
+  float *values = nullptr;      // layer output after activation and dropout
+  float *deriv = nullptr;       // error after the activation derivative (input of the normalization backward)
+  float *errors = nullptr;      // error w.r.t. z (what Update_Derivative_Weight and the previous layer read)
+  bool has_norm = false;
+  NormParams norm;
+  uint8_t *mask_bernoulli = nullptr;  // [T*n_out]
+  float keep_scale = 1.f;             // factor applied to kept units while training
+  float infer_scale = 1.f;            // factor applied to every unit at inference
+  LstmPlan *lstm = nullptr;
+  // residual block (type RESIDUAL): see residual.cu
+  int block_depth = 0;
+  uint8_t *shake_mask = nullptr;      // [B]
+  float *shake_alpha = nullptr, *shake_beta = nullptr;  // [B, n_out]
+  float *block_out_errors = nullptr;
+  long long norm_unit_offset = 0;     // units of earlier layers in the normalized-unit run
+};
+
+}  // namespace myea
+
+struct myea_b200_net {
+  myea::Context ctx;
+  myea_net_desc desc;
+  std::vector<myea::LayerPlan> layers;
+  uint64_t total_parameters = 0, total_weights = 0, total_bias = 0, total_norm_units = 0;
+  long long T = 1, B = 0;
+  bool any_norm = false;
+  // flat buffers, [P] (norm averages: [total_norm_units])
+  float *params = nullptr, *grads = nullptr, *m1 = nullptr, *m2 = nullptr, *m2hat = nullptr, *prev_delta = nullptr,
+        *mask_reg = nullptr;
+  float *norm_mean_avg = nullptr, *norm_sigma_avg = nullptr;
+  float *norm_stats = nullptr;  // [total_norm_units][6]: mean, sigma, r, d, col_scale, col_shift
+  float *norm_partial = nullptr;
+  float *reduce_partial = nullptr;
+  int reduce_chunks = 64;
+  float *d_input = nullptr;    // [T*B, inputs]
+  float *d_desired = nullptr;  // [T*B, outputs]
+  myea::GemmScratch scratch;
+  double *d_loss_acc = nullptr;  // [2] loss sum, accuracy sum
+  unsigned long long *d_loss_count = nullptr;
+  double *d_sumsq = nullptr;
+  float *d_clip_scale = nullptr;
+  float optimizer_time_step = 0.f;
+  bool training = true;
+  myea::CommState *comm = nullptr;
+  std::vector<void *> allocations;
+};

@@ -1,0 +1,140 @@
+"""numpy-facing wrapper over the C ABI (include/myea_b200.h): one `Net` = one `Neural_Network` object of the
+reference on one GPU.  Method names follow the reference's member functions (Forward_Pass -> forward, Compute__Error ->
+compute_error, Backward_Pass -> backward, Update_Derivative_Weight -> update_derivative_weight, Update_Parameter ->
+update_parameter); every method is a thin call into libmyea_b200.so and raises RuntimeError with the library's
+message when the status is not MYEA_OK.  There is no CPU path: without the library or without a GPU it raises.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class Net:
+    def __init__(self, desc, opt=None, device=0):
+        self.lib = capi.load()
+        self.desc, self.opt = desc, opt
+        self.h = C.c_void_p()
+        rc = self.lib.myea_b200_create(C.byref(self.h), C.byref(desc), device)
+        if rc != 0:
+            msg = self.lib.myea_b200_last_error(self.h).decode() if self.h else "no CUDA device / invalid descriptor"
+            if self.h:
+                self.lib.myea_b200_destroy(self.h)
+                self.h = None
+            raise RuntimeError("myea_b200_create failed (%d): %s" % (rc, msg))
+        self.T = int(desc.number_recurrent_depth)
+        self.B = int(desc.batch_size)
+        self.P, self.W, self.n_bias, self.n_norm = self.sizes()
+
+    def _ck(self, rc, what):
+        if rc != 0:
+            raise RuntimeError("%s failed (%d): %s" % (what, rc, self.lib.myea_b200_last_error(self.h).decode()))
+
+    def close(self):
+        if self.h:
+            self.lib.myea_b200_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def sizes(self):
+        v = [C.c_uint64() for _ in range(4)]
+        self._ck(self.lib.myea_b200_sizes(self.h, *[C.byref(x) for x in v]), "sizes")
+        return tuple(int(x.value) for x in v)
+
+    def layer_index(self, layer):
+        li = capi.LayerIndex()
+        self._ck(self.lib.myea_b200_layer_index(self.h, layer, C.byref(li)), "layer_index")
+        return li
+
+    def _count(self, which):
+        return self.n_norm if which in (capi.BUF_NORM_MEAN_AVERAGE, capi.BUF_NORM_VARIANCE_AVERAGE) else self.P
+
+    def get(self, which):
+        out = np.empty(self._count(which), np.float32)
+        self._ck(self.lib.myea_b200_download(self.h, which, out.ctypes.data, 0, out.size), "download")
+        return out
+
+    def set(self, which, arr):
+        a = _f32(arr).ravel()
+        self._ck(self.lib.myea_b200_upload(self.h, which, a.ctypes.data, 0, a.size), "upload")
+
+    def set_mask_bernoulli(self, layer, mask):
+        m = np.ascontiguousarray(mask, dtype=np.uint8).ravel()
+        self._ck(self.lib.myea_b200_set_mask_bernoulli(self.h, layer, m.ctypes.data, m.size), "set_mask_bernoulli")
+
+    def set_mask_zoneout(self, layer, state, output):
+        s = np.ascontiguousarray(state, dtype=np.uint8).ravel()
+        o = np.ascontiguousarray(output, dtype=np.uint8).ravel()
+        self._ck(self.lib.myea_b200_set_mask_zoneout(self.h, layer, s.ctypes.data, o.ctypes.data, s.size), "set_mask_zoneout")
+
+    def set_shakedrop(self, layer, mask, alpha, beta):
+        m = np.ascontiguousarray(mask, dtype=np.uint8).ravel()
+        a, b = _f32(alpha), _f32(beta)
+        self._ck(self.lib.myea_b200_set_shakedrop(self.h, layer, m.ctypes.data, a.ctypes.data, b.ctypes.data, m.size), "set_shakedrop")
+
+    def forward(self, X, training=True):
+        X = _f32(X)
+        self._ck(self.lib.myea_b200_forward(self.h, self.B, X.ctypes.data, 1 if training else 0), "forward")
+
+    def compute_error(self, Y):
+        Y = _f32(Y)
+        self._ck(self.lib.myea_b200_compute_error(self.h, self.B, Y.ctypes.data), "compute_error")
+
+    def backward(self):
+        self._ck(self.lib.myea_b200_backward(self.h, self.B), "backward")
+
+    def update_derivative_weight(self):
+        self._ck(self.lib.myea_b200_update_derivative_weight(self.h, self.B), "update_derivative_weight")
+
+    def update_parameter(self, training_size=None, opt=None):
+        o = opt or self.opt
+        self._ck(self.lib.myea_b200_update_parameter(self.h, self.B, training_size or self.B, C.byref(o)), "update_parameter")
+
+    def clear_training_arrays(self):
+        self._ck(self.lib.myea_b200_clear_training_arrays(self.h), "clear_training_arrays")
+
+    def reset_loss(self):
+        self._ck(self.lib.myea_b200_reset_loss(self.h), "reset_loss")
+
+    def loss(self):
+        s, n, a = C.c_double(), C.c_uint64(), C.c_double()
+        self._ck(self.lib.myea_b200_get_loss(self.h, C.byref(s), C.byref(n), C.byref(a)), "get_loss")
+        return s.value, int(n.value), a.value
+
+    def outputs(self, layer):
+        w = int(self.layer_index(layer).number_outputs)
+        out = np.empty((self.T, self.B, w), np.float32)
+        self._ck(self.lib.myea_b200_get_outputs(self.h, layer, out.ctypes.data, out.size), "get_outputs")
+        return out
+
+    def errors(self, layer):
+        w = int(self.layer_index(layer).number_outputs)
+        out = np.empty((self.T, self.B, w), np.float32)
+        self._ck(self.lib.myea_b200_get_errors(self.h, layer, out.ctypes.data, out.size), "get_errors")
+        return out
+
+    def synchronize(self):
+        self._ck(self.lib.myea_b200_synchronize(self.h), "synchronize")
+
+    def launches(self):
+        return int(self.lib.myea_b200_kernel_launches(self.h))
+
+    def profile(self, enable):
+        self._ck(self.lib.myea_b200_profile(self.h, 1 if enable else 0), "profile")
+
+    def profile_read(self, reset=True):
+        ms = (C.c_double * capi.TIMER_CLASSES)()
+        ln = (C.c_uint64 * capi.TIMER_CLASSES)()
+        fl = (C.c_double * 1)()
+        self._ck(self.lib.myea_b200_profile_read(self.h, ms, ln, fl, 1 if reset else 0), "profile_read")
+        return list(ms), [int(x) for x in ln], fl[0]
