@@ -1,0 +1,295 @@
+#!/usr/bin/env python
+"""Throughput of one full training step (forward, output error, backward, derivative-weight accumulation, optimizer
+update) on the wide-MLP workload: 8 x FC 4096 + BatchNorm + ReLU + inverted dropout 0.5, FC 4096 -> 1024, MSE, Adam,
+global batch 4096, fp32 (3xTF32 tensor-core contractions), synthetic seeded data.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c3|c4|c5]
+
+N > 1 is launched by torchrun, one rank per GPU; the global batch is split over the ranks (strong scaling), gradients
+are summed with NCCL and batch-norm statistics are synchronised so that the result equals the one-GPU step.
+Prints ONE JSON line.  `value` is measured with inputs resident in HBM; `e2e` goes through the host-buffer entry
+points (host -> device copy of inputs and targets and a device -> host read of the loss inside the timed region).
+`--impl reference` times the reference's own CPU/OpenMP implementation (compiled into oracle/_ref) on the host cores,
+on a bounded sample of the same workload.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+
+def _peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p["bf16_tflops_sustained"],
+                "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """samples SM clocks and throttle reasons with nvidia-smi while the timed region runs"""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device, self.proc, self.lines = device, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_workload(name, world, global_batch=None):
+    from myea_b200 import workloads
+    if name == "c2":
+        gb = global_batch or 4096
+        return workloads.c2_wide_mlp(batch=gb // world), gb
+    wl = workloads.BUILDERS[name]()
+    if world > 1:
+        wl = workloads.BUILDERS[name](batch=wl.B // world)
+    return wl, wl.B * world
+
+
+def cpu_reference_run(wl_name, steps, warmup, sample_batch, threads):
+    """samples/s of the compiled reference on `sample_batch` rows of the workload"""
+    from myea_b200 import workloads
+    from oracle import ref
+    if not ref.available():
+        return None
+    wl = workloads.BUILDERS[wl_name](batch=sample_batch)
+    net = ref.RefNet(wl.desc, wl.opt, threads=threads)
+    wl.materialize(net)
+    X, Y = wl.batch()
+    ms = net.time_steps(X, Y, warmup, steps)
+    used = net.threads
+    net.close()
+    return {"value": sample_batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "cores": used}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = min(os.cpu_count() or 1, 32)
+    sample = {"c2": 64, "c1": 128, "c3": 16, "c4": 64, "c5": 4}[args.workload]
+    steps = max(1, min(args.steps, 3))
+    warm = 1 if args.warmup > 0 else 0
+    r = cpu_reference_run(args.workload, steps, warm, sample, threads)
+    wl, gb = build_workload(args.workload, 1)
+    if r is None:
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libmyea_ref.so was not built (no reference checkout at build time)"}))
+        return
+    line = {"impl": "reference", "metric": "train samples/sec (fwd+bwd+update)", "value": r["value"], "unit": "samples/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": wl.name, "global_batch": gb, "sample_batch": sample},
+            "cpu_baseline": {"value": r["value"], "unit": "samples/s", "cores": r["cores"], "kind": "reference",
+                             "sample": "%d rows of the workload per step, %d timed steps, reference OpenMP path" % (sample, steps)},
+            "e2e": {"value": r["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch
+    from myea_b200 import capi
+    from myea_b200.net import Net
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus %d needs torchrun with %d ranks" % (args.gpus, args.gpus))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    wl, global_batch = build_workload(args.workload, world, args.global_batch)
+    net = Net(wl.desc, wl.opt, device=local)
+    wl.materialize(net)
+    lib = net.lib
+    if world > 1:
+        uid = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_uint8 * 128)()
+            rc = lib.myea_b200_comm_unique_id(buf)
+            if rc != 0:
+                raise RuntimeError("comm_unique_id failed")
+            uid = torch.tensor(list(buf), dtype=torch.uint8)
+        uid = uid.cuda()
+        dist.broadcast(uid, 0)
+        idb = (C.c_uint8 * 128)(*uid.cpu().tolist())
+        net._ck(lib.myea_b200_comm_init(net.h, world, rank, idb), "comm_init")
+    # this rank's shard of the global batch (rank r owns rows [r*B, (r+1)*B) of every time step)
+    Xg, Yg = wl.batch(rows=wl.B * world)
+    X = np.ascontiguousarray(Xg[:, rank * wl.B:(rank + 1) * wl.B])
+    Y = np.ascontiguousarray(Yg[:, rank * wl.B:(rank + 1) * wl.B])
+    Xh, Yh = torch.from_numpy(X).pin_memory(), torch.from_numpy(Y).pin_memory()
+    Xd, Yd = Xh.cuda(), Yh.cuda()
+    stream = torch.cuda.ExternalStream(int(lib.myea_b200_stream(net.h)))
+    h, B, opt = net.h, wl.B, C.byref(wl.opt)
+    N_train = global_batch
+
+    def step_device():
+        lib.myea_b200_forward_device(h, B, Xd.data_ptr(), 1)
+        lib.myea_b200_compute_error_device(h, B, Yd.data_ptr())
+        lib.myea_b200_backward(h, B)
+        lib.myea_b200_update_derivative_weight(h, B)
+        return lib.myea_b200_update_parameter(h, B, N_train, opt)
+
+    def step_host():
+        lib.myea_b200_reset_loss(h)
+        lib.myea_b200_forward(h, B, Xh.data_ptr(), 1)
+        lib.myea_b200_compute_error(h, B, Yh.data_ptr())
+        lib.myea_b200_backward(h, B)
+        lib.myea_b200_update_derivative_weight(h, B)
+        rc = lib.myea_b200_update_parameter(h, B, N_train, opt)
+        s, n, a = C.c_double(), C.c_uint64(), C.c_double()
+        lib.myea_b200_get_loss(h, C.byref(s), C.byref(n), C.byref(a))  # device -> host read of the step's loss
+        return rc
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            if fn() != 0:
+                raise RuntimeError("step failed: " + lib.myea_b200_last_error(h).decode())
+        net.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = net.launches()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        e1.synchronize()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            ms = float(t.item())
+        net.synchronize()
+        return ms, net.launches() - l0
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_dev, launches = timed(step_device, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e, _ = timed(step_host, args.steps, max(1, args.warmup // 2))
+    # kernel-class timing pass (CUDA events around every launch on the library's stream): the GEMM roofline figure
+    net.profile(True)
+    net.profile_read(reset=True)
+    for _ in range(max(1, min(args.steps, 3))):
+        step_device()
+    net.synchronize()
+    cls_ms, cls_n, gemm_flops = net.profile_read(reset=True)
+    net.profile(False)
+    peaks = _peaks()
+    if rank == 0:
+        per_step = ms_dev / args.steps
+        value = global_batch / (per_step / 1e3)
+        e2e_value = global_batch / ((ms_e2e / args.steps) / 1e3)
+        gemm_tflops = gemm_flops / (cls_ms[0] / 1e3) / 1e12 if cls_ms[0] > 0 else 0.0
+        peak = peaks["bf16_tflops_sustained"]
+        names = ["gemm", "split", "normalization", "elementwise", "optimizer", "recurrent", "comm", "other"]
+        line = {
+            "metric": "train samples/sec (fwd+bwd+update)", "value": value, "unit": "samples/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulate)",
+            "data": "synthetic",
+            "config": {"workload": wl.name, "global_batch": global_batch, "per_gpu_batch": wl.B,
+                       "parallelism": "dp%d" % world, "l2": "per-step working set (> 6 GB) far exceeds the 126 MB L2"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": int(X.nbytes + Y.nbytes) * world,
+                    "d2h_bytes_per_step": 24 * world},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "achieved": gemm_tflops, "peak": peak, "unit": "TFLOP/s",
+                         "frac": gemm_tflops / peak if peak else None, "traffic": None,
+                         "kernel": "gemm3x_tf32_tcgen05_kernel", "peak_source": peaks["source"] + " bf16 sustained",
+                         "issued_tf32_tflops": 3.0 * gemm_tflops, "frac_of_tf32_peak": 3.0 * gemm_tflops / (peak / 2.0),
+                         "step_tflops": wl.flops_per_step * world / (per_step / 1e3) / 1e12},
+            "kernel_classes_ms_per_step": {n: m / max(1, min(args.steps, 3)) for n, m in zip(names, cls_ms) if m > 0},
+        }
+        if world == 1 and not args.no_cpu:
+            try:
+                threads = min(os.cpu_count() or 1, 32)
+                sample = {"c2": 64, "c1": 128, "c3": 16, "c4": 64, "c5": 4}[args.workload]
+                r = cpu_reference_run(args.workload, 2, 1, sample, threads)
+                if r is not None:
+                    line["cpu_baseline"] = {"value": r["value"], "unit": "samples/s", "cores": r["cores"], "kind": "reference",
+                                            "sample": "%d rows of the workload per step, 2 timed steps after 1 warm-up, reference OpenMP path" % sample}
+            except Exception as exc:  # the baseline is reported, never required for the GPU number
+                line["cpu_baseline"] = {"value": None, "unit": "samples/s", "cores": 0, "kind": "reference", "sample": "failed: %s" % exc}
+        print(json.dumps(line))
+    net.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--global-batch", type=int, default=None)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,440 @@
+"""Test infrastructure, not product code.
+
+numpy restatement of the reference's training step (MyEA `class Neural_Network`, CPU "Loop" variants), used as the
+parity checker where the compiled reference (oracle/_ref) cannot travel or cannot serve (bidirectional LSTM).  Only
+tests/, __graft_entry__.smoke() and the CPU-baseline leg of bench.py may import it.
+
+Pinned: tests/test_oracle_golden.py checks this module against tests/golden/*.npz, which were produced by running the
+unmodified reference (oracle/_ref, built by oracle/build_ref.sh) through tests/golden/make_golden.py.  The
+bidirectional LSTM has no usable reference run (the reference's own bidirectional wiring overlaps the two
+directions' buffers); for that layer this module composes the reference's unidirectional routines, and parity of
+that case is pinned only against this restatement plus a float64 finite-difference check: "parity unpinned" for
+bidirectional LSTM against the reference binary.
+
+Each routine cites the reference file:line it follows (paths relative to
+Neural_Network_Library_Windows/Source_Files/Neural_Network/).  Arithmetic is float32 unless `dtype=np.float64` is
+passed to OracleNet (tie-breaker / finite differences).  Same method set as oracle.ref.RefNet and myea_b200.net.Net.
+"""
+import numpy as np
+
+from myea_b200 import capi
+
+F = np.float32
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# activation functions: Header_Files/Neural_Network/Activation_Functions.hpp:34-183, Neural_Network.cpp:3157-3204
+# ---------------------------------------------------------------------------------------------------------------
+def af_fire(af, z):
+    dt = z.dtype.type
+    if af == capi.AF_TANH:
+        return dt(2) / (dt(1) + np.exp(dt(-2) * z)) - dt(1)
+    if af == capi.AF_SIGMOID:
+        return dt(1) / (dt(1) + np.exp(-z))
+    if af == capi.AF_RELU:
+        return np.where(z < 0, dt(0), z)
+    if af == capi.AF_LEAKY_RELU:
+        return np.where(z < 0, dt(0.01) * z, z)
+    if af == capi.AF_ELU:
+        return np.where(z < 0, np.exp(np.minimum(z, 0)) - dt(1), z)
+    if af == capi.AF_SELU:
+        a, s = dt(1.6732632423543772848170429916717), dt(1.0507009873554804934193349852946)
+        return s * np.where(z <= 0, a * np.exp(np.minimum(z, 0)) - a, z)
+    return z  # linear
+
+
+def af_derive(af, z, y):
+    dt = y.dtype.type
+    one = np.ones_like(y)
+    if af == capi.AF_TANH:
+        return dt(1) - y * y
+    if af == capi.AF_SIGMOID:
+        return y * (dt(1) - y)
+    if af == capi.AF_RELU:
+        return np.where(z < 0, dt(0), one)
+    if af == capi.AF_LEAKY_RELU:
+        return np.where(z < 0, dt(0.01), one)
+    if af == capi.AF_ELU:          # steepness * alpha * y below zero, y = e^z - 1 (not alpha * e^z)
+        return np.where(z < 0, y, one)
+    if af == capi.AF_SELU:
+        a, s = dt(1.6732632423543772848170429916717), dt(1.0507009873554804934193349852946)
+        return s * np.where(z <= 0, y + a, one)
+    return one  # linear, softmax
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# index map: Neural_Network__Prepare_Connections.cpp:20-252, Neural_Network__Compile.cpp:426-785,
+# normalized-unit slots Neural_Network__Allocate.cpp:2378-2460
+# ---------------------------------------------------------------------------------------------------------------
+class _Layer:
+    pass
+
+
+def build_index_map(desc):
+    n = int(desc.number_layers)
+    Ls = []
+    for l in range(n):
+        d = desc.layers[l]
+        L = _Layer()
+        L.d, L.type = d, int(d.type_layer)
+        L.n_out = 0
+        if L.type == capi.LAYER_FC:
+            L.n_out = int(d.unit_parameters[0])
+        elif L.type == capi.LAYER_LSTM:
+            L.n_out = int(d.unit_parameters[0]) * max(1, int(d.unit_parameters[1]))
+        L.depth = int(d.unit_parameters[0]) if L.type == capi.LAYER_RESIDUAL else 0
+        L.idx = dict(first_connection_index=0, last_connection_index=0, first_bias_connection_index=0,
+                     last_bias_connection_index=0, scale_index=0, shift_index=0, number_inputs=0, number_outputs=0,
+                     block_stride=0, number_units_norm=0)
+        Ls.append(L)
+    for l in range(1, n):
+        if Ls[l].type == capi.LAYER_RESIDUAL:
+            Ls[l].n_out = Ls[l + Ls[l].depth].n_out
+    for l in range(1, n):
+        Ls[l].input_layer, Ls[l].n_in = l - 1, Ls[l - 1].n_out
+    for l in range(1, n):
+        if Ls[l].type == capi.LAYER_RESIDUAL:
+            Ls[l + 1].input_layer, Ls[l + 1].n_in = l - 1, Ls[l - 1].n_out
+            after = l + Ls[l].depth + 1
+            if after < n:
+                Ls[after].input_layer, Ls[after].n_in = l, Ls[l].n_out
+    tw = 0
+    for l in range(1, n):
+        L = Ls[l]
+        L.idx["number_inputs"], L.idx["number_outputs"] = L.n_in, L.n_out
+        if L.type == capi.LAYER_FC:
+            L.idx["first_connection_index"] = tw
+            tw += L.n_out * L.n_in
+            L.idx["last_connection_index"] = tw
+        elif L.type == capi.LAYER_LSTM:
+            dirs = 2 if L.d.use_bidirectional else 1
+            cpb = max(1, int(L.d.unit_parameters[1]))
+            blocks = int(L.d.unit_parameters[0])
+            cells = blocks * cpb
+            L.idx["block_stride"] = cpb * (L.n_in + cells) + 3 * L.n_in + 3 * cells + 3 * cpb
+            L.idx["first_connection_index"] = tw
+            tw += dirs * blocks * L.idx["block_stride"]
+            L.idx["last_connection_index"] = tw
+    Ls[0].idx["number_outputs"] = Ls[0].n_out
+    tb = 0
+    for l in range(1, n):
+        L = Ls[l]
+        if L.type == capi.LAYER_FC:
+            L.idx["first_bias_connection_index"] = tw + tb
+            tb += L.n_out
+            L.idx["last_bias_connection_index"] = tw + tb
+        elif L.type == capi.LAYER_LSTM:
+            dirs = 2 if L.d.use_bidirectional else 1
+            cells, blocks = L.n_out * dirs, int(L.d.unit_parameters[0]) * dirs
+            L.idx["first_bias_connection_index"] = tw + tb + cells   # shifted by the cell count, as the reference does
+            tb += cells + 3 * blocks
+            L.idx["last_bias_connection_index"] = tw + tb
+    P = tw + tb
+    units = 0
+    if any(int(desc.layers[l].type_normalization) != capi.NORM_NONE for l in range(1, n)):
+        off = []
+        for l in range(n):
+            off.append(units)
+            units += Ls[l].n_out
+        for l in range(n):
+            Ls[l].idx["scale_index"] = P + off[l]
+            Ls[l].idx["shift_index"] = P + units + off[l]
+            Ls[l].idx["number_units_norm"] = Ls[l].n_out
+            Ls[l].norm_off = off[l]
+        P += 2 * units
+    return Ls, P, tw, tb, units
+
+
+class OracleNet:
+    def __init__(self, desc, opt, threads=1, dtype=np.float32):
+        self.desc, self.opt, self.dt = desc, opt, dtype
+        self.T, self.B = int(desc.number_recurrent_depth), int(desc.batch_size)
+        self.layers, self.P, self.W, self.n_bias, self.n_norm = build_index_map(desc)
+        z = lambda k: np.zeros(k, dtype)
+        self.buf = {capi.BUF_PARAMETERS: z(self.P), capi.BUF_DERIVATIVES: z(self.P), capi.BUF_FIRST_MOMENT: z(self.P),
+                    capi.BUF_SECOND_MOMENT: z(self.P), capi.BUF_SECOND_MOMENT_HAT: z(self.P), capi.BUF_MASK_REGULARIZED: z(self.P),
+                    capi.BUF_PREVIOUS_DELTA: z(self.P), capi.BUF_NORM_MEAN_AVERAGE: z(self.n_norm),
+                    capi.BUF_NORM_VARIANCE_AVERAGE: np.ones(self.n_norm, dtype)}
+        self.masks, self.zone, self.shake = {}, {}, {}
+        self.time_step = dtype(0)
+        self.loss_sum, self.n_loss, self.acc_sum = 0.0, 0, 0.0
+        self.training = True
+        self.momentum = dtype(desc.normalization_momentum_average if desc.normalization_momentum_average > 0 else 0.999)
+        self.eps = dtype(desc.normalization_epsilon if desc.normalization_epsilon > 0 else 1e-5)
+        self.r_max = dtype(desc.batch_renormalization_r_correction_maximum if desc.batch_renormalization_r_correction_maximum > 0 else 1.0)
+        self.d_max = dtype(desc.batch_renormalization_d_correction_maximum if desc.batch_renormalization_d_correction_maximum > 0 else 0.0)
+
+    # ---- bookkeeping ----------------------------------------------------------------------------------------
+    def close(self):
+        pass
+
+    def sizes(self):
+        return self.P, self.W, self.n_bias, self.n_norm
+
+    def layer_index(self, l):
+        li = capi.LayerIndex()
+        for k, v in self.layers[l].idx.items():
+            setattr(li, k, v)
+        return li
+
+    def get(self, which):
+        return self.buf[which].astype(np.float32).copy()
+
+    def set(self, which, arr):
+        a = np.asarray(arr).ravel()
+        self.buf[which][:a.size] = a.astype(self.dt)
+
+    def set_mask_bernoulli(self, l, mask):
+        self.masks[l] = np.asarray(mask).reshape(self.T, -1).astype(bool)
+
+    def set_mask_zoneout(self, l, state, output):
+        self.zone[l] = (np.asarray(state).reshape(self.T, -1).astype(bool), np.asarray(output).reshape(self.T, -1).astype(bool))
+
+    def set_shakedrop(self, l, mask, alpha, beta):
+        self.shake[l] = (np.asarray(mask).astype(bool), np.asarray(alpha, self.dt), np.asarray(beta, self.dt))
+
+    def reset_loss(self):
+        self.loss_sum, self.n_loss, self.acc_sum = 0.0, 0, 0.0
+
+    def loss(self):
+        return float(self.loss_sum), int(self.n_loss), float(self.acc_sum)
+
+    def outputs(self, l):
+        return np.asarray(self.layers[l].values, np.float32).reshape(self.T, self.B, -1)
+
+    def errors(self, l):
+        L = self.layers[l]
+        e = L.dh if L.type == capi.LAYER_LSTM else L.errors
+        return np.asarray(e, np.float32).reshape(self.T, self.B, -1)
+
+    def _p(self):
+        return self.buf[capi.BUF_PARAMETERS]
+
+    def _g(self):
+        return self.buf[capi.BUF_DERIVATIVES]
+
+    # ---- fully connected layer ---------------------------------------------------------------------------------
+    def _fc_weights(self, L):
+        i = L.idx
+        return self._p()[i["first_connection_index"]:i["last_connection_index"]].reshape(L.n_out, L.n_in)
+
+    def _norm_forward(self, L, z):
+        """Forward_Pass__Batch_Normalization__Training / __Batch_Renormalization__Training
+        (Neural_Network__Forward_Pass__Loop.cpp:4673-4853); inference :4644-4671.  The 'variance' is the standard
+        deviation sqrt(E[x^2]-mean^2+eps); r and d use the already updated running averages."""
+        dt = self.dt
+        o, H = L.norm_off, L.n_out
+        gamma = self._p()[L.idx["scale_index"]:L.idx["scale_index"] + H]
+        beta = self._p()[L.idx["shift_index"]:L.idx["shift_index"] + H]
+        ma = self.buf[capi.BUF_NORM_MEAN_AVERAGE][o:o + H]
+        sa = self.buf[capi.BUF_NORM_VARIANCE_AVERAGE][o:o + H]
+        if self.training:
+            inv = dt(1) / dt(z.shape[0])
+            mean = z.sum(0, dtype=dt) * inv
+            sigma = np.sqrt((z * z).sum(0, dtype=dt) * inv - mean * mean + self.eps)
+            ma += self.momentum * (mean - ma)
+            sa += self.momentum * (sigma - sa)
+            r, d = np.ones(H, dt), np.zeros(H, dt)
+            if int(L.d.type_normalization) == capi.NORM_BRN:
+                r = np.clip(sigma / sa, dt(1) / self.r_max, self.r_max)
+                d = np.clip((mean - ma) / sa, -self.d_max, self.d_max)
+            L.mean, L.sigma, L.r, L.dcorr = mean, sigma, r, d
+            L.xhat = (z - mean) / sigma * r + d
+        else:
+            L.xhat = (z - ma) / sa
+        return gamma * L.xhat + beta
+
+    def _norm_backward(self, L, z, delta):
+        """Backward_Pass__Batch_Normalization / __Batch_Renormalization (Neural_Network__Backward_Pass__Loop.cpp:1380-1628)"""
+        dt = self.dt
+        H, B = L.n_out, dt(z.shape[0])
+        gamma = self._p()[L.idx["scale_index"]:L.idx["scale_index"] + H]
+        self._g()[L.idx["scale_index"]:L.idx["scale_index"] + H] += (delta * L.xhat).sum(0, dtype=dt)
+        self._g()[L.idx["shift_index"]:L.idx["shift_index"] + H] += delta.sum(0, dtype=dt)
+        dh = delta * gamma
+        d_mean = (dh * (-L.r / L.sigma)).sum(0, dtype=dt)
+        d_sigma = (dh * (z - L.mean) * (-L.r / (L.sigma * L.sigma))).sum(0, dtype=dt)
+        return dh * (L.r / L.sigma) + d_sigma * ((z - L.mean) / (B * L.sigma)) + d_mean * (dt(1) / B)
+
+    def _fc_forward(self, l, x):
+        """Forward_Pass__FC (Neural_Network__Forward_Pass__Loop.cpp:350-790): weights, bias (only without
+        normalization), normalization, activation, dropout applied in place on the output (:4917-4990)."""
+        L = self.layers[l]
+        dt = self.dt
+        z = x @ self._fc_weights(L).T
+        norm = int(L.d.type_normalization) != capi.NORM_NONE
+        if not norm:
+            z = z + self._p()[L.idx["first_bias_connection_index"]:L.idx["first_bias_connection_index"] + L.n_out]
+        L.z = z
+        pre = self._norm_forward(L, z) if norm else z
+        L.pre = pre
+        af = int(L.d.type_activation_function)
+        if af == capi.AF_SOFTMAX:
+            e = np.exp(pre - pre.max(1, keepdims=True))
+            y = e * (dt(1) / e.sum(1, keepdims=True, dtype=dt))
+        else:
+            y = af_fire(af, pre)
+        drop = int(L.d.type_dropout)
+        if drop in (capi.DROP_BERNOULLI, capi.DROP_BERNOULLI_INVERTED):
+            p = dt(L.d.dropout_values[0])
+            if self.training:
+                m = self.masks[l][0]
+                y = np.where(m, y * (dt(1) / p) if drop == capi.DROP_BERNOULLI_INVERTED else y, dt(0))
+            elif drop == capi.DROP_BERNOULLI:
+                y = y * p
+        L.values = y.astype(dt)
+        return L.values
+
+    # ---- step functions ------------------------------------------------------------------------------------------
+    def forward(self, X, training=True):
+        self.training = training
+        X = np.asarray(X, self.dt).reshape(self.T * self.B, -1)
+        self.layers[0].values = X
+        n = len(self.layers)
+        l = 1
+        while l < n:
+            L = self.layers[l]
+            x = self.layers[L.input_layer].values
+            if L.type == capi.LAYER_FC:
+                self._fc_forward(l, x)
+                l += 1
+            elif L.type == capi.LAYER_LSTM:
+                from oracle import myea_oracle_lstm
+                myea_oracle_lstm.forward(self, l, x)
+                l += 1
+            else:
+                from oracle import myea_oracle_residual
+                myea_oracle_residual.forward(self, l)
+                l += L.depth + 1
+
+    def compute_error(self, Y):
+        """FF__Compute__Error / RNN__Compute__Error (Neural_Network__Compute__Error__Loop.cpp:20-209,
+        Neural_Network__Recurrent_Compute__Error__Loop.cpp): delta = f'(pre, y) * (y - desired) whatever the loss; steps
+        before number_time_delays are not scored and get zero error."""
+        dt = self.dt
+        L = self.layers[-1]
+        Y = np.asarray(Y, dt).reshape(self.T * self.B, -1)
+        t0 = min(int(self.desc.number_time_delays), self.T) if self.T > 1 else 0
+        skip = t0 * self.B
+        y, t, pre = L.values[skip:], Y[skip:], L.pre[skip:]
+        diff = y - t
+        af = int(L.d.type_activation_function)
+        L.errors = np.zeros_like(L.values)
+        L.errors[skip:] = af_derive(af, pre, y) * diff
+        loss = int(self.desc.type_loss_function)
+        if loss == capi.LOSS_MSE:
+            self.loss_sum += float((diff * diff).sum(dtype=np.float64))
+        elif loss == capi.LOSS_CE:
+            o = np.where(y != 0, y, np.maximum(y, dt(1e-6)))
+            if L.n_out == 1:
+                self.loss_sum += float((-(t * np.log(o) + (1 - t) * np.log(1 - o))).sum(dtype=np.float64))
+            else:
+                self.loss_sum += float((-(t * np.log(o))).sum(dtype=np.float64))
+        self.n_loss += diff.size
+        acc = int(self.desc.type_accuracy_function)
+        if acc == capi.ACC_DISTANCE:
+            var = self.desc.accuracy_variance if self.desc.accuracy_variance > 0 else 0.49
+            self.acc_sum += float((np.abs(diff) <= dt(var)).sum())
+        elif acc == capi.ACC_CE:
+            H = L.n_out
+            want = np.where((t == 1).any(1), (t == 1).argmax(1), H)
+            got = H - 1 - y[:, ::-1].argmax(1)   # the LAST maximum wins (>= in the reference's scan)
+            self.acc_sum += float((want == got).sum())
+
+    def backward(self):
+        """FF__Backward_Pass_Batch (Neural_Network__Backward_Pass__Loop.cpp:80-209): error to the previous layer
+        (:1079-1114), activation derivative (:1259-1294), normalization backward."""
+        n = len(self.layers)
+        l = n - 1
+        while l > 1:
+            N = self.layers[l]
+            p = N.input_layer
+            if p < 1:
+                break
+            Pl = self.layers[p]
+            if N.type == capi.LAYER_FC:
+                D = N.errors @ self._fc_weights(N)
+            else:
+                from oracle import myea_oracle_lstm
+                D = myea_oracle_lstm.error_to_input(self, l)
+            if Pl.type == capi.LAYER_FC:
+                da = D * af_derive(int(Pl.d.type_activation_function), Pl.pre, Pl.values)
+                Pl.errors = self._norm_backward(Pl, Pl.z, da) if int(Pl.d.type_normalization) != capi.NORM_NONE else da
+                l = p
+            elif Pl.type == capi.LAYER_LSTM:
+                from oracle import myea_oracle_lstm
+                Pl.dh = D
+                myea_oracle_lstm.backward(self, p)
+                l = p
+            else:
+                from oracle import myea_oracle_residual
+                Pl.errors = D
+                l = myea_oracle_residual.backward(self, p)
+
+    def update_derivative_weight(self):
+        """Update_Derivative_Weight__FC + bias (Neural_Network__Update_Derivative_Weight__Loop.cpp): sums over the batch,
+        never divided by the batch size."""
+        for l in range(1, len(self.layers)):
+            L = self.layers[l]
+            if L.type == capi.LAYER_FC:
+                x = getattr(L, "dw_input", None)
+                if x is None:
+                    x = self.layers[L.input_layer].values
+                i = L.idx
+                self._g()[i["first_connection_index"]:i["last_connection_index"]] += (L.errors.T @ x).ravel()
+                if int(L.d.type_normalization) == capi.NORM_NONE:
+                    self._g()[i["first_bias_connection_index"]:i["first_bias_connection_index"] + L.n_out] += L.errors.sum(0, dtype=self.dt)
+            elif L.type == capi.LAYER_LSTM:
+                from oracle import myea_oracle_lstm
+                myea_oracle_lstm.update_derivative_weight(self, l)
+
+    def update_parameter(self, training_size=None, opt=None):
+        """Update_Parameter (Neural_Network.cpp:4719-4900): clip (Neural_Network__Clip_Gradient.cpp:82-94), optimizer
+        (Neural_Network__Adam.cpp:39-95, __AMSGrad.cpp, __AdaBound.cpp, __AMSBound.cpp, __Gradient_Descent*.cpp,
+        __Nesterov_Accelerated_Gradient.cpp), derivatives reset to zero.  Update_Parameter's own L2 call is a no-op in
+        the reference (argument order), only the decoupled weight decay inside the optimizers acts."""
+        o = opt or self.opt
+        dt = self.dt
+        N = training_size or self.B
+        g, w = self._g(), self._p()
+        if o.use_clip_gradient:
+            norm = np.sqrt((g * g).sum(dtype=dt))
+            if norm >= dt(o.clip_gradient):
+                g *= dt(o.clip_gradient) / norm
+        self.time_step = dt(self.time_step + 1)
+        t = self.time_step
+        wd = dt(o.regularization__weight_decay)
+        if wd != 0 and o.use_normalized_weight_decay:
+            wd = wd * np.sqrt(dt(self.B) / (dt(N) * dt(o.epoch_time_step if o.epoch_time_step > 0 else 1.0)))
+        decay = self.buf[capi.BUF_MASK_REGULARIZED] * wd * w if wd != 0 else 0
+        kind = int(o.type_optimizer_function)
+        b1, b2, eps = dt(o.adam_beta1), dt(o.adam_beta2), dt(o.adam_epsilon)
+        if kind in (capi.OPT_ADAM, capi.OPT_AMSGRAD, capi.OPT_ADABOUND, capi.OPT_AMSBOUND):
+            lr = dt(o.adam_learning_rate)
+            lr_t = lr * np.sqrt(dt(1) - np.power(b2, t, dtype=dt)) / (dt(1) - np.power(b1, t, dtype=dt)) if o.use_adam_bias_correction else lr
+            m, v = self.buf[capi.BUF_FIRST_MOMENT], self.buf[capi.BUF_SECOND_MOMENT]
+            m[:] = b1 * m + (dt(1) - b1) * g
+            v[:] = b2 * v + (dt(1) - b2) * g * g
+            vv = v
+            if kind in (capi.OPT_AMSGRAD, capi.OPT_AMSBOUND):
+                vh = self.buf[capi.BUF_SECOND_MOMENT_HAT]
+                vh[:] = np.maximum(vh, v)
+                vv = vh
+            if kind in (capi.OPT_ADAM, capi.OPT_AMSGRAD):
+                w -= lr_t * m / (np.sqrt(vv) + eps) + decay
+            else:
+                lo = dt(o.learning_rate_final) * (dt(1) - dt(1) / (dt(o.learning_gamma) * t + dt(1)))
+                hi = dt(o.learning_rate_final) * (dt(1) + dt(1) / (dt(o.learning_gamma) * t))
+                w -= np.clip(lr_t / (np.sqrt(vv) + eps), lo, hi) * m + decay
+        else:
+            lr, mom = dt(o.learning_rate), dt(o.learning_momentum)
+            if mom == 0:
+                w -= lr * g + decay
+            else:
+                prev = self.buf[capi.BUF_PREVIOUS_DELTA]
+                prev[:] = lr * g + mom * prev
+                if o.use_nesterov:
+                    w -= mom * prev - lr * g + decay
+                else:
+                    w -= prev + decay
+        g[:] = 0

@@ -262,10 +262,7 @@ int ref_run(void *h, uint64_t B, int stages) {
 // gradient in OpenMP mode merges first (Neural_Network__Merge.cpp:20-50).
 int ref_merge_derivatives(void *h) {
   RefNet *r = static_cast<RefNet *>(h);
-  if (r->threads > 1) {
-#pragma omp parallel
-    r->nn.Merge_Derivatives_Parameters(0, r->nn.total_parameters);
-  }
+  if (r->threads > 1) r->nn.Merge_Derivatives_Parameters(0, r->nn.total_parameters);  // opens its own parallel loops
   return 0;
 }
 

@@ -1,0 +1,57 @@
+"""Parity cases shared by the golden-fixture generator, the CPU tests and the GPU tests: reduced-shape versions of the
+five benchmark configurations plus targeted variants (every optimizer, plain Bernoulli dropout, batch renormalization,
+clipping, weight decay, ragged widths that are not multiples of any tile)."""
+from myea_b200 import capi, workloads
+
+
+def _mlp_variant(name, hidden, af, opt, B=24, n_in=13, n_out=5, norm=capi.NORM_NONE, drop=capi.DROP_NONE, p=0.6, loss=capi.LOSS_MSE,
+                 out_af=capi.AF_LINEAR, **kw):
+    layers = [capi.fc(n_in)] + [capi.fc(h, af, norm, drop, (p, 0, 0)) for h in hidden] + [capi.fc(n_out, out_af)]
+    acc = capi.ACC_CE if loss == capi.LOSS_CE else capi.ACC_DISTANCE
+    wl = workloads.Workload(name, capi.net(layers, B, loss=loss, accuracy=acc, **kw), opt, n_in, n_out, loss == capi.LOSS_CE, layers)
+    return wl
+
+
+CASES = {
+    "c1_small": lambda: workloads.c1_mlp(scale=0.25),
+    "c2_small": lambda: workloads.c2_wide_mlp(scale=1.0 / 64, batch=48, hidden_layers=3),
+    "mlp_ragged_tanh_adam": lambda: _mlp_variant("ragged", [37, 19], capi.AF_TANH, capi.opt(capi.OPT_ADAM), B=21, n_in=11, n_out=3),
+    "mlp_sigmoid_amsgrad": lambda: _mlp_variant("amsgrad", [20], capi.AF_SIGMOID, capi.opt(capi.OPT_AMSGRAD), out_af=capi.AF_SIGMOID),
+    "mlp_brn_elu_adabound_wd": lambda: _mlp_variant("brn", [28, 28], capi.AF_ELU, capi.opt(capi.OPT_ADABOUND, weight_decay=1e-3), norm=capi.NORM_BRN,
+                                                    r_max=3.0, d_max=5.0, momentum=0.9),
+    "mlp_bernoulli_amsbound_clip": lambda: _mlp_variant("amsbound", [32], capi.AF_LEAKY_RELU, capi.opt(capi.OPT_AMSBOUND, clip=0.5), drop=capi.DROP_BERNOULLI),
+    "mlp_relu_gd": lambda: _mlp_variant("gd", [16, 16], capi.AF_RELU, capi.opt(capi.OPT_GD, gd_lr=0.01)),
+    "mlp_selu_momentum": lambda: _mlp_variant("mom", [16], capi.AF_SELU, capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9)),
+    "mlp_tanh_nesterov_ce": lambda: _mlp_variant("nag", [16], capi.AF_TANH, capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9, nesterov=True),
+                                                 loss=capi.LOSS_CE, out_af=capi.AF_SOFTMAX, n_out=6),
+}
+
+STEPS = 2
+
+
+def run_steps(net, wl, steps=STEPS, record=None):
+    """the reference's training sequence (Dataset.cpp:637-691, 7654-7690) on one seeded batch; returns what a parity
+    check compares"""
+    X, Y = wl.batch()
+    wl.materialize(net)
+    out = {}
+    for it in range(steps):
+        net.reset_loss()
+        net.forward(X)
+        net.compute_error(Y)
+        net.backward()
+        net.update_derivative_weight()
+        out["grad%d" % it] = net.get(capi.BUF_DERIVATIVES)
+        s, n, a = net.loss()
+        out["loss%d" % it] = [s, float(n), a]
+        if it == 0:
+            out["output_last"] = net.outputs(len(wl.layers) - 1)
+        net.update_parameter()
+        out["param%d" % it] = net.get(capi.BUF_PARAMETERS)
+    out["m"] = net.get(capi.BUF_FIRST_MOMENT) if wl.opt.type_optimizer_function != capi.OPT_GD else out["param0"] * 0
+    if net.sizes()[3]:
+        out["norm_mean_avg"] = net.get(capi.BUF_NORM_MEAN_AVERAGE)
+        out["norm_sigma_avg"] = net.get(capi.BUF_NORM_VARIANCE_AVERAGE)
+    out["index_map"] = [list(net.layer_index(l).as_tuple()) for l in range(len(wl.layers))]
+    out["sizes"] = list(net.sizes())
+    return out

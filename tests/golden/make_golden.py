@@ -1,0 +1,45 @@
+"""Generates tests/golden/<case>.npz by running the UNMODIFIED reference (oracle/_ref/libmyea_ref.so, built by
+oracle/build_ref.sh from the reference checkout) on every case of tests/cases.py.  Run from the repository root:
+
+    python tests/golden/make_golden.py [case ...]
+
+The fixtures hold the reference's derivatives, losses, updated parameters, first moments, running normalization
+statistics, last-layer outputs, index map and sizes in float32 / float64 / int64; inputs are regenerated from seeds by
+myea_b200/workloads.py and guarded by a checksum stored beside the results.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import cases  # noqa: E402
+from oracle import ref  # noqa: E402
+
+
+def input_checksum(wl, net):
+    X, Y = wl.batch()
+    p = wl.parameters(net)
+    return np.array([float(np.abs(X).sum(dtype=np.float64)), float(np.abs(Y).sum(dtype=np.float64)), float(np.abs(p).sum(dtype=np.float64))])
+
+
+def main():
+    names = sys.argv[1:] or sorted(cases.CASES)
+    for name in names:
+        wl = cases.CASES[name]()
+        net = ref.RefNet(wl.desc, wl.opt, threads=1)
+        out = cases.run_steps(net, wl)
+        out["input_checksum"] = input_checksum(wl, net)
+        net.close()
+        arrays = {k: (np.asarray(v, np.int64) if k in ("index_map", "sizes") else np.asarray(v, np.float64 if k.startswith("loss") or k == "input_checksum" else np.float32))
+                  for k, v in out.items()}
+        path = os.path.join(ROOT, "tests", "golden", name + ".npz")
+        np.savez_compressed(path, **arrays)
+        print("%-32s P=%-7d %6.1f KiB" % (name, out["sizes"][0], os.path.getsize(path) / 1024.0))
+
+
+if __name__ == "__main__":
+    main()

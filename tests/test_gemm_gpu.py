@@ -1,0 +1,56 @@
+"""GPU tests of the dense contraction alone (myea_b200_gemm_nt): tcgen05 3xTF32 against a float64 product.
+Shapes cover single tiles, ragged edges in all three dimensions (TMA zero fill, guarded epilogue), K tails that are
+not a multiple of the 32-float stage, accumulate mode, long K, and the FP32 FMA engine."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from myea_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+
+def _gemm(M, N, K, engine=0, accumulate=0, seed=0, positive=False):
+    lib = capi.load()
+    rng = np.random.default_rng(seed)
+    gen = (lambda s: rng.uniform(0, 1, s)) if positive else rng.standard_normal
+    A, B = gen((M, K)).astype(np.float32), gen((N, K)).astype(np.float32)
+    C0 = rng.standard_normal((M, N)).astype(np.float32) if accumulate else np.zeros((M, N), np.float32)
+    out = C0.copy()
+    ms = C.c_float(0)
+    rc = lib.myea_b200_gemm_nt(0, engine, M, N, K, A.ctypes.data, B.ctypes.data, out.ctypes.data, accumulate, C.byref(ms), 0)
+    assert rc == 0
+    want = A.astype(np.float64) @ B.astype(np.float64).T + (C0 if accumulate else 0)
+    return float(np.abs(out - want).max() / np.abs(want).max())
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 32), (128, 256, 64), (1, 1, 1), (5, 3, 7), (100, 10, 256), (129, 130, 33),
+                                   (300, 520, 100), (256, 64, 128), (512, 512, 512), (127, 1000, 2048)])
+def test_tcgen05_matches_float64(shape):
+    assert _gemm(*shape) < 2e-5
+
+
+@pytest.mark.parametrize("shape", [(64, 64, 16), (5, 3, 7), (300, 520, 100)])
+def test_fma_engine_matches_float64(shape):
+    assert _gemm(*shape, engine=1) < 2e-5
+
+
+def test_accumulate_into_c():
+    assert _gemm(256, 384, 512, accumulate=1) < 2e-5
+
+
+def test_long_k_stays_accurate():
+    # the multi-accumulator layout keeps a 16384-long sum within 3e-5 even for all-positive data (worst case for the
+    # tensor core's truncating accumulate); zero-mean data is an order of magnitude better
+    assert _gemm(256, 256, 16384) < 3e-5
+    assert _gemm(256, 256, 16384, positive=True) < 1e-4
+
+
+def test_forced_256_wide_tile():
+    assert _gemm(256, 512, 1024, engine=(256 << 8)) < 5e-5
+
+
+def test_invalid_arguments():
+    lib = capi.load()
+    assert lib.myea_b200_gemm_nt(0, 0, 0, 4, 4, None, None, None, 0, None, 0) == -1

@@ -1,0 +1,121 @@
+"""GPU parity tests: every case of tests/cases.py runs through the C ABI on cuda:0 and is compared with the oracle
+(the compiled reference when oracle/_ref is present, else the numpy restatement) and with the committed golden vectors.
+Tolerance: 1e-4 max relative error per tensor (max |a-b| / max |b|) on derivatives, updated parameters and moments;
+sizes, index map, loss-term counts and accuracy hit counts bit-exact."""
+import os
+
+import numpy as np
+import pytest
+
+import cases
+from conftest import rel_err
+from myea_b200 import capi
+from myea_b200.net import Net
+from oracle import myea_oracle, ref
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4
+
+
+def _oracle(wl):
+    return ref.RefNet(wl.desc, wl.opt, threads=1) if ref.available() else myea_oracle.OracleNet(wl.desc, wl.opt)
+
+
+def _compare(out, want, tol=TOL):
+    assert list(out["sizes"]) == [int(x) for x in want["sizes"]]
+    assert np.array_equal(np.asarray(out["index_map"], np.int64), np.asarray(want["index_map"], np.int64))
+    for k in ("grad0", "grad1", "param0", "param1", "output_last", "m"):
+        assert rel_err(out[k], want[k]) < tol, (k, rel_err(out[k], want[k]))
+    for k in ("loss0", "loss1"):
+        assert abs(out[k][0] - want[k][0]) <= 1e-4 * abs(want[k][0]) + 1e-6
+        assert out[k][1] == want[k][1]
+        assert out[k][2] == want[k][2]
+    if "norm_mean_avg" in want:
+        assert rel_err(out["norm_mean_avg"], want["norm_mean_avg"]) < tol
+        assert rel_err(out["norm_sigma_avg"], want["norm_sigma_avg"]) < tol
+
+
+@pytest.mark.parametrize("name", sorted(cases.CASES))
+def test_step_matches_oracle(name):
+    wl = cases.CASES[name]()
+    gpu, cpu = Net(wl.desc, wl.opt), _oracle(wl)
+    out, want = cases.run_steps(gpu, wl), cases.run_steps(cpu, wl)
+    gpu.synchronize()
+    assert gpu.launches() > 0
+    _compare(out, want)
+    gpu.close(); cpu.close()
+
+
+@pytest.mark.parametrize("name", sorted(cases.CASES))
+def test_step_matches_golden(name, golden_dir):
+    path = os.path.join(golden_dir, name + ".npz")
+    if not os.path.exists(path):
+        pytest.skip("no golden fixture")
+    gold = np.load(path)
+    wl = cases.CASES[name]()
+    gpu = Net(wl.desc, wl.opt)
+    out = cases.run_steps(gpu, wl)
+    _compare(out, {k: gold[k] for k in gold.files})
+    gpu.close()
+
+
+@pytest.mark.parametrize("name", ["c1_small", "c2_small"])
+def test_fp32_fma_engine_matches_too(name, monkeypatch):
+    """the second GEMM engine (plain FP32 FMA) gives the same step: isolates tensor-core issues from everything else"""
+    monkeypatch.setenv("MYEA_B200_GEMM_ENGINE", "1")
+    wl = cases.CASES[name]()
+    gpu, cpu = Net(wl.desc, wl.opt), _oracle(wl)
+    _compare(cases.run_steps(gpu, wl), cases.run_steps(cpu, wl))
+    gpu.close(); cpu.close()
+
+
+def test_layer_errors_and_outputs_match_per_layer():
+    wl = cases.CASES["c2_small"]()
+    gpu, cpu = Net(wl.desc, wl.opt), _oracle(wl)
+    X, Y = wl.batch()
+    for net in (gpu, cpu):
+        wl.materialize(net)
+        net.forward(X); net.compute_error(Y); net.backward()
+    for l in range(1, len(wl.layers)):
+        assert rel_err(gpu.outputs(l), cpu.outputs(l)) < TOL
+        assert rel_err(gpu.errors(l), cpu.errors(l)) < TOL
+    gpu.close(); cpu.close()
+
+
+def test_inference_forward_matches():
+    wl = cases.CASES["mlp_bernoulli_amsbound_clip"]()
+    gpu, cpu = Net(wl.desc, wl.opt), _oracle(wl)
+    X, _ = wl.batch()
+    for net in (gpu, cpu):
+        wl.materialize(net)
+        net.forward(X, training=False)
+    last = len(wl.layers) - 1
+    assert rel_err(gpu.outputs(last), cpu.outputs(last)) < TOL
+    gpu.close(); cpu.close()
+
+
+def test_derivatives_accumulate_over_sub_batches():
+    """Update_Derivative_Weight adds into the derivative buffer; two passes before the update give twice the derivative"""
+    wl = cases.CASES["c1_small"]()
+    gpu = Net(wl.desc, wl.opt)
+    wl.materialize(gpu)
+    X, Y = wl.batch()
+    gpu.forward(X); gpu.compute_error(Y); gpu.backward(); gpu.update_derivative_weight()
+    g1 = gpu.get(capi.BUF_DERIVATIVES)
+    gpu.forward(X); gpu.compute_error(Y); gpu.backward(); gpu.update_derivative_weight()
+    g2 = gpu.get(capi.BUF_DERIVATIVES)
+    assert rel_err(g2, 2.0 * g1) < 1e-6
+    gpu.update_parameter()
+    assert not gpu.get(capi.BUF_DERIVATIVES).any()       # the optimizer zeroes the derivatives
+    gpu.close()
+
+
+def test_bad_calls_return_status_not_crash():
+    wl = cases.CASES["c1_small"]()
+    gpu = Net(wl.desc, wl.opt)
+    lib = gpu.lib
+    X, _ = wl.batch()
+    assert lib.myea_b200_forward(gpu.h, wl.B + 1, X.ctypes.data, 1) == -1          # wrong batch
+    assert lib.myea_b200_set_mask_bernoulli(gpu.h, 1, X.ctypes.data, 3) == -1      # layer without a mask
+    assert b"mask" in lib.myea_b200_last_error(gpu.h)
+    gpu.close()
