@@ -176,6 +176,7 @@ __global__ void __launch_bounds__(256) activation_forward_kernel(const float *__
       if (col_scale != nullptr) pre = pre * col_scale[c + k] + col_shift[c + k];
       float y = af_fire(af, pre);
       if (mask != nullptr) y = mask[c + k] ? y * keep_scale : 0.f;
+      else if (keep_scale != 1.0f) y *= keep_scale;   // inference of plain Bernoulli dropout: every unit times p
       v[k] = y;
     }
     if (VEC == 4) {

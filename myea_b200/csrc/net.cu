@@ -448,11 +448,7 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
     return softmax_forward(net->ctx, L.summations, L.values, rows, L.n_out);
   }
   const uint8_t *mask = (net->training && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
-  float scale = net->training ? L.keep_scale : L.infer_scale;
-  if (!net->training && L.mask_bernoulli != nullptr && L.infer_scale != 1.f) {
-    // plain Bernoulli at inference: every unit times the retention probability; expressed as an all-ones mask
-    mask = nullptr;
-  }
+  const float scale = net->training ? (mask != nullptr ? L.keep_scale : 1.f) : L.infer_scale;
   RC(activation_forward(net->ctx, L.summations, L.values, rows, L.n_out, L.desc.type_activation_function, cs, ch, mask, scale));
   return MYEA_OK;
 }
