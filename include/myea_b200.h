@@ -219,6 +219,18 @@ uint64_t myea_b200_kernel_launches(myea_handle h);
 int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N, uint64_t K, const float *A, const float *B,
                       float *C, int accumulate, float *elapsed_ms, int repeats);
 
+/* No counterpart in the reference.  The same contraction for callers that cannot allocate device memory in the call
+ * path (a host that reserved all GPU memory up front, a tick-driven trading loop that cannot absorb cudaMalloc's
+ * device-wide synchronisation or its failure): C[M,N] (+)= A[M,K] * B[N,K]^T with A, B, C DEVICE pointers owned by
+ * the caller and the operand-panel scratch in a fixed 32 MiB array inside the library image, so the call performs no
+ * cudaMalloc / cudaFree.  Limit: 2*(M+N)*round_up(K,32)+64 floats <= 8 Mi floats, else MYEA_E_INVALID with a message in
+ * error_message (optional, error_capacity bytes).  Every GPU that loads the library holds the array until exit.  All
+ * calls share it: calls that overlap on the GPU race and must be serialised by the caller.  The first call on a
+ * device looks up the array's device address; make it outside any stream capture.  Returns after the stream is idle. */
+#define MYEA_STATIC_SCRATCH_BYTES (32u << 20)
+int myea_b200_gemm_nt_static(int device, uint64_t M, uint64_t N, uint64_t K, const float *device_A, const float *device_B,
+                             float *device_C, int accumulate, void *stream, char *error_message, size_t error_capacity);
+
 /* Per-kernel-class device time of the handle since the last call with reset!=0 (CUDA events on the handle's
  * stream); classes: 0 gemm, 1 split/pack, 2 normalization, 3 elementwise, 4 optimizer, 5 recurrent cell. */
 #define MYEA_TIMER_CLASSES 8

@@ -169,6 +169,8 @@ _PROTOS = {
     "myea_b200_kernel_launches": (C.c_uint64, [C.c_void_p]),
     "myea_b200_gemm_nt": (C.c_int, [C.c_int, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_int, C.POINTER(C.c_float), C.c_int]),
+    "myea_b200_gemm_nt_static": (C.c_int, [C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p,
+                                           C.c_int, C.c_void_p, C.c_char_p, C.c_size_t]),
     "myea_b200_profile": (C.c_int, [C.c_void_p, C.c_int]),
     "myea_b200_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64),
                                          C.POINTER(C.c_double), C.c_int]),
