@@ -100,6 +100,13 @@ struct Operand {
   const float *ptr = nullptr;
   long long rows = 0, k = 0;
   long long stride_r = 0, stride_k = 0;
+  const float *lo = nullptr;  // optional second addend with the same strides (value = ptr[..] + lo[..]); FMA engine only
+};
+
+// K-major hi / lo panels of one operand, pitch kp floats (a multiple of 32): what the tensor-core kernel reads with TMA.
+struct Panels {
+  float *hi = nullptr, *lo = nullptr;
+  long long rows = 0, k = 0, kp = 0;
 };
 
 struct GemmScratch {   // hi/lo K-major panels of both operands, reused by every contraction of a handle
@@ -108,6 +115,12 @@ struct GemmScratch {   // hi/lo K-major panels of both operands, reused by every
 };
 
 size_t gemm_scratch_floats(long long M, long long N, long long K);
+size_t panel_floats(long long rows, long long k);
+Panels panels_at(float *mem, long long rows, long long k);
+int gemm_prepare(Context &ctx, const Operand &op, float *mem, Panels *out);
+int gemm_prepare_into(Context &ctx, const Operand &op, const Panels &dst, long long row_offset, long long k_offset);
+int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, const Panels &B, long long b_row0, long long N,
+                const Epilogue &epi);
 // Launches split kernels + the tensor-core kernel (engine 0) or the FP32 FMA kernel (engine 1) on ctx.stream.
 int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &epi, const GemmScratch &scratch);
 

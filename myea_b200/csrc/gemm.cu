@@ -353,10 +353,10 @@ __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
   lo = round_tf32(x - hi);
 }
 
-// source already K-major (stride_k == 1)
+// source already K-major (stride_k == 1); writes columns [0, round_up(k, 4)) of every panel row (pitch kp)
 __global__ void split_rows_kernel(const float *__restrict__ src, long long stride_r, long long rows, long long k, long long kp,
                                   float *__restrict__ hi, float *__restrict__ lo) {
-  const long long kq = kp >> 2;  // float4 groups per panel row
+  const long long kq = (k + 3) >> 2;  // float4 groups written per panel row
   const long long total = rows * kq;
   const bool vec = ((stride_r & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
@@ -394,7 +394,7 @@ __global__ void split_transpose_kernel(const float *__restrict__ src, long long 
   __syncthreads();
   for (int j = threadIdx.y; j < 32; j += 8) {
     const long long rr = r0 + j, kk = k0 + threadIdx.x;
-    if (rr < rows && kk < kp) {
+    if (rr < rows && kk < k) {
       float h, l;
       split_tf32(tile[threadIdx.x][j], h, l);
       hi[rr * kp + kk] = h;
@@ -417,10 +417,10 @@ __global__ void __launch_bounds__(256) gemm_fp32_fma_kernel(const Operand A, con
       int r, kk;
       if (A.stride_k == 1) { r = i >> 4; kk = i & 15; } else { kk = i >> 6; r = i & 63; }
       const long long m = m0 + r, k = k0 + kk;
-      sa[kk][r] = (m < dims.M && k < dims.K) ? A.ptr[m * A.stride_r + k * A.stride_k] : 0.f;
+      sa[kk][r] = (m < dims.M && k < dims.K) ? A.ptr[m * A.stride_r + k * A.stride_k] + (A.lo ? A.lo[m * A.stride_r + k * A.stride_k] : 0.f) : 0.f;
       if (B.stride_k == 1) { r = i >> 4; kk = i & 15; } else { kk = i >> 6; r = i & 63; }
       const long long n = n0 + r;
-      sb[kk][r] = (n < dims.N && k0 + kk < dims.K) ? B.ptr[n * B.stride_r + (k0 + kk) * B.stride_k] : 0.f;
+      sb[kk][r] = (n < dims.N && k0 + kk < dims.K) ? B.ptr[n * B.stride_r + (k0 + kk) * B.stride_k] + (B.lo ? B.lo[n * B.stride_r + (k0 + kk) * B.stride_k] : 0.f) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -479,17 +479,40 @@ size_t gemm_scratch_floats(long long M, long long N, long long K) {
   return static_cast<size_t>(2 * (M + N) * kp) + 64;
 }
 
-static int split_operand(Context &ctx, const Operand &op, long long kp, float *hi, float *lo) {
+size_t panel_floats(long long rows, long long k) { return static_cast<size_t>(2 * rows * round_up(k, BK)); }
+
+Panels panels_at(float *mem, long long rows, long long k) {
+  Panels p;
+  p.rows = rows;
+  p.k = k;
+  p.kp = round_up(k, BK);
+  p.hi = mem;
+  p.lo = mem + rows * p.kp;
+  return p;
+}
+
+// Writes `op` (rows x k) into the region of `dst` that starts at (row_offset, k_offset): several sources can be
+// fused into one panel set (the four LSTM gate matrices side by side, for instance).
+int gemm_prepare_into(Context &ctx, const Operand &op, const Panels &dst, long long row_offset, long long k_offset) {
+  if (op.rows <= 0 || op.k <= 0 || row_offset + op.rows > dst.rows || k_offset + op.k > dst.k || (k_offset & 3) != 0) return MYEA_E_INVALID;
+  float *hi = dst.hi + row_offset * dst.kp + k_offset, *lo = dst.lo + row_offset * dst.kp + k_offset;
+  ctx.begin(TC_SPLIT);
   if (op.stride_k == 1) {
-    const long long total = op.rows * (kp >> 2);
+    const long long total = op.rows * ((op.k + 3) >> 2);
     int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
     if (blocks < 1) blocks = 1;
-    split_rows_kernel<<<blocks, 256, 0, ctx.stream>>>(op.ptr, op.stride_r, op.rows, op.k, kp, hi, lo);
+    split_rows_kernel<<<blocks, 256, 0, ctx.stream>>>(op.ptr, op.stride_r, op.rows, op.k, dst.kp, hi, lo);
   } else {
-    dim3 grid(static_cast<unsigned>((op.rows + 31) / 32), static_cast<unsigned>(kp / 32));
-    split_transpose_kernel<<<grid, dim3(32, 8), 0, ctx.stream>>>(op.ptr, op.stride_k, op.rows, op.k, kp, hi, lo);
+    dim3 grid(static_cast<unsigned>((op.rows + 31) / 32), static_cast<unsigned>((op.k + 31) / 32));
+    split_transpose_kernel<<<grid, dim3(32, 8), 0, ctx.stream>>>(op.ptr, op.stride_k, op.rows, op.k, dst.kp, hi, lo);
   }
+  ctx.end(TC_SPLIT);
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
+int gemm_prepare(Context &ctx, const Operand &op, float *mem, Panels *out) {
+  *out = panels_at(mem, op.rows, op.k);
+  return gemm_prepare_into(ctx, op, *out, 0, 0);
 }
 
 template <int BN, int STAGES>
@@ -507,44 +530,52 @@ static int launch_tcgen05(Context &ctx, const CUtensorMap maps[4], const GemmDim
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
-int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &epi, const GemmScratch &scratch) {
-  GemmDims dims{static_cast<int>(A.rows), static_cast<int>(B.rows), static_cast<int>(A.k)};
-  if (A.k != B.k || dims.M <= 0 || dims.N <= 0 || dims.K <= 0) return MYEA_E_INVALID;
-  const double flops = 2.0 * dims.M * dims.N * static_cast<double>(dims.K);
+// C (+)= A * B^T on operands whose panels are already in place; (row0, rows) select a row range of each panel set.
+int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, const Panels &B, long long b_row0, long long N,
+                const Epilogue &epi) {
+  if (A.k != B.k || M <= 0 || N <= 0 || A.k <= 0 || a_row0 < 0 || b_row0 < 0 || a_row0 + M > A.rows || b_row0 + N > B.rows) return MYEA_E_INVALID;
+  GemmDims dims{static_cast<int>(M), static_cast<int>(N), static_cast<int>(A.k)};
+  int rc;
   if (ctx.gemm_engine == 1) {
+    Operand oa{A.hi + a_row0 * A.kp, M, A.k, A.kp, 1, A.lo + a_row0 * A.kp};
+    Operand ob{B.hi + b_row0 * B.kp, N, B.k, B.kp, 1, B.lo + b_row0 * B.kp};
+    ctx.begin(TC_GEMM);
+    dim3 grid(static_cast<unsigned>((dims.N + 63) / 64), static_cast<unsigned>((dims.M + 63) / 64));
+    gemm_fp32_fma_kernel<<<grid, 256, 0, ctx.stream>>>(oa, ob, dims, epi);
+    ctx.end(TC_GEMM);
+    rc = cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+  } else {
+    const int bn = ctx.gemm_bn == 256 ? 256 : 128;  // 128: four accumulators of 128 columns, the accurate configuration
+    CUtensorMap maps[4];
+    const bool ok = make_panel_map(&maps[0], A.hi + a_row0 * A.kp, M, A.k, A.kp, BM) && make_panel_map(&maps[1], A.lo + a_row0 * A.kp, M, A.k, A.kp, BM) &&
+                    make_panel_map(&maps[2], B.hi + b_row0 * B.kp, N, B.k, B.kp, bn) && make_panel_map(&maps[3], B.lo + b_row0 * B.kp, N, B.k, B.kp, bn);
+    if (!ok) return MYEA_E_CUDA;
+    ctx.begin(TC_GEMM);
+    rc = (bn == 256) ? launch_tcgen05<256, 2>(ctx, maps, dims, epi) : launch_tcgen05<128, 3>(ctx, maps, dims, epi);
+    ctx.end(TC_GEMM);
+  }
+  ctx.gemm_flops += 2.0 * dims.M * dims.N * static_cast<double>(dims.K);
+  return rc;
+}
+
+int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &epi, const GemmScratch &scratch) {
+  if (A.k != B.k || A.rows <= 0 || B.rows <= 0 || A.k <= 0) return MYEA_E_INVALID;
+  if (ctx.gemm_engine == 1) {  // the FP32 FMA engine reads the fp32 sources directly
+    GemmDims dims{static_cast<int>(A.rows), static_cast<int>(B.rows), static_cast<int>(A.k)};
     ctx.begin(TC_GEMM);
     dim3 grid(static_cast<unsigned>((dims.N + 63) / 64), static_cast<unsigned>((dims.M + 63) / 64));
     gemm_fp32_fma_kernel<<<grid, 256, 0, ctx.stream>>>(A, B, dims, epi);
     ctx.end(TC_GEMM);
-    ctx.gemm_flops += flops;
+    ctx.gemm_flops += 2.0 * dims.M * dims.N * static_cast<double>(dims.K);
     return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
   }
-  const long long kp = round_up(dims.K, BK);
-  if (scratch.base == nullptr || scratch.floats < gemm_scratch_floats(dims.M, dims.N, dims.K)) return MYEA_E_INVALID;
+  if (scratch.base == nullptr || scratch.floats < gemm_scratch_floats(A.rows, B.rows, A.k)) return MYEA_E_INVALID;
   float *base = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(scratch.base) + 255) & ~static_cast<uintptr_t>(255));
-  float *a_hi = base, *a_lo = a_hi + dims.M * kp, *b_hi = a_lo + dims.M * kp, *b_lo = b_hi + dims.N * kp;
-  ctx.begin(TC_SPLIT);
-  int rc = split_operand(ctx, A, kp, a_hi, a_lo);
-  if (rc == MYEA_OK) rc = split_operand(ctx, B, kp, b_hi, b_lo);
-  ctx.end(TC_SPLIT, 2);
+  Panels pa, pb;
+  int rc = gemm_prepare(ctx, A, base, &pa);
+  if (rc == MYEA_OK) rc = gemm_prepare(ctx, B, base + panel_floats(A.rows, A.k), &pb);
   if (rc != MYEA_OK) return rc;
-
-  // N tile: 256 columns unless that leaves SMs idle and 128 fills them better
-  int bn = ctx.gemm_bn;
-  if (bn == 0) {
-    const long long tiles256 = ((dims.N + 255) / 256) * ((dims.M + BM - 1) / BM);
-    (void)tiles256;
-    bn = 128;  // four accumulators of 128 columns: the accurate configuration
-  }
-  CUtensorMap maps[4];
-  bool ok = make_panel_map(&maps[0], a_hi, dims.M, dims.K, kp, BM) && make_panel_map(&maps[1], a_lo, dims.M, dims.K, kp, BM) &&
-            make_panel_map(&maps[2], b_hi, dims.N, dims.K, kp, bn) && make_panel_map(&maps[3], b_lo, dims.N, dims.K, kp, bn);
-  if (!ok) return MYEA_E_CUDA;
-  ctx.begin(TC_GEMM);
-  rc = (bn == 256) ? launch_tcgen05<256, 2>(ctx, maps, dims, epi) : launch_tcgen05<128, 3>(ctx, maps, dims, epi);
-  ctx.end(TC_GEMM);
-  ctx.gemm_flops += flops;
-  return rc;
+  return gemm_panels(ctx, pa, 0, A.rows, pb, 0, B.rows, epi);
 }
 
 }  // namespace myea

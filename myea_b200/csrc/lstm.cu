@@ -1,12 +1,511 @@
-// placeholder, replaced below
+// LSTM layer with peephole connections: forward pass, back-propagation through time, derivative-weight accumulation.
+//
+// Reference routines (Source_Files/Neural_Network/): forward Forward_Pass__LSTM__Gates_CIFO / __Gates_CIF_AF_State
+// (and its Zoneout twin) / __States_AF / __Output (Neural_Network__Recurrent_Forward_Pass__OpenMP.cpp:859-1582), BPTT
+// Backward_Pass__LSTM_Derivative__Output / __Cell_State_AF / __Gates_CIF_AF_State
+// (Neural_Network__Recurrent_Backward_Pass__OpenMP.cpp:1130-1604), error to the previous layer Backward_Pass__LSTM (:1024-1120),
+// Recurrent__Update_Derivative_Weight__LSTM + bias (Neural_Network__Recurrent_Update_Derivative_Weight__OpenMP.cpp:492-776).
+//
+// One cell per block (what every configuration uses).  Per step, with prev = the step before in the layer's direction:
+//   z = tanh(Wz x + Rz h_prev + bz)          i = sig(Wi x + Ri h_prev + bi + pi*c_prev)
+//   f = sig(Wf x + Rf h_prev + bf + pf*c_prev)   c = z*i + f*c_prev        (first step: no recurrent terms, no f)
+//   o = sig(Wo x + Ro h_prev + bo + po*c)    h = tanh(c)*o
+// Zoneout (forward only, as in the reference): where the state mask is false c = c_prev (0 at the first step), where
+// the output mask is false h = h_prev (0 at the first step); the backward pass ignores the masks.
+//
+// Mapping to the GPU: the four gate matrices stay in the reference's interleaved per-block parameter layout and are read
+// through strided operands into fused K-major panels ([4C, in], [4C, C] and their transposes), so the input projection
+// of all T steps is ONE tensor-core contraction [T*B, in] x [in, 4C], each recurrent step is one [B, C] x [C, 4C]
+// contraction plus one fused cell kernel (gate nonlinearities, peepholes, cell-state recurrence, zoneout select), each
+// BPTT step is one [B, 4C] x [4C, C] contraction accumulated into the output error plus one fused cell-backward kernel,
+// and the weight derivatives are contractions over K = T*B.  Bias and peephole derivatives are column reductions.
 #include "net.cuh"
+
+#include <algorithm>
+
 namespace myea {
-int lstm_create(myea_b200_net *, LayerPlan &) { return MYEA_E_UNSUPPORTED; }
-void lstm_destroy(LayerPlan &) {}
-int lstm_forward(myea_b200_net *, LayerPlan &, const float *, long long) { return MYEA_E_UNSUPPORTED; }
-int lstm_backward(myea_b200_net *, LayerPlan &) { return MYEA_E_UNSUPPORTED; }
-int lstm_backward_to_input(myea_b200_net *, LayerPlan &, float *, const LayerPlan &) { return MYEA_E_UNSUPPORTED; }
-int lstm_update_derivative_weight(myea_b200_net *, LayerPlan &, const float *, long long) { return MYEA_E_UNSUPPORTED; }
-int lstm_set_zoneout(myea_b200_net *, LayerPlan &, const uint8_t *, const uint8_t *, uint64_t) { return MYEA_E_UNSUPPORTED; }
-float *lstm_output_errors(LayerPlan &) { return nullptr; }
+
+struct LstmDir {
+  long long w_base = 0;   // first parameter of this direction's blocks
+  long long b_base = 0;   // [bz (C) | bi (C) | bf (C) | bo (C)]
+  float *gates_in = nullptr;  // [T*B, 4C] input projection + bias, columns [z | i | f | o]
+  float *act = nullptr;       // [T*B, 4C] activated gates
+  float *cstate = nullptr, *cact = nullptr;  // [T*B, C] cell state, tanh(cell state)
+  float *dgates = nullptr;    // [T*B, 4C] error w.r.t. the gate summations
+  float *dcstate = nullptr;   // [T*B, C]
+  uint8_t *zone_state = nullptr, *zone_output = nullptr;  // [T, C], 1 = compute, 0 = keep the previous value
+};
+
+struct LstmPlan {
+  int dirs = 1;
+  long long C = 0, n_in = 0, stride = 0;
+  bool zoneout = false;
+  LstmDir d[2];
+  float *s_rec = nullptr;      // [B, 4C] recurrent projection of the current step
+  float *panel_mem = nullptr;  // W_rec panels, their transpose, per-step operand panels
+  size_t off_wrec = 0, off_wrect = 0, off_step = 0;
+  float *partial = nullptr;    // [7][chunks][C]
+};
+
+// offsets of the gate matrices inside one block of the parameter buffer (Prepare__Connections__LSTM)
+struct BlockOffsets {
+  long long z_in, z_rec, in[3], rec[3], peep;  // in/rec: input, forget, output gate
+};
+static BlockOffsets block_offsets(long long n_in, long long C) {
+  BlockOffsets o;
+  o.z_in = 0;
+  o.z_rec = n_in;
+  o.in[0] = n_in + C; o.in[1] = 2 * n_in + C; o.in[2] = 3 * n_in + C;
+  o.rec[0] = 4 * n_in + C; o.rec[1] = 4 * n_in + 2 * C; o.rec[2] = 4 * n_in + 3 * C;
+  o.peep = 4 * n_in + 4 * C;
+  return o;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// fused cell kernels
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float tanh_ref(float x) { return 2.0f / (1.0f + expf(-2.0f * x)) - 1.0f; }
+
+struct CellFwd {
+  const float *gates_in;  // rows of step t: [B, 4C]
+  const float *s_rec;     // [B, 4C] or null at the first step
+  const float *c_prev;    // [B, C] or null
+  const float *h_prev;    // [B, ldh] or null
+  const float *peep;      // parameter pointer of block 0's p_i; block c at + c*stride, p_f +1, p_o +2
+  long long stride;
+  float *act, *cstate, *cact, *h;  // rows of step t
+  long long ldh;
+  const uint8_t *zone_state, *zone_output;  // [C] of step t, or null
+  long long B, C;
+};
+
+__global__ void __launch_bounds__(256) lstm_cell_forward_kernel(const CellFwd p) {
+  const long long total = p.B * p.C;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long b = i / p.C, c = i - b * p.C;
+    const float *gi = p.gates_in + b * 4 * p.C;
+    const bool first = p.s_rec == nullptr;
+    const float *sr = first ? nullptr : p.s_rec + b * 4 * p.C;
+    const float pi = p.peep[c * p.stride], pf = p.peep[c * p.stride + 1], po = p.peep[c * p.stride + 2];
+    const float cp = first ? 0.f : p.c_prev[b * p.C + c];
+    const float sz = gi[c] + (first ? 0.f : sr[c]);
+    const float si = gi[p.C + c] + (first ? 0.f : sr[p.C + c] + pi * cp);
+    const float z = tanh_ref(sz);
+    const float ig = sigmoid_ref(si);
+    float fg = 0.f;
+    float cs = z * ig;
+    if (!first) {
+      fg = sigmoid_ref(gi[2 * p.C + c] + sr[2 * p.C + c] + pf * cp);
+      cs += fg * cp;
+    }
+    if (p.zone_state != nullptr && !p.zone_state[c]) cs = cp;  // cp is 0 at the first step
+    const float a = tanh_ref(cs);
+    const float og = sigmoid_ref(gi[3 * p.C + c] + (first ? 0.f : sr[3 * p.C + c]) + po * cs);
+    float h = a * og;
+    if (p.zone_output != nullptr && !p.zone_output[c]) h = first ? 0.f : p.h_prev[b * p.ldh + c];
+    float *act = p.act + b * 4 * p.C;
+    act[c] = z; act[p.C + c] = ig; act[2 * p.C + c] = fg; act[3 * p.C + c] = og;
+    p.cstate[b * p.C + c] = cs;
+    p.cact[b * p.C + c] = a;
+    p.h[b * p.ldh + c] = h;
+  }
+}
+
+struct CellBwd {
+  const float *dh;        // [B, ldh] error on the outputs of step t (recurrent contribution already added)
+  long long ldh;
+  const float *act, *cact;     // step t
+  const float *c_prev;         // cell state of the previous step in the layer's direction, null at the first step
+  const float *act_next, *dgates_next, *dc_next;  // step after t in the layer's direction, null at the last step
+  const float *peep;
+  long long stride;
+  float *dgates, *dcstate;     // step t
+  long long B, C;
+};
+
+__global__ void __launch_bounds__(256) lstm_cell_backward_kernel(const CellBwd p) {
+  const long long total = p.B * p.C;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long b = i / p.C, c = i - b * p.C;
+    const float *act = p.act + b * 4 * p.C;
+    const float z = act[c], ig = act[p.C + c], fg = act[2 * p.C + c], og = act[3 * p.C + c];
+    const float a = p.cact[b * p.C + c];
+    const float pi = p.peep[c * p.stride], pf = p.peep[c * p.stride + 1], po = p.peep[c * p.stride + 2];
+    const float dh = p.dh[b * p.ldh + c];
+    const float d_o = og * (1.f - og) * (dh * a);
+    float dc = dh * og * (1.f - a * a);
+    dc += po * d_o;
+    if (p.dgates_next != nullptr) {
+      const float *dn = p.dgates_next + b * 4 * p.C;
+      dc += pi * dn[p.C + c];
+      dc += pf * dn[2 * p.C + c];
+      dc += p.dc_next[b * p.C + c] * p.act_next[b * 4 * p.C + 2 * p.C + c];
+    }
+    const float dz = dc * ig * (1.f - z * z);
+    const float di = (dc * z) * (ig * (1.f - ig));
+    const float df = p.c_prev != nullptr ? (dc * p.c_prev[b * p.C + c]) * (fg * (1.f - fg)) : 0.f;
+    float *dg = p.dgates + b * 4 * p.C;
+    dg[c] = dz; dg[p.C + c] = di; dg[2 * p.C + c] = df; dg[3 * p.C + c] = d_o;
+    p.dcstate[b * p.C + c] = dc;
+  }
+}
+
+// Bias and peephole derivatives: per cell c, over all rows r of dgates [R, 4C]
+//   out0..3 = sum dz, di, df, do ; out4 = sum di[r]*c[r - shift], out5 = sum df[r]*c[r - shift] (rows whose partner
+//   exists), out6 = sum do[r]*c[r].   partial[k][chunk][c].
+__global__ void __launch_bounds__(256) lstm_bias_peephole_reduce_kernel(const float *__restrict__ dgates, const float *__restrict__ cstate,
+                                                                        long long R, long long C, long long shift, int chunks,
+                                                                        float *__restrict__ partial) {
+  __shared__ float sh[7][8][33];
+  const int cl = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const long long c = static_cast<long long>(blockIdx.x) * 32 + cl;
+  const long long per = (R + chunks - 1) / chunks;
+  const long long r0 = blockIdx.y * per, r1 = min(R, r0 + per);
+  float acc[7] = {0, 0, 0, 0, 0, 0, 0};
+  if (c < C) {
+    for (long long r = r0 + rl; r < r1; r += 8) {
+      const float *dg = dgates + r * 4 * C;
+      const float dz = dg[c], di = dg[C + c], df = dg[2 * C + c], d_o = dg[3 * C + c];
+      acc[0] += dz; acc[1] += di; acc[2] += df; acc[3] += d_o;
+      const long long rp = r - shift;
+      if (rp >= 0 && rp < R) {
+        const float cs = cstate[rp * C + c];
+        acc[4] = fmaf(di, cs, acc[4]);
+        acc[5] = fmaf(df, cs, acc[5]);
+      }
+      acc[6] = fmaf(d_o, cstate[r * C + c], acc[6]);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 7; ++k) sh[k][rl][cl] = acc[k];
+  __syncthreads();
+  if (rl == 0 && c < C) {
+#pragma unroll
+    for (int k = 0; k < 7; ++k) {
+      float t = 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) t += sh[k][r][cl];
+      partial[(static_cast<long long>(k) * chunks + blockIdx.y) * C + c] = t;
+    }
+  }
+}
+
+__global__ void lstm_bias_peephole_finalize_kernel(const float *__restrict__ partial, int chunks, long long C, float *d_bias,
+                                                   float *d_peep, long long stride) {
+  const long long c = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (c >= C) return;
+  float t[7];
+#pragma unroll
+  for (int k = 0; k < 7; ++k) {
+    t[k] = 0.f;
+    for (int ch = 0; ch < chunks; ++ch) t[k] += partial[(static_cast<long long>(k) * chunks + ch) * C + c];
+  }
+  // atomics: with the reference's shifted bias base the output-gate slots alias the next layer's bias slots, which another
+  // kernel of the same stream also accumulates into; stream order already serialises them, the atomics are belt and braces
+  atomicAdd(&d_bias[c], t[0]);
+  atomicAdd(&d_bias[C + c], t[1]);
+  atomicAdd(&d_bias[2 * C + c], t[2]);
+  atomicAdd(&d_bias[3 * C + c], t[3]);
+  d_peep[c * stride] += t[4];
+  d_peep[c * stride + 1] += t[5];
+  d_peep[c * stride + 2] += t[6];
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// plan
+// ---------------------------------------------------------------------------------------------------------
+template <typename T>
+static int lalloc(myea_b200_net *net, T **p, size_t count) {
+  void *q = nullptr;
+  const size_t bytes = std::max<size_t>(count, 1) * sizeof(T);
+  if (cudaMalloc(&q, bytes) != cudaSuccess) { net->ctx.error = "cudaMalloc failed (LSTM buffers)"; return MYEA_E_CUDA; }
+  net->allocations.push_back(q);
+  if (cudaMemsetAsync(q, 0, bytes, net->ctx.stream) != cudaSuccess) return MYEA_E_CUDA;
+  *p = static_cast<T *>(q);
+  return MYEA_OK;
+}
+
+#define LRC(expr) do { int rc__ = (expr); if (rc__ != MYEA_OK) return rc__; } while (0)
+
+int lstm_create(myea_b200_net *net, LayerPlan &L) {
+  const long long cpb = std::max<long long>(1, static_cast<long long>(L.desc.unit_parameters[1]));
+  if (cpb != 1) { net->ctx.error = "LSTM blocks with more than one cell are not built"; return MYEA_E_UNSUPPORTED; }
+  LstmPlan *P = new LstmPlan();
+  L.lstm = P;
+  P->dirs = L.desc.use_bidirectional ? 2 : 1;
+  P->C = L.n_out / P->dirs;
+  P->n_in = L.n_in;
+  P->stride = static_cast<long long>(L.idx.block_stride);
+  if ((P->C & 3) != 0) { net->ctx.error = "LSTM width must be a multiple of 4"; return MYEA_E_UNSUPPORTED; }
+  P->zoneout = L.desc.type_dropout == MYEA_DROPOUT_ZONEOUT;
+  const long long rows = net->T * net->B, C = P->C;
+  // biases: the reference stores first_bias_connection_index already shifted by the number of cells and then reads
+  // [bz | bi | bf | bo] from it, so bo overlaps the next layer's bias slots.  Reproduced for the unidirectional layer;
+  // the bidirectional layer (no usable reference) uses its true, unshifted block, one [bz|bi|bf|bo] run per direction.
+  const long long fb = static_cast<long long>(L.idx.first_bias_connection_index);
+  for (int d = 0; d < P->dirs; ++d) {
+    LstmDir &D = P->d[d];
+    D.w_base = static_cast<long long>(L.idx.first_connection_index) + d * C * P->stride;
+    D.b_base = P->dirs == 1 ? fb : (fb - 2 * C) + d * 4 * C;
+    if (D.b_base + 4 * C > static_cast<long long>(net->total_parameters)) {
+      net->ctx.error = "LSTM output-gate bias would run past the parameter buffer (the next layer must be at least as wide as the LSTM layer)";
+      return MYEA_E_INVALID;
+    }
+    LRC(lalloc(net, &D.gates_in, rows * 4 * C));
+    LRC(lalloc(net, &D.act, rows * 4 * C));
+    LRC(lalloc(net, &D.cstate, rows * C));
+    LRC(lalloc(net, &D.cact, rows * C));
+    LRC(lalloc(net, &D.dgates, rows * 4 * C));
+    LRC(lalloc(net, &D.dcstate, rows * C));
+    if (P->zoneout) {
+      LRC(lalloc(net, &D.zone_state, net->T * C));
+      LRC(lalloc(net, &D.zone_output, net->T * C));
+      cudaMemsetAsync(D.zone_state, 1, net->T * C, net->ctx.stream);
+      cudaMemsetAsync(D.zone_output, 1, net->T * C, net->ctx.stream);
+    }
+  }
+  LRC(lalloc(net, &L.values, rows * L.n_out));
+  LRC(lalloc(net, &L.deriv, rows * L.n_out));
+  L.errors = L.deriv;
+  LRC(lalloc(net, &P->s_rec, net->B * 4 * C));
+  P->off_wrec = 0;
+  P->off_wrect = P->off_wrec + panel_floats(4 * C, C) + 64;
+  P->off_step = P->off_wrect + panel_floats(C, 4 * C) + 64;
+  LRC(lalloc(net, &P->panel_mem, P->off_step + panel_floats(net->B, 4 * C) + 64));
+  LRC(lalloc(net, &P->partial, static_cast<size_t>(7) * net->reduce_chunks * C));
+  // one-shot contractions use the handle's scratch: make sure it is large enough
+  size_t need = 0;
+  need = std::max(need, panel_floats(rows, L.n_in) + panel_floats(4 * C, L.n_in));            // input projection
+  need = std::max(need, panel_floats(rows, 4 * C) + panel_floats(L.n_in, 4 * C));            // error to the previous layer
+  need = std::max(need, panel_floats(4 * C, rows) + panel_floats(std::max(L.n_in, C), rows));  // weight derivatives
+  net->scratch.floats = std::max(net->scratch.floats, need + 256);
+  return MYEA_OK;
+}
+
+void lstm_destroy(LayerPlan &L) {
+  delete L.lstm;
+  L.lstm = nullptr;
+}
+
+float *lstm_output_errors(LayerPlan &L) { return L.deriv; }
+
+int lstm_set_zoneout(myea_b200_net *net, LayerPlan &L, const uint8_t *state, const uint8_t *output, uint64_t count) {
+  LstmPlan *P = L.lstm;
+  if (P == nullptr || !P->zoneout || count != static_cast<uint64_t>(net->T * P->C * P->dirs)) {
+    net->ctx.error = "layer has no zoneout masks of that size";
+    return MYEA_E_INVALID;
+  }
+  // masks arrive as [T][dirs*C]
+  for (int d = 0; d < P->dirs; ++d) {
+    if (cudaMemcpy2DAsync(P->d[d].zone_state, P->C, state + d * P->C, P->dirs * P->C, P->C, net->T, cudaMemcpyHostToDevice, net->ctx.stream) != cudaSuccess ||
+        cudaMemcpy2DAsync(P->d[d].zone_output, P->C, output + d * P->C, P->dirs * P->C, P->C, net->T, cudaMemcpyHostToDevice, net->ctx.stream) != cudaSuccess)
+      return MYEA_E_CUDA;
+  }
+  return cudaStreamSynchronize(net->ctx.stream) == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
+static float *aligned_scratch(myea_b200_net *net) {
+  return reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(net->scratch.base) + 255) & ~static_cast<uintptr_t>(255));
+}
+
+static int cell_blocks(long long total) { return static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, 148 * 8))); }
+
+// ---------------------------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------------------------
+int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long n_in) {
+  LstmPlan *P = L.lstm;
+  Context &ctx = net->ctx;
+  const long long T = net->T, B = net->B, rows = T * B, C = P->C, ldh = L.n_out;
+  const BlockOffsets off = block_offsets(n_in, C);
+  float *scratch = aligned_scratch(net);
+  Panels px;
+  LRC(gemm_prepare(ctx, Operand{input, rows, n_in, n_in, 1}, scratch, &px));
+  for (int d = 0; d < P->dirs; ++d) {
+    LstmDir &D = P->d[d];
+    const float *w = net->params + D.w_base;
+    // fused input panel [4C, in], gate order z, i, f, o
+    Panels pwin = panels_at(scratch + panel_floats(rows, n_in), 4 * C, n_in);
+    LRC(gemm_prepare_into(ctx, Operand{w + off.z_in, C, n_in, P->stride, 1}, pwin, 0, 0));
+    for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.in[g], C, n_in, P->stride, 1}, pwin, (g + 1) * C, 0));
+    Epilogue e;
+    e.C = D.gates_in;
+    e.ldc = 4 * C;
+    e.bias = net->params + D.b_base;
+    LRC(gemm_panels(ctx, px, 0, rows, pwin, 0, 4 * C, e));
+    // fused recurrent panel [4C, C]
+    Panels pwrec = panels_at(P->panel_mem + P->off_wrec, 4 * C, C);
+    LRC(gemm_prepare_into(ctx, Operand{w + off.z_rec, C, C, P->stride, 1}, pwrec, 0, 0));
+    for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.rec[g], C, C, P->stride, 1}, pwrec, (g + 1) * C, 0));
+    const bool zone = P->zoneout && net->training;
+    for (long long s = 0; s < T; ++s) {
+      const long long t = d == 0 ? s : T - 1 - s;
+      const long long tp = d == 0 ? t - 1 : t + 1;
+      float *h_t = L.values + t * B * ldh + d * C;
+      CellFwd cf;
+      cf.gates_in = D.gates_in + t * B * 4 * C;
+      cf.s_rec = nullptr; cf.c_prev = nullptr; cf.h_prev = nullptr;
+      if (s > 0) {
+        const float *h_prev = L.values + tp * B * ldh + d * C;
+        Panels ph;
+        LRC(gemm_prepare(ctx, Operand{h_prev, B, C, ldh, 1}, P->panel_mem + P->off_step, &ph));
+        Epilogue er;
+        er.C = P->s_rec;
+        er.ldc = 4 * C;
+        LRC(gemm_panels(ctx, ph, 0, B, pwrec, 0, 4 * C, er));
+        cf.s_rec = P->s_rec;
+        cf.c_prev = D.cstate + tp * B * C;
+        cf.h_prev = h_prev;
+      }
+      cf.peep = w + off.peep;
+      cf.stride = P->stride;
+      cf.act = D.act + t * B * 4 * C;
+      cf.cstate = D.cstate + t * B * C;
+      cf.cact = D.cact + t * B * C;
+      cf.h = h_t;
+      cf.ldh = ldh;
+      cf.zone_state = zone ? D.zone_state + t * C : nullptr;
+      cf.zone_output = zone ? D.zone_output + t * C : nullptr;
+      cf.B = B; cf.C = C;
+      ctx.begin(TC_RECURRENT);
+      lstm_cell_forward_kernel<<<cell_blocks(B * C), 256, 0, ctx.stream>>>(cf);
+      ctx.end(TC_RECURRENT);
+    }
+  }
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// BPTT: L.deriv holds the error arriving on the layer's outputs from its consumers
+// ---------------------------------------------------------------------------------------------------------
+int lstm_backward(myea_b200_net *net, LayerPlan &L) {
+  LstmPlan *P = L.lstm;
+  Context &ctx = net->ctx;
+  const long long T = net->T, B = net->B, C = P->C, ldh = L.n_out, n_in = P->n_in;
+  const BlockOffsets off = block_offsets(n_in, C);
+  for (int d = 0; d < P->dirs; ++d) {
+    LstmDir &D = P->d[d];
+    const float *w = net->params + D.w_base;
+    // transposed recurrent panel [C (unit j of h), K = 4C (gate, cell)]
+    Panels pwt = panels_at(P->panel_mem + P->off_wrect, C, 4 * C);
+    LRC(gemm_prepare_into(ctx, Operand{w + off.z_rec, C, C, 1, P->stride}, pwt, 0, 0));
+    for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.rec[g], C, C, 1, P->stride}, pwt, 0, (g + 1) * C));
+    for (long long s = 0; s < T; ++s) {
+      const long long t = d == 0 ? T - 1 - s : s;      // walk against the layer's direction
+      const long long tn = d == 0 ? t + 1 : t - 1;     // the step after t in the layer's direction
+      const long long tp = d == 0 ? t - 1 : t + 1;     // the step before t
+      float *dh_t = L.deriv + t * B * ldh + d * C;
+      if (s > 0) {
+        Panels pd;
+        LRC(gemm_prepare(ctx, Operand{D.dgates + tn * B * 4 * C, B, 4 * C, 4 * C, 1}, P->panel_mem + P->off_step, &pd));
+        Epilogue e;
+        e.C = dh_t;
+        e.ldc = ldh;
+        e.accumulate = 1;
+        LRC(gemm_panels(ctx, pd, 0, B, pwt, 0, C, e));
+      }
+      CellBwd cb;
+      cb.dh = dh_t;
+      cb.ldh = ldh;
+      cb.act = D.act + t * B * 4 * C;
+      cb.cact = D.cact + t * B * C;
+      cb.c_prev = (tp >= 0 && tp < T) ? D.cstate + tp * B * C : nullptr;
+      cb.act_next = s > 0 ? D.act + tn * B * 4 * C : nullptr;
+      cb.dgates_next = s > 0 ? D.dgates + tn * B * 4 * C : nullptr;
+      cb.dc_next = s > 0 ? D.dcstate + tn * B * C : nullptr;
+      cb.peep = w + off.peep;
+      cb.stride = P->stride;
+      cb.dgates = D.dgates + t * B * 4 * C;
+      cb.dcstate = D.dcstate + t * B * C;
+      cb.B = B; cb.C = C;
+      ctx.begin(TC_RECURRENT);
+      lstm_cell_backward_kernel<<<cell_blocks(B * C), 256, 0, ctx.stream>>>(cb);
+      ctx.end(TC_RECURRENT);
+    }
+  }
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
+// error of the LSTM layer L propagated to the outputs of the layer feeding it: prev_deriv [T*B, n_in] = sum over
+// directions of dgates [T*B, 4C] * W_in [4C, n_in]
+int lstm_backward_to_input(myea_b200_net *net, LayerPlan &L, float *prev_deriv, const LayerPlan &prev) {
+  LstmPlan *P = L.lstm;
+  Context &ctx = net->ctx;
+  const long long rows = net->T * net->B, C = P->C, n_in = P->n_in;
+  if (prev.n_out != n_in) return MYEA_E_INVALID;
+  const BlockOffsets off = block_offsets(n_in, C);
+  float *scratch = aligned_scratch(net);
+  for (int d = 0; d < P->dirs; ++d) {
+    LstmDir &D = P->d[d];
+    const float *w = net->params + D.w_base;
+    Panels pd;
+    LRC(gemm_prepare(ctx, Operand{D.dgates, rows, 4 * C, 4 * C, 1}, scratch, &pd));
+    Panels pwt = panels_at(scratch + panel_floats(rows, 4 * C), n_in, 4 * C);  // [n_in, K = 4C]
+    LRC(gemm_prepare_into(ctx, Operand{w + off.z_in, n_in, C, 1, P->stride}, pwt, 0, 0));
+    for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.in[g], n_in, C, 1, P->stride}, pwt, 0, (g + 1) * C));
+    Epilogue e;
+    e.C = prev_deriv;
+    e.ldc = n_in;
+    e.accumulate = d > 0 ? 1 : 0;
+    LRC(gemm_panels(ctx, pd, 0, rows, pwt, 0, n_in, e));
+  }
+  return MYEA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// derivative weights: dW_in,g += dg^T x ; dW_rec,g += dg(next step)^T h ; peepholes and biases by column reductions
+// ---------------------------------------------------------------------------------------------------------
+int lstm_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float *input, long long n_in) {
+  LstmPlan *P = L.lstm;
+  Context &ctx = net->ctx;
+  const long long T = net->T, B = net->B, rows = T * B, C = P->C, ldh = L.n_out;
+  const BlockOffsets off = block_offsets(n_in, C);
+  float *scratch = aligned_scratch(net);
+  for (int d = 0; d < P->dirs; ++d) {
+    LstmDir &D = P->d[d];
+    float *gw = net->grads + D.w_base;
+    // input weights: K = all T*B rows
+    Panels pdt, pxt;
+    LRC(gemm_prepare(ctx, Operand{D.dgates, 4 * C, rows, 1, 4 * C}, scratch, &pdt));                        // dgates^T [4C, rows]
+    LRC(gemm_prepare(ctx, Operand{input, n_in, rows, 1, n_in}, scratch + panel_floats(4 * C, rows), &pxt));  // x^T [n_in, rows]
+    const long long in_off[4] = {off.z_in, off.in[0], off.in[1], off.in[2]};
+    for (int g = 0; g < 4; ++g) {
+      Epilogue e;
+      e.C = gw + in_off[g];
+      e.ldc = P->stride;
+      e.accumulate = 1;
+      LRC(gemm_panels(ctx, pdt, g * C, C, pxt, 0, n_in, e));
+    }
+    // recurrent weights: pairs (gate error of the next step in the layer's direction, output of this step)
+    if (T > 1) {
+      const long long K = (T - 1) * B;
+      const float *dg0 = d == 0 ? D.dgates + B * 4 * C : D.dgates;              // rows of steps 1..T-1 (forward) / 0..T-2 (backward)
+      const float *h0 = d == 0 ? L.values + d * C : L.values + B * ldh + d * C;  // rows of steps 0..T-2 (forward) / 1..T-1 (backward)
+      Panels pdr, pht;
+      LRC(gemm_prepare(ctx, Operand{dg0, 4 * C, K, 1, 4 * C}, scratch, &pdr));
+      LRC(gemm_prepare(ctx, Operand{h0, C, K, 1, ldh}, scratch + panel_floats(4 * C, K), &pht));
+      const long long rec_off[4] = {off.z_rec, off.rec[0], off.rec[1], off.rec[2]};
+      for (int g = 0; g < 4; ++g) {
+        Epilogue e;
+        e.C = gw + rec_off[g];
+        e.ldc = P->stride;
+        e.accumulate = 1;
+        LRC(gemm_panels(ctx, pdr, g * C, C, pht, 0, C, e));
+      }
+    }
+    // biases and peepholes
+    const int chunks = static_cast<int>(std::max<long long>(1, std::min<long long>(net->reduce_chunks, rows / 8)));
+    ctx.begin(TC_RECURRENT);
+    dim3 grid(static_cast<unsigned>((C + 31) / 32), chunks);
+    lstm_bias_peephole_reduce_kernel<<<grid, 256, 0, ctx.stream>>>(D.dgates, D.cstate, rows, C, d == 0 ? B : -B, chunks, P->partial);
+    lstm_bias_peephole_finalize_kernel<<<static_cast<unsigned>((C + 255) / 256), 256, 0, ctx.stream>>>(P->partial, chunks, C, net->grads + D.b_base,
+                                                                                                    gw + off.peep, P->stride);
+    ctx.end(TC_RECURRENT, 2);
+  }
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
+}  // namespace myea

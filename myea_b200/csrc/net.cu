@@ -85,7 +85,9 @@ static int build_index_map(myea_b200_net *net) {
       case MYEA_LAYER_LSTM: {
         const long long blocks = static_cast<long long>(d.layers[l].unit_parameters[0]);
         const long long cpb = std::max<long long>(1, static_cast<long long>(d.layers[l].unit_parameters[1]));
-        L.n_out = blocks * cpb;  // per direction; the reference keeps number_outputs at this width even when bidirectional
+        // a bidirectional layer outputs [forward | backward] side by side (the reference keeps number_outputs at the
+        // one-direction width and overlaps the two directions' buffers, which is not a usable definition)
+        L.n_out = blocks * cpb * (d.layers[l].use_bidirectional ? 2 : 1);
         break;
       }
       case MYEA_LAYER_RESIDUAL: L.block_depth = static_cast<int>(d.layers[l].unit_parameters[0]); break;
@@ -133,7 +135,7 @@ static int build_index_map(myea_b200_net *net) {
     } else if (L.type == MYEA_LAYER_LSTM) {
       const uint64_t blocks = L.desc.unit_parameters[0] << (L.desc.use_bidirectional ? 1 : 0);
       const uint64_t cpb = std::max<uint64_t>(1, L.desc.unit_parameters[1]);
-      const uint64_t cells_dir = L.desc.unit_parameters[0] * cpb;
+      const uint64_t cells_dir = L.desc.unit_parameters[0] * cpb;  // cells of one direction
       // per block: per cell [W_z,in (in) | W_z,rec (cells)], then W_i,in W_f,in W_o,in (in each), W_i,rec W_f,rec W_o,rec
       // (cells each), then peepholes p_i p_f p_o (cells per block each)
       L.idx.block_stride = cpb * (L.n_in + cells_dir) + 3 * L.n_in + 3 * cells_dir + 3 * cpb;
@@ -154,7 +156,7 @@ static int build_index_map(myea_b200_net *net) {
       L.idx.last_bias_connection_index = tw + tb;
     } else if (L.type == MYEA_LAYER_LSTM) {
       const uint64_t dirs = L.desc.use_bidirectional ? 2 : 1;
-      const uint64_t cells = L.n_out * dirs, blocks = L.desc.unit_parameters[0] * dirs;
+      const uint64_t cells = L.n_out, blocks = L.desc.unit_parameters[0] * dirs;
       // Prepare__Bias__LSTM overwrites first_bias_connection_index with (base + cells): the stored range is
       // [base + cells, base + cells + 3*blocks) although cells + 3*blocks slots are counted.
       L.idx.first_bias_connection_index = tw + tb + cells;
@@ -290,7 +292,7 @@ static int allocate_buffers(myea_b200_net *net) {
     }
   }
   RC(dev_alloc(net, &net->reduce_partial, static_cast<size_t>(net->reduce_chunks) * max_h));
-  net->scratch.floats = scratch + 64;
+  net->scratch.floats = std::max(net->scratch.floats, scratch + 64);
   RC(dev_alloc(net, &net->scratch.base, net->scratch.floats, false));
   return MYEA_OK;
 }

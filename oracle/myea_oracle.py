@@ -81,7 +81,7 @@ def build_index_map(desc):
         if L.type == capi.LAYER_FC:
             L.n_out = int(d.unit_parameters[0])
         elif L.type == capi.LAYER_LSTM:
-            L.n_out = int(d.unit_parameters[0]) * max(1, int(d.unit_parameters[1]))
+            L.n_out = int(d.unit_parameters[0]) * max(1, int(d.unit_parameters[1])) * (2 if d.use_bidirectional else 1)
         L.depth = int(d.unit_parameters[0]) if L.type == capi.LAYER_RESIDUAL else 0
         L.idx = dict(first_connection_index=0, last_connection_index=0, first_bias_connection_index=0,
                      last_bias_connection_index=0, scale_index=0, shift_index=0, number_inputs=0, number_outputs=0,
@@ -125,7 +125,7 @@ def build_index_map(desc):
             L.idx["last_bias_connection_index"] = tw + tb
         elif L.type == capi.LAYER_LSTM:
             dirs = 2 if L.d.use_bidirectional else 1
-            cells, blocks = L.n_out * dirs, int(L.d.unit_parameters[0]) * dirs
+            cells, blocks = L.n_out, int(L.d.unit_parameters[0]) * dirs
             L.idx["first_bias_connection_index"] = tw + tb + cells   # shifted by the cell count, as the reference does
             tb += cells + 3 * blocks
             L.idx["last_bias_connection_index"] = tw + tb

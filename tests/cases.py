@@ -55,3 +55,21 @@ def run_steps(net, wl, steps=STEPS, record=None):
     out["index_map"] = [list(net.layer_index(l).as_tuple()) for l in range(len(wl.layers))]
     out["sizes"] = list(net.sizes())
     return out
+
+
+def _lstm_case(name, opt, T=5, B=6, n_in=7, H=8, layers=2, zoneout=None, delays=None, out=None):
+    out = out or H
+    ls = [capi.fc(n_in)]
+    for _ in range(layers):
+        ls.append(capi.lstm(H, dropout=capi.DROP_ZONEOUT if zoneout else capi.DROP_NONE, p=(zoneout or 0.0, zoneout or 0.0, 0.0)))
+    ls.append(capi.fc(out, capi.AF_LINEAR))
+    wl = workloads.Workload(name, capi.net(ls, B, T=T, loss=capi.LOSS_MSE, accuracy=capi.ACC_DISTANCE,
+                                           time_delays=(T - 1 if delays is None else delays)), opt, n_in, out, False, ls)
+    return wl
+
+
+CASES.update({
+    "c3_small": lambda: workloads.c3_lstm(scale=1.0 / 32, batch=10, T=6),
+    "lstm1_all_steps_adam": lambda: _lstm_case("lstm1", capi.opt(capi.OPT_ADAM), layers=1, delays=0, H=12, out=16),
+    "lstm2_zoneout_clip": lambda: _lstm_case("lstm2z", capi.opt(capi.OPT_ADAM, clip=1.0), zoneout=0.3, delays=2),
+})
