@@ -63,7 +63,7 @@ class Workload:
                 p[a:b] = rng.uniform(-bound, bound, b - a)
             elif L.type_layer == capi.LAYER_LSTM:
                 dirs = 2 if L.use_bidirectional else 1
-                C = n_out
+                C = n_out // dirs
                 stride = int(li.block_stride)
                 base = int(li.first_connection_index)
                 bound_in = math.sqrt(6.0 / (n_in + C))
@@ -101,8 +101,7 @@ class Workload:
             if L.type_dropout in (capi.DROP_BERNOULLI, capi.DROP_BERNOULLI_INVERTED):
                 net.set_mask_bernoulli(l, (rng.random(self.T * width) < L.dropout_values[0]).astype(np.uint8))
             elif L.type_dropout == capi.DROP_ZONEOUT:
-                dirs = 2 if L.use_bidirectional else 1
-                n = self.T * width * dirs
+                n = self.T * width   # a bidirectional layer's width already counts both directions
                 net.set_mask_zoneout(l, (rng.random(n) >= L.dropout_values[0]).astype(np.uint8),
                                      (rng.random(n) >= L.dropout_values[1]).astype(np.uint8))
             elif L.type_dropout == capi.DROP_SHAKEDROP and hasattr(net, "set_shakedrop"):

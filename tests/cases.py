@@ -73,3 +73,17 @@ CASES.update({
     "lstm1_all_steps_adam": lambda: _lstm_case("lstm1", capi.opt(capi.OPT_ADAM), layers=1, delays=0, H=12, out=16),
     "lstm2_zoneout_clip": lambda: _lstm_case("lstm2z", capi.opt(capi.OPT_ADAM, clip=1.0), zoneout=0.3, delays=2),
 })
+
+
+def _bilstm_case(name, opt, T=5, B=6, n_in=7, H=8, out=5, zoneout=None):
+    ls = [capi.fc(n_in), capi.lstm(H, bidirectional=True, dropout=capi.DROP_ZONEOUT if zoneout else capi.DROP_NONE,
+                                   p=(zoneout or 0.0, zoneout or 0.0, 0.0)), capi.fc(out, capi.AF_LINEAR)]
+    return workloads.Workload(name, capi.net(ls, B, T=T, loss=capi.LOSS_MSE, accuracy=capi.ACC_DISTANCE), opt, n_in, out, False, ls)
+
+
+# The reference's own bidirectional LSTM is unusable as an oracle (its two directions share overlapping buffers and the
+# next layer gets a one-direction fan-in); these cases are checked against the numpy restatement only.
+CASES_WITHOUT_REFERENCE = {
+    "c5_small": lambda: workloads.c5_bilstm(scale=1.0 / 128, batch=6, T=5, out=12),
+    "bilstm_no_zoneout_amsgrad": lambda: _bilstm_case("bilstm", capi.opt(capi.OPT_AMSGRAD)),
+}
