@@ -86,6 +86,8 @@ struct Epilogue {
   long long ldc = 0;
   int accumulate = 0;            // C += acc instead of C = acc
   const float *bias = nullptr;   // [N], added to every row
+  const float *addend = nullptr; // [M,N] (pitch ld_addend) added before the activation derivative (skip-connection error)
+  long long ld_addend = 0;
   uint32_t deriv_af = 0;         // != 0: result *= f'(pre, y) of this activation
   const float *aux_pre = nullptr;  // [M,N] pre-activation source (may be null when f' only needs y)
   const float *aux_y = nullptr;    // [M,N] activation output

@@ -160,6 +160,7 @@ struct GemmDims {
 __device__ __forceinline__ float epilogue_value(const Epilogue &e, float acc, long long m, long long n) {
   float v = acc;
   if (e.bias != nullptr) v += e.bias[n];
+  if (e.addend != nullptr) v += e.addend[m * e.ld_addend + n];
   if (e.deriv_af != 0u) {
     float pre = 0.f, y = 0.f;
     if (e.aux_pre != nullptr) {

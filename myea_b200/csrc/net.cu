@@ -25,6 +25,7 @@ float *lstm_output_errors(LayerPlan &L);
 // residual.cu
 int residual_forward(myea_b200_net *net, int layer);
 int residual_backward(myea_b200_net *net, int layer);
+const float *residual_fc_input(myea_b200_net *net, int r, int k);
 // comm.cu
 int comm_all_reduce_sum(myea_b200_net *net, float *buf, size_t n);
 int comm_all_reduce_sum_f64(myea_b200_net *net, double *buf, size_t n);
@@ -126,7 +127,7 @@ static int build_index_map(myea_b200_net *net) {
   uint64_t tw = 0;
   for (uint32_t l = 1; l < n; ++l) {
     LayerPlan &L = net->layers[l];
-    L.idx.number_inputs = L.n_in;
+    L.idx.number_inputs = L.type == MYEA_LAYER_RESIDUAL ? 0 : L.n_in;  // a residual layer has no connections of its own
     L.idx.number_outputs = L.n_out;
     if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
       L.idx.first_connection_index = tw;
@@ -226,9 +227,11 @@ static int allocate_buffers(myea_b200_net *net) {
       L.use_bias = !L.has_norm;
       if (L.has_norm && !L.desc.use_layer_normalization_before_activation && !layer_in_block(net, static_cast<int>(l), nullptr))
         return fail(net, MYEA_E_UNSUPPORTED, "normalization after the activation is not built");
+      // a layer inside a residual block keeps its normalized / activated INPUT in `values` and `deriv`
+      const long long wide = layer_in_block(net, static_cast<int>(l), nullptr) ? std::max(L.n_out, L.n_in) : L.n_out;
       RC(dev_alloc(net, &L.summations, rows * L.n_out));
-      RC(dev_alloc(net, &L.values, rows * L.n_out));
-      RC(dev_alloc(net, &L.deriv, rows * L.n_out));
+      RC(dev_alloc(net, &L.values, rows * wide));
+      RC(dev_alloc(net, &L.deriv, rows * wide));
       if (L.has_norm) RC(dev_alloc(net, &L.errors, rows * L.n_out));
       else L.errors = L.deriv;
       scratch = std::max(scratch, gemm_scratch_floats(rows, L.n_out, L.n_in));   // forward
@@ -470,6 +473,7 @@ static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cu
     const LayerPlan &in = net->layers[L.input_layer];
     if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
       if (net->T > 1 && L.mask_bernoulli != nullptr) return fail(net, MYEA_E_UNSUPPORTED, "Bernoulli dropout on a recurrent network is not built");
+      if (layer_in_block(net, l, nullptr)) return fail(net, MYEA_E_INVALID, "block layer outside its block");
       RC(fc_forward(net, L, in.values, rows));
       ++l;
     } else if (L.type == MYEA_LAYER_LSTM) {
@@ -581,35 +585,32 @@ extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
   CK(cudaSetDevice(net->ctx.device));
   const long long rows = net->T * net->B;
   const int n = static_cast<int>(net->layers.size());
-  // walk the consumers: `l` is the layer whose error is known, `p` the layer feeding it
+  // `l` is a layer whose error is complete; send it to the layer feeding it, finish that layer, move down
   int l = n - 1;
-  while (l > 1) {
+  while (l >= 1) {
     LayerPlan &N = net->layers[l];
+    if (N.type == MYEA_LAYER_RESIDUAL) {  // the block handles its own layers and the layer feeding it
+      RC(residual_backward(net, l));
+      l = N.input_layer;
+      continue;
+    }
     const int p = N.input_layer;
     if (p < 1) break;
     LayerPlan &P = net->layers[p];
-    if (N.type != MYEA_LAYER_FULLY_CONNECTED && N.type != MYEA_LAYER_LSTM) return fail(net, MYEA_E_INVALID, "unexpected consumer layer");
     if (P.type == MYEA_LAYER_FULLY_CONNECTED) {
-      if (N.type == MYEA_LAYER_FULLY_CONNECTED) RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, true));
-      else return fail(net, MYEA_E_UNSUPPORTED, "a fully connected hidden layer below an LSTM layer is not built");
+      if (N.type != MYEA_LAYER_FULLY_CONNECTED) return fail(net, MYEA_E_UNSUPPORTED, "a fully connected hidden layer below an LSTM layer is not built");
+      RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, true));
       RC(fc_finish_backward(net, P, rows));
-      l = p;
     } else if (P.type == MYEA_LAYER_LSTM) {
       float *dh = lstm_output_errors(P);
       if (N.type == MYEA_LAYER_FULLY_CONNECTED) RC(fc_backward_from_fc(net, P, N, N.errors, rows, dh, false));
       else RC(lstm_backward_to_input(net, N, dh, P));
       RC(lstm_backward(net, P));
-      l = p;
-    } else {  // residual block feeding N
-      if (N.type != MYEA_LAYER_FULLY_CONNECTED) return fail(net, MYEA_E_UNSUPPORTED, "residual block below an LSTM layer is not built");
+    } else {  // residual block feeding N: its output has no activation of its own
+      if (N.type != MYEA_LAYER_FULLY_CONNECTED) return fail(net, MYEA_E_UNSUPPORTED, "a residual block below an LSTM layer is not built");
       RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, false));
-      RC(residual_backward(net, p));
-      l = p;  // the residual layer now stands for its block; its input layer is the one before the block
-      // error for the layer feeding the block has been written by residual_backward; continue from that layer
-      l = P.input_layer + 0;
-      if (l >= 1 && net->layers[l].type == MYEA_LAYER_RESIDUAL) continue;
-      // a fully connected layer feeding the block: its error is final after residual_backward
     }
+    l = p;
   }
   return MYEA_OK;
 }
@@ -644,11 +645,7 @@ extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batc
     if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
       const float *input = net->layers[L.input_layer].values;
       int blk = 0;
-      if (layer_in_block(net, l, &blk)) {
-        // inside a residual block the layer's input is the normalized / activated copy kept by the block
-        // (Layer::ptr_array_pre_summations): residual.cu stores it in the previous slot's `deriv`-independent buffer
-        input = net->layers[l].block_out_errors != nullptr ? reinterpret_cast<const float *>(net->layers[l].block_out_errors) : input;
-      }
+      if (layer_in_block(net, l, &blk)) input = residual_fc_input(net, blk, l - blk);  // normalized / activated copy kept by the block
       RC(fc_update_derivative_weight(net, L, input, rows));
     } else if (L.type == MYEA_LAYER_LSTM) {
       RC(lstm_update_derivative_weight(net, L, net->layers[L.input_layer].values, L.n_in));

@@ -34,7 +34,6 @@ struct LayerPlan {
   int block_depth = 0;
   uint8_t *shake_mask = nullptr;      // [B]
   float *shake_alpha = nullptr, *shake_beta = nullptr;  // [B, n_out]
-  float *block_out_errors = nullptr;
   long long norm_unit_offset = 0;     // units of earlier layers in the normalized-unit run
 };
 

@@ -104,11 +104,14 @@ class Workload:
                 n = self.T * width   # a bidirectional layer's width already counts both directions
                 net.set_mask_zoneout(l, (rng.random(n) >= L.dropout_values[0]).astype(np.uint8),
                                      (rng.random(n) >= L.dropout_values[1]).astype(np.uint8))
-            elif L.type_dropout == capi.DROP_SHAKEDROP and hasattr(net, "set_shakedrop"):
+            elif L.type_dropout == capi.DROP_SHAKEDROP:
+                # drawn for every kind of net so that the seeded stream stays aligned; the compiled reference draws its
+                # own coefficients while it runs (tests read them back and impose them on the other side)
                 mask = (rng.random(self.B) < L.dropout_values[0]).astype(np.uint8)
                 alpha = rng.uniform(-1.0, 1.0, (self.B, width)).astype(np.float32)
                 beta = rng.uniform(0.0, 1.0, (self.B, width)).astype(np.float32)
-                net.set_shakedrop(l, mask, alpha, beta)
+                if hasattr(net, "set_shakedrop"):
+                    net.set_shakedrop(l, mask, alpha, beta)
 
 
 def _orthogonal(rng, n):

@@ -101,7 +101,7 @@ def build_index_map(desc):
     tw = 0
     for l in range(1, n):
         L = Ls[l]
-        L.idx["number_inputs"], L.idx["number_outputs"] = L.n_in, L.n_out
+        L.idx["number_inputs"], L.idx["number_outputs"] = (0 if L.type == capi.LAYER_RESIDUAL else L.n_in), L.n_out
         if L.type == capi.LAYER_FC:
             L.idx["first_connection_index"] = tw
             tw += L.n_out * L.n_in
@@ -346,8 +346,12 @@ class OracleNet:
         (:1079-1114), activation derivative (:1259-1294), normalization backward."""
         n = len(self.layers)
         l = n - 1
-        while l > 1:
+        while l >= 1:
             N = self.layers[l]
+            if N.type == capi.LAYER_RESIDUAL:
+                from oracle import myea_oracle_residual
+                l = myea_oracle_residual.backward(self, l)
+                continue
             p = N.input_layer
             if p < 1:
                 break
@@ -360,16 +364,13 @@ class OracleNet:
             if Pl.type == capi.LAYER_FC:
                 da = D * af_derive(int(Pl.d.type_activation_function), Pl.pre, Pl.values)
                 Pl.errors = self._norm_backward(Pl, Pl.z, da) if int(Pl.d.type_normalization) != capi.NORM_NONE else da
-                l = p
             elif Pl.type == capi.LAYER_LSTM:
                 from oracle import myea_oracle_lstm
                 Pl.dh = D
                 myea_oracle_lstm.backward(self, p)
-                l = p
             else:
-                from oracle import myea_oracle_residual
                 Pl.errors = D
-                l = myea_oracle_residual.backward(self, p)
+            l = p
 
     def update_derivative_weight(self):
         """Update_Derivative_Weight__FC + bias (Neural_Network__Update_Derivative_Weight__Loop.cpp): sums over the batch,

@@ -44,6 +44,7 @@ def _lib():
         lib.ref_get_loss.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_double)]
         lib.ref_get_outputs.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p]
         lib.ref_get_errors.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p]
+        lib.ref_shakedrop_replay.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
         lib.ref_time_steps.restype = C.c_double
         lib.ref_time_steps.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int, C.c_int]
         _LIB = lib
@@ -150,6 +151,26 @@ class RefNet:
         out = np.empty((self.T, self.B, w), np.float32)
         if self.lib.ref_get_errors(self.h, layer, self.B, out.ctypes.data) != 0:
             raise RuntimeError("layer %d has no error buffer" % layer)
+        return out
+
+    def next_shakedrop(self):
+        """{residual layer: (mask[B], alpha[B, width], beta[B, width])} the reference will draw in its NEXT training step"""
+        layers = [l for l in range(1, int(self.desc.number_layers))
+                  if self.desc.layers[l].type_layer == capi.LAYER_RESIDUAL and self.desc.layers[l].type_dropout == capi.DROP_SHAKEDROP]
+        if not layers:
+            return {}
+        widths = [int(self.layer_index(l).number_outputs) for l in layers]
+        total = sum(self.B * w for w in widths)
+        masks = np.zeros(len(layers) * self.B, np.uint8)
+        alpha, beta = np.zeros(total, np.float32), np.zeros(total, np.float32)
+        n = self.lib.ref_shakedrop_replay(self.h, self.B, masks.ctypes.data, alpha.ctypes.data, beta.ctypes.data)
+        if n != len(layers):
+            raise RuntimeError("ShakeDrop replay found %d blocks, expected %d" % (n, len(layers)))
+        out, off = {}, 0
+        for k, (l, w) in enumerate(zip(layers, widths)):
+            out[l] = (masks[k * self.B:(k + 1) * self.B].copy(), alpha[off:off + self.B * w].reshape(self.B, w).copy(),
+                      beta[off:off + self.B * w].reshape(self.B, w).copy())
+            off += self.B * w
         return out
 
     def time_steps(self, X, Y, warmup, steps, training_size=None):

@@ -322,4 +322,48 @@ double ref_time_steps(void *h, uint64_t B, uint64_t N, int warmup, int steps) {
   return std::chrono::duration<double, std::milli>(t1 - t0).count();
 }
 
+// Makes the ShakeDrop draws of the NEXT training step explicit without touching the reference: copies of its two
+// generator objects are advanced through exactly the draw sequence the step will make (Loop mode, one generator of each
+// kind) - forward, blocks in layer order, rows in order: one Bernoulli(p) draw per row and, when it is set, `width`
+// draws of U(-1, 1) (Neural_Network__Forward_Pass__Loop.cpp:5016-5045); backward, blocks in reverse order, `width`
+// draws of U(0, 1) from the same real generator for every row whose mask is set
+// (Neural_Network__Backward_Pass__Loop.cpp:1050-1077).  Blocks are packed in layer order: masks [block][B],
+// alpha / beta [block][B * width].  Returns the number of ShakeDrop blocks, or -1.
+int ref_shakedrop_replay(void *h, uint64_t B, uint8_t *masks, float *alpha, float *beta) {
+  RefNet *r = static_cast<RefNet *>(h);
+  Neural_Network &nn = r->nn;
+  if (nn.ptr_array_Class_Generator_Bernoulli_ShakeDrop == nullptr || nn.ptr_array_Class_Generator_Real_ShakeDrop == nullptr) return -1;
+  MyEA::Random::Bernoulli<T_> bern;
+  MyEA::Random::Floating<T_> real;
+  bern = nn.ptr_array_Class_Generator_Bernoulli_ShakeDrop[0];
+  real = nn.ptr_array_Class_Generator_Real_ShakeDrop[0];
+  std::vector<size_t> blocks, widths, offsets;
+  size_t off = 0;
+  for (size_t l = 1; l < nn.total_layers; ++l) {
+    Layer *L = nn.ptr_array_layers + l;
+    if (L->type_layer == ENUM_TYPE_LAYER::TYPE_LAYER_RESIDUAL && L->type_dropout == ENUM_TYPE_LAYER_DROPOUT::TYPE_LAYER_DROPOUT_SHAKEDROP) {
+      blocks.push_back(l);
+      widths.push_back(*L->ptr_number_outputs);
+      offsets.push_back(off);
+      off += B * *L->ptr_number_outputs;
+    }
+  }
+  for (size_t k = 0; k < blocks.size(); ++k) {
+    Layer *L = nn.ptr_array_layers + blocks[k];
+    bern.Probability(L->dropout_values[0]);
+    real.Range(-1_T, 1_T);
+    for (size_t b = 0; b < B; ++b) {
+      const bool m = bern();
+      masks[k * B + b] = m ? 1 : 0;
+      for (size_t j = 0; j < widths[k]; ++j) alpha[offsets[k] + b * widths[k] + j] = m ? real() : 1.0f;
+    }
+  }
+  for (size_t k = blocks.size(); k-- > 0;) {
+    real.Range(0_T, 1_T);
+    for (size_t b = 0; b < B; ++b)
+      for (size_t j = 0; j < widths[k]; ++j) beta[offsets[k] + b * widths[k] + j] = masks[k * B + b] ? real() : 1.0f;
+  }
+  return static_cast<int>(blocks.size());
+}
+
 }  // extern "C"

@@ -1,6 +1,8 @@
 """Parity cases shared by the golden-fixture generator, the CPU tests and the GPU tests: reduced-shape versions of the
 five benchmark configurations plus targeted variants (every optimizer, plain Bernoulli dropout, batch renormalization,
 clipping, weight decay, ragged widths that are not multiples of any tile)."""
+import numpy as np
+
 from myea_b200 import capi, workloads
 
 
@@ -29,13 +31,19 @@ CASES = {
 STEPS = 2
 
 
-def run_steps(net, wl, steps=STEPS, record=None):
+def run_steps(net, wl, steps=STEPS, shake=None):
     """the reference's training sequence (Dataset.cpp:637-691, 7654-7690) on one seeded batch; returns what a parity
-    check compares"""
+    check compares.  `shake`: per-step ShakeDrop draws {layer: (mask, alpha, beta)} to impose (a list, one dict per
+    step); the compiled reference draws its own and reports them (they come back under the key "shake")."""
     X, Y = wl.batch()
     wl.materialize(net)
-    out = {}
+    out = {"shake": []}
     for it in range(steps):
+        if hasattr(net, "next_shakedrop"):
+            out["shake"].append(net.next_shakedrop())
+        elif shake is not None:
+            for layer, (m, a, b) in shake[it].items():
+                net.set_shakedrop(layer, m, a, b)
         net.reset_loss()
         net.forward(X)
         net.compute_error(Y)
@@ -87,3 +95,29 @@ CASES_WITHOUT_REFERENCE = {
     "c5_small": lambda: workloads.c5_bilstm(scale=1.0 / 128, batch=6, T=5, out=12),
     "bilstm_no_zoneout_amsgrad": lambda: _bilstm_case("bilstm", capi.opt(capi.OPT_AMSGRAD)),
 }
+
+
+def _res_case(name, opt, B=10, n_in=9, H=12, out=5, blocks=2, p=0.5, norm=capi.NORM_BRN, af=capi.AF_ELU, shake=True, inner_drop=capi.DROP_NONE):
+    ls = [capi.fc(n_in), capi.fc(H, af)]
+    for _ in range(blocks):
+        ls += [capi.residual(2, capi.DROP_SHAKEDROP if shake else capi.DROP_NONE, (p, 0, 0)), capi.fc(H, af), capi.fc(H, af, norm, inner_drop, (0.7, 0, 0))]
+    ls.append(capi.fc(out, capi.AF_SOFTMAX))
+    return workloads.Workload(name, capi.net(ls, B, loss=capi.LOSS_CE, accuracy=capi.ACC_CE, r_max=3.0, d_max=5.0), opt, n_in, out, True, ls)
+
+
+CASES.update({
+    "c4_small": lambda: workloads.c4_residual(scale=1.0 / 64, batch=24, blocks=2),
+    "res_bn_tanh_adam_noshake": lambda: _res_case("res1", capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9), norm=capi.NORM_BN, af=capi.AF_TANH, shake=False, blocks=1),
+    "res_plain_relu_shake_drop": lambda: _res_case("res2", capi.opt(capi.OPT_AMSGRAD), norm=capi.NORM_NONE, af=capi.AF_RELU, inner_drop=capi.DROP_BERNOULLI_INVERTED),
+})
+
+
+def shake_from_golden(gold, steps=STEPS):
+    """per-step ShakeDrop draws stored in a golden fixture, in the form run_steps(shake=...) takes"""
+    out = [dict() for _ in range(steps)]
+    for key in gold.files:
+        if key.startswith("shake_") and key.endswith("_mask"):
+            _, it, layer, _ = key.split("_")
+            it, layer = int(it), int(layer)
+            out[it][layer] = (gold[key].astype(np.uint8), gold["shake_%d_%d_alpha" % (it, layer)], gold["shake_%d_%d_beta" % (it, layer)])
+    return out

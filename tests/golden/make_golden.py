@@ -34,6 +34,12 @@ def main():
         out = cases.run_steps(net, wl)
         out["input_checksum"] = input_checksum(wl, net)
         net.close()
+        shake = out.pop("shake")
+        for it, draws in enumerate(shake):          # the reference's own ShakeDrop draws, so that they can be imposed elsewhere
+            for layer, (m, a, b) in draws.items():
+                out["shake_%d_%d_mask" % (it, layer)] = m
+                out["shake_%d_%d_alpha" % (it, layer)] = a
+                out["shake_%d_%d_beta" % (it, layer)] = b
         arrays = {k: (np.asarray(v, np.int64) if k in ("index_map", "sizes") else np.asarray(v, np.float64 if k.startswith("loss") or k == "input_checksum" else np.float32))
                   for k, v in out.items()}
         path = os.path.join(ROOT, "tests", "golden", name + ".npz")

@@ -21,6 +21,21 @@ def _oracle(wl):
     return ref.RefNet(wl.desc, wl.opt, threads=1) if ref.available() else myea_oracle.OracleNet(wl.desc, wl.opt)
 
 
+def _seeded_shake(wl):
+    """ShakeDrop draws for an oracle that does not draw its own (the numpy restatement): seeded, one dict per step"""
+    rng = np.random.default_rng(99)
+    steps = []
+    for _ in range(cases.STEPS):
+        d = {}
+        for l, L in enumerate(wl.layers):
+            if L.type_layer == capi.LAYER_RESIDUAL and L.type_dropout == capi.DROP_SHAKEDROP:
+                w = int(wl.layers[l + int(L.unit_parameters[0])].unit_parameters[0])
+                d[l] = ((rng.random(wl.B) < L.dropout_values[0]).astype(np.uint8), rng.uniform(-1, 1, (wl.B, w)).astype(np.float32),
+                        rng.uniform(0, 1, (wl.B, w)).astype(np.float32))
+        steps.append(d)
+    return steps
+
+
 def _compare(out, want, tol=TOL):
     assert list(out["sizes"]) == [int(x) for x in want["sizes"]]
     assert np.array_equal(np.asarray(out["index_map"], np.int64), np.asarray(want["index_map"], np.int64))
@@ -39,7 +54,8 @@ def _compare(out, want, tol=TOL):
 def test_step_matches_oracle(name):
     wl = cases.CASES[name]()
     gpu, cpu = Net(wl.desc, wl.opt), _oracle(wl)
-    out, want = cases.run_steps(gpu, wl), cases.run_steps(cpu, wl)
+    want = cases.run_steps(cpu, wl, shake=_seeded_shake(wl))
+    out = cases.run_steps(gpu, wl, shake=want["shake"] if want["shake"] and want["shake"][0] else _seeded_shake(wl))
     gpu.synchronize()
     assert gpu.launches() > 0
     _compare(out, want)
@@ -66,7 +82,7 @@ def test_step_matches_golden(name, golden_dir):
     gold = np.load(path)
     wl = cases.CASES[name]()
     gpu = Net(wl.desc, wl.opt)
-    out = cases.run_steps(gpu, wl)
+    out = cases.run_steps(gpu, wl, shake=cases.shake_from_golden(gold))
     _compare(out, {k: gold[k] for k in gold.files})
     gpu.close()
 
