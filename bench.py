@@ -180,7 +180,7 @@ def run_ours(args):
         lib.myea_b200_compute_error_device(h, B, Yd.data_ptr())
         lib.myea_b200_backward(h, B)
         lib.myea_b200_update_derivative_weight(h, B)
-        return lib.myea_b200_update_parameter(h, B, N_train, opt)
+        return lib.myea_b200_update_parameter(h, global_batch, N_train, opt)
 
     def step_host():
         lib.myea_b200_reset_loss(h)
@@ -188,7 +188,7 @@ def run_ours(args):
         lib.myea_b200_compute_error(h, B, Yh.data_ptr())
         lib.myea_b200_backward(h, B)
         lib.myea_b200_update_derivative_weight(h, B)
-        rc = lib.myea_b200_update_parameter(h, B, N_train, opt)
+        rc = lib.myea_b200_update_parameter(h, global_batch, N_train, opt)
         s, n, a = C.c_double(), C.c_uint64(), C.c_double()
         lib.myea_b200_get_loss(h, C.byref(s), C.byref(n), C.byref(a))  # device -> host read of the step's loss
         return rc

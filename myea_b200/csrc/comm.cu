@@ -1,9 +1,173 @@
-// placeholder, replaced below
+// Data-parallel plumbing: one handle per GPU, each on its shard of the batch, joined by an NCCL communicator.
+//
+// What is exchanged is exactly what the reference merges across its OpenMP threads: the per-thread derivative slices
+// summed by Merge_Derivatives_Parameters (Neural_Network__Merge.cpp:20-50) become an all-reduce(sum) of the flat
+// derivative buffer, issued in per-layer buckets on a second stream as soon as a layer's weight derivative is complete so
+// that it overlaps the remaining layers; the per-thread partial sums of the batch-normalization statistics
+// (Neural_Network__Forward_Pass__OpenMP.cpp:4591-4701, …Backward_Pass__OpenMP.cpp:1346-1709) become small all-reduces of
+// [2][H] column sums, so a sharded step computes the same statistics as the one-GPU step; the loss / accuracy
+// accumulators (Merge__Post__Training, Neural_Network__Merge.cpp:52-98) are summed when they are read.
+// Derivatives are sums over samples (never divided by the batch), so no rescaling is needed.
+//
+// NCCL is loaded at run time (dlopen) so that the library itself has no link-time dependency on it.
 #include "net.cuh"
+
+#include <dlfcn.h>
+#include <nccl.h>
+#include <stdio.h>
+#include <string.h>
+
 namespace myea {
-int comm_all_reduce_sum(myea_b200_net *, float *, size_t) { return MYEA_E_UNSUPPORTED; }
-int comm_all_reduce_sum_f64(myea_b200_net *, double *, size_t) { return MYEA_E_UNSUPPORTED; }
-void comm_destroy(myea_b200_net *) {}
+
+struct NcclApi {
+  void *lib = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  const char *(*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+static NcclApi *nccl_api() {
+  static NcclApi api;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    const char *names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) {
+      api.lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+      if (api.lib != nullptr) break;
+    }
+    if (api.lib != nullptr) {
+      api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.lib, "ncclGetUniqueId"));
+      api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.lib, "ncclCommInitRank"));
+      api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.lib, "ncclAllReduce"));
+      api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.lib, "ncclCommDestroy"));
+      api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.lib, "ncclGetErrorString"));
+      if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy) api.lib = nullptr;
+    }
+  }
+  return api.lib != nullptr ? &api : nullptr;
 }
-extern "C" int myea_b200_comm_unique_id(uint8_t *) { return MYEA_E_UNSUPPORTED; }
-extern "C" int myea_b200_comm_init(myea_handle, int, int, const uint8_t *) { return MYEA_E_UNSUPPORTED; }
+
+struct CommState {
+  ncclComm_t comm = nullptr;
+  int world = 1, rank = 0;
+  cudaStream_t stream = nullptr;   // bucket all-reduces run here, beside the compute stream
+  cudaEvent_t ready = nullptr;     // compute -> comm: the bucket is complete
+  cudaEvent_t done = nullptr;      // comm -> compute: every bucket issued so far is reduced
+  bool pending = false;
+  size_t reduced_weights = 0;      // how much of the weight range has been handed to the comm stream this step
+};
+
+static int nccl_fail(myea_b200_net *net, ncclResult_t r, const char *what) {
+  NcclApi *api = nccl_api();
+  char msg[256];
+  snprintf(msg, sizeof(msg), "%s: %s", what, (api && api->GetErrorString) ? api->GetErrorString(r) : "NCCL error");
+  net->ctx.error = msg;
+  return MYEA_E_COMM;
+}
+
+int comm_world(const myea_b200_net *net) { return net->comm != nullptr ? net->comm->world : 1; }
+
+// in-place sum over ranks on the COMPUTE stream (small, latency-bound messages: normalization sums, loss counters)
+int comm_all_reduce_sum(myea_b200_net *net, float *buf, size_t n) {
+  if (net->comm == nullptr || n == 0) return MYEA_OK;
+  NcclApi *api = nccl_api();
+  net->ctx.begin(TC_COMM);
+  ncclResult_t r = api->AllReduce(buf, buf, n, ncclFloat, ncclSum, net->comm->comm, net->ctx.stream);
+  net->ctx.end(TC_COMM);
+  return r == ncclSuccess ? MYEA_OK : nccl_fail(net, r, "ncclAllReduce");
+}
+
+int comm_all_reduce_sum_f64(myea_b200_net *net, double *buf, size_t n) {
+  if (net->comm == nullptr || n == 0) return MYEA_OK;
+  NcclApi *api = nccl_api();
+  ncclResult_t r = api->AllReduce(buf, buf, n, ncclDouble, ncclSum, net->comm->comm, net->ctx.stream);
+  net->ctx.launches += 1;
+  return r == ncclSuccess ? MYEA_OK : nccl_fail(net, r, "ncclAllReduce");
+}
+
+// Hands the derivative range [offset, offset + n) to the communication stream: it is summed over ranks while the compute
+// stream carries on with the next layer.  Every rank issues the same buckets in the same order.
+int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n) {
+  CommState *c = net->comm;
+  if (c == nullptr || n == 0) return MYEA_OK;
+  NcclApi *api = nccl_api();
+  if (cudaEventRecord(c->ready, net->ctx.stream) != cudaSuccess || cudaStreamWaitEvent(c->stream, c->ready, 0) != cudaSuccess) return MYEA_E_CUDA;
+  ncclResult_t r = api->AllReduce(net->grads + offset, net->grads + offset, n, ncclFloat, ncclSum, c->comm, c->stream);
+  if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllReduce (bucket)");
+  c->pending = true;
+  net->ctx.launches += 1;
+  net->ctx.class_launches[TC_COMM] += 1;
+  return MYEA_OK;
+}
+
+// Makes the compute stream wait until every bucket issued so far has been reduced.
+int comm_join(myea_b200_net *net) {
+  CommState *c = net->comm;
+  if (c == nullptr || !c->pending) return MYEA_OK;
+  if (cudaEventRecord(c->done, c->stream) != cudaSuccess || cudaStreamWaitEvent(net->ctx.stream, c->done, 0) != cudaSuccess) return MYEA_E_CUDA;
+  c->pending = false;
+  return MYEA_OK;
+}
+
+size_t &comm_reduced_weights(myea_b200_net *net) {
+  static size_t none = 0;
+  return net->comm != nullptr ? net->comm->reduced_weights : none;
+}
+
+void comm_destroy(myea_b200_net *net) {
+  if (net->comm == nullptr) return;
+  NcclApi *api = nccl_api();
+  if (net->comm->stream) cudaStreamSynchronize(net->comm->stream);
+  if (api && net->comm->comm) api->CommDestroy(net->comm->comm);
+  if (net->comm->ready) cudaEventDestroy(net->comm->ready);
+  if (net->comm->done) cudaEventDestroy(net->comm->done);
+  if (net->comm->stream) cudaStreamDestroy(net->comm->stream);
+  delete net->comm;
+  net->comm = nullptr;
+}
+
+}  // namespace myea
+
+using namespace myea;
+
+extern "C" int myea_b200_comm_unique_id(uint8_t id_out[128]) {
+  if (id_out == nullptr) return MYEA_E_INVALID;
+  NcclApi *api = nccl_api();
+  if (api == nullptr) return MYEA_E_COMM;
+  ncclUniqueId id;
+  if (api->GetUniqueId(&id) != ncclSuccess) return MYEA_E_COMM;
+  static_assert(sizeof(id) == 128, "ncclUniqueId is 128 bytes");
+  memcpy(id_out, &id, 128);
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_comm_init(myea_handle net, int world, int rank, const uint8_t unique_id[128]) {
+  if (net == nullptr || unique_id == nullptr || world < 1 || rank < 0 || rank >= world) return MYEA_E_INVALID;
+  if (net->comm != nullptr) { net->ctx.error = "a communicator is already attached"; return MYEA_E_INVALID; }
+  if (world == 1) return MYEA_OK;
+  NcclApi *api = nccl_api();
+  if (api == nullptr) { net->ctx.error = "libnccl.so.2 could not be loaded"; return MYEA_E_COMM; }
+  if (cudaSetDevice(net->ctx.device) != cudaSuccess) return MYEA_E_CUDA;
+  CommState *c = new CommState();
+  c->world = world;
+  c->rank = rank;
+  ncclUniqueId id;
+  memcpy(&id, unique_id, 128);
+  ncclResult_t r = api->CommInitRank(&c->comm, world, id, rank);
+  if (r != ncclSuccess) { delete c; return nccl_fail(net, r, "ncclCommInitRank"); }
+  if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&c->ready, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming) != cudaSuccess) {
+    delete c;
+    net->ctx.error = "stream / event creation failed";
+    return MYEA_E_CUDA;
+  }
+  net->comm = c;
+  net->hook.world = world;
+  net->hook.user = net;
+  net->hook.all_reduce = [](void *user, float *buf, size_t n) { return comm_all_reduce_sum(static_cast<myea_b200_net *>(user), buf, n); };
+  return MYEA_OK;
+}

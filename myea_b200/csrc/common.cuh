@@ -141,15 +141,23 @@ struct NormParams {        // one normalized layer
   int chunks = 0;
 };
 
+// Cross-GPU sum of a small device vector, supplied by the communicator when the batch is sharded over `world` ranks.
+struct SumHook {
+  int world = 1;
+  void *user = nullptr;
+  int (*all_reduce)(void *user, float *buf, size_t n) = nullptr;
+};
+
 // z [rows,H] -> batch statistics (training) or running statistics (inference) -> col_scale / col_shift
-int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H, const NormParams &np, int training);
+int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H, const NormParams &np, int training,
+                       const SumHook *hook = nullptr);
 // out = dropout(f(z*col_scale+col_shift)) ; col_scale null = no normalization. mask: uint8[H] or null; keep_scale = 1/p for inverted dropout
 int activation_forward(Context &ctx, const float *z, float *out, long long rows, long long H, uint32_t af,
                        const float *col_scale, const float *col_shift, const uint8_t *mask, float keep_scale);
 int softmax_forward(Context &ctx, const float *z, float *out, long long rows, long long H);
 // delta_af [rows,H] (error after the activation derivative) -> error before the normalization, plus d_gamma / d_beta
 int norm_backward(Context &ctx, const float *z, const float *delta_af, float *delta_out, long long rows, long long H,
-                  const NormParams &np);
+                  const NormParams &np, const SumHook *hook = nullptr);
 // delta = f'(pre,y) * (y - desired); loss / accuracy accumulators (double[2] + uint64) on the device
 int output_error(Context &ctx, const float *pre, const float *y, const float *desired, float *delta, long long rows,
                  long long H, uint32_t af, uint32_t loss, uint32_t accuracy, float accuracy_variance, double *d_acc,

@@ -99,6 +99,18 @@ static void launch_column_reduce(Context &ctx, const float *x, const float *y, c
 // The "variance" buffers of the reference hold the standard deviation sqrt(E[x^2] - mean^2 + eps); the running
 // averages are exponential averages of mean and standard deviation; r and d use the ALREADY UPDATED averages.
 // ---------------------------------------------------------------------------------------------------------
+// sums[2][H] = chunk sums of partial[2][chunks][H]: the message of the cross-GPU all-reduce
+__global__ void chunk_sum_kernel(const float *__restrict__ partial, int chunks, long long H, float *__restrict__ sums) {
+  const long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (j >= H) return;
+  float s = 0.f, q = 0.f;
+  for (int c = 0; c < chunks; ++c) { s += partial[(0ll * chunks + c) * H + j]; q += partial[(1ll * chunks + c) * H + j]; }
+  sums[j] = s;
+  sums[H + j] = q;
+}
+
+// `rows` is the batch the statistics are taken over: the global batch when the column sums were all-reduced (chunks == 1
+// then, partial = the reduced [2][H] sums).
 __global__ void norm_stats_finalize_kernel(const float *__restrict__ partial, int chunks, long long rows, long long H,
                                            NormParams np, int training) {
   const long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -133,16 +145,31 @@ __global__ void norm_stats_finalize_kernel(const float *__restrict__ partial, in
   np.col_shift[j] = b + g * (d - mean * k);
 }
 
-int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H, const NormParams &np, int training) {
+int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H, const NormParams &np, int training,
+                       const SumHook *hook) {
   ctx.begin(TC_NORM);
   int launches = 1;
   int chunks = 1;
+  const float *sums = np.partial;
+  long long rows_total = rows;
   if (training) {
     chunks = pick_chunks(rows, H, (H % 4 == 0) ? 4 : 1, np.chunks);
     launch_column_reduce<RK_SUM_SQ>(ctx, z, nullptr, nullptr, rows, H, chunks, np.partial);
     ++launches;
+    if (hook != nullptr && hook->world > 1) {
+      // sharded batch: sum the column sums over the ranks, then every rank finalizes the same global statistics
+      float *g = np.partial + 2ll * np.chunks * H + 3 * H;
+      chunk_sum_kernel<<<static_cast<unsigned>((H + 255) / 256), 256, 0, ctx.stream>>>(np.partial, chunks, H, g);
+      ctx.end(TC_NORM, launches + 1);
+      if (hook->all_reduce(hook->user, g, static_cast<size_t>(2 * H)) != MYEA_OK) return MYEA_E_COMM;
+      ctx.begin(TC_NORM);
+      launches = 1;
+      sums = g;
+      chunks = 1;
+      rows_total = rows * hook->world;
+    }
   }
-  norm_stats_finalize_kernel<<<static_cast<unsigned>((H + 255) / 256), 256, 0, ctx.stream>>>(np.partial, chunks, rows, H, np, training);
+  norm_stats_finalize_kernel<<<static_cast<unsigned>((H + 255) / 256), 256, 0, ctx.stream>>>(sums, chunks, rows_total, H, np, training);
   ctx.end(TC_NORM, launches);
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
@@ -259,8 +286,10 @@ int softmax_forward(Context &ctx, const float *z, float *out, long long rows, lo
 // d_mean = -gamma*(r/sigma)*S1, d_sigma = -gamma*(r/sigma^2)*S2, so one reduction pass and one apply pass suffice.
 // r and d are constants of the backward pass, as in the reference.
 // ---------------------------------------------------------------------------------------------------------
-__global__ void norm_backward_finalize_kernel(const float *__restrict__ partial, int chunks, long long rows, long long H,
-                                              NormParams np, float *__restrict__ coef) {
+// `global` (may be null): the column sums added over all ranks of a sharded batch; d_gamma / d_beta take the LOCAL sums
+// (the derivative buffers are summed over ranks later), d_mean / d_sigma and `rows` are those of the whole batch.
+__global__ void norm_backward_finalize_kernel(const float *__restrict__ partial, int chunks, const float *__restrict__ global,
+                                              long long rows, long long H, NormParams np, float *__restrict__ coef) {
   const long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   if (j >= H) return;
   float s1 = 0.f, s2 = 0.f;
@@ -269,6 +298,7 @@ __global__ void norm_backward_finalize_kernel(const float *__restrict__ partial,
   const float k = r / sigma;
   np.d_beta[j] += s1;
   np.d_gamma[j] += k * s2 + d * s1;
+  if (global != nullptr) { s1 = global[j]; s2 = global[H + j]; }
   const float d_mean = -g * k * s1;
   const float d_sigma = -g * (r / (sigma * sigma)) * s2;
   const float inv_b = 1.0f / static_cast<float>(rows);
@@ -308,12 +338,23 @@ __global__ void __launch_bounds__(256) norm_backward_apply_kernel(const float *_
 }
 
 int norm_backward(Context &ctx, const float *z, const float *delta_af, float *delta_out, long long rows, long long H,
-                  const NormParams &np) {
+                  const NormParams &np, const SumHook *hook) {
   ctx.begin(TC_NORM);
   const int chunks = pick_chunks(rows, H, (H % 4 == 0) ? 4 : 1, np.chunks);
   launch_column_reduce<RK_NORM_BWD>(ctx, z, delta_af, np.mean, rows, H, chunks, np.partial);
   float *coef = np.partial + 2ll * np.chunks * H;  // [3][H] behind the partial sums
-  norm_backward_finalize_kernel<<<static_cast<unsigned>((H + 255) / 256), 256, 0, ctx.stream>>>(np.partial, chunks, rows, H, np, coef);
+  const float *global = nullptr;
+  long long rows_total = rows;
+  if (hook != nullptr && hook->world > 1) {
+    float *g = coef + 3 * H;
+    chunk_sum_kernel<<<static_cast<unsigned>((H + 255) / 256), 256, 0, ctx.stream>>>(np.partial, chunks, H, g);
+    ctx.end(TC_NORM, 2);
+    if (hook->all_reduce(hook->user, g, static_cast<size_t>(2 * H)) != MYEA_OK) return MYEA_E_COMM;
+    ctx.begin(TC_NORM);
+    global = g;
+    rows_total = rows * hook->world;
+  }
+  norm_backward_finalize_kernel<<<static_cast<unsigned>((H + 255) / 256), 256, 0, ctx.stream>>>(np.partial, chunks, global, rows_total, H, np, coef);
   const bool vec4 = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(z) & 15) == 0) && ((reinterpret_cast<uintptr_t>(delta_af) & 15) == 0) &&
                     ((reinterpret_cast<uintptr_t>(delta_out) & 15) == 0);
   const long long total = rows * (vec4 ? H / 4 : H);

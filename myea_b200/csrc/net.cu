@@ -29,6 +29,9 @@ const float *residual_fc_input(myea_b200_net *net, int r, int k);
 // comm.cu
 int comm_all_reduce_sum(myea_b200_net *net, float *buf, size_t n);
 int comm_all_reduce_sum_f64(myea_b200_net *net, double *buf, size_t n);
+int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n);
+int comm_join(myea_b200_net *net);
+int comm_world(const myea_b200_net *net);
 void comm_destroy(myea_b200_net *net);
 }  // namespace myea
 
@@ -213,6 +216,7 @@ static int allocate_buffers(myea_b200_net *net) {
   RC(dev_alloc(net, &net->d_loss_count, 1));
   RC(dev_alloc(net, &net->d_sumsq, 1));
   RC(dev_alloc(net, &net->d_clip_scale, 1));
+  RC(dev_alloc(net, &net->d_loss_tmp, 3));
   RC(dev_alloc(net, &net->ctx.d_error_flag, 1));
   RC(dev_alloc(net, &net->d_input, rows * net->layers[0].n_out));
   RC(dev_alloc(net, &net->d_desired, rows * net->layers.back().n_out));
@@ -267,7 +271,7 @@ static int allocate_buffers(myea_b200_net *net) {
     RC(dev_alloc(net, &net->norm_mean_avg, U));
     RC(dev_alloc(net, &net->norm_sigma_avg, U));
     RC(dev_alloc(net, &net->norm_stats, U * 6));
-    RC(dev_alloc(net, &net->norm_partial, static_cast<size_t>(2 * net->reduce_chunks + 3) * max_h));
+    RC(dev_alloc(net, &net->norm_partial, static_cast<size_t>(2 * net->reduce_chunks + 5) * max_h));  // partial sums | 3 coefficients | 2 cross-GPU sums
     for (size_t l = 1; l < net->layers.size(); ++l) {
       LayerPlan &L = net->layers[l];
       if (!L.has_norm) continue;
@@ -444,7 +448,7 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
   RC(gemm_nt(net->ctx, a, b, e, net->scratch));
   const float *cs = nullptr, *ch = nullptr;
   if (L.has_norm) {
-    RC(norm_forward_stats(net->ctx, L.summations, rows, L.n_out, L.norm, net->training ? 1 : 0));
+    RC(norm_forward_stats(net->ctx, L.summations, rows, L.n_out, L.norm, net->training ? 1 : 0, &net->hook));
     cs = L.norm.col_scale;
     ch = L.norm.col_shift;
   }
@@ -539,6 +543,14 @@ extern "C" int myea_b200_get_loss(myea_handle net, double *loss_sum, uint64_t *n
   CK(cudaMemcpyAsync(acc, net->d_loss_acc, sizeof(acc), cudaMemcpyDeviceToHost, net->ctx.stream));
   CK(cudaMemcpyAsync(&cnt, net->d_loss_count, sizeof(cnt), cudaMemcpyDeviceToHost, net->ctx.stream));
   CK(cudaStreamSynchronize(net->ctx.stream));
+  if (net->comm != nullptr) {  // Merge__Post__Training across ranks: every rank must call get_loss
+    double all[3] = {acc[0], acc[1], static_cast<double>(cnt)};
+    CK(cudaMemcpyAsync(net->d_loss_tmp, all, sizeof(all), cudaMemcpyHostToDevice, net->ctx.stream));
+    RC(comm_all_reduce_sum_f64(net, net->d_loss_tmp, 3));
+    CK(cudaMemcpyAsync(all, net->d_loss_tmp, sizeof(all), cudaMemcpyDeviceToHost, net->ctx.stream));
+    CK(cudaStreamSynchronize(net->ctx.stream));
+    acc[0] = all[0]; acc[1] = all[1]; cnt = static_cast<unsigned long long>(all[2] + 0.5);
+  }
   if (loss_sum) *loss_sum = acc[0];
   if (accuracy_sum) *accuracy_sum = acc[1];
   if (number_loss) *number_loss = cnt;
@@ -572,7 +584,7 @@ int fc_backward_from_fc(myea_b200_net *net, LayerPlan &L, const LayerPlan &next,
 }
 
 int fc_finish_backward(myea_b200_net *net, LayerPlan &L, long long rows) {
-  if (L.has_norm) return norm_backward(net->ctx, L.summations, L.deriv, L.errors, rows, L.n_out, L.norm);
+  if (L.has_norm) return norm_backward(net->ctx, L.summations, L.deriv, L.errors, rows, L.n_out, L.norm, &net->hook);
   return MYEA_OK;
 }
 
@@ -639,7 +651,9 @@ extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batc
   if (static_cast<long long>(batch) != net->B) return fail(net, MYEA_E_INVALID, "batch must equal the batch size the network was created for");
   CK(cudaSetDevice(net->ctx.device));
   const long long rows = net->T * net->B;
-  // last layer first: its bucket is ready first when a communicator overlaps the reduction
+  if (net->comm != nullptr && net->grads_reduced)
+    return fail(net, MYEA_E_UNSUPPORTED, "with a communicator attached, call update_parameter after every update_derivative_weight (the derivative buckets of this step were already summed over the ranks)");
+  // last layer first: its bucket is complete first, and its all-reduce overlaps the contractions of the layers below
   for (int l = static_cast<int>(net->layers.size()) - 1; l >= 1; --l) {
     LayerPlan &L = net->layers[l];
     if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
@@ -650,6 +664,12 @@ extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batc
     } else if (L.type == MYEA_LAYER_LSTM) {
       RC(lstm_update_derivative_weight(net, L, net->layers[L.input_layer].values, L.n_in));
     }
+    if (net->comm != nullptr && L.type != MYEA_LAYER_RESIDUAL)
+      RC(comm_reduce_bucket_async(net, L.idx.first_connection_index, L.idx.last_connection_index - L.idx.first_connection_index));
+  }
+  if (net->comm != nullptr) {  // biases and normalization scales / shifts: one last bucket behind the weights
+    RC(comm_reduce_bucket_async(net, net->total_weights, net->total_parameters - net->total_weights));
+    net->grads_reduced = true;
   }
   return MYEA_OK;
 }
@@ -662,7 +682,11 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
   if (net == nullptr || opt == nullptr || training_size == 0) return MYEA_E_INVALID;
   CK(cudaSetDevice(net->ctx.device));
   const size_t P = net->total_parameters;
-  if (net->comm != nullptr) RC(comm_all_reduce_sum(net, net->grads, P));
+  if (net->comm != nullptr) {
+    if (net->grads_reduced) RC(comm_join(net));            // buckets issued by update_derivative_weight
+    else RC(comm_all_reduce_sum(net, net->grads, P));      // nothing was issued: reduce everything now
+    net->grads_reduced = false;
+  }
   OptLaunch o;
   o.type = opt->type_optimizer_function;
   if (opt->use_clip_gradient) {

@@ -64,5 +64,8 @@ struct myea_b200_net {
   float optimizer_time_step = 0.f;
   bool training = true;
   myea::CommState *comm = nullptr;
+  myea::SumHook hook;            // cross-GPU sum of normalization column sums (world 1: unused)
+  bool grads_reduced = false;    // this step's derivative buckets have already been handed to the communicator
+  double *d_loss_tmp = nullptr;  // [3] staging for the cross-GPU sum of the loss accumulators
   std::vector<void *> allocations;
 };

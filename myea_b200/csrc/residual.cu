@@ -104,7 +104,7 @@ int residual_forward(myea_b200_net *net, int r) {
       const float *prev = net->layers[r + k - 1].summations;
       const float *cs = nullptr, *ch = nullptr;
       if (L.has_norm) {
-        RRC(norm_forward_stats(ctx, prev, rows, L.n_in, L.norm, net->training ? 1 : 0));
+        RRC(norm_forward_stats(ctx, prev, rows, L.n_in, L.norm, net->training ? 1 : 0, &net->hook));
         cs = L.norm.col_scale;
         ch = L.norm.col_shift;
       }
@@ -152,7 +152,7 @@ int residual_backward(myea_b200_net *net, int r) {
     e.ld_aux = L.n_in;
     if (L.has_norm) { e.col_scale = L.norm.col_scale; e.col_shift = L.norm.col_shift; }
     RRC(gemm_nt(ctx, a, b, e, net->scratch));
-    if (L.has_norm) RRC(norm_backward(ctx, below.summations, L.deriv, below.errors, rows, L.n_in, L.norm));
+    if (L.has_norm) RRC(norm_backward(ctx, below.summations, L.deriv, below.errors, rows, L.n_in, L.norm, &net->hook));
   }
   // the layer feeding the block: skip error + W_1^T delta_1, then its own activation derivative / normalization
   LayerPlan &first = net->layers[r + 1];

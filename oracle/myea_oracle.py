@@ -156,6 +156,8 @@ class OracleNet:
                     capi.BUF_PREVIOUS_DELTA: z(self.P), capi.BUF_NORM_MEAN_AVERAGE: z(self.n_norm),
                     capi.BUF_NORM_VARIANCE_AVERAGE: np.ones(self.n_norm, dtype)}
         self.masks, self.zone, self.shake = {}, {}, {}
+        # sharded batch: `allreduce(array) -> array summed over the ranks` and the number of ranks (tests/test_sharding_cpu.py)
+        self.allreduce, self.world = None, 1
         self.time_step = dtype(0)
         self.loss_sum, self.n_loss, self.acc_sum = 0.0, 0, 0.0
         self.training = True
@@ -229,9 +231,12 @@ class OracleNet:
         ma = self.buf[capi.BUF_NORM_MEAN_AVERAGE][o:o + H]
         sa = self.buf[capi.BUF_NORM_VARIANCE_AVERAGE][o:o + H]
         if self.training:
-            inv = dt(1) / dt(z.shape[0])
-            mean = z.sum(0, dtype=dt) * inv
-            sigma = np.sqrt((z * z).sum(0, dtype=dt) * inv - mean * mean + self.eps)
+            s1, s2 = z.sum(0, dtype=dt), (z * z).sum(0, dtype=dt)
+            if self.allreduce is not None:   # the statistics are those of the whole batch, whichever rank holds which rows
+                s1, s2 = self.allreduce(s1), self.allreduce(s2)
+            inv = dt(1) / dt(z.shape[0] * self.world)
+            mean = s1 * inv
+            sigma = np.sqrt(s2 * inv - mean * mean + self.eps)
             ma += self.momentum * (mean - ma)
             sa += self.momentum * (sigma - sa)
             r, d = np.ones(H, dt), np.zeros(H, dt)
@@ -247,13 +252,15 @@ class OracleNet:
     def _norm_backward(self, L, z, delta):
         """Backward_Pass__Batch_Normalization / __Batch_Renormalization (Neural_Network__Backward_Pass__Loop.cpp:1380-1628)"""
         dt = self.dt
-        H, B = L.n_out, dt(z.shape[0])
+        H, B = L.n_out, dt(z.shape[0] * self.world)
         gamma = self._p()[L.idx["scale_index"]:L.idx["scale_index"] + H]
         self._g()[L.idx["scale_index"]:L.idx["scale_index"] + H] += (delta * L.xhat).sum(0, dtype=dt)
         self._g()[L.idx["shift_index"]:L.idx["shift_index"] + H] += delta.sum(0, dtype=dt)
         dh = delta * gamma
         d_mean = (dh * (-L.r / L.sigma)).sum(0, dtype=dt)
         d_sigma = (dh * (z - L.mean) * (-L.r / (L.sigma * L.sigma))).sum(0, dtype=dt)
+        if self.allreduce is not None:       # scale / shift derivatives stay local (summed with the other derivatives later)
+            d_mean, d_sigma = self.allreduce(d_mean), self.allreduce(d_sigma)
         return dh * (L.r / L.sigma) + d_sigma * ((z - L.mean) / (B * L.sigma)) + d_mean * (dt(1) / B)
 
     def _fc_forward(self, l, x):
@@ -398,6 +405,8 @@ class OracleNet:
         dt = self.dt
         N = training_size or self.B
         g, w = self._g(), self._p()
+        if self.allreduce is not None:       # Merge_Derivatives_Parameters across ranks
+            g[:] = self.allreduce(g)
         if o.use_clip_gradient:
             norm = np.sqrt((g * g).sum(dtype=dt))
             if norm >= dt(o.clip_gradient):
