@@ -27,6 +27,7 @@
 
 #include <cudaTypedefs.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace myea {
 
@@ -122,6 +123,47 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- CTA-pair (cta_group::2) forms ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion bytes are counted on the LEADER CTA's mbarrier (same offset, peer bit of the cluster
+// shared-memory address cleared); no multicast: every CTA fetches its own tile.
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_holder, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrives on the mbarrier at this offset in BOTH CTAs of the pair once all earlier MMAs of this thread are complete
+__device__ __forceinline__ void tc_commit_pair(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+               "h"(static_cast<uint16_t>(3))
+               : "memory");
+}
+__device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 }  // namespace ptx
 
 // ---------------------------------------------------------------------------------------------------------
@@ -172,6 +214,44 @@ __device__ __forceinline__ float epilogue_value(const Epilogue &e, float acc, lo
   }
   if (e.accumulate) v += e.C[m * e.ldc + n];
   return v;
+}
+
+
+// Epilogue of one 32-row x 32-column chunk held transposed in shared memory (tr[row][column], pitch 33): lane = column.
+// All global reads of a half-chunk (16 rows x up to 4 arrays) are issued before the first dependent use, so their
+// latencies overlap instead of adding up row after row.
+__device__ __forceinline__ void epilogue_chunk(const Epilogue &e, const float *tr, int lane, long long row_base, long long n, int rows_valid,
+                                               bool col_valid) {
+  if (!col_valid || rows_valid <= 0) return;
+  const float bias = e.bias != nullptr ? e.bias[n] : 0.f;
+  const bool deriv = e.deriv_af != 0u;
+  const bool affine = deriv && e.aux_pre != nullptr && e.col_scale != nullptr;
+  const float cs = affine ? e.col_scale[n] : 1.f, ch = affine ? e.col_shift[n] : 0.f;
+  const float *__restrict__ p_add = e.addend, *__restrict__ p_pre = deriv ? e.aux_pre : nullptr, *__restrict__ p_y = deriv ? e.aux_y : nullptr;
+  float *__restrict__ C = e.C;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    float add[16], pre[16], y[16], old[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int rr = half * 16 + i;
+      const long long m = row_base + rr;
+      const bool in = rr < rows_valid;
+      add[i] = (p_add != nullptr && in) ? p_add[m * e.ld_addend + n] : 0.f;
+      pre[i] = (p_pre != nullptr && in) ? p_pre[m * e.ld_aux + n] : 0.f;
+      y[i] = (p_y != nullptr && in) ? p_y[m * e.ld_aux + n] : 0.f;
+      old[i] = (e.accumulate && in) ? C[m * e.ldc + n] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int rr = half * 16 + i;
+      if (rr < rows_valid) {
+        float v = tr[rr * 33 + lane] + bias + add[i];
+        if (deriv) v *= af_derive(e.deriv_af, pre[i] * cs + ch, y[i]);
+        C[(row_base + rr) * e.ldc + n] = v + old[i];
+      }
+    }
+  }
 }
 
 template <int BN, int STAGES>
@@ -309,14 +389,8 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
         for (int j = 0; j < 32; ++j) tr[lane * 33 + j] = sum[j];
         __syncwarp();
         const long long n = static_cast<long long>(n0) + c + lane;
-        if (n < dims.N) {
-#pragma unroll 4
-          for (int rr = 0; rr < 32; ++rr) {
-            const long long m = row_base + rr;
-            if (m >= dims.M) break;
-            epi.C[m * epi.ldc + n] = epilogue_value(epi, tr[rr * 33 + lane], m, n);
-          }
-        }
+        const long long left = static_cast<long long>(dims.M) - row_base;
+        epilogue_chunk(epi, tr, lane, row_base, n, left > 32 ? 32 : static_cast<int>(left), n < dims.N);
         __syncwarp();
       }
     }
@@ -336,6 +410,159 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// CTA-pair variant: two CTAs of a cluster (two SMs) compute one 256 x 128 output tile with tcgen05.mma.cta_group::2
+// (M = 256, N = 128, K = 8).  Each CTA stages only ITS 128 rows of A and ITS 64 rows of B (hi and lo: 48 KB per
+// stage, 4 stages) and the tensor cores of the pair exchange the B halves themselves, so every SM writes 25 % fewer
+// bytes into shared memory per product and the tensor core reads 6 KB instead of 8 KB of it per MMA: the 128 x 128
+// single-CTA tile is bounded by shared-memory bandwidth at about 60 % of the tensor peak, this shape at about 80 %.
+// The leader CTA (cluster rank 0) issues every MMA; completion bytes of both CTAs' TMA loads are counted on the
+// leader's "full" barrier; tcgen05.commit multicasts the "empty" / "accumulator ready" arrivals to both CTAs.  Each CTA
+// owns the accumulator rows of its half (tensor memory lanes 0-127, the same four 128-column accumulators) and runs
+// its own epilogue.  No TMA multicast is used.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int PAIR_STAGES = 4;
+struct PairSmem {
+  static constexpr int A_BYTES = BM * BK * 4;        // 128 rows
+  static constexpr int B_BYTES = 64 * BK * 4;        // this CTA's half of the 128-row B tile
+  static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  static constexpr int BAR_OFFSET = PAIR_STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm3x_tf32_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
+                                const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
+                                const GemmDims dims, const Epilogue epi, int *error_flag) {
+  using S = PairSmem;
+  constexpr int BN = 128, N_MAIN = 3, TMEM_COLS = 512, STAGES = PAIR_STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  // the dynamic shared-memory window starts at the same offset in both CTAs, so aligned offsets match as well
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + S::BAR_OFFSET);
+  uint64_t *empty_bar = full_bar + STAGES;
+  uint64_t *tmem_full_bar = empty_bar + STAGES;
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tmem_full_bar + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = ptx::cluster_ctarank();  // 0 = leader
+  const int m0 = (blockIdx.x >> 1) * 256 + static_cast<int>(cta_rank) * BM;  // this CTA's 128 rows (the pair sits along grid x)
+  const int n0 = blockIdx.y * BN;
+  const int nb0 = n0 + static_cast<int>(cta_rank) * 64;                       // this CTA's 64 rows of B
+  const int num_kb = (dims.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);   // leader: its own arrive.expect_tx (bytes of both CTAs)
+      ptx::mbar_init(&empty_bar[s], 1);  // one multicast commit
+    }
+    ptx::mbar_init(tmem_full_bar, 1);
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(tmem_holder, TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  bool ok = true;
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = static_cast<uint32_t>(kb / STAGES) & 1u;
+        if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u)) { ok = false; break; }
+        uint8_t *st = smem + s * S::STAGE_BYTES;
+        if (cta_rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * S::STAGE_BYTES);
+        ptx::tma_load_2d_pair(st, &tm_a_hi, &full_bar[s], kb * BK, m0);
+        ptx::tma_load_2d_pair(st + S::A_BYTES, &tm_a_lo, &full_bar[s], kb * BK, m0);
+        ptx::tma_load_2d_pair(st + 2 * S::A_BYTES, &tm_b_hi, &full_bar[s], kb * BK, nb0);
+        ptx::tma_load_2d_pair(st + 2 * S::A_BYTES + S::B_BYTES, &tm_b_lo, &full_bar[s], kb * BK, nb0);
+      }
+      if (!ok) atomicCAS(error_flag, 0, 201);
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_tf32(256, BN);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = static_cast<uint32_t>(kb / STAGES) & 1u;
+        if (!ptx::mbar_wait(&full_bar[s], ph)) { ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t st = ptx::smem_u32(smem + s * S::STAGE_BYTES);
+        const uint64_t a_hi = make_smem_desc(st);
+        const uint64_t a_lo = make_smem_desc(st + S::A_BYTES);
+        const uint64_t b_hi = make_smem_desc(st + 2 * S::A_BYTES);
+        const uint64_t b_lo = make_smem_desc(st + 2 * S::A_BYTES + S::B_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint64_t koff = static_cast<uint64_t>((k * UMMA_K * 4) >> 4);
+          const int step = kb * (BK / UMMA_K) + k;
+          const int main_acc = step % N_MAIN;
+          const uint32_t t_small = tmem_base + static_cast<uint32_t>(N_MAIN * BN);
+          ptx::mma_tf32_pair(t_small, a_lo + koff, b_hi + koff, idesc, step > 0 ? 1u : 0u);
+          ptx::mma_tf32_pair(t_small, a_hi + koff, b_lo + koff, idesc, 1u);
+          ptx::mma_tf32_pair(tmem_base + static_cast<uint32_t>(main_acc * BN), a_hi + koff, b_hi + koff, idesc, step >= N_MAIN ? 1u : 0u);
+        }
+        ptx::tc_commit_pair(&empty_bar[s]);
+      }
+      ptx::tc_commit_pair(tmem_full_bar);
+      if (!ok) atomicCAS(error_flag, 0, 202);
+    }
+  } else {
+    const int q = warp & 3;
+    if (!ptx::mbar_wait(tmem_full_bar, 0)) {
+      ok = false;
+      if (lane == 0) atomicCAS(error_flag, 0, 203);
+    }
+    ptx::tc_fence_after();
+    if (ok && num_kb > 0) {
+      float *tr = reinterpret_cast<float *>(smem) + (warp - 2) * (32 * 33);
+      const long long row_base = static_cast<long long>(m0) + q * 32;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        if (n0 + c >= dims.N) break;
+        uint32_t r[32];
+        float sum[32];
+        const uint32_t t_chunk = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c);
+        ptx::tmem_ld_32x32(t_chunk + static_cast<uint32_t>(N_MAIN * BN), r);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum[j] = __uint_as_float(r[j]);
+#pragma unroll
+        for (int a = 0; a < N_MAIN; ++a) {
+          ptx::tmem_ld_32x32(t_chunk + static_cast<uint32_t>(a * BN), r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[j] += __uint_as_float(r[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tr[lane * 33 + j] = sum[j];
+        __syncwarp();
+        const long long n = static_cast<long long>(n0) + c + lane;
+        const long long left = static_cast<long long>(dims.M) - row_base;
+        epilogue_chunk(epi, tr, lane, row_base, n, left > 32 ? 32 : static_cast<int>(left), n < dims.N);
+        __syncwarp();
+      }
+    }
+  }
+  // the accumulator-ready arrival is the last thing the leader sends; once both CTAs have seen it (or given up) nobody
+  // touches the peer's shared memory or barriers any more
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -531,6 +758,33 @@ static int launch_tcgen05(Context &ctx, const CUtensorMap maps[4], const GemmDim
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
+static int launch_tcgen05_pair(Context &ctx, const CUtensorMap maps[4], const GemmDims &dims, const Epilogue &epi) {
+  static bool configured[16] = {};
+  if (!configured[ctx.device & 15]) {
+    if (cudaFuncSetAttribute(gemm3x_tf32_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL) != cudaSuccess) return MYEA_E_CUDA;
+    configured[ctx.device & 15] = true;
+  }
+  // the cluster shape (2, 1, 1) is a compile-time attribute of the kernel: the two CTAs of a pair are neighbours along
+  // grid x and split the 256 rows of the tile; grid y walks the column tiles
+  dim3 grid(static_cast<unsigned>(2 * ((dims.M + 255) / 256)), static_cast<unsigned>((dims.N + 127) / 128));
+  gemm3x_tf32_tcgen05_pair_kernel<<<grid, GEMM_THREADS, PairSmem::TOTAL, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], dims, epi, ctx.d_error_flag);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess && getenv("MYEA_B200_DEBUG") != nullptr) {
+    fprintf(stderr, "pair kernel launch: %s\n", cudaGetErrorString(err));
+    cudaFuncAttributes fa;
+    cudaError_t e2 = cudaFuncGetAttributes(&fa, gemm3x_tf32_tcgen05_pair_kernel);
+    fprintf(stderr, "  attrs (%s): regs %d static smem %zu maxdyn %d maxthreads %d clusterDimMustBeSet %d required cluster %d %d %d nonportable %d\n",
+            cudaGetErrorString(e2), fa.numRegs, fa.sharedSizeBytes, fa.maxDynamicSharedSizeBytes, fa.maxThreadsPerBlock, fa.clusterDimMustBeSet,
+            fa.requiredClusterWidth, fa.requiredClusterHeight, fa.requiredClusterDepth, fa.nonPortableClusterSizeAllowed);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = PairSmem::TOTAL;
+    int n = -1;
+    cudaError_t e3 = cudaOccupancyMaxActiveClusters(&n, gemm3x_tf32_tcgen05_pair_kernel, &cfg);
+    fprintf(stderr, "  occupancy: %s clusters %d grid %u %u\n", cudaGetErrorString(e3), n, grid.x, grid.y);
+  }
+  return err == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
 // C (+)= A * B^T on operands whose panels are already in place; (row0, rows) select a row range of each panel set.
 int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, const Panels &B, long long b_row0, long long N,
                 const Epilogue &epi) {
@@ -546,13 +800,18 @@ int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, co
     ctx.end(TC_GEMM);
     rc = cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
   } else {
-    const int bn = ctx.gemm_bn == 256 ? 256 : 128;  // 128: four accumulators of 128 columns, the accurate configuration
+    // tile shape: CTA pairs (256 x 128 per pair) unless forced to a single-CTA shape (gemm_bn 128 / 256) or there is
+    // only one row tile; 128-column accumulators (four of them) are the accurate configuration
+    const bool pair = ctx.gemm_bn == 0 ? (M > 128) : (ctx.gemm_bn == 2);
+    const int bn = ctx.gemm_bn == 256 ? 256 : 128;
     CUtensorMap maps[4];
     const bool ok = make_panel_map(&maps[0], A.hi + a_row0 * A.kp, M, A.k, A.kp, BM) && make_panel_map(&maps[1], A.lo + a_row0 * A.kp, M, A.k, A.kp, BM) &&
-                    make_panel_map(&maps[2], B.hi + b_row0 * B.kp, N, B.k, B.kp, bn) && make_panel_map(&maps[3], B.lo + b_row0 * B.kp, N, B.k, B.kp, bn);
+                    make_panel_map(&maps[2], B.hi + b_row0 * B.kp, N, B.k, B.kp, pair ? 64 : bn) &&
+                    make_panel_map(&maps[3], B.lo + b_row0 * B.kp, N, B.k, B.kp, pair ? 64 : bn);
     if (!ok) return MYEA_E_CUDA;
     ctx.begin(TC_GEMM);
-    rc = (bn == 256) ? launch_tcgen05<256, 2>(ctx, maps, dims, epi) : launch_tcgen05<128, 3>(ctx, maps, dims, epi);
+    if (pair) rc = launch_tcgen05_pair(ctx, maps, dims, epi);
+    else rc = (bn == 256) ? launch_tcgen05<256, 2>(ctx, maps, dims, epi) : launch_tcgen05<128, 3>(ctx, maps, dims, epi);
     ctx.end(TC_GEMM);
   }
   ctx.gemm_flops += 2.0 * dims.M * dims.N * static_cast<double>(dims.K);

@@ -2,6 +2,7 @@
 // parity tests and by roofline timing of the GEMM alone.
 #include "common.cuh"
 
+#include <stdio.h>
 #include <stdlib.h>
 #include <vector>
 
@@ -14,7 +15,7 @@ extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N,
   Context ctx;
   ctx.device = device;
   ctx.gemm_engine = engine & 1;
-  ctx.gemm_bn = (engine >> 8) & 0x1FF;  // bits 8..16: forced N tile (0 = heuristic), for tile-shape experiments
+  ctx.gemm_bn = (engine >> 8) & 0x1FF;  // bits 8..16: forced tile shape (0 = heuristic, 2 = CTA pair, 128 / 256 = single-CTA N tile)
   int rc = MYEA_OK;
   float *dA = nullptr, *dB = nullptr, *dC = nullptr, *dS = nullptr;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
@@ -59,7 +60,13 @@ extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N,
     if (cudaMemcpyAsync(C, dC, M * N * 4, cudaMemcpyDeviceToHost, ctx.stream) != cudaSuccess) rc = MYEA_E_CUDA;
     int flag = 0;
     cudaMemcpyAsync(&flag, ctx.d_error_flag, sizeof(int), cudaMemcpyDeviceToHost, ctx.stream);
-    if (cudaStreamSynchronize(ctx.stream) != cudaSuccess) rc = MYEA_E_CUDA;
+    {
+      const cudaError_t se = cudaStreamSynchronize(ctx.stream);
+      if (se != cudaSuccess) {
+        if (getenv("MYEA_B200_DEBUG") != nullptr) fprintf(stderr, "gemm_nt: %s\n", cudaGetErrorString(se));
+        rc = MYEA_E_CUDA;
+      }
+    }
     if (rc == MYEA_OK && flag != 0) rc = MYEA_E_KERNEL;
   }
   if (e0) cudaEventDestroy(e0);

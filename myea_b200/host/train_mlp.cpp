@@ -1,0 +1,64 @@
+// Example and self-check of the host mirror: config 1 of the benchmark list (MLP 64-256-256-10, tanh / softmax,
+// cross-entropy, Adam, batch 128) trained for a few steps on seeded synthetic data, written the way the reference's
+// own harness drives `class Neural_Network` (Neural_Network_Launcher_Windows/Source_Files/debug.cpp).
+// Prints one line per step: "step <i> loss <mean cross-entropy term> accuracy <percent>".
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <random>
+#include <vector>
+
+#include "Neural_Network.hpp"
+
+using MyEA::B200::Layer_Parameters;
+using MyEA::B200::Neural_Network;
+
+int main(int argc, char **argv) {
+  int const steps = argc > 1 ? atoi(argv[1]) : 10;
+  size_t const B = 128, sizes[4] = {64, 256, 256, 10};
+  Layer_Parameters lp[4];
+  for (int i = 0; i < 4; ++i) { lp[i].type_layer = MYEA_LAYER_FULLY_CONNECTED; lp[i].unit_parameters[0] = sizes[i]; }
+  Neural_Network nn;
+  if (!nn.Compile(4, 1, MYEA_NETWORK_FEEDFORWARD, lp)) return 1;
+  nn.Set__Layer_Activation_Function(1, MYEA_AF_TANH);
+  nn.Set__Layer_Activation_Function(2, MYEA_AF_TANH);
+  nn.Set__Layer_Activation_Function(3, MYEA_AF_SOFTMAX);
+  nn.Set__Loss_Function(MYEA_LOSS_CROSS_ENTROPY);
+  nn.Set__Accuracy_Function(MYEA_ACCURACY_CROSS_ENTROPY);
+  nn.Set__Optimizer_Function(MYEA_OPT_ADAM);
+  if (!nn.Update__Batch_Size(B) || !nn.Initialize__CUDA(0)) return 1;
+  std::mt19937 gen(0);
+  for (int l = 1; l < 4; ++l) {  // Glorot-uniform, tanh gain 5/3 on the hidden layers
+    float const gain = l < 3 ? 5.f / 3.f : 1.f, bound = gain * sqrtf(6.f / float(sizes[l - 1] + sizes[l]));
+    std::uniform_real_distribution<float> u(-bound, bound);
+    myea_layer_index const &ix = nn.Get__Layer_Index(l);
+    for (uint64_t i = ix.first_connection_index; i < ix.last_connection_index; ++i) nn.ptr_array_parameters[i] = u(gen);
+  }
+  if (!nn.Copy__Parameters__Host_To_Device()) return 1;
+  std::uniform_real_distribution<float> ux(-1.f, 1.f);
+  std::vector<std::vector<float>> X(B, std::vector<float>(64)), Y(B, std::vector<float>(10, 0.f));
+  std::vector<float const *> xp(B), yp(B);
+  for (size_t b = 0; b < B; ++b) {
+    for (float &v : X[b]) v = ux(gen);
+    Y[b][gen() % 10] = 1.f;
+    xp[b] = X[b].data();
+    yp[b] = Y[b].data();
+  }
+  nn.type_state_propagation = 1;
+  nn.Clear_Training_Arrays();
+  float first = 0.f, last = 0.f;
+  for (int it = 0; it < steps; ++it) {
+    nn.Reset__Loss();
+    nn.Forward_Pass(B, xp.data());
+    nn.Compute__Error(B, yp.data());
+    nn.Backward_Pass(B);
+    nn.Update_Derivative_Weight(B);
+    nn.number_accuracy_trial = B;
+    last = nn.Get__Loss();
+    if (it == 0) first = last;
+    printf("step %d loss %.6f accuracy %.2f\n", it, last, nn.Get__Accuracy());
+    nn.Update_Parameter(B, B);
+  }
+  if (!nn.Copy__Parameters__Device_To_Host()) return 1;
+  return (last < first) ? 0 : 2;   // the loss must go down on a fixed batch
+}
