@@ -106,9 +106,14 @@ struct Operand {
 };
 
 // K-major hi / lo panels of one operand, pitch kp floats (a multiple of 32): what the tensor-core kernel reads with TMA.
+// `hi`: TF32-rounded values in fp32 containers.  `lo`: the CROSS panel, per 8 K elements 16 bf16 = [lo x8 | hi x8] for the
+// left operand (role A) and [hi x8 | lo x8] for the right operand (role B), so that one K = 16 BF16 MMA of an A group with
+// a B group yields lo_a*hi_b + hi_a*lo_b.
+enum { PANEL_ROLE_A = 0, PANEL_ROLE_B = 1 };
 struct Panels {
   float *hi = nullptr, *lo = nullptr;
   long long rows = 0, k = 0, kp = 0;
+  int role = PANEL_ROLE_A;
 };
 
 struct GemmScratch {   // hi/lo K-major panels of both operands, reused by every contraction of a handle
@@ -118,8 +123,8 @@ struct GemmScratch {   // hi/lo K-major panels of both operands, reused by every
 
 size_t gemm_scratch_floats(long long M, long long N, long long K);
 size_t panel_floats(long long rows, long long k);
-Panels panels_at(float *mem, long long rows, long long k);
-int gemm_prepare(Context &ctx, const Operand &op, float *mem, Panels *out);
+Panels panels_at(float *mem, long long rows, long long k, int role);
+int gemm_prepare(Context &ctx, const Operand &op, float *mem, Panels *out, int role);
 int gemm_prepare_into(Context &ctx, const Operand &op, const Panels &dst, long long row_offset, long long k_offset);
 int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, const Panels &B, long long b_row0, long long N,
                 const Epilogue &epi);

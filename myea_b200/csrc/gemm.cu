@@ -26,6 +26,7 @@
 #include "common.cuh"
 
 #include <cudaTypedefs.h>
+#include <cuda_bf16.h>
 #include <stdio.h>
 #include <stdlib.h>
 
@@ -108,6 +109,18 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
       : "memory");
 }
 
+// D[tmem] (+)= A * B, BF16 inputs (K = 16), FP32 accumulate: the cross-term instruction
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // 32 lanes x 32 consecutive fp32 columns of tensor memory -> 32 registers per thread
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -153,6 +166,16 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t *bar) {
                "h"(static_cast<uint16_t>(3))
                : "memory");
 }
+__device__ __forceinline__ void mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n"
@@ -192,6 +215,10 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 // 10-12, both operands K-major (bits 15, 16 clear), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
 __host__ __device__ constexpr uint32_t make_idesc_tf32(int m, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+// tcgen05.mma.kind::f16 with BF16 inputs (format 1) and an F32 accumulator
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 struct GemmDims {
@@ -346,8 +373,7 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
           const int step = kb * (BK / UMMA_K) + k;
           const int main_acc = step % N_MAIN;
           const uint32_t t_small = tmem_base + static_cast<uint32_t>(N_MAIN * BN);
-          ptx::mma_tf32(t_small, a_lo + koff, b_hi + koff, idesc, step > 0 ? 1u : 0u);
-          ptx::mma_tf32(t_small, a_hi + koff, b_lo + koff, idesc, 1u);
+          ptx::mma_bf16(t_small, a_lo + koff, b_lo + koff, make_idesc_bf16(BM, BN), step > 0 ? 1u : 0u);  // both cross terms
           ptx::mma_tf32(tmem_base + static_cast<uint32_t>(main_acc * BN), a_hi + koff, b_hi + koff, idesc,
                         step >= N_MAIN ? 1u : 0u);
         }
@@ -509,8 +535,7 @@ gemm3x_tf32_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
           const int step = kb * (BK / UMMA_K) + k;
           const int main_acc = step % N_MAIN;
           const uint32_t t_small = tmem_base + static_cast<uint32_t>(N_MAIN * BN);
-          ptx::mma_tf32_pair(t_small, a_lo + koff, b_hi + koff, idesc, step > 0 ? 1u : 0u);
-          ptx::mma_tf32_pair(t_small, a_hi + koff, b_lo + koff, idesc, 1u);
+          ptx::mma_bf16_pair(t_small, a_lo + koff, b_lo + koff, make_idesc_bf16(256, BN), step > 0 ? 1u : 0u);  // both cross terms
           ptx::mma_tf32_pair(tmem_base + static_cast<uint32_t>(main_acc * BN), a_hi + koff, b_hi + koff, idesc, step >= N_MAIN ? 1u : 0u);
         }
         ptx::tc_commit_pair(&empty_bar[s]);
@@ -569,49 +594,75 @@ gemm3x_tf32_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
 // ---------------------------------------------------------------------------------------------------------
 // Operand preparation: fp32 matrix (either stride order) -> K-major hi / lo panels [rows][kp]
 // ---------------------------------------------------------------------------------------------------------
-// Round-to-nearest on both parts: truncation would bias every product the same way and the error of a K-long
-// sum would grow like K instead of sqrt(K).
+// Operand panels.  x = hi + lo with hi = x rounded to TF32 (round to nearest: truncation would bias every product the
+// same way) and lo = x - hi (exact in fp32, at most 2^-11 |x|).  A product a*b is evaluated as
+//     hi_a*hi_b                      one TF32 MMA (K = 8) into a "main" accumulator
+//   + lo_a*hi_b + hi_a*lo_b          ONE BF16 MMA (K = 16) into the "cross" accumulator
+// The cross terms are 2^-11 of the result, so 8 significant bits are enough for them (error 2^-19 of the result, below
+// the fp32 accumulation noise of a long sum); packing both into one K = 16 instruction saves a third of the tensor work
+// of the classical three-pass split.  Per 8 consecutive K elements the cross panel holds 16 bf16 (32 bytes, the same
+// footprint as 8 fp32):  operand A: [lo x8 | hi x8],  operand B: [hi x8 | lo x8],  so that the K = 16 dot product of
+// an A group with a B group is sum lo_a*hi_b + sum hi_a*lo_b.
+// `raw` panels (FP32 FMA engine): hi = x unrounded, cross = 0.
 __device__ __forceinline__ float round_tf32(float x) {
   uint32_t r;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return __uint_as_float(r);
 }
-__device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
-  hi = round_tf32(x);
-  lo = round_tf32(x - hi);
-}
+__device__ __forceinline__ uint32_t bf16_bits(float x) { return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(x))); }
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) { return bf16_bits(a) | (bf16_bits(b) << 16); }
 
-// source already K-major (stride_k == 1); writes columns [0, round_up(k, 4)) of every panel row (pitch kp)
-__global__ void split_rows_kernel(const float *__restrict__ src, long long stride_r, long long rows, long long k, long long kp,
-                                  float *__restrict__ hi, float *__restrict__ lo) {
-  const long long kq = (k + 3) >> 2;  // float4 groups written per panel row
-  const long long total = rows * kq;
-  const bool vec = ((stride_r & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / kq;
-    const long long c = (i - r * kq) << 2;
-    float v[4];
-    if (vec && c + 3 < k) {
-      const float4 t = *reinterpret_cast<const float4 *>(src + r * stride_r + c);
-      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-    } else {
+// one group of 8 K elements -> 8 hi floats and the 8 words of the cross group
+__device__ __forceinline__ void split_group(const float (&v)[8], int role_b, int raw, float (&hi)[8], uint32_t (&cross)[8]) {
+  float lo[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] = (c + j < k) ? src[r * stride_r + c + j] : 0.f;
-    }
-    float4 h, l;
-    split_tf32(v[0], h.x, l.x);
-    split_tf32(v[1], h.y, l.y);
-    split_tf32(v[2], h.z, l.z);
-    split_tf32(v[3], h.w, l.w);
-    *reinterpret_cast<float4 *>(hi + r * kp + c) = h;
-    *reinterpret_cast<float4 *>(lo + r * kp + c) = l;
+  for (int j = 0; j < 8; ++j) {
+    hi[j] = raw ? v[j] : round_tf32(v[j]);
+    lo[j] = v[j] - hi[j];
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t l = raw ? 0u : pack_bf16(lo[2 * j], lo[2 * j + 1]);
+    const uint32_t h = raw ? 0u : pack_bf16(hi[2 * j], hi[2 * j + 1]);
+    cross[j] = role_b ? h : l;
+    cross[4 + j] = role_b ? l : h;
   }
 }
 
-// source MN-major (stride_r == 1): tiled transposition, 32x32 tile per block of 32x8 threads
+// source already K-major (stride_k == 1); writes columns [0, round_up(k, 8)) of every panel row (pitch kp)
+__global__ void split_rows_kernel(const float *__restrict__ src, long long stride_r, long long rows, long long k, long long kp,
+                                  float *__restrict__ hi, float *__restrict__ cross, int role_b, int raw) {
+  const long long kg = (k + 7) >> 3;  // groups of 8 per panel row
+  const long long total = rows * kg;
+  const bool vec = ((stride_r & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / kg;
+    const long long c = (i - r * kg) << 3;
+    float v[8];
+    if (vec && c + 7 < k) {
+      const float4 t = *reinterpret_cast<const float4 *>(src + r * stride_r + c);
+      const float4 u = *reinterpret_cast<const float4 *>(src + r * stride_r + c + 4);
+      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; v[4] = u.x; v[5] = u.y; v[6] = u.z; v[7] = u.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (c + j < k) ? src[r * stride_r + c + j] : 0.f;
+    }
+    float h[8];
+    uint32_t x[8];
+    split_group(v, role_b, raw, h, x);
+    float4 *ph = reinterpret_cast<float4 *>(hi + r * kp + c);
+    ph[0] = make_float4(h[0], h[1], h[2], h[3]);
+    ph[1] = make_float4(h[4], h[5], h[6], h[7]);
+    uint4 *px = reinterpret_cast<uint4 *>(cross + r * kp + c);
+    px[0] = make_uint4(x[0], x[1], x[2], x[3]);
+    px[1] = make_uint4(x[4], x[5], x[6], x[7]);
+  }
+}
+
+// source MN-major (stride_r == 1): tiled transposition, 32 (K) x 32 (rows) tile per block of 32 x 8 threads
 __global__ void split_transpose_kernel(const float *__restrict__ src, long long stride_k, long long rows, long long k,
-                                       long long kp, float *__restrict__ hi, float *__restrict__ lo) {
+                                       long long kp, float *__restrict__ hi, float *__restrict__ cross, int role_b, int raw) {
   __shared__ float tile[32][33];
   const long long r0 = static_cast<long long>(blockIdx.x) * 32;  // panel rows (contiguous in the source)
   const long long k0 = static_cast<long long>(blockIdx.y) * 32;
@@ -620,13 +671,20 @@ __global__ void split_transpose_kernel(const float *__restrict__ src, long long 
     tile[j][threadIdx.x] = (kk < k && rr < rows) ? src[kk * stride_k + rr] : 0.f;
   }
   __syncthreads();
+  // thread x = word x of the row's 32 words: hi word = element x; cross word = bf16 pair (see the group layout above)
+  const int g = threadIdx.x >> 3, q = threadIdx.x & 7;       // group of 8 within the 32, word within the group
+  const int e = g * 8 + (q & 3) * 2;                         // first of the two source elements of this cross word
+  const bool want_lo = role_b ? (q >= 4) : (q < 4);
+  uint32_t *xw = reinterpret_cast<uint32_t *>(cross);
   for (int j = threadIdx.y; j < 32; j += 8) {
     const long long rr = r0 + j, kk = k0 + threadIdx.x;
-    if (rr < rows && kk < k) {
-      float h, l;
-      split_tf32(tile[threadIdx.x][j], h, l);
-      hi[rr * kp + kk] = h;
-      lo[rr * kp + kk] = l;
+    if (rr >= rows) continue;
+    if (kk < ((k + 7) & ~7ll)) {
+      const float x = tile[threadIdx.x][j];
+      hi[rr * kp + kk] = raw ? x : round_tf32(x);
+      const float x0 = tile[e][j], x1 = tile[e + 1][j];
+      const float h0 = round_tf32(x0), h1 = round_tf32(x1);
+      xw[rr * kp + kk] = raw ? 0u : (want_lo ? pack_bf16(x0 - h0, x1 - h1) : pack_bf16(h0, h1));
     }
   }
 }
@@ -690,7 +748,8 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
 static bool make_panel_map(CUtensorMap *map, const float *panel, long long rows, long long k, long long kp, int box_rows) {
   PFN_cuTensorMapEncodeTiled_v12000 fn = get_encode_fn();
   if (fn == nullptr) return false;
-  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  // panels are zero-filled up to the next multiple of 8 along K and the cross panel is only meaningful in whole groups of 8
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>((k + 7) & ~7ll), static_cast<cuuint64_t>(rows)};
   cuuint64_t gstride[1] = {static_cast<cuuint64_t>(kp) * 4};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
@@ -709,8 +768,9 @@ size_t gemm_scratch_floats(long long M, long long N, long long K) {
 
 size_t panel_floats(long long rows, long long k) { return static_cast<size_t>(2 * rows * round_up(k, BK)); }
 
-Panels panels_at(float *mem, long long rows, long long k) {
+Panels panels_at(float *mem, long long rows, long long k, int role) {
   Panels p;
+  p.role = role;
   p.rows = rows;
   p.k = k;
   p.kp = round_up(k, BK);
@@ -722,24 +782,27 @@ Panels panels_at(float *mem, long long rows, long long k) {
 // Writes `op` (rows x k) into the region of `dst` that starts at (row_offset, k_offset): several sources can be
 // fused into one panel set (the four LSTM gate matrices side by side, for instance).
 int gemm_prepare_into(Context &ctx, const Operand &op, const Panels &dst, long long row_offset, long long k_offset) {
-  if (op.rows <= 0 || op.k <= 0 || row_offset + op.rows > dst.rows || k_offset + op.k > dst.k || (k_offset & 3) != 0) return MYEA_E_INVALID;
+  // cross groups are 8 K elements wide: a fused source must start on a group boundary (its tail is zero-filled up to the
+  // next boundary, so the following source may start there)
+  if (op.rows <= 0 || op.k <= 0 || row_offset + op.rows > dst.rows || k_offset + op.k > dst.k || (k_offset & 7) != 0) return MYEA_E_INVALID;
   float *hi = dst.hi + row_offset * dst.kp + k_offset, *lo = dst.lo + row_offset * dst.kp + k_offset;
+  const int raw = ctx.gemm_engine == 1 ? 1 : 0;
   ctx.begin(TC_SPLIT);
   if (op.stride_k == 1) {
-    const long long total = op.rows * ((op.k + 3) >> 2);
+    const long long total = op.rows * ((op.k + 7) >> 3);
     int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
     if (blocks < 1) blocks = 1;
-    split_rows_kernel<<<blocks, 256, 0, ctx.stream>>>(op.ptr, op.stride_r, op.rows, op.k, dst.kp, hi, lo);
+    split_rows_kernel<<<blocks, 256, 0, ctx.stream>>>(op.ptr, op.stride_r, op.rows, op.k, dst.kp, hi, lo, dst.role, raw);
   } else {
     dim3 grid(static_cast<unsigned>((op.rows + 31) / 32), static_cast<unsigned>((op.k + 31) / 32));
-    split_transpose_kernel<<<grid, dim3(32, 8), 0, ctx.stream>>>(op.ptr, op.stride_k, op.rows, op.k, dst.kp, hi, lo);
+    split_transpose_kernel<<<grid, dim3(32, 8), 0, ctx.stream>>>(op.ptr, op.stride_k, op.rows, op.k, dst.kp, hi, lo, dst.role, raw);
   }
   ctx.end(TC_SPLIT);
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
-int gemm_prepare(Context &ctx, const Operand &op, float *mem, Panels *out) {
-  *out = panels_at(mem, op.rows, op.k);
+int gemm_prepare(Context &ctx, const Operand &op, float *mem, Panels *out, int role) {
+  *out = panels_at(mem, op.rows, op.k, role);
   return gemm_prepare_into(ctx, op, *out, 0, 0);
 }
 
@@ -789,6 +852,7 @@ static int launch_tcgen05_pair(Context &ctx, const CUtensorMap maps[4], const Ge
 int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, const Panels &B, long long b_row0, long long N,
                 const Epilogue &epi) {
   if (A.k != B.k || M <= 0 || N <= 0 || A.k <= 0 || a_row0 < 0 || b_row0 < 0 || a_row0 + M > A.rows || b_row0 + N > B.rows) return MYEA_E_INVALID;
+  if (A.role != PANEL_ROLE_A || B.role != PANEL_ROLE_B) return MYEA_E_INVALID;  // the cross panels of the two sides differ
   GemmDims dims{static_cast<int>(M), static_cast<int>(N), static_cast<int>(A.k)};
   int rc;
   if (ctx.gemm_engine == 1) {
@@ -832,8 +896,8 @@ int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &ep
   if (scratch.base == nullptr || scratch.floats < gemm_scratch_floats(A.rows, B.rows, A.k)) return MYEA_E_INVALID;
   float *base = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(scratch.base) + 255) & ~static_cast<uintptr_t>(255));
   Panels pa, pb;
-  int rc = gemm_prepare(ctx, A, base, &pa);
-  if (rc == MYEA_OK) rc = gemm_prepare(ctx, B, base + panel_floats(A.rows, A.k), &pb);
+  int rc = gemm_prepare(ctx, A, base, &pa, PANEL_ROLE_A);
+  if (rc == MYEA_OK) rc = gemm_prepare(ctx, B, base + panel_floats(A.rows, A.k), &pb, PANEL_ROLE_B);
   if (rc != MYEA_OK) return rc;
   return gemm_panels(ctx, pa, 0, A.rows, pb, 0, B.rows, epi);
 }

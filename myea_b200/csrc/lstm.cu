@@ -272,14 +272,15 @@ int lstm_create(myea_b200_net *net, LayerPlan &L) {
   L.errors = L.deriv;
   LRC(lalloc(net, &P->s_rec, net->B * 4 * C));
   P->off_wrec = 0;
+  const long long Cp = (C + 7) & ~7ll;
   P->off_wrect = P->off_wrec + panel_floats(4 * C, C) + 64;
-  P->off_step = P->off_wrect + panel_floats(C, 4 * C) + 64;
-  LRC(lalloc(net, &P->panel_mem, P->off_step + panel_floats(net->B, 4 * C) + 64));
+  P->off_step = P->off_wrect + panel_floats(C, 4 * Cp) + 64;
+  LRC(lalloc(net, &P->panel_mem, P->off_step + panel_floats(net->B, 4 * Cp) + 64));
   LRC(lalloc(net, &P->partial, static_cast<size_t>(7) * net->reduce_chunks * C));
   // one-shot contractions use the handle's scratch: make sure it is large enough
   size_t need = 0;
   need = std::max(need, panel_floats(rows, L.n_in) + panel_floats(4 * C, L.n_in));            // input projection
-  need = std::max(need, panel_floats(rows, 4 * C) + panel_floats(L.n_in, 4 * C));            // error to the previous layer
+  need = std::max(need, panel_floats(rows, 4 * Cp) + panel_floats(L.n_in, 4 * Cp));          // error to the previous layer
   need = std::max(need, panel_floats(4 * C, rows) + panel_floats(std::max(L.n_in, C), rows));  // weight derivatives
   net->scratch.floats = std::max(net->scratch.floats, need + 256);
   return MYEA_OK;
@@ -311,6 +312,17 @@ static float *aligned_scratch(myea_b200_net *net) {
   return reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(net->scratch.base) + 255) & ~static_cast<uintptr_t>(255));
 }
 
+// [rows, 4C] gate matrix -> panel [rows, K = 4*Cp]: gate g occupies K columns [g*Cp, g*Cp + C); one pass when C is a
+// multiple of 8, else one pass per gate (the panel builder zero-fills each gate's tail up to its group boundary)
+static int prepare_gates(Context &ctx, const float *gates, long long rows, long long C, long long Cp, const Panels &dst) {
+  if (Cp == C) return gemm_prepare_into(ctx, Operand{gates, rows, 4 * C, 4 * C, 1}, dst, 0, 0);
+  for (int g = 0; g < 4; ++g) {
+    int rc = gemm_prepare_into(ctx, Operand{gates + g * C, rows, C, 4 * C, 1}, dst, 0, g * Cp);
+    if (rc != MYEA_OK) return rc;
+  }
+  return MYEA_OK;
+}
+
 static int cell_blocks(long long total) { return static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, 148 * 8))); }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -323,12 +335,12 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
   const BlockOffsets off = block_offsets(n_in, C);
   float *scratch = aligned_scratch(net);
   Panels px;
-  LRC(gemm_prepare(ctx, Operand{input, rows, n_in, n_in, 1}, scratch, &px));
+  LRC(gemm_prepare(ctx, Operand{input, rows, n_in, n_in, 1}, scratch, &px, PANEL_ROLE_A));
   for (int d = 0; d < P->dirs; ++d) {
     LstmDir &D = P->d[d];
     const float *w = net->params + D.w_base;
     // fused input panel [4C, in], gate order z, i, f, o
-    Panels pwin = panels_at(scratch + panel_floats(rows, n_in), 4 * C, n_in);
+    Panels pwin = panels_at(scratch + panel_floats(rows, n_in), 4 * C, n_in, PANEL_ROLE_B);
     LRC(gemm_prepare_into(ctx, Operand{w + off.z_in, C, n_in, P->stride, 1}, pwin, 0, 0));
     for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.in[g], C, n_in, P->stride, 1}, pwin, (g + 1) * C, 0));
     Epilogue e;
@@ -337,7 +349,7 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
     e.bias = net->params + D.b_base;
     LRC(gemm_panels(ctx, px, 0, rows, pwin, 0, 4 * C, e));
     // fused recurrent panel [4C, C]
-    Panels pwrec = panels_at(P->panel_mem + P->off_wrec, 4 * C, C);
+    Panels pwrec = panels_at(P->panel_mem + P->off_wrec, 4 * C, C, PANEL_ROLE_B);
     LRC(gemm_prepare_into(ctx, Operand{w + off.z_rec, C, C, P->stride, 1}, pwrec, 0, 0));
     for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.rec[g], C, C, P->stride, 1}, pwrec, (g + 1) * C, 0));
     const bool zone = P->zoneout && net->training;
@@ -351,7 +363,7 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
       if (s > 0) {
         const float *h_prev = L.values + tp * B * ldh + d * C;
         Panels ph;
-        LRC(gemm_prepare(ctx, Operand{h_prev, B, C, ldh, 1}, P->panel_mem + P->off_step, &ph));
+        LRC(gemm_prepare(ctx, Operand{h_prev, B, C, ldh, 1}, P->panel_mem + P->off_step, &ph, PANEL_ROLE_A));
         Epilogue er;
         er.C = P->s_rec;
         er.ldc = 4 * C;
@@ -385,22 +397,23 @@ int lstm_backward(myea_b200_net *net, LayerPlan &L) {
   LstmPlan *P = L.lstm;
   Context &ctx = net->ctx;
   const long long T = net->T, B = net->B, C = P->C, ldh = L.n_out, n_in = P->n_in;
+  const long long Cp = (C + 7) & ~7ll;  // each gate's K segment starts on a group-of-8 boundary
   const BlockOffsets off = block_offsets(n_in, C);
   for (int d = 0; d < P->dirs; ++d) {
     LstmDir &D = P->d[d];
     const float *w = net->params + D.w_base;
     // transposed recurrent panel [C (unit j of h), K = 4C (gate, cell)]
-    Panels pwt = panels_at(P->panel_mem + P->off_wrect, C, 4 * C);
+    Panels pwt = panels_at(P->panel_mem + P->off_wrect, C, 4 * Cp, PANEL_ROLE_B);
     LRC(gemm_prepare_into(ctx, Operand{w + off.z_rec, C, C, 1, P->stride}, pwt, 0, 0));
-    for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.rec[g], C, C, 1, P->stride}, pwt, 0, (g + 1) * C));
+    for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.rec[g], C, C, 1, P->stride}, pwt, 0, (g + 1) * Cp));
     for (long long s = 0; s < T; ++s) {
       const long long t = d == 0 ? T - 1 - s : s;      // walk against the layer's direction
       const long long tn = d == 0 ? t + 1 : t - 1;     // the step after t in the layer's direction
       const long long tp = d == 0 ? t - 1 : t + 1;     // the step before t
       float *dh_t = L.deriv + t * B * ldh + d * C;
       if (s > 0) {
-        Panels pd;
-        LRC(gemm_prepare(ctx, Operand{D.dgates + tn * B * 4 * C, B, 4 * C, 4 * C, 1}, P->panel_mem + P->off_step, &pd));
+        Panels pd = panels_at(P->panel_mem + P->off_step, B, 4 * Cp, PANEL_ROLE_A);
+        LRC(prepare_gates(ctx, D.dgates + tn * B * 4 * C, B, C, Cp, pd));
         Epilogue e;
         e.C = dh_t;
         e.ldc = ldh;
@@ -436,16 +449,17 @@ int lstm_backward_to_input(myea_b200_net *net, LayerPlan &L, float *prev_deriv, 
   Context &ctx = net->ctx;
   const long long rows = net->T * net->B, C = P->C, n_in = P->n_in;
   if (prev.n_out != n_in) return MYEA_E_INVALID;
+  const long long Cp = (C + 7) & ~7ll;
   const BlockOffsets off = block_offsets(n_in, C);
   float *scratch = aligned_scratch(net);
   for (int d = 0; d < P->dirs; ++d) {
     LstmDir &D = P->d[d];
     const float *w = net->params + D.w_base;
-    Panels pd;
-    LRC(gemm_prepare(ctx, Operand{D.dgates, rows, 4 * C, 4 * C, 1}, scratch, &pd));
-    Panels pwt = panels_at(scratch + panel_floats(rows, 4 * C), n_in, 4 * C);  // [n_in, K = 4C]
+    Panels pd = panels_at(scratch, rows, 4 * Cp, PANEL_ROLE_A);
+    LRC(prepare_gates(ctx, D.dgates, rows, C, Cp, pd));
+    Panels pwt = panels_at(scratch + panel_floats(rows, 4 * Cp), n_in, 4 * Cp, PANEL_ROLE_B);  // [n_in, K = 4 gates]
     LRC(gemm_prepare_into(ctx, Operand{w + off.z_in, n_in, C, 1, P->stride}, pwt, 0, 0));
-    for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.in[g], n_in, C, 1, P->stride}, pwt, 0, (g + 1) * C));
+    for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.in[g], n_in, C, 1, P->stride}, pwt, 0, (g + 1) * Cp));
     Epilogue e;
     e.C = prev_deriv;
     e.ldc = n_in;
@@ -469,8 +483,8 @@ int lstm_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float 
     float *gw = net->grads + D.w_base;
     // input weights: K = all T*B rows
     Panels pdt, pxt;
-    LRC(gemm_prepare(ctx, Operand{D.dgates, 4 * C, rows, 1, 4 * C}, scratch, &pdt));                        // dgates^T [4C, rows]
-    LRC(gemm_prepare(ctx, Operand{input, n_in, rows, 1, n_in}, scratch + panel_floats(4 * C, rows), &pxt));  // x^T [n_in, rows]
+    LRC(gemm_prepare(ctx, Operand{D.dgates, 4 * C, rows, 1, 4 * C}, scratch, &pdt, PANEL_ROLE_A));                        // dgates^T [4C, rows]
+    LRC(gemm_prepare(ctx, Operand{input, n_in, rows, 1, n_in}, scratch + panel_floats(4 * C, rows), &pxt, PANEL_ROLE_B));  // x^T [n_in, rows]
     const long long in_off[4] = {off.z_in, off.in[0], off.in[1], off.in[2]};
     for (int g = 0; g < 4; ++g) {
       Epilogue e;
@@ -485,8 +499,8 @@ int lstm_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float 
       const float *dg0 = d == 0 ? D.dgates + B * 4 * C : D.dgates;              // rows of steps 1..T-1 (forward) / 0..T-2 (backward)
       const float *h0 = d == 0 ? L.values + d * C : L.values + B * ldh + d * C;  // rows of steps 0..T-2 (forward) / 1..T-1 (backward)
       Panels pdr, pht;
-      LRC(gemm_prepare(ctx, Operand{dg0, 4 * C, K, 1, 4 * C}, scratch, &pdr));
-      LRC(gemm_prepare(ctx, Operand{h0, C, K, 1, ldh}, scratch + panel_floats(4 * C, K), &pht));
+      LRC(gemm_prepare(ctx, Operand{dg0, 4 * C, K, 1, 4 * C}, scratch, &pdr, PANEL_ROLE_A));
+      LRC(gemm_prepare(ctx, Operand{h0, C, K, 1, ldh}, scratch + panel_floats(4 * C, K), &pht, PANEL_ROLE_B));
       const long long rec_off[4] = {off.z_rec, off.rec[0], off.rec[1], off.rec[2]};
       for (int g = 0; g < 4; ++g) {
         Epilogue e;
