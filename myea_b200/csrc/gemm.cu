@@ -187,7 +187,47 @@ __device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, 
       : "memory");
 }
 
+// arrive on the mbarrier at the same shared-memory offset in CTA `cta` of the cluster
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t *bar, uint32_t cta) {
+  asm volatile(
+      "{\n"
+      ".reg .b32 ra;\n"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n"
+      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n"
+      "}\n" ::"r"(smem_u32(bar)),
+      "r"(cta)
+      : "memory");
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
+
+// Bounded wait that gives up at once when another wait of this CTA has already failed (keeps the worst case short).
+__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+  if (*abort_flag) return false;
+  if (mbar_wait(bar, parity)) return true;
+  *abort_flag = 1;
+  return false;
+}
+
 }  // namespace ptx
+
+// Optional phase timeline of CTA (0,0) (a profiling build only: -DMYEA_GEMM_TIMELINE); compiles to nothing otherwise.
+#ifdef MYEA_GEMM_TIMELINE
+__device__ long long g_timeline[32];
+#define TL_ON (blockIdx.x == 0 && blockIdx.y == 0)
+#define TL(slot) do { if (TL_ON) g_timeline[slot] = clock64(); } while (0)
+#define TL_DECL(name) long long name = 0
+#define TL_BEGIN(name) const long long name##_t0 = clock64()
+#define TL_END(name) name += clock64() - name##_t0
+#define TL_STORE(slot, name) do { if (TL_ON) g_timeline[slot] = name; } while (0)
+#define TL_GLOBAL(slot) do { if (TL_ON) { unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt)); g_timeline[slot] = (long long)gt; } } while (0)
+#else
+#define TL(slot)
+#define TL_DECL(name)
+#define TL_BEGIN(name)
+#define TL_END(name)
+#define TL_STORE(slot, name)
+#define TL_GLOBAL(slot)
+#endif
 
 // ---------------------------------------------------------------------------------------------------------
 // Descriptors
@@ -244,39 +284,88 @@ __device__ __forceinline__ float epilogue_value(const Epilogue &e, float acc, lo
 }
 
 
-// Epilogue of one 32-row x 32-column chunk held transposed in shared memory (tr[row][column], pitch 33): lane = column.
-// All global reads of a half-chunk (16 rows x up to 4 arrays) are issued before the first dependent use, so their
-// latencies overlap instead of adding up row after row.
-__device__ __forceinline__ void epilogue_chunk(const Epilogue &e, const float *tr, int lane, long long row_base, long long n, int rows_valid,
-                                               bool col_valid) {
-  if (!col_valid || rows_valid <= 0) return;
-  const float bias = e.bias != nullptr ? e.bias[n] : 0.f;
-  const bool deriv = e.deriv_af != 0u;
-  const bool affine = deriv && e.aux_pre != nullptr && e.col_scale != nullptr;
-  const float cs = affine ? e.col_scale[n] : 1.f, ch = affine ? e.col_shift[n] : 0.f;
-  const float *__restrict__ p_add = e.addend, *__restrict__ p_pre = deriv ? e.aux_pre : nullptr, *__restrict__ p_y = deriv ? e.aux_y : nullptr;
-  float *__restrict__ C = e.C;
+__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+
+// The vector path of the epilogue needs 16-byte aligned bases and pitches that are multiples of four floats.
+__device__ __forceinline__ bool epilogue_vector_ok(const Epilogue &e) {
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(e.C) | reinterpret_cast<uintptr_t>(e.bias) | reinterpret_cast<uintptr_t>(e.addend) |
+                         reinterpret_cast<uintptr_t>(e.aux_pre) | reinterpret_cast<uintptr_t>(e.aux_y) |
+                         reinterpret_cast<uintptr_t>(e.col_scale) | reinterpret_cast<uintptr_t>(e.col_shift);
+  return (bits & 15) == 0 && ((e.ldc | e.ld_addend | e.ld_aux) & 3) == 0;
+}
+// 0 plain (bias only), 1 activation derivative, 2 accumulate, 3 anything else
+__device__ __forceinline__ int epilogue_mode(const Epilogue &e) {
+  if (e.addend != nullptr) return 3;
+  if (e.deriv_af != 0u) return e.accumulate ? 3 : 1;
+  return e.accumulate ? 2 : 0;
+}
+
+// Epilogue of output row m, columns [col0, col0 + 32), the accumulator values in v: the thread owns the row (that is how
+// tensor memory hands an accumulator to a warp: lane = row), so every access is a float4 of this row.  The loads of four
+// float4 columns are issued before their first use.  ADD / DERIV / ACC say what MAY be present.
+template <bool ADD, bool DERIV, bool ACC>
+__device__ __forceinline__ void epilogue_row32_vec(const Epilogue &e, const float (&v)[32], long long m, long long col0) {
+  float *__restrict__ c = e.C + m * e.ldc + col0;
+  const float *__restrict__ p_add = (ADD && e.addend != nullptr) ? e.addend + m * e.ld_addend + col0 : nullptr;
+  const float *__restrict__ p_pre = (DERIV && e.aux_pre != nullptr) ? e.aux_pre + m * e.ld_aux + col0 : nullptr;
+  const float *__restrict__ p_y = (DERIV && e.aux_y != nullptr) ? e.aux_y + m * e.ld_aux + col0 : nullptr;
+  const bool affine = DERIV && p_pre != nullptr && e.col_scale != nullptr;
+  const bool acc = ACC && e.accumulate;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    float add[16], pre[16], y[16], old[16];
+  for (int g = 0; g < 2; ++g) {
+    float4 add[4], pre[4], y[4], old[4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int rr = half * 16 + i;
-      const long long m = row_base + rr;
-      const bool in = rr < rows_valid;
-      add[i] = (p_add != nullptr && in) ? p_add[m * e.ld_addend + n] : 0.f;
-      pre[i] = (p_pre != nullptr && in) ? p_pre[m * e.ld_aux + n] : 0.f;
-      y[i] = (p_y != nullptr && in) ? p_y[m * e.ld_aux + n] : 0.f;
-      old[i] = (e.accumulate && in) ? C[m * e.ldc + n] : 0.f;
+    for (int i = 0; i < 4; ++i) {
+      const int j = (g * 4 + i) * 4;
+      if (ADD) add[i] = p_add != nullptr ? ld4(p_add + j) : zero;
+      if (DERIV) {
+        pre[i] = p_pre != nullptr ? ld4(p_pre + j) : zero;
+        y[i] = p_y != nullptr ? ld4(p_y + j) : zero;
+      }
+      if (ACC) old[i] = acc ? ld4(c + j) : zero;
     }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int rr = half * 16 + i;
-      if (rr < rows_valid) {
-        float v = tr[rr * 33 + lane] + bias + add[i];
-        if (deriv) v *= af_derive(e.deriv_af, pre[i] * cs + ch, y[i]);
-        C[(row_base + rr) * e.ldc + n] = v + old[i];
+    for (int i = 0; i < 4; ++i) {
+      const int j = (g * 4 + i) * 4;
+      float4 x = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      if (e.bias != nullptr) {
+        const float4 b = ld4(e.bias + col0 + j);
+        x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
       }
+      if (ADD) { x.x += add[i].x; x.y += add[i].y; x.z += add[i].z; x.w += add[i].w; }
+      if (DERIV) {
+        float4 z = pre[i];
+        if (affine) {
+          const float4 cs = ld4(e.col_scale + col0 + j), ch = ld4(e.col_shift + col0 + j);
+          z.x = z.x * cs.x + ch.x; z.y = z.y * cs.y + ch.y; z.z = z.z * cs.z + ch.z; z.w = z.w * cs.w + ch.w;
+        }
+        x.x *= af_derive(e.deriv_af, z.x, y[i].x);
+        x.y *= af_derive(e.deriv_af, z.y, y[i].y);
+        x.z *= af_derive(e.deriv_af, z.z, y[i].z);
+        x.w *= af_derive(e.deriv_af, z.w, y[i].w);
+      }
+      if (ACC) { x.x += old[i].x; x.y += old[i].y; x.z += old[i].z; x.w += old[i].w; }
+      *reinterpret_cast<float4 *>(c + j) = x;
+    }
+  }
+}
+
+__device__ __forceinline__ void epilogue_row32(const Epilogue &e, const float (&v)[32], long long m, long long col0, int M, int N,
+                                               bool vec_ok, int mode) {
+  if (m >= M || col0 >= N) return;
+  if (vec_ok && col0 + 32 <= N) {
+    switch (mode) {
+      case 0: epilogue_row32_vec<false, false, false>(e, v, m, col0); break;
+      case 1: epilogue_row32_vec<false, true, false>(e, v, m, col0); break;
+      case 2: epilogue_row32_vec<false, false, true>(e, v, m, col0); break;
+      default: epilogue_row32_vec<true, true, true>(e, v, m, col0); break;
+    }
+  } else {  // ragged right edge or unaligned arrays: one element at a time
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const long long n = col0 + j;
+      if (n < N) e.C[m * e.ldc + n] = epilogue_value(e, v[j], m, n);
     }
   }
 }
@@ -317,6 +406,7 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
   const int m0 = blockIdx.y * BM;
   const int n0 = blockIdx.x * BN;
   const int num_kb = (dims.K + BK - 1) / BK;
+  if (threadIdx.x == 0) { TL(0); TL_GLOBAL(16); }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -335,15 +425,19 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  if (threadIdx.x == 0) TL(1);
 
   bool ok = true;
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
+      TL_DECL(w_empty);
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = static_cast<uint32_t>(kb / STAGES) & 1u;
+        TL_BEGIN(w_empty);
         if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u)) { ok = false; break; }
+        TL_END(w_empty);
         uint8_t *st = smem + s * S::STAGE_BYTES;
         ptx::mbar_arrive_expect_tx(&full_bar[s], S::STAGE_BYTES);
         ptx::tma_load_2d(st, &tm_a_hi, &full_bar[s], kb * BK, m0);
@@ -351,16 +445,21 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
         ptx::tma_load_2d(st + 2 * S::A_BYTES, &tm_b_hi, &full_bar[s], kb * BK, n0);
         ptx::tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tm_b_lo, &full_bar[s], kb * BK, n0);
       }
+      TL_STORE(5, w_empty);
       if (!ok) atomicCAS(error_flag, 0, 101);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_tf32(BM, BN);
+      TL_DECL(w_full);
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = static_cast<uint32_t>(kb / STAGES) & 1u;
+        TL_BEGIN(w_full);
         if (!ptx::mbar_wait(&full_bar[s], ph)) { ok = false; break; }
+        TL_END(w_full);
+        if (kb == 0) TL(2);
         ptx::tc_fence_after();
         const uint32_t st = ptx::smem_u32(smem + s * S::STAGE_BYTES);
         const uint64_t a_hi = make_smem_desc(st);
@@ -380,6 +479,8 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
         ptx::tc_commit(&empty_bar[s]);  // the stage may be refilled once these MMAs have read it
       }
       ptx::tc_commit(tmem_full_bar);  // accumulator complete
+      TL(3);
+      TL_STORE(4, w_full);
       if (!ok) atomicCAS(error_flag, 0, 102);
     }
   } else {
@@ -390,15 +491,20 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
       if (lane == 0) atomicCAS(error_flag, 0, 103);
     }
     ptx::tc_fence_after();
+    if (warp == 2 && lane == 0) TL(6);
     if (ok && num_kb > 0) {
-      // all MMAs are complete, so the pipeline stages are free: use them as the transposition buffer
-      float *tr = reinterpret_cast<float *>(smem) + (warp - 2) * (32 * 33);
       const long long row_base = static_cast<long long>(m0) + q * 32;
+      const bool vec_ok = epilogue_vector_ok(epi);
+      const int mode = epilogue_mode(epi);
+      TL_DECL(t_ld);
+      TL_DECL(t_tr);
+      TL_DECL(t_out);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= dims.N) break;
         uint32_t r[32];
         float sum[32];
+        TL_BEGIN(t_ld);
         const uint32_t t_chunk = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c);
         ptx::tmem_ld_32x32(t_chunk + static_cast<uint32_t>(N_MAIN * BN), r);  // cross terms first
         ptx::tmem_ld_wait();
@@ -411,15 +517,16 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
 #pragma unroll
           for (int j = 0; j < 32; ++j) sum[j] += __uint_as_float(r[j]);
         }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) tr[lane * 33 + j] = sum[j];
-        __syncwarp();
-        const long long n = static_cast<long long>(n0) + c + lane;
-        const long long left = static_cast<long long>(dims.M) - row_base;
-        epilogue_chunk(epi, tr, lane, row_base, n, left > 32 ? 32 : static_cast<int>(left), n < dims.N);
-        __syncwarp();
+        TL_END(t_ld);
+        TL_BEGIN(t_tr);
+        TL_END(t_tr);
+        TL_BEGIN(t_out);
+        epilogue_row32(epi, sum, row_base + lane, static_cast<long long>(n0) + c, dims.M, dims.N, vec_ok, mode);
+        TL_END(t_out);
       }
+      if (warp == 2 && lane == 0) { TL_STORE(11, t_ld); TL_STORE(12, t_tr); TL_STORE(13, t_out); }
     }
+    if (warp == 2 && lane == 0) TL(7);
   }
 
   // drain: the producer makes sure none of its copies is still in flight before the CTA's shared memory goes away
@@ -433,6 +540,7 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) { TL(8); TL_GLOBAL(17); }
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
@@ -551,8 +659,9 @@ gemm3x_tf32_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
     }
     ptx::tc_fence_after();
     if (ok && num_kb > 0) {
-      float *tr = reinterpret_cast<float *>(smem) + (warp - 2) * (32 * 33);
       const long long row_base = static_cast<long long>(m0) + q * 32;
+      const bool vec_ok = epilogue_vector_ok(epi);
+      const int mode = epilogue_mode(epi);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= dims.N) break;
@@ -570,13 +679,7 @@ gemm3x_tf32_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
 #pragma unroll
           for (int j = 0; j < 32; ++j) sum[j] += __uint_as_float(r[j]);
         }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) tr[lane * 33 + j] = sum[j];
-        __syncwarp();
-        const long long n = static_cast<long long>(n0) + c + lane;
-        const long long left = static_cast<long long>(dims.M) - row_base;
-        epilogue_chunk(epi, tr, lane, row_base, n, left > 32 ? 32 : static_cast<int>(left), n < dims.N);
-        __syncwarp();
+        epilogue_row32(epi, sum, row_base + lane, static_cast<long long>(n0) + c, dims.M, dims.N, vec_ok, mode);
       }
     }
   }
@@ -593,6 +696,236 @@ gemm3x_tf32_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
 
 // ---------------------------------------------------------------------------------------------------------
 // Operand preparation: fp32 matrix (either stride order) -> K-major hi / lo panels [rows][kp]
+// ---------------------------------------------------------------------------------------------------------
+// Wide CTA-pair variant, persistent: two SMs compute 256 x 256 output tiles (each CTA 128 rows x 256 columns) with
+// tcgen05.mma.cta_group::2 (M = 256, N = 256).  Per 32 floats of K each CTA stages 64 KB (its 128 rows of A and its
+// 128 rows of B, hi and cross panels; 3 stages) for 128 x 256 x 32 products: half the shared-memory and L2 traffic per
+// product of the 128 x 128 tile, every MMA instruction carries twice the work, and the main loop runs at the tensor
+// pipe's own pace (the 128 x 128 tile is held back by shared-memory reads: about 100 instead of 64 cycles per MMA).
+// Tensor memory holds two 256-column accumulators, used as a ping-pong pair: all MMAs of one K chunk
+// (WIDE_KC stages = 256 of K, 64 instructions) go into one buffer while the eight drain warps read the other into
+// fp32 registers and add it, round to nearest, to the running sum.  A chain of truncating tensor-core adds is therefore
+// never longer than 64 instructions, whatever K is (the 4-accumulator layout of the narrower kernels bounds it by K/24).
+// The grid is one cluster per SM pair; each cluster walks tiles cluster, cluster + clusters, ... and the three roles
+// (TMA producer, MMA issuer, drain warps) keep running stage / chunk counters across tiles, so the loads and MMAs of
+// the next tile start while the drain warps, which hold the finished tile in registers, run its epilogue.
+// Tiles are numbered in bands of 8 row tiles so that the tiles in flight at one time share operand panels in L2.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int WIDE_STAGES = 3;
+constexpr int WIDE_THREADS = 320;  // warp 0 TMA, warp 1 MMA + tensor-memory allocation, warps 2-9 drain / epilogue
+constexpr int WIDE_KC = 8;
+constexpr int WIDE_BAND = 8;
+struct WideSmem {
+  static constexpr int TILE_BYTES = 128 * BK * 4;           // 128 rows x 128 bytes
+  static constexpr int STAGE_BYTES = 4 * TILE_BYTES;        // A hi, A cross, B hi, B cross
+  static constexpr int BAR_OFFSET = WIDE_STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;
+};
+
+struct WideTiles {
+  int tiles_m, tiles_n, num_tiles;
+};
+
+__device__ __forceinline__ void wide_tile_coords(const WideTiles &w, int t, int &tm, int &tn) {
+  const int per_band = WIDE_BAND * w.tiles_n;
+  const int band = t / per_band;
+  const int within = t - band * per_band;
+  const int rows = min(WIDE_BAND, w.tiles_m - band * WIDE_BAND);
+  tn = within / rows;
+  tm = band * WIDE_BAND + (within - tn * rows);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(WIDE_THREADS, 1)
+gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
+                                const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
+                                const GemmDims dims, const WideTiles tiles, const Epilogue epi, int *error_flag) {
+  using S = WideSmem;
+  constexpr int STAGES = WIDE_STAGES, BN = 256, TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + S::BAR_OFFSET);
+  uint64_t *empty_bar = full_bar + STAGES;
+  uint64_t *acc_full_bar = empty_bar + STAGES;   // [2] a buffer holds a finished K chunk (multicast to both CTAs)
+  uint64_t *acc_empty_bar = acc_full_bar + 2;    // [2] leader only: every drain warp of both CTAs has read the buffer
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(acc_empty_bar + 2);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = ptx::cluster_ctarank();
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+  const int num_kb = (dims.K + BK - 1) / BK;
+  const int num_chunks = (num_kb + WIDE_KC - 1) / WIDE_KC;
+  if (threadIdx.x == 0) { TL(0); TL_GLOBAL(16); }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&acc_full_bar[b], 1);
+      ptx::mbar_init(&acc_empty_bar[b], 16);  // one arrival per drain warp of the pair
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(tmem_holder, TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  if (threadIdx.x == 0) TL(1);
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t it = 0;  // k-blocks staged so far, over all tiles
+      TL_DECL(w_empty);
+      for (int t = cluster_id; t < tiles.num_tiles && ok; t += num_clusters) {
+        int tm, tn;
+        wide_tile_coords(tiles, t, tm, tn);
+        const int m0 = tm * 256 + static_cast<int>(cta_rank) * 128;
+        const int nb0 = tn * BN + static_cast<int>(cta_rank) * 128;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = static_cast<int>(it % STAGES);
+          const uint32_t ph = (it / STAGES) & 1u;
+          TL_BEGIN(w_empty);
+          if (!ptx::mbar_wait_or_abort(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          TL_END(w_empty);
+          uint8_t *st = smem + s * S::STAGE_BYTES;
+          if (cta_rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * S::STAGE_BYTES);
+          ptx::tma_load_2d_pair(st, &tm_a_hi, &full_bar[s], kb * BK, m0);
+          ptx::tma_load_2d_pair(st + S::TILE_BYTES, &tm_a_lo, &full_bar[s], kb * BK, m0);
+          ptx::tma_load_2d_pair(st + 2 * S::TILE_BYTES, &tm_b_hi, &full_bar[s], kb * BK, nb0);
+          ptx::tma_load_2d_pair(st + 3 * S::TILE_BYTES, &tm_b_lo, &full_bar[s], kb * BK, nb0);
+        }
+      }
+      TL_STORE(5, w_empty);
+      if (!ok) atomicCAS(error_flag, 0, 301);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA) ----------------
+    if (lane == 0 && cta_rank == 0) {
+      bool ok = true;
+      constexpr uint32_t idesc_main = make_idesc_tf32(256, BN);
+      constexpr uint32_t idesc_cross = make_idesc_bf16(256, BN);
+      uint32_t it = 0;  // k-blocks consumed so far
+      uint32_t g = 0;   // K chunks issued so far: chunk g goes into buffer g & 1
+      TL_DECL(w_full);
+      TL_DECL(w_acc);
+      for (int t = cluster_id; t < tiles.num_tiles && ok; t += num_clusters) {
+        for (int c = 0; c < num_chunks && ok; ++c, ++g) {
+          const uint32_t b = g & 1u;
+          if (g >= 2) {
+            TL_BEGIN(w_acc);
+            if (!ptx::mbar_wait_or_abort(&acc_empty_bar[b], ((g >> 1) - 1u) & 1u, abort_flag)) { ok = false; break; }
+            TL_END(w_acc);
+            ptx::tc_fence_after();
+          }
+          const uint32_t acc = tmem_base + b * static_cast<uint32_t>(BN);
+          const int kb_end = min(num_kb, (c + 1) * WIDE_KC);
+          for (int kb = c * WIDE_KC; kb < kb_end; ++kb, ++it) {
+            const int s = static_cast<int>(it % STAGES);
+            const uint32_t ph = (it / STAGES) & 1u;
+            TL_BEGIN(w_full);
+            if (!ptx::mbar_wait_or_abort(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+            TL_END(w_full);
+            if (it == 0) TL(2);
+            ptx::tc_fence_after();
+            const uint32_t st = ptx::smem_u32(smem + s * S::STAGE_BYTES);
+            const uint64_t a_hi = make_smem_desc(st), a_x = make_smem_desc(st + S::TILE_BYTES);
+            const uint64_t b_hi = make_smem_desc(st + 2 * S::TILE_BYTES), b_x = make_smem_desc(st + 3 * S::TILE_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t koff = static_cast<uint64_t>((k * UMMA_K * 4) >> 4);
+              const bool first = (kb == c * WIDE_KC) && (k == 0);
+              ptx::mma_bf16_pair(acc, a_x + koff, b_x + koff, idesc_cross, first ? 0u : 1u);  // lo*hi + hi*lo
+              ptx::mma_tf32_pair(acc, a_hi + koff, b_hi + koff, idesc_main, 1u);             // hi*hi
+            }
+            ptx::tc_commit_pair(&empty_bar[s]);
+          }
+          if (ok) ptx::tc_commit_pair(&acc_full_bar[b]);
+        }
+        if (t == cluster_id) TL(3);
+      }
+      TL_STORE(4, w_full);
+      TL_STORE(9, w_acc);
+      if (!ok) atomicCAS(error_flag, 0, 302);
+    }
+  } else {
+    // ---------------- drain + epilogue: 8 warps; lane quarter = warp % 4, column half = (warp - 2) / 4 ----------------
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const bool vec_ok = epilogue_vector_ok(epi);
+    const int mode = epilogue_mode(epi);
+    bool ok = true;
+    uint32_t g = 0;
+    TL_DECL(w_accfull);
+    for (int t = cluster_id; t < tiles.num_tiles && ok; t += num_clusters) {
+      float sum[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) sum[j] = 0.f;
+      for (int c = 0; c < num_chunks; ++c, ++g) {
+        const uint32_t b = g & 1u;
+        TL_BEGIN(w_accfull);
+        if (!ptx::mbar_wait_or_abort(&acc_full_bar[b], (g >> 1) & 1u, abort_flag)) {
+          ok = false;
+          if (lane == 0) atomicCAS(error_flag, 0, 303);
+          break;
+        }
+        TL_END(w_accfull);
+        ptx::tc_fence_after();
+        const uint32_t tsrc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * static_cast<uint32_t>(BN) + static_cast<uint32_t>(half * 128);
+#pragma unroll
+        for (int jc = 0; jc < 4; ++jc) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(tsrc + static_cast<uint32_t>(jc * 32), r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[jc * 32 + j] += __uint_as_float(r[j]);
+        }
+        // this warp's reads of the buffer are complete: hand it back to the MMA issuer
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(&acc_empty_bar[b], 0);
+      }
+      if (t == cluster_id && warp == 2 && lane == 0) { TL(6); TL_STORE(10, w_accfull); }
+      if (ok && num_kb > 0) {
+        int tm, tn;
+        wide_tile_coords(tiles, t, tm, tn);
+        const long long m = static_cast<long long>(tm) * 256 + static_cast<long long>(cta_rank) * 128 + q * 32 + lane;
+        const long long col_base = static_cast<long long>(tn) * BN + half * 128;
+#pragma unroll
+        for (int jc = 0; jc < 4; ++jc) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = sum[jc * 32 + j];
+          epilogue_row32(epi, v, m, col_base + jc * 32, dims.M, dims.N, vec_ok, mode);
+        }
+      }
+      if (t == cluster_id && warp == 2 && lane == 0) TL(7);
+    }
+  }
+  // every role leaves its loop only when all tiles are done or a wait has given up; the pair stays together until both
+  // CTAs are here, so nobody signals a barrier of a CTA that has exited
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();
+  if (threadIdx.x == 0) { TL(8); TL_GLOBAL(17); }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Operand panels.  x = hi + lo with hi = x rounded to TF32 (round to nearest: truncation would bias every product the
 // same way) and lo = x - hi (exact in fp32, at most 2^-11 |x|).  A product a*b is evaluated as
@@ -848,6 +1181,37 @@ static int launch_tcgen05_pair(Context &ctx, const CUtensorMap maps[4], const Ge
   return err == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
+static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const GemmDims &dims, const Epilogue &epi) {
+  static int clusters[16] = {};  // clusters of two CTAs that can be resident at once, per device
+  const int dev = ctx.device & 15;
+  if (clusters[dev] == 0) {
+    if (cudaFuncSetAttribute(gemm3x_tf32_tcgen05_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WideSmem::TOTAL) != cudaSuccess) return MYEA_E_CUDA;
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device) != cudaSuccess || sms < 2) return MYEA_E_CUDA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1));
+    cfg.blockDim = dim3(WIDE_THREADS);
+    cfg.dynamicSmemBytes = WideSmem::TOTAL;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm3x_tf32_tcgen05_wide_kernel, &cfg) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = sms / 2;
+    }
+    clusters[dev] = n < sms / 2 ? n : sms / 2;
+    if (getenv("MYEA_B200_DEBUG") != nullptr) fprintf(stderr, "wide kernel: %d resident clusters on %d SMs\n", clusters[dev], sms);
+  }
+  WideTiles tiles;
+  tiles.tiles_m = (dims.M + 255) / 256;
+  tiles.tiles_n = (dims.N + 255) / 256;
+  tiles.num_tiles = tiles.tiles_m * tiles.tiles_n;
+  const int grid_clusters = tiles.num_tiles < clusters[dev] ? tiles.num_tiles : clusters[dev];
+  gemm3x_tf32_tcgen05_wide_kernel<<<dim3(static_cast<unsigned>(2 * grid_clusters)), WIDE_THREADS, WideSmem::TOTAL, ctx.stream>>>(
+      maps[0], maps[1], maps[2], maps[3], dims, tiles, epi, ctx.d_error_flag);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess && getenv("MYEA_B200_DEBUG") != nullptr) fprintf(stderr, "wide kernel launch: %s\n", cudaGetErrorString(err));
+  return err == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
 // C (+)= A * B^T on operands whose panels are already in place; (row0, rows) select a row range of each panel set.
 int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, const Panels &B, long long b_row0, long long N,
                 const Epilogue &epi) {
@@ -866,15 +1230,18 @@ int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, co
   } else {
     // tile shape: CTA pairs (256 x 128 per pair) unless forced to a single-CTA shape (gemm_bn 128 / 256) or there is
     // only one row tile; 128-column accumulators (four of them) are the accurate configuration
-    const bool pair = ctx.gemm_bn == 0 ? (M > 128) : (ctx.gemm_bn == 2);
+    // gemm_bn: 0 = heuristic, 3 = wide CTA pair (256 x 256), 2 = CTA pair (256 x 128), 128 / 256 = single CTA
+    const bool wide = ctx.gemm_bn == 0 ? (M > 128 && N > 128) : (ctx.gemm_bn == 3);
+    const bool pair = !wide && (ctx.gemm_bn == 0 ? (M > 128) : (ctx.gemm_bn == 2));
     const int bn = ctx.gemm_bn == 256 ? 256 : 128;
+    const int b_box = wide ? 128 : (pair ? 64 : bn);
     CUtensorMap maps[4];
     const bool ok = make_panel_map(&maps[0], A.hi + a_row0 * A.kp, M, A.k, A.kp, BM) && make_panel_map(&maps[1], A.lo + a_row0 * A.kp, M, A.k, A.kp, BM) &&
-                    make_panel_map(&maps[2], B.hi + b_row0 * B.kp, N, B.k, B.kp, pair ? 64 : bn) &&
-                    make_panel_map(&maps[3], B.lo + b_row0 * B.kp, N, B.k, B.kp, pair ? 64 : bn);
+                    make_panel_map(&maps[2], B.hi + b_row0 * B.kp, N, B.k, B.kp, b_box) && make_panel_map(&maps[3], B.lo + b_row0 * B.kp, N, B.k, B.kp, b_box);
     if (!ok) return MYEA_E_CUDA;
     ctx.begin(TC_GEMM);
-    if (pair) rc = launch_tcgen05_pair(ctx, maps, dims, epi);
+    if (wide) rc = launch_tcgen05_wide(ctx, maps, dims, epi);
+    else if (pair) rc = launch_tcgen05_pair(ctx, maps, dims, epi);
     else rc = (bn == 256) ? launch_tcgen05<256, 2>(ctx, maps, dims, epi) : launch_tcgen05<128, 3>(ctx, maps, dims, epi);
     ctx.end(TC_GEMM);
   }
@@ -903,3 +1270,9 @@ int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &ep
 }
 
 }  // namespace myea
+
+#ifdef MYEA_GEMM_TIMELINE
+extern "C" int myea_b200_gemm_timeline(long long *out32) {
+  return cudaMemcpyFromSymbol(out32, myea::g_timeline, sizeof(long long) * 32) == cudaSuccess ? 0 : 1;
+}
+#endif
