@@ -32,6 +32,9 @@ struct Context {
   std::string error;
   int gemm_engine = 0;  // 0 = tcgen05 3xTF32, 1 = FP32 FMA
   int gemm_bn = 0;      // forced N tile of the tcgen05 kernel (0 = heuristic)
+  float *sk_ws = nullptr;               // partial sums of tiles split along K (gemm_splitk_reserve)
+  unsigned int *sk_counters = nullptr;  // arrival counters of those tiles, all zero between launches
+  int sk_clusters = 0;                  // clusters the workspace has slots for
 
   void begin(TimerClass) {
     if (profiling) cudaEventRecord(ev0, stream);
@@ -130,6 +133,10 @@ int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, co
                 const Epilogue &epi);
 // Launches split kernels + the tensor-core kernel (engine 0) or the FP32 FMA kernel (engine 1) on ctx.stream.
 int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &epi, const GemmScratch &scratch);
+// Optional workspace that lets the 256 x 256 tensor-core kernel split the tiles of a partial last wave along K
+// (39 MB per context); without it that kernel computes whole tiles only.
+int gemm_splitk_reserve(Context &ctx);
+void gemm_splitk_release(Context &ctx);
 
 // ---------------------------------------------------------------------------------------------------------
 // Bandwidth-bound kernels (kernels_elementwise.cu, optimizer.cu)

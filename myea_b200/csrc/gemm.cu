@@ -722,11 +722,21 @@ struct WideSmem {
   static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;
 };
 
-struct WideTiles {
+// Work list of the wide kernel.  Tiles [0, dp_tiles) are computed whole, round-robin over the clusters.  The K chunks
+// of the remaining tiles (the partial last wave, or every tile of a contraction with fewer tiles than clusters) form
+// one sequence of sk_units chunks that is cut into equal runs of sk_chunks, one run per cluster ("stream-K"), so that
+// the tail of the work list is spread over all SM pairs instead of leaving most of them idle.
+struct WideWork {
   int tiles_m, tiles_n, num_tiles;
+  int dp_tiles;
+  int sk_chunks;           // chunks per cluster of the split part (0: nothing is split)
+  int sk_units;            // (num_tiles - dp_tiles) * chunks per tile
+  float *ws;               // partial sums of split tiles: [cluster][2][16 warp regions][32 float4 columns][32 lanes]
+  unsigned int *counters;  // [split tile][16 warp regions] arrivals; the last arrival adds the partials up and resets it
 };
+constexpr int WIDE_REGION_FLOATS = 32 * 128;  // one drain warp's share of a tile: 32 rows x 128 columns
 
-__device__ __forceinline__ void wide_tile_coords(const WideTiles &w, int t, int &tm, int &tn) {
+__device__ __forceinline__ void wide_tile_coords(const WideWork &w, int t, int &tm, int &tn) {
   const int per_band = WIDE_BAND * w.tiles_n;
   const int band = t / per_band;
   const int within = t - band * per_band;
@@ -735,10 +745,37 @@ __device__ __forceinline__ void wide_tile_coords(const WideTiles &w, int t, int 
   tm = band * WIDE_BAND + (within - tn * rows);
 }
 
+// The segments (tile, chunk range) of one cluster, in the order every role of the kernel walks them.
+struct WideSegments {
+  int next_tile, stride, dp_tiles, num_chunks, u, u_end;
+  int tile, c0, c1;  // the current segment
+  __device__ __forceinline__ WideSegments(const WideWork &w, int cluster, int clusters, int chunks_per_tile)
+      : next_tile(cluster), stride(clusters), dp_tiles(w.dp_tiles), num_chunks(chunks_per_tile) {
+    u = min(cluster * w.sk_chunks, w.sk_units);
+    u_end = min(u + w.sk_chunks, w.sk_units);
+  }
+  __device__ __forceinline__ bool next() {
+    if (next_tile < dp_tiles) {
+      tile = next_tile; c0 = 0; c1 = num_chunks;
+      next_tile += stride;
+      return true;
+    }
+    if (u < u_end) {
+      const int ts = u / num_chunks;
+      c0 = u - ts * num_chunks;
+      c1 = min(num_chunks, c0 + (u_end - u));
+      tile = dp_tiles + ts;
+      u += c1 - c0;
+      return true;
+    }
+    return false;
+  }
+};
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(WIDE_THREADS, 1)
 gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
                                 const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
-                                const GemmDims dims, const WideTiles tiles, const Epilogue epi, int *error_flag) {
+                                const GemmDims dims, const WideWork work, const Epilogue epi, int *error_flag) {
   using S = WideSmem;
   constexpr int STAGES = WIDE_STAGES, BN = 256, TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
@@ -787,14 +824,16 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
       bool ok = true;
-      uint32_t it = 0;  // k-blocks staged so far, over all tiles
+      uint32_t it = 0;  // k-blocks staged so far, over all segments
       TL_DECL(w_empty);
-      for (int t = cluster_id; t < tiles.num_tiles && ok; t += num_clusters) {
+      WideSegments seg(work, cluster_id, num_clusters, num_chunks);
+      while (ok && seg.next()) {
         int tm, tn;
-        wide_tile_coords(tiles, t, tm, tn);
+        wide_tile_coords(work, seg.tile, tm, tn);
         const int m0 = tm * 256 + static_cast<int>(cta_rank) * 128;
         const int nb0 = tn * BN + static_cast<int>(cta_rank) * 128;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb_end = min(num_kb, seg.c1 * WIDE_KC);
+        for (int kb = seg.c0 * WIDE_KC; kb < kb_end; ++kb, ++it) {
           const int s = static_cast<int>(it % STAGES);
           const uint32_t ph = (it / STAGES) & 1u;
           TL_BEGIN(w_empty);
@@ -821,8 +860,9 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
       uint32_t g = 0;   // K chunks issued so far: chunk g goes into buffer g & 1
       TL_DECL(w_full);
       TL_DECL(w_acc);
-      for (int t = cluster_id; t < tiles.num_tiles && ok; t += num_clusters) {
-        for (int c = 0; c < num_chunks && ok; ++c, ++g) {
+      WideSegments seg(work, cluster_id, num_clusters, num_chunks);
+      while (ok && seg.next()) {
+        for (int c = seg.c0; c < seg.c1 && ok; ++c, ++g) {
           const uint32_t b = g & 1u;
           if (g >= 2) {
             TL_BEGIN(w_acc);
@@ -854,7 +894,7 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
           }
           if (ok) ptx::tc_commit_pair(&acc_full_bar[b]);
         }
-        if (t == cluster_id) TL(3);
+        if (g <= static_cast<uint32_t>(num_chunks)) TL(3);
       }
       TL_STORE(4, w_full);
       TL_STORE(9, w_acc);
@@ -864,16 +904,18 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
     // ---------------- drain + epilogue: 8 warps; lane quarter = warp % 4, column half = (warp - 2) / 4 ----------------
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
+    const int region = static_cast<int>(cta_rank) * 8 + (warp - 2);  // this warp's 32 x 128 share of the pair's tile
     const bool vec_ok = epilogue_vector_ok(epi);
     const int mode = epilogue_mode(epi);
     bool ok = true;
     uint32_t g = 0;
     TL_DECL(w_accfull);
-    for (int t = cluster_id; t < tiles.num_tiles && ok; t += num_clusters) {
+    WideSegments seg(work, cluster_id, num_clusters, num_chunks);
+    while (ok && seg.next()) {
       float sum[128];
 #pragma unroll
       for (int j = 0; j < 128; ++j) sum[j] = 0.f;
-      for (int c = 0; c < num_chunks; ++c, ++g) {
+      for (int c = seg.c0; c < seg.c1; ++c, ++g) {
         const uint32_t b = g & 1u;
         TL_BEGIN(w_accfull);
         if (!ptx::mbar_wait_or_abort(&acc_full_bar[b], (g >> 1) & 1u, abort_flag)) {
@@ -897,10 +939,60 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(&acc_empty_bar[b], 0);
       }
-      if (t == cluster_id && warp == 2 && lane == 0) { TL(6); TL_STORE(10, w_accfull); }
-      if (ok && num_kb > 0) {
+      if (g <= static_cast<uint32_t>(num_chunks) && warp == 2 && lane == 0) { TL(6); TL_STORE(10, w_accfull); }
+      if (!ok || num_kb <= 0) break;
+      bool finish = true;  // this warp writes its share of the tile
+      if (seg.c0 != 0 || seg.c1 != num_chunks) {
+        // A split tile.  Every contributor leaves its partial sums in its own slot and counts itself in; the warp that
+        // arrives last adds the slots up in cluster order (the same order whoever is last, so the result does not
+        // depend on timing) and runs the epilogue.  Nobody waits for anybody.
+        const int ts = seg.tile - work.dp_tiles;
+        const int tile_u0 = ts * num_chunks;
+        const int first = tile_u0 / work.sk_chunks;
+        const int last = min((tile_u0 + num_chunks - 1) / work.sk_chunks, num_clusters - 1);
+        const int my_slot = (cluster_id * work.sk_chunks >= tile_u0) ? 0 : 1;
+        float4 *mine = reinterpret_cast<float4 *>(work.ws + (static_cast<size_t>(cluster_id * 2 + my_slot) * 16 + region) * WIDE_REGION_FLOATS);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) __stcg(mine + j * 32 + lane, make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]));
+        __threadfence();
+        __syncwarp();
+        unsigned int arrived = 0;
+        unsigned int *counter = work.counters + ts * 16 + region;
+        if (lane == 0) arrived = atomicAdd(counter, 1u);
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        finish = arrived == static_cast<unsigned int>(last - first);
+        if (finish) {
+          if (lane == 0) *counter = 0u;  // every contributor has arrived: ready for the next launch
+          __threadfence();
+          // two contributors (the usual case): a + b is the same whichever of them is last, so the sum in registers
+          // stays and only the other slot is read; more than two are added from zero in cluster order
+          const bool pairwise = last == first + 1;
+          const int skip = pairwise ? cluster_id : -1;
+          if (!pairwise) {
+#pragma unroll
+            for (int j = 0; j < 128; ++j) sum[j] = 0.f;
+          }
+          // eight float4 loads in flight per lane; the order of the additions into one element is the cluster order
+#pragma unroll
+          for (int jb = 0; jb < 32; jb += 8) {
+            for (int cc = first; cc <= last; ++cc) {
+              if (cc == skip) continue;
+              const int slot = (cc * work.sk_chunks >= tile_u0) ? 0 : 1;
+              const float4 *theirs = reinterpret_cast<const float4 *>(work.ws + (static_cast<size_t>(cc * 2 + slot) * 16 + region) * WIDE_REGION_FLOATS);
+              float4 v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = __ldcg(theirs + (jb + j) * 32 + lane);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                sum[4 * (jb + j)] += v[j].x; sum[4 * (jb + j) + 1] += v[j].y; sum[4 * (jb + j) + 2] += v[j].z; sum[4 * (jb + j) + 3] += v[j].w;
+              }
+            }
+          }
+        }
+      }
+      if (finish) {
         int tm, tn;
-        wide_tile_coords(tiles, t, tm, tn);
+        wide_tile_coords(work, seg.tile, tm, tn);
         const long long m = static_cast<long long>(tm) * 256 + static_cast<long long>(cta_rank) * 128 + q * 32 + lane;
         const long long col_base = static_cast<long long>(tn) * BN + half * 128;
 #pragma unroll
@@ -911,11 +1003,11 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
           epilogue_row32(epi, v, m, col_base + jc * 32, dims.M, dims.N, vec_ok, mode);
         }
       }
-      if (t == cluster_id && warp == 2 && lane == 0) TL(7);
+      if (g <= static_cast<uint32_t>(num_chunks) && warp == 2 && lane == 0) TL(7);
     }
   }
-  // every role leaves its loop only when all tiles are done or a wait has given up; the pair stays together until both
-  // CTAs are here, so nobody signals a barrier of a CTA that has exited
+  // every role leaves its loop only when its segments are done or a wait has given up; the pair stays together until
+  // both CTAs are here, so nobody signals a barrier of a CTA that has exited
   ptx::tc_fence_before();
   __syncthreads();
   ptx::cluster_sync_all();
@@ -1181,6 +1273,32 @@ static int launch_tcgen05_pair(Context &ctx, const CUtensorMap maps[4], const Ge
   return err == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
+// Workspace of the wide kernel's split tiles: two partial-sum slots of one 256 x 256 tile per cluster and one arrival
+// counter per (split tile, warp region).  Without it the wide kernel computes whole tiles only.
+int gemm_splitk_reserve(Context &ctx) {
+  if (ctx.sk_ws != nullptr) return MYEA_OK;
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device) != cudaSuccess || sms < 2) return MYEA_E_CUDA;
+  const int clusters = sms / 2;
+  const size_t floats = static_cast<size_t>(clusters) * 2 * 16 * WIDE_REGION_FLOATS;
+  if (cudaMalloc(&ctx.sk_ws, floats * sizeof(float)) != cudaSuccess) { ctx.sk_ws = nullptr; return MYEA_E_CUDA; }
+  if (cudaMalloc(&ctx.sk_counters, static_cast<size_t>(clusters) * 16 * sizeof(unsigned int)) != cudaSuccess ||
+      cudaMemset(ctx.sk_counters, 0, static_cast<size_t>(clusters) * 16 * sizeof(unsigned int)) != cudaSuccess) {
+    cudaFree(ctx.sk_ws);
+    ctx.sk_ws = nullptr;
+    return MYEA_E_CUDA;
+  }
+  ctx.sk_clusters = clusters;
+  return MYEA_OK;
+}
+void gemm_splitk_release(Context &ctx) {
+  if (ctx.sk_ws != nullptr) cudaFree(ctx.sk_ws);
+  if (ctx.sk_counters != nullptr) cudaFree(ctx.sk_counters);
+  ctx.sk_ws = nullptr;
+  ctx.sk_counters = nullptr;
+  ctx.sk_clusters = 0;
+}
+
 static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const GemmDims &dims, const Epilogue &epi) {
   static int clusters[16] = {};  // clusters of two CTAs that can be resident at once, per device
   const int dev = ctx.device & 15;
@@ -1200,13 +1318,35 @@ static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const Ge
     clusters[dev] = n < sms / 2 ? n : sms / 2;
     if (getenv("MYEA_B200_DEBUG") != nullptr) fprintf(stderr, "wide kernel: %d resident clusters on %d SMs\n", clusters[dev], sms);
   }
-  WideTiles tiles;
-  tiles.tiles_m = (dims.M + 255) / 256;
-  tiles.tiles_n = (dims.N + 255) / 256;
-  tiles.num_tiles = tiles.tiles_m * tiles.tiles_n;
-  const int grid_clusters = tiles.num_tiles < clusters[dev] ? tiles.num_tiles : clusters[dev];
+  const int G = clusters[dev];
+  const int num_kb = (dims.K + BK - 1) / BK;
+  const int num_chunks = (num_kb + WIDE_KC - 1) / WIDE_KC;
+  WideWork work = {};
+  work.tiles_m = (dims.M + 255) / 256;
+  work.tiles_n = (dims.N + 255) / 256;
+  work.num_tiles = work.tiles_m * work.tiles_n;
+  work.dp_tiles = work.num_tiles;
+  int grid_clusters = work.num_tiles < G ? work.num_tiles : G;
+  // stream-K for the partial last wave (gemm_bn 4 switches it off): needs the partial-sum workspace and more than one
+  // K chunk per tile
+  const int rem = work.num_tiles % G;
+  if (ctx.gemm_bn != 4 && ctx.sk_ws != nullptr && ctx.sk_clusters >= G && rem != 0 && num_chunks >= 2) {
+    const int units = rem * num_chunks;
+    const int per_cluster = (units + G - 1) / G;
+    // splitting a tile costs about one chunk's time (partial sums through L2, one counter round trip, the second
+    // pass of the warp that arrives last): worth it when it takes at least two chunks off the longest cluster
+    if (num_chunks - per_cluster >= 2) {
+      work.dp_tiles = work.num_tiles - rem;
+      work.sk_units = units;
+      work.sk_chunks = per_cluster;
+      work.ws = ctx.sk_ws;
+      work.counters = ctx.sk_counters;
+      const int used = (units + per_cluster - 1) / per_cluster;
+      grid_clusters = work.dp_tiles > 0 ? G : used;
+    }
+  }
   gemm3x_tf32_tcgen05_wide_kernel<<<dim3(static_cast<unsigned>(2 * grid_clusters)), WIDE_THREADS, WideSmem::TOTAL, ctx.stream>>>(
-      maps[0], maps[1], maps[2], maps[3], dims, tiles, epi, ctx.d_error_flag);
+      maps[0], maps[1], maps[2], maps[3], dims, work, epi, ctx.d_error_flag);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess && getenv("MYEA_B200_DEBUG") != nullptr) fprintf(stderr, "wide kernel launch: %s\n", cudaGetErrorString(err));
   return err == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
@@ -1230,8 +1370,9 @@ int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, co
   } else {
     // tile shape: CTA pairs (256 x 128 per pair) unless forced to a single-CTA shape (gemm_bn 128 / 256) or there is
     // only one row tile; 128-column accumulators (four of them) are the accurate configuration
-    // gemm_bn: 0 = heuristic, 3 = wide CTA pair (256 x 256), 2 = CTA pair (256 x 128), 128 / 256 = single CTA
-    const bool wide = ctx.gemm_bn == 0 ? (M > 128 && N > 128) : (ctx.gemm_bn == 3);
+    // gemm_bn: 0 = heuristic, 3 = wide CTA pair (256 x 256), 4 = the same without stream-K, 2 = CTA pair (256 x 128),
+    // 128 / 256 = single CTA
+    const bool wide = ctx.gemm_bn == 0 ? (M > 128 && N > 128) : (ctx.gemm_bn == 3 || ctx.gemm_bn == 4);
     const bool pair = !wide && (ctx.gemm_bn == 0 ? (M > 128) : (ctx.gemm_bn == 2));
     const int bn = ctx.gemm_bn == 256 ? 256 : 128;
     const int b_box = wide ? 128 : (pair ? 64 : bn);

@@ -15,7 +15,7 @@ extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N,
   Context ctx;
   ctx.device = device;
   ctx.gemm_engine = engine & 1;
-  ctx.gemm_bn = (engine >> 8) & 0x1FF;  // bits 8..16: forced tile shape (0 = heuristic, 2 = CTA pair, 128 / 256 = single-CTA N tile)
+  ctx.gemm_bn = (engine >> 8) & 0x1FF;  // bits 8..16: forced tile shape (0 = heuristic, 3 = 256 x 256 CTA pair, 4 = the same without stream-K, 2 = 256 x 128 CTA pair, 128 / 256 = single-CTA N tile)
   int rc = MYEA_OK;
   float *dA = nullptr, *dB = nullptr, *dC = nullptr, *dS = nullptr;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
@@ -26,6 +26,7 @@ extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N,
       cudaMalloc(&ctx.d_error_flag, sizeof(int)) != cudaSuccess) {
     rc = MYEA_E_CUDA;
   }
+  if (rc == MYEA_OK) rc = gemm_splitk_reserve(ctx);
   if (rc == MYEA_OK) {
     cudaMemsetAsync(ctx.d_error_flag, 0, sizeof(int), ctx.stream);
     cudaMemcpyAsync(dA, A, M * K * 4, cudaMemcpyHostToDevice, ctx.stream);
@@ -72,6 +73,7 @@ extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N,
   if (e0) cudaEventDestroy(e0);
   if (e1) cudaEventDestroy(e1);
   cudaFree(dA); cudaFree(dB); cudaFree(dC); cudaFree(dS); cudaFree(ctx.d_error_flag);
+  gemm_splitk_release(ctx);
   cudaStreamDestroy(ctx.stream);
   return rc;
 }

@@ -218,6 +218,7 @@ static int allocate_buffers(myea_b200_net *net) {
   RC(dev_alloc(net, &net->d_clip_scale, 1));
   RC(dev_alloc(net, &net->d_loss_tmp, 3));
   RC(dev_alloc(net, &net->ctx.d_error_flag, 1));
+  RC(gemm_splitk_reserve(net->ctx));
   RC(dev_alloc(net, &net->d_input, rows * net->layers[0].n_out));
   RC(dev_alloc(net, &net->d_desired, rows * net->layers.back().n_out));
   long long max_h = 1;
@@ -343,6 +344,7 @@ extern "C" void myea_b200_destroy(myea_handle net) {
   comm_destroy(net);
   for (auto &L : net->layers) lstm_destroy(L);
   for (void *p : net->allocations) cudaFree(p);
+  gemm_splitk_release(net->ctx);
   if (net->ctx.ev0) cudaEventDestroy(net->ctx.ev0);
   if (net->ctx.ev1) cudaEventDestroy(net->ctx.ev1);
   if (net->ctx.stream) cudaStreamDestroy(net->ctx.stream);
