@@ -113,10 +113,15 @@ struct Operand {
 // left operand (role A) and [hi x8 | lo x8] for the right operand (role B), so that one K = 16 BF16 MMA of an A group with
 // a B group yields lo_a*hi_b + hi_a*lo_b.
 enum { PANEL_ROLE_A = 0, PANEL_ROLE_B = 1 };
+// An MN-major panel set (major == PANEL_MN) describes the operand TRANSPOSED: the arrays are [k][kp] (hi, fp32) and
+// [2 * round_up(k, 8)][kp] (cross, bf16; per 8 K rows 16 panel rows, lo rows / hi rows ordered by role), the operand's
+// `rows` run along the contiguous axis.  Only the 256 x 256 kernel reads this form; it needs kp to be a multiple of 64.
+enum { PANEL_K = 0, PANEL_MN = 1 };
 struct Panels {
   float *hi = nullptr, *lo = nullptr;
   long long rows = 0, k = 0, kp = 0;
   int role = PANEL_ROLE_A;
+  int major = PANEL_K;
 };
 
 struct GemmScratch {   // hi/lo K-major panels of both operands, reused by every contraction of a handle
@@ -131,6 +136,14 @@ int gemm_prepare(Context &ctx, const Operand &op, float *mem, Panels *out, int r
 int gemm_prepare_into(Context &ctx, const Operand &op, const Panels &dst, long long row_offset, long long k_offset);
 int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, const Panels &B, long long b_row0, long long N,
                 const Epilogue &epi);
+// One pass over a row-major source S[R][C] that serves BOTH readings of it: `as_rows` is the K-major operand
+// (rows = R, K = C) and `as_cols` the MN-major operand (rows = C, K = R); they share the hi panel.  Either output may
+// be null.  `mem` needs shared_panel_floats(R, C) floats.
+size_t shared_panel_floats(long long R, long long C);
+int gemm_prepare_shared(Context &ctx, const float *src, long long stride_r, long long R, long long C, float *mem, int role_rows,
+                        Panels *as_rows, int role_cols, Panels *as_cols);
+// true when a contraction of this shape runs on the 256 x 256 kernel (the only one that takes MN-major operands)
+bool gemm_takes_mn_major(const Context &ctx, long long M, long long N);
 // Launches split kernels + the tensor-core kernel (engine 0) or the FP32 FMA kernel (engine 1) on ctx.stream.
 int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &epi, const GemmScratch &scratch);
 // Optional workspace that lets the 256 x 256 tensor-core kernel split the tiles of a partial last wave along K

@@ -6,23 +6,26 @@
 // (Neural_Network__Forward_Pass__OpenMP.cpp:4517-4557), Backward_Pass__FC (…Backward_Pass__OpenMP.cpp:1044-1082) and
 // Update_Derivative_Weight__FC (…Update_Derivative_Weight__OpenMP.cpp:178-216), and the LSTM gate products.
 //
-// Precision: 3xTF32.  Every fp32 operand x is split into hi = x with the 13 low mantissa bits cleared (exactly a
-// TF32 number) and lo = x - hi (exact in fp32, at most 13 significant bits), and the tensor core accumulates
-// hi*hi + hi*lo + lo*hi in fp32 in tensor memory; only lo*lo (2^-22 relative) is dropped.
+// Precision: split fp32 on the tensor cores.  Every fp32 operand x is split into hi = x rounded to TF32 and
+// lo = x - hi (exact in fp32); the tensor core accumulates hi*hi (one TF32 instruction per 8 of K) and
+// lo*hi + hi*lo (ONE bf16 K = 16 instruction per 8 of K, both terms packed into its K dimension) in fp32 in tensor
+// memory; only lo*lo (2^-22 relative) is dropped.  See "Operand panels" below for the packing.
 //
-// Pipeline of one CTA (192 threads, one 128 x BN output tile):
-//   warp 0   : TMA producer - cp.async.bulk.tensor 2D loads of the four K-major panels (A_hi, A_lo, B_hi, B_lo),
+// Three kernels share the operand format and the epilogue:
+//   gemm3x_tf32_tcgen05_kernel       one CTA, 128 x 128 tile, 192 threads (small M)
+//   gemm3x_tf32_tcgen05_pair_kernel  CTA pair (cta_group::2), 256 x 128 tile
+//   gemm3x_tf32_tcgen05_wide_kernel  CTA pair, persistent, 256 x 256 tiles, stream-K tail: the one large layers use
+// Common structure:
+//   warp 0   : TMA producer - cp.async.bulk.tensor 2D loads of the four K-major panels (A hi, A cross, B hi, B cross),
 //              128-byte swizzle, 32 floats of K per stage, completing on a per-stage "full" mbarrier
-//   warp 1   : allocates tensor memory, one elected lane issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8) three times
-//              per K step, tcgen05.commit releases the stage ("empty" mbarrier) and finally signals the epilogue
-//   warps 2-5: epilogue - tcgen05.ld of the accumulator (each warp its own 32-lane quarter), transposition through
-//              shared memory so that global accesses are row-contiguous, fused bias / accumulate / activation
-//              derivative, stores
+//   warp 1   : allocates tensor memory; one elected lane issues the tcgen05.mma pairs, tcgen05.commit releases the
+//              stage ("empty" mbarrier) and signals finished accumulators
+//   others   : read accumulators with tcgen05.ld (each warp its own 32-lane quarter: the thread owns an output row),
+//              fused bias / accumulate / skip-connection addend / activation derivative, float4 stores
 // Every mbarrier wait is bounded (about one second of SM clock); a wait that runs out sets the handle's error flag
-// and the CTA drains its own copies, frees its tensor memory and returns.
+// and the CTA frees its tensor memory and returns.
 //
-// The FP32 FMA kernel at the end of the file is the second engine (exact fp32 products; used for tiny shapes whose
-// rows cannot be described to TMA, and selectable for debugging).
+// The FP32 FMA kernel at the end of the file is the second engine (exact fp32 products; selectable for debugging).
 #include "common.cuh"
 
 #include <cudaTypedefs.h>
@@ -153,6 +156,12 @@ __device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorM
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(void *smem_dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_holder, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)), "r"(ncols) : "memory");
 }
@@ -251,14 +260,32 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   return d;
 }
 
+// The same for an MN-major tile: rows of 128 bytes run along M (or N) - 32 fp32 or 64 bf16 elements -, consecutive rows
+// are consecutive K, 8 rows form one swizzle atom (stride byte offset 1024 B between atoms along K) and the next 128
+// bytes' worth of M / N elements starts `chunk_bytes` further on (leading byte offset).
+// 32-bit elements (the TF32 hi panel) must use the 128-byte swizzle with 32-byte atoms in this orientation (TMA
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, layout type 1): its pattern repeats every 4 rows, so the stride byte offset
+// between K groups is 512 B.  16-bit elements (the bf16 cross panel) use the ordinary 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32_t chunk_bytes, bool atom32) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(chunk_bytes >> 4) << 16;
+  d |= static_cast<uint64_t>((atom32 ? 512 : 1024) >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(atom32 ? 1 : 2) << 61;
+  return d;
+}
+
 // Instruction descriptor of tcgen05.mma.kind::tf32: D format F32 (1) bits 4-5, A and B format TF32 (2) bits 7-9 and
 // 10-12, both operands K-major (bits 15, 16 clear), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-__host__ __device__ constexpr uint32_t make_idesc_tf32(int m, int n) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc_tf32(int m, int n, bool a_mn = false, bool b_mn = false) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
 }
 // tcgen05.mma.kind::f16 with BF16 inputs (format 1) and an F32 accumulator
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn = false, bool b_mn = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 struct GemmDims {
@@ -772,6 +799,21 @@ struct WideSegments {
   }
 };
 
+// one operand's 128 rows of one stage: a K-major panel is one 2-D box per panel (32 floats of K x 128 rows), an
+// MN-major panel one 3-D box (hi: 32 floats x 32 K rows x 4 chunks; cross: 64 bf16 x 64 K rows x 2 chunks)
+template <bool MN>
+__device__ __forceinline__ void wide_load_operand(uint8_t *dst_hi, uint8_t *dst_x, const CUtensorMap *m_hi, const CUtensorMap *m_x,
+                                                  uint64_t *bar, int kb, int row0) {
+  if (!MN) {
+    ptx::tma_load_2d_pair(dst_hi, m_hi, bar, kb * BK, row0);
+    ptx::tma_load_2d_pair(dst_x, m_x, bar, kb * BK, row0);
+  } else {
+    ptx::tma_load_3d_pair(dst_hi, m_hi, bar, 0, kb * BK, row0 >> 5);
+    ptx::tma_load_3d_pair(dst_x, m_x, bar, 0, kb * 2 * BK, row0 >> 6);
+  }
+}
+
+template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(WIDE_THREADS, 1)
 gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
                                 const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
@@ -841,10 +883,8 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
           TL_END(w_empty);
           uint8_t *st = smem + s * S::STAGE_BYTES;
           if (cta_rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * S::STAGE_BYTES);
-          ptx::tma_load_2d_pair(st, &tm_a_hi, &full_bar[s], kb * BK, m0);
-          ptx::tma_load_2d_pair(st + S::TILE_BYTES, &tm_a_lo, &full_bar[s], kb * BK, m0);
-          ptx::tma_load_2d_pair(st + 2 * S::TILE_BYTES, &tm_b_hi, &full_bar[s], kb * BK, nb0);
-          ptx::tma_load_2d_pair(st + 3 * S::TILE_BYTES, &tm_b_lo, &full_bar[s], kb * BK, nb0);
+          wide_load_operand<A_MN>(st, st + S::TILE_BYTES, &tm_a_hi, &tm_a_lo, &full_bar[s], kb, m0);
+          wide_load_operand<B_MN>(st + 2 * S::TILE_BYTES, st + 3 * S::TILE_BYTES, &tm_b_hi, &tm_b_lo, &full_bar[s], kb, nb0);
         }
       }
       TL_STORE(5, w_empty);
@@ -854,8 +894,12 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
     // ---------------- MMA issuer (leader CTA) ----------------
     if (lane == 0 && cta_rank == 0) {
       bool ok = true;
-      constexpr uint32_t idesc_main = make_idesc_tf32(256, BN);
-      constexpr uint32_t idesc_cross = make_idesc_bf16(256, BN);
+      constexpr uint32_t idesc_main = make_idesc_tf32(256, BN, A_MN, B_MN);
+      constexpr uint32_t idesc_cross = make_idesc_bf16(256, BN, A_MN, B_MN);
+      // descriptor advance per K step of 8 (in 16-byte units): 32 bytes inside the swizzle row of a K-major tile; one
+      // atom of 8 K rows (hi) or two (cross: 16 bf16 K rows) of an MN-major tile
+      constexpr uint64_t a_step_hi = A_MN ? 64 : 2, a_step_x = A_MN ? 128 : 2;
+      constexpr uint64_t b_step_hi = B_MN ? 64 : 2, b_step_x = B_MN ? 128 : 2;
       uint32_t it = 0;  // k-blocks consumed so far
       uint32_t g = 0;   // K chunks issued so far: chunk g goes into buffer g & 1
       TL_DECL(w_full);
@@ -881,14 +925,15 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
             if (it == 0) TL(2);
             ptx::tc_fence_after();
             const uint32_t st = ptx::smem_u32(smem + s * S::STAGE_BYTES);
-            const uint64_t a_hi = make_smem_desc(st), a_x = make_smem_desc(st + S::TILE_BYTES);
-            const uint64_t b_hi = make_smem_desc(st + 2 * S::TILE_BYTES), b_x = make_smem_desc(st + 3 * S::TILE_BYTES);
+            const uint64_t a_hi = A_MN ? make_smem_desc_mn(st, 4096, true) : make_smem_desc(st);
+            const uint64_t a_x = A_MN ? make_smem_desc_mn(st + S::TILE_BYTES, 8192, false) : make_smem_desc(st + S::TILE_BYTES);
+            const uint64_t b_hi = B_MN ? make_smem_desc_mn(st + 2 * S::TILE_BYTES, 4096, true) : make_smem_desc(st + 2 * S::TILE_BYTES);
+            const uint64_t b_x = B_MN ? make_smem_desc_mn(st + 3 * S::TILE_BYTES, 8192, false) : make_smem_desc(st + 3 * S::TILE_BYTES);
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint64_t koff = static_cast<uint64_t>((k * UMMA_K * 4) >> 4);
               const bool first = (kb == c * WIDE_KC) && (k == 0);
-              ptx::mma_bf16_pair(acc, a_x + koff, b_x + koff, idesc_cross, first ? 0u : 1u);  // lo*hi + hi*lo
-              ptx::mma_tf32_pair(acc, a_hi + koff, b_hi + koff, idesc_main, 1u);             // hi*hi
+              ptx::mma_bf16_pair(acc, a_x + k * a_step_x, b_x + k * b_step_x, idesc_cross, first ? 0u : 1u);  // lo*hi + hi*lo
+              ptx::mma_tf32_pair(acc, a_hi + k * a_step_hi, b_hi + k * b_step_hi, idesc_main, 1u);          // hi*hi
             }
             ptx::tc_commit_pair(&empty_bar[s]);
           }
@@ -1055,17 +1100,25 @@ __device__ __forceinline__ void split_group(const float (&v)[8], int role_b, int
 }
 
 // source already K-major (stride_k == 1); writes columns [0, round_up(k, 8)) of every panel row (pitch kp)
+// With cross_mn != null the same pass also writes the cross panel of the source's OTHER reading, the one whose K runs
+// along the source rows (MN-major operand, see gemm_prepare_shared): [2 * round_up(rows, 8)][kp] bf16, per 8 source
+// rows 16 panel rows (role A: lo rows then hi rows; role B: hi rows then lo rows); source rows past `rows` are zero.
 __global__ void split_rows_kernel(const float *__restrict__ src, long long stride_r, long long rows, long long k, long long kp,
-                                  float *__restrict__ hi, float *__restrict__ cross, int role_b, int raw) {
+                                  float *__restrict__ hi, float *__restrict__ cross, int role_b, int raw,
+                                  uint16_t *__restrict__ cross_mn = nullptr, int role_mn_b = 0) {
   const long long kg = (k + 7) >> 3;  // groups of 8 per panel row
-  const long long total = rows * kg;
+  const long long rows_all = cross_mn != nullptr ? ((rows + 7) & ~7ll) : rows;
+  const long long total = rows_all * kg;
   const bool vec = ((stride_r & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long r = i / kg;
     const long long c = (i - r * kg) << 3;
     float v[8];
-    if (vec && c + 7 < k) {
+    if (r >= rows) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    } else if (vec && c + 7 < k) {
       const float4 t = *reinterpret_cast<const float4 *>(src + r * stride_r + c);
       const float4 u = *reinterpret_cast<const float4 *>(src + r * stride_r + c + 4);
       v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; v[4] = u.x; v[5] = u.y; v[6] = u.z; v[7] = u.w;
@@ -1076,12 +1129,25 @@ __global__ void split_rows_kernel(const float *__restrict__ src, long long strid
     float h[8];
     uint32_t x[8];
     split_group(v, role_b, raw, h, x);
-    float4 *ph = reinterpret_cast<float4 *>(hi + r * kp + c);
-    ph[0] = make_float4(h[0], h[1], h[2], h[3]);
-    ph[1] = make_float4(h[4], h[5], h[6], h[7]);
-    uint4 *px = reinterpret_cast<uint4 *>(cross + r * kp + c);
-    px[0] = make_uint4(x[0], x[1], x[2], x[3]);
-    px[1] = make_uint4(x[4], x[5], x[6], x[7]);
+    if (r < rows) {
+      float4 *ph = reinterpret_cast<float4 *>(hi + r * kp + c);
+      ph[0] = make_float4(h[0], h[1], h[2], h[3]);
+      ph[1] = make_float4(h[4], h[5], h[6], h[7]);
+      if (cross != nullptr) {
+        uint4 *px = reinterpret_cast<uint4 *>(cross + r * kp + c);
+        px[0] = make_uint4(x[0], x[1], x[2], x[3]);
+        px[1] = make_uint4(x[4], x[5], x[6], x[7]);
+      }
+    }
+    if (cross_mn != nullptr) {
+      // x[0..3] / x[4..7] are the packed lo and hi values of these 8 columns (in the order of role_b)
+      const uint4 lo4 = role_b ? make_uint4(x[4], x[5], x[6], x[7]) : make_uint4(x[0], x[1], x[2], x[3]);
+      const uint4 hi4 = role_b ? make_uint4(x[0], x[1], x[2], x[3]) : make_uint4(x[4], x[5], x[6], x[7]);
+      const long long g16 = (r >> 3) * 16 + (r & 7);
+      const long long row_lo = g16 + (role_mn_b ? 8 : 0), row_hi = g16 + (role_mn_b ? 0 : 8);
+      *reinterpret_cast<uint4 *>(cross_mn + row_lo * kp + c) = lo4;
+      *reinterpret_cast<uint4 *>(cross_mn + row_hi * kp + c) = hi4;
+    }
   }
 }
 
@@ -1184,7 +1250,61 @@ static bool make_panel_map(CUtensorMap *map, const float *panel, long long rows,
   return r == CUDA_SUCCESS;
 }
 
+// MN-major panels (arrays [k][kp]): 3-D views (128 bytes of rows, K, 128-byte chunk) so that one box lands in shared
+// memory chunk after chunk, each chunk K rows of 128 bytes.  hi: fp32, 32 K rows per stage; cross: bf16, 64 panel rows.
+static bool make_panel_map_mn(CUtensorMap *map, const void *panel, bool cross, long long rows, long long k, long long kp) {
+  PFN_cuTensorMapEncodeTiled_v12000 fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  const long long elems = cross ? 64 : 32;                     // elements in 128 bytes
+  const long long krows = cross ? 2 * ((k + 7) & ~7ll) : k;    // panel rows along K
+  cuuint64_t gdim[3] = {static_cast<cuuint64_t>(elems), static_cast<cuuint64_t>(krows), static_cast<cuuint64_t>((rows + elems - 1) / elems)};
+  cuuint64_t gstride[2] = {static_cast<cuuint64_t>(kp) * (cross ? 2 : 4), 128};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(elems), static_cast<cuuint32_t>(cross ? 2 * BK : BK), static_cast<cuuint32_t>(128 / elems)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, cross ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(panel), gdim, gstride,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, cross ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 static inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
+
+size_t shared_panel_floats(long long R, long long C) {
+  const long long pitch = round_up(C, 64), r8 = round_up(R, 8);
+  return static_cast<size_t>(3 * r8 * pitch) + 64;  // hi, K-major cross, MN-major cross (2 * r8 rows of bf16)
+}
+
+int gemm_prepare_shared(Context &ctx, const float *src, long long stride_r, long long R, long long C, float *mem, int role_rows,
+                        Panels *as_rows, int role_cols, Panels *as_cols) {
+  if (src == nullptr || mem == nullptr || R <= 0 || C <= 0 || (reinterpret_cast<uintptr_t>(mem) & 255) != 0) return MYEA_E_INVALID;
+  const long long pitch = round_up(C, 64), r8 = round_up(R, 8);
+  float *hi = mem, *cross_k = mem + r8 * pitch;
+  uint16_t *cross_mn = reinterpret_cast<uint16_t *>(mem + 2 * r8 * pitch);
+  if (as_rows != nullptr) {
+    *as_rows = Panels{};
+    as_rows->hi = hi; as_rows->lo = cross_k; as_rows->rows = R; as_rows->k = C; as_rows->kp = pitch;
+    as_rows->role = role_rows; as_rows->major = PANEL_K;
+  }
+  if (as_cols != nullptr) {
+    *as_cols = Panels{};
+    as_cols->hi = hi; as_cols->lo = reinterpret_cast<float *>(cross_mn); as_cols->rows = C; as_cols->k = R; as_cols->kp = pitch;
+    as_cols->role = role_cols; as_cols->major = PANEL_MN;
+  }
+  const int raw = ctx.gemm_engine == 1 ? 1 : 0;
+  const long long total = r8 * ((C + 7) >> 3);
+  int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
+  if (blocks < 1) blocks = 1;
+  ctx.begin(TC_SPLIT);
+  split_rows_kernel<<<blocks, 256, 0, ctx.stream>>>(src, stride_r, R, C, pitch, hi, as_rows != nullptr ? cross_k : nullptr, role_rows, raw,
+                                                    as_cols != nullptr ? cross_mn : nullptr, role_cols);
+  ctx.end(TC_SPLIT);
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
+bool gemm_takes_mn_major(const Context &ctx, long long M, long long N) {
+  if (ctx.gemm_engine == 1) return true;
+  return ctx.gemm_bn == 0 ? (M > 128 && N > 128) : (ctx.gemm_bn == 3 || ctx.gemm_bn == 4);
+}
 
 size_t gemm_scratch_floats(long long M, long long N, long long K) {
   const long long kp = round_up(K, BK);
@@ -1299,11 +1419,13 @@ void gemm_splitk_release(Context &ctx) {
   ctx.sk_clusters = 0;
 }
 
+template <bool A_MN, bool B_MN>
 static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const GemmDims &dims, const Epilogue &epi) {
   static int clusters[16] = {};  // clusters of two CTAs that can be resident at once, per device
   const int dev = ctx.device & 15;
+  auto kernel = gemm3x_tf32_tcgen05_wide_kernel<A_MN, B_MN>;
   if (clusters[dev] == 0) {
-    if (cudaFuncSetAttribute(gemm3x_tf32_tcgen05_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WideSmem::TOTAL) != cudaSuccess) return MYEA_E_CUDA;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WideSmem::TOTAL) != cudaSuccess) return MYEA_E_CUDA;
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device) != cudaSuccess || sms < 2) return MYEA_E_CUDA;
     cudaLaunchConfig_t cfg = {};
@@ -1311,7 +1433,7 @@ static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const Ge
     cfg.blockDim = dim3(WIDE_THREADS);
     cfg.dynamicSmemBytes = WideSmem::TOTAL;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm3x_tf32_tcgen05_wide_kernel, &cfg) != cudaSuccess || n < 1) {
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n < 1) {
       cudaGetLastError();
       n = sms / 2;
     }
@@ -1345,7 +1467,7 @@ static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const Ge
       grid_clusters = work.dp_tiles > 0 ? G : used;
     }
   }
-  gemm3x_tf32_tcgen05_wide_kernel<<<dim3(static_cast<unsigned>(2 * grid_clusters)), WIDE_THREADS, WideSmem::TOTAL, ctx.stream>>>(
+  kernel<<<dim3(static_cast<unsigned>(2 * grid_clusters)), WIDE_THREADS, WideSmem::TOTAL, ctx.stream>>>(
       maps[0], maps[1], maps[2], maps[3], dims, work, epi, ctx.d_error_flag);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess && getenv("MYEA_B200_DEBUG") != nullptr) fprintf(stderr, "wide kernel launch: %s\n", cudaGetErrorString(err));
@@ -1357,33 +1479,43 @@ int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, co
                 const Epilogue &epi) {
   if (A.k != B.k || M <= 0 || N <= 0 || A.k <= 0 || a_row0 < 0 || b_row0 < 0 || a_row0 + M > A.rows || b_row0 + N > B.rows) return MYEA_E_INVALID;
   if (A.role != PANEL_ROLE_A || B.role != PANEL_ROLE_B) return MYEA_E_INVALID;  // the cross panels of the two sides differ
+  const bool a_mn = A.major == PANEL_MN, b_mn = B.major == PANEL_MN;
+  if ((a_mn && (a_row0 != 0 || (A.kp & 63) != 0)) || (b_mn && (b_row0 != 0 || (B.kp & 63) != 0))) return MYEA_E_INVALID;
   GemmDims dims{static_cast<int>(M), static_cast<int>(N), static_cast<int>(A.k)};
   int rc;
   if (ctx.gemm_engine == 1) {
-    Operand oa{A.hi + a_row0 * A.kp, M, A.k, A.kp, 1, A.lo + a_row0 * A.kp};
-    Operand ob{B.hi + b_row0 * B.kp, N, B.k, B.kp, 1, B.lo + b_row0 * B.kp};
+    // the FP32 FMA engine reads the (unrounded) hi panels by strides; their cross panels are zero
+    Operand oa = a_mn ? Operand{A.hi, M, A.k, 1, A.kp, nullptr} : Operand{A.hi + a_row0 * A.kp, M, A.k, A.kp, 1, A.lo + a_row0 * A.kp};
+    Operand ob = b_mn ? Operand{B.hi, N, B.k, 1, B.kp, nullptr} : Operand{B.hi + b_row0 * B.kp, N, B.k, B.kp, 1, B.lo + b_row0 * B.kp};
     ctx.begin(TC_GEMM);
     dim3 grid(static_cast<unsigned>((dims.N + 63) / 64), static_cast<unsigned>((dims.M + 63) / 64));
     gemm_fp32_fma_kernel<<<grid, 256, 0, ctx.stream>>>(oa, ob, dims, epi);
     ctx.end(TC_GEMM);
     rc = cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
   } else {
-    // tile shape: CTA pairs (256 x 128 per pair) unless forced to a single-CTA shape (gemm_bn 128 / 256) or there is
-    // only one row tile; 128-column accumulators (four of them) are the accurate configuration
     // gemm_bn: 0 = heuristic, 3 = wide CTA pair (256 x 256), 4 = the same without stream-K, 2 = CTA pair (256 x 128),
     // 128 / 256 = single CTA
-    const bool wide = ctx.gemm_bn == 0 ? (M > 128 && N > 128) : (ctx.gemm_bn == 3 || ctx.gemm_bn == 4);
+    const bool wide = gemm_takes_mn_major(ctx, M, N);
+    if ((a_mn || b_mn) && !wide) return MYEA_E_INVALID;
     const bool pair = !wide && (ctx.gemm_bn == 0 ? (M > 128) : (ctx.gemm_bn == 2));
     const int bn = ctx.gemm_bn == 256 ? 256 : 128;
     const int b_box = wide ? 128 : (pair ? 64 : bn);
     CUtensorMap maps[4];
-    const bool ok = make_panel_map(&maps[0], A.hi + a_row0 * A.kp, M, A.k, A.kp, BM) && make_panel_map(&maps[1], A.lo + a_row0 * A.kp, M, A.k, A.kp, BM) &&
-                    make_panel_map(&maps[2], B.hi + b_row0 * B.kp, N, B.k, B.kp, b_box) && make_panel_map(&maps[3], B.lo + b_row0 * B.kp, N, B.k, B.kp, b_box);
+    bool ok = true;
+    if (a_mn) ok = ok && make_panel_map_mn(&maps[0], A.hi, false, M, A.k, A.kp) && make_panel_map_mn(&maps[1], A.lo, true, M, A.k, A.kp);
+    else ok = ok && make_panel_map(&maps[0], A.hi + a_row0 * A.kp, M, A.k, A.kp, BM) && make_panel_map(&maps[1], A.lo + a_row0 * A.kp, M, A.k, A.kp, BM);
+    if (b_mn) ok = ok && make_panel_map_mn(&maps[2], B.hi, false, N, B.k, B.kp) && make_panel_map_mn(&maps[3], B.lo, true, N, B.k, B.kp);
+    else ok = ok && make_panel_map(&maps[2], B.hi + b_row0 * B.kp, N, B.k, B.kp, b_box) && make_panel_map(&maps[3], B.lo + b_row0 * B.kp, N, B.k, B.kp, b_box);
     if (!ok) return MYEA_E_CUDA;
     ctx.begin(TC_GEMM);
-    if (wide) rc = launch_tcgen05_wide(ctx, maps, dims, epi);
-    else if (pair) rc = launch_tcgen05_pair(ctx, maps, dims, epi);
-    else rc = (bn == 256) ? launch_tcgen05<256, 2>(ctx, maps, dims, epi) : launch_tcgen05<128, 3>(ctx, maps, dims, epi);
+    if (wide) {
+      if (a_mn) rc = b_mn ? launch_tcgen05_wide<true, true>(ctx, maps, dims, epi) : launch_tcgen05_wide<true, false>(ctx, maps, dims, epi);
+      else rc = b_mn ? launch_tcgen05_wide<false, true>(ctx, maps, dims, epi) : launch_tcgen05_wide<false, false>(ctx, maps, dims, epi);
+    } else if (pair) {
+      rc = launch_tcgen05_pair(ctx, maps, dims, epi);
+    } else {
+      rc = (bn == 256) ? launch_tcgen05<256, 2>(ctx, maps, dims, epi) : launch_tcgen05<128, 3>(ctx, maps, dims, epi);
+    }
     ctx.end(TC_GEMM);
   }
   ctx.gemm_flops += 2.0 * dims.M * dims.N * static_cast<double>(dims.K);

@@ -19,7 +19,10 @@ extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N,
   int rc = MYEA_OK;
   float *dA = nullptr, *dB = nullptr, *dC = nullptr, *dS = nullptr;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
-  const size_t scratch = gemm_scratch_floats(M, N, K);
+  // bits 17 / 18: A / B are handed over transposed ([K][M] / [K][N] row-major) and read as MN-major operands
+  const bool a_t = (engine >> 17) & 1, b_t = (engine >> 18) & 1;
+  const size_t a_floats = a_t ? shared_panel_floats(K, M) + 64 : panel_floats(M, K) + 64;
+  const size_t scratch = (a_t || b_t) ? a_floats + (b_t ? shared_panel_floats(K, N) : panel_floats(N, K)) + 128 : gemm_scratch_floats(M, N, K);
   if (cudaStreamCreate(&ctx.stream) != cudaSuccess) return MYEA_E_CUDA;
   if (cudaMalloc(&dA, M * K * 4) != cudaSuccess || cudaMalloc(&dB, N * K * 4) != cudaSuccess ||
       cudaMalloc(&dC, M * N * 4) != cudaSuccess || cudaMalloc(&dS, scratch * 4) != cudaSuccess ||
@@ -41,16 +44,30 @@ extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N,
     epi.ldc = (long long)N;
     epi.accumulate = accumulate;
     GemmScratch gs{dS, scratch};
-    rc = gemm_nt(ctx, oa, ob, epi, gs);  // the call whose result is returned
+    auto run = [&]() -> int {
+      if (!a_t && !b_t) return gemm_nt(ctx, oa, ob, epi, gs);
+      if (!gemm_takes_mn_major(ctx, (long long)M, (long long)N)) return MYEA_E_INVALID;
+      float *base = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(dS) + 255) & ~static_cast<uintptr_t>(255));
+      float *mem_b = base + ((a_floats + 63) & ~static_cast<size_t>(63));
+      Panels pa, pb;
+      int r = a_t ? gemm_prepare_shared(ctx, dA, (long long)M, (long long)K, (long long)M, base, PANEL_ROLE_A, nullptr, PANEL_ROLE_A, &pa)
+                  : gemm_prepare(ctx, oa, base, &pa, PANEL_ROLE_A);
+      if (r != MYEA_OK) return r;
+      r = b_t ? gemm_prepare_shared(ctx, dB, (long long)N, (long long)K, (long long)N, mem_b, PANEL_ROLE_B, nullptr, PANEL_ROLE_B, &pb)
+              : gemm_prepare(ctx, ob, mem_b, &pb, PANEL_ROLE_B);
+      if (r != MYEA_OK) return r;
+      return gemm_panels(ctx, pa, 0, (long long)M, pb, 0, (long long)N, epi);
+    };
+    rc = run();  // the call whose result is returned
     if (rc == MYEA_OK && repeats > 0 && elapsed_ms != nullptr) {
       // timing passes write a second output buffer so that `accumulate` does not pile up in C
       float *dC2 = nullptr;
       if (cudaMalloc(&dC2, M * N * 4) == cudaSuccess) {
         epi.C = dC2;
         epi.accumulate = 0;
-        gemm_nt(ctx, oa, ob, epi, gs);
+        run();
         cudaEventRecord(e0, ctx.stream);
-        for (int i = 0; i < repeats && rc == MYEA_OK; ++i) rc = gemm_nt(ctx, oa, ob, epi, gs);
+        for (int i = 0; i < repeats && rc == MYEA_OK; ++i) rc = run();
         cudaEventRecord(e1, ctx.stream);
         cudaEventSynchronize(e1);
         cudaEventElapsedTime(elapsed_ms, e0, e1);

@@ -239,6 +239,13 @@ static int allocate_buffers(myea_b200_net *net) {
       RC(dev_alloc(net, &L.deriv, rows * wide));
       if (L.has_norm) RC(dev_alloc(net, &L.errors, rows * L.n_out));
       else L.errors = L.deriv;
+      if (!layer_in_block(net, static_cast<int>(l), nullptr) && gemm_takes_mn_major(net->ctx, rows, L.n_out) &&
+          gemm_takes_mn_major(net->ctx, rows, L.n_in) && gemm_takes_mn_major(net->ctx, L.n_out, L.n_in) && net->ctx.gemm_engine == 0) {
+        L.shared_panels = true;
+        RC(dev_alloc(net, &L.in_panel_mem, shared_panel_floats(rows, L.n_in)));
+        RC(dev_alloc(net, &L.w_panel_mem, shared_panel_floats(L.n_out, L.n_in)));
+        RC(dev_alloc(net, &L.d_panel_mem, shared_panel_floats(rows, L.n_out)));
+      }
       scratch = std::max(scratch, gemm_scratch_floats(rows, L.n_out, L.n_in));   // forward
       scratch = std::max(scratch, gemm_scratch_floats(rows, L.n_in, L.n_out));   // backward data
       scratch = std::max(scratch, gemm_scratch_floats(L.n_out, L.n_in, rows));   // backward weight
@@ -392,6 +399,9 @@ extern "C" int myea_b200_upload(myea_handle net, int which, const float *host, u
   CK(cudaSetDevice(net->ctx.device));
   CK(cudaMemcpyAsync(dst + offset, host, count * sizeof(float), cudaMemcpyHostToDevice, net->ctx.stream));
   CK(cudaStreamSynchronize(net->ctx.stream));
+  if (dst == net->params) {
+    for (auto &L : net->layers) L.w_valid = false;  // weight panels of the last forward pass no longer match
+  }
   return MYEA_OK;
 }
 
@@ -449,7 +459,17 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
   e.C = L.summations;
   e.ldc = L.n_out;
   e.bias = L.use_bias ? net->params + L.idx.first_bias_connection_index : nullptr;
-  RC(gemm_nt(net->ctx, a, b, e, net->scratch));
+  if (L.shared_panels) {
+    // while training, the same pass also writes the column readings the backward contractions will want
+    const bool tr = net->training;
+    RC(gemm_prepare_shared(net->ctx, input, L.n_in, rows, L.n_in, L.in_panel_mem, PANEL_ROLE_A, &L.in_rows, PANEL_ROLE_B, tr ? &L.in_cols : nullptr));
+    RC(gemm_prepare_shared(net->ctx, b.ptr, L.n_in, L.n_out, L.n_in, L.w_panel_mem, PANEL_ROLE_B, &L.w_rows, PANEL_ROLE_B, tr ? &L.w_cols : nullptr));
+    L.in_valid = L.w_valid = tr;
+    L.d_valid = false;
+    RC(gemm_panels(net->ctx, L.in_rows, 0, rows, L.w_rows, 0, L.n_out, e));
+  } else {
+    RC(gemm_nt(net->ctx, a, b, e, net->scratch));
+  }
   const float *cs = nullptr, *ch = nullptr;
   if (L.has_norm) {
     RC(norm_forward_stats(net->ctx, L.summations, rows, L.n_out, L.norm, net->training ? 1 : 0, &net->hook));
@@ -584,6 +604,12 @@ int fc_backward_from_fc(myea_b200_net *net, LayerPlan &L, const LayerPlan &next,
     e.ld_aux = L.n_out;
     if (L.has_norm) { e.col_scale = L.norm.col_scale; e.col_shift = L.norm.col_shift; }
   }
+  if (next.shared_panels && next.w_valid && next_errors == next.errors) {
+    LayerPlan &N = const_cast<LayerPlan &>(next);
+    RC(gemm_prepare_shared(net->ctx, N.errors, N.n_out, rows, N.n_out, N.d_panel_mem, PANEL_ROLE_A, &N.d_rows, PANEL_ROLE_A, &N.d_cols));
+    N.d_valid = true;
+    return gemm_panels(net->ctx, N.d_rows, 0, rows, N.w_cols, 0, N.n_in, e);
+  }
   return gemm_nt(net->ctx, a, b, e, net->scratch);
 }
 
@@ -643,7 +669,15 @@ int fc_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float *i
   e.C = net->grads + L.idx.first_connection_index;
   e.ldc = L.n_in;
   e.accumulate = 1;
-  RC(gemm_nt(net->ctx, a, b, e, net->scratch));
+  if (L.shared_panels && L.in_valid && input == net->layers[L.input_layer].values) {
+    if (!L.d_valid) {  // no error propagation below this layer (first hidden layer): only the column reading is needed
+      RC(gemm_prepare_shared(net->ctx, L.errors, L.n_out, rows, L.n_out, L.d_panel_mem, PANEL_ROLE_A, nullptr, PANEL_ROLE_A, &L.d_cols));
+    }
+    RC(gemm_panels(net->ctx, L.d_cols, 0, L.n_out, L.in_cols, 0, L.n_in, e));
+    L.d_valid = false;  // the errors of the next step will differ
+  } else {
+    RC(gemm_nt(net->ctx, a, b, e, net->scratch));
+  }
   if (L.use_bias)
     RC(column_sum(net->ctx, L.errors, rows, L.n_out, net->grads + L.idx.first_bias_connection_index, 1, net->reduce_partial, net->reduce_chunks));
   return MYEA_OK;
@@ -691,6 +725,7 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
     else RC(comm_all_reduce_sum(net, net->grads, P));      // nothing was issued: reduce everything now
     net->grads_reduced = false;
   }
+  for (auto &L : net->layers) L.w_valid = false;  // the weights change below
   OptLaunch o;
   o.type = opt->type_optimizer_function;
   if (opt->use_clip_gradient) {

@@ -35,6 +35,14 @@ struct LayerPlan {
   uint8_t *shake_mask = nullptr;      // [B]
   float *shake_alpha = nullptr, *shake_beta = nullptr;  // [B, n_out]
   long long norm_unit_offset = 0;     // units of earlier layers in the normalized-unit run
+  // Operand panels shared by the three contractions of a large fully connected layer (all on the 256 x 256 kernel):
+  // one split pass per tensor and step serves both of its readings.  input: forward (rows, role A) and dW (columns,
+  // role B); weights: forward (rows, role B) and error propagation (columns, role B); errors: error propagation
+  // (rows, role A) and dW (columns, role A).
+  bool shared_panels = false;
+  float *in_panel_mem = nullptr, *w_panel_mem = nullptr, *d_panel_mem = nullptr;
+  Panels in_rows, in_cols, w_rows, w_cols, d_rows, d_cols;
+  bool in_valid = false, w_valid = false, d_valid = false;
 };
 
 }  // namespace myea
