@@ -212,8 +212,12 @@ void *myea_b200_stream(myea_handle h);
 uint64_t myea_b200_kernel_launches(myea_handle h);
 
 /* Stand-alone dense contraction used by the step, exposed for kernel-level tests and roofline timing:
- * C[M,N] (+)= A[M,K] · B[N,K]^T, fp32 in HOST memory, computed on tcgen05 with 3xTF32 split precision
- * (engine 0) or with the FP32 FMA kernel (engine 1). Replaces the triple loops
+ * C[M,N] (+)= A[M,K] · B[N,K]^T, fp32 in HOST memory, computed on tcgen05 with split precision (TF32 main
+ * product + bf16 cross terms; bit 0 of `engine` clear) or with the FP32 FMA kernel (bit 0 set).  Bits 8..16 of
+ * `engine` force a tile shape (0 heuristic, 128 single CTA, 2 CTA pair 256x128, 3 CTA pair 256x256, 4 the same
+ * without splitting tiles along K); bit 17 / bit 18: A / B is handed over transposed, [K][M] / [K][N] row-major,
+ * and read as it lies (256x256 kernel only).  `elapsed_ms` (may be null) receives the mean device time of `repeats`
+ * extra runs.  Replaces the triple loops
  * Forward_Pass__FC / Backward_Pass__FC / Update_Derivative_Weight__FC
  * (Neural_Network__Forward_Pass__OpenMP.cpp:4517, …Backward_Pass__OpenMP.cpp:1044, …Update_Derivative_Weight__OpenMP.cpp:178). */
 int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N, uint64_t K, const float *A, const float *B,

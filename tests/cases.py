@@ -22,6 +22,10 @@ CASES = {
     "mlp_brn_elu_adabound_wd": lambda: _mlp_variant("brn", [28, 28], capi.AF_ELU, capi.opt(capi.OPT_ADABOUND, weight_decay=1e-3), norm=capi.NORM_BRN,
                                                     r_max=3.0, d_max=5.0, momentum=0.9),
     "mlp_bernoulli_amsbound_clip": lambda: _mlp_variant("amsbound", [32], capi.AF_LEAKY_RELU, capi.opt(capi.OPT_AMSBOUND, clip=0.5), drop=capi.DROP_BERNOULLI),
+    # every width and the batch above 128 (and ragged): the three contractions of each layer run on the 256 x 256
+    # tensor-core kernel from operand panels shared between the forward and the backward readings
+    "mlp_wide_bn_dropout_adam": lambda: _mlp_variant("wide", [144, 132], capi.AF_RELU, capi.opt(capi.OPT_ADAM), B=130, n_in=136, n_out=129,
+                                                     norm=capi.NORM_BN, drop=capi.DROP_BERNOULLI_INVERTED, p=0.5),
     "mlp_relu_gd": lambda: _mlp_variant("gd", [16, 16], capi.AF_RELU, capi.opt(capi.OPT_GD, gd_lr=0.01)),
     "mlp_selu_momentum": lambda: _mlp_variant("mom", [16], capi.AF_SELU, capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9)),
     "mlp_tanh_nesterov_ce": lambda: _mlp_variant("nag", [16], capi.AF_TANH, capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9, nesterov=True),
