@@ -27,6 +27,7 @@
 //
 // The FP32 FMA kernel at the end of the file is the second engine (exact fp32 products; selectable for debugging).
 #include "common.cuh"
+#include "panel_math.cuh"
 
 #include <cudaTypedefs.h>
 #include <cuda_bf16.h>
@@ -222,6 +223,8 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parit
 // Optional phase timeline of CTA (0,0) (a profiling build only: -DMYEA_GEMM_TIMELINE); compiles to nothing otherwise.
 #ifdef MYEA_GEMM_TIMELINE
 __device__ long long g_timeline[32];
+__device__ long long g_cluster_times[2][128];  // globaltimer at entry / exit of every cluster's leader thread
+#define TL_CLUSTER(which, id) do { unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt)); g_cluster_times[which][(id) & 127] = (long long)gt; } while (0)
 #define TL_ON (blockIdx.x == 0 && blockIdx.y == 0)
 #define TL(slot) do { if (TL_ON) g_timeline[slot] = clock64(); } while (0)
 #define TL_DECL(name) long long name = 0
@@ -231,6 +234,7 @@ __device__ long long g_timeline[32];
 #define TL_GLOBAL(slot) do { if (TL_ON) { unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt)); g_timeline[slot] = (long long)gt; } } while (0)
 #else
 #define TL(slot)
+#define TL_CLUSTER(which, id)
 #define TL_DECL(name)
 #define TL_BEGIN(name)
 #define TL_END(name)
@@ -381,6 +385,22 @@ __device__ __forceinline__ void epilogue_row32_vec(const Epilogue &e, const floa
 __device__ __forceinline__ void epilogue_row32(const Epilogue &e, const float (&v)[32], long long m, long long col0, int M, int N,
                                                bool vec_ok, int mode) {
   if (m >= M || col0 >= N) return;
+  if (e.lstm.kind == 1) {  // 32 columns = 8 cells x 4 gates
+    lstm_forward_cells8(e.lstm, v, m, col0 >> 2);
+    return;
+  }
+  if (e.lstm.kind == 2) {  // 32 columns = 32 cells (N = C is a multiple of 8)
+#pragma unroll
+    for (int g8 = 0; g8 < 4; ++g8) {
+      if (col0 + g8 * 8 < N) {
+        float r8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r8[j] = v[g8 * 8 + j];
+        lstm_backward_cells8(e.lstm, r8, m, col0 + g8 * 8);
+      }
+    }
+    return;
+  }
   if (vec_ok && col0 + 32 <= N) {
     switch (mode) {
       case 0: epilogue_row32_vec<false, false, false>(e, v, m, col0); break;
@@ -837,6 +857,7 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
   const int num_kb = (dims.K + BK - 1) / BK;
   const int num_chunks = (num_kb + WIDE_KC - 1) / WIDE_KC;
   if (threadIdx.x == 0) { TL(0); TL_GLOBAL(16); }
+  if (threadIdx.x == 0 && cta_rank == 0) TL_CLUSTER(0, cluster_id);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -1009,21 +1030,18 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
         if (finish) {
           if (lane == 0) *counter = 0u;  // every contributor has arrived: ready for the next launch
           __threadfence();
-          // two contributors (the usual case): a + b is the same whichever of them is last, so the sum in registers
-          // stays and only the other slot is read; more than two are added from zero in cluster order
-          const bool pairwise = last == first + 1;
-          const int skip = pairwise ? cluster_id : -1;
-          if (!pairwise) {
+          int tm, tn;
+          wide_tile_coords(work, seg.tile, tm, tn);
+          const long long m = static_cast<long long>(tm) * 256 + static_cast<long long>(cta_rank) * 128 + q * 32 + lane;
+          const long long col_base = static_cast<long long>(tn) * BN + half * 128;
+          if (last == first + 1) {
+            // two contributors (the usual case): a + b is the same whichever of them is last, so the sum in registers
+            // stays and only the other slot is read
+            const int other = cluster_id == first ? last : first;
+            const int slot = (other * work.sk_chunks >= tile_u0) ? 0 : 1;
+            const float4 *theirs = reinterpret_cast<const float4 *>(work.ws + (static_cast<size_t>(other * 2 + slot) * 16 + region) * WIDE_REGION_FLOATS);
 #pragma unroll
-            for (int j = 0; j < 128; ++j) sum[j] = 0.f;
-          }
-          // eight float4 loads in flight per lane; the order of the additions into one element is the cluster order
-#pragma unroll
-          for (int jb = 0; jb < 32; jb += 8) {
-            for (int cc = first; cc <= last; ++cc) {
-              if (cc == skip) continue;
-              const int slot = (cc * work.sk_chunks >= tile_u0) ? 0 : 1;
-              const float4 *theirs = reinterpret_cast<const float4 *>(work.ws + (static_cast<size_t>(cc * 2 + slot) * 16 + region) * WIDE_REGION_FLOATS);
+            for (int jb = 0; jb < 32; jb += 8) {
               float4 v[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[j] = __ldcg(theirs + (jb + j) * 32 + lane);
@@ -1032,6 +1050,37 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
                 sum[4 * (jb + j)] += v[j].x; sum[4 * (jb + j) + 1] += v[j].y; sum[4 * (jb + j) + 2] += v[j].z; sum[4 * (jb + j) + 3] += v[j].w;
               }
             }
+          } else {
+            // more than two: every slot is added from zero in cluster order, 32 columns at a time with the loads of
+            // four contributors in flight, and each 32 columns go straight to the epilogue
+#pragma unroll 1
+            for (int jc = 0; jc < 4; ++jc) {
+              float acc[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+              for (int c4 = first; c4 <= last; c4 += 4) {
+                float4 v[4][8];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  const int cc = min(c4 + u, last);
+                  const int slot = (cc * work.sk_chunks >= tile_u0) ? 0 : 1;
+                  const float4 *theirs = reinterpret_cast<const float4 *>(work.ws + (static_cast<size_t>(cc * 2 + slot) * 16 + region) * WIDE_REGION_FLOATS);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[u][j] = __ldcg(theirs + (jc * 8 + j) * 32 + lane);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  if (c4 + u <= last) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                      acc[4 * j] += v[u][j].x; acc[4 * j + 1] += v[u][j].y; acc[4 * j + 2] += v[u][j].z; acc[4 * j + 3] += v[u][j].w;
+                    }
+                  }
+                }
+              }
+              epilogue_row32(epi, acc, m, col_base + jc * 32, dims.M, dims.N, vec_ok, mode);
+            }
+            finish = false;  // already written
           }
         }
       }
@@ -1057,6 +1106,7 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
   __syncthreads();
   ptx::cluster_sync_all();
   if (threadIdx.x == 0) { TL(8); TL_GLOBAL(17); }
+  if (threadIdx.x == 0 && cta_rank == 0) TL_CLUSTER(1, cluster_id);
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
@@ -1074,30 +1124,6 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
 // footprint as 8 fp32):  operand A: [lo x8 | hi x8],  operand B: [hi x8 | lo x8],  so that the K = 16 dot product of
 // an A group with a B group is sum lo_a*hi_b + sum hi_a*lo_b.
 // `raw` panels (FP32 FMA engine): hi = x unrounded, cross = 0.
-__device__ __forceinline__ float round_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
-}
-__device__ __forceinline__ uint32_t bf16_bits(float x) { return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(x))); }
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) { return bf16_bits(a) | (bf16_bits(b) << 16); }
-
-// one group of 8 K elements -> 8 hi floats and the 8 words of the cross group
-__device__ __forceinline__ void split_group(const float (&v)[8], int role_b, int raw, float (&hi)[8], uint32_t (&cross)[8]) {
-  float lo[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    hi[j] = raw ? v[j] : round_tf32(v[j]);
-    lo[j] = v[j] - hi[j];
-  }
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint32_t l = raw ? 0u : pack_bf16(lo[2 * j], lo[2 * j + 1]);
-    const uint32_t h = raw ? 0u : pack_bf16(hi[2 * j], hi[2 * j + 1]);
-    cross[j] = role_b ? h : l;
-    cross[4 + j] = role_b ? l : h;
-  }
-}
 
 // source already K-major (stride_k == 1); writes columns [0, round_up(k, 8)) of every panel row (pitch kp)
 // With cross_mn != null the same pass also writes the cross panel of the source's OTHER reading, the one whose K runs
@@ -1346,6 +1372,21 @@ int gemm_prepare_into(Context &ctx, const Operand &op, const Panels &dst, long l
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
+int gemm_prepare_interleaved(Context &ctx, const Operand &op, const Panels &dst, long long row_offset, long long row_step) {
+  if (op.rows <= 0 || op.k != dst.k || op.stride_k != 1 || row_step < 1 || row_offset + (op.rows - 1) * row_step >= dst.rows || dst.major != PANEL_K)
+    return MYEA_E_INVALID;
+  const int raw = ctx.gemm_engine == 1 ? 1 : 0;
+  const long long total = op.rows * ((op.k + 7) >> 3);
+  int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
+  if (blocks < 1) blocks = 1;
+  ctx.begin(TC_SPLIT);
+  // the kernel only sees a wider pitch: source row r lands on panel row row_offset + r * row_step
+  split_rows_kernel<<<blocks, 256, 0, ctx.stream>>>(op.ptr, op.stride_r, op.rows, op.k, dst.kp * row_step, dst.hi + row_offset * dst.kp,
+                                                    dst.lo + row_offset * dst.kp, dst.role, raw);
+  ctx.end(TC_SPLIT);
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
 int gemm_prepare(Context &ctx, const Operand &op, float *mem, Panels *out, int role) {
   *out = panels_at(mem, op.rows, op.k, role);
   return gemm_prepare_into(ctx, op, *out, 0, 0);
@@ -1547,5 +1588,8 @@ int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &ep
 #ifdef MYEA_GEMM_TIMELINE
 extern "C" int myea_b200_gemm_timeline(long long *out32) {
   return cudaMemcpyFromSymbol(out32, myea::g_timeline, sizeof(long long) * 32) == cudaSuccess ? 0 : 1;
+}
+extern "C" int myea_b200_gemm_cluster_times(long long *out256) {
+  return cudaMemcpyFromSymbol(out256, myea::g_cluster_times, sizeof(long long) * 256) == cudaSuccess ? 0 : 1;
 }
 #endif

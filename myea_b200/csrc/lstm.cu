@@ -20,6 +20,7 @@
 // BPTT step is one [B, 4C] x [4C, C] contraction accumulated into the output error plus one fused cell-backward kernel,
 // and the weight derivatives are contractions over K = T*B.  Bias and peephole derivatives are column reductions.
 #include "net.cuh"
+#include "panel_math.cuh"
 
 #include <algorithm>
 
@@ -45,6 +46,17 @@ struct LstmPlan {
   float *panel_mem = nullptr;  // W_rec panels, their transpose, per-step operand panels
   size_t off_wrec = 0, off_wrect = 0, off_step = 0;
   float *partial = nullptr;    // [7][chunks][C]
+  // cell fused into the recurrent contraction (C a multiple of 8, tensor-core engine): compact peepholes
+  // [dirs][3][C], ping-pong operand panels of h (forward) and of the gate errors (backward)
+  bool fuse = false;
+  // With `fuse`, a step is two kernels: the contraction and an 8-cells-per-thread cell kernel that also writes the next
+  // operand panels.  fuse_mask (MYEA_B200_LSTM_FUSE) moves the cell into the contraction's epilogue instead: bit 0
+  // forward, bit 1 backward.  One kernel per step, but measured slower on C3 (the few threads that own accumulator
+  // rows walk their cells one memory round trip after the other), so it is off by default.
+  int fuse_mask = 0;
+  float *peep_compact = nullptr;
+  float *h_panels[2] = {nullptr, nullptr};
+  float *dg_panels[2] = {nullptr, nullptr};
 };
 
 // offsets of the gate matrices inside one block of the parameter buffer (Prepare__Connections__LSTM)
@@ -64,8 +76,6 @@ static BlockOffsets block_offsets(long long n_in, long long C) {
 // ---------------------------------------------------------------------------------------------------------
 // fused cell kernels
 // ---------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + expf(-x)); }
-__device__ __forceinline__ float tanh_ref(float x) { return 2.0f / (1.0f + expf(-2.0f * x)) - 1.0f; }
 
 struct CellFwd {
   const float *gates_in;  // rows of step t: [B, 4C]
@@ -214,6 +224,42 @@ __global__ void lstm_bias_peephole_finalize_kernel(const float *__restrict__ par
   d_peep[c * stride + 2] += t[6];
 }
 
+// Cell kernels of the steps that have a predecessor / successor, 8 consecutive cells of one batch row per thread: the
+// arithmetic of lstm_cell_forward_kernel / lstm_cell_backward_kernel, and the results also leave as the operand panels
+// of the next step's contraction (no separate split pass).  p.kind selects; s_rec / rec_dh is the contraction's output.
+__global__ void __launch_bounds__(256) lstm_cells8_forward_kernel(const LstmFuse p, const float *__restrict__ s_rec, long long B) {
+  const long long groups = p.C >> 3, total = B * groups;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long b = i / groups, c0 = (i - b * groups) << 3;
+    float gz[8], gi[8], gf[8], go[8], rec[32];
+    const float *r = s_rec + b * 4 * p.C + c0;
+    load8(gz, r); load8(gi, r + p.C); load8(gf, r + 2 * p.C); load8(go, r + 3 * p.C);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { rec[4 * k] = gz[k]; rec[4 * k + 1] = gi[k]; rec[4 * k + 2] = gf[k]; rec[4 * k + 3] = go[k]; }
+    lstm_forward_cells8(p, rec, b, c0);
+  }
+}
+// the error through time has already been added into p.dh by the contraction (accumulate epilogue): rec = 0
+__global__ void __launch_bounds__(256) lstm_cells8_backward_kernel(const LstmFuse p, long long B) {
+  const long long groups = p.C >> 3, total = B * groups;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long b = i / groups, c0 = (i - b * groups) << 3;
+    const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    lstm_backward_cells8(p, zero, b, c0);
+  }
+}
+
+// peepholes p_i, p_f, p_o of every cell, gathered from the blocks of the parameter buffer into [3][C]
+__global__ void lstm_gather_peepholes_kernel(const float *__restrict__ peep, long long stride, long long C, float *__restrict__ out) {
+  const long long c = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (c >= C) return;
+  out[c] = peep[c * stride];
+  out[C + c] = peep[c * stride + 1];
+  out[2 * C + c] = peep[c * stride + 2];
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // plan
 // ---------------------------------------------------------------------------------------------------------
@@ -277,6 +323,15 @@ int lstm_create(myea_b200_net *net, LayerPlan &L) {
   P->off_step = P->off_wrect + panel_floats(C, 4 * Cp) + 64;
   LRC(lalloc(net, &P->panel_mem, P->off_step + panel_floats(net->B, 4 * Cp) + 64));
   LRC(lalloc(net, &P->partial, static_cast<size_t>(7) * net->reduce_chunks * C));
+  P->fuse = (C % 8 == 0) && net->ctx.gemm_engine == 0;
+  if (const char *fm = getenv("MYEA_B200_LSTM_FUSE")) P->fuse_mask = atoi(fm);
+  if (P->fuse) {
+    LRC(lalloc(net, &P->peep_compact, static_cast<size_t>(P->dirs) * 3 * C));
+    for (int i = 0; i < 2; ++i) {
+      LRC(lalloc(net, &P->h_panels[i], panel_floats(net->B, C) + 64));
+      LRC(lalloc(net, &P->dg_panels[i], panel_floats(net->B, 4 * Cp) + 64));
+    }
+  }
   // one-shot contractions use the handle's scratch: make sure it is large enough
   size_t need = 0;
   need = std::max(need, panel_floats(rows, L.n_in) + panel_floats(4 * C, L.n_in));            // input projection
@@ -350,13 +405,60 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
     LRC(gemm_panels(ctx, px, 0, rows, pwin, 0, 4 * C, e));
     // fused recurrent panel [4C, C]
     Panels pwrec = panels_at(P->panel_mem + P->off_wrec, 4 * C, C, PANEL_ROLE_B);
-    LRC(gemm_prepare_into(ctx, Operand{w + off.z_rec, C, C, P->stride, 1}, pwrec, 0, 0));
-    for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.rec[g], C, C, P->stride, 1}, pwrec, (g + 1) * C, 0));
+    float *peep_c = nullptr;
+    if (P->fuse) {
+      peep_c = P->peep_compact + static_cast<size_t>(d) * 3 * C;
+      ctx.begin(TC_RECURRENT);
+      lstm_gather_peepholes_kernel<<<static_cast<unsigned>((C + 255) / 256), 256, 0, ctx.stream>>>(w + off.peep, P->stride, C, peep_c);
+      ctx.end(TC_RECURRENT);
+    }
+    if (P->fuse && (P->fuse_mask & 1)) {
+      // rows interleaved cell by cell (row 4 * cell + gate): one output row of the contraction then holds the four
+      // gate sums of a cell side by side and the cell can be finished in the epilogue
+      LRC(gemm_prepare_interleaved(ctx, Operand{w + off.z_rec, C, C, P->stride, 1}, pwrec, 0, 4));
+      for (int g = 0; g < 3; ++g) LRC(gemm_prepare_interleaved(ctx, Operand{w + off.rec[g], C, C, P->stride, 1}, pwrec, g + 1, 4));
+    } else {
+      LRC(gemm_prepare_into(ctx, Operand{w + off.z_rec, C, C, P->stride, 1}, pwrec, 0, 0));
+      for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.rec[g], C, C, P->stride, 1}, pwrec, (g + 1) * C, 0));
+    }
     const bool zone = P->zoneout && net->training;
     for (long long s = 0; s < T; ++s) {
       const long long t = d == 0 ? s : T - 1 - s;
       const long long tp = d == 0 ? t - 1 : t + 1;
       float *h_t = L.values + t * B * ldh + d * C;
+      if (P->fuse && s > 0) {
+        // recurrent contraction on the panels the previous step left, then the cell (in the contraction's epilogue or
+        // as a kernel of its own); h_t leaves as the layer output and as the operand panels of step s + 1
+        const Panels ph_prev = panels_at(P->h_panels[(s - 1) & 1], B, C, PANEL_ROLE_A);
+        const Panels ph_next = panels_at(P->h_panels[s & 1], B, C, PANEL_ROLE_A);
+        Epilogue e;
+        LstmFuse f;
+        f.kind = 1;
+        f.C = C; f.ldh = ldh; f.kp = ph_next.kp;
+        f.peep = peep_c;
+        if (s + 1 < T) { f.p_hi = ph_next.hi; f.p_cross = ph_next.lo; }
+        f.gates_in = D.gates_in + t * B * 4 * C;
+        f.c_prev = D.cstate + tp * B * C;
+        f.h_prev = L.values + tp * B * ldh + d * C;
+        f.act = D.act + t * B * 4 * C;
+        f.cstate = D.cstate + t * B * C;
+        f.cact = D.cact + t * B * C;
+        f.h = h_t;
+        f.zone_state = zone ? D.zone_state + t * C : nullptr;
+        f.zone_output = zone ? D.zone_output + t * C : nullptr;
+        if (P->fuse_mask & 1) {
+          e.lstm = f;
+          LRC(gemm_panels(ctx, ph_prev, 0, B, pwrec, 0, 4 * C, e));
+        } else {
+          e.C = P->s_rec;
+          e.ldc = 4 * C;
+          LRC(gemm_panels(ctx, ph_prev, 0, B, pwrec, 0, 4 * C, e));
+          ctx.begin(TC_RECURRENT);
+          lstm_cells8_forward_kernel<<<cell_blocks(B * C / 8), 256, 0, ctx.stream>>>(f, P->s_rec, B);
+          ctx.end(TC_RECURRENT);
+        }
+        continue;
+      }
       CellFwd cf;
       cf.gates_in = D.gates_in + t * B * 4 * C;
       cf.s_rec = nullptr; cf.c_prev = nullptr; cf.h_prev = nullptr;
@@ -385,6 +487,10 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
       ctx.begin(TC_RECURRENT);
       lstm_cell_forward_kernel<<<cell_blocks(B * C), 256, 0, ctx.stream>>>(cf);
       ctx.end(TC_RECURRENT);
+      if (P->fuse && T > 1) {  // first step: its output becomes the operand of the second step
+        Panels ph0;
+        LRC(gemm_prepare(ctx, Operand{h_t, B, C, ldh, 1}, P->h_panels[0], &ph0, PANEL_ROLE_A));
+      }
     }
   }
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
@@ -411,6 +517,40 @@ int lstm_backward(myea_b200_net *net, LayerPlan &L) {
       const long long tn = d == 0 ? t + 1 : t - 1;     // the step after t in the layer's direction
       const long long tp = d == 0 ? t - 1 : t + 1;     // the step before t
       float *dh_t = L.deriv + t * B * ldh + d * C;
+      if (P->fuse && s > 0) {
+        // error through time (gate errors of the next step times W_rec) on the panels the previous step left, then the
+        // cell's backward arithmetic; the gate errors of step t leave as arrays and as the next operand panels
+        const Panels pd_prev = panels_at(P->dg_panels[(s - 1) & 1], B, 4 * Cp, PANEL_ROLE_A);
+        const Panels pd_next = panels_at(P->dg_panels[s & 1], B, 4 * Cp, PANEL_ROLE_A);
+        Epilogue e;
+        LstmFuse f;
+        f.kind = 2;
+        f.C = C; f.ldh = ldh; f.kp = pd_next.kp; f.Cp = Cp;
+        f.peep = P->peep_compact + static_cast<size_t>(d) * 3 * C;
+        if (s + 1 < T) { f.p_hi = pd_next.hi; f.p_cross = pd_next.lo; }
+        f.dh = dh_t;
+        f.b_act = D.act + t * B * 4 * C;
+        f.b_cact = D.cact + t * B * C;
+        f.b_c_prev = (tp >= 0 && tp < T) ? D.cstate + tp * B * C : nullptr;
+        f.act_next = D.act + tn * B * 4 * C;
+        f.dgates_next = D.dgates + tn * B * 4 * C;
+        f.dc_next = D.dcstate + tn * B * C;
+        f.dgates = D.dgates + t * B * 4 * C;
+        f.dcstate = D.dcstate + t * B * C;
+        if (P->fuse_mask & 2) {
+          e.lstm = f;
+          LRC(gemm_panels(ctx, pd_prev, 0, B, pwt, 0, C, e));
+        } else {
+          e.C = dh_t;
+          e.ldc = ldh;
+          e.accumulate = 1;
+          LRC(gemm_panels(ctx, pd_prev, 0, B, pwt, 0, C, e));
+          ctx.begin(TC_RECURRENT);
+          lstm_cells8_backward_kernel<<<cell_blocks(B * C / 8), 256, 0, ctx.stream>>>(f, B);
+          ctx.end(TC_RECURRENT);
+        }
+        continue;
+      }
       if (s > 0) {
         Panels pd = panels_at(P->panel_mem + P->off_step, B, 4 * Cp, PANEL_ROLE_A);
         LRC(prepare_gates(ctx, D.dgates + tn * B * 4 * C, B, C, Cp, pd));
@@ -437,6 +577,10 @@ int lstm_backward(myea_b200_net *net, LayerPlan &L) {
       ctx.begin(TC_RECURRENT);
       lstm_cell_backward_kernel<<<cell_blocks(B * C), 256, 0, ctx.stream>>>(cb);
       ctx.end(TC_RECURRENT);
+      if (P->fuse && T > 1) {  // last time step (first of the walk): its gate errors are the operand of the next contraction
+        const Panels pd0 = panels_at(P->dg_panels[0], B, 4 * Cp, PANEL_ROLE_A);
+        LRC(prepare_gates(ctx, D.dgates + t * B * 4 * C, B, C, Cp, pd0));
+      }
     }
   }
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;

@@ -1,0 +1,133 @@
+// Device helpers shared by the contraction kernels and the LSTM cell kernels: the fp32 -> (TF32 hi, bf16 cross) split
+// of 8 consecutive K elements and the arithmetic of one LSTM cell step for 8 consecutive cells of one batch row.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace myea {
+
+__device__ __forceinline__ float round_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+__device__ __forceinline__ uint32_t bf16_bits(float x) { return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(x))); }
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) { return bf16_bits(a) | (bf16_bits(b) << 16); }
+
+// one group of 8 K elements -> 8 hi floats and the 8 words of the cross group
+__device__ __forceinline__ void split_group(const float (&v)[8], int role_b, int raw, float (&hi)[8], uint32_t (&cross)[8]) {
+  float lo[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    hi[j] = raw ? v[j] : round_tf32(v[j]);
+    lo[j] = v[j] - hi[j];
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t l = raw ? 0u : pack_bf16(lo[2 * j], lo[2 * j + 1]);
+    const uint32_t h = raw ? 0u : pack_bf16(hi[2 * j], hi[2 * j + 1]);
+    cross[j] = role_b ? h : l;
+    cross[4 + j] = role_b ? l : h;
+  }
+}
+
+__device__ __forceinline__ void load8(float (&d)[8], const float *p) {
+  const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+  d[0] = a.x; d[1] = a.y; d[2] = a.z; d[3] = a.w; d[4] = b.x; d[5] = b.y; d[6] = b.z; d[7] = b.w;
+}
+__device__ __forceinline__ void store8(float *p, const float (&d)[8]) {
+  *reinterpret_cast<float4 *>(p) = make_float4(d[0], d[1], d[2], d[3]);
+  *reinterpret_cast<float4 *>(p + 4) = make_float4(d[4], d[5], d[6], d[7]);
+}
+// 8 consecutive K elements of one operand row written as panels (role A)
+__device__ __forceinline__ void store_panel_group(float *hi_row, float *cross_row, const float (&v)[8]) {
+  float h[8];
+  uint32_t x[8];
+  split_group(v, 0, 0, h, x);
+  store8(hi_row, h);
+  *reinterpret_cast<uint4 *>(cross_row) = make_uint4(x[0], x[1], x[2], x[3]);
+  *reinterpret_cast<uint4 *>(cross_row + 4) = make_uint4(x[4], x[5], x[6], x[7]);
+}
+
+// LSTM forward cell for batch row b, cells [c0, c0 + 8): rec[4 * i + g] is the recurrent sum of gate g of cell c0 + i.
+// Same arithmetic, in the same order, as lstm_cell_forward_kernel (lstm.cu) on a step that has a predecessor.
+__device__ __forceinline__ void lstm_forward_cells8(const LstmFuse &p, const float (&rec)[32], long long b, long long c0) {
+  const long long C = p.C;
+  float gz[8], gi[8], gf[8], go[8], cp[8], pi[8], pf[8], po[8], hp[8];
+  const float *g = p.gates_in + b * 4 * C + c0;
+  load8(gz, g); load8(gi, g + C); load8(gf, g + 2 * C); load8(go, g + 3 * C);
+  load8(cp, p.c_prev + b * C + c0);
+  load8(pi, p.peep + c0); load8(pf, p.peep + C + c0); load8(po, p.peep + 2 * C + c0);
+  const unsigned long long zs = p.zone_state != nullptr ? *reinterpret_cast<const unsigned long long *>(p.zone_state + c0) : ~0ull;
+  const unsigned long long zo = p.zone_output != nullptr ? *reinterpret_cast<const unsigned long long *>(p.zone_output + c0) : ~0ull;
+  if (p.zone_output != nullptr) load8(hp, p.h_prev + b * p.ldh + c0);
+  float z[8], ig[8], fg[8], og[8], cs[8], a[8], h[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    z[i] = tanh_ref(gz[i] + rec[4 * i]);
+    ig[i] = sigmoid_ref(gi[i] + (rec[4 * i + 1] + pi[i] * cp[i]));
+    fg[i] = sigmoid_ref(gf[i] + rec[4 * i + 2] + pf[i] * cp[i]);
+    float c = z[i] * ig[i];
+    c += fg[i] * cp[i];
+    if (((zs >> (8 * i)) & 0xFFull) == 0ull) c = cp[i];
+    cs[i] = c;
+    a[i] = tanh_ref(c);
+    og[i] = sigmoid_ref(go[i] + rec[4 * i + 3] + po[i] * c);
+    float hh = a[i] * og[i];
+    if (((zo >> (8 * i)) & 0xFFull) == 0ull) hh = hp[i];
+    h[i] = hh;
+  }
+  float *act = p.act + b * 4 * C + c0;
+  store8(act, z); store8(act + C, ig); store8(act + 2 * C, fg); store8(act + 3 * C, og);
+  store8(p.cstate + b * C + c0, cs);
+  store8(p.cact + b * C + c0, a);
+  store8(p.h + b * p.ldh + c0, h);
+  if (p.p_hi != nullptr) store_panel_group(p.p_hi + b * p.kp + c0, p.p_cross + b * p.kp + c0, h);
+}
+
+// LSTM backward cell for batch row b, cells [c0, c0 + 8): rec[i] is the error arriving on h of cell c0 + i through time.
+// Same arithmetic as lstm_cell_backward_kernel on a step that has a successor.
+__device__ __forceinline__ void lstm_backward_cells8(const LstmFuse &p, const float (&rec)[8], long long b, long long c0) {
+  const long long C = p.C;
+  float dh[8], z[8], ig[8], fg[8], og[8], a[8], pi[8], pf[8], po[8], cp[8], dni[8], dnf[8], dcn[8], fn[8];
+  load8(dh, p.dh + b * p.ldh + c0);
+  const float *act = p.b_act + b * 4 * C + c0;
+  load8(z, act); load8(ig, act + C); load8(fg, act + 2 * C); load8(og, act + 3 * C);
+  load8(a, p.b_cact + b * C + c0);
+  load8(pi, p.peep + c0); load8(pf, p.peep + C + c0); load8(po, p.peep + 2 * C + c0);
+  if (p.b_c_prev != nullptr) load8(cp, p.b_c_prev + b * C + c0);
+  const float *dn = p.dgates_next + b * 4 * C + c0;
+  load8(dni, dn + C); load8(dnf, dn + 2 * C);
+  load8(dcn, p.dc_next + b * C + c0);
+  load8(fn, p.act_next + b * 4 * C + 2 * C + c0);
+  float dz[8], di[8], df[8], d_o[8], dc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    dh[i] += rec[i];
+    d_o[i] = og[i] * (1.f - og[i]) * (dh[i] * a[i]);
+    float d = dh[i] * og[i] * (1.f - a[i] * a[i]);
+    d += po[i] * d_o[i];
+    d += pi[i] * dni[i];
+    d += pf[i] * dnf[i];
+    d += dcn[i] * fn[i];
+    dc[i] = d;
+    dz[i] = d * ig[i] * (1.f - z[i] * z[i]);
+    di[i] = (d * z[i]) * (ig[i] * (1.f - ig[i]));
+    df[i] = p.b_c_prev != nullptr ? (d * cp[i]) * (fg[i] * (1.f - fg[i])) : 0.f;
+  }
+  store8(p.dh + b * p.ldh + c0, dh);
+  float *dg = p.dgates + b * 4 * C + c0;
+  store8(dg, dz); store8(dg + C, di); store8(dg + 2 * C, df); store8(dg + 3 * C, d_o);
+  store8(p.dcstate + b * C + c0, dc);
+  if (p.p_hi != nullptr) {
+    float *hi = p.p_hi + b * p.kp + c0, *cr = p.p_cross + b * p.kp + c0;
+    store_panel_group(hi, cr, dz);
+    store_panel_group(hi + p.Cp, cr + p.Cp, di);
+    store_panel_group(hi + 2 * p.Cp, cr + 2 * p.Cp, df);
+    store_panel_group(hi + 3 * p.Cp, cr + 3 * p.Cp, d_o);
+  }
+}
+
+}  // namespace myea
