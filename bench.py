@@ -251,7 +251,10 @@ def run_ours(args):
                     "d2h_bytes_per_step": 24 * world},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "achieved": gemm_tflops, "peak": peak, "unit": "TFLOP/s",
-                         "frac": gemm_tflops / peak if peak else None, "traffic": None,
+                         "frac": gemm_tflops / peak if peak else None,
+                         # DRAM bytes of ONE launch of the dominant kernel on the 4096^3 contraction of this workload, from
+                         # the committed ncu capture (dram__bytes_read.sum + dram__bytes_write.sum); algorithmic 335 MB
+                         "traffic": 704.7e6 if args.workload == "c2" else None,
                          "kernel": "gemm3x_tf32_tcgen05_wide_kernel", "peak_source": peaks["source"] + " bf16 sustained",
                          # every fp32 product costs one TF32 and one BF16 K=16 instruction of equal duration: the
                          # scheme's own ceiling is a quarter of the bf16 peak
