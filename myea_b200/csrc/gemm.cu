@@ -1521,13 +1521,16 @@ int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, co
   if (A.k != B.k || M <= 0 || N <= 0 || A.k <= 0 || a_row0 < 0 || b_row0 < 0 || a_row0 + M > A.rows || b_row0 + N > B.rows) return MYEA_E_INVALID;
   if (A.role != PANEL_ROLE_A || B.role != PANEL_ROLE_B) return MYEA_E_INVALID;  // the cross panels of the two sides differ
   const bool a_mn = A.major == PANEL_MN, b_mn = B.major == PANEL_MN;
-  if ((a_mn && (a_row0 != 0 || (A.kp & 63) != 0)) || (b_mn && (b_row0 != 0 || (B.kp & 63) != 0))) return MYEA_E_INVALID;
+  // a row range of an MN-major operand starts on a multiple of 8 (16-byte TMA base) and its last 128-byte chunk must
+  // stay inside the pitch
+  if (a_mn && ((a_row0 & 7) != 0 || (A.kp & 63) != 0 || a_row0 + ((M + 63) & ~63ll) > A.kp)) return MYEA_E_INVALID;
+  if (b_mn && ((b_row0 & 7) != 0 || (B.kp & 63) != 0 || b_row0 + ((N + 63) & ~63ll) > B.kp)) return MYEA_E_INVALID;
   GemmDims dims{static_cast<int>(M), static_cast<int>(N), static_cast<int>(A.k)};
   int rc;
   if (ctx.gemm_engine == 1) {
     // the FP32 FMA engine reads the (unrounded) hi panels by strides; their cross panels are zero
-    Operand oa = a_mn ? Operand{A.hi, M, A.k, 1, A.kp, nullptr} : Operand{A.hi + a_row0 * A.kp, M, A.k, A.kp, 1, A.lo + a_row0 * A.kp};
-    Operand ob = b_mn ? Operand{B.hi, N, B.k, 1, B.kp, nullptr} : Operand{B.hi + b_row0 * B.kp, N, B.k, B.kp, 1, B.lo + b_row0 * B.kp};
+    Operand oa = a_mn ? Operand{A.hi + a_row0, M, A.k, 1, A.kp, nullptr} : Operand{A.hi + a_row0 * A.kp, M, A.k, A.kp, 1, A.lo + a_row0 * A.kp};
+    Operand ob = b_mn ? Operand{B.hi + b_row0, N, B.k, 1, B.kp, nullptr} : Operand{B.hi + b_row0 * B.kp, N, B.k, B.kp, 1, B.lo + b_row0 * B.kp};
     ctx.begin(TC_GEMM);
     dim3 grid(static_cast<unsigned>((dims.N + 63) / 64), static_cast<unsigned>((dims.M + 63) / 64));
     gemm_fp32_fma_kernel<<<grid, 256, 0, ctx.stream>>>(oa, ob, dims, epi);
@@ -1543,9 +1546,11 @@ int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, co
     const int b_box = wide ? 128 : (pair ? 64 : bn);
     CUtensorMap maps[4];
     bool ok = true;
-    if (a_mn) ok = ok && make_panel_map_mn(&maps[0], A.hi, false, M, A.k, A.kp) && make_panel_map_mn(&maps[1], A.lo, true, M, A.k, A.kp);
+    if (a_mn) ok = ok && make_panel_map_mn(&maps[0], A.hi + a_row0, false, M, A.k, A.kp) &&
+                  make_panel_map_mn(&maps[1], reinterpret_cast<const uint16_t *>(A.lo) + a_row0, true, M, A.k, A.kp);
     else ok = ok && make_panel_map(&maps[0], A.hi + a_row0 * A.kp, M, A.k, A.kp, BM) && make_panel_map(&maps[1], A.lo + a_row0 * A.kp, M, A.k, A.kp, BM);
-    if (b_mn) ok = ok && make_panel_map_mn(&maps[2], B.hi, false, N, B.k, B.kp) && make_panel_map_mn(&maps[3], B.lo, true, N, B.k, B.kp);
+    if (b_mn) ok = ok && make_panel_map_mn(&maps[2], B.hi + b_row0, false, N, B.k, B.kp) &&
+                  make_panel_map_mn(&maps[3], reinterpret_cast<const uint16_t *>(B.lo) + b_row0, true, N, B.k, B.kp);
     else ok = ok && make_panel_map(&maps[2], B.hi + b_row0 * B.kp, N, B.k, B.kp, b_box) && make_panel_map(&maps[3], B.lo + b_row0 * B.kp, N, B.k, B.kp, b_box);
     if (!ok) return MYEA_E_CUDA;
     ctx.begin(TC_GEMM);

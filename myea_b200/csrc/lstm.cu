@@ -48,6 +48,7 @@ struct LstmPlan {
   float *partial = nullptr;    // [7][chunks][C]
   // cell fused into the recurrent contraction (C a multiple of 8, tensor-core engine): compact peepholes
   // [dirs][3][C], ping-pong operand panels of h (forward) and of the gate errors (backward)
+  bool shared_dw = false;  // weight derivatives from untransposed (column-read) operand panels
   bool fuse = false;
   // With `fuse`, a step is two kernels: the contraction and an 8-cells-per-thread cell kernel that also writes the next
   // operand panels.  fuse_mask (MYEA_B200_LSTM_FUSE) moves the cell into the contraction's epilogue instead: bit 0
@@ -337,6 +338,9 @@ int lstm_create(myea_b200_net *net, LayerPlan &L) {
   need = std::max(need, panel_floats(rows, L.n_in) + panel_floats(4 * C, L.n_in));            // input projection
   need = std::max(need, panel_floats(rows, 4 * Cp) + panel_floats(L.n_in, 4 * Cp));          // error to the previous layer
   need = std::max(need, panel_floats(4 * C, rows) + panel_floats(std::max(L.n_in, C), rows));  // weight derivatives
+  P->shared_dw = net->ctx.gemm_engine == 0 && (C % 64) == 0 && (net->B % 8) == 0 && gemm_takes_mn_major(net->ctx, C, L.n_in) &&
+                 gemm_takes_mn_major(net->ctx, C, C);
+  if (P->shared_dw) need = std::max(need, shared_panel_floats(rows, 4 * C) + shared_panel_floats(rows, L.n_in) + shared_panel_floats(rows, L.n_out) + 256);
   net->scratch.floats = std::max(net->scratch.floats, need + 256);
   return MYEA_OK;
 }
@@ -625,6 +629,47 @@ int lstm_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float 
   for (int d = 0; d < P->dirs; ++d) {
     LstmDir &D = P->d[d];
     float *gw = net->grads + D.w_base;
+    if (P->shared_dw) {
+      // Both operands of every weight-derivative contraction are read through their columns (K = rows of the batch
+      // and time axis), so one untransposed split pass per tensor serves all of them: gate errors, layer input, and
+      // the layer's own outputs for the recurrent weights (a sub-range of K rows and of columns).
+      float *mem_d = scratch;
+      float *mem_x = mem_d + ((shared_panel_floats(rows, 4 * C) + 63) & ~static_cast<size_t>(63));
+      float *mem_h = mem_x + ((shared_panel_floats(rows, n_in) + 63) & ~static_cast<size_t>(63));
+      Panels pd, px, ph;
+      LRC(gemm_prepare_shared(ctx, D.dgates, 4 * C, rows, 4 * C, mem_d, PANEL_ROLE_A, nullptr, PANEL_ROLE_A, &pd));
+      LRC(gemm_prepare_shared(ctx, input, n_in, rows, n_in, mem_x, PANEL_ROLE_B, nullptr, PANEL_ROLE_B, &px));
+      const long long in_off[4] = {off.z_in, off.in[0], off.in[1], off.in[2]};
+      for (int g = 0; g < 4; ++g) {
+        Epilogue e;
+        e.C = gw + in_off[g];
+        e.ldc = P->stride;
+        e.accumulate = 1;
+        LRC(gemm_panels(ctx, pd, g * C, C, px, 0, n_in, e));
+      }
+      if (T > 1) {
+        LRC(gemm_prepare_shared(ctx, L.values, ldh, rows, ldh, mem_h, PANEL_ROLE_B, nullptr, PANEL_ROLE_B, &ph));
+        const long long K = (T - 1) * B;
+        // K rows of steps 1..T-1 of the gate errors against steps 0..T-2 of the outputs (forward direction), the
+        // other way round for the backward direction: a K offset of B rows on one side
+        Panels pdk = pd, phk = ph;
+        const long long kd = d == 0 ? B : 0, kh = d == 0 ? 0 : B;
+        pdk.hi += kd * pd.kp;
+        pdk.lo = reinterpret_cast<float *>(reinterpret_cast<uint16_t *>(pd.lo) + 2 * kd * pd.kp);
+        pdk.k = K;
+        phk.hi += kh * ph.kp;
+        phk.lo = reinterpret_cast<float *>(reinterpret_cast<uint16_t *>(ph.lo) + 2 * kh * ph.kp);
+        phk.k = K;
+        const long long rec_off[4] = {off.z_rec, off.rec[0], off.rec[1], off.rec[2]};
+        for (int g = 0; g < 4; ++g) {
+          Epilogue e;
+          e.C = gw + rec_off[g];
+          e.ldc = P->stride;
+          e.accumulate = 1;
+          LRC(gemm_panels(ctx, pdk, g * C, C, phk, d * C, C, e));
+        }
+      }
+    } else {
     // input weights: K = all T*B rows
     Panels pdt, pxt;
     LRC(gemm_prepare(ctx, Operand{D.dgates, 4 * C, rows, 1, 4 * C}, scratch, &pdt, PANEL_ROLE_A));                        // dgates^T [4C, rows]
@@ -653,6 +698,7 @@ int lstm_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float 
         e.accumulate = 1;
         LRC(gemm_panels(ctx, pdr, g * C, C, pht, 0, C, e));
       }
+    }
     }
     // biases and peepholes
     const int chunks = static_cast<int>(std::max<long long>(1, std::min<long long>(net->reduce_chunks, rows / 8)));

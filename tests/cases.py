@@ -87,6 +87,19 @@ CASES.update({
 })
 
 
+# Larger shapes that reach the kernels only big layers use (256 x 256 tensor-core tiles, column-read operand panels,
+# 8-cells-per-thread LSTM steps).  Compared with the compiled reference on the GPU box, without a committed fixture
+# (the parameter vectors would be megabytes).  Momentum descent: an update that is linear in the derivatives (Adam-type
+# updates turn the rounding noise of near-zero derivatives into +-lr steps, and half a million parameters hold enough
+# of those to cross 1e-4 on the updated parameters although the derivatives agree to 1e-6).
+CASES_ORACLE_ONLY = {
+    "lstm_wide_nesterov": lambda: _lstm_case("lstm_wide", capi.opt(capi.OPT_GD, gd_lr=0.001, momentum=0.9, nesterov=True), T=4, B=16, n_in=136,
+                                             H=192, layers=1, out=192),
+    "lstm2_wide_zoneout": lambda: _lstm_case("lstm2_wide", capi.opt(capi.OPT_GD, gd_lr=0.001, momentum=0.9), T=3, B=136, n_in=64, H=192, layers=2,
+                                             out=192, zoneout=0.2, delays=0),
+}
+
+
 def _bilstm_case(name, opt, T=5, B=6, n_in=7, H=8, out=5, zoneout=None):
     ls = [capi.fc(n_in), capi.lstm(H, bidirectional=True, dropout=capi.DROP_ZONEOUT if zoneout else capi.DROP_NONE,
                                    p=(zoneout or 0.0, zoneout or 0.0, 0.0)), capi.fc(out, capi.AF_LINEAR)]

@@ -50,9 +50,9 @@ def _compare(out, want, tol=TOL):
         assert rel_err(out["norm_sigma_avg"], want["norm_sigma_avg"]) < tol
 
 
-@pytest.mark.parametrize("name", sorted(cases.CASES))
+@pytest.mark.parametrize("name", sorted(cases.CASES) + sorted(cases.CASES_ORACLE_ONLY))
 def test_step_matches_oracle(name):
-    wl = cases.CASES[name]()
+    wl = (cases.CASES.get(name) or cases.CASES_ORACLE_ONLY[name])()
     gpu, cpu = Net(wl.desc, wl.opt), _oracle(wl)
     want = cases.run_steps(cpu, wl, shake=_seeded_shake(wl))
     out = cases.run_steps(gpu, wl, shake=want["shake"] if want["shake"] and want["shake"][0] else _seeded_shake(wl))
