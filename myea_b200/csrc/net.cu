@@ -239,7 +239,7 @@ static int allocate_buffers(myea_b200_net *net) {
       RC(dev_alloc(net, &L.deriv, rows * wide));
       if (L.has_norm) RC(dev_alloc(net, &L.errors, rows * L.n_out));
       else L.errors = L.deriv;
-      if (!layer_in_block(net, static_cast<int>(l), nullptr) && gemm_takes_mn_major(net->ctx, rows, L.n_out) &&
+      if (gemm_takes_mn_major(net->ctx, rows, L.n_out) &&
           gemm_takes_mn_major(net->ctx, rows, L.n_in) && gemm_takes_mn_major(net->ctx, L.n_out, L.n_in) && net->ctx.gemm_engine == 0) {
         L.shared_panels = true;
         RC(dev_alloc(net, &L.in_panel_mem, shared_panel_floats(rows, L.n_in)));
@@ -452,24 +452,40 @@ namespace myea {
 
 // One fully connected layer on `rows` rows: z = x W^T (+ b); normalization statistics; activation; dropout.
 // Forward_Pass__FC (Neural_Network__Forward_Pass__Loop.cpp:350-790 is the per-layer driver).
-int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long rows) {
-  Operand a{input, rows, L.n_in, L.n_in, 1};
-  Operand b{net->params + L.idx.first_connection_index, L.n_out, L.n_in, L.n_in, 1};
-  Epilogue e;
-  e.C = L.summations;
-  e.ldc = L.n_out;
-  e.bias = L.use_bias ? net->params + L.idx.first_bias_connection_index : nullptr;
+int fc_product_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long rows, const Epilogue &e) {
+  const float *w = net->params + L.idx.first_connection_index;
   if (L.shared_panels) {
     // while training, the same pass also writes the column readings the backward contractions will want
     const bool tr = net->training;
     RC(gemm_prepare_shared(net->ctx, input, L.n_in, rows, L.n_in, L.in_panel_mem, PANEL_ROLE_A, &L.in_rows, PANEL_ROLE_B, tr ? &L.in_cols : nullptr));
-    RC(gemm_prepare_shared(net->ctx, b.ptr, L.n_in, L.n_out, L.n_in, L.w_panel_mem, PANEL_ROLE_B, &L.w_rows, PANEL_ROLE_B, tr ? &L.w_cols : nullptr));
+    RC(gemm_prepare_shared(net->ctx, w, L.n_in, L.n_out, L.n_in, L.w_panel_mem, PANEL_ROLE_B, &L.w_rows, PANEL_ROLE_B, tr ? &L.w_cols : nullptr));
     L.in_valid = L.w_valid = tr;
+    L.in_src = input;
     L.d_valid = false;
-    RC(gemm_panels(net->ctx, L.in_rows, 0, rows, L.w_rows, 0, L.n_out, e));
-  } else {
-    RC(gemm_nt(net->ctx, a, b, e, net->scratch));
+    return gemm_panels(net->ctx, L.in_rows, 0, rows, L.w_rows, 0, L.n_out, e);
   }
+  Operand a{input, rows, L.n_in, L.n_in, 1};
+  Operand b{w, L.n_out, L.n_in, L.n_in, 1};
+  return gemm_nt(net->ctx, a, b, e, net->scratch);
+}
+
+int fc_product_backward(myea_b200_net *net, LayerPlan &N, long long rows, const Epilogue &e) {
+  if (N.shared_panels && N.w_valid) {
+    RC(gemm_prepare_shared(net->ctx, N.errors, N.n_out, rows, N.n_out, N.d_panel_mem, PANEL_ROLE_A, &N.d_rows, PANEL_ROLE_A, &N.d_cols));
+    N.d_valid = true;
+    return gemm_panels(net->ctx, N.d_rows, 0, rows, N.w_cols, 0, N.n_in, e);
+  }
+  Operand a{N.errors, rows, N.n_out, N.n_out, 1};
+  Operand b{net->params + N.idx.first_connection_index, N.n_in, N.n_out, 1, N.n_in};  // W[out,in] read as [in rows, K=out]
+  return gemm_nt(net->ctx, a, b, e, net->scratch);
+}
+
+int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long rows) {
+  Epilogue e;
+  e.C = L.summations;
+  e.ldc = L.n_out;
+  e.bias = L.use_bias ? net->params + L.idx.first_bias_connection_index : nullptr;
+  RC(fc_product_forward(net, L, input, rows, e));
   const float *cs = nullptr, *ch = nullptr;
   if (L.has_norm) {
     RC(norm_forward_stats(net->ctx, L.summations, rows, L.n_out, L.norm, net->training ? 1 : 0, &net->hook));
@@ -592,8 +608,6 @@ namespace myea {
 // by Backward_Pass__FC__DF :1225-1263), then the normalization backward (:1346-1709).
 int fc_backward_from_fc(myea_b200_net *net, LayerPlan &L, const LayerPlan &next, const float *next_errors, long long rows,
                         float *dst, bool fuse_derivative) {
-  Operand a{next_errors, rows, next.n_out, next.n_out, 1};
-  Operand b{net->params + next.idx.first_connection_index, next.n_in, next.n_out, 1, next.n_in};  // W[out,in] read as [in rows, K=out]
   Epilogue e;
   e.C = dst;
   e.ldc = next.n_in;
@@ -604,13 +618,12 @@ int fc_backward_from_fc(myea_b200_net *net, LayerPlan &L, const LayerPlan &next,
     e.ld_aux = L.n_out;
     if (L.has_norm) { e.col_scale = L.norm.col_scale; e.col_shift = L.norm.col_shift; }
   }
-  if (next.shared_panels && next.w_valid && next_errors == next.errors) {
-    LayerPlan &N = const_cast<LayerPlan &>(next);
-    RC(gemm_prepare_shared(net->ctx, N.errors, N.n_out, rows, N.n_out, N.d_panel_mem, PANEL_ROLE_A, &N.d_rows, PANEL_ROLE_A, &N.d_cols));
-    N.d_valid = true;
-    return gemm_panels(net->ctx, N.d_rows, 0, rows, N.w_cols, 0, N.n_in, e);
+  if (next_errors != next.errors) {  // (not the case today) an error array other than the layer's own: no shared panels
+    Operand a{next_errors, rows, next.n_out, next.n_out, 1};
+    Operand b{net->params + next.idx.first_connection_index, next.n_in, next.n_out, 1, next.n_in};
+    return gemm_nt(net->ctx, a, b, e, net->scratch);
   }
-  return gemm_nt(net->ctx, a, b, e, net->scratch);
+  return fc_product_backward(net, const_cast<LayerPlan &>(next), rows, e);
 }
 
 int fc_finish_backward(myea_b200_net *net, LayerPlan &L, long long rows) {
@@ -669,7 +682,7 @@ int fc_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float *i
   e.C = net->grads + L.idx.first_connection_index;
   e.ldc = L.n_in;
   e.accumulate = 1;
-  if (L.shared_panels && L.in_valid && input == net->layers[L.input_layer].values) {
+  if (L.shared_panels && L.in_valid && input == L.in_src) {
     if (!L.d_valid) {  // no error propagation below this layer (first hidden layer): only the column reading is needed
       RC(gemm_prepare_shared(net->ctx, L.errors, L.n_out, rows, L.n_out, L.d_panel_mem, PANEL_ROLE_A, nullptr, PANEL_ROLE_A, &L.d_cols));
     }

@@ -9,6 +9,7 @@
 namespace myea {
 
 struct LstmPlan;   // lstm.cu
+struct LayerPlan;
 struct CommState;  // comm.cu
 
 struct LayerPlan {
@@ -43,7 +44,13 @@ struct LayerPlan {
   float *in_panel_mem = nullptr, *w_panel_mem = nullptr, *d_panel_mem = nullptr;
   Panels in_rows, in_cols, w_rows, w_cols, d_rows, d_cols;
   bool in_valid = false, w_valid = false, d_valid = false;
+  const float *in_src = nullptr;  // the array the input panels were made from
 };
+
+// z = input * W^T of a fully connected layer and D = errors * W (error on the layer's inputs), from the layer's shared
+// operand panels when it has them, else through gemm_nt; `e` carries destination and fused extras (net.cu)
+int fc_product_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long rows, const Epilogue &e);
+int fc_product_backward(myea_b200_net *net, LayerPlan &N, long long rows, const Epilogue &e);
 
 }  // namespace myea
 

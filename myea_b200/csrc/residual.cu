@@ -113,13 +113,11 @@ int residual_forward(myea_b200_net *net, int r) {
       RRC(activation_forward(ctx, prev, L.values, rows, L.n_in, L.desc.type_activation_function, cs, ch, mask, scale));
       in = L.values;
     }
-    Operand a{in, rows, L.n_in, L.n_in, 1};
-    Operand b{net->params + L.idx.first_connection_index, L.n_out, L.n_in, L.n_in, 1};
     Epilogue e;
     e.C = L.summations;
     e.ldc = L.n_out;
     e.bias = L.use_bias ? net->params + L.idx.first_bias_connection_index : nullptr;
-    RRC(gemm_nt(ctx, a, b, e, net->scratch));
+    RRC(fc_product_forward(net, L, in, rows, e));
   }
   const LayerPlan &last = net->layers[r + R.block_depth];
   const bool shake = R.desc.type_dropout == MYEA_DROPOUT_SHAKEDROP;
@@ -141,8 +139,6 @@ int residual_backward(myea_b200_net *net, int r) {
   for (int k = R.block_depth; k > 1; --k) {
     LayerPlan &L = net->layers[r + k];
     LayerPlan &below = net->layers[r + k - 1];
-    Operand a{L.errors, rows, L.n_out, L.n_out, 1};
-    Operand b{net->params + L.idx.first_connection_index, L.n_in, L.n_out, 1, L.n_in};
     Epilogue e;
     e.C = L.has_norm ? L.deriv : below.errors;  // without normalization the result IS the error on the layer below's output
     e.ldc = L.n_in;
@@ -151,15 +147,13 @@ int residual_backward(myea_b200_net *net, int r) {
     e.aux_y = L.values;
     e.ld_aux = L.n_in;
     if (L.has_norm) { e.col_scale = L.norm.col_scale; e.col_shift = L.norm.col_shift; }
-    RRC(gemm_nt(ctx, a, b, e, net->scratch));
+    RRC(fc_product_backward(net, L, rows, e));
     if (L.has_norm) RRC(norm_backward(ctx, below.summations, L.deriv, below.errors, rows, L.n_in, L.norm, &net->hook));
   }
   // the layer feeding the block: skip error + W_1^T delta_1, then its own activation derivative / normalization
   LayerPlan &first = net->layers[r + 1];
   LayerPlan &F = net->layers[R.input_layer];
   if (R.input_layer < 1) return MYEA_OK;  // the block reads the network input: nothing to propagate to
-  Operand a{first.errors, rows, first.n_out, first.n_out, 1};
-  Operand b{net->params + first.idx.first_connection_index, first.n_in, first.n_out, 1, first.n_in};
   Epilogue e;
   e.C = F.deriv;
   e.ldc = first.n_in;
@@ -175,7 +169,7 @@ int residual_backward(myea_b200_net *net, int r) {
     net->ctx.error = "a residual block fed by an LSTM layer is not built";
     return MYEA_E_UNSUPPORTED;
   }
-  RRC(gemm_nt(ctx, a, b, e, net->scratch));
+  RRC(fc_product_backward(net, first, rows, e));
   if (F.type == MYEA_LAYER_FULLY_CONNECTED) RRC(fc_finish_backward(net, F, rows));
   return MYEA_OK;
 }

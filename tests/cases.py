@@ -97,7 +97,12 @@ CASES_ORACLE_ONLY = {
                                              H=192, layers=1, out=192),
     "lstm2_wide_zoneout": lambda: _lstm_case("lstm2_wide", capi.opt(capi.OPT_GD, gd_lr=0.001, momentum=0.9), T=3, B=136, n_in=64, H=192, layers=2,
                                              out=192, zoneout=0.2, delays=0),
+    "residual_wide_brn_shakedrop": lambda: _res_wide(),
 }
+
+
+def _res_wide():
+    return _res_case("res_wide", capi.opt(capi.OPT_GD, gd_lr=0.001, momentum=0.9), B=136, n_in=40, H=144, out=7, blocks=2)
 
 
 def _bilstm_case(name, opt, T=5, B=6, n_in=7, H=8, out=5, zoneout=None):
