@@ -166,6 +166,21 @@ int myea_b200_set_mask_bernoulli(myea_handle h, uint32_t layer, const uint8_t *m
  * (both directions: [T][2*cells]); true = compute, false = keep the previous value. */
 int myea_b200_set_mask_zoneout(myea_handle h, uint32_t layer, const uint8_t *mask_state, const uint8_t *mask_output,
                                uint64_t count);
+/* Device-side replacement of Dropout_Bernoulli (Neural_Network__Dropout__Bernoulli__Loop.cpp:70-90), Dropout_Zoneout
+ * (Neural_Network__Dropout__Zoneout__Loop.cpp:57-100) and the ShakeDrop draws of the forward / backward passes
+ * (Neural_Network__Forward_Pass__Loop.cpp:5016-5045): fills every mask and coefficient array of the network on the GPU
+ * with a counter-based generator (Philox4x32-10).  The draws are a pure function of (seed, step, layer, kind, element),
+ * identical on every GPU; statistically, not bit for bit, comparable to the reference's std::mt19937 streams.
+ * myea_b200_download_mask reads one array back (uint8 masks, float coefficients; zoneout as [T][dirs*cells]). */
+#define MYEA_MASK_BERNOULLI 0
+#define MYEA_MASK_ZONEOUT_STATE 1
+#define MYEA_MASK_ZONEOUT_OUTPUT 2
+#define MYEA_MASK_SHAKEDROP 3
+#define MYEA_MASK_SHAKEDROP_ALPHA 4
+#define MYEA_MASK_SHAKEDROP_BETA 5
+int myea_b200_generate_masks(myea_handle h, uint64_t seed, uint64_t step);
+int myea_b200_download_mask(myea_handle h, uint32_t layer, int kind, void *host, uint64_t bytes);
+
 /* ShakeDrop draws of one residual block made explicit: mask bool[B] (Layer::ptr_array__mask__dropout__shakedrop,
  * Data.hpp:612), forward coefficients alpha[B][units] and backward coefficients beta[B][units]
  * (Neural_Network__Forward_Pass__OpenMP.cpp:5021-5056, Neural_Network__Backward_Pass__OpenMP.cpp:1009-1042). */

@@ -16,6 +16,7 @@ LAYER_FC, LAYER_LSTM, LAYER_RESIDUAL = 4, 8, 10
 NET_FEEDFORWARD, NET_RECURRENT = 3, 4
 AF_ELU, AF_LINEAR, AF_LEAKY_RELU, AF_RELU, AF_SELU, AF_SIGMOID, AF_SOFTMAX, AF_TANH = 3, 11, 14, 16, 17, 18, 22, 23
 NORM_NONE, NORM_BN, NORM_BRN = 0, 1, 2
+MASK_BERNOULLI, MASK_ZONEOUT_STATE, MASK_ZONEOUT_OUTPUT, MASK_SHAKEDROP, MASK_SHAKEDROP_ALPHA, MASK_SHAKEDROP_BETA = range(6)
 DROP_NONE, DROP_BERNOULLI, DROP_BERNOULLI_INVERTED, DROP_SHAKEDROP, DROP_ZONEOUT = 0, 2, 3, 5, 7
 LOSS_CE, LOSS_MSE = 2, 10
 ACC_NONE, ACC_CE, ACC_DISTANCE = 0, 1, 3
@@ -145,6 +146,8 @@ _PROTOS = {
     "myea_b200_last_error": (C.c_char_p, [C.c_void_p]),
     "myea_b200_sizes": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_uint64)] * 4),
     "myea_b200_layer_index": (C.c_int, [C.c_void_p, C.c_uint32, C.POINTER(LayerIndex)]),
+    "myea_b200_generate_masks": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64]),
+    "myea_b200_download_mask": (C.c_int, [C.c_void_p, C.c_uint32, C.c_int, C.c_void_p, C.c_uint64]),
     "myea_b200_upload": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_uint64, C.c_uint64]),
     "myea_b200_download": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_uint64, C.c_uint64]),
     "myea_b200_set_mask_bernoulli": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64]),

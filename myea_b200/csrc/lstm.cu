@@ -367,6 +367,19 @@ int lstm_set_zoneout(myea_b200_net *net, LayerPlan &L, const uint8_t *state, con
   return cudaStreamSynchronize(net->ctx.stream) == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
+// the per-direction zoneout arrays ([T][C] each) and probabilities of layer L, for the device-side mask generator
+void lstm_zoneout_arrays(LayerPlan &L, int dir, uint8_t **state, uint8_t **output, long long *cells, int *dirs, float *p_state, float *p_output) {
+  LstmPlan *P = L.lstm;
+  *state = nullptr; *output = nullptr;
+  if (P == nullptr || !P->zoneout || dir < 0 || dir >= P->dirs) return;
+  *state = P->d[dir].zone_state;
+  *output = P->d[dir].zone_output;
+  *cells = P->C;
+  *dirs = P->dirs;
+  *p_state = L.desc.dropout_values[0];
+  *p_output = L.desc.dropout_values[1];
+}
+
 static float *aligned_scratch(myea_b200_net *net) {
   return reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(net->scratch.base) + 255) & ~static_cast<uintptr_t>(255));
 }

@@ -161,6 +161,11 @@ bool Neural_Network::Upload__Dropout_ShakeDrop(size_t l, bool const *mask, float
   return rc == MYEA_OK ? true : fail("Upload__Dropout_ShakeDrop", rc);
 }
 
+bool Neural_Network::Draw__Masks(void) {
+  int rc = myea_b200_generate_masks(ptr_device_Neural_Network, seed_dropout, draws_++);
+  return rc == MYEA_OK ? true : fail("Draw__Masks", rc);
+}
+
 // row pointers (one [T * width] row per sample, Neural_Network__Assign_Inputs.cpp:273-304) -> packed [T][B][width]
 bool Neural_Network::pack(float const *const *rows, size_t B, size_t width, std::vector<float> &dst) {
   if (rows == nullptr) return false;

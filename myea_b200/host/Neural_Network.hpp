@@ -68,6 +68,12 @@ class Neural_Network {
   bool Upload__Mask_Dropout_Bernoulli(size_t index_layer, bool const *mask, size_t count);
   bool Upload__Mask_Dropout_Zoneout(size_t index_layer, bool const *mask_state, bool const *mask_output, size_t count);
   bool Upload__Dropout_ShakeDrop(size_t index_layer, bool const *mask, float const *alpha, float const *beta, size_t batch);
+  // Dropout_Bernoulli() / Dropout_Zoneout() and the ShakeDrop draws (Data.hpp:944-958): new masks and coefficients for
+  // every layer, drawn on the device from (seed_dropout, number of calls so far); nothing is uploaded
+  void Dropout_Bernoulli(void) { Draw__Masks(); }
+  void Dropout_Zoneout(void) { Draw__Masks(); }
+  bool Draw__Masks(void);
+  unsigned long long seed_dropout = 5413u;
 
   // ---- the training step (Dataset.cpp:637-691, 7654-7690) ----
   void Forward_Pass(size_t batch_size, float const *const *ptr_array_inputs, long long input_layer = -1, long long output_layer = -1);
@@ -100,6 +106,7 @@ class Neural_Network {
 
  private:
   bool fail(char const *where, int status);
+  unsigned long long draws_ = 0;
   bool pack(float const *const *rows, size_t batch, size_t width, std::vector<float> &dst);
   myea_net_desc desc_ = {};
   myea_opt_desc opt_ = {};

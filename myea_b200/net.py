@@ -82,6 +82,15 @@ class Net:
         a, b = _f32(alpha), _f32(beta)
         self._ck(self.lib.myea_b200_set_shakedrop(self.h, layer, m.ctypes.data, a.ctypes.data, b.ctypes.data, m.size), "set_shakedrop")
 
+    def generate_masks(self, seed, step):
+        """fills every dropout / zoneout / ShakeDrop array on the device from the counter-based generator"""
+        self._ck(self.lib.myea_b200_generate_masks(self.h, int(seed), int(step)), "generate_masks")
+
+    def download_mask(self, layer, kind, shape):
+        out = np.zeros(shape, np.float32 if kind in (capi.MASK_SHAKEDROP_ALPHA, capi.MASK_SHAKEDROP_BETA) else np.uint8)
+        self._ck(self.lib.myea_b200_download_mask(self.h, layer, kind, out.ctypes.data, out.nbytes), "download_mask")
+        return out
+
     def forward(self, X, training=True):
         X = _f32(X)
         self._ck(self.lib.myea_b200_forward(self.h, self.B, X.ctypes.data, 1 if training else 0), "forward")
