@@ -181,6 +181,26 @@ int myea_b200_set_mask_zoneout(myea_handle h, uint32_t layer, const uint8_t *mas
 int myea_b200_generate_masks(myea_handle h, uint64_t seed, uint64_t step);
 int myea_b200_download_mask(myea_handle h, uint32_t layer, int kind, void *host, uint64_t bytes);
 
+/* The caller of the step, with the dataset resident on the device.
+ * myea_b200_dataset_set: `number_examples` rows of [T * inputs] and [T * outputs] floats, example-major, as
+ *   Dataset::ptr_array_inputs_array[i] / ptr_array_outputs_array[i] point to them.
+ * myea_b200_train_epoch: Dataset_Mini_Batch::Training_Loop (Dataset__Mini_Batch.cpp:394-436) over
+ *   Dataset::Train_Batch_BP_Loop (Dataset.cpp:667-691): for every mini-batch of `order` (the host shuffles, as
+ *   Dataset_Mini_Batch::Shuffle does) - reset loss, then per sub-batch of the network's batch size gather, forward,
+ *   error, backward, derivative accumulation - then Update_Parameter(mini_batch_size, examples of the dataset).
+ *   `mean_loss`: Get__Loss(TYPE_DATASET_NONE) averaged over the mini-batches; `accuracy_sum`: summed accuracy hits.
+ *   mask_seed != 0 draws new masks before mini-batch i with myea_b200_generate_masks(seed, first_step + i).
+ *   The caller advances opt->epoch_time_step between epochs as the reference does.
+ *   mini_batch_size must be a multiple of the network's batch size and divide number_examples (MYEA_E_UNSUPPORTED else).
+ * myea_b200_evaluate: the forward-only loop of Dataset::Testing: inference-mode forward (running normalization
+ *   statistics, dropout scaling) and loss / accuracy accumulation over `number_examples` examples (`order` may be
+ *   null: the first examples of the dataset); number_examples must be a multiple of the network's batch size. */
+int myea_b200_dataset_set(myea_handle h, uint64_t number_examples, const float *inputs, const float *outputs);
+int myea_b200_train_epoch(myea_handle h, const uint64_t *order, uint64_t number_examples, uint64_t mini_batch_size,
+                          const myea_opt_desc *opt, uint64_t mask_seed, uint64_t first_step, double *mean_loss, double *accuracy_sum);
+int myea_b200_evaluate(myea_handle h, const uint64_t *order, uint64_t number_examples, double *loss, double *loss_sum,
+                       uint64_t *number_loss, double *accuracy_sum);
+
 /* ShakeDrop draws of one residual block made explicit: mask bool[B] (Layer::ptr_array__mask__dropout__shakedrop,
  * Data.hpp:612), forward coefficients alpha[B][units] and backward coefficients beta[B][units]
  * (Neural_Network__Forward_Pass__OpenMP.cpp:5021-5056, Neural_Network__Backward_Pass__OpenMP.cpp:1009-1042). */

@@ -146,6 +146,11 @@ _PROTOS = {
     "myea_b200_last_error": (C.c_char_p, [C.c_void_p]),
     "myea_b200_sizes": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_uint64)] * 4),
     "myea_b200_layer_index": (C.c_int, [C.c_void_p, C.c_uint32, C.POINTER(LayerIndex)]),
+    "myea_b200_dataset_set": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]),
+    "myea_b200_train_epoch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(OptDesc), C.c_uint64, C.c_uint64,
+                                        C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "myea_b200_evaluate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_uint64),
+                                     C.POINTER(C.c_double)]),
     "myea_b200_generate_masks": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64]),
     "myea_b200_download_mask": (C.c_int, [C.c_void_p, C.c_uint32, C.c_int, C.c_void_p, C.c_uint64]),
     "myea_b200_upload": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_uint64, C.c_uint64]),

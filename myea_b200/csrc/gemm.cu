@@ -1495,7 +1495,10 @@ static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const Ge
   const int rem = work.num_tiles % G;
   if (ctx.gemm_bn != 4 && ctx.sk_ws != nullptr && ctx.sk_clusters >= G && rem != 0 && num_chunks >= 2) {
     const int units = rem * num_chunks;
-    const int per_cluster = (units + G - 1) / G;
+    int per_cluster = (units + G - 1) / G;
+#ifdef MYEA_GEMM_TIMELINE
+    if (const char *ev = getenv("MYEA_SK_MIN")) per_cluster = std::max(per_cluster, atoi(ev));
+#endif
     // splitting a tile costs about one chunk's time (partial sums through L2, one counter round trip, the second
     // pass of the warp that arrives last): worth it when it takes at least two chunks off the longest cluster
     if (num_chunks - per_cluster >= 2) {

@@ -352,6 +352,9 @@ extern "C" void myea_b200_destroy(myea_handle net) {
   for (auto &L : net->layers) lstm_destroy(L);
   for (void *p : net->allocations) cudaFree(p);
   gemm_splitk_release(net->ctx);
+  for (void *p : {static_cast<void *>(net->ds_inputs), static_cast<void *>(net->ds_outputs), static_cast<void *>(net->ds_batch_inputs),
+                  static_cast<void *>(net->ds_batch_outputs), static_cast<void *>(net->ds_order)})
+    if (p != nullptr) cudaFree(p);
   if (net->ctx.ev0) cudaEventDestroy(net->ctx.ev0);
   if (net->ctx.ev1) cudaEventDestroy(net->ctx.ev1);
   if (net->ctx.stream) cudaStreamDestroy(net->ctx.stream);

@@ -82,5 +82,9 @@ struct myea_b200_net {
   myea::SumHook hook;            // cross-GPU sum of normalization column sums (world 1: unused)
   bool grads_reduced = false;    // this step's derivative buckets have already been handed to the communicator
   double *d_loss_tmp = nullptr;  // [3] staging for the cross-GPU sum of the loss accumulators
+  // dataset kept on the device for the epoch loop (epoch.cu): rows [example][T * width], the staged batch, the order
+  float *ds_inputs = nullptr, *ds_outputs = nullptr, *ds_batch_inputs = nullptr, *ds_batch_outputs = nullptr;
+  unsigned long long *ds_order = nullptr;
+  uint64_t ds_examples = 0, ds_order_capacity = 0;
   std::vector<void *> allocations;
 };

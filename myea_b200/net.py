@@ -82,6 +82,25 @@ class Net:
         a, b = _f32(alpha), _f32(beta)
         self._ck(self.lib.myea_b200_set_shakedrop(self.h, layer, m.ctypes.data, a.ctypes.data, b.ctypes.data, m.size), "set_shakedrop")
 
+    def dataset_set(self, X, Y):
+        """X: [N, T*inputs], Y: [N, T*outputs] example-major rows; kept on the device"""
+        X, Y = _f32(X), _f32(Y)
+        self._ck(self.lib.myea_b200_dataset_set(self.h, X.shape[0], X.ctypes.data, Y.ctypes.data), "dataset_set")
+
+    def train_epoch(self, order, mini_batch, opt=None, mask_seed=0, first_step=0):
+        order = np.ascontiguousarray(order, dtype=np.uint64)
+        loss, acc = C.c_double(), C.c_double()
+        self._ck(self.lib.myea_b200_train_epoch(self.h, order.ctypes.data, order.size, mini_batch, C.byref(opt or self.opt), mask_seed, first_step,
+                                                C.byref(loss), C.byref(acc)), "train_epoch")
+        return loss.value, acc.value
+
+    def evaluate(self, n, order=None):
+        o = None if order is None else np.ascontiguousarray(order, dtype=np.uint64)
+        loss, ls, nl, acc = C.c_double(), C.c_double(), C.c_uint64(), C.c_double()
+        self._ck(self.lib.myea_b200_evaluate(self.h, None if o is None else o.ctypes.data, n, C.byref(loss), C.byref(ls), C.byref(nl), C.byref(acc)),
+                 "evaluate")
+        return loss.value, ls.value, nl.value, acc.value
+
     def generate_masks(self, seed, step):
         """fills every dropout / zoneout / ShakeDrop array on the device from the counter-based generator"""
         self._ck(self.lib.myea_b200_generate_masks(self.h, int(seed), int(step)), "generate_masks")
