@@ -70,6 +70,7 @@ extern "C" {
 #define MYEA_OPT_AMSBOUND 4u
 #define MYEA_OPT_AMSGRAD 5u
 #define MYEA_OPT_GD 6u
+#define MYEA_OPT_NOSADAM 9u
 
 /* One layer, as `struct Layer_Parameters` (Data.hpp:56-80) plus the per-layer Set__* state. */
 typedef struct myea_layer_desc {
@@ -116,6 +117,9 @@ typedef struct myea_opt_desc {
   uint32_t use_clip_gradient; /* Set__Clip_Gradient(bool)  (Data.hpp:837)                        */
   float clip_gradient;        /* Set__Clip_Gradient(T_)    (Data.hpp:2718)                       */
   float epoch_time_step;      /* divisor of the normalized weight decay (Train.cpp:284-286)      */
+  float adam_gamma;           /* NosAdam: beta2_t = B/(B + t^-gamma), B += t^-gamma (Neural_Network__NosAdam.cpp:97-160); 0 = the class default 0.1 */
+  float regularization__max_norm_constraints; /* Set__Regularization__Max_Norm_Constraints (Data.hpp:2744): after the update every
+                                                 neuron's weight row with norm >= c is scaled to norm c; 0 = off */
 } myea_opt_desc;
 
 /* Where one layer's parameters sit in the flat [P] buffer: the index map that

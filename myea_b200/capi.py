@@ -20,7 +20,7 @@ MASK_BERNOULLI, MASK_ZONEOUT_STATE, MASK_ZONEOUT_OUTPUT, MASK_SHAKEDROP, MASK_SH
 DROP_NONE, DROP_BERNOULLI, DROP_BERNOULLI_INVERTED, DROP_SHAKEDROP, DROP_ZONEOUT = 0, 2, 3, 5, 7
 LOSS_CE, LOSS_MSE = 2, 10
 ACC_NONE, ACC_CE, ACC_DISTANCE = 0, 1, 3
-OPT_ADABOUND, OPT_ADAM, OPT_AMSBOUND, OPT_AMSGRAD, OPT_GD = 1, 2, 4, 5, 6
+OPT_ADABOUND, OPT_ADAM, OPT_AMSBOUND, OPT_AMSGRAD, OPT_GD, OPT_NOSADAM = 1, 2, 4, 5, 6, 9
 (BUF_PARAMETERS, BUF_DERIVATIVES, BUF_FIRST_MOMENT, BUF_SECOND_MOMENT, BUF_SECOND_MOMENT_HAT, BUF_MASK_REGULARIZED,
  BUF_NORM_MEAN_AVERAGE, BUF_NORM_VARIANCE_AVERAGE, BUF_PREVIOUS_DELTA) = range(9)
 TIMER_CLASSES = 8
@@ -49,7 +49,8 @@ class OptDesc(C.Structure):
                 ("adam_learning_rate", C.c_float), ("adam_beta1", C.c_float), ("adam_beta2", C.c_float),
                 ("adam_epsilon", C.c_float), ("learning_rate_final", C.c_float), ("learning_gamma", C.c_float),
                 ("regularization__weight_decay", C.c_float), ("use_normalized_weight_decay", C.c_uint32),
-                ("use_clip_gradient", C.c_uint32), ("clip_gradient", C.c_float), ("epoch_time_step", C.c_float)]
+                ("use_clip_gradient", C.c_uint32), ("clip_gradient", C.c_float), ("epoch_time_step", C.c_float),
+                ("adam_gamma", C.c_float), ("regularization__max_norm_constraints", C.c_float)]
 
 
 class LayerIndex(C.Structure):
@@ -121,7 +122,8 @@ def net(layers, batch, T=1, loss=LOSS_MSE, accuracy=ACC_NONE, time_delays=0, mom
 
 
 def opt(kind=OPT_ADAM, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, bias_correction=True, final_lr=0.1, gamma=1e-3,
-        weight_decay=0.0, normalized_wd=True, clip=None, gd_lr=0.01, momentum=0.0, nesterov=False, epoch=1.0):
+        weight_decay=0.0, normalized_wd=True, clip=None, gd_lr=0.01, momentum=0.0, nesterov=False, epoch=1.0, nosadam_gamma=0.1,
+        max_norm=0.0):
     o = OptDesc()
     o.type_optimizer_function = kind
     o.use_adam_bias_correction = 1 if bias_correction else 0
@@ -135,6 +137,8 @@ def opt(kind=OPT_ADAM, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, bias_correctio
     o.use_clip_gradient = 0 if clip is None else 1
     o.clip_gradient = 1.0 if clip is None else clip
     o.epoch_time_step = epoch
+    o.adam_gamma = nosadam_gamma
+    o.regularization__max_norm_constraints = max_norm
     return o
 
 

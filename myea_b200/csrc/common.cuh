@@ -234,6 +234,9 @@ struct OptLaunch {
 };
 int optimizer_update(Context &ctx, const OptLaunch &o, float *w, float *g, float *m, float *v, float *vhat,
                      float *prev_delta, const float *mask, size_t n);
+// every row of w[rows][cols] whose Euclidean norm is >= max_norm is scaled to norm max_norm (Euclidean_Norm__Loop,
+// Neural_Network__Regularization__Max_Norm_Constraints.cpp:48-88)
+int row_max_norm(Context &ctx, float *w, long long rows, long long cols, float max_norm);
 // d_out[0] = sum g^2 (double)
 int sum_squares(Context &ctx, const float *g, size_t n, double *d_out);
 // clip_scale[0] = norm >= clip ? clip / norm : 1

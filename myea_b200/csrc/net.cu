@@ -770,14 +770,38 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
       o.upper = opt->learning_rate_final * (1.f + 1.f / (opt->learning_gamma * t));
       break;
     }
+    case MYEA_OPT_NOSADAM: {
+      // Adam whose second-moment decay changes with time (Neural_Network__NosAdam.cpp:97-160): the bias correction keeps
+      // using the fixed adam_beta2; the running sum B lives on the handle like adam_previous_beta2 on the reference object
+      const float gamma = opt->adam_gamma > 0.f ? opt->adam_gamma : 0.1f;
+      const float pw = powf(t, -gamma);
+      o.type = MYEA_OPT_ADAM;
+      o.beta1 = opt->adam_beta1;
+      o.beta2 = net->nosadam_previous_beta2 / (net->nosadam_previous_beta2 + pw);
+      o.epsilon = opt->adam_epsilon;
+      const float lr = opt->adam_learning_rate;
+      o.lr_t = opt->use_adam_bias_correction ? lr * sqrtf(1.f - powf(opt->adam_beta2, t)) / (1.f - powf(opt->adam_beta1, t)) : lr;
+      net->nosadam_previous_beta2 += pw;
+      break;
+    }
     case MYEA_OPT_GD:
       o.gd_lr = opt->learning_rate;
       o.momentum = opt->learning_momentum;
       o.nesterov = opt->use_nesterov != 0;
       break;
-    default: return fail(net, MYEA_E_UNSUPPORTED, "optimizer not built (Adam, AMSGrad, AdaBound, AMSBound, gradient descent / momentum / Nesterov)");
+    default: return fail(net, MYEA_E_UNSUPPORTED, "optimizer not built (Adam, AMSGrad, NosAdam, AdaBound, AMSBound, gradient descent / momentum / Nesterov)");
+  }
+  const float max_norm = opt->regularization__max_norm_constraints;
+  if (max_norm != 0.f) {
+    for (const auto &L : net->layers)
+      if (L.type == MYEA_LAYER_LSTM) return fail(net, MYEA_E_UNSUPPORTED, "max-norm constraints on LSTM blocks are not built");
   }
   RC(optimizer_update(net->ctx, o, net->params, net->grads, net->m1, net->m2, net->m2hat, net->prev_delta, net->mask_reg, P));
+  if (max_norm != 0.f) {
+    // Update_Weight_Regularization__Max_Norm_Constraints__Neurons (…Max_Norm_Constraints.cpp:147-165): one weight row per neuron
+    for (const auto &L : net->layers)
+      if (L.type == MYEA_LAYER_FULLY_CONNECTED) RC(row_max_norm(net->ctx, net->params + L.idx.first_connection_index, L.n_out, L.n_in, max_norm));
+  }
   return MYEA_OK;
 }
 
@@ -790,6 +814,7 @@ extern "C" int myea_b200_clear_training_arrays(myea_handle net) {
   CK(cudaMemsetAsync(net->m2hat, 0, bytes, net->ctx.stream));
   CK(cudaMemsetAsync(net->prev_delta, 0, bytes, net->ctx.stream));
   net->optimizer_time_step = 0.f;
+  net->nosadam_previous_beta2 = 0.f;
   return MYEA_OK;
 }
 

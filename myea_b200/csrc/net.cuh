@@ -77,6 +77,7 @@ struct myea_b200_net {
   double *d_sumsq = nullptr;
   float *d_clip_scale = nullptr;
   float optimizer_time_step = 0.f;
+  float nosadam_previous_beta2 = 0.f;  // adam_previous_beta2 (Data.hpp:2953)
   bool training = true;
   myea::CommState *comm = nullptr;
   myea::SumHook hook;            // cross-GPU sum of normalization column sums (world 1: unused)

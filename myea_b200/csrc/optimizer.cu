@@ -151,4 +151,31 @@ int clip_scale_from_norm(Context &ctx, const double *d_sumsq, float clip, float 
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
+// one block per row: sum of squares (fp32 partials, tree), then the scale
+__global__ void __launch_bounds__(256) row_max_norm_kernel(float *__restrict__ w, long long cols, float max_norm) {
+  __shared__ float sh[256];
+  float *row = w + static_cast<long long>(blockIdx.x) * cols;
+  float acc = 0.f;
+  for (long long j = threadIdx.x; j < cols; j += blockDim.x) acc = fmaf(row[j], row[j], acc);
+  sh[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) sh[threadIdx.x] += sh[threadIdx.x + s];
+    __syncthreads();
+  }
+  const float norm = sqrtf(sh[0]);
+  if (norm >= max_norm) {
+    const float scale = max_norm / norm;
+    for (long long j = threadIdx.x; j < cols; j += blockDim.x) row[j] *= scale;
+  }
+}
+
+int row_max_norm(Context &ctx, float *w, long long rows, long long cols, float max_norm) {
+  if (rows <= 0 || cols <= 0) return MYEA_OK;
+  ctx.begin(TC_OPTIMIZER);
+  row_max_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, ctx.stream>>>(w, cols, max_norm);
+  ctx.end(TC_OPTIMIZER);
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
 }  // namespace myea

@@ -47,6 +47,7 @@ class Neural_Network {
   bool Set__Accurancy_Variance(float v) { desc_.accuracy_variance = v; return v >= 0.f; }
   bool Set__Number_Time_Delays(size_t d) { desc_.number_time_delays = d; return d < desc_.number_recurrent_depth; }
   bool Set__Regularization__Weight_Decay(float v) { opt_.regularization__weight_decay = v; return v >= 0.f; }
+  bool Set__Regularization__Max_Norm_Constraints(float v) { opt_.regularization__max_norm_constraints = v; return v >= 0.f; }
   void Set__Clip_Gradient(bool use) { opt_.use_clip_gradient = use ? 1u : 0u; }
   bool Set__Clip_Gradient(float v) { opt_.clip_gradient = v; return v > 0.f; }
   bool Set__Normalization_Momentum_Average(float v) { desc_.normalization_momentum_average = v; return v > 0.f && v <= 1.f; }

@@ -419,7 +419,19 @@ class OracleNet:
         decay = self.buf[capi.BUF_MASK_REGULARIZED] * wd * w if wd != 0 else 0
         kind = int(o.type_optimizer_function)
         b1, b2, eps = dt(o.adam_beta1), dt(o.adam_beta2), dt(o.adam_epsilon)
-        if kind in (capi.OPT_ADAM, capi.OPT_AMSGRAD, capi.OPT_ADABOUND, capi.OPT_AMSBOUND):
+        if kind == capi.OPT_NOSADAM:
+            # Neural_Network__NosAdam.cpp:97-160: beta2_t = B / (B + t^-gamma), then B += t^-gamma; bias correction with the fixed beta2
+            pw = np.power(t, -dt(o.adam_gamma if o.adam_gamma > 0 else 0.1), dtype=dt)
+            prev = dt(getattr(self, "nosadam_previous_beta2", 0.0))
+            b2t = prev / (prev + pw)
+            self.nosadam_previous_beta2 = dt(prev + pw)
+            lr = dt(o.adam_learning_rate)
+            lr_t = lr * np.sqrt(dt(1) - np.power(b2, t, dtype=dt)) / (dt(1) - np.power(b1, t, dtype=dt)) if o.use_adam_bias_correction else lr
+            m, v = self.buf[capi.BUF_FIRST_MOMENT], self.buf[capi.BUF_SECOND_MOMENT]
+            m[:] = b1 * m + (dt(1) - b1) * g
+            v[:] = b2t * v + (dt(1) - b2t) * g * g
+            w -= lr_t * m / (np.sqrt(v) + eps) + decay
+        elif kind in (capi.OPT_ADAM, capi.OPT_AMSGRAD, capi.OPT_ADABOUND, capi.OPT_AMSBOUND):
             lr = dt(o.adam_learning_rate)
             lr_t = lr * np.sqrt(dt(1) - np.power(b2, t, dtype=dt)) / (dt(1) - np.power(b1, t, dtype=dt)) if o.use_adam_bias_correction else lr
             m, v = self.buf[capi.BUF_FIRST_MOMENT], self.buf[capi.BUF_SECOND_MOMENT]
@@ -447,4 +459,13 @@ class OracleNet:
                     w -= mom * prev - lr * g + decay
                 else:
                     w -= prev + decay
+        c = dt(o.regularization__max_norm_constraints)
+        if c != 0:   # …Max_Norm_Constraints.cpp:147-165 + Euclidean_Norm__Loop :48-88: one weight row per neuron of every FC layer
+            for L in self.layers[1:]:
+                if L.type != capi.LAYER_FC:
+                    continue
+                W = self._fc_weights(L)   # a view into the parameter buffer
+                norms = np.sqrt((W * W).sum(axis=1, dtype=dt))
+                big = norms >= c
+                W[big] *= (c / norms[big])[:, None]
         g[:] = 0

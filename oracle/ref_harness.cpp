@@ -44,6 +44,8 @@ void apply_opt(Neural_Network &nn, const myea_opt_desc &o) {
   nn.use_adam_bias_correction = o.use_adam_bias_correction != 0;
   nn.use_normalized_weight_decay = o.use_normalized_weight_decay != 0;
   nn.epoch_time_step = o.epoch_time_step;
+  if (o.adam_gamma > 0.f) nn.adam_gamma = o.adam_gamma;
+  nn.Set__Regularization__Max_Norm_Constraints(o.regularization__max_norm_constraints);
 }
 
 // [T][B][W] packed block -> one contiguous [T*W] row per sample (Neural_Network__Assign_Inputs.cpp:273-304).

@@ -26,6 +26,9 @@ CASES = {
     # tensor-core kernel from operand panels shared between the forward and the backward readings
     "mlp_wide_bn_dropout_adam": lambda: _mlp_variant("wide", [144, 132], capi.AF_RELU, capi.opt(capi.OPT_ADAM), B=130, n_in=136, n_out=129,
                                                      norm=capi.NORM_BN, drop=capi.DROP_BERNOULLI_INVERTED, p=0.5),
+    "mlp_tanh_nosadam": lambda: _mlp_variant("nosadam", [20, 12], capi.AF_TANH, capi.opt(capi.OPT_NOSADAM, nosadam_gamma=0.1)),
+    # descent with a large rate so that rows do cross the bound and get rescaled
+    "mlp_relu_momentum_max_norm": lambda: _mlp_variant("maxnorm", [16, 16], capi.AF_RELU, capi.opt(capi.OPT_GD, gd_lr=0.05, momentum=0.9, max_norm=0.8)),
     "mlp_relu_gd": lambda: _mlp_variant("gd", [16, 16], capi.AF_RELU, capi.opt(capi.OPT_GD, gd_lr=0.01)),
     "mlp_selu_momentum": lambda: _mlp_variant("mom", [16], capi.AF_SELU, capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9)),
     "mlp_tanh_nesterov_ce": lambda: _mlp_variant("nag", [16], capi.AF_TANH, capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9, nesterov=True),
