@@ -8,6 +8,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <utility>
 
 #include "myea_b200.h"
 
@@ -32,6 +33,7 @@ struct Context {
   std::string error;
   int gemm_engine = 0;  // 0 = tcgen05 3xTF32, 1 = FP32 FMA
   int gemm_bn = 0;      // forced N tile of the tcgen05 kernel (0 = heuristic)
+  bool dependent_launch = true;  // programmatic dependent launch for the kernels that support it (MYEA_B200_PDL=0 turns it off)
   float *sk_ws = nullptr;               // partial sums of tiles split along K (gemm_splitk_reserve)
   unsigned int *sk_counters = nullptr;  // arrival counters of those tiles, all zero between launches
   int sk_clusters = 0;                  // clusters the workspace has slots for
@@ -51,6 +53,33 @@ struct Context {
     }
   }
 };
+
+// ---------------------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched through launch_dependent() may begin (block scheduling, barrier
+// and tensor-memory setup) while the kernel before it in the stream is still draining; it must call
+// grid_dependency_wait() before its first access to global memory - the wait returns when the preceding kernel has
+// completed and its writes are visible - and calls grid_dependency_release() so that ITS successor may start early too.
+// Launched the ordinary way the two calls do nothing.
+// ---------------------------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_dependent(const Context &ctx, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx.stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = (ctx.dependent_launch && !ctx.profiling) ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#endif
 
 // ---------------------------------------------------------------------------------------------------------
 // Activation functions, value and derivative, exactly as the reference codes them (steepness 1):

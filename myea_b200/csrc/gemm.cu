@@ -473,6 +473,8 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   if (threadIdx.x == 0) TL(1);
+  grid_dependency_wait();     // everything above touched no global memory
+  grid_dependency_release();
 
   bool ok = true;
   if (warp == 0) {
@@ -882,6 +884,8 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   if (threadIdx.x == 0) TL(1);
+  grid_dependency_wait();     // everything above touched no global memory
+  grid_dependency_release();
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -1132,6 +1136,8 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
 __global__ void split_rows_kernel(const float *__restrict__ src, long long stride_r, long long rows, long long k, long long kp,
                                   float *__restrict__ hi, float *__restrict__ cross, int role_b, int raw,
                                   uint16_t *__restrict__ cross_mn = nullptr, int role_mn_b = 0) {
+  grid_dependency_wait();
+  grid_dependency_release();
   const long long kg = (k + 7) >> 3;  // groups of 8 per panel row
   const long long rows_all = cross_mn != nullptr ? ((rows + 7) & ~7ll) : rows;
   const long long total = rows_all * kg;
@@ -1321,8 +1327,8 @@ int gemm_prepare_shared(Context &ctx, const float *src, long long stride_r, long
   int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
   if (blocks < 1) blocks = 1;
   ctx.begin(TC_SPLIT);
-  split_rows_kernel<<<blocks, 256, 0, ctx.stream>>>(src, stride_r, R, C, pitch, hi, as_rows != nullptr ? cross_k : nullptr, role_rows, raw,
-                                                    as_cols != nullptr ? cross_mn : nullptr, role_cols);
+  launch_dependent(ctx, split_rows_kernel, dim3(blocks), dim3(256), 0, src, stride_r, R, C, pitch, hi, as_rows != nullptr ? cross_k : nullptr, role_rows,
+                   raw, as_cols != nullptr ? cross_mn : nullptr, role_cols);
   ctx.end(TC_SPLIT);
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
@@ -1363,7 +1369,8 @@ int gemm_prepare_into(Context &ctx, const Operand &op, const Panels &dst, long l
     const long long total = op.rows * ((op.k + 7) >> 3);
     int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
     if (blocks < 1) blocks = 1;
-    split_rows_kernel<<<blocks, 256, 0, ctx.stream>>>(op.ptr, op.stride_r, op.rows, op.k, dst.kp, hi, lo, dst.role, raw);
+    launch_dependent(ctx, split_rows_kernel, dim3(blocks), dim3(256), 0, op.ptr, op.stride_r, op.rows, op.k, dst.kp, hi, lo, dst.role, raw,
+                     static_cast<uint16_t *>(nullptr), 0);
   } else {
     dim3 grid(static_cast<unsigned>((op.rows + 31) / 32), static_cast<unsigned>((op.k + 31) / 32));
     split_transpose_kernel<<<grid, dim3(32, 8), 0, ctx.stream>>>(op.ptr, op.stride_k, op.rows, op.k, dst.kp, hi, lo, dst.role, raw);
@@ -1381,8 +1388,8 @@ int gemm_prepare_interleaved(Context &ctx, const Operand &op, const Panels &dst,
   if (blocks < 1) blocks = 1;
   ctx.begin(TC_SPLIT);
   // the kernel only sees a wider pitch: source row r lands on panel row row_offset + r * row_step
-  split_rows_kernel<<<blocks, 256, 0, ctx.stream>>>(op.ptr, op.stride_r, op.rows, op.k, dst.kp * row_step, dst.hi + row_offset * dst.kp,
-                                                    dst.lo + row_offset * dst.kp, dst.role, raw);
+  launch_dependent(ctx, split_rows_kernel, dim3(blocks), dim3(256), 0, op.ptr, op.stride_r, op.rows, op.k, dst.kp * row_step,
+                   dst.hi + row_offset * dst.kp, dst.lo + row_offset * dst.kp, dst.role, raw, static_cast<uint16_t *>(nullptr), 0);
   ctx.end(TC_SPLIT);
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
@@ -1402,8 +1409,8 @@ static int launch_tcgen05(Context &ctx, const CUtensorMap maps[4], const GemmDim
     configured[ctx.device & 15] = true;
   }
   dim3 grid(static_cast<unsigned>((dims.N + BN - 1) / BN), static_cast<unsigned>((dims.M + BM - 1) / BM));
-  gemm3x_tf32_tcgen05_kernel<BN, STAGES><<<grid, GEMM_THREADS, S::TOTAL, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], dims, epi,
-                                                                                     ctx.d_error_flag);
+  launch_dependent(ctx, gemm3x_tf32_tcgen05_kernel<BN, STAGES>, grid, dim3(GEMM_THREADS), S::TOTAL, maps[0], maps[1], maps[2], maps[3], dims, epi,
+                   ctx.d_error_flag);
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
@@ -1511,8 +1518,8 @@ static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const Ge
       grid_clusters = work.dp_tiles > 0 ? G : used;
     }
   }
-  kernel<<<dim3(static_cast<unsigned>(2 * grid_clusters)), WIDE_THREADS, WideSmem::TOTAL, ctx.stream>>>(
-      maps[0], maps[1], maps[2], maps[3], dims, work, epi, ctx.d_error_flag);
+  launch_dependent(ctx, kernel, dim3(static_cast<unsigned>(2 * grid_clusters)), dim3(WIDE_THREADS), WideSmem::TOTAL, maps[0], maps[1], maps[2],
+                   maps[3], dims, work, epi, ctx.d_error_flag);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess && getenv("MYEA_B200_DEBUG") != nullptr) fprintf(stderr, "wide kernel launch: %s\n", cudaGetErrorString(err));
   return err == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;

@@ -229,6 +229,8 @@ __global__ void lstm_bias_peephole_finalize_kernel(const float *__restrict__ par
 // arithmetic of lstm_cell_forward_kernel / lstm_cell_backward_kernel, and the results also leave as the operand panels
 // of the next step's contraction (no separate split pass).  p.kind selects; s_rec / rec_dh is the contraction's output.
 __global__ void __launch_bounds__(256) lstm_cells8_forward_kernel(const LstmFuse p, const float *__restrict__ s_rec, long long B) {
+  grid_dependency_wait();
+  grid_dependency_release();
   const long long groups = p.C >> 3, total = B * groups;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -243,6 +245,8 @@ __global__ void __launch_bounds__(256) lstm_cells8_forward_kernel(const LstmFuse
 }
 // the error through time has already been added into p.dh by the contraction (accumulate epilogue): rec = 0
 __global__ void __launch_bounds__(256) lstm_cells8_backward_kernel(const LstmFuse p, long long B) {
+  grid_dependency_wait();
+  grid_dependency_release();
   const long long groups = p.C >> 3, total = B * groups;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -471,7 +475,7 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
           e.ldc = 4 * C;
           LRC(gemm_panels(ctx, ph_prev, 0, B, pwrec, 0, 4 * C, e));
           ctx.begin(TC_RECURRENT);
-          lstm_cells8_forward_kernel<<<cell_blocks(B * C / 8), 256, 0, ctx.stream>>>(f, P->s_rec, B);
+          launch_dependent(ctx, lstm_cells8_forward_kernel, dim3(cell_blocks(B * C / 8)), dim3(256), 0, f, static_cast<const float *>(P->s_rec), B);
           ctx.end(TC_RECURRENT);
         }
         continue;
@@ -563,7 +567,7 @@ int lstm_backward(myea_b200_net *net, LayerPlan &L) {
           e.accumulate = 1;
           LRC(gemm_panels(ctx, pd_prev, 0, B, pwt, 0, C, e));
           ctx.begin(TC_RECURRENT);
-          lstm_cells8_backward_kernel<<<cell_blocks(B * C / 8), 256, 0, ctx.stream>>>(f, B);
+          launch_dependent(ctx, lstm_cells8_backward_kernel, dim3(cell_blocks(B * C / 8)), dim3(256), 0, f, B);
           ctx.end(TC_RECURRENT);
         }
         continue;

@@ -334,6 +334,8 @@ extern "C" int myea_b200_create(myea_handle *out, const myea_net_desc *desc, int
   if (eng != nullptr && eng[0] == '1') net->ctx.gemm_engine = 1;
   const char *tile = getenv("MYEA_B200_GEMM_TILE");  // 2 = CTA pairs, 128 / 256 = single-CTA column tile, unset = heuristic
   if (tile != nullptr) net->ctx.gemm_bn = atoi(tile);
+  const char *pdl = getenv("MYEA_B200_PDL");  // 0 = launch every kernel fully serialised
+  if (pdl != nullptr && pdl[0] == '0') net->ctx.dependent_launch = false;
   *out = net;  // returned even on failure so that the caller can read last_error, then destroy
   if (cudaStreamCreateWithFlags(&net->ctx.stream, cudaStreamNonBlocking) != cudaSuccess) return fail(net, MYEA_E_CUDA, "cudaStreamCreate failed");
   cudaEventCreate(&net->ctx.ev0);
