@@ -86,7 +86,7 @@ inline cudaError_t launch_dependent(const Context &ctx, void (*kernel)(KernelArg
 // tanh is 2/(1+e^-2z)-1 (Activation_Functions.hpp:45), sigmoid 1/(1+e^-z) (:40); the ELU derivative below zero is
 // alpha*y with y = e^z-1 (:93-94), not alpha*e^z; the softmax derivative is 1 (cross-entropy pairing).
 // ---------------------------------------------------------------------------------------------------------
-__host__ __device__ inline float af_fire(uint32_t af, float z) {
+__host__ __device__ __forceinline__ float af_fire(uint32_t af, float z) {
   switch (af) {
     case MYEA_AF_TANH: return 2.0f / (1.0f + expf(-2.0f * z)) - 1.0f;
     case MYEA_AF_SIGMOID: return 1.0f / (1.0f + expf(-z));
@@ -98,7 +98,7 @@ __host__ __device__ inline float af_fire(uint32_t af, float z) {
   }
 }
 
-__host__ __device__ inline float af_derive(uint32_t af, float z, float y) {
+__host__ __device__ __forceinline__ float af_derive(uint32_t af, float z, float y) {
   switch (af) {
     case MYEA_AF_TANH: return 1.0f - y * y;
     case MYEA_AF_SIGMOID: return y * (1.0f - y);

@@ -331,65 +331,102 @@ __device__ __forceinline__ int epilogue_mode(const Epilogue &e) {
   return e.accumulate ? 2 : 0;
 }
 
-// Epilogue of output row m, columns [col0, col0 + 32), the accumulator values in v: the thread owns the row (that is how
-// tensor memory hands an accumulator to a warp: lane = row), so every access is a float4 of this row.  The loads of four
-// float4 columns are issued before their first use.  ADD / DERIV / ACC say what MAY be present.
+// Epilogue of a 32-row x 32-column block, warp-collective: lane l holds row row0 + l (that is how tensor memory hands an
+// accumulator to a warp), but global memory wants rows of 128 contiguous bytes.  The block goes through a 16 x 36
+// float staging buffer in shared memory, half at a time: the owning lanes write their rows as float4 (conflict-free at
+// pitch 36), then every lane takes one float4 column slot (lane % 8) of the rows lane / 8 + 4 i, so that each global
+// instruction of the warp covers four full 128-byte row segments.  The loads of the four rows are issued before their
+// first use.  ADD / DERIV / ACC say what MAY be present.  `tr`: this warp's 16 * 36 floats.
+constexpr int TR_PITCH = 36;
+constexpr int TR_WARP_FLOATS = 16 * TR_PITCH;
+
+// x[i] *= f'(z[i], y[i]) for four float4; the activation is the same for the whole launch, so the switch is taken once
+// per call and every case is straight-line code (a switch per element made this epilogue as long as a whole tile's
+// main loop)
+template <uint32_t AF>
+__device__ __forceinline__ void derive4x4(float4 (&x)[4], const float4 (&z)[4], const float4 (&y)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[i].x *= af_derive(AF, z[i].x, y[i].x);
+    x[i].y *= af_derive(AF, z[i].y, y[i].y);
+    x[i].z *= af_derive(AF, z[i].z, y[i].z);
+    x[i].w *= af_derive(AF, z[i].w, y[i].w);
+  }
+}
+__device__ __forceinline__ void derive4x4_any(uint32_t af, float4 (&x)[4], const float4 (&z)[4], const float4 (&y)[4]) {
+  switch (af) {
+    case MYEA_AF_TANH: derive4x4<MYEA_AF_TANH>(x, z, y); break;
+    case MYEA_AF_SIGMOID: derive4x4<MYEA_AF_SIGMOID>(x, z, y); break;
+    case MYEA_AF_RELU: derive4x4<MYEA_AF_RELU>(x, z, y); break;
+    case MYEA_AF_LEAKY_RELU: derive4x4<MYEA_AF_LEAKY_RELU>(x, z, y); break;
+    case MYEA_AF_ELU: derive4x4<MYEA_AF_ELU>(x, z, y); break;
+    case MYEA_AF_SELU: derive4x4<MYEA_AF_SELU>(x, z, y); break;
+    default: break;  // linear, softmax: derivative 1
+  }
+}
+
 template <bool ADD, bool DERIV, bool ACC>
-__device__ __forceinline__ void epilogue_row32_vec(const Epilogue &e, const float (&v)[32], long long m, long long col0) {
-  float *__restrict__ c = e.C + m * e.ldc + col0;
-  const float *__restrict__ p_add = (ADD && e.addend != nullptr) ? e.addend + m * e.ld_addend + col0 : nullptr;
-  const float *__restrict__ p_pre = (DERIV && e.aux_pre != nullptr) ? e.aux_pre + m * e.ld_aux + col0 : nullptr;
-  const float *__restrict__ p_y = (DERIV && e.aux_y != nullptr) ? e.aux_y + m * e.ld_aux + col0 : nullptr;
-  const bool affine = DERIV && p_pre != nullptr && e.col_scale != nullptr;
+__device__ __forceinline__ void epilogue_block32(const Epilogue &e, float *tr, const float (&v)[32], int lane, long long row0, long long col0, int M) {
+  const int c4 = (lane & 7) * 4, rsub = lane >> 3;
+  const long long n = col0 + c4;
+  const bool has_add = ADD && e.addend != nullptr, has_pre = DERIV && e.aux_pre != nullptr, has_y = DERIV && e.aux_y != nullptr;
+  const bool affine = has_pre && e.col_scale != nullptr;
   const bool acc = ACC && e.accumulate;
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 bias = e.bias != nullptr ? ld4(e.bias + n) : zero;
+  const float4 cs = affine ? ld4(e.col_scale + n) : make_float4(1.f, 1.f, 1.f, 1.f), ch = affine ? ld4(e.col_shift + n) : zero;
 #pragma unroll
-  for (int g = 0; g < 2; ++g) {
+  for (int h = 0; h < 2; ++h) {
+    __syncwarp();
+    if ((lane >> 4) == h) {
+      float *dst = tr + (lane & 15) * TR_PITCH;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) *reinterpret_cast<float4 *>(dst + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    }
+    __syncwarp();
     float4 add[4], pre[4], y[4], old[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int j = (g * 4 + i) * 4;
-      if (ADD) add[i] = p_add != nullptr ? ld4(p_add + j) : zero;
+      const long long m = row0 + h * 16 + rsub + 4 * i;
+      const bool in = m < M;
+      if (ADD) add[i] = (has_add && in) ? ld4(e.addend + m * e.ld_addend + n) : zero;
       if (DERIV) {
-        pre[i] = p_pre != nullptr ? ld4(p_pre + j) : zero;
-        y[i] = p_y != nullptr ? ld4(p_y + j) : zero;
+        pre[i] = (has_pre && in) ? ld4(e.aux_pre + m * e.ld_aux + n) : zero;
+        y[i] = (has_y && in) ? ld4(e.aux_y + m * e.ld_aux + n) : zero;
       }
-      if (ACC) old[i] = acc ? ld4(c + j) : zero;
+      if (ACC) old[i] = (acc && in) ? ld4(e.C + m * e.ldc + n) : zero;
     }
+    float4 x[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int j = (g * 4 + i) * 4;
-      float4 x = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-      if (e.bias != nullptr) {
-        const float4 b = ld4(e.bias + col0 + j);
-        x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
-      }
-      if (ADD) { x.x += add[i].x; x.y += add[i].y; x.z += add[i].z; x.w += add[i].w; }
+      x[i] = *reinterpret_cast<const float4 *>(tr + (rsub + 4 * i) * TR_PITCH + c4);
+      x[i].x += bias.x; x[i].y += bias.y; x[i].z += bias.z; x[i].w += bias.w;
+      if (ADD) { x[i].x += add[i].x; x[i].y += add[i].y; x[i].z += add[i].z; x[i].w += add[i].w; }
       if (DERIV) {
-        float4 z = pre[i];
-        if (affine) {
-          const float4 cs = ld4(e.col_scale + col0 + j), ch = ld4(e.col_shift + col0 + j);
-          z.x = z.x * cs.x + ch.x; z.y = z.y * cs.y + ch.y; z.z = z.z * cs.z + ch.z; z.w = z.w * cs.w + ch.w;
-        }
-        x.x *= af_derive(e.deriv_af, z.x, y[i].x);
-        x.y *= af_derive(e.deriv_af, z.y, y[i].y);
-        x.z *= af_derive(e.deriv_af, z.z, y[i].z);
-        x.w *= af_derive(e.deriv_af, z.w, y[i].w);
+        pre[i].x = pre[i].x * cs.x + ch.x; pre[i].y = pre[i].y * cs.y + ch.y; pre[i].z = pre[i].z * cs.z + ch.z; pre[i].w = pre[i].w * cs.w + ch.w;
       }
-      if (ACC) { x.x += old[i].x; x.y += old[i].y; x.z += old[i].z; x.w += old[i].w; }
-      *reinterpret_cast<float4 *>(c + j) = x;
+    }
+    if (DERIV) derive4x4_any(e.deriv_af, x, pre, y);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const long long m = row0 + h * 16 + rsub + 4 * i;
+      if (ACC) { x[i].x += old[i].x; x[i].y += old[i].y; x[i].z += old[i].z; x[i].w += old[i].w; }
+      if (m < M) *reinterpret_cast<float4 *>(e.C + m * e.ldc + n) = x[i];
     }
   }
 }
 
-__device__ __forceinline__ void epilogue_row32(const Epilogue &e, const float (&v)[32], long long m, long long col0, int M, int N,
-                                               bool vec_ok, int mode) {
-  if (m >= M || col0 >= N) return;
-  if (e.lstm.kind == 1) {  // 32 columns = 8 cells x 4 gates
-    lstm_forward_cells8(e.lstm, v, m, col0 >> 2);
+// Warp-collective: every lane of the warp calls it (row0, col0, M, N are the same for all of them).
+__device__ __forceinline__ void epilogue_row32(const Epilogue &e, const float (&v)[32], long long row0, int lane, long long col0, int M, int N,
+                                               bool vec_ok, int mode, float *tr) {
+  const long long m = row0 + lane;
+  if (col0 >= N) return;
+  if (e.lstm.kind == 1) {  // 32 columns = 8 cells x 4 gates; the thread keeps its row
+    if (m < M) lstm_forward_cells8(e.lstm, v, m, col0 >> 2);
     return;
   }
   if (e.lstm.kind == 2) {  // 32 columns = 32 cells (N = C is a multiple of 8)
+    if (m >= M) return;
 #pragma unroll
     for (int g8 = 0; g8 < 4; ++g8) {
       if (col0 + g8 * 8 < N) {
@@ -403,12 +440,12 @@ __device__ __forceinline__ void epilogue_row32(const Epilogue &e, const float (&
   }
   if (vec_ok && col0 + 32 <= N) {
     switch (mode) {
-      case 0: epilogue_row32_vec<false, false, false>(e, v, m, col0); break;
-      case 1: epilogue_row32_vec<false, true, false>(e, v, m, col0); break;
-      case 2: epilogue_row32_vec<false, false, true>(e, v, m, col0); break;
-      default: epilogue_row32_vec<true, true, true>(e, v, m, col0); break;
+      case 0: epilogue_block32<false, false, false>(e, tr, v, lane, row0, col0, M); break;
+      case 1: epilogue_block32<false, true, false>(e, tr, v, lane, row0, col0, M); break;
+      case 2: epilogue_block32<false, false, true>(e, tr, v, lane, row0, col0, M); break;
+      default: epilogue_block32<true, true, true>(e, tr, v, lane, row0, col0, M); break;
     }
-  } else {  // ragged right edge or unaligned arrays: one element at a time
+  } else if (m < M) {  // ragged right edge or unaligned arrays: one element at a time, the thread keeps its row
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const long long n = col0 + j;
@@ -545,6 +582,8 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
       const long long row_base = static_cast<long long>(m0) + q * 32;
       const bool vec_ok = epilogue_vector_ok(epi);
       const int mode = epilogue_mode(epi);
+      // every MMA has completed, so the pipeline stages are free: the first bytes serve as the staging buffers
+      float *tr = reinterpret_cast<float *>(smem) + (warp - 2) * TR_WARP_FLOATS;
       TL_DECL(t_ld);
       TL_DECL(t_tr);
       TL_DECL(t_out);
@@ -570,7 +609,7 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
         TL_BEGIN(t_tr);
         TL_END(t_tr);
         TL_BEGIN(t_out);
-        epilogue_row32(epi, sum, row_base + lane, static_cast<long long>(n0) + c, dims.M, dims.N, vec_ok, mode);
+        epilogue_row32(epi, sum, row_base, lane, static_cast<long long>(n0) + c, dims.M, dims.N, vec_ok, mode, tr);
         TL_END(t_out);
       }
       if (warp == 2 && lane == 0) { TL_STORE(11, t_ld); TL_STORE(12, t_tr); TL_STORE(13, t_out); }
@@ -711,6 +750,8 @@ gemm3x_tf32_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
       const long long row_base = static_cast<long long>(m0) + q * 32;
       const bool vec_ok = epilogue_vector_ok(epi);
       const int mode = epilogue_mode(epi);
+      // every MMA has completed, so the pipeline stages are free: the first bytes serve as the staging buffers
+      float *tr = reinterpret_cast<float *>(smem) + (warp - 2) * TR_WARP_FLOATS;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= dims.N) break;
@@ -728,7 +769,7 @@ gemm3x_tf32_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
 #pragma unroll
           for (int j = 0; j < 32; ++j) sum[j] += __uint_as_float(r[j]);
         }
-        epilogue_row32(epi, sum, row_base + lane, static_cast<long long>(n0) + c, dims.M, dims.N, vec_ok, mode);
+        epilogue_row32(epi, sum, row_base, lane, static_cast<long long>(n0) + c, dims.M, dims.N, vec_ok, mode, tr);
       }
     }
   }
@@ -768,7 +809,8 @@ struct WideSmem {
   static constexpr int TILE_BYTES = 128 * BK * 4;           // 128 rows x 128 bytes
   static constexpr int STAGE_BYTES = 4 * TILE_BYTES;        // A hi, A cross, B hi, B cross
   static constexpr int BAR_OFFSET = WIDE_STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;
+  static constexpr int TR_OFFSET = BAR_OFFSET + 512;        // epilogue staging: 8 warps x 16 x 36 floats (the stages stay busy)
+  static constexpr int TOTAL = TR_OFFSET + 8 * TR_WARP_FLOATS * 4 + 1024;
 };
 
 // Work list of the wide kernel.  Tiles [0, dp_tiles) are computed whole, round-robin over the clusters.  The K chunks
@@ -977,6 +1019,7 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
     const int region = static_cast<int>(cta_rank) * 8 + (warp - 2);  // this warp's 32 x 128 share of the pair's tile
     const bool vec_ok = epilogue_vector_ok(epi);
     const int mode = epilogue_mode(epi);
+    float *tr = reinterpret_cast<float *>(smem + S::TR_OFFSET) + (warp - 2) * TR_WARP_FLOATS;
     bool ok = true;
     uint32_t g = 0;
     TL_DECL(w_accfull);
@@ -1036,7 +1079,7 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
           __threadfence();
           int tm, tn;
           wide_tile_coords(work, seg.tile, tm, tn);
-          const long long m = static_cast<long long>(tm) * 256 + static_cast<long long>(cta_rank) * 128 + q * 32 + lane;
+          const long long row0 = static_cast<long long>(tm) * 256 + static_cast<long long>(cta_rank) * 128 + q * 32;
           const long long col_base = static_cast<long long>(tn) * BN + half * 128;
           if (last == first + 1) {
             // two contributors (the usual case): a + b is the same whichever of them is last, so the sum in registers
@@ -1082,7 +1125,7 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
                   }
                 }
               }
-              epilogue_row32(epi, acc, m, col_base + jc * 32, dims.M, dims.N, vec_ok, mode);
+              epilogue_row32(epi, acc, row0, lane, col_base + jc * 32, dims.M, dims.N, vec_ok, mode, tr);
             }
             finish = false;  // already written
           }
@@ -1091,14 +1134,14 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
       if (finish) {
         int tm, tn;
         wide_tile_coords(work, seg.tile, tm, tn);
-        const long long m = static_cast<long long>(tm) * 256 + static_cast<long long>(cta_rank) * 128 + q * 32 + lane;
+        const long long row0 = static_cast<long long>(tm) * 256 + static_cast<long long>(cta_rank) * 128 + q * 32;
         const long long col_base = static_cast<long long>(tn) * BN + half * 128;
 #pragma unroll
         for (int jc = 0; jc < 4; ++jc) {
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = sum[jc * 32 + j];
-          epilogue_row32(epi, v, m, col_base + jc * 32, dims.M, dims.N, vec_ok, mode);
+          epilogue_row32(epi, v, row0, lane, col_base + jc * 32, dims.M, dims.N, vec_ok, mode, tr);
         }
       }
       if (g <= static_cast<uint32_t>(num_chunks) && warp == 2 && lane == 0) TL(7);

@@ -17,7 +17,7 @@ extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N,
   ctx.gemm_engine = engine & 1;
   ctx.gemm_bn = (engine >> 8) & 0x1FF;  // bits 8..16: forced tile shape (0 = heuristic, 3 = 256 x 256 CTA pair, 4 = the same without stream-K, 2 = 256 x 128 CTA pair, 128 / 256 = single-CTA N tile)
   int rc = MYEA_OK;
-  float *dA = nullptr, *dB = nullptr, *dC = nullptr, *dS = nullptr;
+  float *dA = nullptr, *dB = nullptr, *dC = nullptr, *dS = nullptr, *dAux = nullptr;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   // bits 17 / 18: A / B are handed over transposed ([K][M] / [K][N] row-major) and read as MN-major operands
   const bool a_t = (engine >> 17) & 1, b_t = (engine >> 18) & 1;
@@ -43,6 +43,19 @@ extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N,
     epi.C = dC;
     epi.ldc = (long long)N;
     epi.accumulate = accumulate;
+    if ((engine >> 19) & 1) {
+      // bit 19: the fused activation-derivative epilogue of the error-propagation product, for kernel-level tests:
+      // C = (A * B^T) .* relu'(C_in), the incoming C serving as the pre-activation array
+      if (cudaMalloc(&dAux, M * N * 4) != cudaSuccess) rc = MYEA_E_CUDA;
+      else {
+        cudaMemcpyAsync(dAux, C, M * N * 4, cudaMemcpyHostToDevice, ctx.stream);
+        epi.deriv_af = ((engine >> 21) & 1) ? MYEA_AF_TANH : MYEA_AF_RELU;   // bits 20 / 21: timing variants (one array only)
+        epi.aux_pre = ((engine >> 21) & 1) ? nullptr : dAux;
+        epi.aux_y = ((engine >> 20) & 1) ? nullptr : dAux;
+        epi.ld_aux = (long long)N;
+        epi.accumulate = 0;
+      }
+    }
     GemmScratch gs{dS, scratch};
     auto run = [&]() -> int {
       if (!a_t && !b_t) return gemm_nt(ctx, oa, ob, epi, gs);
@@ -90,6 +103,7 @@ extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N,
   if (e0) cudaEventDestroy(e0);
   if (e1) cudaEventDestroy(e1);
   cudaFree(dA); cudaFree(dB); cudaFree(dC); cudaFree(dS); cudaFree(ctx.d_error_flag);
+  if (dAux != nullptr) cudaFree(dAux);
   gemm_splitk_release(ctx);
   cudaStreamDestroy(ctx.stream);
   return rc;
