@@ -208,6 +208,9 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t *bar, uint32_t cta)
       "r"(cta)
       : "memory");
 }
+// setmaxnreg: a warpgroup (4 aligned warps) hands registers back to the SM / takes more; the count is a multiple of 8
+template <int N> __device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
 // Bounded wait that gives up at once when another wait of this CTA has already failed (keeps the worst case short).
@@ -802,7 +805,11 @@ gemm3x_tf32_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
 // Tiles are numbered in bands of 8 row tiles so that the tiles in flight at one time share operand panels in L2.
 // ---------------------------------------------------------------------------------------------------------
 constexpr int WIDE_STAGES = 3;
-constexpr int WIDE_THREADS = 320;  // warp 0 TMA, warp 1 MMA + tensor-memory allocation, warps 2-9 drain / epilogue
+// Three warpgroups: warps 0-3 hold the two single-thread roles (warp 0 TMA, warp 1 MMA + tensor-memory allocation;
+// warps 2-3 idle) and give most of their registers away; warps 4-11 drain and run the epilogue with 232 registers each
+// (setmaxnreg), which is what keeps the 128-float running sum and the epilogue's loads out of local memory.
+constexpr int WIDE_THREADS = 384;
+constexpr int WIDE_DRAIN_WARP0 = 4;
 constexpr int WIDE_KC = 8;
 constexpr int WIDE_BAND = 8;
 struct WideSmem {
@@ -931,6 +938,7 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
+    ptx::reg_release<40>();
     if (lane == 0) {
       bool ok = true;
       uint32_t it = 0;  // k-blocks staged so far, over all segments
@@ -959,6 +967,7 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA) ----------------
+    ptx::reg_release<40>();
     if (lane == 0 && cta_rank == 0) {
       bool ok = true;
       constexpr uint32_t idesc_main = make_idesc_tf32(256, BN, A_MN, B_MN);
@@ -1012,14 +1021,15 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
       TL_STORE(9, w_acc);
       if (!ok) atomicCAS(error_flag, 0, 302);
     }
-  } else {
-    // ---------------- drain + epilogue: 8 warps; lane quarter = warp % 4, column half = (warp - 2) / 4 ----------------
+  } else if (warp >= WIDE_DRAIN_WARP0) {
+    // ---------------- drain + epilogue: 8 warps; lane quarter = warp % 4, column half = (warp - 4) / 4 ----------------
+    ptx::reg_acquire<232>();
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;
-    const int region = static_cast<int>(cta_rank) * 8 + (warp - 2);  // this warp's 32 x 128 share of the pair's tile
+    const int half = (warp - WIDE_DRAIN_WARP0) >> 2;
+    const int region = static_cast<int>(cta_rank) * 8 + (warp - WIDE_DRAIN_WARP0);  // this warp's 32 x 128 share of the pair's tile
     const bool vec_ok = epilogue_vector_ok(epi);
     const int mode = epilogue_mode(epi);
-    float *tr = reinterpret_cast<float *>(smem + S::TR_OFFSET) + (warp - 2) * TR_WARP_FLOATS;
+    float *tr = reinterpret_cast<float *>(smem + S::TR_OFFSET) + (warp - WIDE_DRAIN_WARP0) * TR_WARP_FLOATS;
     bool ok = true;
     uint32_t g = 0;
     TL_DECL(w_accfull);
@@ -1052,7 +1062,7 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(&acc_empty_bar[b], 0);
       }
-      if (g <= static_cast<uint32_t>(num_chunks) && warp == 2 && lane == 0) { TL(6); TL_STORE(10, w_accfull); }
+      if (g <= static_cast<uint32_t>(num_chunks) && warp == WIDE_DRAIN_WARP0 && lane == 0) { TL(6); TL_STORE(10, w_accfull); }
       if (!ok || num_kb <= 0) break;
       bool finish = true;  // this warp writes its share of the tile
       if (seg.c0 != 0 || seg.c1 != num_chunks) {
@@ -1144,8 +1154,10 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
           epilogue_row32(epi, v, row0, lane, col_base + jc * 32, dims.M, dims.N, vec_ok, mode, tr);
         }
       }
-      if (g <= static_cast<uint32_t>(num_chunks) && warp == 2 && lane == 0) TL(7);
+      if (g <= static_cast<uint32_t>(num_chunks) && warp == WIDE_DRAIN_WARP0 && lane == 0) TL(7);
     }
+  } else {
+    ptx::reg_release<40>();  // warps 2-3: no role, but the whole warpgroup has to give its registers back
   }
   // every role leaves its loop only when its segments are done or a wait has given up; the pair stays together until
   // both CTAs are here, so nobody signals a barrier of a CTA that has exited
