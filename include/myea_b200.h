@@ -255,7 +255,8 @@ uint64_t myea_b200_kernel_launches(myea_handle h);
  * product + bf16 cross terms; bit 0 of `engine` clear) or with the FP32 FMA kernel (bit 0 set).  Bits 8..16 of
  * `engine` force a tile shape (0 heuristic, 128 single CTA, 2 CTA pair 256x128, 3 CTA pair 256x256, 4 the same
  * without splitting tiles along K); bit 17 / bit 18: A / B is handed over transposed, [K][M] / [K][N] row-major,
- * and read as it lies (256x256 kernel only).  `elapsed_ms` (may be null) receives the mean device time of `repeats`
+ * and read as it lies (256x256 kernel only); bit 19: C = (A·B^T) .* relu'(C on entry), the fused activation-derivative
+ * epilogue of the error-propagation product, for kernel-level tests (bits 20 / 21: timing variants of it).  `elapsed_ms` (may be null) receives the mean device time of `repeats`
  * extra runs.  Replaces the triple loops
  * Forward_Pass__FC / Backward_Pass__FC / Update_Derivative_Weight__FC
  * (Neural_Network__Forward_Pass__OpenMP.cpp:4517, …Backward_Pass__OpenMP.cpp:1044, …Update_Derivative_Weight__OpenMP.cpp:178). */

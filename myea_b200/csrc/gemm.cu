@@ -378,8 +378,33 @@ __device__ __forceinline__ void epilogue_block32(const Epilogue &e, float *tr, c
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
   const float4 bias = e.bias != nullptr ? ld4(e.bias + n) : zero;
   const float4 cs = affine ? ld4(e.col_scale + n) : make_float4(1.f, 1.f, 1.f, 1.f), ch = affine ? ld4(e.col_shift + n) : zero;
+  // The global reads of BOTH halves go out before anything else (one memory round trip per block instead of two);
+  // the variant that may read all four arrays keeps to one half at a time for the sake of registers.
+  constexpr bool AHEAD = !(ADD && DERIV && ACC);
+  constexpr int SLOTS = AHEAD ? 8 : 4;
+  float4 add[ADD ? SLOTS : 1], pre[DERIV ? SLOTS : 1], y[DERIV ? SLOTS : 1], old[ACC ? SLOTS : 1];
+  auto load_rows = [&](int first_slot, int h0, int h1) {
+#pragma unroll
+    for (int h = h0; h < h1; ++h) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int s = first_slot + (h - h0) * 4 + i;
+        const long long m = row0 + h * 16 + rsub + 4 * i;
+        const bool in = m < M;
+        if (ADD) add[s] = (has_add && in) ? ld4(e.addend + m * e.ld_addend + n) : zero;
+        if (DERIV) {
+          pre[s] = (has_pre && in) ? ld4(e.aux_pre + m * e.ld_aux + n) : zero;
+          y[s] = (has_y && in) ? ld4(e.aux_y + m * e.ld_aux + n) : zero;
+        }
+        if (ACC) old[s] = (acc && in) ? ld4(e.C + m * e.ldc + n) : zero;
+      }
+    }
+  };
+  if (AHEAD) load_rows(0, 0, 2);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
+    if (!AHEAD) load_rows(0, h, h + 1);
+    const int s0 = AHEAD ? h * 4 : 0;
     __syncwarp();
     if ((lane >> 4) == h) {
       float *dst = tr + (lane & 15) * TR_PITCH;
@@ -387,33 +412,23 @@ __device__ __forceinline__ void epilogue_block32(const Epilogue &e, float *tr, c
       for (int j = 0; j < 8; ++j) *reinterpret_cast<float4 *>(dst + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     }
     __syncwarp();
-    float4 add[4], pre[4], y[4], old[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const long long m = row0 + h * 16 + rsub + 4 * i;
-      const bool in = m < M;
-      if (ADD) add[i] = (has_add && in) ? ld4(e.addend + m * e.ld_addend + n) : zero;
-      if (DERIV) {
-        pre[i] = (has_pre && in) ? ld4(e.aux_pre + m * e.ld_aux + n) : zero;
-        y[i] = (has_y && in) ? ld4(e.aux_y + m * e.ld_aux + n) : zero;
-      }
-      if (ACC) old[i] = (acc && in) ? ld4(e.C + m * e.ldc + n) : zero;
-    }
-    float4 x[4];
+    float4 x[4], z4[4], y4[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       x[i] = *reinterpret_cast<const float4 *>(tr + (rsub + 4 * i) * TR_PITCH + c4);
       x[i].x += bias.x; x[i].y += bias.y; x[i].z += bias.z; x[i].w += bias.w;
-      if (ADD) { x[i].x += add[i].x; x[i].y += add[i].y; x[i].z += add[i].z; x[i].w += add[i].w; }
+      if (ADD) { x[i].x += add[s0 + i].x; x[i].y += add[s0 + i].y; x[i].z += add[s0 + i].z; x[i].w += add[s0 + i].w; }
       if (DERIV) {
-        pre[i].x = pre[i].x * cs.x + ch.x; pre[i].y = pre[i].y * cs.y + ch.y; pre[i].z = pre[i].z * cs.z + ch.z; pre[i].w = pre[i].w * cs.w + ch.w;
+        const float4 p = pre[s0 + i];
+        z4[i] = make_float4(p.x * cs.x + ch.x, p.y * cs.y + ch.y, p.z * cs.z + ch.z, p.w * cs.w + ch.w);
+        y4[i] = y[s0 + i];
       }
     }
-    if (DERIV) derive4x4_any(e.deriv_af, x, pre, y);
+    if (DERIV) derive4x4_any(e.deriv_af, x, z4, y4);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const long long m = row0 + h * 16 + rsub + 4 * i;
-      if (ACC) { x[i].x += old[i].x; x[i].y += old[i].y; x[i].z += old[i].z; x[i].w += old[i].w; }
+      if (ACC) { x[i].x += old[s0 + i].x; x[i].y += old[s0 + i].y; x[i].z += old[s0 + i].z; x[i].w += old[s0 + i].w; }
       if (m < M) *reinterpret_cast<float4 *>(e.C + m * e.ldc + n) = x[i];
     }
   }
@@ -802,6 +817,7 @@ gemm3x_tf32_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
 // The grid is one cluster per SM pair; each cluster walks tiles cluster, cluster + clusters, ... and the three roles
 // (TMA producer, MMA issuer, drain warps) keep running stage / chunk counters across tiles, so the loads and MMAs of
 // the next tile start while the drain warps, which hold the finished tile in registers, run its epilogue.
+// 384 threads in three warpgroups: the role warps give registers back (setmaxnreg) and the eight drain warps take 232.
 // Tiles are numbered in bands of 8 row tiles so that the tiles in flight at one time share operand panels in L2.
 // ---------------------------------------------------------------------------------------------------------
 constexpr int WIDE_STAGES = 3;
@@ -1557,10 +1573,8 @@ static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const Ge
   const int rem = work.num_tiles % G;
   if (ctx.gemm_bn != 4 && ctx.sk_ws != nullptr && ctx.sk_clusters >= G && rem != 0 && num_chunks >= 2) {
     const int units = rem * num_chunks;
-    int per_cluster = (units + G - 1) / G;
-#ifdef MYEA_GEMM_TIMELINE
-    if (const char *ev = getenv("MYEA_SK_MIN")) per_cluster = std::max(per_cluster, atoi(ev));
-#endif
+    const int per_cluster = (units + G - 1) / G;
+
     // splitting a tile costs about one chunk's time (partial sums through L2, one counter round trip, the second
     // pass of the warp that arrives last): worth it when it takes at least two chunks off the longest cluster
     if (num_chunks - per_cluster >= 2) {

@@ -84,6 +84,22 @@ def test_operands_read_through_their_columns(flags, shape):
     assert _gemm(*shape, engine=1 | TILE_WIDE | flags) < 2e-5   # the FP32 FMA engine on the same panels
 
 
+@pytest.mark.parametrize("tile", [TILE_SINGLE, TILE_PAIR, TILE_WIDE])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (300, 520, 100), (1024, 512, 2048)])
+def test_fused_activation_derivative_epilogue(tile, shape):
+    """bit 19: C = (A B^T) .* relu'(C_in) - the epilogue of the error-propagation product, staged through shared memory"""
+    M, N, K = shape
+    lib = capi.load()
+    rng = np.random.default_rng(5)
+    A, B = rng.standard_normal((M, K)).astype(np.float32), rng.standard_normal((N, K)).astype(np.float32)
+    pre = rng.standard_normal((M, N)).astype(np.float32)
+    out = pre.copy()
+    rc = lib.myea_b200_gemm_nt(0, tile | (1 << 19), M, N, K, A.ctypes.data, B.ctypes.data, out.ctypes.data, 0, None, 0)
+    assert rc == 0
+    want = (A.astype(np.float64) @ B.astype(np.float64).T) * (pre >= 0)
+    assert float(np.abs(out - want).max() / np.abs(want).max()) < 2e-5
+
+
 def test_invalid_arguments():
     lib = capi.load()
     assert lib.myea_b200_gemm_nt(0, 0, 0, 4, 4, None, None, None, 0, None, 0) == -1
