@@ -195,10 +195,12 @@ int myea_b200_download_mask(myea_handle h, uint32_t layer, int kind, void *host,
  *   `mean_loss`: Get__Loss(TYPE_DATASET_NONE) averaged over the mini-batches; `accuracy_sum`: summed accuracy hits.
  *   mask_seed != 0 draws new masks before mini-batch i with myea_b200_generate_masks(seed, first_step + i).
  *   The caller advances opt->epoch_time_step between epochs as the reference does.
- *   mini_batch_size must be a multiple of the network's batch size and divide number_examples (MYEA_E_UNSUPPORTED else).
+ *   A mini-batch is walked in sub-batches of the network's batch size, the last one shorter, and the last mini-batch
+ *   of the epoch may be shorter too, as in the reference; recurrent (and multi-GPU) networks take full batches only
+ *   (MYEA_E_UNSUPPORTED otherwise).
  * myea_b200_evaluate: the forward-only loop of Dataset::Testing: inference-mode forward (running normalization
  *   statistics, dropout scaling) and loss / accuracy accumulation over `number_examples` examples (`order` may be
- *   null: the first examples of the dataset); number_examples must be a multiple of the network's batch size. */
+ *   null: the first examples of the dataset); a recurrent network needs a multiple of its batch size. */
 int myea_b200_dataset_set(myea_handle h, uint64_t number_examples, const float *inputs, const float *outputs);
 int myea_b200_train_epoch(myea_handle h, const uint64_t *order, uint64_t number_examples, uint64_t mini_batch_size,
                           const myea_opt_desc *opt, uint64_t mask_seed, uint64_t first_step, double *mean_loss, double *accuracy_sum);
@@ -212,7 +214,10 @@ int myea_b200_set_shakedrop(myea_handle h, uint32_t layer, const uint8_t *mask, 
                             uint64_t batch);
 
 /* void Forward_Pass(size_t B, T_ const *const *X, …) (Data.hpp:2896). X is the packed [T][B][inputs] block the
- * host class gathers from the reference's row pointers; host memory. training: type_state_propagation (Data.hpp:3048). */
+ * host class gathers from the reference's row pointers; host memory. training: type_state_propagation (Data.hpp:3048).
+ * `batch` may be anything from 1 to the batch size the network was created for when the network is feed-forward
+ * (one time step); recurrent networks and networks with a communicator take the full batch only.  The calls that
+ * follow (compute_error, backward, update_derivative_weight) take the batch of the last forward pass. */
 int myea_b200_forward(myea_handle h, uint64_t batch, const float *inputs_TBI, int training);
 /* same, inputs already resident on this handle's GPU */
 int myea_b200_forward_device(myea_handle h, uint64_t batch, const float *device_inputs_TBI, int training);

@@ -28,17 +28,17 @@ __global__ void __launch_bounds__(256) gather_batch_vec4_kernel(const float4 *__
   }
 }
 
-static int gather(myea_b200_net *net, const float *src, long long first, long long W, float *dst) {
+static int gather(myea_b200_net *net, const float *src, long long first, long long B, long long W, float *dst) {
   Context &ctx = net->ctx;
-  const long long total = net->T * net->B * W;
+  const long long total = net->T * B * W;
   ctx.begin(TC_ELEMENTWISE);
   if ((W & 3) == 0) {
     const int blocks = static_cast<int>(std::min<long long>((total / 4 + 255) / 256, 148 * 16));
-    gather_batch_vec4_kernel<<<std::max(blocks, 1), 256, 0, ctx.stream>>>(reinterpret_cast<const float4 *>(src), net->ds_order, first, net->B, net->T,
+    gather_batch_vec4_kernel<<<std::max(blocks, 1), 256, 0, ctx.stream>>>(reinterpret_cast<const float4 *>(src), net->ds_order, first, B, net->T,
                                                                           W / 4, reinterpret_cast<float4 *>(dst));
   } else {
     const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
-    gather_batch_kernel<<<std::max(blocks, 1), 256, 0, ctx.stream>>>(src, net->ds_order, first, net->B, net->T, W, dst);
+    gather_batch_kernel<<<std::max(blocks, 1), 256, 0, ctx.stream>>>(src, net->ds_order, first, B, net->T, W, dst);
   }
   ctx.end(TC_ELEMENTWISE);
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
@@ -100,34 +100,41 @@ extern "C" int myea_b200_train_epoch(myea_handle net, const uint64_t *order, uin
   if (net == nullptr || order == nullptr || opt == nullptr || number_examples == 0) return MYEA_E_INVALID;
   if (net->ds_examples == 0) { net->ctx.error = "no dataset on the device (myea_b200_dataset_set)"; return MYEA_E_INVALID; }
   const uint64_t B = static_cast<uint64_t>(net->B);
-  if (mini_batch_size == 0 || mini_batch_size % B != 0 || number_examples % mini_batch_size != 0) {
-    net->ctx.error = "train_epoch: the mini-batch must be a multiple of the network's batch size and divide the number of examples (ragged last batches are not built)";
+  if (mini_batch_size == 0) return MYEA_E_INVALID;
+  // Train_Batch_BP walks a mini-batch in sub-batches of the network's batch size, the last one shorter
+  // (Dataset.cpp:667-691); the last mini-batch of the epoch may be shorter as well.  Short batches need a feed-forward
+  // network (see myea_b200_forward).
+  if ((mini_batch_size % B != 0 || number_examples % mini_batch_size != 0) && (net->T != 1 || net->comm != nullptr)) {
+    net->ctx.error = "train_epoch: a recurrent (or multi-GPU) network needs a mini-batch that is a multiple of its batch size and divides the number of examples";
     return MYEA_E_UNSUPPORTED;
   }
   if (cudaSetDevice(net->ctx.device) != cudaSuccess) return MYEA_E_CUDA;
   int rc = set_order(net, order, number_examples);
   if (rc != MYEA_OK) return rc;
   const long long wi = net->layers[0].n_out, wo = net->layers.back().n_out;
-  const uint64_t mini_batches = number_examples / mini_batch_size, subs = mini_batch_size / B;
+  const uint64_t mini_batches = (number_examples + mini_batch_size - 1) / mini_batch_size;
   double loss_total = 0.0, acc_total = 0.0;
   for (uint64_t mb = 0; mb < mini_batches; ++mb) {
+    const uint64_t mb_first = mb * mini_batch_size;
+    const uint64_t mb_size = std::min<uint64_t>(mini_batch_size, number_examples - mb_first);
     if (mask_seed != 0 && (rc = myea_b200_generate_masks(net, mask_seed, first_step + mb)) != MYEA_OK) return rc;
     if ((rc = myea_b200_reset_loss(net)) != MYEA_OK) return rc;
-    for (uint64_t sub = 0; sub < subs; ++sub) {  // Train_Batch_BP: derivatives accumulate over the sub-batches of one mini-batch
-      const long long first = static_cast<long long>(mb * mini_batch_size + sub * B);
-      if ((rc = gather(net, net->ds_inputs, first, wi, net->ds_batch_inputs)) != MYEA_OK) return rc;
-      if ((rc = gather(net, net->ds_outputs, first, wo, net->ds_batch_outputs)) != MYEA_OK) return rc;
-      if ((rc = myea_b200_forward_device(net, B, net->ds_batch_inputs, 1)) != MYEA_OK) return rc;
-      if ((rc = myea_b200_compute_error_device(net, B, net->ds_batch_outputs)) != MYEA_OK) return rc;
-      if ((rc = myea_b200_backward(net, B)) != MYEA_OK) return rc;
-      if ((rc = myea_b200_update_derivative_weight(net, B)) != MYEA_OK) return rc;
+    for (uint64_t done = 0; done < mb_size; done += B) {  // derivatives accumulate over the sub-batches of one mini-batch
+      const uint64_t b = std::min<uint64_t>(B, mb_size - done);
+      const long long first = static_cast<long long>(mb_first + done);
+      if ((rc = gather(net, net->ds_inputs, first, static_cast<long long>(b), wi, net->ds_batch_inputs)) != MYEA_OK) return rc;
+      if ((rc = gather(net, net->ds_outputs, first, static_cast<long long>(b), wo, net->ds_batch_outputs)) != MYEA_OK) return rc;
+      if ((rc = myea_b200_forward_device(net, b, net->ds_batch_inputs, 1)) != MYEA_OK) return rc;
+      if ((rc = myea_b200_compute_error_device(net, b, net->ds_batch_outputs)) != MYEA_OK) return rc;
+      if ((rc = myea_b200_backward(net, b)) != MYEA_OK) return rc;
+      if ((rc = myea_b200_update_derivative_weight(net, b)) != MYEA_OK) return rc;
     }
     double ls = 0.0, as = 0.0;
     uint64_t nl = 0;
     if ((rc = myea_b200_get_loss(net, &ls, &nl, &as)) != MYEA_OK) return rc;
     loss_total += reference_loss(net, ls, nl);
     acc_total += as;
-    if ((rc = myea_b200_update_parameter(net, mini_batch_size, net->ds_examples, opt)) != MYEA_OK) return rc;
+    if ((rc = myea_b200_update_parameter(net, mb_size, net->ds_examples, opt)) != MYEA_OK) return rc;
   }
   if (mean_loss != nullptr) *mean_loss = loss_total / static_cast<double>(mini_batches);
   if (accuracy_sum != nullptr) *accuracy_sum = acc_total;
@@ -139,8 +146,8 @@ extern "C" int myea_b200_evaluate(myea_handle net, const uint64_t *order, uint64
   if (net == nullptr || number_examples == 0) return MYEA_E_INVALID;
   if (net->ds_examples == 0) { net->ctx.error = "no dataset on the device (myea_b200_dataset_set)"; return MYEA_E_INVALID; }
   const uint64_t B = static_cast<uint64_t>(net->B);
-  if (number_examples % B != 0) {
-    net->ctx.error = "evaluate: the number of examples must be a multiple of the network's batch size (ragged last batches are not built)";
+  if (number_examples % B != 0 && (net->T != 1 || net->comm != nullptr)) {
+    net->ctx.error = "evaluate: a recurrent (or multi-GPU) network needs a number of examples that is a multiple of its batch size";
     return MYEA_E_UNSUPPORTED;
   }
   if (cudaSetDevice(net->ctx.device) != cudaSuccess) return MYEA_E_CUDA;
@@ -156,10 +163,11 @@ extern "C" int myea_b200_evaluate(myea_handle net, const uint64_t *order, uint64
   const long long wi = net->layers[0].n_out, wo = net->layers.back().n_out;
   if ((rc = myea_b200_reset_loss(net)) != MYEA_OK) return rc;
   for (uint64_t first = 0; first < number_examples; first += B) {
-    if ((rc = gather(net, net->ds_inputs, static_cast<long long>(first), wi, net->ds_batch_inputs)) != MYEA_OK) return rc;
-    if ((rc = gather(net, net->ds_outputs, static_cast<long long>(first), wo, net->ds_batch_outputs)) != MYEA_OK) return rc;
-    if ((rc = myea_b200_forward_device(net, B, net->ds_batch_inputs, 0)) != MYEA_OK) return rc;   // inference: running statistics, no masks
-    if ((rc = myea_b200_compute_error_device(net, B, net->ds_batch_outputs)) != MYEA_OK) return rc;
+    const uint64_t b = std::min<uint64_t>(B, number_examples - first);
+    if ((rc = gather(net, net->ds_inputs, static_cast<long long>(first), static_cast<long long>(b), wi, net->ds_batch_inputs)) != MYEA_OK) return rc;
+    if ((rc = gather(net, net->ds_outputs, static_cast<long long>(first), static_cast<long long>(b), wo, net->ds_batch_outputs)) != MYEA_OK) return rc;
+    if ((rc = myea_b200_forward_device(net, b, net->ds_batch_inputs, 0)) != MYEA_OK) return rc;   // inference: running statistics, no masks
+    if ((rc = myea_b200_compute_error_device(net, b, net->ds_batch_outputs)) != MYEA_OK) return rc;
   }
   double ls = 0.0, as = 0.0;
   uint64_t nl = 0;

@@ -330,6 +330,7 @@ extern "C" int myea_b200_create(myea_handle *out, const myea_net_desc *desc, int
   net->ctx.device = device;
   net->T = static_cast<long long>(desc->number_recurrent_depth);
   net->B = static_cast<long long>(desc->batch_size);
+  net->active_B = net->B;
   const char *eng = getenv("MYEA_B200_GEMM_ENGINE");
   if (eng != nullptr && eng[0] == '1') net->ctx.gemm_engine = 1;
   const char *tile = getenv("MYEA_B200_GEMM_TILE");  // 2 = CTA pairs, 128 / 256 = single-CTA column tile, unset = heuristic
@@ -459,7 +460,8 @@ namespace myea {
 // Forward_Pass__FC (Neural_Network__Forward_Pass__Loop.cpp:350-790 is the per-layer driver).
 int fc_product_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long rows, const Epilogue &e) {
   const float *w = net->params + L.idx.first_connection_index;
-  if (L.shared_panels) {
+  if (L.shared_panels && gemm_takes_mn_major(net->ctx, rows, L.n_out) && gemm_takes_mn_major(net->ctx, rows, L.n_in)) {
+    // (a short last batch may fall below the 256 x 256 kernel's shapes: then the layer goes the per-contraction way)
     // while training, the same pass also writes the column readings the backward contractions will want
     const bool tr = net->training;
     RC(gemm_prepare_shared(net->ctx, input, L.n_in, rows, L.n_in, L.in_panel_mem, PANEL_ROLE_A, &L.in_rows, PANEL_ROLE_B, tr ? &L.in_cols : nullptr));
@@ -469,6 +471,7 @@ int fc_product_forward(myea_b200_net *net, LayerPlan &L, const float *input, lon
     L.d_valid = false;
     return gemm_panels(net->ctx, L.in_rows, 0, rows, L.w_rows, 0, L.n_out, e);
   }
+  L.in_valid = L.w_valid = L.d_valid = false;
   Operand a{input, rows, L.n_in, L.n_in, 1};
   Operand b{w, L.n_out, L.n_in, L.n_in, 1};
   return gemm_nt(net->ctx, a, b, e, net->scratch);
@@ -509,12 +512,30 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
 
 }  // namespace myea
 
+// Forward_Pass(batch_size_received, ...) accepts any batch up to the allocated one (the last batch of
+// Dataset::Train_Batch_BP is smaller, Dataset.cpp:667-691).  Here: the full batch always; fewer rows for feed-forward
+// networks (one time step), whose buffers are plain [rows][units]; recurrent buffers are [T][B][units] with the
+// allocated B as pitch, so a recurrent network takes full batches only.
+static int batch_for_forward(myea_b200_net *net, uint64_t batch) {
+  const long long b = static_cast<long long>(batch);
+  if (b == net->B) return MYEA_OK;
+  if (b < 1 || b > net->B) return fail(net, MYEA_E_INVALID, "batch must be between 1 and the batch size the network was created for");
+  if (net->T != 1) return fail(net, MYEA_E_UNSUPPORTED, "a recurrent network takes full batches only");
+  if (net->comm != nullptr) return fail(net, MYEA_E_UNSUPPORTED, "with a communicator attached every rank takes full batches");
+  return MYEA_OK;
+}
+static int batch_in_flight(myea_b200_net *net, uint64_t batch) {
+  if (static_cast<long long>(batch) != net->active_B) return fail(net, MYEA_E_INVALID, "batch must equal the batch of the last forward pass");
+  return MYEA_OK;
+}
+
 static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cudaMemcpyKind kind, int training) {
   if (net == nullptr || src == nullptr) return MYEA_E_INVALID;
-  if (static_cast<long long>(batch) != net->B) return fail(net, MYEA_E_INVALID, "batch must equal the batch size the network was created for");
+  RC(batch_for_forward(net, batch));
   CK(cudaSetDevice(net->ctx.device));
   net->training = training != 0;
-  const long long rows = net->T * net->B;
+  net->active_B = static_cast<long long>(batch);
+  const long long rows = net->T * net->active_B;
   CK(cudaMemcpyAsync(net->d_input, src, rows * net->layers[0].n_out * sizeof(float), kind, net->ctx.stream));
   const int n = static_cast<int>(net->layers.size());
   for (int l = 1; l < n;) {
@@ -548,15 +569,15 @@ extern "C" int myea_b200_forward_device(myea_handle net, uint64_t batch, const f
 // ---------------------------------------------------------------------------------------------------------
 static int compute_error_impl(myea_b200_net *net, uint64_t batch, const float *src, cudaMemcpyKind kind) {
   if (net == nullptr || src == nullptr) return MYEA_E_INVALID;
-  if (static_cast<long long>(batch) != net->B) return fail(net, MYEA_E_INVALID, "batch must equal the batch size the network was created for");
+  RC(batch_in_flight(net, batch));
   CK(cudaSetDevice(net->ctx.device));
   LayerPlan &L = net->layers.back();
-  const long long rows = net->T * net->B;
+  const long long rows = net->T * net->active_B;
   CK(cudaMemcpyAsync(net->d_desired, src, rows * L.n_out * sizeof(float), kind, net->ctx.stream));
   // Recurrent networks only score the steps t >= number_time_delays; earlier steps get a zero error
   // (RNN__Compute__Error, Neural_Network__Recurrent_Compute__Error__OpenMP.cpp:22-159).
   const long long t0 = net->T > 1 ? std::min<long long>(static_cast<long long>(net->desc.number_time_delays), net->T) : 0;
-  const long long skip = t0 * net->B;
+  const long long skip = t0 * net->active_B;
   if (skip > 0) RC(fill_zero(net->ctx, L.errors, skip * L.n_out));
   if (rows > skip) {
     const size_t off = static_cast<size_t>(skip) * L.n_out;
@@ -640,10 +661,10 @@ int fc_finish_backward(myea_b200_net *net, LayerPlan &L, long long rows) {
 
 extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
   if (net == nullptr) return MYEA_E_INVALID;
-  if (static_cast<long long>(batch) != net->B) return fail(net, MYEA_E_INVALID, "batch must equal the batch size the network was created for");
+  RC(batch_in_flight(net, batch));
   if (!net->training) return fail(net, MYEA_E_INVALID, "can not back propagate in inference mode");
   CK(cudaSetDevice(net->ctx.device));
-  const long long rows = net->T * net->B;
+  const long long rows = net->T * net->active_B;
   const int n = static_cast<int>(net->layers.size());
   // `l` is a layer whose error is complete; send it to the layer feeding it, finish that layer, move down
   int l = n - 1;
@@ -704,9 +725,9 @@ int fc_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float *i
 
 extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batch) {
   if (net == nullptr) return MYEA_E_INVALID;
-  if (static_cast<long long>(batch) != net->B) return fail(net, MYEA_E_INVALID, "batch must equal the batch size the network was created for");
+  RC(batch_in_flight(net, batch));
   CK(cudaSetDevice(net->ctx.device));
-  const long long rows = net->T * net->B;
+  const long long rows = net->T * net->active_B;
   if (net->comm != nullptr && net->grads_reduced)
     return fail(net, MYEA_E_UNSUPPORTED, "with a communicator attached, call update_parameter after every update_derivative_weight (the derivative buckets of this step were already summed over the ranks)");
   // last layer first: its bucket is complete first, and its all-reduce overlaps the contractions of the layers below

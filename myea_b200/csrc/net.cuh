@@ -60,6 +60,7 @@ struct myea_b200_net {
   std::vector<myea::LayerPlan> layers;
   uint64_t total_parameters = 0, total_weights = 0, total_bias = 0, total_norm_units = 0;
   long long T = 1, B = 0;
+  long long active_B = 0;  // rows of the batch in flight: B, or fewer for the last batch of a feed-forward network
   bool any_norm = false;
   // flat buffers, [P] (norm averages: [total_norm_units])
   float *params = nullptr, *grads = nullptr, *m1 = nullptr, *m2 = nullptr, *m2hat = nullptr, *prev_delta = nullptr,

@@ -95,7 +95,7 @@ int residual_forward(myea_b200_net *net, int r) {
   LayerPlan &R = net->layers[r];
   RRC(residual_check(net, r));
   Context &ctx = net->ctx;
-  const long long rows = net->B;
+  const long long rows = net->active_B;
   const float *x = net->layers[R.input_layer].values;
   for (int k = 1; k <= R.block_depth; ++k) {
     LayerPlan &L = net->layers[r + k];
@@ -131,7 +131,7 @@ int residual_forward(myea_b200_net *net, int r) {
 int residual_backward(myea_b200_net *net, int r) {
   LayerPlan &R = net->layers[r];
   Context &ctx = net->ctx;
-  const long long rows = net->B;
+  const long long rows = net->active_B;
   LayerPlan &last = net->layers[r + R.block_depth];
   const bool shake = R.desc.type_dropout == MYEA_DROPOUT_SHAKEDROP;
   // error on the last layer's output: the block error, times beta on the masked rows

@@ -110,23 +110,25 @@ class Net:
         self._ck(self.lib.myea_b200_download_mask(self.h, layer, kind, out.ctypes.data, out.nbytes), "download_mask")
         return out
 
-    def forward(self, X, training=True):
+    def forward(self, X, training=True, batch=None):
+        """X: [T, batch, inputs]; `batch` below the allocated batch size is allowed for feed-forward networks"""
         X = _f32(X)
-        self._ck(self.lib.myea_b200_forward(self.h, self.B, X.ctypes.data, 1 if training else 0), "forward")
+        self.active_B = int(batch or self.B)
+        self._ck(self.lib.myea_b200_forward(self.h, self.active_B, X.ctypes.data, 1 if training else 0), "forward")
 
     def compute_error(self, Y):
         Y = _f32(Y)
-        self._ck(self.lib.myea_b200_compute_error(self.h, self.B, Y.ctypes.data), "compute_error")
+        self._ck(self.lib.myea_b200_compute_error(self.h, getattr(self, "active_B", self.B), Y.ctypes.data), "compute_error")
 
     def backward(self):
-        self._ck(self.lib.myea_b200_backward(self.h, self.B), "backward")
+        self._ck(self.lib.myea_b200_backward(self.h, getattr(self, "active_B", self.B)), "backward")
 
     def update_derivative_weight(self):
-        self._ck(self.lib.myea_b200_update_derivative_weight(self.h, self.B), "update_derivative_weight")
+        self._ck(self.lib.myea_b200_update_derivative_weight(self.h, getattr(self, "active_B", self.B)), "update_derivative_weight")
 
-    def update_parameter(self, training_size=None, opt=None):
+    def update_parameter(self, training_size=None, opt=None, batch=None):
         o = opt or self.opt
-        self._ck(self.lib.myea_b200_update_parameter(self.h, self.B, training_size or self.B, C.byref(o)), "update_parameter")
+        self._ck(self.lib.myea_b200_update_parameter(self.h, batch or self.B, training_size or self.B, C.byref(o)), "update_parameter")
 
     def clear_training_arrays(self):
         self._ck(self.lib.myea_b200_clear_training_arrays(self.h), "clear_training_arrays")

@@ -293,9 +293,10 @@ class OracleNet:
         return L.values
 
     # ---- step functions ------------------------------------------------------------------------------------------
-    def forward(self, X, training=True):
+    def forward(self, X, training=True, batch=None):
         self.training = training
-        X = np.asarray(X, self.dt).reshape(self.T * self.B, -1)
+        self.active_B = int(batch or self.B)   # Forward_Pass(batch_size_received, ...): any batch up to the allocated one (T = 1)
+        X = np.asarray(X, self.dt).reshape(self.T * self.active_B, -1)
         self.layers[0].values = X
         n = len(self.layers)
         l = 1
@@ -320,9 +321,9 @@ class OracleNet:
         before number_time_delays are not scored and get zero error."""
         dt = self.dt
         L = self.layers[-1]
-        Y = np.asarray(Y, dt).reshape(self.T * self.B, -1)
+        Y = np.asarray(Y, dt).reshape(self.T * getattr(self, "active_B", self.B), -1)
         t0 = min(int(self.desc.number_time_delays), self.T) if self.T > 1 else 0
-        skip = t0 * self.B
+        skip = t0 * getattr(self, "active_B", self.B)
         y, t, pre = L.values[skip:], Y[skip:], L.pre[skip:]
         diff = y - t
         af = int(L.d.type_activation_function)
@@ -396,7 +397,7 @@ class OracleNet:
                 from oracle import myea_oracle_lstm
                 myea_oracle_lstm.update_derivative_weight(self, l)
 
-    def update_parameter(self, training_size=None, opt=None):
+    def update_parameter(self, training_size=None, opt=None, batch=None):
         """Update_Parameter (Neural_Network.cpp:4719-4900): clip (Neural_Network__Clip_Gradient.cpp:82-94), optimizer
         (Neural_Network__Adam.cpp:39-95, __AMSGrad.cpp, __AdaBound.cpp, __AMSBound.cpp, __Gradient_Descent*.cpp,
         __Nesterov_Accelerated_Gradient.cpp), derivatives reset to zero.  Update_Parameter's own L2 call is a no-op in
@@ -415,7 +416,7 @@ class OracleNet:
         t = self.time_step
         wd = dt(o.regularization__weight_decay)
         if wd != 0 and o.use_normalized_weight_decay:
-            wd = wd * np.sqrt(dt(self.B) / (dt(N) * dt(o.epoch_time_step if o.epoch_time_step > 0 else 1.0)))
+            wd = wd * np.sqrt(dt(batch or self.B) / (dt(N) * dt(o.epoch_time_step if o.epoch_time_step > 0 else 1.0)))
         decay = self.buf[capi.BUF_MASK_REGULARIZED] * wd * w if wd != 0 else 0
         kind = int(o.type_optimizer_function)
         b1, b2, eps = dt(o.adam_beta1), dt(o.adam_beta2), dt(o.adam_epsilon)

@@ -110,27 +110,29 @@ class RefNet:
         if self.lib.ref_set_mask_zoneout(self.h, layer, s.ctypes.data, o.ctypes.data, s.size) != 0:
             raise RuntimeError("layer %d has no zoneout mask" % layer)
 
-    def forward(self, X, training=True):
+    def forward(self, X, training=True, batch=None):
         X = _f32(X)
+        self.active_B = int(batch or self.B)   # Forward_Pass(batch_size_received, ...): any batch up to the allocated one
         self.lib.ref_set_training(self.h, 1 if training else 0)
-        self.lib.ref_load_batch(self.h, self.B, X.ctypes.data, None)
-        self.lib.ref_run(self.h, self.B, 1)
+        self.lib.ref_load_batch(self.h, self.active_B, X.ctypes.data, None)
+        self.lib.ref_run(self.h, self.active_B, 1)
 
     def compute_error(self, Y):
         Y = _f32(Y)
-        self.lib.ref_load_batch(self.h, self.B, None, Y.ctypes.data)
-        self.lib.ref_run(self.h, self.B, 2)
+        b = getattr(self, "active_B", self.B)
+        self.lib.ref_load_batch(self.h, b, None, Y.ctypes.data)
+        self.lib.ref_run(self.h, b, 2)
 
     def backward(self):
-        self.lib.ref_run(self.h, self.B, 4)
+        self.lib.ref_run(self.h, getattr(self, "active_B", self.B), 4)
 
     def update_derivative_weight(self):
-        self.lib.ref_run(self.h, self.B, 8)
+        self.lib.ref_run(self.h, getattr(self, "active_B", self.B), 8)
         self.lib.ref_merge_derivatives(self.h)
 
-    def update_parameter(self, training_size=None, opt=None):
+    def update_parameter(self, training_size=None, opt=None, batch=None):
         o = opt or self.opt
-        self.lib.ref_update_parameter(self.h, self.B, training_size or self.B, C.byref(o))
+        self.lib.ref_update_parameter(self.h, batch or self.B, training_size or self.B, C.byref(o))
 
     def reset_loss(self):
         self.lib.ref_reset_loss(self.h)

@@ -94,8 +94,52 @@ def test_epoch_with_device_drawn_masks_runs_and_is_repeatable():
     assert out[0][0] == out[1][0] and np.array_equal(out[0][1], out[1][1])
 
 
-def test_ragged_requests_are_refused_not_mangled():
-    wl = cases.CASES["c1_small"]()
+@pytest.mark.parametrize("name", ["mlp_relu_gd", "c2_small"])
+def test_short_last_batches_match_the_reference(name):
+    """feed-forward networks: the last sub-batch of a mini-batch and the last mini-batch of the epoch may be shorter
+    than the allocated batch (Dataset::Train_Batch_BP, Dataset.cpp:667-691); BN statistics are then those of the short batch"""
+    wl = cases.CASES[name]()
+    B = wl.B
+    mini = B + B // 2                 # one full sub-batch + a half one
+    n = 2 * mini + B // 3 + 1         # two whole mini-batches + a short one
+    X, Y = _dataset(wl, n)
+    gpu, cpu = Net(wl.desc, wl.opt), _oracle(wl)
+    wl.materialize(gpu); wl.materialize(cpu)
+    gpu.dataset_set(X.reshape(n, -1), Y.reshape(n, -1))
+    order = np.random.default_rng(2).permutation(n)
+    loss_gpu, acc_gpu = gpu.train_epoch(order, mini)
+    losses, acc_cpu = [], 0.0
+    for first in range(0, n, mini):
+        size = min(mini, n - first)
+        cpu.reset_loss()
+        for done in range(0, size, B):
+            b = min(B, size - done)
+            idx = order[first + done: first + done + b]
+            cpu.forward(np.ascontiguousarray(X[idx].transpose(1, 0, 2)), batch=b)
+            cpu.compute_error(np.ascontiguousarray(Y[idx].transpose(1, 0, 2)))
+            cpu.backward(); cpu.update_derivative_weight()
+        s, cnt, a = cpu.loss()
+        losses.append(_reference_loss(wl, s, cnt)); acc_cpu += a
+        cpu.update_parameter(training_size=n, batch=size)
+    assert abs(loss_gpu - np.mean(losses)) <= 1e-4 * abs(np.mean(losses)) + 1e-6
+    assert acc_gpu == acc_cpu
+    assert rel_err(gpu.get(capi.BUF_PARAMETERS), cpu.get(capi.BUF_PARAMETERS)) < TOL
+    # evaluation over a number of examples that is not a multiple of the batch
+    m = B + 3
+    loss_e, ls, nl, acc = gpu.evaluate(m)
+    cpu.reset_loss()
+    for first in range(0, m, B):
+        b = min(B, m - first)
+        cpu.forward(np.ascontiguousarray(X[first:first + b].transpose(1, 0, 2)), training=False, batch=b)
+        cpu.compute_error(np.ascontiguousarray(Y[first:first + b].transpose(1, 0, 2)))
+    s, cnt, a = cpu.loss()
+    assert nl == cnt and acc == a and abs(ls - s) <= 1e-4 * abs(s) + 1e-6
+    gpu.close(); cpu.close()
+
+
+def test_requests_that_are_not_built_are_refused_not_mangled():
+    # a recurrent network takes full batches only
+    wl = cases.CASES["lstm1_all_steps_adam"]()
     gpu = Net(wl.desc, wl.opt)
     wl.materialize(gpu)
     n = wl.B * 2 + 1
@@ -104,7 +148,7 @@ def test_ragged_requests_are_refused_not_mangled():
     order = np.arange(n, dtype=np.uint64)
     loss, acc = C.c_double(), C.c_double()
     assert gpu.lib.myea_b200_train_epoch(gpu.h, order.ctypes.data, n, wl.B, C.byref(wl.opt), 0, 0, C.byref(loss), C.byref(acc)) == -4
+    assert gpu.lib.myea_b200_evaluate(gpu.h, None, wl.B + 1, None, None, None, None) == -4
     bad = np.array([0, n + 5] * wl.B, dtype=np.uint64)[:wl.B * 2]
     assert gpu.lib.myea_b200_train_epoch(gpu.h, bad.ctypes.data, bad.size, wl.B, C.byref(wl.opt), 0, 0, C.byref(loss), C.byref(acc)) == -1
-    assert gpu.lib.myea_b200_evaluate(gpu.h, None, wl.B + 1, None, None, None, None) == -4
     gpu.close()

@@ -143,7 +143,9 @@ def test_bad_calls_return_status_not_crash():
     gpu = Net(wl.desc, wl.opt)
     lib = gpu.lib
     X, _ = wl.batch()
-    assert lib.myea_b200_forward(gpu.h, wl.B + 1, X.ctypes.data, 1) == -1          # wrong batch
+    assert lib.myea_b200_forward(gpu.h, wl.B + 1, X.ctypes.data, 1) == -1          # more rows than were allocated
+    assert lib.myea_b200_forward(gpu.h, wl.B - 1, X.ctypes.data, 1) == 0           # fewer rows: fine for a feed-forward network
+    assert lib.myea_b200_backward(gpu.h, wl.B) == -1                                # not the batch in flight
     assert lib.myea_b200_set_mask_bernoulli(gpu.h, 1, X.ctypes.data, 3) == -1      # layer without a mask
     assert b"mask" in lib.myea_b200_last_error(gpu.h)
     gpu.close()
