@@ -214,15 +214,72 @@ __global__ void __launch_bounds__(256) activation_forward_kernel(const float *__
   }
 }
 
+// The same for H a multiple of 4 and 16-byte aligned arrays: a thread keeps four COLUMNS (affine coefficients and mask
+// bytes loaded once) and walks rows four at a time with the four loads in flight; the activation is a template
+// argument, so no switch is left in the loop.  Grid: x = column groups of 1024, y = row walkers.
+template <uint32_t AF>
+__global__ void __launch_bounds__(256) activation_forward_cols_kernel(const float *__restrict__ z, float *__restrict__ out, long long rows,
+                                                                      long long H, const float *__restrict__ col_scale,
+                                                                      const float *__restrict__ col_shift, const uint8_t *__restrict__ mask,
+                                                                      float keep_scale) {
+  const long long c = (blockIdx.x * 256ll + threadIdx.x) * 4;
+  if (c >= H) return;
+  const bool affine = col_scale != nullptr;
+  const float4 cs = affine ? *reinterpret_cast<const float4 *>(col_scale + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+  const float4 ch = affine ? *reinterpret_cast<const float4 *>(col_shift + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool masked = mask != nullptr;
+  const bool k0 = !masked || mask[c] != 0, k1 = !masked || mask[c + 1] != 0, k2 = !masked || mask[c + 2] != 0, k3 = !masked || mask[c + 3] != 0;
+  const bool scale = masked || keep_scale != 1.0f;  // kept units of a training mask, or every unit at inference of plain Bernoulli dropout
+  for (long long r0 = blockIdx.y * 4ll; r0 < rows; r0 += gridDim.y * 4ll) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (r0 + u < rows) v[u] = *reinterpret_cast<const float4 *>(z + (r0 + u) * H + c);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (r0 + u >= rows) break;
+      float4 y;
+      y.x = af_fire(AF, affine ? v[u].x * cs.x + ch.x : v[u].x);
+      y.y = af_fire(AF, affine ? v[u].y * cs.y + ch.y : v[u].y);
+      y.z = af_fire(AF, affine ? v[u].z * cs.z + ch.z : v[u].z);
+      y.w = af_fire(AF, affine ? v[u].w * cs.w + ch.w : v[u].w);
+      if (scale) { y.x *= keep_scale; y.y *= keep_scale; y.z *= keep_scale; y.w *= keep_scale; }
+      if (!k0) y.x = 0.f;
+      if (!k1) y.y = 0.f;
+      if (!k2) y.z = 0.f;
+      if (!k3) y.w = 0.f;
+      *reinterpret_cast<float4 *>(out + (r0 + u) * H + c) = y;
+    }
+  }
+}
+
+static dim3 column_walk_grid(long long rows, long long H) {
+  const unsigned gx = static_cast<unsigned>((H / 4 + 255) / 256);
+  const long long walkers = std::max<long long>(1, (148 * 8) / gx);
+  return dim3(gx, static_cast<unsigned>(std::max<long long>(1, std::min<long long>((rows + 3) / 4, walkers))));
+}
+
 int activation_forward(Context &ctx, const float *z, float *out, long long rows, long long H, uint32_t af, const float *col_scale,
                        const float *col_shift, const uint8_t *mask, float keep_scale) {
   ctx.begin(TC_ELEMENTWISE);
-  const bool vec4 = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(z) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  const bool vec4 = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(z) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+                    ((reinterpret_cast<uintptr_t>(col_scale) & 15) == 0) && ((reinterpret_cast<uintptr_t>(col_shift) & 15) == 0);
   const long long total = rows * (vec4 ? H / 4 : H);
   const int blocks = static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, 148 * 16)));
-  if (vec4)
-    activation_forward_kernel<4><<<blocks, 256, 0, ctx.stream>>>(z, out, rows, H, af, col_scale, col_shift, mask, keep_scale);
-  else
+  if (vec4) {
+    const dim3 grid = column_walk_grid(rows, H);
+#define MYEA_AF_CASE(A) case A: activation_forward_cols_kernel<A><<<grid, 256, 0, ctx.stream>>>(z, out, rows, H, col_scale, col_shift, mask, keep_scale); break
+    switch (af) {
+      MYEA_AF_CASE(MYEA_AF_TANH);
+      MYEA_AF_CASE(MYEA_AF_SIGMOID);
+      MYEA_AF_CASE(MYEA_AF_RELU);
+      MYEA_AF_CASE(MYEA_AF_LEAKY_RELU);
+      MYEA_AF_CASE(MYEA_AF_ELU);
+      MYEA_AF_CASE(MYEA_AF_SELU);
+      default: activation_forward_kernel<4><<<blocks, 256, 0, ctx.stream>>>(z, out, rows, H, af, col_scale, col_shift, mask, keep_scale); break;
+    }
+#undef MYEA_AF_CASE
+  } else
     activation_forward_kernel<1><<<blocks, 256, 0, ctx.stream>>>(z, out, rows, H, af, col_scale, col_shift, mask, keep_scale);
   ctx.end(TC_ELEMENTWISE);
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
@@ -337,6 +394,37 @@ __global__ void __launch_bounds__(256) norm_backward_apply_kernel(const float *_
   }
 }
 
+// vectorized form: a thread keeps four columns (mean and the three coefficients loaded once) and walks rows four at a time
+__global__ void __launch_bounds__(256) norm_backward_apply_cols_kernel(const float *__restrict__ z, const float *__restrict__ delta,
+                                                                       float *__restrict__ out, long long rows, long long H,
+                                                                       const float *__restrict__ mean, const float *__restrict__ coef) {
+  const long long c = (blockIdx.x * 256ll + threadIdx.x) * 4;
+  if (c >= H) return;
+  const float4 mu = *reinterpret_cast<const float4 *>(mean + c);
+  const float4 k0 = *reinterpret_cast<const float4 *>(coef + c), k1 = *reinterpret_cast<const float4 *>(coef + H + c),
+               k2 = *reinterpret_cast<const float4 *>(coef + 2 * H + c);
+  for (long long r0 = blockIdx.y * 4ll; r0 < rows; r0 += gridDim.y * 4ll) {
+    float4 t[4], u[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (r0 + i < rows) {
+        t[i] = *reinterpret_cast<const float4 *>(z + (r0 + i) * H + c);
+        u[i] = *reinterpret_cast<const float4 *>(delta + (r0 + i) * H + c);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (r0 + i >= rows) break;
+      float4 d;
+      d.x = u[i].x * k0.x + (t[i].x - mu.x) * k1.x + k2.x;
+      d.y = u[i].y * k0.y + (t[i].y - mu.y) * k1.y + k2.y;
+      d.z = u[i].z * k0.z + (t[i].z - mu.z) * k1.z + k2.z;
+      d.w = u[i].w * k0.w + (t[i].w - mu.w) * k1.w + k2.w;
+      *reinterpret_cast<float4 *>(out + (r0 + i) * H + c) = d;
+    }
+  }
+}
+
 int norm_backward(Context &ctx, const float *z, const float *delta_af, float *delta_out, long long rows, long long H,
                   const NormParams &np, const SumHook *hook) {
   ctx.begin(TC_NORM);
@@ -359,7 +447,9 @@ int norm_backward(Context &ctx, const float *z, const float *delta_af, float *de
                     ((reinterpret_cast<uintptr_t>(delta_out) & 15) == 0);
   const long long total = rows * (vec4 ? H / 4 : H);
   const int blocks = static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, 148 * 16)));
-  if (vec4)
+  if (vec4 && (reinterpret_cast<uintptr_t>(np.mean) & 15) == 0 && (reinterpret_cast<uintptr_t>(coef) & 15) == 0)
+    norm_backward_apply_cols_kernel<<<column_walk_grid(rows, H), 256, 0, ctx.stream>>>(z, delta_af, delta_out, rows, H, np.mean, coef);
+  else if (vec4)
     norm_backward_apply_kernel<4><<<blocks, 256, 0, ctx.stream>>>(z, delta_af, delta_out, rows, H, np.mean, coef);
   else
     norm_backward_apply_kernel<1><<<blocks, 256, 0, ctx.stream>>>(z, delta_af, delta_out, rows, H, np.mean, coef);
