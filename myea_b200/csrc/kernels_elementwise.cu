@@ -35,6 +35,8 @@ __global__ void __launch_bounds__(256) column_reduce_kernel(const float *__restr
     for (int v = 0; v < VEC; ++v) mu[v] = mean[col + v];
   }
   if (active) {
+    // four rows per trip so that four (eight with a second array) 16-byte loads are in flight per thread
+#pragma unroll 4
     for (long long r = r_begin + rl; r < r_end; r += 8) {
       float xv[VEC], yv[VEC];
       if (VEC == 4) {
@@ -104,6 +106,7 @@ __global__ void chunk_sum_kernel(const float *__restrict__ partial, int chunks, 
   const long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   if (j >= H) return;
   float s = 0.f, q = 0.f;
+#pragma unroll 8
   for (int c = 0; c < chunks; ++c) { s += partial[(0ll * chunks + c) * H + j]; q += partial[(1ll * chunks + c) * H + j]; }
   sums[j] = s;
   sums[H + j] = q;
@@ -118,7 +121,8 @@ __global__ void norm_stats_finalize_kernel(const float *__restrict__ partial, in
   float mean, sigma, r = 1.f, d = 0.f;
   if (training) {
     float s = 0.f, q = 0.f;
-    for (int c = 0; c < chunks; ++c) { s += partial[(0ll * chunks + c) * H + j]; q += partial[(1ll * chunks + c) * H + j]; }
+  #pragma unroll 8
+  for (int c = 0; c < chunks; ++c) { s += partial[(0ll * chunks + c) * H + j]; q += partial[(1ll * chunks + c) * H + j]; }
     const float scale = 1.0f / static_cast<float>(rows);
     mean = s * scale;
     sigma = sqrtf(q * scale - mean * mean + np.epsilon);
@@ -350,6 +354,7 @@ __global__ void norm_backward_finalize_kernel(const float *__restrict__ partial,
   const long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   if (j >= H) return;
   float s1 = 0.f, s2 = 0.f;
+#pragma unroll 8
   for (int c = 0; c < chunks; ++c) { s1 += partial[(0ll * chunks + c) * H + j]; s2 += partial[(1ll * chunks + c) * H + j]; }
   const float sigma = np.sigma[j], r = np.r[j], d = np.d[j], g = np.gamma[j];
   const float k = r / sigma;
@@ -539,6 +544,7 @@ __global__ void column_sum_finalize_kernel(const float *__restrict__ partial, in
   const long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   if (j >= H) return;
   float s = 0.f;
+#pragma unroll 8
   for (int c = 0; c < chunks; ++c) s += partial[static_cast<long long>(c) * H + j];
   out[j] = accumulate ? out[j] + s : s;
 }
