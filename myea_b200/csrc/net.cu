@@ -341,6 +341,10 @@ extern "C" int myea_b200_create(myea_handle *out, const myea_net_desc *desc, int
   if (cudaStreamCreateWithFlags(&net->ctx.stream, cudaStreamNonBlocking) != cudaSuccess) return fail(net, MYEA_E_CUDA, "cudaStreamCreate failed");
   cudaEventCreate(&net->ctx.ev0);
   cudaEventCreate(&net->ctx.ev1);
+  if (cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&net->ev_desired_ready, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&net->ev_desired_free, cudaEventDisableTiming) != cudaSuccess)
+    return fail(net, MYEA_E_CUDA, "cudaStreamCreate / cudaEventCreate failed");
   RC(build_index_map(net));
   RC(allocate_buffers(net));
   CK(cudaStreamSynchronize(net->ctx.stream));
@@ -360,6 +364,9 @@ extern "C" void myea_b200_destroy(myea_handle net) {
     if (p != nullptr) cudaFree(p);
   if (net->ctx.ev0) cudaEventDestroy(net->ctx.ev0);
   if (net->ctx.ev1) cudaEventDestroy(net->ctx.ev1);
+  if (net->copy_stream) { cudaStreamSynchronize(net->copy_stream); cudaStreamDestroy(net->copy_stream); }
+  if (net->ev_desired_ready) cudaEventDestroy(net->ev_desired_ready);
+  if (net->ev_desired_free) cudaEventDestroy(net->ev_desired_free);
   if (net->ctx.stream) cudaStreamDestroy(net->ctx.stream);
   delete net;
 }
@@ -573,7 +580,16 @@ static int compute_error_impl(myea_b200_net *net, uint64_t batch, const float *s
   CK(cudaSetDevice(net->ctx.device));
   LayerPlan &L = net->layers.back();
   const long long rows = net->T * net->active_B;
-  CK(cudaMemcpyAsync(net->d_desired, src, rows * L.n_out * sizeof(float), kind, net->ctx.stream));
+  if (kind == cudaMemcpyHostToDevice) {
+    // host targets: copy beside the forward pass still in flight on the main stream (the last use of d_desired by an
+    // error kernel is behind ev_desired_free), and let the main stream wait for the copy only now
+    CK(cudaStreamWaitEvent(net->copy_stream, net->ev_desired_free, 0));
+    CK(cudaMemcpyAsync(net->d_desired, src, rows * L.n_out * sizeof(float), kind, net->copy_stream));
+    CK(cudaEventRecord(net->ev_desired_ready, net->copy_stream));
+    CK(cudaStreamWaitEvent(net->ctx.stream, net->ev_desired_ready, 0));
+  } else {
+    CK(cudaMemcpyAsync(net->d_desired, src, rows * L.n_out * sizeof(float), kind, net->ctx.stream));
+  }
   // Recurrent networks only score the steps t >= number_time_delays; earlier steps get a zero error
   // (RNN__Compute__Error, Neural_Network__Recurrent_Compute__Error__OpenMP.cpp:22-159).
   const long long t0 = net->T > 1 ? std::min<long long>(static_cast<long long>(net->desc.number_time_delays), net->T) : 0;
@@ -585,6 +601,7 @@ static int compute_error_impl(myea_b200_net *net, uint64_t batch, const float *s
                     L.desc.type_activation_function, net->desc.type_loss_function, net->desc.type_accuracy_function,
                     net->desc.accuracy_variance > 0.f ? net->desc.accuracy_variance : 0.49f, net->d_loss_acc, net->d_loss_count));
   }
+  CK(cudaEventRecord(net->ev_desired_free, net->ctx.stream));
   return MYEA_OK;
 }
 

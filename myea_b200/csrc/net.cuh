@@ -88,5 +88,9 @@ struct myea_b200_net {
   float *ds_inputs = nullptr, *ds_outputs = nullptr, *ds_batch_inputs = nullptr, *ds_batch_outputs = nullptr;
   unsigned long long *ds_order = nullptr;
   uint64_t ds_examples = 0, ds_order_capacity = 0;
+  // targets arriving from the host are copied on a stream of their own, so that the copy runs under the forward pass
+  // that is still executing; the two events order it against the error kernel's use of d_desired
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t ev_desired_ready = nullptr, ev_desired_free = nullptr;
   std::vector<void *> allocations;
 };
