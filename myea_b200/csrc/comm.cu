@@ -12,6 +12,8 @@
 // NCCL is loaded at run time (dlopen) so that the library itself has no link-time dependency on it.
 #include "net.cuh"
 
+#include <vector>
+
 #include <dlfcn.h>
 #include <nccl.h>
 #include <stdio.h>
@@ -58,6 +60,9 @@ struct CommState {
   cudaEvent_t done = nullptr;      // comm -> compute: every bucket issued so far is reduced
   bool pending = false;
   size_t reduced_weights = 0;      // how much of the weight range has been handed to the comm stream this step
+  struct Bucket { size_t offset = 0, n = 0; cudaEvent_t reduced = nullptr; };
+  std::vector<Bucket> buckets;     // the ranges issued this step, each with the event that says its sum has arrived
+  size_t used = 0;
 };
 
 static int nccl_fail(myea_b200_net *net, ncclResult_t r, const char *what) {
@@ -97,6 +102,15 @@ int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n) {
   if (cudaEventRecord(c->ready, net->ctx.stream) != cudaSuccess || cudaStreamWaitEvent(c->stream, c->ready, 0) != cudaSuccess) return MYEA_E_CUDA;
   ncclResult_t r = api->AllReduce(net->grads + offset, net->grads + offset, n, ncclFloat, ncclSum, c->comm, c->stream);
   if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllReduce (bucket)");
+  if (c->used == c->buckets.size()) {
+    CommState::Bucket b;
+    if (cudaEventCreateWithFlags(&b.reduced, cudaEventDisableTiming) != cudaSuccess) return MYEA_E_CUDA;
+    c->buckets.push_back(b);
+  }
+  CommState::Bucket &b = c->buckets[c->used++];
+  b.offset = offset;
+  b.n = n;
+  if (cudaEventRecord(b.reduced, c->stream) != cudaSuccess) return MYEA_E_CUDA;
   c->pending = true;
   net->ctx.launches += 1;
   net->ctx.class_launches[TC_COMM] += 1;
@@ -109,7 +123,23 @@ int comm_join(myea_b200_net *net) {
   if (c == nullptr || !c->pending) return MYEA_OK;
   if (cudaEventRecord(c->done, c->stream) != cudaSuccess || cudaStreamWaitEvent(net->ctx.stream, c->done, 0) != cudaSuccess) return MYEA_E_CUDA;
   c->pending = false;
+  c->used = 0;
   return MYEA_OK;
+}
+
+// The ranges handed to the communicator this step, in the order their sums arrive.
+size_t comm_bucket_count(const myea_b200_net *net) { return net->comm != nullptr ? net->comm->used : 0; }
+// Makes the compute stream wait for bucket i only and says which range it covers.
+int comm_bucket_wait(myea_b200_net *net, size_t i, size_t *offset, size_t *n) {
+  CommState *c = net->comm;
+  if (c == nullptr || i >= c->used) return MYEA_E_INVALID;
+  if (cudaStreamWaitEvent(net->ctx.stream, c->buckets[i].reduced, 0) != cudaSuccess) return MYEA_E_CUDA;
+  *offset = c->buckets[i].offset;
+  *n = c->buckets[i].n;
+  return MYEA_OK;
+}
+void comm_buckets_done(myea_b200_net *net) {
+  if (net->comm != nullptr) { net->comm->used = 0; net->comm->pending = false; }
 }
 
 size_t &comm_reduced_weights(myea_b200_net *net) {
@@ -124,6 +154,7 @@ void comm_destroy(myea_b200_net *net) {
   if (api && net->comm->comm) api->CommDestroy(net->comm->comm);
   if (net->comm->ready) cudaEventDestroy(net->comm->ready);
   if (net->comm->done) cudaEventDestroy(net->comm->done);
+  for (auto &b : net->comm->buckets) if (b.reduced) cudaEventDestroy(b.reduced);
   if (net->comm->stream) cudaStreamDestroy(net->comm->stream);
   delete net->comm;
   net->comm = nullptr;

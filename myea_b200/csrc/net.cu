@@ -24,6 +24,9 @@ int lstm_set_zoneout(myea_b200_net *net, LayerPlan &L, const uint8_t *state, con
 float *lstm_output_errors(LayerPlan &L);
 // residual.cu
 int residual_forward(myea_b200_net *net, int layer);
+size_t comm_bucket_count(const myea_b200_net *net);
+int comm_bucket_wait(myea_b200_net *net, size_t i, size_t *offset, size_t *n);
+void comm_buckets_done(myea_b200_net *net);
 int residual_backward(myea_b200_net *net, int layer);
 const float *residual_fc_input(myea_b200_net *net, int r, int k);
 // comm.cu
@@ -776,7 +779,13 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
   if (net == nullptr || opt == nullptr || training_size == 0) return MYEA_E_INVALID;
   CK(cudaSetDevice(net->ctx.device));
   const size_t P = net->total_parameters;
-  if (net->comm != nullptr) {
+  // Without a global-norm clip the update is element by element, so each derivative bucket can be applied as soon as
+  // ITS sum over the ranks has arrived, while the later (lower-layer) buckets are still on the wire.
+  bool by_bucket = net->comm != nullptr && net->grads_reduced && !opt->use_clip_gradient && opt->regularization__max_norm_constraints == 0.f &&
+                   comm_bucket_count(net) > 0 && (net->total_weights & 3) == 0;
+  for (const auto &L : net->layers)  // the update kernel reads float4: every bucket has to start on a 16-byte boundary
+    if (L.type != MYEA_LAYER_RESIDUAL && (L.idx.first_connection_index & 3) != 0) by_bucket = false;
+  if (net->comm != nullptr && !by_bucket) {
     if (net->grads_reduced) RC(comm_join(net));            // buckets issued by update_derivative_weight
     else RC(comm_all_reduce_sum(net, net->grads, P));      // nothing was issued: reduce everything now
     net->grads_reduced = false;
@@ -836,7 +845,23 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
     for (const auto &L : net->layers)
       if (L.type == MYEA_LAYER_LSTM) return fail(net, MYEA_E_UNSUPPORTED, "max-norm constraints on LSTM blocks are not built");
   }
-  RC(optimizer_update(net->ctx, o, net->params, net->grads, net->m1, net->m2, net->m2hat, net->prev_delta, net->mask_reg, P));
+  if (by_bucket) {
+    const size_t count = comm_bucket_count(net);
+    size_t covered = 0;
+    for (size_t i = 0; i < count; ++i) {
+      size_t off = 0, n = 0;
+      RC(comm_bucket_wait(net, i, &off, &n));
+      if ((off & 3) != 0) return fail(net, MYEA_E_INVALID, "derivative bucket does not start on a 16-byte boundary");
+      RC(optimizer_update(net->ctx, o, net->params + off, net->grads + off, net->m1 + off, net->m2 + off, net->m2hat + off, net->prev_delta + off,
+                          net->mask_reg + off, n));
+      covered += n;
+    }
+    comm_buckets_done(net);
+    net->grads_reduced = false;
+    if (covered != P) return fail(net, MYEA_E_INVALID, "derivative buckets do not cover the parameter buffer");
+  } else {
+    RC(optimizer_update(net->ctx, o, net->params, net->grads, net->m1, net->m2, net->m2hat, net->prev_delta, net->mask_reg, P));
+  }
   if (max_norm != 0.f) {
     // Update_Weight_Regularization__Max_Norm_Constraints__Neurons (…Max_Norm_Constraints.cpp:147-165): one weight row per neuron
     for (const auto &L : net->layers)
