@@ -346,7 +346,9 @@ extern "C" int myea_b200_create(myea_handle *out, const myea_net_desc *desc, int
   cudaEventCreate(&net->ctx.ev1);
   if (cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaEventCreateWithFlags(&net->ev_desired_ready, cudaEventDisableTiming) != cudaSuccess ||
-      cudaEventCreateWithFlags(&net->ev_desired_free, cudaEventDisableTiming) != cudaSuccess)
+      cudaEventCreateWithFlags(&net->ev_desired_free, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&net->ev_input_ready, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&net->ev_input_free, cudaEventDisableTiming) != cudaSuccess)
     return fail(net, MYEA_E_CUDA, "cudaStreamCreate / cudaEventCreate failed");
   RC(build_index_map(net));
   RC(allocate_buffers(net));
@@ -370,6 +372,8 @@ extern "C" void myea_b200_destroy(myea_handle net) {
   if (net->copy_stream) { cudaStreamSynchronize(net->copy_stream); cudaStreamDestroy(net->copy_stream); }
   if (net->ev_desired_ready) cudaEventDestroy(net->ev_desired_ready);
   if (net->ev_desired_free) cudaEventDestroy(net->ev_desired_free);
+  if (net->ev_input_ready) cudaEventDestroy(net->ev_input_ready);
+  if (net->ev_input_free) cudaEventDestroy(net->ev_input_free);
   if (net->ctx.stream) cudaStreamDestroy(net->ctx.stream);
   delete net;
 }
@@ -468,14 +472,29 @@ namespace myea {
 
 // One fully connected layer on `rows` rows: z = x W^T (+ b); normalization statistics; activation; dropout.
 // Forward_Pass__FC (Neural_Network__Forward_Pass__Loop.cpp:350-790 is the per-layer driver).
+// (a short last batch may fall below the 256 x 256 kernel's shapes: then the layer goes the per-contraction way)
+static bool fc_uses_shared_panels(const myea_b200_net *net, const LayerPlan &L, long long rows) {
+  return L.shared_panels && gemm_takes_mn_major(net->ctx, rows, L.n_out) && gemm_takes_mn_major(net->ctx, rows, L.n_in);
+}
+
+// The weight panels of a layer depend on no activation: a forward pass whose inputs come from the host makes them all
+// while the inputs are still on their way (see forward_impl).
+static int fc_prepare_weights(myea_b200_net *net, LayerPlan &L) {
+  const bool tr = net->training;
+  RC(gemm_prepare_shared(net->ctx, net->params + L.idx.first_connection_index, L.n_in, L.n_out, L.n_in, L.w_panel_mem, PANEL_ROLE_B, &L.w_rows,
+                         PANEL_ROLE_B, tr ? &L.w_cols : nullptr));
+  L.w_prepared = true;
+  return MYEA_OK;
+}
+
 int fc_product_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long rows, const Epilogue &e) {
   const float *w = net->params + L.idx.first_connection_index;
-  if (L.shared_panels && gemm_takes_mn_major(net->ctx, rows, L.n_out) && gemm_takes_mn_major(net->ctx, rows, L.n_in)) {
-    // (a short last batch may fall below the 256 x 256 kernel's shapes: then the layer goes the per-contraction way)
+  if (fc_uses_shared_panels(net, L, rows)) {
     // while training, the same pass also writes the column readings the backward contractions will want
     const bool tr = net->training;
     RC(gemm_prepare_shared(net->ctx, input, L.n_in, rows, L.n_in, L.in_panel_mem, PANEL_ROLE_A, &L.in_rows, PANEL_ROLE_B, tr ? &L.in_cols : nullptr));
-    RC(gemm_prepare_shared(net->ctx, w, L.n_in, L.n_out, L.n_in, L.w_panel_mem, PANEL_ROLE_B, &L.w_rows, PANEL_ROLE_B, tr ? &L.w_cols : nullptr));
+    if (!L.w_prepared) RC(fc_prepare_weights(net, L));
+    L.w_prepared = false;
     L.in_valid = L.w_valid = tr;
     L.in_src = input;
     L.d_valid = false;
@@ -546,8 +565,23 @@ static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cu
   net->training = training != 0;
   net->active_B = static_cast<long long>(batch);
   const long long rows = net->T * net->active_B;
-  CK(cudaMemcpyAsync(net->d_input, src, rows * net->layers[0].n_out * sizeof(float), kind, net->ctx.stream));
   const int n = static_cast<int>(net->layers.size());
+  for (auto &L : net->layers) L.w_prepared = false;
+  if (kind == cudaMemcpyHostToDevice) {
+    // inputs from the host: copy them on the side stream (once everything already queued has finished with d_input)
+    // and split every large layer's weights meanwhile - the copy takes longer than all those passes together
+    CK(cudaEventRecord(net->ev_input_free, net->ctx.stream));
+    CK(cudaStreamWaitEvent(net->copy_stream, net->ev_input_free, 0));
+    CK(cudaMemcpyAsync(net->d_input, src, rows * net->layers[0].n_out * sizeof(float), kind, net->copy_stream));
+    CK(cudaEventRecord(net->ev_input_ready, net->copy_stream));
+    for (int l = 1; l < n; ++l) {
+      LayerPlan &L = net->layers[l];
+      if (L.type == MYEA_LAYER_FULLY_CONNECTED && fc_uses_shared_panels(net, L, rows)) RC(fc_prepare_weights(net, L));
+    }
+    CK(cudaStreamWaitEvent(net->ctx.stream, net->ev_input_ready, 0));
+  } else {
+    CK(cudaMemcpyAsync(net->d_input, src, rows * net->layers[0].n_out * sizeof(float), kind, net->ctx.stream));
+  }
   for (int l = 1; l < n;) {
     LayerPlan &L = net->layers[l];
     const LayerPlan &in = net->layers[L.input_layer];

@@ -44,6 +44,7 @@ struct LayerPlan {
   float *in_panel_mem = nullptr, *w_panel_mem = nullptr, *d_panel_mem = nullptr;
   Panels in_rows, in_cols, w_rows, w_cols, d_rows, d_cols;
   bool in_valid = false, w_valid = false, d_valid = false;
+  bool w_prepared = false;  // the weight panels have already been made in this forward pass (hoisted under the input copy)
   const float *in_src = nullptr;  // the array the input panels were made from
 };
 
@@ -92,5 +93,6 @@ struct myea_b200_net {
   // that is still executing; the two events order it against the error kernel's use of d_desired
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t ev_desired_ready = nullptr, ev_desired_free = nullptr;
+  cudaEvent_t ev_input_ready = nullptr, ev_input_free = nullptr;  // the same for inputs arriving from the host
   std::vector<void *> allocations;
 };
