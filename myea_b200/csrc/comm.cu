@@ -58,6 +58,7 @@ struct CommState {
   cudaStream_t stream = nullptr;   // bucket all-reduces run here, beside the compute stream
   cudaEvent_t ready = nullptr;     // compute -> comm: the bucket is complete
   cudaEvent_t done = nullptr;      // comm -> compute: every bucket issued so far is reduced
+  cudaEvent_t side_done = nullptr; // comm -> compute: the small sum started by comm_side_sum_begin has arrived
   bool pending = false;
   size_t reduced_weights = 0;      // how much of the weight range has been handed to the comm stream this step
   struct Bucket { size_t offset = 0, n = 0; cudaEvent_t reduced = nullptr; };
@@ -117,6 +118,25 @@ int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n) {
   return MYEA_OK;
 }
 
+// A small in-place sum over the ranks on the comm stream, beside whatever the compute stream is given next.
+int comm_side_sum_begin(myea_b200_net *net, float *buf, size_t n) {
+  CommState *c = net->comm;
+  if (c == nullptr) return MYEA_E_INVALID;
+  NcclApi *api = nccl_api();
+  if (cudaEventRecord(c->ready, net->ctx.stream) != cudaSuccess || cudaStreamWaitEvent(c->stream, c->ready, 0) != cudaSuccess) return MYEA_E_CUDA;
+  ncclResult_t r = api->AllReduce(buf, buf, n, ncclFloat, ncclSum, c->comm, c->stream);
+  if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllReduce (side)");
+  if (cudaEventRecord(c->side_done, c->stream) != cudaSuccess) return MYEA_E_CUDA;
+  net->ctx.launches += 1;
+  net->ctx.class_launches[TC_COMM] += 1;
+  return MYEA_OK;
+}
+int comm_side_sum_end(myea_b200_net *net) {
+  CommState *c = net->comm;
+  if (c == nullptr) return MYEA_E_INVALID;
+  return cudaStreamWaitEvent(net->ctx.stream, c->side_done, 0) == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
 // Makes the compute stream wait until every bucket issued so far has been reduced.
 int comm_join(myea_b200_net *net) {
   CommState *c = net->comm;
@@ -154,6 +174,7 @@ void comm_destroy(myea_b200_net *net) {
   if (api && net->comm->comm) api->CommDestroy(net->comm->comm);
   if (net->comm->ready) cudaEventDestroy(net->comm->ready);
   if (net->comm->done) cudaEventDestroy(net->comm->done);
+  if (net->comm->side_done) cudaEventDestroy(net->comm->side_done);
   for (auto &b : net->comm->buckets) if (b.reduced) cudaEventDestroy(b.reduced);
   if (net->comm->stream) cudaStreamDestroy(net->comm->stream);
   delete net->comm;
@@ -191,7 +212,8 @@ extern "C" int myea_b200_comm_init(myea_handle net, int world, int rank, const u
   if (r != ncclSuccess) { delete c; return nccl_fail(net, r, "ncclCommInitRank"); }
   if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->ready, cudaEventDisableTiming) != cudaSuccess ||
-      cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming) != cudaSuccess) {
+      cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&c->side_done, cudaEventDisableTiming) != cudaSuccess) {
     delete c;
     net->ctx.error = "stream / event creation failed";
     return MYEA_E_CUDA;
@@ -200,5 +222,7 @@ extern "C" int myea_b200_comm_init(myea_handle net, int world, int rank, const u
   net->hook.world = world;
   net->hook.user = net;
   net->hook.all_reduce = [](void *user, float *buf, size_t n) { return comm_all_reduce_sum(static_cast<myea_b200_net *>(user), buf, n); };
+  net->hook.begin = [](void *user, float *buf, size_t n) { return comm_side_sum_begin(static_cast<myea_b200_net *>(user), buf, n); };
+  net->hook.end = [](void *user) { return comm_side_sum_end(static_cast<myea_b200_net *>(user)); };
   return MYEA_OK;
 }

@@ -233,11 +233,20 @@ struct SumHook {
   int world = 1;
   void *user = nullptr;
   int (*all_reduce)(void *user, float *buf, size_t n) = nullptr;
+  // split form: `begin` starts the sum on a side stream once everything queued so far has finished, `end` makes the
+  // main stream wait for it; work queued on the main stream in between runs beside the exchange
+  int (*begin)(void *user, float *buf, size_t n) = nullptr;
+  int (*end)(void *user) = nullptr;
+};
+// something independent of the sums that can be queued while they travel (may be null)
+struct OverlapWork {
+  int (*run)(void *arg) = nullptr;
+  void *arg = nullptr;
 };
 
 // z [rows,H] -> batch statistics (training) or running statistics (inference) -> col_scale / col_shift
 int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H, const NormParams &np, int training,
-                       const SumHook *hook = nullptr);
+                       const SumHook *hook = nullptr, const OverlapWork *meanwhile = nullptr);
 // out = dropout(f(z*col_scale+col_shift)) ; col_scale null = no normalization. mask: uint8[H] or null; keep_scale = 1/p for inverted dropout
 int activation_forward(Context &ctx, const float *z, float *out, long long rows, long long H, uint32_t af,
                        const float *col_scale, const float *col_shift, const uint8_t *mask, float keep_scale);

@@ -150,7 +150,7 @@ __global__ void norm_stats_finalize_kernel(const float *__restrict__ partial, in
 }
 
 int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H, const NormParams &np, int training,
-                       const SumHook *hook) {
+                       const SumHook *hook, const OverlapWork *meanwhile) {
   ctx.begin(TC_NORM);
   int launches = 1;
   int chunks = 1;
@@ -165,7 +165,15 @@ int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H
       float *g = np.partial + 2ll * np.chunks * H + 3 * H;
       chunk_sum_kernel<<<static_cast<unsigned>((H + 255) / 256), 256, 0, ctx.stream>>>(np.partial, chunks, H, g);
       ctx.end(TC_NORM, launches + 1);
-      if (hook->all_reduce(hook->user, g, static_cast<size_t>(2 * H)) != MYEA_OK) return MYEA_E_COMM;
+      if (hook->begin != nullptr && hook->end != nullptr && meanwhile != nullptr && meanwhile->run != nullptr && !ctx.profiling) {
+        // the exchange is pure latency (a few KB): queue the caller's independent work beside it
+        if (hook->begin(hook->user, g, static_cast<size_t>(2 * H)) != MYEA_OK) return MYEA_E_COMM;
+        const int rc = meanwhile->run(meanwhile->arg);
+        if (hook->end(hook->user) != MYEA_OK) return MYEA_E_COMM;
+        if (rc != MYEA_OK) return rc;
+      } else if (hook->all_reduce(hook->user, g, static_cast<size_t>(2 * H)) != MYEA_OK) {
+        return MYEA_E_COMM;
+      }
       ctx.begin(TC_NORM);
       launches = 1;
       sums = g;

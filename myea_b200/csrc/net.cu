@@ -525,7 +525,18 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
   RC(fc_product_forward(net, L, input, rows, e));
   const float *cs = nullptr, *ch = nullptr;
   if (L.has_norm) {
-    RC(norm_forward_stats(net->ctx, L.summations, rows, L.n_out, L.norm, net->training ? 1 : 0, &net->hook));
+    // data-parallel ranks exchange the column sums here; the next layer's weight panels depend on nothing that is in
+    // flight and are made while the sums travel
+    struct Next { myea_b200_net *net; LayerPlan *layer; } next{net, nullptr};
+    const size_t li = static_cast<size_t>(&L - net->layers.data());
+    if (li + 1 < net->layers.size()) {
+      LayerPlan &N = net->layers[li + 1];
+      if (N.type == MYEA_LAYER_FULLY_CONNECTED && !N.w_prepared && fc_uses_shared_panels(net, N, rows)) next.layer = &N;
+    }
+    OverlapWork work;
+    work.arg = &next;
+    work.run = [](void *arg) { Next *p = static_cast<Next *>(arg); return fc_prepare_weights(p->net, *p->layer); };
+    RC(norm_forward_stats(net->ctx, L.summations, rows, L.n_out, L.norm, net->training ? 1 : 0, &net->hook, next.layer != nullptr ? &work : nullptr));
     cs = L.norm.col_scale;
     ch = L.norm.col_shift;
   }
