@@ -207,6 +207,39 @@ int myea_b200_train_epoch(myea_handle h, const uint64_t *order, uint64_t number_
 int myea_b200_evaluate(myea_handle h, const uint64_t *order, uint64_t number_examples, double *loss, double *loss_sum,
                        uint64_t *number_loss, double *accuracy_sum);
 
+/* Checkpoint files in the reference's text format, written from and read into the device-resident network.
+ * myea_b200_save_dimension_parameters: Neural_Network::Save_Dimension_Parameters (Neural_Network__Save.cpp:204-624),
+ *   the `.nn` file: dimensions, every connection with its weight, biases, normalization scale / shift / running
+ *   averages.  Parameters and averages are copied from the device first, as the reference does (Save.cpp:227-237).
+ * myea_b200_save_general_parameters: Neural_Network::Save_General_Parameters (Save.cpp:23-202), the `.net` file:
+ *   optimizer, loss, accuracy, regularization and normalization settings, taken from the handle's description and
+ *   `opt`; fields of optimizers that are not built here carry the reference constructor's values.
+ * myea_b200_load: Neural_Network::Load (Neural_Network__Load.cpp:2323): builds the network both files describe for
+ *   `batch_size` rows on `device`, uploads parameters and averages, and returns the optimizer settings in `opt` (may
+ *   be null).  Optimizer moments are in neither file (the reference does not save them): a loaded network starts
+ *   with zero moments; its regularization mask covers the weights, as the reference builds it.  Bidirectional LSTM layers, pooling and independently recurrent layers: MYEA_E_UNSUPPORTED.
+ * Both files are byte-identical to the reference's for the same network state, and each side reads the other's.
+ *
+ * The format / parse halves work on host arrays and need no GPU:
+ * myea_b200_checkpoint_format_dimension / _format_general write the two files from a description, `parameters`
+ *   [total_parameters] and the two average arrays [total_normalized_units] (null without normalization);
+ * myea_b200_checkpoint_parse reads them back: with `parameters` null it returns the description (batch_size filled
+ *   in from the argument) and the two totals; with arrays of at least those sizes it fills them as well.
+ *   `path_general` may be null (description fields that live in the `.net` file then stay 0 = class default).
+ * myea_b200_checkpoint_last_error: why the last parse / load on this thread failed. */
+int myea_b200_save_dimension_parameters(myea_handle h, const char *path);
+int myea_b200_save_general_parameters(myea_handle h, const myea_opt_desc *opt, const char *path);
+int myea_b200_load(myea_handle *out, const char *path_dimension, const char *path_general, uint64_t batch_size, int device,
+                   myea_opt_desc *opt);
+int myea_b200_checkpoint_format_dimension(const myea_net_desc *desc, const float *parameters, const float *mean_average,
+                                          const float *variance_average, const char *path);
+int myea_b200_checkpoint_format_general(const myea_net_desc *desc, const myea_opt_desc *opt, const char *path);
+int myea_b200_checkpoint_parse(const char *path_dimension, const char *path_general, uint64_t batch_size, myea_net_desc *desc,
+                               myea_opt_desc *opt, float *parameters, uint64_t parameters_capacity, float *mean_average,
+                               float *variance_average, uint64_t norm_capacity, uint64_t *total_parameters,
+                               uint64_t *total_normalized_units);
+const char *myea_b200_checkpoint_last_error(void);
+
 /* ShakeDrop draws of one residual block made explicit: mask bool[B] (Layer::ptr_array__mask__dropout__shakedrop,
  * Data.hpp:612), forward coefficients alpha[B][units] and backward coefficients beta[B][units]
  * (Neural_Network__Forward_Pass__OpenMP.cpp:5021-5056, Neural_Network__Backward_Pass__OpenMP.cpp:1009-1042). */

@@ -155,6 +155,14 @@ _PROTOS = {
                                         C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "myea_b200_evaluate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_uint64),
                                      C.POINTER(C.c_double)]),
+    "myea_b200_save_dimension_parameters": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "myea_b200_save_general_parameters": (C.c_int, [C.c_void_p, C.POINTER(OptDesc), C.c_char_p]),
+    "myea_b200_load": (C.c_int, [C.POINTER(C.c_void_p), C.c_char_p, C.c_char_p, C.c_uint64, C.c_int, C.POINTER(OptDesc)]),
+    "myea_b200_checkpoint_format_dimension": (C.c_int, [C.POINTER(NetDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p]),
+    "myea_b200_checkpoint_format_general": (C.c_int, [C.POINTER(NetDesc), C.POINTER(OptDesc), C.c_char_p]),
+    "myea_b200_checkpoint_parse": (C.c_int, [C.c_char_p, C.c_char_p, C.c_uint64, C.POINTER(NetDesc), C.POINTER(OptDesc), C.c_void_p, C.c_uint64,
+                                             C.c_void_p, C.c_void_p, C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "myea_b200_checkpoint_last_error": (C.c_char_p, []),
     "myea_b200_generate_masks": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64]),
     "myea_b200_download_mask": (C.c_int, [C.c_void_p, C.c_uint32, C.c_int, C.c_void_p, C.c_uint64]),
     "myea_b200_upload": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_uint64, C.c_uint64]),

@@ -77,7 +77,7 @@ static int dev_alloc(myea_b200_net *net, T **p, size_t count, bool zero = true) 
 // (Neural_Network__Allocate.cpp:2378-2460): once ANY layer is normalized, gamma for every unit of every layer (input,
 // residual and output layers included) is appended after the biases, then beta for every unit.
 // ---------------------------------------------------------------------------------------------------------
-static int build_index_map(myea_b200_net *net) {
+int myea::build_index_map(myea_b200_net *net) {
   const myea_net_desc &d = net->desc;
   const uint32_t n = d.number_layers;
   net->layers.assign(n, LayerPlan());
@@ -350,7 +350,7 @@ extern "C" int myea_b200_create(myea_handle *out, const myea_net_desc *desc, int
       cudaEventCreateWithFlags(&net->ev_input_ready, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&net->ev_input_free, cudaEventDisableTiming) != cudaSuccess)
     return fail(net, MYEA_E_CUDA, "cudaStreamCreate / cudaEventCreate failed");
-  RC(build_index_map(net));
+  RC(myea::build_index_map(net));
   RC(allocate_buffers(net));
   CK(cudaStreamSynchronize(net->ctx.stream));
   return MYEA_OK;

@@ -55,6 +55,12 @@ int fc_product_backward(myea_b200_net *net, LayerPlan &N, long long rows, const 
 
 }  // namespace myea
 
+struct myea_b200_net;
+namespace myea {
+// fills net->layers (widths, input layers, index map) and the parameter totals from net->desc; host arithmetic only
+int build_index_map(myea_b200_net *net);
+}  // namespace myea
+
 struct myea_b200_net {
   myea::Context ctx;
   myea_net_desc desc;

@@ -76,6 +76,13 @@ bool Neural_Network::Initialize__CUDA(size_t device) {
     ptr_device_Neural_Network = nullptr;
     return false;
   }
+  if (!adopt_device()) return false;
+  is_device_initialized = true;
+  return Copy__Parameters__Host_To_Device();
+}
+
+// sizes, index map and the public host arrays of a freshly created device network
+bool Neural_Network::adopt_device(void) {
   uint64_t P, W, Bn, U;
   myea_b200_sizes(ptr_device_Neural_Network, &P, &W, &Bn, &U);
   total_parameters = P; total_weights = W; total_bias = Bn; total_normalized_units = U;
@@ -94,8 +101,7 @@ bool Neural_Network::Initialize__CUDA(size_t device) {
   ptr_array_normalized_batch_units_variances_averages = host_[7].data();
   for (size_t i = 0; i < W; ++i) host_[5][i] = 1.f;   // weights are regularized, biases and scales / shifts are not
   if (U) for (size_t i = 0; i < U; ++i) host_[0][W + Bn + i] = 1.f;   // scales start at one
-  is_device_initialized = true;
-  return Copy__Parameters__Host_To_Device();
+  return true;
 }
 
 bool Neural_Network::Deinitialize__CUDA(void) {
@@ -197,13 +203,57 @@ void Neural_Network::Update_Derivative_Weight(size_t B) {
   if (rc != MYEA_OK) fail("Update_Derivative_Weight", rc);
 }
 
-void Neural_Network::Update_Parameter(size_t B, size_t N) {
+// the public optimizer members are the state of record, as in the reference; the descriptor follows them
+void Neural_Network::sync_optimizer(void) {
   opt_.learning_rate = learning_rate; opt_.learning_momentum = learning_momentum; opt_.use_nesterov = use_Nesterov ? 1u : 0u;
   opt_.adam_learning_rate = adam_learning_rate; opt_.adam_beta1 = adam_beta1; opt_.adam_beta2 = adam_beta2; opt_.adam_epsilon = adam_epsilon;
   opt_.learning_rate_final = learning_rate_final; opt_.learning_gamma = learning_gamma;
   opt_.use_adam_bias_correction = use_adam_bias_correction ? 1u : 0u;
   opt_.use_normalized_weight_decay = use_normalized_weight_decay ? 1u : 0u;
   opt_.epoch_time_step = epoch_time_step;
+}
+
+bool Neural_Network::Save_General_Parameters(std::string const &path) {
+  sync_optimizer();
+  int rc = myea_b200_checkpoint_format_general(&desc_, &opt_, path.c_str());
+  return rc == MYEA_OK ? true : fail("Save_General_Parameters", rc);
+}
+
+bool Neural_Network::Save_Dimension_Parameters(std::string const &path) {
+  if (!is_device_initialized) return fail("Save_Dimension_Parameters", MYEA_E_INVALID);
+  int rc = myea_b200_save_dimension_parameters(ptr_device_Neural_Network, path.c_str());
+  return rc == MYEA_OK ? true : fail("Save_Dimension_Parameters", rc);
+}
+
+bool Neural_Network::Load(std::string const &path_dimension, std::string const &path_general, size_t desired_batch_size, size_t device) {
+  if (is_device_initialized || desired_batch_size == 0) return fail("Load", MYEA_E_INVALID);
+  int rc = myea_b200_checkpoint_parse(path_dimension.c_str(), path_general.c_str(), desired_batch_size, &desc_, &opt_, nullptr, 0, nullptr, nullptr, 0,
+                                      nullptr, nullptr);
+  if (rc == MYEA_OK) rc = myea_b200_load(&ptr_device_Neural_Network, path_dimension.c_str(), path_general.c_str(), desired_batch_size, static_cast<int>(device), nullptr);
+  if (rc != MYEA_OK) {
+    error_ = std::string("Load: ") + myea_b200_checkpoint_last_error();
+    fprintf(stderr, "%s\n", error_.c_str());
+    if (ptr_device_Neural_Network != nullptr) myea_b200_destroy(ptr_device_Neural_Network);
+    ptr_device_Neural_Network = nullptr;
+    return false;
+  }
+  total_layers = desc_.number_layers;
+  number_recurrent_depth = desc_.number_recurrent_depth;
+  number_inputs = desc_.layers[0].unit_parameters[0];
+  number_outputs = desc_.layers[total_layers - 1].unit_parameters[0];
+  batch_size = desired_batch_size;
+  learning_rate = opt_.learning_rate; learning_momentum = opt_.learning_momentum; use_Nesterov = opt_.use_nesterov != 0;
+  adam_learning_rate = opt_.adam_learning_rate; adam_beta1 = opt_.adam_beta1; adam_beta2 = opt_.adam_beta2; adam_epsilon = opt_.adam_epsilon;
+  learning_rate_final = opt_.learning_rate_final; learning_gamma = opt_.learning_gamma;
+  use_adam_bias_correction = opt_.use_adam_bias_correction != 0;
+  use_normalized_weight_decay = opt_.use_normalized_weight_decay != 0;
+  if (!adopt_device()) return false;
+  is_device_initialized = true;
+  return Copy__Parameters__Device_To_Host() && (total_normalized_units == 0 || Copy__Batch_Normalization_Neurons__Device_To_Host());
+}
+
+void Neural_Network::Update_Parameter(size_t B, size_t N) {
+  sync_optimizer();
   int rc = is_device_initialized ? myea_b200_update_parameter(ptr_device_Neural_Network, B, N, &opt_) : MYEA_E_INVALID;
   if (rc != MYEA_OK) fail("Update_Parameter", rc);
 }

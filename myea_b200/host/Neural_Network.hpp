@@ -87,6 +87,16 @@ class Neural_Network {
   float Get__Accuracy(void);   // accumulated hits / number_accuracy_trial * 100
   float const *Get__Outputs(size_t data_index, size_t time_step_index = 0);
 
+  // ---- checkpoint files in the reference's text format (Neural_Network__Save.cpp:23, :204; Neural_Network__Load.cpp:2323) ----
+  // Save_*: written from the device-resident state (parameters and normalization averages are copied back first, as
+  // Save.cpp:227-237 does).  Load: call on a fresh object; it takes the place of Compile + Set__* and leaves the
+  // network initialized on `device_index` for `desired_batch_size` rows with parameters uploaded.  The reference's
+  // third argument (maximum allowable memory) has no meaning here and is replaced by the batch size the device
+  // buffers are carved for.
+  bool Save_General_Parameters(std::string const &path);
+  bool Save_Dimension_Parameters(std::string const &path);
+  bool Load(std::string const &path_dimension, std::string const &path_general, size_t desired_batch_size, size_t device_index = 0);
+
   char const *Get__Last_Error(void) const { return error_.c_str(); }
 
   // ---- public state, as in the reference (Data.hpp:2786-3048) ----
@@ -107,6 +117,8 @@ class Neural_Network {
 
  private:
   bool fail(char const *where, int status);
+  void sync_optimizer(void);
+  bool adopt_device(void);
   unsigned long long draws_ = 0;
   bool pack(float const *const *rows, size_t batch, size_t width, std::vector<float> &dst);
   myea_net_desc desc_ = {};

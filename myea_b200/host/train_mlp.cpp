@@ -2,10 +2,14 @@
 // cross-entropy, Adam, batch 128) trained for a few steps on seeded synthetic data, written the way the reference's
 // own harness drives `class Neural_Network` (Neural_Network_Launcher_Windows/Source_Files/debug.cpp).
 // Prints one line per step: "step <i> loss <mean cross-entropy term> accuracy <percent>".
+// With a second argument <prefix> the trained network is then written to <prefix>.nn / <prefix>.net in the reference's
+// checkpoint format, read back into a second object with Load, and both answer the batch in inference mode:
+// "checkpoint round trip: identical" when every output agrees bit for bit.
 #include <stdio.h>
 #include <stdlib.h>
 
 #include <random>
+#include <string>
 #include <vector>
 
 #include "Neural_Network.hpp"
@@ -60,5 +64,22 @@ int main(int argc, char **argv) {
     nn.Update_Parameter(B, B);
   }
   if (!nn.Copy__Parameters__Device_To_Host()) return 1;
+  if (argc > 2) {
+    std::string const prefix(argv[2]);
+    if (!nn.Save_Dimension_Parameters(prefix + ".nn") || !nn.Save_General_Parameters(prefix + ".net")) return 3;
+    Neural_Network again;
+    if (!again.Load(prefix + ".nn", prefix + ".net", B, 0)) return 3;
+    nn.type_state_propagation = again.type_state_propagation = 0;
+    nn.Forward_Pass(B, xp.data());
+    again.Forward_Pass(B, xp.data());
+    size_t differing = 0;
+    for (size_t b = 0; b < B; ++b) {
+      float const *p = nn.Get__Outputs(b), *q = again.Get__Outputs(b);
+      for (size_t o = 0; o < sizes[3]; ++o) differing += (p[o] != q[o]) ? 1 : 0;
+    }
+    for (size_t i = 0; i < nn.total_parameters; ++i) differing += (nn.ptr_array_parameters[i] != again.ptr_array_parameters[i]) ? 1 : 0;
+    printf("checkpoint round trip: %s\n", differing == 0 ? "identical" : "DIFFERENT");
+    if (differing != 0) return 4;
+  }
   return (last < first) ? 0 : 2;   // the loss must go down on a fixed batch
 }

@@ -31,6 +31,35 @@ class Net:
         self.B = int(desc.batch_size)
         self.P, self.W, self.n_bias, self.n_norm = self.sizes()
 
+    @classmethod
+    def load(cls, path_dimension, path_general, batch, device=0):
+        """Neural_Network::Load (Neural_Network__Load.cpp:2323): the network the reference's `.nn` / `.net` files describe,
+        built for `batch` rows with parameters and normalization averages uploaded; .opt holds the optimizer settings"""
+        self = cls.__new__(cls)
+        self.lib = capi.load()
+        self.h = C.c_void_p()
+        opt = capi.OptDesc()
+        rc = self.lib.myea_b200_load(C.byref(self.h), str(path_dimension).encode(), str(path_general).encode(), int(batch), device, C.byref(opt))
+        if rc != 0:
+            msg = self.lib.myea_b200_checkpoint_last_error().decode() or (self.lib.myea_b200_last_error(self.h).decode() if self.h else "")
+            if self.h:
+                self.lib.myea_b200_destroy(self.h)
+            self.h = None
+            raise RuntimeError("myea_b200_load failed (%d): %s" % (rc, msg))
+        from . import checkpoint
+        self.desc = checkpoint.parse(path_dimension, path_general, batch, arrays=False)[0]
+        self.opt = opt
+        self.T = int(self.desc.number_recurrent_depth)
+        self.B = int(batch)
+        self.P, self.W, self.n_bias, self.n_norm = self.sizes()
+        return self
+
+    def save(self, path_dimension, path_general=None, opt=None):
+        """Save_Dimension_Parameters / Save_General_Parameters (Neural_Network__Save.cpp:204, :23)"""
+        self._ck(self.lib.myea_b200_save_dimension_parameters(self.h, str(path_dimension).encode()), "save_dimension_parameters")
+        if path_general is not None:
+            self._ck(self.lib.myea_b200_save_general_parameters(self.h, C.byref(opt or self.opt), str(path_general).encode()), "save_general_parameters")
+
     def _ck(self, rc, what):
         if rc != 0:
             raise RuntimeError("%s failed (%d): %s" % (what, rc, self.lib.myea_b200_last_error(self.h).decode()))

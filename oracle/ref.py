@@ -45,6 +45,11 @@ def _lib():
         lib.ref_get_outputs.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p]
         lib.ref_get_errors.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p]
         lib.ref_shakedrop_replay.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.ref_save.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p]
+        lib.ref_load.restype = C.c_void_p
+        lib.ref_load.argtypes = [C.c_char_p, C.c_char_p]
+        lib.ref_layer_state.argtypes = [C.c_void_p, C.c_uint32, C.POINTER(capi.LayerDesc)]
+        lib.ref_general_state.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]
         lib.ref_time_steps.restype = C.c_double
         lib.ref_time_steps.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int, C.c_int]
         _LIB = lib
@@ -66,6 +71,35 @@ class RefNet:
         self.B = int(desc.batch_size)
         self.P, self.W, self.n_bias, self.n_norm = self.sizes()
         self.threads = self.lib.ref_threads(self.h)
+
+    @classmethod
+    def load(cls, path_dimension, path_general):
+        """the reference's own Load (Neural_Network__Load.cpp:2323) into a fresh object (buffers and state queries only)"""
+        self = cls.__new__(cls)
+        self.lib = _lib()
+        self.h = self.lib.ref_load(str(path_dimension).encode(), str(path_general).encode())
+        if not self.h:
+            raise RuntimeError("the reference's Load rejected the files")
+        self.P, self.W, self.n_bias, self.n_norm = self.sizes()
+        self.T = self.B = 1
+        self.threads = 1
+        return self
+
+    def save(self, path_dimension, path_general=None):
+        """the reference's own Save_Dimension_Parameters / Save_General_Parameters (Neural_Network__Save.cpp:204, :23)"""
+        if self.lib.ref_save(self.h, str(path_dimension).encode(), None if path_general is None else str(path_general).encode()) != 0:
+            raise RuntimeError("the reference's Save_* failed")
+
+    def layer_state(self, layer):
+        d = capi.LayerDesc()
+        if self.lib.ref_layer_state(self.h, layer, C.byref(d)) != 0:
+            raise IndexError(layer)
+        return d
+
+    def general_state(self):
+        v, u = (C.c_float * 12)(), (C.c_uint64 * 8)()
+        self.lib.ref_general_state(self.h, v, u)
+        return list(v), list(u)
 
     def close(self):
         if self.h:

@@ -368,4 +368,61 @@ int ref_shakedrop_replay(void *h, uint64_t B, uint8_t *masks, float *alpha, floa
   return static_cast<int>(blocks.size());
 }
 
+// The reference's own checkpoint writers (Neural_Network__Save.cpp:23 and :204) on this network.
+int ref_save(void *h, const char *path_dimension, const char *path_general) {
+  Neural_Network &nn = static_cast<RefNet *>(h)->nn;
+  if (path_dimension != nullptr && !nn.Save_Dimension_Parameters(path_dimension)) return -1;
+  if (path_general != nullptr && !nn.Save_General_Parameters(path_general)) return -1;
+  return 0;
+}
+
+// The reference's own checkpoint reader (Neural_Network__Load.cpp:2323) into a fresh object; the handle supports
+// ref_sizes / ref_layer_index / ref_buffer / ref_layer_state / ref_general_state.
+void *ref_load(const char *path_dimension, const char *path_general) {
+  RefNet *r = new RefNet();
+  if (!r->nn.Load(path_dimension, path_general, size_t(1) << 40)) {
+    delete r;
+    return nullptr;
+  }
+  r->n_inputs = r->nn.number_inputs;
+  r->n_outputs = r->nn.number_outputs;
+  r->T = r->nn.number_recurrent_depth;
+  return r;
+}
+
+// Per-layer configuration of a loaded object, in descriptor form.
+int ref_layer_state(void *h, uint32_t layer, myea_layer_desc *out) {
+  Neural_Network &nn = static_cast<RefNet *>(h)->nn;
+  if (layer >= nn.total_layers) return -1;
+  Layer *L = nn.ptr_array_layers + layer;
+  std::memset(out, 0, sizeof(*out));
+  out->type_layer = L->type_layer;
+  out->use_bidirectional = L->use_bidirectional;
+  out->type_activation_function = L->ptr_array_AF_units != L->ptr_last_AF_unit
+                                      ? static_cast<uint32_t>(*L->ptr_array_AF_units->ptr_type_activation_function) : 0u;
+  out->type_normalization = L->type_normalization;
+  out->use_layer_normalization_before_activation = L->use_layer_normalization_before_activation;
+  out->type_dropout = L->type_dropout;
+  for (int k = 0; k < 3; ++k) out->dropout_values[k] = L->dropout_values[k];
+  out->unit_parameters[0] = *L->ptr_number_outputs;
+  return 0;
+}
+
+// Network-level training state of a loaded object: v[0..] = learning_rate, learning_momentum, adam_learning_rate,
+// adam_beta1, adam_beta2, adam_epsilon, regularization__weight_decay, clip_gradient, normalization_momentum_average,
+// normalization_epsilon, accuracy_variance, regularization__max_norm_constraints; u[0..] = type_optimizer_function,
+// type_loss_function, type_accuracy_function, use_Nesterov, use_clip_gradient, type_network, number_recurrent_depth,
+// number_time_delays.
+int ref_general_state(void *h, float v[12], uint64_t u[8]) {
+  Neural_Network &nn = static_cast<RefNet *>(h)->nn;
+  v[0] = nn.learning_rate; v[1] = nn.learning_momentum; v[2] = nn.adam_learning_rate; v[3] = nn.adam_beta1;
+  v[4] = nn.adam_beta2; v[5] = nn.adam_epsilon; v[6] = nn.regularization__weight_decay; v[7] = nn.clip_gradient;
+  v[8] = nn.normalization_momentum_average; v[9] = nn.normalization_epsilon; v[10] = nn.accuracy_variance;
+  v[11] = nn.regularization__max_norm_constraints;
+  u[0] = nn.type_optimizer_function; u[1] = nn.type_loss_function; u[2] = nn.type_accuracy_function;
+  u[3] = nn.use_Nesterov; u[4] = nn.use_clip_gradient; u[5] = nn.type_network; u[6] = nn.number_recurrent_depth;
+  u[7] = nn.number_time_delays;
+  return 0;
+}
+
 }  // extern "C"

@@ -1,0 +1,107 @@
+"""Checkpoint files from and into the device-resident network (myea_b200_save_dimension_parameters,
+myea_b200_save_general_parameters, myea_b200_load; Neural_Network__Save.cpp:23, :204, Neural_Network__Load.cpp:2323).
+
+  * a network trained for two steps on the GPU is saved; the files parse back to exactly the parameters and running
+    statistics the device holds, and a second network made by myea_b200_load answers the same batch in inference mode
+    bit for bit, its description equal to the first one's,
+  * files the unmodified reference wrote after its own two training steps (tests/golden/checkpoint) load onto the GPU
+    and the loaded network's inference outputs equal, bit for bit, those of a network built from the description with
+    the fixture's parameters uploaded: a reference-trained model continues here.
+
+Exact equality throughout: the text round-trips fp32, and both networks run the same kernels on the same values."""
+import gzip
+import os
+
+import numpy as np
+import pytest
+
+import cases
+from myea_b200 import capi, checkpoint
+from myea_b200.net import Net
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TRAINED = ["mlp_brn_elu_adabound_wd", "mlp_wide_bn_dropout_adam", "c2_small", "lstm2_zoneout_clip", "c3_small", "c4_small", "mlp_tanh_nesterov_ce"]
+FIXTURES = ["mlp_brn_elu_adabound_wd", "mlp_tanh_nesterov_ce", "lstm2_zoneout_clip", "res_bn_tanh_adam_noshake"]
+
+
+def _inference(net, wl, X):
+    net.forward(X, training=False)
+    return net.outputs(len(wl.layers) - 1).copy()
+
+
+@pytest.mark.parametrize("name", TRAINED)
+def test_save_then_load_from_the_device(name, tmp_path):
+    wl = cases.CASES[name]()
+    net = Net(wl.desc, wl.opt)
+    shake = cases.shake_from_golden(np.load(os.path.join(GOLD, name + ".npz"))) if name == "c4_small" else None
+    cases.run_steps(net, wl, shake=shake)
+    nn, general = tmp_path / "t.nn", tmp_path / "t.net"
+    net.save(nn, general)
+    params = net.get(capi.BUF_PARAMETERS)
+    units = net.sizes()[3]
+    desc, opt, p, m, s = checkpoint.parse(nn, general, batch=wl.desc.batch_size)
+    saved = np.ones(params.size, bool)
+    for l in range(1, wl.desc.number_layers):            # cell-input bias slots of LSTM layers are not in the file
+        if wl.desc.layers[l].type_layer == capi.LAYER_LSTM:
+            li = net.layer_index(l)
+            saved[int(li.first_bias_connection_index) - int(li.number_outputs):int(li.first_bias_connection_index)] = False
+        li = net.layer_index(l)
+    for l in range(wl.desc.number_layers):               # scale / shift slots of layers that are not normalized neither
+        li = net.layer_index(l)
+        if units and wl.desc.layers[l].type_normalization == capi.NORM_NONE:
+            saved[int(li.scale_index):int(li.scale_index) + int(li.number_units_norm)] = False
+            saved[int(li.shift_index):int(li.shift_index) + int(li.number_units_norm)] = False
+    assert np.array_equal(p[saved], params[saved])
+    if units:
+        mean, sigma = net.get(capi.BUF_NORM_MEAN_AVERAGE), net.get(capi.BUF_NORM_VARIANCE_AVERAGE)
+        for l in range(1, wl.desc.number_layers):
+            if wl.desc.layers[l].type_normalization != capi.NORM_NONE:
+                li = net.layer_index(l)
+                lo = int(li.scale_index) - (params.size - 2 * units)
+                hi = lo + int(li.number_units_norm)
+                assert np.array_equal(m[lo:hi], mean[lo:hi]) and np.array_equal(s[lo:hi], sigma[lo:hi])
+                assert np.abs(mean[lo:hi]).max() > 0           # the statistics did move during the two steps
+    X, _ = wl.batch()
+    want = _inference(net, wl, X)
+    again = Net.load(nn, general, wl.desc.batch_size)
+    assert again.sizes() == net.sizes()
+    got = _inference(again, wl, X)
+    assert np.array_equal(got, want)
+    assert again.opt.type_optimizer_function == wl.opt.type_optimizer_function
+    # and the loaded network saves to the same bytes
+    nn2 = tmp_path / "t2.nn"
+    again.save(nn2)
+    if not (~saved).any():
+        assert nn2.read_bytes() == nn.read_bytes()
+    net.close()
+    again.close()
+
+
+@pytest.mark.parametrize("name", FIXTURES)
+def test_reference_written_files_load_onto_the_gpu(name, tmp_path):
+    wl = cases.CASES[name]()
+    nn, general = tmp_path / "r.nn", tmp_path / "r.net"
+    with gzip.open(os.path.join(GOLD, "checkpoint", name + ".nn.gz"), "rb") as f:
+        nn.write_bytes(f.read())
+    with open(os.path.join(GOLD, "checkpoint", name + ".net"), "rb") as f:
+        general.write_bytes(f.read())
+    loaded = Net.load(nn, general, wl.desc.batch_size)
+    g = np.load(os.path.join(GOLD, name + ".npz"))
+    P, _, _, units = [int(v) for v in g["sizes"]]
+    assert loaded.sizes()[0] == P and loaded.sizes()[3] == units
+    built = Net(wl.desc, wl.opt)
+    wl.materialize(built)
+    built.set(capi.BUF_PARAMETERS, g["param1"][:P])
+    if units:
+        built.set(capi.BUF_NORM_MEAN_AVERAGE, g["norm_mean_avg"][:units])
+        built.set(capi.BUF_NORM_VARIANCE_AVERAGE, g["norm_sigma_avg"][:units])
+    X, _ = wl.batch()
+    assert np.array_equal(_inference(loaded, wl, X), _inference(built, wl, X))
+    loaded.close()
+    built.close()
+
+
+def test_load_reports_why_it_failed(tmp_path):
+    with pytest.raises(RuntimeError, match="cannot open"):
+        Net.load(tmp_path / "none.nn", tmp_path / "none.net", 8)

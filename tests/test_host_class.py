@@ -36,3 +36,16 @@ def test_trains_config_1_through_the_reference_api():
     assert len(losses) == 12
     assert 0.15 < losses[0] < 0.6                      # mean of -t*log(y) over 10 outputs, near ln(10)/10 at the start
     assert all(b < a for a, b in zip(losses, losses[1:]))
+
+
+@pytest.mark.gpu
+def test_checkpoint_round_trip_through_the_reference_api(tmp_path):
+    """Save_Dimension_Parameters / Save_General_Parameters / Load of the host class: the trained network written in
+    the reference's text format and read into a second object answers the batch identically"""
+    prefix = str(tmp_path / "mlp")
+    r = subprocess.run([EXE, "4", prefix], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "checkpoint round trip: identical" in r.stdout
+    head = open(prefix + ".nn", "rb").read(200)
+    assert head.startswith(b"|===| DIMENSION |===|\r\ntype_network 3\r\nnumber_layers 4\r\n")
+    assert b"type_optimizer_function 2\r\n" in open(prefix + ".net", "rb").read()
