@@ -42,11 +42,18 @@ def test_save_then_load_from_the_device(name, tmp_path):
     units = net.sizes()[3]
     desc, opt, p, m, s = checkpoint.parse(nn, general, batch=wl.desc.batch_size)
     saved = np.ones(params.size, bool)
-    for l in range(1, wl.desc.number_layers):            # cell-input bias slots of LSTM layers are not in the file
+    # The first `cells` bias slots of an LSTM layer are not in the file: the reference's writer lists 3 * blocks values
+    # from the index it already shifted by the cell count.  The layer BEFORE reads its output-gate bias from those very
+    # slots (its four bias runs start at its own shifted index), so in the reference's format a stacked LSTM network
+    # comes back with that bias at zero.  The comparison below therefore starts from a network whose slots are zero.
+    for l in range(1, wl.desc.number_layers):
         if wl.desc.layers[l].type_layer == capi.LAYER_LSTM:
             li = net.layer_index(l)
             saved[int(li.first_bias_connection_index) - int(li.number_outputs):int(li.first_bias_connection_index)] = False
-        li = net.layer_index(l)
+    if (~saved).any():
+        params = params.copy()
+        params[~saved] = 0.0
+        net.set(capi.BUF_PARAMETERS, params)
     for l in range(wl.desc.number_layers):               # scale / shift slots of layers that are not normalized neither
         li = net.layer_index(l)
         if units and wl.desc.layers[l].type_normalization == capi.NORM_NONE:
@@ -72,8 +79,7 @@ def test_save_then_load_from_the_device(name, tmp_path):
     # and the loaded network saves to the same bytes
     nn2 = tmp_path / "t2.nn"
     again.save(nn2)
-    if not (~saved).any():
-        assert nn2.read_bytes() == nn.read_bytes()
+    assert nn2.read_bytes() == nn.read_bytes()
     net.close()
     again.close()
 
@@ -92,7 +98,12 @@ def test_reference_written_files_load_onto_the_gpu(name, tmp_path):
     assert loaded.sizes()[0] == P and loaded.sizes()[3] == units
     built = Net(wl.desc, wl.opt)
     wl.materialize(built)
-    built.set(capi.BUF_PARAMETERS, g["param1"][:P])
+    params = g["param1"][:P].copy()
+    for l in range(1, wl.desc.number_layers):            # slots the reference's format does not carry (see above) come back as zero
+        if wl.desc.layers[l].type_layer == capi.LAYER_LSTM:
+            li = built.layer_index(l)
+            params[int(li.first_bias_connection_index) - int(li.number_outputs):int(li.first_bias_connection_index)] = 0.0
+    built.set(capi.BUF_PARAMETERS, params)
     if units:
         built.set(capi.BUF_NORM_MEAN_AVERAGE, g["norm_mean_avg"][:units])
         built.set(capi.BUF_NORM_VARIANCE_AVERAGE, g["norm_sigma_avg"][:units])
