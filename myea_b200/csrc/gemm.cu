@@ -1618,9 +1618,15 @@ int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, co
   } else {
     // gemm_bn: 0 = heuristic, 3 = wide CTA pair (256 x 256), 4 = the same without stream-K, 2 = CTA pair (256 x 128),
     // 128 / 256 = single CTA
-    const bool wide = gemm_takes_mn_major(ctx, M, N);
+    // A short contraction whose 128 x 128 tiles fit one wave of CTAs runs on the single-CTA kernel: every tile walks
+    // its whole K without a partial-sum hand-over, which on such shapes (a recurrent LSTM step, 256 x 4096 x 1024:
+    // 16 wide tiles for 74 clusters) costs more than it saves.  Measured with K <= 1024 for 32 to 128 tiles: 3 to 7 us
+    // less per launch; at K = 2048 the wide kernel with stream-K is ahead again.
+    const long long tiles128 = ((M + 127) / 128) * ((N + 127) / 128);
+    const bool one_wave = ctx.gemm_bn == 0 && !a_mn && !b_mn && M > 128 && N > 128 && A.k <= 1024 && tiles128 <= 148;
+    const bool wide = gemm_takes_mn_major(ctx, M, N) && !one_wave;
     if ((a_mn || b_mn) && !wide) return MYEA_E_INVALID;
-    const bool pair = !wide && (ctx.gemm_bn == 0 ? (M > 128) : (ctx.gemm_bn == 2));
+    const bool pair = !wide && !one_wave && (ctx.gemm_bn == 0 ? (M > 128) : (ctx.gemm_bn == 2));
     const int bn = ctx.gemm_bn == 256 ? 256 : 128;
     const int b_box = wide ? 128 : (pair ? 64 : bn);
     CUtensorMap maps[4];
