@@ -1573,7 +1573,12 @@ static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const Ge
   const int rem = work.num_tiles % G;
   if (ctx.gemm_bn != 4 && ctx.sk_ws != nullptr && ctx.sk_clusters >= G && rem != 0 && num_chunks >= 2) {
     const int units = rem * num_chunks;
-    const int per_cluster = (units + G - 1) / G;
+    int per_cluster = (units + G - 1) / G;
+    // at most 8 clusters share one tile (MYEA_B200_SK_MAX_SPLIT overrides, 0 = no limit): the cluster that arrives last
+    // adds up every other contributor's 256 KB of partial sums, and past 8 that pass outweighs the shorter K walk
+    // (256 x 1024 x 4096, 4 tiles: 16-way split 53.6 us, 8-way 47.2 us, 4-way 51.0 us per call with its split passes)
+    static const int max_split = getenv("MYEA_B200_SK_MAX_SPLIT") != nullptr ? atoi(getenv("MYEA_B200_SK_MAX_SPLIT")) : 8;
+    if (max_split > 0) per_cluster = std::max(per_cluster, (num_chunks + max_split - 1) / max_split);
 
     // splitting a tile costs about one chunk's time (partial sums through L2, one counter round trip, the second
     // pass of the warp that arrives last): worth it when it takes at least two chunks off the longest cluster
