@@ -70,6 +70,7 @@ extern "C" {
 #define MYEA_OPT_AMSBOUND 4u
 #define MYEA_OPT_AMSGRAD 5u
 #define MYEA_OPT_GD 6u
+#define MYEA_OPT_IRPROP_PLUS 8u
 #define MYEA_OPT_NOSADAM 9u
 
 /* One layer, as `struct Layer_Parameters` (Data.hpp:56-80) plus the per-layer Set__* state. */
@@ -120,6 +121,13 @@ typedef struct myea_opt_desc {
   float adam_gamma;           /* NosAdam: beta2_t = B/(B + t^-gamma), B += t^-gamma (Neural_Network__NosAdam.cpp:97-160); 0 = the class default 0.1 */
   float regularization__max_norm_constraints; /* Set__Regularization__Max_Norm_Constraints (Data.hpp:2744): after the update every
                                                  neuron's weight row with norm >= c is scaled to norm c; 0 = off */
+  /* iRPROP+ (Neural_Network__iRPROP_plus.cpp:30-187); 0 in a factor or bound = the class default
+   * (1.2, 0.5, 1e-6, 50, 0.1).  loss_rprop / previous_loss_rprop are the two members Dataset::Train_Epoch keeps
+   * (Dataset.cpp:575-579): a weight whose derivative changed sign is stepped back only when loss_rprop >
+   * previous_loss_rprop.  The reference assigns previous = current before the batch and the new loss after it, so
+   * inside its own training loop the two are always equal at update time; a caller may pass them differently. */
+  float rprop_increase_factor, rprop_decrease_factor, rprop_delta_min, rprop_delta_max, rprop_delta_zero;
+  float loss_rprop, previous_loss_rprop;
 } myea_opt_desc;
 
 /* Where one layer's parameters sit in the flat [P] buffer: the index map that
@@ -145,7 +153,9 @@ typedef struct myea_b200_net *myea_handle;
 #define MYEA_BUF_MASK_REGULARIZED 5  /* ptr_array_mask_regularized_parameters                           */
 #define MYEA_BUF_NORM_MEAN_AVERAGE 6     /* normalized_batch_units.ptr_mean_average, all units          */
 #define MYEA_BUF_NORM_VARIANCE_AVERAGE 7 /* normalized_batch_units.ptr_variance_average, all units      */
-#define MYEA_BUF_PREVIOUS_DELTA 8 /* ptr_array_previous_delta_parameters (GD momentum)                  */
+#define MYEA_BUF_PREVIOUS_DELTA 8 /* ptr_array_previous_delta_parameters (GD momentum, iRPROP+)         */
+#define MYEA_BUF_PREVIOUS_DERIVATIVES 9 /* ptr_array_previous_derivatives_parameters (iRPROP+); shares the first-moment storage  */
+#define MYEA_BUF_PREVIOUS_STEPS 10      /* ptr_array_previous_steps (iRPROP+; 0 reads as rprop_delta_zero); shares the second-moment storage */
 
 /* Neural_Network::Compile + Set__* + Update__Batch_Size (Neural_Network__Compile.cpp:426-785,
  * Neural_Network__Update.cpp:187-231): builds the index map, carves device buffers for batch_size rows. */

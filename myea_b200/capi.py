@@ -20,9 +20,9 @@ MASK_BERNOULLI, MASK_ZONEOUT_STATE, MASK_ZONEOUT_OUTPUT, MASK_SHAKEDROP, MASK_SH
 DROP_NONE, DROP_BERNOULLI, DROP_BERNOULLI_INVERTED, DROP_SHAKEDROP, DROP_ZONEOUT = 0, 2, 3, 5, 7
 LOSS_CE, LOSS_MSE = 2, 10
 ACC_NONE, ACC_CE, ACC_DISTANCE = 0, 1, 3
-OPT_ADABOUND, OPT_ADAM, OPT_AMSBOUND, OPT_AMSGRAD, OPT_GD, OPT_NOSADAM = 1, 2, 4, 5, 6, 9
+OPT_ADABOUND, OPT_ADAM, OPT_AMSBOUND, OPT_AMSGRAD, OPT_GD, OPT_IRPROP_PLUS, OPT_NOSADAM = 1, 2, 4, 5, 6, 8, 9
 (BUF_PARAMETERS, BUF_DERIVATIVES, BUF_FIRST_MOMENT, BUF_SECOND_MOMENT, BUF_SECOND_MOMENT_HAT, BUF_MASK_REGULARIZED,
- BUF_NORM_MEAN_AVERAGE, BUF_NORM_VARIANCE_AVERAGE, BUF_PREVIOUS_DELTA) = range(9)
+ BUF_NORM_MEAN_AVERAGE, BUF_NORM_VARIANCE_AVERAGE, BUF_PREVIOUS_DELTA, BUF_PREVIOUS_DERIVATIVES, BUF_PREVIOUS_STEPS) = range(11)
 TIMER_CLASSES = 8
 
 
@@ -50,7 +50,9 @@ class OptDesc(C.Structure):
                 ("adam_epsilon", C.c_float), ("learning_rate_final", C.c_float), ("learning_gamma", C.c_float),
                 ("regularization__weight_decay", C.c_float), ("use_normalized_weight_decay", C.c_uint32),
                 ("use_clip_gradient", C.c_uint32), ("clip_gradient", C.c_float), ("epoch_time_step", C.c_float),
-                ("adam_gamma", C.c_float), ("regularization__max_norm_constraints", C.c_float)]
+                ("adam_gamma", C.c_float), ("regularization__max_norm_constraints", C.c_float),
+                ("rprop_increase_factor", C.c_float), ("rprop_decrease_factor", C.c_float), ("rprop_delta_min", C.c_float),
+                ("rprop_delta_max", C.c_float), ("rprop_delta_zero", C.c_float), ("loss_rprop", C.c_float), ("previous_loss_rprop", C.c_float)]
 
 
 class LayerIndex(C.Structure):
@@ -123,7 +125,8 @@ def net(layers, batch, T=1, loss=LOSS_MSE, accuracy=ACC_NONE, time_delays=0, mom
 
 def opt(kind=OPT_ADAM, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, bias_correction=True, final_lr=0.1, gamma=1e-3,
         weight_decay=0.0, normalized_wd=True, clip=None, gd_lr=0.01, momentum=0.0, nesterov=False, epoch=1.0, nosadam_gamma=0.1,
-        max_norm=0.0):
+        max_norm=0.0, rprop=(0.0, 0.0, 0.0, 0.0, 0.0)):
+    """rprop: (increase factor, decrease factor, delta min, delta max, delta zero) of iRPROP+, 0 = class default"""
     o = OptDesc()
     o.type_optimizer_function = kind
     o.use_adam_bias_correction = 1 if bias_correction else 0
@@ -139,6 +142,7 @@ def opt(kind=OPT_ADAM, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, bias_correctio
     o.epoch_time_step = epoch
     o.adam_gamma = nosadam_gamma
     o.regularization__max_norm_constraints = max_norm
+    (o.rprop_increase_factor, o.rprop_decrease_factor, o.rprop_delta_min, o.rprop_delta_max, o.rprop_delta_zero) = rprop
     return o
 
 

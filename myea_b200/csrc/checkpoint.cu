@@ -334,7 +334,7 @@ int format_dimension(const HostPlan &P, const float *params, const float *mean, 
 float or_default(float v, float dflt) { return v > 0.f ? v : dflt; }
 
 // the `.net` text (Save_General_Parameters, Save.cpp:42-149).  Fields of optimizers this library does not run
-// (QuickProp, RPROP, SARPROP, warm restarts) carry the reference constructor's values so that its loader accepts the file.
+// (QuickProp, SARPROP, warm restarts) carry the reference constructor's values so that its loader accepts the file.
 std::string format_general(const myea_net_desc &d, const myea_opt_desc &o) {
   std::string s;
   auto put = [&](const char *key, const std::string &value) { s += key; s += ' '; s += value; s += NL; };
@@ -352,11 +352,11 @@ std::string format_general(const myea_net_desc &d, const myea_opt_desc &o) {
   put("quickprop_mu", real(1.75f));
   close("QUICKPROP PARAMETERS");
   open("RESILLENT PROPAGATION PARAMETERS");
-  put("rprop_increase_factor", real(1.2f));
-  put("rprop_decrease_factor", real(0.5f));
-  put("rprop_delta_min", real(1e-6f));
-  put("rprop_delta_max", real(50.f));
-  put("rprop_delta_zero", real(0.1f));
+  put("rprop_increase_factor", real(or_default(o.rprop_increase_factor, 1.2f)));
+  put("rprop_decrease_factor", real(or_default(o.rprop_decrease_factor, 0.5f)));
+  put("rprop_delta_min", real(or_default(o.rprop_delta_min, 1e-6f)));
+  put("rprop_delta_max", real(or_default(o.rprop_delta_max, 50.f)));
+  put("rprop_delta_zero", real(or_default(o.rprop_delta_zero, 0.1f)));
   close("RESILLENT PROPAGATION PARAMETERS");
   open("SARPROP PARAMETERS");
   put("sarprop_weight_decay_shift", real(-6.644f));
@@ -748,6 +748,11 @@ int parse_general(const char *path, myea_net_desc &d, myea_opt_desc &o, std::str
     else if (k == "learning_momentum") o.learning_momentum = f;
     else if (k == "learning_gamma") o.learning_gamma = f;
     else if (k == "use_Nesterov") o.use_nesterov = u;
+    else if (k == "rprop_increase_factor") o.rprop_increase_factor = f;
+    else if (k == "rprop_decrease_factor") o.rprop_decrease_factor = f;
+    else if (k == "rprop_delta_min") o.rprop_delta_min = f;
+    else if (k == "rprop_delta_max") o.rprop_delta_max = f;
+    else if (k == "rprop_delta_zero") o.rprop_delta_zero = f;
     else if (k == "adam_learning_rate") o.adam_learning_rate = f;
     else if (k == "adam_beta1") o.adam_beta1 = f;
     else if (k == "adam_beta2") o.adam_beta2 = f;

@@ -268,6 +268,8 @@ struct OptLaunch {
   float lr_t = 0, beta1 = 0, beta2 = 0, epsilon = 0, weight_decay = 0, lower = 0, upper = 0;
   float gd_lr = 0, momentum = 0;
   int nesterov = 0;
+  float rprop_increase = 1.2f, rprop_decrease = 0.5f, rprop_min = 1e-6f, rprop_max = 50.f, rprop_zero = 0.1f;  // iRPROP+
+  int rprop_error_is_worse = 0;
   const float *clip_scale = nullptr;  // device float: multiply the gradient by it first (global-norm clip), may be null
 };
 int optimizer_update(Context &ctx, const OptLaunch &o, float *w, float *g, float *m, float *v, float *vhat,

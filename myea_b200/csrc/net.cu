@@ -400,8 +400,8 @@ static float *select_buffer(myea_b200_net *net, int which, size_t *count) {
   switch (which) {
     case MYEA_BUF_PARAMETERS: return net->params;
     case MYEA_BUF_DERIVATIVES: return net->grads;
-    case MYEA_BUF_FIRST_MOMENT: return net->m1;
-    case MYEA_BUF_SECOND_MOMENT: return net->m2;
+    case MYEA_BUF_FIRST_MOMENT: case MYEA_BUF_PREVIOUS_DERIVATIVES: return net->m1;
+    case MYEA_BUF_SECOND_MOMENT: case MYEA_BUF_PREVIOUS_STEPS: return net->m2;
     case MYEA_BUF_SECOND_MOMENT_HAT: return net->m2hat;
     case MYEA_BUF_MASK_REGULARIZED: return net->mask_reg;
     case MYEA_BUF_PREVIOUS_DELTA: return net->prev_delta;
@@ -883,7 +883,16 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
       o.momentum = opt->learning_momentum;
       o.nesterov = opt->use_nesterov != 0;
       break;
-    default: return fail(net, MYEA_E_UNSUPPORTED, "optimizer not built (Adam, AMSGrad, NosAdam, AdaBound, AMSBound, gradient descent / momentum / Nesterov)");
+    case MYEA_OPT_IRPROP_PLUS:
+      o.weight_decay = 0.f;
+      o.rprop_increase = opt->rprop_increase_factor > 0.f ? opt->rprop_increase_factor : 1.2f;
+      o.rprop_decrease = opt->rprop_decrease_factor > 0.f ? opt->rprop_decrease_factor : 0.5f;
+      o.rprop_min = opt->rprop_delta_min > 0.f ? opt->rprop_delta_min : 1e-6f;
+      o.rprop_max = opt->rprop_delta_max > 0.f ? opt->rprop_delta_max : 50.f;
+      o.rprop_zero = opt->rprop_delta_zero > 0.f ? opt->rprop_delta_zero : 0.1f;
+      o.rprop_error_is_worse = opt->loss_rprop > opt->previous_loss_rprop ? 1 : 0;
+      break;
+    default: return fail(net, MYEA_E_UNSUPPORTED, "optimizer not built (Adam, AMSGrad, NosAdam, AdaBound, AMSBound, gradient descent / momentum / Nesterov, iRPROP+)");
   }
   const float max_norm = opt->regularization__max_norm_constraints;
   if (max_norm != 0.f) {

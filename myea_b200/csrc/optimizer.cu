@@ -1,7 +1,8 @@
 // One fused parameter update over the flat parameter buffer, the global-norm clip that precedes it and the
 // derivative reset that follows it: Update_Parameters__Adam (Neural_Network__Adam.cpp:39-95), AMSGrad
 // (Neural_Network__AMSGrad.cpp), AdaBound / AMSBound (Neural_Network__AdaBound.cpp, …AMSBound.cpp), gradient descent,
-// momentum and Nesterov (Neural_Network__Gradient_Descent.cpp, …_Momentum.cpp, Neural_Network__Nesterov_Accelerated_Gradient.cpp),
+// momentum and Nesterov (Neural_Network__Gradient_Descent.cpp, …_Momentum.cpp, Neural_Network__Nesterov_Accelerated_Gradient.cpp), iRPROP+
+// (Neural_Network__iRPROP_plus.cpp),
 // Clip_Gradient / Euclidean_Norm (Neural_Network__Clip_Gradient.cpp:82-94, …Regularization__Max_Norm_Constraints.cpp:48-87).
 // Pure HBM streaming: every array is read and written once with 128-bit accesses; the optimizer is a uniform branch.
 #include "common.cuh"
@@ -41,6 +42,28 @@ __device__ __forceinline__ float opt_one(const OptLaunch &o, float w, float g, f
       vhat = fmaxf(vhat, v);
       const float step = fminf(fmaxf(o.lr_t / (sqrtf(vhat) + o.epsilon), o.lower), o.upper);
       return w - (step * m + decay);
+    }
+    case MYEA_OPT_IRPROP_PLUS: {
+      // Update_Parameter__iRPROP_plus__Loop (Neural_Network__iRPROP_plus.cpp:30-120).  m: previous derivative,
+      // v: previous step (a cleared 0 stands for rprop_delta_zero, Clear_Optimizer, Train.cpp:163-190), prev: previous
+      // delta weight.  No decay term: the reference has none on this path.
+      if (v == 0.f) v = o.rprop_zero;
+      const float same = m * g;
+      const float sign = static_cast<float>(0.f < g) - static_cast<float>(g < 0.f);
+      if (same > 0.f) {
+        v = fminf(v * o.rprop_increase, o.rprop_max);
+        prev = -sign * v;
+        m = g;
+        return w + prev;
+      }
+      if (same < 0.f) {
+        v = fmaxf(v * o.rprop_decrease, o.rprop_min);
+        m = 0.f;
+        return o.rprop_error_is_worse ? w - prev : w;
+      }
+      prev = -sign * v;
+      m = g;
+      return w + prev;
     }
     default: {  // gradient descent family
       if (o.momentum == 0.f) return w - (o.gd_lr * g + decay);
@@ -99,7 +122,7 @@ int optimizer_update(Context &ctx, const OptLaunch &o, float *w, float *g, float
                      const float *mask, size_t n) {
   OptArrays a{w, g, m, v, vhat, prev_delta, mask};
   const bool has_vhat = (o.type == MYEA_OPT_AMSGRAD || o.type == MYEA_OPT_AMSBOUND);
-  const bool has_prev = (o.type == MYEA_OPT_GD && o.momentum != 0.f);
+  const bool has_prev = (o.type == MYEA_OPT_GD && o.momentum != 0.f) || o.type == MYEA_OPT_IRPROP_PLUS;
   if ((has_vhat && vhat == nullptr) || (has_prev && prev_delta == nullptr) || (o.type != MYEA_OPT_GD && (m == nullptr || v == nullptr)))
     return MYEA_E_INVALID;
   const int blocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(((n >> 2) + 255) / 256, 148 * 16)));

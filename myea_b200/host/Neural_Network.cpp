@@ -211,6 +211,9 @@ void Neural_Network::sync_optimizer(void) {
   opt_.use_adam_bias_correction = use_adam_bias_correction ? 1u : 0u;
   opt_.use_normalized_weight_decay = use_normalized_weight_decay ? 1u : 0u;
   opt_.epoch_time_step = epoch_time_step;
+  opt_.rprop_increase_factor = rprop_increase_factor; opt_.rprop_decrease_factor = rprop_decrease_factor;
+  opt_.rprop_delta_min = rprop_delta_min; opt_.rprop_delta_max = rprop_delta_max; opt_.rprop_delta_zero = rprop_delta_zero;
+  opt_.loss_rprop = loss_rprop; opt_.previous_loss_rprop = previous_loss_rprop;
 }
 
 bool Neural_Network::Save_General_Parameters(std::string const &path) {
@@ -247,6 +250,11 @@ bool Neural_Network::Load(std::string const &path_dimension, std::string const &
   learning_rate_final = opt_.learning_rate_final; learning_gamma = opt_.learning_gamma;
   use_adam_bias_correction = opt_.use_adam_bias_correction != 0;
   use_normalized_weight_decay = opt_.use_normalized_weight_decay != 0;
+  if (opt_.rprop_increase_factor > 0.f) rprop_increase_factor = opt_.rprop_increase_factor;
+  if (opt_.rprop_decrease_factor > 0.f) rprop_decrease_factor = opt_.rprop_decrease_factor;
+  if (opt_.rprop_delta_min > 0.f) rprop_delta_min = opt_.rprop_delta_min;
+  if (opt_.rprop_delta_max > 0.f) rprop_delta_max = opt_.rprop_delta_max;
+  if (opt_.rprop_delta_zero > 0.f) rprop_delta_zero = opt_.rprop_delta_zero;
   if (!adopt_device()) return false;
   is_device_initialized = true;
   return Copy__Parameters__Device_To_Host() && (total_normalized_units == 0 || Copy__Batch_Normalization_Neurons__Device_To_Host());

@@ -107,6 +107,8 @@ class Neural_Network {
   float learning_rate = 0.01f, learning_momentum = 0.9f, learning_rate_final = 0.1f, learning_gamma = 1e-3f;
   float adam_learning_rate = 0.001f, adam_beta1 = 0.9f, adam_beta2 = 0.999f, adam_epsilon = 1e-8f, epoch_time_step = 1.f;
   bool use_Nesterov = false, use_normalized_weight_decay = true, use_adam_bias_correction = true;
+  float rprop_increase_factor = 1.2f, rprop_decrease_factor = 0.5f, rprop_delta_min = 1e-6f, rprop_delta_max = 50.f, rprop_delta_zero = 0.1f;
+  float loss_rprop = 3.402823466e+38f, previous_loss_rprop = 3.402823466e+38f;  // iRPROP+ (Data.hpp, Dataset.cpp:575-579)
   float *ptr_array_parameters = nullptr;                     // [total_parameters]
   float *ptr_array_derivatives_parameters = nullptr;         // [total_parameters], merged
   float *ptr_array_previous_biased_first_moment = nullptr, *ptr_array_previous_biased_second_moment = nullptr,

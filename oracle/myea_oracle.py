@@ -179,12 +179,14 @@ class OracleNet:
             setattr(li, k, v)
         return li
 
+    _ALIAS = {capi.BUF_PREVIOUS_DERIVATIVES: capi.BUF_FIRST_MOMENT, capi.BUF_PREVIOUS_STEPS: capi.BUF_SECOND_MOMENT}
+
     def get(self, which):
-        return self.buf[which].astype(np.float32).copy()
+        return self.buf[self._ALIAS.get(which, which)].astype(np.float32).copy()
 
     def set(self, which, arr):
         a = np.asarray(arr).ravel()
-        self.buf[which][:a.size] = a.astype(self.dt)
+        self.buf[self._ALIAS.get(which, which)][:a.size] = a.astype(self.dt)
 
     def set_mask_bernoulli(self, l, mask):
         self.masks[l] = np.asarray(mask).reshape(self.T, -1).astype(bool)
@@ -449,6 +451,25 @@ class OracleNet:
                 lo = dt(o.learning_rate_final) * (dt(1) - dt(1) / (dt(o.learning_gamma) * t + dt(1)))
                 hi = dt(o.learning_rate_final) * (dt(1) + dt(1) / (dt(o.learning_gamma) * t))
                 w -= np.clip(lr_t / (np.sqrt(vv) + eps), lo, hi) * m + decay
+        elif kind == capi.OPT_IRPROP_PLUS:
+            # Update_Parameter__iRPROP_plus__Loop (Neural_Network__iRPROP_plus.cpp:30-120); the first-moment buffer holds
+            # the previous derivatives, the second-moment buffer the previous steps (0 = rprop_delta_zero, what
+            # Clear_Optimizer, Train.cpp:163-190, writes there); no decay term on this path
+            d = lambda v, dflt: dt(v) if v > 0 else dt(dflt)
+            inc, dec = d(o.rprop_increase_factor, 1.2), d(o.rprop_decrease_factor, 0.5)
+            dmin, dmax, dzero = d(o.rprop_delta_min, 1e-6), d(o.rprop_delta_max, 50.0), d(o.rprop_delta_zero, 0.1)
+            pd, step, prev = self.buf[capi.BUF_FIRST_MOMENT], self.buf[capi.BUF_SECOND_MOMENT], self.buf[capi.BUF_PREVIOUS_DELTA]
+            step[step == 0] = dzero
+            same = pd * g
+            up, down = same > 0, same < 0
+            sign = (g > 0).astype(dt) - (g < 0).astype(dt)
+            step[up] = np.minimum(step[up] * inc, dmax)
+            step[down] = np.maximum(step[down] * dec, dmin)
+            if o.loss_rprop > o.previous_loss_rprop:
+                w[down] -= prev[down]
+            prev[~down] = -sign[~down] * step[~down]
+            w[~down] += prev[~down]
+            pd[:] = np.where(down, dt(0), g)
         else:
             lr, mom = dt(o.learning_rate), dt(o.learning_momentum)
             if mom == 0:

@@ -46,6 +46,15 @@ void apply_opt(Neural_Network &nn, const myea_opt_desc &o) {
   nn.epoch_time_step = o.epoch_time_step;
   if (o.adam_gamma > 0.f) nn.adam_gamma = o.adam_gamma;
   nn.Set__Regularization__Max_Norm_Constraints(o.regularization__max_norm_constraints);
+  if (o.rprop_increase_factor > 0.f) nn.rprop_increase_factor = o.rprop_increase_factor;
+  if (o.rprop_decrease_factor > 0.f) nn.rprop_decrease_factor = o.rprop_decrease_factor;
+  if (o.rprop_delta_min > 0.f) nn.rprop_delta_min = o.rprop_delta_min;
+  if (o.rprop_delta_max > 0.f) nn.rprop_delta_max = o.rprop_delta_max;
+  if (o.rprop_delta_zero > 0.f) nn.rprop_delta_zero = o.rprop_delta_zero;
+  if (o.type_optimizer_function == MYEA_OPT_IRPROP_PLUS) {
+    nn.loss_rprop = o.loss_rprop;
+    nn.previous_loss_rprop = o.previous_loss_rprop;
+  }
 }
 
 // [T][B][W] packed block -> one contiguous [T*W] row per sample (Neural_Network__Assign_Inputs.cpp:273-304).
@@ -194,6 +203,8 @@ float *ref_buffer(void *h, int which) {
     case MYEA_BUF_NORM_MEAN_AVERAGE: return nn.ptr_array_normalized_batch_units_means_averages;
     case MYEA_BUF_NORM_VARIANCE_AVERAGE: return nn.ptr_array_normalized_batch_units_variances_averages;
     case MYEA_BUF_PREVIOUS_DELTA: return nn.ptr_array_previous_delta_parameters;
+    case MYEA_BUF_PREVIOUS_DERIVATIVES: return nn.ptr_array_previous_derivatives_parameters;
+    case MYEA_BUF_PREVIOUS_STEPS: return nn.ptr_array_previous_steps;
     default: return nullptr;
   }
 }

@@ -29,6 +29,9 @@ CASES = {
     "mlp_tanh_nosadam": lambda: _mlp_variant("nosadam", [20, 12], capi.AF_TANH, capi.opt(capi.OPT_NOSADAM, nosadam_gamma=0.1)),
     # descent with a large rate so that rows do cross the bound and get rescaled
     "mlp_relu_momentum_max_norm": lambda: _mlp_variant("maxnorm", [16, 16], capi.AF_RELU, capi.opt(capi.OPT_GD, gd_lr=0.05, momentum=0.9, max_norm=0.8)),
+    # sign-based steps of 0.1 from the first update on: a derivative's sign, not its size, decides, so the case keeps to
+    # tanh units (no exactly-zero derivatives that a rounding difference could push to either side)
+    "mlp_tanh_irprop_plus": lambda: _mlp_variant("irprop", [20, 12], capi.AF_TANH, capi.opt(capi.OPT_IRPROP_PLUS)),
     "mlp_relu_gd": lambda: _mlp_variant("gd", [16, 16], capi.AF_RELU, capi.opt(capi.OPT_GD, gd_lr=0.01)),
     "mlp_selu_momentum": lambda: _mlp_variant("mom", [16], capi.AF_SELU, capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9)),
     "mlp_tanh_nesterov_ce": lambda: _mlp_variant("nag", [16], capi.AF_TANH, capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9, nesterov=True),
@@ -63,7 +66,13 @@ def run_steps(net, wl, steps=STEPS, shake=None):
             out["output_last"] = net.outputs(len(wl.layers) - 1)
         net.update_parameter()
         out["param%d" % it] = net.get(capi.BUF_PARAMETERS)
-    out["m"] = net.get(capi.BUF_FIRST_MOMENT) if wl.opt.type_optimizer_function != capi.OPT_GD else out["param0"] * 0
+    kind = wl.opt.type_optimizer_function
+    if kind == capi.OPT_IRPROP_PLUS:     # previous derivatives (they share the first-moment slot); steps and delta weights ride along
+        out["m"] = net.get(capi.BUF_PREVIOUS_DERIVATIVES)
+        out["rprop_steps"] = net.get(capi.BUF_PREVIOUS_STEPS)
+        out["rprop_delta"] = net.get(capi.BUF_PREVIOUS_DELTA)
+    else:
+        out["m"] = net.get(capi.BUF_FIRST_MOMENT) if kind != capi.OPT_GD else out["param0"] * 0
     if net.sizes()[3]:
         out["norm_mean_avg"] = net.get(capi.BUF_NORM_MEAN_AVERAGE)
         out["norm_sigma_avg"] = net.get(capi.BUF_NORM_VARIANCE_AVERAGE)

@@ -32,7 +32,7 @@ def test_struct_layouts_match_header():
     # sizes implied by the header's field lists on an LP64 ABI
     assert C.sizeof(capi.LayerDesc) == 4 + 4 + 5 * 8 + 4 * 4 + 3 * 4 + 4
     assert C.sizeof(capi.NetDesc) == 4 + 4 + 8 * 3 + 4 * 2 + 4 * 5 + 4 + capi.MAX_LAYERS * C.sizeof(capi.LayerDesc)
-    assert C.sizeof(capi.OptDesc) == 18 * 4
+    assert C.sizeof(capi.OptDesc) == 25 * 4
     assert C.sizeof(capi.LayerIndex) == 10 * 8
 
 
@@ -41,7 +41,7 @@ def test_enumerators_match_header():
     for macro, value in (("MYEA_LAYER_FULLY_CONNECTED", capi.LAYER_FC), ("MYEA_LAYER_LSTM", capi.LAYER_LSTM),
                          ("MYEA_LAYER_RESIDUAL", capi.LAYER_RESIDUAL), ("MYEA_AF_TANH", capi.AF_TANH), ("MYEA_AF_RELU", capi.AF_RELU),
                          ("MYEA_AF_SOFTMAX", capi.AF_SOFTMAX), ("MYEA_OPT_ADAM", capi.OPT_ADAM), ("MYEA_OPT_AMSGRAD", capi.OPT_AMSGRAD),
-                         ("MYEA_OPT_ADABOUND", capi.OPT_ADABOUND), ("MYEA_OPT_NOSADAM", capi.OPT_NOSADAM), ("MYEA_LOSS_MSE", capi.LOSS_MSE), ("MYEA_DROPOUT_ZONEOUT", capi.DROP_ZONEOUT)):
+                         ("MYEA_OPT_ADABOUND", capi.OPT_ADABOUND), ("MYEA_OPT_NOSADAM", capi.OPT_NOSADAM), ("MYEA_OPT_IRPROP_PLUS", capi.OPT_IRPROP_PLUS), ("MYEA_LOSS_MSE", capi.LOSS_MSE), ("MYEA_DROPOUT_ZONEOUT", capi.DROP_ZONEOUT)):
         m = re.search(r"#define\s+%s\s+(\d+)u?" % macro, h)
         assert m and int(m.group(1)) == value, macro
 

@@ -29,6 +29,9 @@ def test_oracle_matches_golden(name, golden_dir):
     assert np.array_equal(np.asarray(out["index_map"], np.int64), gold["index_map"])
     for k in ("grad0", "grad1", "param0", "param1", "output_last", "m"):
         assert rel_err(out[k], gold[k]) < TOL, k
+    for k in ("rprop_steps", "rprop_delta"):                              # iRPROP+: exact multiples of the initial step
+        if k in out:
+            assert np.array_equal(np.asarray(out[k], np.float32), gold[k]), k
     for k in ("loss0", "loss1"):
         assert abs(out[k][0] - gold[k][0]) <= 1e-4 * abs(gold[k][0]) + 1e-6
         assert out[k][1] == gold[k][1]                                    # number of loss terms: exact

@@ -41,6 +41,9 @@ def _compare(out, want, tol=TOL):
     assert np.array_equal(np.asarray(out["index_map"], np.int64), np.asarray(want["index_map"], np.int64))
     for k in ("grad0", "grad1", "param0", "param1", "output_last", "m"):
         assert rel_err(out[k], want[k]) < tol, (k, rel_err(out[k], want[k]))
+    for k in ("rprop_steps", "rprop_delta"):        # iRPROP+: step sizes and last weight changes are exact multiples, not approximations
+        if k in out:
+            assert np.array_equal(np.asarray(out[k], np.float32), np.asarray(want[k], np.float32)), k
     for k in ("loss0", "loss1"):
         assert abs(out[k][0] - want[k][0]) <= 1e-4 * abs(want[k][0]) + 1e-6
         assert out[k][1] == want[k][1]
