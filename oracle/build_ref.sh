@@ -4,7 +4,7 @@
 # Common_Library helpers they need) from where they lie in the read-only reference checkout into
 # oracle/_ref/libmyea_ref.so, together with oracle/ref_harness.cpp (a C-ABI driver) and oracle/ref_stubs.cpp.
 # No reference source is copied into the repository: BOM-stripped copies live only in oracle/_ref/build.
-#   usage: oracle/build_ref.sh [reference checkout]     (default /root/reference)
+#   usage: oracle/build_ref.sh [reference checkout]     (without the argument: the default of REF below)
 # Nothing is built (exit 0) when the checkout is absent; a prebuilt oracle/_ref/libmyea_ref.so is used as is.
 set -e
 HERE=$(cd "$(dirname "$0")" && pwd)
