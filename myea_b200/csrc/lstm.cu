@@ -399,6 +399,13 @@ static int prepare_gates(Context &ctx, const float *gates, long long rows, long 
   return MYEA_OK;
 }
 
+// the 8-cell kernels: 128-thread blocks while 256-thread ones would leave SMs without a block (a 256 x 1024 step has
+// 32768 threads: 128 blocks of 256 for 148 SMs), 256-thread blocks otherwise
+static int cell_threads8(long long total) { return (total + 255) / 256 < 148 ? 128 : 256; }
+static int cell_blocks8(long long total) {
+  const long long t = cell_threads8(total);
+  return static_cast<int>(std::max<long long>(1, std::min<long long>((total + t - 1) / t, 148 * 8)));
+}
 static int cell_blocks(long long total) { return static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, 148 * 8))); }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -475,7 +482,7 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
           e.ldc = 4 * C;
           LRC(gemm_panels(ctx, ph_prev, 0, B, pwrec, 0, 4 * C, e));
           ctx.begin(TC_RECURRENT);
-          launch_dependent(ctx, lstm_cells8_forward_kernel, dim3(cell_blocks(B * C / 8)), dim3(256), 0, f, static_cast<const float *>(P->s_rec), B);
+          launch_dependent(ctx, lstm_cells8_forward_kernel, dim3(cell_blocks8(B * C / 8)), dim3(cell_threads8(B * C / 8)), 0, f, static_cast<const float *>(P->s_rec), B);
           ctx.end(TC_RECURRENT);
         }
         continue;
@@ -567,7 +574,7 @@ int lstm_backward(myea_b200_net *net, LayerPlan &L) {
           e.accumulate = 1;
           LRC(gemm_panels(ctx, pd_prev, 0, B, pwt, 0, C, e));
           ctx.begin(TC_RECURRENT);
-          launch_dependent(ctx, lstm_cells8_backward_kernel, dim3(cell_blocks(B * C / 8)), dim3(256), 0, f, B);
+          launch_dependent(ctx, lstm_cells8_backward_kernel, dim3(cell_blocks8(B * C / 8)), dim3(cell_threads8(B * C / 8)), 0, f, B);
           ctx.end(TC_RECURRENT);
         }
         continue;
