@@ -156,6 +156,11 @@ struct Epilogue {
   const float *col_scale = nullptr;  // pre = aux_pre * col_scale[n] + col_shift[n] when non-null (normalization folded in)
   const float *col_shift = nullptr;
   LstmFuse lstm;                     // kind != 0: the accumulator feeds an LSTM cell instead of being stored (tensor-core kernels only)
+  // seg_rows != 0: the output rows come in up to 4 segments of seg_rows rows; row m of the product is row
+  // (m mod seg_rows) of the array that starts at C + seg_off[m / seg_rows] (the four gate matrices of an LSTM layer
+  // inside the reference's per-block parameter layout: one contraction instead of four)
+  long long seg_rows = 0;
+  long long seg_off[4] = {0, 0, 0, 0};
 };
 
 // A fp32 matrix operand given by strides: element (r, k) at ptr[r * stride_r + k * stride_k]; one of the two

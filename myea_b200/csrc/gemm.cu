@@ -300,6 +300,13 @@ struct GemmDims {
 };
 
 // epilogue math for one element
+// offset of output row m from e.C: plain pitch, or one of up to four row segments that start at their own offsets
+__device__ __forceinline__ long long c_row(const Epilogue &e, long long m) {
+  if (e.seg_rows == 0) return m * e.ldc;
+  const int s = static_cast<int>(m >= e.seg_rows) + static_cast<int>(m >= 2 * e.seg_rows) + static_cast<int>(m >= 3 * e.seg_rows);
+  return (m - s * e.seg_rows) * e.ldc + e.seg_off[s];
+}
+
 __device__ __forceinline__ float epilogue_value(const Epilogue &e, float acc, long long m, long long n) {
   float v = acc;
   if (e.bias != nullptr) v += e.bias[n];
@@ -313,7 +320,7 @@ __device__ __forceinline__ float epilogue_value(const Epilogue &e, float acc, lo
     if (e.aux_y != nullptr) y = e.aux_y[m * e.ld_aux + n];
     v *= af_derive(e.deriv_af, pre, y);
   }
-  if (e.accumulate) v += e.C[m * e.ldc + n];
+  if (e.accumulate) v += e.C[c_row(e, m) + n];
   return v;
 }
 
@@ -325,7 +332,7 @@ __device__ __forceinline__ bool epilogue_vector_ok(const Epilogue &e) {
   const uintptr_t bits = reinterpret_cast<uintptr_t>(e.C) | reinterpret_cast<uintptr_t>(e.bias) | reinterpret_cast<uintptr_t>(e.addend) |
                          reinterpret_cast<uintptr_t>(e.aux_pre) | reinterpret_cast<uintptr_t>(e.aux_y) |
                          reinterpret_cast<uintptr_t>(e.col_scale) | reinterpret_cast<uintptr_t>(e.col_shift);
-  return (bits & 15) == 0 && ((e.ldc | e.ld_addend | e.ld_aux) & 3) == 0;
+  return (bits & 15) == 0 && ((e.ldc | e.ld_addend | e.ld_aux | e.seg_off[0] | e.seg_off[1] | e.seg_off[2] | e.seg_off[3]) & 3) == 0;
 }
 // 0 plain (bias only), 1 activation derivative, 2 accumulate, 3 anything else
 __device__ __forceinline__ int epilogue_mode(const Epilogue &e) {
@@ -396,7 +403,7 @@ __device__ __forceinline__ void epilogue_block32(const Epilogue &e, float *tr, c
           pre[s] = (has_pre && in) ? ld4(e.aux_pre + m * e.ld_aux + n) : zero;
           y[s] = (has_y && in) ? ld4(e.aux_y + m * e.ld_aux + n) : zero;
         }
-        if (ACC) old[s] = (acc && in) ? ld4(e.C + m * e.ldc + n) : zero;
+        if (ACC) old[s] = (acc && in) ? ld4(e.C + c_row(e, m) + n) : zero;
       }
     }
   };
@@ -429,7 +436,7 @@ __device__ __forceinline__ void epilogue_block32(const Epilogue &e, float *tr, c
     for (int i = 0; i < 4; ++i) {
       const long long m = row0 + h * 16 + rsub + 4 * i;
       if (ACC) { x[i].x += old[s0 + i].x; x[i].y += old[s0 + i].y; x[i].z += old[s0 + i].z; x[i].w += old[s0 + i].w; }
-      if (m < M) *reinterpret_cast<float4 *>(e.C + m * e.ldc + n) = x[i];
+      if (m < M) *reinterpret_cast<float4 *>(e.C + c_row(e, m) + n) = x[i];
     }
   }
 }
@@ -467,7 +474,7 @@ __device__ __forceinline__ void epilogue_row32(const Epilogue &e, const float (&
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const long long n = col0 + j;
-      if (n < N) e.C[m * e.ldc + n] = epilogue_value(e, v[j], m, n);
+      if (n < N) e.C[c_row(e, m) + n] = epilogue_value(e, v[j], m, n);
     }
   }
 }
@@ -1320,7 +1327,7 @@ __global__ void __launch_bounds__(256) gemm_fp32_fma_kernel(const Operand A, con
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const long long m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
-      if (m < dims.M && n < dims.N) epi.C[m * epi.ldc + n] = epilogue_value(epi, acc[i][j], m, n);
+      if (m < dims.M && n < dims.N) epi.C[c_row(epi, m) + n] = epilogue_value(epi, acc[i][j], m, n);
     }
 }
 

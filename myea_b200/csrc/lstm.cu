@@ -664,12 +664,14 @@ int lstm_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float 
       LRC(gemm_prepare_shared(ctx, D.dgates, 4 * C, rows, 4 * C, mem_d, PANEL_ROLE_A, nullptr, PANEL_ROLE_A, &pd));
       LRC(gemm_prepare_shared(ctx, input, n_in, rows, n_in, mem_x, PANEL_ROLE_B, nullptr, PANEL_ROLE_B, &px));
       const long long in_off[4] = {off.z_in, off.in[0], off.in[1], off.in[2]};
-      for (int g = 0; g < 4; ++g) {
+      {  // the four gates in one contraction: row g*C + c of the product lands in block c at gate g's offset
         Epilogue e;
-        e.C = gw + in_off[g];
+        e.C = gw;
         e.ldc = P->stride;
         e.accumulate = 1;
-        LRC(gemm_panels(ctx, pd, g * C, C, px, 0, n_in, e));
+        e.seg_rows = C;
+        for (int g = 0; g < 4; ++g) e.seg_off[g] = in_off[g];
+        LRC(gemm_panels(ctx, pd, 0, 4 * C, px, 0, n_in, e));
       }
       if (T > 1) {
         LRC(gemm_prepare_shared(ctx, L.values, ldh, rows, ldh, mem_h, PANEL_ROLE_B, nullptr, PANEL_ROLE_B, &ph));
@@ -685,13 +687,13 @@ int lstm_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float 
         phk.lo = reinterpret_cast<float *>(reinterpret_cast<uint16_t *>(ph.lo) + 2 * kh * ph.kp);
         phk.k = K;
         const long long rec_off[4] = {off.z_rec, off.rec[0], off.rec[1], off.rec[2]};
-        for (int g = 0; g < 4; ++g) {
-          Epilogue e;
-          e.C = gw + rec_off[g];
-          e.ldc = P->stride;
-          e.accumulate = 1;
-          LRC(gemm_panels(ctx, pdk, g * C, C, phk, d * C, C, e));
-        }
+        Epilogue e;
+        e.C = gw;
+        e.ldc = P->stride;
+        e.accumulate = 1;
+        e.seg_rows = C;
+        for (int g = 0; g < 4; ++g) e.seg_off[g] = rec_off[g];
+        LRC(gemm_panels(ctx, pdk, 0, 4 * C, phk, d * C, C, e));
       }
     } else {
     // input weights: K = all T*B rows
