@@ -318,7 +318,9 @@ int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N, uint64_t K
  * cudaMalloc / cudaFree.  Limit: 2*(M+N)*round_up(K,32)+64 floats <= 8 Mi floats, else MYEA_E_INVALID with a message in
  * error_message (optional, error_capacity bytes).  Every GPU that loads the library holds the array until exit.  All
  * calls share it: calls that overlap on the GPU race and must be serialised by the caller.  The first call on a
- * device looks up the array's device address; make it outside any stream capture.  Returns after the stream is idle. */
+ * device looks up the array's device address.  The call is synchronous (it returns after the stream is idle and has
+ * read a status word back), so never make it on a stream that is being captured.  It makes `device` current for its
+ * own work and restores the caller's current device before returning. */
 #define MYEA_STATIC_SCRATCH_BYTES (32u << 20)
 int myea_b200_gemm_nt_static(int device, uint64_t M, uint64_t N, uint64_t K, const float *device_A, const float *device_B,
                              float *device_C, int accumulate, void *stream, char *error_message, size_t error_capacity);

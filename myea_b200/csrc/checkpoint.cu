@@ -886,5 +886,10 @@ extern "C" int myea_b200_load(myea_handle *out, const char *path_dimension, cons
     rc = myea_b200_upload(*out, MYEA_BUF_NORM_MEAN_AVERAGE, mean.data(), 0, U);
     if (rc == MYEA_OK) rc = myea_b200_upload(*out, MYEA_BUF_NORM_VARIANCE_AVERAGE, sigma.data(), 0, U);
   }
+  if (rc != MYEA_OK) {  // a half-loaded network is of no use to the caller: keep the reason, give the handle back
+    g_parse_error = std::string("load: copying the parsed state to the device failed: ") + myea_b200_last_error(*out);
+    myea_b200_destroy(*out);
+    *out = nullptr;
+  }
   return rc;
 }

@@ -26,30 +26,35 @@ struct NcclApi {
   ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*ReduceScatter)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 
+// Loaded once; the function-local static's initialiser runs on one thread and every caller sees the finished table
+// (two host threads, one per GPU, may make their first communicator calls at the same time).
 static NcclApi *nccl_api() {
-  static NcclApi api;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  static const NcclApi api = [] {
+    NcclApi a;
     const char *names[] = {"libnccl.so.2", "libnccl.so"};
     for (const char *n : names) {
-      api.lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
-      if (api.lib != nullptr) break;
+      a.lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+      if (a.lib != nullptr) break;
     }
-    if (api.lib != nullptr) {
-      api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.lib, "ncclGetUniqueId"));
-      api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.lib, "ncclCommInitRank"));
-      api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.lib, "ncclAllReduce"));
-      api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.lib, "ncclCommDestroy"));
-      api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.lib, "ncclGetErrorString"));
-      if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy) api.lib = nullptr;
+    if (a.lib != nullptr) {
+      a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(a.lib, "ncclGetUniqueId"));
+      a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(a.lib, "ncclCommInitRank"));
+      a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(a.lib, "ncclAllReduce"));
+      a.ReduceScatter = reinterpret_cast<decltype(a.ReduceScatter)>(dlsym(a.lib, "ncclReduceScatter"));
+      a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(a.lib, "ncclAllGather"));
+      a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(a.lib, "ncclCommDestroy"));
+      a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(a.lib, "ncclGetErrorString"));
+      if (!a.GetUniqueId || !a.CommInitRank || !a.AllReduce || !a.ReduceScatter || !a.AllGather || !a.CommDestroy) a.lib = nullptr;
     }
-  }
-  return api.lib != nullptr ? &api : nullptr;
+    return a;
+  }();
+  return api.lib != nullptr ? const_cast<NcclApi *>(&api) : nullptr;
 }
 
 struct CommState {
@@ -214,6 +219,11 @@ extern "C" int myea_b200_comm_init(myea_handle net, int world, int rank, const u
       cudaEventCreateWithFlags(&c->ready, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->side_done, cudaEventDisableTiming) != cudaSuccess) {
+    api->CommDestroy(c->comm);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    if (c->ready) cudaEventDestroy(c->ready);
+    if (c->done) cudaEventDestroy(c->done);
+    if (c->side_done) cudaEventDestroy(c->side_done);
     delete c;
     net->ctx.error = "stream / event creation failed";
     return MYEA_E_CUDA;

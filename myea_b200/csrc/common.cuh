@@ -33,7 +33,7 @@ struct Context {
   std::string error;
   int gemm_engine = 0;  // 0 = tcgen05 3xTF32, 1 = FP32 FMA
   int gemm_bn = 0;      // forced N tile of the tcgen05 kernel (0 = heuristic)
-  bool dependent_launch = true;  // programmatic dependent launch for the kernels that support it (MYEA_B200_PDL=0 turns it off)
+  bool dependent_launch = true;  // programmatic dependent launch for the kernels that support it
   float *sk_ws = nullptr;               // partial sums of tiles split along K (gemm_splitk_reserve)
   unsigned int *sk_counters = nullptr;  // arrival counters of those tiles, all zero between launches
   int sk_clusters = 0;                  // clusters the workspace has slots for

@@ -108,6 +108,12 @@ extern "C" int myea_b200_train_epoch(myea_handle net, const uint64_t *order, uin
     net->ctx.error = "train_epoch: a recurrent (or multi-GPU) network needs a mini-batch that is a multiple of its batch size and divides the number of examples";
     return MYEA_E_UNSUPPORTED;
   }
+  // With a communicator the derivative buckets are summed over the ranks inside update_derivative_weight, so a
+  // mini-batch is exactly one batch: a second sub-batch would add to sums that have already travelled.
+  if (net->comm != nullptr && mini_batch_size != B) {
+    net->ctx.error = "train_epoch: with a communicator attached the mini-batch must equal the network's batch size";
+    return MYEA_E_UNSUPPORTED;
+  }
   if (cudaSetDevice(net->ctx.device) != cudaSuccess) return MYEA_E_CUDA;
   int rc = set_order(net, order, number_examples);
   if (rc != MYEA_OK) return rc;

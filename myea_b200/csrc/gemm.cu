@@ -31,8 +31,9 @@
 
 #include <cudaTypedefs.h>
 #include <cuda_bf16.h>
-#include <stdio.h>
-#include <stdlib.h>
+
+#include <algorithm>
+#include <mutex>
 
 namespace myea {
 
@@ -222,28 +223,6 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parit
 }
 
 }  // namespace ptx
-
-// Optional phase timeline of CTA (0,0) (a profiling build only: -DMYEA_GEMM_TIMELINE); compiles to nothing otherwise.
-#ifdef MYEA_GEMM_TIMELINE
-__device__ long long g_timeline[32];
-__device__ long long g_cluster_times[2][128];  // globaltimer at entry / exit of every cluster's leader thread
-#define TL_CLUSTER(which, id) do { unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt)); g_cluster_times[which][(id) & 127] = (long long)gt; } while (0)
-#define TL_ON (blockIdx.x == 0 && blockIdx.y == 0)
-#define TL(slot) do { if (TL_ON) g_timeline[slot] = clock64(); } while (0)
-#define TL_DECL(name) long long name = 0
-#define TL_BEGIN(name) const long long name##_t0 = clock64()
-#define TL_END(name) name += clock64() - name##_t0
-#define TL_STORE(slot, name) do { if (TL_ON) g_timeline[slot] = name; } while (0)
-#define TL_GLOBAL(slot) do { if (TL_ON) { unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt)); g_timeline[slot] = (long long)gt; } } while (0)
-#else
-#define TL(slot)
-#define TL_CLUSTER(which, id)
-#define TL_DECL(name)
-#define TL_BEGIN(name)
-#define TL_END(name)
-#define TL_STORE(slot, name)
-#define TL_GLOBAL(slot)
-#endif
 
 // ---------------------------------------------------------------------------------------------------------
 // Descriptors
@@ -515,7 +494,6 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
   const int m0 = blockIdx.y * BM;
   const int n0 = blockIdx.x * BN;
   const int num_kb = (dims.K + BK - 1) / BK;
-  if (threadIdx.x == 0) { TL(0); TL_GLOBAL(16); }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -534,7 +512,6 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  if (threadIdx.x == 0) TL(1);
   grid_dependency_wait();     // everything above touched no global memory
   grid_dependency_release();
 
@@ -542,13 +519,10 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      TL_DECL(w_empty);
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = static_cast<uint32_t>(kb / STAGES) & 1u;
-        TL_BEGIN(w_empty);
         if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u)) { ok = false; break; }
-        TL_END(w_empty);
         uint8_t *st = smem + s * S::STAGE_BYTES;
         ptx::mbar_arrive_expect_tx(&full_bar[s], S::STAGE_BYTES);
         ptx::tma_load_2d(st, &tm_a_hi, &full_bar[s], kb * BK, m0);
@@ -556,21 +530,16 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
         ptx::tma_load_2d(st + 2 * S::A_BYTES, &tm_b_hi, &full_bar[s], kb * BK, n0);
         ptx::tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tm_b_lo, &full_bar[s], kb * BK, n0);
       }
-      TL_STORE(5, w_empty);
       if (!ok) atomicCAS(error_flag, 0, 101);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_tf32(BM, BN);
-      TL_DECL(w_full);
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = static_cast<uint32_t>(kb / STAGES) & 1u;
-        TL_BEGIN(w_full);
         if (!ptx::mbar_wait(&full_bar[s], ph)) { ok = false; break; }
-        TL_END(w_full);
-        if (kb == 0) TL(2);
         ptx::tc_fence_after();
         const uint32_t st = ptx::smem_u32(smem + s * S::STAGE_BYTES);
         const uint64_t a_hi = make_smem_desc(st);
@@ -590,8 +559,6 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
         ptx::tc_commit(&empty_bar[s]);  // the stage may be refilled once these MMAs have read it
       }
       ptx::tc_commit(tmem_full_bar);  // accumulator complete
-      TL(3);
-      TL_STORE(4, w_full);
       if (!ok) atomicCAS(error_flag, 0, 102);
     }
   } else {
@@ -602,22 +569,17 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
       if (lane == 0) atomicCAS(error_flag, 0, 103);
     }
     ptx::tc_fence_after();
-    if (warp == 2 && lane == 0) TL(6);
     if (ok && num_kb > 0) {
       const long long row_base = static_cast<long long>(m0) + q * 32;
       const bool vec_ok = epilogue_vector_ok(epi);
       const int mode = epilogue_mode(epi);
       // every MMA has completed, so the pipeline stages are free: the first bytes serve as the staging buffers
       float *tr = reinterpret_cast<float *>(smem) + (warp - 2) * TR_WARP_FLOATS;
-      TL_DECL(t_ld);
-      TL_DECL(t_tr);
-      TL_DECL(t_out);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= dims.N) break;
         uint32_t r[32];
         float sum[32];
-        TL_BEGIN(t_ld);
         const uint32_t t_chunk = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c);
         ptx::tmem_ld_32x32(t_chunk + static_cast<uint32_t>(N_MAIN * BN), r);  // cross terms first
         ptx::tmem_ld_wait();
@@ -630,16 +592,9 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
 #pragma unroll
           for (int j = 0; j < 32; ++j) sum[j] += __uint_as_float(r[j]);
         }
-        TL_END(t_ld);
-        TL_BEGIN(t_tr);
-        TL_END(t_tr);
-        TL_BEGIN(t_out);
         epilogue_row32(epi, sum, row_base, lane, static_cast<long long>(n0) + c, dims.M, dims.N, vec_ok, mode, tr);
-        TL_END(t_out);
       }
-      if (warp == 2 && lane == 0) { TL_STORE(11, t_ld); TL_STORE(12, t_tr); TL_STORE(13, t_out); }
     }
-    if (warp == 2 && lane == 0) TL(7);
   }
 
   // drain: the producer makes sure none of its copies is still in flight before the CTA's shared memory goes away
@@ -653,7 +608,6 @@ gemm3x_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __
   }
   ptx::tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) { TL(8); TL_GLOBAL(17); }
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
@@ -930,8 +884,6 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
   const int num_clusters = gridDim.x >> 1;
   const int num_kb = (dims.K + BK - 1) / BK;
   const int num_chunks = (num_kb + WIDE_KC - 1) / WIDE_KC;
-  if (threadIdx.x == 0) { TL(0); TL_GLOBAL(16); }
-  if (threadIdx.x == 0 && cta_rank == 0) TL_CLUSTER(0, cluster_id);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -955,7 +907,6 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
   ptx::cluster_sync_all();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  if (threadIdx.x == 0) TL(1);
   grid_dependency_wait();     // everything above touched no global memory
   grid_dependency_release();
 
@@ -965,7 +916,6 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
     if (lane == 0) {
       bool ok = true;
       uint32_t it = 0;  // k-blocks staged so far, over all segments
-      TL_DECL(w_empty);
       WideSegments seg(work, cluster_id, num_clusters, num_chunks);
       while (ok && seg.next()) {
         int tm, tn;
@@ -976,16 +926,13 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
         for (int kb = seg.c0 * WIDE_KC; kb < kb_end; ++kb, ++it) {
           const int s = static_cast<int>(it % STAGES);
           const uint32_t ph = (it / STAGES) & 1u;
-          TL_BEGIN(w_empty);
           if (!ptx::mbar_wait_or_abort(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-          TL_END(w_empty);
           uint8_t *st = smem + s * S::STAGE_BYTES;
           if (cta_rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * S::STAGE_BYTES);
           wide_load_operand<A_MN>(st, st + S::TILE_BYTES, &tm_a_hi, &tm_a_lo, &full_bar[s], kb, m0);
           wide_load_operand<B_MN>(st + 2 * S::TILE_BYTES, st + 3 * S::TILE_BYTES, &tm_b_hi, &tm_b_lo, &full_bar[s], kb, nb0);
         }
       }
-      TL_STORE(5, w_empty);
       if (!ok) atomicCAS(error_flag, 0, 301);
     }
   } else if (warp == 1) {
@@ -1001,16 +948,12 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
       constexpr uint64_t b_step_hi = B_MN ? 64 : 2, b_step_x = B_MN ? 128 : 2;
       uint32_t it = 0;  // k-blocks consumed so far
       uint32_t g = 0;   // K chunks issued so far: chunk g goes into buffer g & 1
-      TL_DECL(w_full);
-      TL_DECL(w_acc);
       WideSegments seg(work, cluster_id, num_clusters, num_chunks);
       while (ok && seg.next()) {
         for (int c = seg.c0; c < seg.c1 && ok; ++c, ++g) {
           const uint32_t b = g & 1u;
           if (g >= 2) {
-            TL_BEGIN(w_acc);
             if (!ptx::mbar_wait_or_abort(&acc_empty_bar[b], ((g >> 1) - 1u) & 1u, abort_flag)) { ok = false; break; }
-            TL_END(w_acc);
             ptx::tc_fence_after();
           }
           const uint32_t acc = tmem_base + b * static_cast<uint32_t>(BN);
@@ -1018,10 +961,7 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
           for (int kb = c * WIDE_KC; kb < kb_end; ++kb, ++it) {
             const int s = static_cast<int>(it % STAGES);
             const uint32_t ph = (it / STAGES) & 1u;
-            TL_BEGIN(w_full);
             if (!ptx::mbar_wait_or_abort(&full_bar[s], ph, abort_flag)) { ok = false; break; }
-            TL_END(w_full);
-            if (it == 0) TL(2);
             ptx::tc_fence_after();
             const uint32_t st = ptx::smem_u32(smem + s * S::STAGE_BYTES);
             const uint64_t a_hi = A_MN ? make_smem_desc_mn(st, 4096, true) : make_smem_desc(st);
@@ -1038,10 +978,7 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
           }
           if (ok) ptx::tc_commit_pair(&acc_full_bar[b]);
         }
-        if (g <= static_cast<uint32_t>(num_chunks)) TL(3);
       }
-      TL_STORE(4, w_full);
-      TL_STORE(9, w_acc);
       if (!ok) atomicCAS(error_flag, 0, 302);
     }
   } else if (warp >= WIDE_DRAIN_WARP0) {
@@ -1055,7 +992,6 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
     float *tr = reinterpret_cast<float *>(smem + S::TR_OFFSET) + (warp - WIDE_DRAIN_WARP0) * TR_WARP_FLOATS;
     bool ok = true;
     uint32_t g = 0;
-    TL_DECL(w_accfull);
     WideSegments seg(work, cluster_id, num_clusters, num_chunks);
     while (ok && seg.next()) {
       float sum[128];
@@ -1063,13 +999,11 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
       for (int j = 0; j < 128; ++j) sum[j] = 0.f;
       for (int c = seg.c0; c < seg.c1; ++c, ++g) {
         const uint32_t b = g & 1u;
-        TL_BEGIN(w_accfull);
         if (!ptx::mbar_wait_or_abort(&acc_full_bar[b], (g >> 1) & 1u, abort_flag)) {
           ok = false;
           if (lane == 0) atomicCAS(error_flag, 0, 303);
           break;
         }
-        TL_END(w_accfull);
         ptx::tc_fence_after();
         const uint32_t tsrc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * static_cast<uint32_t>(BN) + static_cast<uint32_t>(half * 128);
 #pragma unroll
@@ -1085,7 +1019,6 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(&acc_empty_bar[b], 0);
       }
-      if (g <= static_cast<uint32_t>(num_chunks) && warp == WIDE_DRAIN_WARP0 && lane == 0) { TL(6); TL_STORE(10, w_accfull); }
       if (!ok || num_kb <= 0) break;
       bool finish = true;  // this warp writes its share of the tile
       if (seg.c0 != 0 || seg.c1 != num_chunks) {
@@ -1177,7 +1110,6 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
           epilogue_row32(epi, v, row0, lane, col_base + jc * 32, dims.M, dims.N, vec_ok, mode, tr);
         }
       }
-      if (g <= static_cast<uint32_t>(num_chunks) && warp == WIDE_DRAIN_WARP0 && lane == 0) TL(7);
     }
   } else {
     ptx::reg_release<40>();  // warps 2-3: no role, but the whole warpgroup has to give its registers back
@@ -1187,8 +1119,6 @@ gemm3x_tf32_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tm_a_hi, con
   ptx::tc_fence_before();
   __syncthreads();
   ptx::cluster_sync_all();
-  if (threadIdx.x == 0) { TL(8); TL_GLOBAL(17); }
-  if (threadIdx.x == 0 && cta_rank == 0) TL_CLUSTER(1, cluster_id);
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
@@ -1335,16 +1265,36 @@ __global__ void __launch_bounds__(256) gemm_fp32_fma_kernel(const Operand A, con
 // Host side
 // ---------------------------------------------------------------------------------------------------------
 static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  if (fn == nullptr) {
+  // function-local static: initialised once, by one thread, before any caller sees the pointer
+  static const PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
     void *p = nullptr;
     cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
-  }
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    return static_cast<PFN_cuTensorMapEncodeTiled_v12000>(nullptr);
+  }();
   return fn;
 }
+
+// First-use set-up per (kernel, device): the opt-in to large dynamic shared memory is a per-device attribute of the
+// kernel.  One table per kernel, indexed by the full device number and guarded, so that two host threads that drive
+// two GPUs can make their first calls at the same time.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+  std::mutex mutex;
+  int value[kMaxDevices] = {};  // 0 = not configured yet
+  // returns the cached value (> 0) or the result of `configure` (<= 0 on failure, not cached)
+  template <typename F> int get(int device, F configure) {
+    if (device < 0 || device >= kMaxDevices) return 0;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (value[device] == 0) {
+      const int v = configure();
+      if (v > 0) value[device] = v;
+      return v;
+    }
+    return value[device];
+  }
+};
 
 static bool make_panel_map(CUtensorMap *map, const float *panel, long long rows, long long k, long long kp, int box_rows) {
   PFN_cuTensorMapEncodeTiled_v12000 fn = get_encode_fn();
@@ -1480,12 +1430,11 @@ int gemm_prepare(Context &ctx, const Operand &op, float *mem, Panels *out, int r
 template <int BN, int STAGES>
 static int launch_tcgen05(Context &ctx, const CUtensorMap maps[4], const GemmDims &dims, const Epilogue &epi) {
   using S = GemmSmem<BN, STAGES>;
-  static bool configured[16] = {};
-  if (!configured[ctx.device & 15]) {
-    if (cudaFuncSetAttribute(gemm3x_tf32_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess)
-      return MYEA_E_CUDA;
-    configured[ctx.device & 15] = true;
-  }
+  static PerDeviceOnce once;
+  if (once.get(ctx.device, [] {
+        return cudaFuncSetAttribute(gemm3x_tf32_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) == cudaSuccess ? 1 : 0;
+      }) <= 0)
+    return MYEA_E_CUDA;
   dim3 grid(static_cast<unsigned>((dims.N + BN - 1) / BN), static_cast<unsigned>((dims.M + BM - 1) / BM));
   launch_dependent(ctx, gemm3x_tf32_tcgen05_kernel<BN, STAGES>, grid, dim3(GEMM_THREADS), S::TOTAL, maps[0], maps[1], maps[2], maps[3], dims, epi,
                    ctx.d_error_flag);
@@ -1493,30 +1442,16 @@ static int launch_tcgen05(Context &ctx, const CUtensorMap maps[4], const GemmDim
 }
 
 static int launch_tcgen05_pair(Context &ctx, const CUtensorMap maps[4], const GemmDims &dims, const Epilogue &epi) {
-  static bool configured[16] = {};
-  if (!configured[ctx.device & 15]) {
-    if (cudaFuncSetAttribute(gemm3x_tf32_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL) != cudaSuccess) return MYEA_E_CUDA;
-    configured[ctx.device & 15] = true;
-  }
+  static PerDeviceOnce once;
+  if (once.get(ctx.device, [] {
+        return cudaFuncSetAttribute(gemm3x_tf32_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL) == cudaSuccess ? 1 : 0;
+      }) <= 0)
+    return MYEA_E_CUDA;
   // the cluster shape (2, 1, 1) is a compile-time attribute of the kernel: the two CTAs of a pair are neighbours along
   // grid x and split the 256 rows of the tile; grid y walks the column tiles
   dim3 grid(static_cast<unsigned>(2 * ((dims.M + 255) / 256)), static_cast<unsigned>((dims.N + 127) / 128));
   gemm3x_tf32_tcgen05_pair_kernel<<<grid, GEMM_THREADS, PairSmem::TOTAL, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], dims, epi, ctx.d_error_flag);
-  const cudaError_t err = cudaGetLastError();
-  if (err != cudaSuccess && getenv("MYEA_B200_DEBUG") != nullptr) {
-    fprintf(stderr, "pair kernel launch: %s\n", cudaGetErrorString(err));
-    cudaFuncAttributes fa;
-    cudaError_t e2 = cudaFuncGetAttributes(&fa, gemm3x_tf32_tcgen05_pair_kernel);
-    fprintf(stderr, "  attrs (%s): regs %d static smem %zu maxdyn %d maxthreads %d clusterDimMustBeSet %d required cluster %d %d %d nonportable %d\n",
-            cudaGetErrorString(e2), fa.numRegs, fa.sharedSizeBytes, fa.maxDynamicSharedSizeBytes, fa.maxThreadsPerBlock, fa.clusterDimMustBeSet,
-            fa.requiredClusterWidth, fa.requiredClusterHeight, fa.requiredClusterDepth, fa.nonPortableClusterSizeAllowed);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = PairSmem::TOTAL;
-    int n = -1;
-    cudaError_t e3 = cudaOccupancyMaxActiveClusters(&n, gemm3x_tf32_tcgen05_pair_kernel, &cfg);
-    fprintf(stderr, "  occupancy: %s clusters %d grid %u %u\n", cudaGetErrorString(e3), n, grid.x, grid.y);
-  }
-  return err == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
 // Workspace of the wide kernel's split tiles: two partial-sum slots of one 256 x 256 tile per cluster and one arrival
@@ -1547,13 +1482,13 @@ void gemm_splitk_release(Context &ctx) {
 
 template <bool A_MN, bool B_MN>
 static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const GemmDims &dims, const Epilogue &epi) {
-  static int clusters[16] = {};  // clusters of two CTAs that can be resident at once, per device
-  const int dev = ctx.device & 15;
   auto kernel = gemm3x_tf32_tcgen05_wide_kernel<A_MN, B_MN>;
-  if (clusters[dev] == 0) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WideSmem::TOTAL) != cudaSuccess) return MYEA_E_CUDA;
+  static PerDeviceOnce once;  // value: clusters of two CTAs that can be resident at once on the device
+  const int device = ctx.device;
+  const int G = once.get(device, [kernel, device] {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WideSmem::TOTAL) != cudaSuccess) return 0;
     int sms = 0;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device) != cudaSuccess || sms < 2) return MYEA_E_CUDA;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 2) return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1));
     cfg.blockDim = dim3(WIDE_THREADS);
@@ -1563,10 +1498,9 @@ static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const Ge
       cudaGetLastError();
       n = sms / 2;
     }
-    clusters[dev] = n < sms / 2 ? n : sms / 2;
-    if (getenv("MYEA_B200_DEBUG") != nullptr) fprintf(stderr, "wide kernel: %d resident clusters on %d SMs\n", clusters[dev], sms);
-  }
-  const int G = clusters[dev];
+    return n < sms / 2 ? n : sms / 2;
+  });
+  if (G <= 0) return MYEA_E_CUDA;
   const int num_kb = (dims.K + BK - 1) / BK;
   const int num_chunks = (num_kb + WIDE_KC - 1) / WIDE_KC;
   WideWork work = {};
@@ -1581,11 +1515,11 @@ static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const Ge
   if (ctx.gemm_bn != 4 && ctx.sk_ws != nullptr && ctx.sk_clusters >= G && rem != 0 && num_chunks >= 2) {
     const int units = rem * num_chunks;
     int per_cluster = (units + G - 1) / G;
-    // at most 8 clusters share one tile (MYEA_B200_SK_MAX_SPLIT overrides, 0 = no limit): the cluster that arrives last
-    // adds up every other contributor's 256 KB of partial sums, and past 8 that pass outweighs the shorter K walk
-    // (256 x 1024 x 4096, 4 tiles: 16-way split 53.6 us, 8-way 47.2 us, 4-way 51.0 us per call with its split passes)
-    static const int max_split = getenv("MYEA_B200_SK_MAX_SPLIT") != nullptr ? atoi(getenv("MYEA_B200_SK_MAX_SPLIT")) : 8;
-    if (max_split > 0) per_cluster = std::max(per_cluster, (num_chunks + max_split - 1) / max_split);
+    // at most 8 clusters share one tile: the cluster that arrives last adds up every other contributor's 256 KB of
+    // partial sums, and past 8 that pass outweighs the shorter K walk (256 x 1024 x 4096, 4 tiles: 16-way split
+    // 53.6 us, 8-way 47.2 us, 4-way 51.0 us per call with its split passes)
+    constexpr int max_split = 8;
+    per_cluster = std::max(per_cluster, (num_chunks + max_split - 1) / max_split);
 
     // splitting a tile costs about one chunk's time (partial sums through L2, one counter round trip, the second
     // pass of the warp that arrives last): worth it when it takes at least two chunks off the longest cluster
@@ -1601,9 +1535,7 @@ static int launch_tcgen05_wide(Context &ctx, const CUtensorMap maps[4], const Ge
   }
   launch_dependent(ctx, kernel, dim3(static_cast<unsigned>(2 * grid_clusters)), dim3(WIDE_THREADS), WideSmem::TOTAL, maps[0], maps[1], maps[2],
                    maps[3], dims, work, epi, ctx.d_error_flag);
-  const cudaError_t err = cudaGetLastError();
-  if (err != cudaSuccess && getenv("MYEA_B200_DEBUG") != nullptr) fprintf(stderr, "wide kernel launch: %s\n", cudaGetErrorString(err));
-  return err == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
 // C (+)= A * B^T on operands whose panels are already in place; (row0, rows) select a row range of each panel set.
@@ -1686,12 +1618,3 @@ int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &ep
 }
 
 }  // namespace myea
-
-#ifdef MYEA_GEMM_TIMELINE
-extern "C" int myea_b200_gemm_timeline(long long *out32) {
-  return cudaMemcpyFromSymbol(out32, myea::g_timeline, sizeof(long long) * 32) == cudaSuccess ? 0 : 1;
-}
-extern "C" int myea_b200_gemm_cluster_times(long long *out256) {
-  return cudaMemcpyFromSymbol(out256, myea::g_cluster_times, sizeof(long long) * 256) == cudaSuccess ? 0 : 1;
-}
-#endif

@@ -91,13 +91,7 @@ extern "C" int myea_b200_gemm_nt(int device, int engine, uint64_t M, uint64_t N,
     if (cudaMemcpyAsync(C, dC, M * N * 4, cudaMemcpyDeviceToHost, ctx.stream) != cudaSuccess) rc = MYEA_E_CUDA;
     int flag = 0;
     cudaMemcpyAsync(&flag, ctx.d_error_flag, sizeof(int), cudaMemcpyDeviceToHost, ctx.stream);
-    {
-      const cudaError_t se = cudaStreamSynchronize(ctx.stream);
-      if (se != cudaSuccess) {
-        if (getenv("MYEA_B200_DEBUG") != nullptr) fprintf(stderr, "gemm_nt: %s\n", cudaGetErrorString(se));
-        rc = MYEA_E_CUDA;
-      }
-    }
+    if (cudaStreamSynchronize(ctx.stream) != cudaSuccess) rc = MYEA_E_CUDA;
     if (rc == MYEA_OK && flag != 0) rc = MYEA_E_KERNEL;
   }
   if (e0) cudaEventDestroy(e0);

@@ -13,11 +13,17 @@
 // Limit: the hi/lo K-major panels of both operands must fit: 2 * (M + N) * round_up(K, 32) + 64 floats <= 8 Mi floats;
 // larger problems are refused with MYEA_E_INVALID and a message, never truncated.
 // Sharing: all calls on a device use the same array, which keeps whatever the previous call left in it.  Nothing in
-// it has to start at zero (both panels are rewritten in full, padding included) except the status word, which each
-// call clears first.  Two calls that overlap on the GPU (different streams, or different host threads) would
-// overwrite each other's panels: callers must serialise them.
+// it has to start at zero except the status word, which each call clears first: a call rewrites columns
+// [0, round_up(K, 8)) of every panel row it uses, and what an earlier, larger call left beyond that is never read,
+// because the tensor maps the kernel loads through end at round_up(K, 8) and the hardware fills the rest of a tile
+// with zeros.  Two calls that overlap on the GPU (different streams, or different host threads) would overwrite each
+// other's panels: callers must serialise them.
 // Set-up: the device address of the array is looked up once per device, on the first call for that device, with that
-// device current.  Make that first call outside any stream capture.
+// device current.
+// The call is synchronous: it waits for the result and reads the status word back, so it must never be made on a
+// stream that is being captured (neither the first call nor a later one).
+// Current device: the call makes `device` current for its own work and puts the caller's current device back before
+// it returns.
 #include "common.cuh"
 
 #include <mutex>
@@ -67,10 +73,16 @@ extern "C" int myea_b200_gemm_nt_static(int device, uint64_t M, uint64_t N, uint
     say(error_message, error_capacity, msg);
     return MYEA_E_INVALID;
   }
-  if (cudaSetDevice(device) != cudaSuccess) {
+  int previous_device = -1;
+  if (cudaGetDevice(&previous_device) != cudaSuccess || cudaSetDevice(device) != cudaSuccess) {
     say(error_message, error_capacity, "gemm_nt_static: cudaSetDevice failed");
     return MYEA_E_CUDA;
   }
+  // the caller's current device comes back on every way out of this function
+  struct RestoreDevice {
+    int device;
+    ~RestoreDevice() { if (device >= 0) cudaSetDevice(device); }
+  } restore{previous_device == device ? -1 : previous_device};
   StaticSetup &su = g_setup[device];
   {
     std::lock_guard<std::mutex> lock(g_setup_mutex);

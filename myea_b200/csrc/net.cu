@@ -123,7 +123,6 @@ int myea::build_index_map(myea_b200_net *net) {
   for (uint32_t l = 1; l < n; ++l) {
     LayerPlan &L = net->layers[l];
     if (L.type != MYEA_LAYER_RESIDUAL) continue;
-    if (net->layers[l - 1].type == MYEA_LAYER_RESIDUAL && false) return fail(net, MYEA_E_INVALID, "unreachable");
     net->layers[l + 1].input_layer = static_cast<int>(l) - 1;
     net->layers[l + 1].n_in = net->layers[l - 1].n_out;
     const uint32_t after = l + L.block_depth + 1;
@@ -334,12 +333,8 @@ extern "C" int myea_b200_create(myea_handle *out, const myea_net_desc *desc, int
   net->T = static_cast<long long>(desc->number_recurrent_depth);
   net->B = static_cast<long long>(desc->batch_size);
   net->active_B = net->B;
-  const char *eng = getenv("MYEA_B200_GEMM_ENGINE");
+  const char *eng = getenv("MYEA_B200_GEMM_ENGINE");  // 1 = the exact FP32 FMA engine (tests use it to tell tensor-core effects apart)
   if (eng != nullptr && eng[0] == '1') net->ctx.gemm_engine = 1;
-  const char *tile = getenv("MYEA_B200_GEMM_TILE");  // 2 = CTA pairs, 128 / 256 = single-CTA column tile, unset = heuristic
-  if (tile != nullptr) net->ctx.gemm_bn = atoi(tile);
-  const char *pdl = getenv("MYEA_B200_PDL");  // 0 = launch every kernel fully serialised
-  if (pdl != nullptr && pdl[0] == '0') net->ctx.dependent_launch = false;
   *out = net;  // returned even on failure so that the caller can read last_error, then destroy
   if (cudaStreamCreateWithFlags(&net->ctx.stream, cudaStreamNonBlocking) != cudaSuccess) return fail(net, MYEA_E_CUDA, "cudaStreamCreate failed");
   cudaEventCreate(&net->ctx.ev0);
@@ -415,7 +410,7 @@ extern "C" int myea_b200_upload(myea_handle net, int which, const float *host, u
   if (net == nullptr || host == nullptr) return MYEA_E_INVALID;
   size_t n = 0;
   float *dst = select_buffer(net, which, &n);
-  if (dst == nullptr || offset + count > n) return fail(net, MYEA_E_INVALID, "upload: buffer selector or range out of bounds");
+  if (dst == nullptr || offset > n || count > n - offset) return fail(net, MYEA_E_INVALID, "upload: buffer selector or range out of bounds");
   CK(cudaSetDevice(net->ctx.device));
   CK(cudaMemcpyAsync(dst + offset, host, count * sizeof(float), cudaMemcpyHostToDevice, net->ctx.stream));
   CK(cudaStreamSynchronize(net->ctx.stream));
@@ -429,7 +424,7 @@ extern "C" int myea_b200_download(myea_handle net, int which, float *host, uint6
   if (net == nullptr || host == nullptr) return MYEA_E_INVALID;
   size_t n = 0;
   float *src = select_buffer(net, which, &n);
-  if (src == nullptr || offset + count > n) return fail(net, MYEA_E_INVALID, "download: buffer selector or range out of bounds");
+  if (src == nullptr || offset > n || count > n - offset) return fail(net, MYEA_E_INVALID, "download: buffer selector or range out of bounds");
   CK(cudaSetDevice(net->ctx.device));
   CK(cudaMemcpyAsync(host, src + offset, count * sizeof(float), cudaMemcpyDeviceToHost, net->ctx.stream));
   CK(cudaStreamSynchronize(net->ctx.stream));

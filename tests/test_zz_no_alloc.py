@@ -44,6 +44,27 @@ def test_static_scratch_matches_allocating_entry_point_twice():
     _both(lib, torch, 129, 70, 45, accumulate=1, seed=2)      # smaller second call over the first call's leftovers
 
 
+def test_static_scratch_reaches_the_wide_kernel_and_allocates_nothing():
+    """a shape that takes the 256 x 256 persistent kernel yet fits the fixed array (about 4.7 M of 8 Mi floats); this entry
+    point has no partial-sum workspace, so that kernel computes whole tiles only.  A second, warm call must leave the
+    device's free memory exactly where it was."""
+    torch = pytest.importorskip("torch")
+    lib = capi.load()
+    M, N, K = 512, 640, 2048
+    _both(lib, torch, M, N, K, accumulate=0, seed=3)
+    rng = np.random.default_rng(4)
+    dA = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).cuda()
+    dB = torch.from_numpy(rng.standard_normal((N, K)).astype(np.float32)).cuda()
+    dC = torch.zeros((M, N), device="cuda")
+    msg = C.create_string_buffer(256)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    assert lib.myea_b200_gemm_nt_static(0, M, N, K, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0, None, msg, 256) == 0, msg.value
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert torch.cuda.current_device() == 0
+
+
 def test_static_scratch_refuses_oversized_problems():
     torch = pytest.importorskip("torch")
     lib = capi.load()
