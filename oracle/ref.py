@@ -14,24 +14,27 @@ from myea_b200 import capi
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "_ref", "libmyea_ref.so")
-_LIB = None
+LIB_PATH_F64 = os.path.join(HERE, "_ref", "libmyea_ref_f64.so")   # the reference built with its COMPILE_DOUBLE switch
+_LIBS = {}
 
 
-def available():
-    return os.path.exists(LIB_PATH)
+def available(double=False):
+    return os.path.exists(LIB_PATH_F64 if double else LIB_PATH)
 
 
-def _lib():
-    global _LIB
-    if _LIB is None:
-        lib = C.CDLL(LIB_PATH)
+def _lib(double=False):
+    if double not in _LIBS:
+        lib = C.CDLL(LIB_PATH_F64 if double else LIB_PATH)
+        lib.ref_scalar_bytes.restype = C.c_int
+        scalar = C.c_double if lib.ref_scalar_bytes() == 8 else C.c_float
+        lib.scalar, lib.np_scalar = scalar, (np.float64 if scalar is C.c_double else np.float32)
         lib.ref_create.restype = C.c_void_p
         lib.ref_create.argtypes = [C.POINTER(capi.NetDesc), C.POINTER(capi.OptDesc), C.c_int]
         lib.ref_destroy.argtypes = [C.c_void_p]
         lib.ref_threads.argtypes = [C.c_void_p]
         lib.ref_sizes.argtypes = [C.c_void_p] + [C.POINTER(C.c_uint64)] * 4
         lib.ref_layer_index.argtypes = [C.c_void_p, C.c_uint32, C.POINTER(capi.LayerIndex)]
-        lib.ref_buffer.restype = C.POINTER(C.c_float)
+        lib.ref_buffer.restype = C.POINTER(scalar)
         lib.ref_buffer.argtypes = [C.c_void_p, C.c_int]
         lib.ref_set_mask_bernoulli.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64]
         lib.ref_set_mask_zoneout.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint64]
@@ -52,8 +55,8 @@ def _lib():
         lib.ref_general_state.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]
         lib.ref_time_steps.restype = C.c_double
         lib.ref_time_steps.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int, C.c_int]
-        _LIB = lib
-    return _LIB
+        _LIBS[double] = lib
+    return _LIBS[double]
 
 
 def _f32(a):
@@ -61,8 +64,9 @@ def _f32(a):
 
 
 class RefNet:
-    def __init__(self, desc, opt, threads=1):
-        self.lib = _lib()
+    def __init__(self, desc, opt, threads=1, double=False):
+        """double=True: the COMPILE_DOUBLE build of the same sources; buffers, outputs and errors are float64 arrays then"""
+        self.lib = _lib(double)
         self.desc, self.opt = desc, opt
         self.h = self.lib.ref_create(C.byref(desc), C.byref(opt), threads)
         if not self.h:
@@ -130,7 +134,7 @@ class RefNet:
         return self._buf(which, self._count(which)).copy()
 
     def set(self, which, arr):
-        a = _f32(arr).ravel()
+        a = np.ascontiguousarray(arr, dtype=self.lib.np_scalar).ravel()
         self._buf(which, a.size)[:] = a
 
     def set_mask_bernoulli(self, layer, mask):
@@ -178,13 +182,13 @@ class RefNet:
 
     def outputs(self, layer):
         w = int(self.layer_index(layer).number_outputs)
-        out = np.empty((self.T, self.B, w), np.float32)
+        out = np.empty((self.T, self.B, w), self.lib.np_scalar)
         self.lib.ref_get_outputs(self.h, layer, self.B, out.ctypes.data)
         return out
 
     def errors(self, layer):
         w = int(self.layer_index(layer).number_outputs)
-        out = np.empty((self.T, self.B, w), np.float32)
+        out = np.empty((self.T, self.B, w), self.lib.np_scalar)
         if self.lib.ref_get_errors(self.h, layer, self.B, out.ctypes.data) != 0:
             raise RuntimeError("layer %d has no error buffer" % layer)
         return out

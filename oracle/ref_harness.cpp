@@ -27,8 +27,8 @@ struct RefNet {
   myea_net_desc desc;
   int threads = 1;
   size_t n_inputs = 0, n_outputs = 0, T = 1;
-  std::vector<std::vector<float>> xrows, yrows;
-  std::vector<const float *> xptr, yptr;
+  std::vector<std::vector<T_>> xrows, yrows;   // T_ is the reference's scalar: float, or double in the COMPILE_DOUBLE build
+  std::vector<const T_ *> xptr, yptr;
 };
 
 void apply_opt(Neural_Network &nn, const myea_opt_desc &o) {
@@ -58,13 +58,14 @@ void apply_opt(Neural_Network &nn, const myea_opt_desc &o) {
 }
 
 // [T][B][W] packed block -> one contiguous [T*W] row per sample (Neural_Network__Assign_Inputs.cpp:273-304).
-void unpack_rows(const float *tbw, size_t T, size_t B, size_t W, std::vector<std::vector<float>> &rows,
-                 std::vector<const float *> &ptrs) {
+void unpack_rows(const float *tbw, size_t T, size_t B, size_t W, std::vector<std::vector<T_>> &rows,
+                 std::vector<const T_ *> &ptrs) {
   rows.resize(B);
   ptrs.resize(B);
   for (size_t b = 0; b < B; ++b) {
     rows[b].resize(T * W);
-    for (size_t t = 0; t < T; ++t) std::memcpy(&rows[b][t * W], tbw + (t * B + b) * W, W * sizeof(float));
+    for (size_t t = 0; t < T; ++t)
+      for (size_t j = 0; j < W; ++j) rows[b][t * W + j] = static_cast<T_>(tbw[(t * B + b) * W + j]);
     ptrs[b] = rows[b].data();
   }
 }
@@ -133,8 +134,10 @@ void *ref_create(const myea_net_desc *d, const myea_opt_desc *opt, int threads) 
     nn.Set__Batch_Renormalization_d_Correction_Maximum(d->batch_renormalization_d_correction_maximum);
   for (uint32_t i = 1; i < d->number_layers; ++i) {
     const myea_layer_desc &L = d->layers[i];
-    if (L.type_dropout != MYEA_DROPOUT_NONE)
-      ok = ok && nn.Set__Dropout(i, static_cast<ENUM_TYPE_LAYER_DROPOUT>(L.type_dropout), L.dropout_values, false);
+    if (L.type_dropout != MYEA_DROPOUT_NONE) {
+      const T_ values[3] = {static_cast<T_>(L.dropout_values[0]), static_cast<T_>(L.dropout_values[1]), static_cast<T_>(L.dropout_values[2])};
+      ok = ok && nn.Set__Dropout(i, static_cast<ENUM_TYPE_LAYER_DROPOUT>(L.type_dropout), values, false);
+    }
   }
   if (opt != nullptr) {
     if (opt->regularization__weight_decay != 0.f) ok = ok && nn.Set__Regularization__Weight_Decay(opt->regularization__weight_decay);
@@ -152,6 +155,10 @@ void *ref_create(const myea_net_desc *d, const myea_opt_desc *opt, int threads) 
 }
 
 void ref_destroy(void *h) { delete static_cast<RefNet *>(h); }
+
+// bytes of the reference's scalar type in this build: 4 (float) or 8 (COMPILE_DOUBLE); buffers, outputs and errors
+// cross this interface in that type, inputs and targets always arrive as float
+int ref_scalar_bytes(void) { return static_cast<int>(sizeof(T_)); }
 
 int ref_threads(void *h) { return static_cast<RefNet *>(h)->threads; }
 
@@ -191,7 +198,7 @@ int ref_layer_index(void *h, uint32_t layer, myea_layer_index *out) {
   return 0;
 }
 
-float *ref_buffer(void *h, int which) {
+T_ *ref_buffer(void *h, int which) {
   Neural_Network &nn = static_cast<RefNet *>(h)->nn;
   switch (which) {
     case MYEA_BUF_PARAMETERS: return nn.ptr_array_parameters;
@@ -297,30 +304,30 @@ int ref_get_loss(void *h, double *loss_sum, uint64_t *number_loss, double *accur
 }
 
 // outputs of `layer` for the batch of the last forward pass, packed [T][B][outputs]
-int ref_get_outputs(void *h, uint32_t layer, uint64_t B, float *out) {
+int ref_get_outputs(void *h, uint32_t layer, uint64_t B, T_ *out) {
   RefNet *r = static_cast<RefNet *>(h);
   Neural_Network &nn = r->nn;
   Layer *L = nn.ptr_array_layers + layer;
   size_t W = *L->ptr_number_outputs;
   for (size_t t = 0; t < r->T; ++t)
-    for (size_t b = 0; b < B; ++b) std::memcpy(out + (t * B + b) * W, nn.Get__Outputs(L, b, t), W * sizeof(float));
+    for (size_t b = 0; b < B; ++b) std::memcpy(out + (t * B + b) * W, nn.Get__Outputs(L, b, t), W * sizeof(T_));
   return 0;
 }
 
 // delta of `layer` after the backward pass, packed [T][B][units]: FC = Neuron_unit::ptr_array_errors,
 // LSTM = Cell_unit::ptr_delta_cell_output (error arriving on the cell outputs)
-int ref_get_errors(void *h, uint32_t layer, uint64_t B, float *out) {
+int ref_get_errors(void *h, uint32_t layer, uint64_t B, T_ *out) {
   RefNet *r = static_cast<RefNet *>(h);
   Neural_Network &nn = r->nn;
   Layer *L = nn.ptr_array_layers + layer;
   size_t W = *L->ptr_number_outputs;
-  const float *src = nullptr;
+  const T_ *src = nullptr;
   if (L->type_layer == ENUM_TYPE_LAYER::TYPE_LAYER_FULLY_CONNECTED) src = L->ptr_array_neuron_units->ptr_array_errors;
   else if (L->type_layer == ENUM_TYPE_LAYER::TYPE_LAYER_LSTM) src = L->ptr_array_cell_units->ptr_delta_cell_output;
   if (src == nullptr) return -1;
   for (size_t t = 0; t < r->T; ++t)
     for (size_t b = 0; b < B; ++b)
-      std::memcpy(out + (t * B + b) * W, src + (t * nn.batch_size + b) * W, W * sizeof(float));
+      std::memcpy(out + (t * B + b) * W, src + (t * nn.batch_size + b) * W, W * sizeof(T_));
   return 0;
 }
 
@@ -368,13 +375,13 @@ int ref_shakedrop_replay(void *h, uint64_t B, uint8_t *masks, float *alpha, floa
     for (size_t b = 0; b < B; ++b) {
       const bool m = bern();
       masks[k * B + b] = m ? 1 : 0;
-      for (size_t j = 0; j < widths[k]; ++j) alpha[offsets[k] + b * widths[k] + j] = m ? real() : 1.0f;
+      for (size_t j = 0; j < widths[k]; ++j) alpha[offsets[k] + b * widths[k] + j] = m ? static_cast<float>(real()) : 1.0f;
     }
   }
   for (size_t k = blocks.size(); k-- > 0;) {
     real.Range(0_T, 1_T);
     for (size_t b = 0; b < B; ++b)
-      for (size_t j = 0; j < widths[k]; ++j) beta[offsets[k] + b * widths[k] + j] = masks[k * B + b] ? real() : 1.0f;
+      for (size_t j = 0; j < widths[k]; ++j) beta[offsets[k] + b * widths[k] + j] = masks[k * B + b] ? static_cast<float>(real()) : 1.0f;
   }
   return static_cast<int>(blocks.size());
 }

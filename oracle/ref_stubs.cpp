@@ -26,6 +26,7 @@ template unsigned long Cin_Number<unsigned long>(unsigned long, unsigned long, s
 template long long Cin_Number<long long>(long long, std::string const &);
 template long long Cin_Number<long long>(long long, long long, std::string const &);
 template double Cin_Real_Number<double>(double, double, std::string const &);
+template double Cin_Real_Number<double>(double, std::string const &);
 template float Cin_Real_Number<float>(float, std::string const &);
 template float Cin_Real_Number<float>(float, float, std::string const &);
 template bool Read_Stream_Block_And_Parse_Number<double>(char *&, char *&, size_t &, size_t const, size_t const,

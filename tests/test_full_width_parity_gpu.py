@@ -1,0 +1,234 @@
+"""GPU parity against the COMPILED REFERENCE at the benchmark configurations' stated widths.
+
+One training step on both sides (same seeded parameters, masks, inputs), compared tensor by tensor:
+  C1  64-256-256-10, batch 128 (the full configuration)
+  C2  4096 -> 8 x FC 4096 + BatchNorm + ReLU + inverted dropout -> 1024, batch 256 (all widths and all 8 layers; the
+      batch is cut so that the reference's per-sample loops finish in seconds; 256 rows still take the 256 x 256
+      tensor-core kernel, the shared operand panels and the tiles split along K)
+  C3  2 x LSTM(1024) with peepholes, input 512, T = 64, batch 136
+  C4  FC 1024 -> 2048, 6 residual blocks of 2 x FC 2048 (batch renormalization, ELU, ShakeDrop), softmax 1000, batch 136
+
+Error metric.  `rel_err` is NORM-WISE per tensor: max |a - b| / max |b|.  Every derivative tensor (each layer's weights,
+biases, scales, shifts taken separately), the first moment (linear in the derivative), the loss, the running averages
+and the outputs must agree within 1e-4.  Besides, `miss_share` counts the ELEMENTS whose error exceeds 1e-4 of their
+own magnitude.
+
+Updated parameters under Adam-type optimizers.  The first Adam step is lr_t * m / (sqrt(v) + eps) ~ lr * sign(g): an
+element whose derivative is smaller than the rounding noise of the sum that produced it may get the opposite sign on
+two correct fp32 implementations, and its updated weight then differs by 2 * lr - far more than 1e-4 of max |w|.
+Those elements are decided by the reference's own sources built with its COMPILE_DOUBLE switch (float64 truth): the
+test requires (1) that the update applied on the GPU is the optimizer's formula on the GPU's own derivative, (2) that
+the share of elements whose updated value differs from the fp32 reference by more than 1e-4 of max |w| is small, and
+(3) that on those elements the GPU is not farther from the float64 result than the fp32 reference is.
+
+Setting MYEA_PARITY_REPORT=<file> appends one JSON line per case with every figure.
+"""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+import pytest
+
+from conftest import rel_err
+from myea_b200 import capi, workloads
+from myea_b200.net import Net
+from oracle import myea_oracle, ref
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4
+THREADS = min(os.cpu_count() or 1, 32)
+
+
+def _tensors(net, wl):
+    """(name, slice) of every parameter tensor of the flat buffer: per layer weights and biases, then scales / shifts"""
+    P, W, nb, nn = net.sizes()
+    out = []
+    for l in range(1, len(wl.layers)):
+        li = net.layer_index(l)
+        a, b = int(li.first_connection_index), int(li.last_connection_index)
+        if b > a:
+            out.append(("layer%d.weights" % l, slice(a, b)))
+    out.append(("biases", slice(W, W + nb)))
+    if nn:
+        out.append(("norm.scale", slice(W + nb, W + nb + nn)))
+        out.append(("norm.shift", slice(W + nb + nn, P)))
+    return out
+
+
+def miss_share(a, b, tol=TOL):
+    """share of elements whose error exceeds tol of their OWN magnitude (elements that are zero on both sides agree)"""
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    bad = np.abs(a - b) > tol * np.abs(b)
+    return float(bad.mean()) if b.size else 0.0
+
+
+def _step(net, wl, X, Y, shake=None):
+    wl.materialize(net)
+    drawn = None
+    if hasattr(net, "next_shakedrop"):
+        drawn = net.next_shakedrop()
+    elif shake:
+        for layer, (m, a, b) in shake.items():
+            net.set_shakedrop(layer, m, a, b)
+    out = {"param_before": net.get(capi.BUF_PARAMETERS)}
+    net.reset_loss()
+    net.forward(X)
+    net.compute_error(Y)
+    net.backward()
+    net.update_derivative_weight()
+    out["grad"] = net.get(capi.BUF_DERIVATIVES)
+    out["loss"] = net.loss()
+    out["output"] = net.outputs(len(wl.layers) - 1)
+    net.update_parameter()
+    out["param"] = net.get(capi.BUF_PARAMETERS)
+    out["m"] = net.get(capi.BUF_FIRST_MOMENT)
+    out["v"] = net.get(capi.BUF_SECOND_MOMENT)
+    if net.sizes()[3]:
+        out["norm_mean_avg"] = net.get(capi.BUF_NORM_MEAN_AVERAGE)
+        out["norm_sigma_avg"] = net.get(capi.BUF_NORM_VARIANCE_AVERAGE)
+    return out, drawn
+
+
+def _report(record):
+    path = os.environ.get("MYEA_PARITY_REPORT")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps(record) + "\n")
+
+
+def _adam_first_step(opt, p0, g):
+    """the first update of Adam / AMSGrad as the reference codes it (Neural_Network__Adam.cpp:97-159, fp32 arithmetic)"""
+    f = np.float32
+    b1, b2, eps, lr = f(opt.adam_beta1), f(opt.adam_beta2), f(opt.adam_epsilon), f(opt.adam_learning_rate)
+    lr_t = lr * np.sqrt(f(1) - b2) / (f(1) - b1)
+    m, v = (f(1) - b1) * g, (f(1) - b2) * g * g
+    return p0 - lr_t * m / (np.sqrt(v) + eps)
+
+
+def _check_case(name, wl, check_formula, truth="reference"):
+    """truth: who arbitrates the updated parameters - "reference": the reference's sources built with COMPILE_DOUBLE;
+    "restatement": the numpy restatement in float64 (takes imposed ShakeDrop draws, which the compiled float64 build,
+    whose generators produce doubles and therefore other draws, cannot)"""
+    X, Y = wl.batch()
+    gpu = Net(wl.desc, wl.opt)
+    # ShakeDrop: the reference draws inside the step from one generator per thread in schedule order; only its
+    # single-thread mode has a draw sequence that can be replayed and imposed on the other side
+    shake = any(L.type_dropout == capi.DROP_SHAKEDROP for L in wl.layers)
+    cpu = ref.RefNet(wl.desc, wl.opt, threads=1 if shake else THREADS)
+    want, drawn = _step(cpu, wl, X, Y)
+    got, _ = _step(gpu, wl, X, Y, shake=drawn)
+    gpu.synchronize()
+    assert gpu.launches() > 0
+    record = {"case": name, "workload": wl.name, "batch": wl.B, "T": wl.T, "parameters": int(gpu.sizes()[0]), "tensors": {}}
+    # sizes and index map exact
+    assert gpu.sizes() == cpu.sizes()
+    for l in range(len(wl.layers)):
+        assert gpu.layer_index(l).as_tuple() == cpu.layer_index(l).as_tuple()
+    # loss and counts
+    assert got["loss"][1] == want["loss"][1] and got["loss"][2] == want["loss"][2]
+    assert abs(got["loss"][0] - want["loss"][0]) <= TOL * abs(want["loss"][0])
+    record["loss_rel_err"] = abs(got["loss"][0] - want["loss"][0]) / abs(want["loss"][0])
+    record["output_rel_err"] = rel_err(got["output"], want["output"])
+    assert record["output_rel_err"] < TOL
+    worst = 0.0
+    for tname, sl in _tensors(gpu, wl):
+        if not np.abs(want["grad"][sl]).max() > 0:
+            assert not got["grad"][sl].any()
+            continue
+        e_g, e_m = rel_err(got["grad"][sl], want["grad"][sl]), rel_err(got["m"][sl], want["m"][sl])
+        record["tensors"][tname] = {"grad_rel_err": e_g, "grad_miss_share": miss_share(got["grad"][sl], want["grad"][sl]),
+                                    "moment_rel_err": e_m, "param_rel_err": rel_err(got["param"][sl], want["param"][sl]),
+                                    "param_miss_share": miss_share(got["param"][sl], want["param"][sl])}
+        worst = max(worst, e_g, e_m)
+    record["grad_rel_err_worst_tensor"] = worst
+    if "norm_mean_avg" in want:
+        record["norm_avg_rel_err"] = max(rel_err(got["norm_mean_avg"], want["norm_mean_avg"]), rel_err(got["norm_sigma_avg"], want["norm_sigma_avg"]))
+        assert record["norm_avg_rel_err"] < TOL
+    # updated parameters
+    scale = float(np.abs(want["param"]).max())
+    diff = np.abs(got["param"].astype(np.float64) - want["param"])
+    differing = diff > TOL * scale
+    record["param_rel_err_whole_buffer"] = float(diff.max() / scale)
+    record["param_share_beyond_1e-4_of_max"] = float(differing.mean())
+    if check_formula:   # (1) the update is the optimizer's formula on the GPU's own derivative
+        mine = _adam_first_step(wl.opt, got["param_before"], got["grad"])
+        record["update_formula_rel_err"] = rel_err(got["param"], mine)
+        assert record["update_formula_rel_err"] < 1e-6
+    if differing.any():
+        cpu.close()
+        cpu = None
+        if truth == "reference":
+            assert ref.available(double=True), "the float64 build of the reference is missing (SCALAR=double oracle/build_ref.sh)"
+            f64 = ref.RefNet(wl.desc, wl.opt, threads=THREADS, double=True)
+        else:
+            f64 = myea_oracle.OracleNet(wl.desc, wl.opt, dtype=np.float64)
+        exact, _ = _step(f64, wl, X, Y, shake=drawn)
+        f64.close()
+        idx = np.nonzero(differing)[0]
+        e_gpu = np.abs(got["param"][idx].astype(np.float64) - exact["param"][idx])
+        e_ref = np.abs(want["param"][idx].astype(np.float64) - exact["param"][idx])
+        record["tie_break"] = {"elements": int(idx.size), "gpu_closer": int((e_gpu < e_ref).sum()), "reference_closer": int((e_ref < e_gpu).sum()),
+                               "gpu_mean_error": float(e_gpu.mean()), "reference_mean_error": float(e_ref.mean()),
+                               "gpu_grad_rel_err_vs_f64": rel_err(got["grad"], exact["grad"]),
+                               "reference_grad_rel_err_vs_f64": rel_err(want["grad"], exact["grad"]),
+                               "gpu_param_rel_err_vs_f64": rel_err(got["param"], exact["param"]),
+                               "reference_param_rel_err_vs_f64": rel_err(want["param"], exact["param"])}
+    _report(record)
+    assert worst < TOL, record["tensors"]
+    # (2) few elements differ, (3) and where they do the GPU is no farther from float64 than the fp32 reference
+    assert record["param_share_beyond_1e-4_of_max"] < 2e-3, record
+    if "tie_break" in record:
+        tb = record["tie_break"]
+        assert tb["gpu_mean_error"] <= 1.5 * tb["reference_mean_error"] + 1e-12, tb
+    gpu.close()
+    if cpu is not None:
+        cpu.close()
+
+
+needs_reference = pytest.mark.skipif(not ref.available(), reason="the compiled reference (oracle/_ref) is not present")
+
+
+@needs_reference
+def test_c1_full_size_against_the_reference():
+    _check_case("c1", workloads.c1_mlp(), check_formula=True)
+
+
+@needs_reference
+def test_c2_all_layers_full_width_against_the_reference():
+    _check_case("c2", workloads.c2_wide_mlp(batch=256), check_formula=True)
+
+
+@needs_reference
+def test_c3_full_width_full_length_against_the_reference():
+    _check_case("c3", workloads.c3_lstm(batch=136), check_formula=True)   # AMSGrad's first step equals Adam's (v_hat = v)
+
+
+@needs_reference
+def test_c4_full_width_against_the_reference():
+    _check_case("c4", workloads.c4_residual(batch=136), check_formula=False, truth="restatement")
+
+
+def test_contraction_over_131072_rows():
+    """the weight derivative of the bidirectional configuration sums over T x B = 131072 rows: zero-mean data as the errors
+    are, and all-positive data as the worst case for the tensor core's truncating accumulation"""
+    lib = capi.load()
+    M, N, K = 256, 384, 131072
+    rng = np.random.default_rng(3)
+    for positive, tol in ((False, 2e-5), (True, TOL)):
+        gen = (lambda s: rng.uniform(0, 1, s)) if positive else rng.standard_normal
+        A, B = gen((M, K)).astype(np.float32), gen((N, K)).astype(np.float32)
+        out = np.zeros((M, N), np.float32)
+        assert lib.myea_b200_gemm_nt(0, 0, M, N, K, A.ctypes.data, B.ctypes.data, out.ctypes.data, 0, None, 0) == 0
+        want = A.astype(np.float64) @ B.astype(np.float64).T
+        err = float(np.abs(out - want).max() / np.abs(want).max())
+        _report({"case": "gemm_k131072", "positive": positive, "rel_err": err})
+        assert err < tol, (positive, err)
+        # the same sum with the operands read through their columns (how the weight derivative reads them)
+        out2 = np.zeros((M, N), np.float32)
+        At, Bt = np.ascontiguousarray(A.T), np.ascontiguousarray(B.T)
+        flags = (3 << 8) | (1 << 17) | (1 << 18)
+        assert lib.myea_b200_gemm_nt(0, flags, M, N, K, At.ctypes.data, Bt.ctypes.data, out2.ctypes.data, 0, None, 0) == 0
+        err2 = float(np.abs(out2 - want).max() / np.abs(want).max())
+        _report({"case": "gemm_k131072_columns", "positive": positive, "rel_err": err2})
+        assert err2 < tol, (positive, err2)
