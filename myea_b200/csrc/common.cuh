@@ -117,31 +117,6 @@ __host__ __device__ __forceinline__ float af_derive(uint32_t af, float z, float 
 __host__ __device__ inline float sigmoid_ref(float x) { return 1.0f / (1.0f + expf(-x)); }
 __host__ __device__ inline float tanh_ref(float x) { return 2.0f / (1.0f + expf(-2.0f * x)) - 1.0f; }
 
-// LSTM cell of one time step fused into the epilogue of that step's recurrent contraction (C a multiple of 8).
-//   kind 1, forward: the contraction is h_prev [B, C] * W_rec^T with the rows of W_rec interleaved (column 4 * cell +
-//     gate, gates z, i, f, o), so the thread that owns a batch row holds all four recurrent sums of 8 consecutive cells;
-//     it adds the input projections, applies peepholes, gates, cell state and zoneout exactly as
-//     lstm_cell_forward_kernel does, stores what the backward pass needs and writes h both as the layer's output and
-//     as the K-major operand panels of the next step's contraction.
-//   kind 2, backward: the contraction is dgates_next [B, 4C] * W_rec [4C, C] (error arriving on h of step t through
-//     time); the thread adds the error from the layers above, runs lstm_cell_backward_kernel's arithmetic for its
-//     cells and writes the gate errors of step t as arrays and as the operand panels of the next contraction.
-struct LstmFuse {
-  int kind = 0;
-  long long C = 0, ldh = 0, kp = 0;
-  const float *peep = nullptr;  // compact peepholes [3][C]: p_i, p_f, p_o
-  float *p_hi = nullptr, *p_cross = nullptr;  // operand panels written for the next step (role A, pitch kp)
-  // forward (rows of step t unless said otherwise)
-  const float *gates_in = nullptr, *c_prev = nullptr, *h_prev = nullptr;
-  float *act = nullptr, *cstate = nullptr, *cact = nullptr, *h = nullptr;
-  const uint8_t *zone_state = nullptr, *zone_output = nullptr;
-  // backward
-  float *dh = nullptr;  // [B, ldh] error on h of step t from above; the recurrent part is added in place
-  const float *b_act = nullptr, *b_cact = nullptr, *b_c_prev = nullptr, *act_next = nullptr, *dgates_next = nullptr, *dc_next = nullptr;
-  float *dgates = nullptr, *dcstate = nullptr;
-  long long Cp = 0;  // K offset of gate g inside the gate-error panel is g * Cp
-};
-
 struct Epilogue {
   float *C = nullptr;
   long long ldc = 0;
@@ -155,7 +130,6 @@ struct Epilogue {
   long long ld_aux = 0;
   const float *col_scale = nullptr;  // pre = aux_pre * col_scale[n] + col_shift[n] when non-null (normalization folded in)
   const float *col_shift = nullptr;
-  LstmFuse lstm;                     // kind != 0: the accumulator feeds an LSTM cell instead of being stored (tensor-core kernels only)
   // seg_rows != 0: the output rows come in up to 4 segments of seg_rows rows; row m of the product is row
   // (m mod seg_rows) of the array that starts at C + seg_off[m / seg_rows] (the four gate matrices of an LSTM layer
   // inside the reference's per-block parameter layout: one contraction instead of four)
@@ -203,6 +177,9 @@ int gemm_prepare_into(Context &ctx, const Operand &op, const Panels &dst, long l
 int gemm_prepare_interleaved(Context &ctx, const Operand &op, const Panels &dst, long long row_offset, long long row_step);
 int gemm_panels(Context &ctx, const Panels &A, long long a_row0, long long M, const Panels &B, long long b_row0, long long N,
                 const Epilogue &epi);
+// TMA descriptor of a K-major panel [rows][kp] (hi, or cross seen as 32-bit words): boxes of 32 floats of K x box_rows
+// rows, 128-byte swizzle; K ends at round_up(k, 8) and rows at `rows` (the hardware fills the rest of a box with zeros)
+bool make_panel_map(CUtensorMap *map, const float *panel, long long rows, long long k, long long kp, int box_rows);
 // One pass over a row-major source S[R][C] that serves BOTH readings of it: `as_rows` is the K-major operand
 // (rows = R, K = C) and `as_cols` the MN-major operand (rows = C, K = R); they share the hi panel.  Either output may
 // be null.  `mem` needs shared_panel_floats(R, C) floats.

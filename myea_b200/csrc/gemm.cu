@@ -28,6 +28,7 @@
 // The FP32 FMA kernel at the end of the file is the second engine (exact fp32 products; selectable for debugging).
 #include "common.cuh"
 #include "panel_math.cuh"
+#include "tcgen05.cuh"
 
 #include <cudaTypedefs.h>
 #include <cuda_bf16.h>
@@ -36,243 +37,6 @@
 #include <mutex>
 
 namespace myea {
-
-// ---------------------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------------------
-namespace ptx {
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// Bounded wait: gives up after ~2^31 SM cycles (about a second). Returns false on timeout.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > (1ll << 31)) return false;
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t *smem_holder, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)), "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_commit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// D[tmem] (+)= A[smem desc] * B[smem desc], TF32 inputs, FP32 accumulate
-__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// D[tmem] (+)= A * B, BF16 inputs (K = 16), FP32 accumulate: the cross-term instruction
-__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// 32 lanes x 32 consecutive fp32 columns of tensor memory -> 32 registers per thread
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// ---- CTA-pair (cta_group::2) forms ----
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// TMA load whose completion bytes are counted on the LEADER CTA's mbarrier (same offset, peer bit of the cluster
-// shared-memory address cleared); no multicast: every CTA fetches its own tile.
-__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d_pair(void *smem_dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_holder, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-// arrives on the mbarrier at this offset in BOTH CTAs of the pair once all earlier MMAs of this thread are complete
-__device__ __forceinline__ void tc_commit_pair(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
-               "h"(static_cast<uint16_t>(3))
-               : "memory");
-}
-__device__ __forceinline__ void mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// arrive on the mbarrier at the same shared-memory offset in CTA `cta` of the cluster
-__device__ __forceinline__ void mbar_arrive_cluster(uint64_t *bar, uint32_t cta) {
-  asm volatile(
-      "{\n"
-      ".reg .b32 ra;\n"
-      "mapa.shared::cluster.u32 ra, %0, %1;\n"
-      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n"
-      "}\n" ::"r"(smem_u32(bar)),
-      "r"(cta)
-      : "memory");
-}
-// setmaxnreg: a warpgroup (4 aligned warps) hands registers back to the SM / takes more; the count is a multiple of 8
-template <int N> __device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N> __device__ __forceinline__ void reg_acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-__device__ __forceinline__ void named_barrier_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
-
-// Bounded wait that gives up at once when another wait of this CTA has already failed (keeps the worst case short).
-__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-  if (*abort_flag) return false;
-  if (mbar_wait(bar, parity)) return true;
-  *abort_flag = 1;
-  return false;
-}
-
-}  // namespace ptx
-
-// ---------------------------------------------------------------------------------------------------------
-// Descriptors
-// ---------------------------------------------------------------------------------------------------------
-constexpr int BM = 128;       // rows of the output tile = UMMA M = tensor-memory lanes
-constexpr int BK = 32;        // floats of K per pipeline stage = one 128-byte swizzle row
-constexpr int UMMA_K = 8;     // K of one tcgen05.mma.kind::tf32 (32 bytes)
-constexpr int GEMM_THREADS = 192;
-
-// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte swizzle TMA
-// wrote it with: start address >> 4 in bits 0-13, leading byte offset (unused for swizzled K-major) bits 16-29,
-// stride byte offset = 1024 B (8 rows) >> 4 in bits 32-45, descriptor version 1 in bits 46-47, layout type
-// SWIZZLE_128B (2) in bits 61-63.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>(1) << 16;
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
-  return d;
-}
-
-// The same for an MN-major tile: rows of 128 bytes run along M (or N) - 32 fp32 or 64 bf16 elements -, consecutive rows
-// are consecutive K, 8 rows form one swizzle atom (stride byte offset 1024 B between atoms along K) and the next 128
-// bytes' worth of M / N elements starts `chunk_bytes` further on (leading byte offset).
-// 32-bit elements (the TF32 hi panel) must use the 128-byte swizzle with 32-byte atoms in this orientation (TMA
-// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, layout type 1): its pattern repeats every 4 rows, so the stride byte offset
-// between K groups is 512 B.  16-bit elements (the bf16 cross panel) use the ordinary 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32_t chunk_bytes, bool atom32) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>(chunk_bytes >> 4) << 16;
-  d |= static_cast<uint64_t>((atom32 ? 512 : 1024) >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(atom32 ? 1 : 2) << 61;
-  return d;
-}
-
-// Instruction descriptor of tcgen05.mma.kind::tf32: D format F32 (1) bits 4-5, A and B format TF32 (2) bits 7-9 and
-// 10-12, both operands K-major (bits 15, 16 clear), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-__host__ __device__ constexpr uint32_t make_idesc_tf32(int m, int n, bool a_mn = false, bool b_mn = false) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
-         (static_cast<uint32_t>(m >> 4) << 24);
-}
-// tcgen05.mma.kind::f16 with BF16 inputs (format 1) and an F32 accumulator
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn = false, bool b_mn = false) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
-         (static_cast<uint32_t>(m >> 4) << 24);
-}
 
 struct GemmDims {
   int M, N, K;
@@ -425,23 +189,6 @@ __device__ __forceinline__ void epilogue_row32(const Epilogue &e, const float (&
                                                bool vec_ok, int mode, float *tr) {
   const long long m = row0 + lane;
   if (col0 >= N) return;
-  if (e.lstm.kind == 1) {  // 32 columns = 8 cells x 4 gates; the thread keeps its row
-    if (m < M) lstm_forward_cells8(e.lstm, v, m, col0 >> 2);
-    return;
-  }
-  if (e.lstm.kind == 2) {  // 32 columns = 32 cells (N = C is a multiple of 8)
-    if (m >= M) return;
-#pragma unroll
-    for (int g8 = 0; g8 < 4; ++g8) {
-      if (col0 + g8 * 8 < N) {
-        float r8[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) r8[j] = v[g8 * 8 + j];
-        lstm_backward_cells8(e.lstm, r8, m, col0 + g8 * 8);
-      }
-    }
-    return;
-  }
   if (vec_ok && col0 + 32 <= N) {
     switch (mode) {
       case 0: epilogue_block32<false, false, false>(e, tr, v, lane, row0, col0, M); break;
@@ -1296,7 +1043,7 @@ struct PerDeviceOnce {
   }
 };
 
-static bool make_panel_map(CUtensorMap *map, const float *panel, long long rows, long long k, long long kp, int box_rows) {
+bool make_panel_map(CUtensorMap *map, const float *panel, long long rows, long long k, long long kp, int box_rows) {
   PFN_cuTensorMapEncodeTiled_v12000 fn = get_encode_fn();
   if (fn == nullptr) return false;
   // panels are zero-filled up to the next multiple of 8 along K and the cross panel is only meaningful in whole groups of 8

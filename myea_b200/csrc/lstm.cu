@@ -19,46 +19,12 @@
 // contraction plus one fused cell kernel (gate nonlinearities, peepholes, cell-state recurrence, zoneout select), each
 // BPTT step is one [B, 4C] x [4C, C] contraction accumulated into the output error plus one fused cell-backward kernel,
 // and the weight derivatives are contractions over K = T*B.  Bias and peephole derivatives are column reductions.
-#include "net.cuh"
+#include "lstm.cuh"
 #include "panel_math.cuh"
 
 #include <algorithm>
 
 namespace myea {
-
-struct LstmDir {
-  long long w_base = 0;   // first parameter of this direction's blocks
-  long long b_base = 0;   // [bz (C) | bi (C) | bf (C) | bo (C)]
-  float *gates_in = nullptr;  // [T*B, 4C] input projection + bias, columns [z | i | f | o]
-  float *act = nullptr;       // [T*B, 4C] activated gates
-  float *cstate = nullptr, *cact = nullptr;  // [T*B, C] cell state, tanh(cell state)
-  float *dgates = nullptr;    // [T*B, 4C] error w.r.t. the gate summations
-  float *dcstate = nullptr;   // [T*B, C]
-  uint8_t *zone_state = nullptr, *zone_output = nullptr;  // [T, C], 1 = compute, 0 = keep the previous value
-};
-
-struct LstmPlan {
-  int dirs = 1;
-  long long C = 0, n_in = 0, stride = 0;
-  bool zoneout = false;
-  LstmDir d[2];
-  float *s_rec = nullptr;      // [B, 4C] recurrent projection of the current step
-  float *panel_mem = nullptr;  // W_rec panels, their transpose, per-step operand panels
-  size_t off_wrec = 0, off_wrect = 0, off_step = 0;
-  float *partial = nullptr;    // [7][chunks][C]
-  // cell fused into the recurrent contraction (C a multiple of 8, tensor-core engine): compact peepholes
-  // [dirs][3][C], ping-pong operand panels of h (forward) and of the gate errors (backward)
-  bool shared_dw = false;  // weight derivatives from untransposed (column-read) operand panels
-  bool fuse = false;
-  // With `fuse`, a step is two kernels: the contraction and an 8-cells-per-thread cell kernel that also writes the next
-  // operand panels.  fuse_mask (MYEA_B200_LSTM_FUSE) moves the cell into the contraction's epilogue instead: bit 0
-  // forward, bit 1 backward.  One kernel per step, but measured slower on C3 (the few threads that own accumulator
-  // rows walk their cells one memory round trip after the other), so it is off by default.
-  int fuse_mask = 0;
-  float *peep_compact = nullptr;
-  float *h_panels[2] = {nullptr, nullptr};
-  float *dg_panels[2] = {nullptr, nullptr};
-};
 
 // offsets of the gate matrices inside one block of the parameter buffer (Prepare__Connections__LSTM)
 struct BlockOffsets {

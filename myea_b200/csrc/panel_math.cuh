@@ -51,32 +51,57 @@ __device__ __forceinline__ void store_panel_group(float *hi_row, float *cross_ro
   *reinterpret_cast<uint4 *>(cross_row + 4) = make_uint4(x[4], x[5], x[6], x[7]);
 }
 
-// LSTM forward cell for batch row b, cells [c0, c0 + 8): rec[4 * i + g] is the recurrent sum of gate g of cell c0 + i.
-// Same arithmetic, in the same order, as lstm_cell_forward_kernel (lstm.cu) on a step that has a predecessor.
-__device__ __forceinline__ void lstm_forward_cells8(const LstmFuse &p, const float (&rec)[32], long long b, long long c0) {
+// One time step of an LSTM layer as the cell arithmetic sees it: the arrays of step t, of the step before / after it in
+// the layer's direction, and where the results also leave as operand panels of the next step's contraction.
+struct LstmStep {
+  long long C = 0, ldh = 0, kp = 0;
+  const float *peep = nullptr;  // compact peepholes [3][C]: p_i, p_f, p_o
+  float *p_hi = nullptr, *p_cross = nullptr;  // operand panels written for the next step (role A, pitch kp), or null
+  // forward (rows of step t unless said otherwise)
+  const float *gates_in = nullptr, *c_prev = nullptr, *h_prev = nullptr;
+  float *act = nullptr, *cstate = nullptr, *cact = nullptr, *h = nullptr;
+  const uint8_t *zone_state = nullptr, *zone_output = nullptr;
+  // backward
+  float *dh = nullptr;  // [B, ldh] error on h of step t from above; the error through time is added in place
+  const float *b_act = nullptr, *b_cact = nullptr, *b_c_prev = nullptr, *act_next = nullptr, *dgates_next = nullptr, *dc_next = nullptr;
+  float *dgates = nullptr, *dcstate = nullptr;
+  long long Cp = 0;  // K offset of gate g inside the gate-error panel is g * Cp
+};
+
+// LSTM forward cell for batch row b, cells [c0, c0 + 8), in two halves so that a caller can issue the loads before it
+// waits for the recurrent sums: load8 fetches everything the step needs from memory, finish8 takes the recurrent sums
+// (rec[4 * i + g] = gate g of cell c0 + i) and writes the results.  Same arithmetic, in the same order, as
+// lstm_cell_forward_kernel (lstm.cu) on a step that has a predecessor.
+struct LstmForwardIn {
+  float gz[8], gi[8], gf[8], go[8], cp[8], hp[8], pi[8], pf[8], po[8];
+  unsigned long long zs, zo;
+};
+__device__ __forceinline__ void lstm_forward_load8(const LstmStep &p, LstmForwardIn &in, long long b, long long c0) {
   const long long C = p.C;
-  float gz[8], gi[8], gf[8], go[8], cp[8], pi[8], pf[8], po[8], hp[8];
   const float *g = p.gates_in + b * 4 * C + c0;
-  load8(gz, g); load8(gi, g + C); load8(gf, g + 2 * C); load8(go, g + 3 * C);
-  load8(cp, p.c_prev + b * C + c0);
-  load8(pi, p.peep + c0); load8(pf, p.peep + C + c0); load8(po, p.peep + 2 * C + c0);
-  const unsigned long long zs = p.zone_state != nullptr ? *reinterpret_cast<const unsigned long long *>(p.zone_state + c0) : ~0ull;
-  const unsigned long long zo = p.zone_output != nullptr ? *reinterpret_cast<const unsigned long long *>(p.zone_output + c0) : ~0ull;
-  if (p.zone_output != nullptr) load8(hp, p.h_prev + b * p.ldh + c0);
+  load8(in.gz, g); load8(in.gi, g + C); load8(in.gf, g + 2 * C); load8(in.go, g + 3 * C);
+  load8(in.cp, p.c_prev + b * C + c0);
+  load8(in.pi, p.peep + c0); load8(in.pf, p.peep + C + c0); load8(in.po, p.peep + 2 * C + c0);
+  in.zs = p.zone_state != nullptr ? *reinterpret_cast<const unsigned long long *>(p.zone_state + c0) : ~0ull;
+  in.zo = p.zone_output != nullptr ? *reinterpret_cast<const unsigned long long *>(p.zone_output + c0) : ~0ull;
+  if (p.zone_output != nullptr) load8(in.hp, p.h_prev + b * p.ldh + c0);
+}
+__device__ __forceinline__ void lstm_forward_finish8(const LstmStep &p, const LstmForwardIn &in, const float (&rec)[32], long long b, long long c0) {
+  const long long C = p.C;
   float z[8], ig[8], fg[8], og[8], cs[8], a[8], h[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    z[i] = tanh_ref(gz[i] + rec[4 * i]);
-    ig[i] = sigmoid_ref(gi[i] + (rec[4 * i + 1] + pi[i] * cp[i]));
-    fg[i] = sigmoid_ref(gf[i] + rec[4 * i + 2] + pf[i] * cp[i]);
+    z[i] = tanh_ref(in.gz[i] + rec[4 * i]);
+    ig[i] = sigmoid_ref(in.gi[i] + (rec[4 * i + 1] + in.pi[i] * in.cp[i]));
+    fg[i] = sigmoid_ref(in.gf[i] + rec[4 * i + 2] + in.pf[i] * in.cp[i]);
     float c = z[i] * ig[i];
-    c += fg[i] * cp[i];
-    if (((zs >> (8 * i)) & 0xFFull) == 0ull) c = cp[i];
+    c += fg[i] * in.cp[i];
+    if (((in.zs >> (8 * i)) & 0xFFull) == 0ull) c = in.cp[i];
     cs[i] = c;
     a[i] = tanh_ref(c);
-    og[i] = sigmoid_ref(go[i] + rec[4 * i + 3] + po[i] * c);
+    og[i] = sigmoid_ref(in.go[i] + rec[4 * i + 3] + in.po[i] * c);
     float hh = a[i] * og[i];
-    if (((zo >> (8 * i)) & 0xFFull) == 0ull) hh = hp[i];
+    if (((in.zo >> (8 * i)) & 0xFFull) == 0ull) hh = in.hp[i];
     h[i] = hh;
   }
   float *act = p.act + b * 4 * C + c0;
@@ -86,36 +111,46 @@ __device__ __forceinline__ void lstm_forward_cells8(const LstmFuse &p, const flo
   store8(p.h + b * p.ldh + c0, h);
   if (p.p_hi != nullptr) store_panel_group(p.p_hi + b * p.kp + c0, p.p_cross + b * p.kp + c0, h);
 }
+__device__ __forceinline__ void lstm_forward_cells8(const LstmStep &p, const float (&rec)[32], long long b, long long c0) {
+  LstmForwardIn in;
+  lstm_forward_load8(p, in, b, c0);
+  lstm_forward_finish8(p, in, rec, b, c0);
+}
 
 // LSTM backward cell for batch row b, cells [c0, c0 + 8): rec[i] is the error arriving on h of cell c0 + i through time.
-// Same arithmetic as lstm_cell_backward_kernel on a step that has a successor.
-__device__ __forceinline__ void lstm_backward_cells8(const LstmFuse &p, const float (&rec)[8], long long b, long long c0) {
-  const long long C = p.C;
+// Same arithmetic as lstm_cell_backward_kernel on a step that has a successor; load8 / finish8 as above.
+struct LstmBackwardIn {
   float dh[8], z[8], ig[8], fg[8], og[8], a[8], pi[8], pf[8], po[8], cp[8], dni[8], dnf[8], dcn[8], fn[8];
-  load8(dh, p.dh + b * p.ldh + c0);
+};
+__device__ __forceinline__ void lstm_backward_load8(const LstmStep &p, LstmBackwardIn &in, long long b, long long c0) {
+  const long long C = p.C;
+  load8(in.dh, p.dh + b * p.ldh + c0);
   const float *act = p.b_act + b * 4 * C + c0;
-  load8(z, act); load8(ig, act + C); load8(fg, act + 2 * C); load8(og, act + 3 * C);
-  load8(a, p.b_cact + b * C + c0);
-  load8(pi, p.peep + c0); load8(pf, p.peep + C + c0); load8(po, p.peep + 2 * C + c0);
-  if (p.b_c_prev != nullptr) load8(cp, p.b_c_prev + b * C + c0);
+  load8(in.z, act); load8(in.ig, act + C); load8(in.fg, act + 2 * C); load8(in.og, act + 3 * C);
+  load8(in.a, p.b_cact + b * C + c0);
+  load8(in.pi, p.peep + c0); load8(in.pf, p.peep + C + c0); load8(in.po, p.peep + 2 * C + c0);
+  if (p.b_c_prev != nullptr) load8(in.cp, p.b_c_prev + b * C + c0);
   const float *dn = p.dgates_next + b * 4 * C + c0;
-  load8(dni, dn + C); load8(dnf, dn + 2 * C);
-  load8(dcn, p.dc_next + b * C + c0);
-  load8(fn, p.act_next + b * 4 * C + 2 * C + c0);
-  float dz[8], di[8], df[8], d_o[8], dc[8];
+  load8(in.dni, dn + C); load8(in.dnf, dn + 2 * C);
+  load8(in.dcn, p.dc_next + b * C + c0);
+  load8(in.fn, p.act_next + b * 4 * C + 2 * C + c0);
+}
+__device__ __forceinline__ void lstm_backward_finish8(const LstmStep &p, const LstmBackwardIn &in, const float (&rec)[8], long long b, long long c0) {
+  const long long C = p.C;
+  float dh[8], dz[8], di[8], df[8], d_o[8], dc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    dh[i] += rec[i];
-    d_o[i] = og[i] * (1.f - og[i]) * (dh[i] * a[i]);
-    float d = dh[i] * og[i] * (1.f - a[i] * a[i]);
-    d += po[i] * d_o[i];
-    d += pi[i] * dni[i];
-    d += pf[i] * dnf[i];
-    d += dcn[i] * fn[i];
+    dh[i] = in.dh[i] + rec[i];
+    d_o[i] = in.og[i] * (1.f - in.og[i]) * (dh[i] * in.a[i]);
+    float d = dh[i] * in.og[i] * (1.f - in.a[i] * in.a[i]);
+    d += in.po[i] * d_o[i];
+    d += in.pi[i] * in.dni[i];
+    d += in.pf[i] * in.dnf[i];
+    d += in.dcn[i] * in.fn[i];
     dc[i] = d;
-    dz[i] = d * ig[i] * (1.f - z[i] * z[i]);
-    di[i] = (d * z[i]) * (ig[i] * (1.f - ig[i]));
-    df[i] = p.b_c_prev != nullptr ? (d * cp[i]) * (fg[i] * (1.f - fg[i])) : 0.f;
+    dz[i] = d * in.ig[i] * (1.f - in.z[i] * in.z[i]);
+    di[i] = (d * in.z[i]) * (in.ig[i] * (1.f - in.ig[i]));
+    df[i] = p.b_c_prev != nullptr ? (d * in.cp[i]) * (in.fg[i] * (1.f - in.fg[i])) : 0.f;
   }
   store8(p.dh + b * p.ldh + c0, dh);
   float *dg = p.dgates + b * 4 * C + c0;
@@ -128,6 +163,11 @@ __device__ __forceinline__ void lstm_backward_cells8(const LstmFuse &p, const fl
     store_panel_group(hi + 2 * p.Cp, cr + 2 * p.Cp, df);
     store_panel_group(hi + 3 * p.Cp, cr + 3 * p.Cp, d_o);
   }
+}
+__device__ __forceinline__ void lstm_backward_cells8(const LstmStep &p, const float (&rec)[8], long long b, long long c0) {
+  LstmBackwardIn in;
+  lstm_backward_load8(p, in, b, c0);
+  lstm_backward_finish8(p, in, rec, b, c0);
 }
 
 }  // namespace myea

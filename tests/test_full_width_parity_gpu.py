@@ -13,6 +13,16 @@ biases, scales, shifts taken separately), the first moment (linear in the deriva
 and the outputs must agree within 1e-4.  Besides, `miss_share` counts the ELEMENTS whose error exceeds 1e-4 of their
 own magnitude.
 
+Ties at activation kinks.  ReLU's derivative jumps at 0 and the reference's ELU derivative jumps there too (it codes
+alpha * y below zero).  A pre-activation within rounding distance of 0 therefore gets a different gate on two correct
+fp32 implementations, which changes that row's error outright and, through W^T, every derivative of the layers below
+by about 1e-3: measured on C2 at batch 256 with the seeded parameters as they come, the fp32 reference is 1.4e-2 away
+from ITS OWN float64 build on the derivatives and the GPU 1.2e-2, with about one such tie per layer among a million
+pre-activations.  To make the comparison about arithmetic and not about coin flips, the cases with such activations
+run from a parameter state without ties: a float64 forward pass (the numpy restatement) finds every pre-activation
+within 5e-4 of zero and moves the unit's shift (or bias) by the smallest amount that clears all rows of the batch.
+The adjusted vector is then the common starting point of all sides, so every side still sees identical parameters.
+
 Updated parameters under Adam-type optimizers.  The first Adam step is lr_t * m / (sqrt(v) + eps) ~ lr * sign(g): an
 element whose derivative is smaller than the rounding noise of the sum that produced it may get the opposite sign on
 two correct fp32 implementations, and its updated weight then differs by 2 * lr - far more than 1e-4 of max |w|.
@@ -63,8 +73,67 @@ def miss_share(a, b, tol=TOL):
     return float(bad.mean()) if b.size else 0.0
 
 
-def _step(net, wl, X, Y, shake=None):
+KINKED = (capi.AF_RELU, capi.AF_LEAKY_RELU, capi.AF_ELU, capi.AF_SELU)
+
+
+def _clear_ties(pre, margin):
+    """per column j the offset of smallest magnitude such that no pre[:, j] + offset lies within `margin` of zero"""
+    out = np.zeros(pre.shape[1])
+    for j in np.nonzero((np.abs(pre) < margin).any(axis=0))[0]:
+        v = np.sort(pre[:, j])
+        # the new zero point p = -offset must have no value in (p - margin, p + margin): the ends and every wide enough gap
+        lo = np.concatenate(([-np.inf], v + margin))
+        hi = np.concatenate((v - margin, [np.inf]))
+        ok = hi >= lo
+        p = np.clip(0.0, lo[ok], hi[ok])
+        out[j] = -p[np.argmin(np.abs(p))]
+    return out
+
+
+def _tie_free_parameters(wl, X, shake, margin=5e-4):
+    """the workload's seeded parameter vector with shifts / biases nudged so that, in float64, no pre-activation of an
+    activation with a kink lies within `margin` of zero; None when the network has no such activation"""
+    if not any(L.type_layer == capi.LAYER_FC and L.type_activation_function in KINKED for L in wl.layers[1:-1]):
+        return None
+    net = myea_oracle.OracleNet(wl.desc, wl.opt, dtype=np.float64)
     wl.materialize(net)
+    for layer, (m, a, b) in (shake or {}).items():
+        net.set_shakedrop(layer, m, a, b)
+    P = net.buf[capi.BUF_PARAMETERS]
+    done = set()
+    while True:
+        if net.n_norm:
+            net.buf[capi.BUF_NORM_MEAN_AVERAGE][:] = 0.0
+            net.buf[capi.BUF_NORM_VARIANCE_AVERAGE][:] = 1.0
+        net.forward(X)
+        changed = False
+        for l in range(1, len(wl.layers) - 1):
+            L = net.layers[l]
+            if l in done or L.type != capi.LAYER_FC or int(L.d.type_activation_function) not in KINKED:
+                continue
+            done.add(l)
+            in_block = hasattr(L, "dw_input")   # layers of a residual block activate their INPUT (pre-activation order)
+            if in_block and not hasattr(L, "pre_in"):
+                continue                         # first layer of a block: no activation in front of it
+            pre = L.pre_in if in_block else L.pre
+            if not (np.abs(pre) < margin).any():
+                continue
+            normed = int(L.d.type_normalization) != capi.NORM_NONE
+            if normed:
+                slot = L.idx["shift_index"]
+            else:   # the bias that enters this pre-activation: the layer's own, or the previous block layer's
+                slot = (net.layers[l - 1] if in_block else L).idx["first_bias_connection_index"]
+            P[slot:slot + pre.shape[1]] += _clear_ties(np.asarray(pre, np.float64), margin)
+            changed = True
+            break
+        if not changed:
+            return P.astype(np.float32)
+
+
+def _step(net, wl, X, Y, shake=None, params=None):
+    wl.materialize(net)
+    if params is not None:
+        net.set(capi.BUF_PARAMETERS, params)
     drawn = None
     if hasattr(net, "next_shakedrop"):
         drawn = net.next_shakedrop()
@@ -116,8 +185,11 @@ def _check_case(name, wl, check_formula, truth="reference"):
     # single-thread mode has a draw sequence that can be replayed and imposed on the other side
     shake = any(L.type_dropout == capi.DROP_SHAKEDROP for L in wl.layers)
     cpu = ref.RefNet(wl.desc, wl.opt, threads=1 if shake else THREADS)
-    want, drawn = _step(cpu, wl, X, Y)
-    got, _ = _step(gpu, wl, X, Y, shake=drawn)
+    wl.materialize(cpu)
+    drawn = cpu.next_shakedrop()            # the reference's draws of its next step (copies of its generators are replayed)
+    params = _tie_free_parameters(wl, X, drawn)
+    want, _ = _step(cpu, wl, X, Y, params=params)
+    got, _ = _step(gpu, wl, X, Y, shake=drawn, params=params)
     gpu.synchronize()
     assert gpu.launches() > 0
     record = {"case": name, "workload": wl.name, "batch": wl.B, "T": wl.T, "parameters": int(gpu.sizes()[0]), "tensors": {}}
@@ -163,7 +235,7 @@ def _check_case(name, wl, check_formula, truth="reference"):
             f64 = ref.RefNet(wl.desc, wl.opt, threads=THREADS, double=True)
         else:
             f64 = myea_oracle.OracleNet(wl.desc, wl.opt, dtype=np.float64)
-        exact, _ = _step(f64, wl, X, Y, shake=drawn)
+        exact, _ = _step(f64, wl, X, Y, shake=drawn, params=params)
         f64.close()
         idx = np.nonzero(differing)[0]
         e_gpu = np.abs(got["param"][idx].astype(np.float64) - exact["param"][idx])
