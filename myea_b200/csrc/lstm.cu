@@ -194,7 +194,7 @@ __global__ void lstm_bias_peephole_finalize_kernel(const float *__restrict__ par
 // Cell kernels of the steps that have a predecessor / successor, 8 consecutive cells of one batch row per thread: the
 // arithmetic of lstm_cell_forward_kernel / lstm_cell_backward_kernel, and the results also leave as the operand panels
 // of the next step's contraction (no separate split pass).  p.kind selects; s_rec / rec_dh is the contraction's output.
-__global__ void __launch_bounds__(256) lstm_cells8_forward_kernel(const LstmFuse p, const float *__restrict__ s_rec, long long B) {
+__global__ void __launch_bounds__(256) lstm_cells8_forward_kernel(const LstmStep p, const float *__restrict__ s_rec, long long B) {
   grid_dependency_wait();
   grid_dependency_release();
   const long long groups = p.C >> 3, total = B * groups;
@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(256) lstm_cells8_forward_kernel(const LstmFuse
   }
 }
 // the error through time has already been added into p.dh by the contraction (accumulate epilogue): rec = 0
-__global__ void __launch_bounds__(256) lstm_cells8_backward_kernel(const LstmFuse p, long long B) {
+__global__ void __launch_bounds__(256) lstm_cells8_backward_kernel(const LstmStep p, long long B) {
   grid_dependency_wait();
   grid_dependency_release();
   const long long groups = p.C >> 3, total = B * groups;
@@ -295,13 +295,26 @@ int lstm_create(myea_b200_net *net, LayerPlan &L) {
   LRC(lalloc(net, &P->panel_mem, P->off_step + panel_floats(net->B, 4 * Cp) + 64));
   LRC(lalloc(net, &P->partial, static_cast<size_t>(7) * net->reduce_chunks * C));
   P->fuse = (C % 8 == 0) && net->ctx.gemm_engine == 0;
-  if (const char *fm = getenv("MYEA_B200_LSTM_FUSE")) P->fuse_mask = atoi(fm);
   if (P->fuse) {
     LRC(lalloc(net, &P->peep_compact, static_cast<size_t>(P->dirs) * 3 * C));
-    for (int i = 0; i < 2; ++i) {
-      LRC(lalloc(net, &P->h_panels[i], panel_floats(net->B, C) + 64));
-      LRC(lalloc(net, &P->dg_panels[i], panel_floats(net->B, 4 * Cp) + 64));
-    }
+    // ping-pong operand panels, rows padded to whole 128-row tiles and zero (rows past the batch stay zero for ever)
+    const long long prow = (net->B + 127) / 128 * 128;
+    auto two_buffers = [&](long long k, Panels (&pan)[2]) -> int {
+      const long long kp = (k + 31) / 32 * 32;
+      float *mem = nullptr;
+      LRC(lalloc(net, &mem, static_cast<size_t>(4 * prow * kp) + 64));
+      for (int i = 0; i < 2; ++i) {
+        pan[i] = Panels{};
+        pan[i].hi = mem + i * prow * kp;
+        pan[i].lo = mem + (2 + i) * prow * kp;
+        pan[i].rows = net->B; pan[i].k = k; pan[i].kp = kp;
+        pan[i].role = PANEL_ROLE_A; pan[i].major = PANEL_K;
+      }
+      return MYEA_OK;
+    };
+    LRC(two_buffers(C, P->h_pan));
+    LRC(two_buffers(4 * Cp, P->dg_pan));
+    LRC(lstm_persistent_plan(net, L));
   }
   // one-shot contractions use the handle's scratch: make sure it is large enough
   size_t need = 0;
@@ -316,6 +329,7 @@ int lstm_create(myea_b200_net *net, LayerPlan &L) {
 }
 
 void lstm_destroy(LayerPlan &L) {
+  lstm_persistent_destroy(L.lstm);
   delete L.lstm;
   L.lstm = nullptr;
 }
@@ -406,9 +420,10 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
       lstm_gather_peepholes_kernel<<<static_cast<unsigned>((C + 255) / 256), 256, 0, ctx.stream>>>(w + off.peep, P->stride, C, peep_c);
       ctx.end(TC_RECURRENT);
     }
-    if (P->fuse && (P->fuse_mask & 1)) {
-      // rows interleaved cell by cell (row 4 * cell + gate): one output row of the contraction then holds the four
-      // gate sums of a cell side by side and the cell can be finished in the epilogue
+    const bool persistent = lstm_persistent_ready(P);
+    if (persistent) {
+      // rows interleaved cell by cell (row 4 * cell + gate): the 128 columns of a tile of the step's product then hold the
+      // four gate sums of 32 cells side by side and the kernel finishes whole cells from its share of the tile
       LRC(gemm_prepare_interleaved(ctx, Operand{w + off.z_rec, C, C, P->stride, 1}, pwrec, 0, 4));
       for (int g = 0; g < 3; ++g) LRC(gemm_prepare_interleaved(ctx, Operand{w + off.rec[g], C, C, P->stride, 1}, pwrec, g + 1, 4));
     } else {
@@ -420,14 +435,17 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
       const long long t = d == 0 ? s : T - 1 - s;
       const long long tp = d == 0 ? t - 1 : t + 1;
       float *h_t = L.values + t * B * ldh + d * C;
+      if (persistent && s > 0) {  // one launch walks steps 1 .. T-1
+        LRC(lstm_persistent_forward(net, L, d, pwrec, peep_c, zone));
+        break;
+      }
       if (P->fuse && s > 0) {
-        // recurrent contraction on the panels the previous step left, then the cell (in the contraction's epilogue or
-        // as a kernel of its own); h_t leaves as the layer output and as the operand panels of step s + 1
-        const Panels ph_prev = panels_at(P->h_panels[(s - 1) & 1], B, C, PANEL_ROLE_A);
-        const Panels ph_next = panels_at(P->h_panels[s & 1], B, C, PANEL_ROLE_A);
+        // recurrent contraction on the panels the previous step left, then the cell kernel; h_t leaves as the layer
+        // output and as the operand panels of step s + 1
+        const Panels &ph_prev = P->h_pan[(s - 1) & 1];
+        const Panels &ph_next = P->h_pan[s & 1];
         Epilogue e;
-        LstmFuse f;
-        f.kind = 1;
+        LstmStep f;
         f.C = C; f.ldh = ldh; f.kp = ph_next.kp;
         f.peep = peep_c;
         if (s + 1 < T) { f.p_hi = ph_next.hi; f.p_cross = ph_next.lo; }
@@ -440,17 +458,12 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
         f.h = h_t;
         f.zone_state = zone ? D.zone_state + t * C : nullptr;
         f.zone_output = zone ? D.zone_output + t * C : nullptr;
-        if (P->fuse_mask & 1) {
-          e.lstm = f;
-          LRC(gemm_panels(ctx, ph_prev, 0, B, pwrec, 0, 4 * C, e));
-        } else {
-          e.C = P->s_rec;
-          e.ldc = 4 * C;
-          LRC(gemm_panels(ctx, ph_prev, 0, B, pwrec, 0, 4 * C, e));
-          ctx.begin(TC_RECURRENT);
-          launch_dependent(ctx, lstm_cells8_forward_kernel, dim3(cell_blocks8(B * C / 8)), dim3(cell_threads8(B * C / 8)), 0, f, static_cast<const float *>(P->s_rec), B);
-          ctx.end(TC_RECURRENT);
-        }
+        e.C = P->s_rec;
+        e.ldc = 4 * C;
+        LRC(gemm_panels(ctx, ph_prev, 0, B, pwrec, 0, 4 * C, e));
+        ctx.begin(TC_RECURRENT);
+        launch_dependent(ctx, lstm_cells8_forward_kernel, dim3(cell_blocks8(B * C / 8)), dim3(cell_threads8(B * C / 8)), 0, f, static_cast<const float *>(P->s_rec), B);
+        ctx.end(TC_RECURRENT);
         continue;
       }
       CellFwd cf;
@@ -481,10 +494,8 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
       ctx.begin(TC_RECURRENT);
       lstm_cell_forward_kernel<<<cell_blocks(B * C), 256, 0, ctx.stream>>>(cf);
       ctx.end(TC_RECURRENT);
-      if (P->fuse && T > 1) {  // first step: its output becomes the operand of the second step
-        Panels ph0;
-        LRC(gemm_prepare(ctx, Operand{h_t, B, C, ldh, 1}, P->h_panels[0], &ph0, PANEL_ROLE_A));
-      }
+      if (P->fuse && T > 1)  // first step: its output becomes the operand of the second step
+        LRC(gemm_prepare_into(ctx, Operand{h_t, B, C, ldh, 1}, P->h_pan[0], 0, 0));
     }
   }
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
@@ -511,14 +522,17 @@ int lstm_backward(myea_b200_net *net, LayerPlan &L) {
       const long long tn = d == 0 ? t + 1 : t - 1;     // the step after t in the layer's direction
       const long long tp = d == 0 ? t - 1 : t + 1;     // the step before t
       float *dh_t = L.deriv + t * B * ldh + d * C;
+      if (lstm_persistent_ready(P) && s > 0) {  // one launch walks the remaining steps
+        LRC(lstm_persistent_backward(net, L, d, pwt, P->peep_compact + static_cast<size_t>(d) * 3 * C));
+        break;
+      }
       if (P->fuse && s > 0) {
         // error through time (gate errors of the next step times W_rec) on the panels the previous step left, then the
         // cell's backward arithmetic; the gate errors of step t leave as arrays and as the next operand panels
-        const Panels pd_prev = panels_at(P->dg_panels[(s - 1) & 1], B, 4 * Cp, PANEL_ROLE_A);
-        const Panels pd_next = panels_at(P->dg_panels[s & 1], B, 4 * Cp, PANEL_ROLE_A);
+        const Panels &pd_prev = P->dg_pan[(s - 1) & 1];
+        const Panels &pd_next = P->dg_pan[s & 1];
         Epilogue e;
-        LstmFuse f;
-        f.kind = 2;
+        LstmStep f;
         f.C = C; f.ldh = ldh; f.kp = pd_next.kp; f.Cp = Cp;
         f.peep = P->peep_compact + static_cast<size_t>(d) * 3 * C;
         if (s + 1 < T) { f.p_hi = pd_next.hi; f.p_cross = pd_next.lo; }
@@ -531,18 +545,13 @@ int lstm_backward(myea_b200_net *net, LayerPlan &L) {
         f.dc_next = D.dcstate + tn * B * C;
         f.dgates = D.dgates + t * B * 4 * C;
         f.dcstate = D.dcstate + t * B * C;
-        if (P->fuse_mask & 2) {
-          e.lstm = f;
-          LRC(gemm_panels(ctx, pd_prev, 0, B, pwt, 0, C, e));
-        } else {
-          e.C = dh_t;
-          e.ldc = ldh;
-          e.accumulate = 1;
-          LRC(gemm_panels(ctx, pd_prev, 0, B, pwt, 0, C, e));
-          ctx.begin(TC_RECURRENT);
-          launch_dependent(ctx, lstm_cells8_backward_kernel, dim3(cell_blocks8(B * C / 8)), dim3(cell_threads8(B * C / 8)), 0, f, B);
-          ctx.end(TC_RECURRENT);
-        }
+        e.C = dh_t;
+        e.ldc = ldh;
+        e.accumulate = 1;
+        LRC(gemm_panels(ctx, pd_prev, 0, B, pwt, 0, C, e));
+        ctx.begin(TC_RECURRENT);
+        launch_dependent(ctx, lstm_cells8_backward_kernel, dim3(cell_blocks8(B * C / 8)), dim3(cell_threads8(B * C / 8)), 0, f, B);
+        ctx.end(TC_RECURRENT);
         continue;
       }
       if (s > 0) {
@@ -571,10 +580,8 @@ int lstm_backward(myea_b200_net *net, LayerPlan &L) {
       ctx.begin(TC_RECURRENT);
       lstm_cell_backward_kernel<<<cell_blocks(B * C), 256, 0, ctx.stream>>>(cb);
       ctx.end(TC_RECURRENT);
-      if (P->fuse && T > 1) {  // last time step (first of the walk): its gate errors are the operand of the next contraction
-        const Panels pd0 = panels_at(P->dg_panels[0], B, 4 * Cp, PANEL_ROLE_A);
-        LRC(prepare_gates(ctx, D.dgates + t * B * 4 * C, B, C, Cp, pd0));
-      }
+      if (P->fuse && T > 1)  // last time step (first of the walk): its gate errors are the operand of the next contraction
+        LRC(prepare_gates(ctx, D.dgates + t * B * 4 * C, B, C, Cp, P->dg_pan[0]));
     }
   }
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;

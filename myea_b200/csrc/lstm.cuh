@@ -17,6 +17,7 @@ struct LstmDir {
   uint8_t *zone_state = nullptr, *zone_output = nullptr;  // [T, C], 1 = compute, 0 = keep the previous value
 };
 
+struct LstmPersistent;
 struct LstmPlan {
   int dirs = 1;
   long long C = 0, n_in = 0, stride = 0;
@@ -26,29 +27,28 @@ struct LstmPlan {
   float *panel_mem = nullptr;  // W_rec panels, their transpose, per-step operand panels
   size_t off_wrec = 0, off_wrect = 0, off_step = 0;
   float *partial = nullptr;    // [7][chunks][C]
-  // cell fused into the recurrent contraction (C a multiple of 8, tensor-core engine): compact peepholes
-  // [dirs][3][C], ping-pong operand panels of h (forward) and of the gate errors (backward)
   bool shared_dw = false;  // weight derivatives from untransposed (column-read) operand panels
+  // `fuse` (C a multiple of 8, tensor-core engine): the cell arithmetic of a step also writes the next step's operand
+  // panels - ping-pong panels of h (forward) and of the gate errors (backward) - and reads compact peepholes
+  // [dirs][3][C].  All steps but the first then run in one persistent launch (`persist`, lstm_persistent.cu) when the
+  // layer's tiles fit the device at once, else as a contraction plus an 8-cells-per-thread cell kernel per step.
   bool fuse = false;
-  // With `fuse`, a step is two kernels: the contraction and an 8-cells-per-thread cell kernel that also writes the next
-  // operand panels.  fuse_mask (MYEA_B200_LSTM_FUSE) moves the cell into the contraction's epilogue instead: bit 0
-  // forward, bit 1 backward.  One kernel per step, but measured slower on C3 (the few threads that own accumulator
-  // rows walk their cells one memory round trip after the other), so it is off by default.
-  int fuse_mask = 0;
   float *peep_compact = nullptr;
-  float *h_panels[2] = {nullptr, nullptr};
-  float *dg_panels[2] = {nullptr, nullptr};
+  // both buffers of a ping-pong pair lie in one allocation, hi [2][rows][kp] then cross [2][rows][kp] with rows = the
+  // batch rounded up to 128, so that one tensor map covers both
+  Panels h_pan[2], dg_pan[2];
+  LstmPersistent *persist = nullptr;
 };
+
 
 // One launch that walks ALL remaining time steps of one layer and direction (lstm_persistent.cu): the recurrent
 // contraction of every step on the tensor cores, the cell arithmetic in its epilogue, the step's results written as the
-// next step's operand panels, and a bounded grid-wide barrier between steps.  `first_step` is the first step of the
-// walk this launch computes (the steps before it were computed by the per-step kernels and left their panels behind).
+// next step's operand panels, and a bounded grid-wide barrier between steps.  The first step of a walk has no predecessor
+// and is computed by the per-step kernels, which leave its panels behind.
 //   forward: steps s = 1 .. T-1 of direction `dir` (step s reads the h panels of buffer (s - 1) & 1)
 //   backward: steps s = 1 .. T-1 of the walk against the direction (step s reads the gate-error panels of (s - 1) & 1)
 // lstm_persistent_plan decides at creation whether the layer's shapes fit (every tile resident at once); the step
 // functions return MYEA_E_UNSUPPORTED when they do not apply and the caller takes the per-step path.
-struct LstmPersistent;
 int lstm_persistent_plan(myea_b200_net *net, LayerPlan &L);
 void lstm_persistent_destroy(LstmPlan *P);
 bool lstm_persistent_ready(const LstmPlan *P);

