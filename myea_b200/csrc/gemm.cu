@@ -184,10 +184,32 @@ __device__ __forceinline__ void epilogue_block32(const Epilogue &e, float *tr, c
   }
 }
 
+// The same block for arrays the vector path cannot take (bases or pitches that are not multiples of 16 bytes: the weight
+// derivatives of LSTM layers land inside the reference's per-block parameter layout, whose row pitch is odd) and for the
+// ragged right edge: staged through the same buffer, then lane l takes column col0 + l of one row after the other, so a
+// warp's accesses still cover one contiguous row segment each.
+__device__ __forceinline__ void epilogue_block32_rows(const Epilogue &e, float *tr, const float (&v)[32], int lane, long long row0, long long col0, int M, int N) {
+  const long long n = col0 + lane;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    __syncwarp();
+    if ((lane >> 4) == h) {
+      float *dst = tr + (lane & 15) * TR_PITCH;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) *reinterpret_cast<float4 *>(dst + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    }
+    __syncwarp();
+#pragma unroll 4
+    for (int r = 0; r < 16; ++r) {
+      const long long m = row0 + h * 16 + r;
+      if (m < M && n < N) e.C[c_row(e, m) + n] = epilogue_value(e, tr[r * TR_PITCH + lane], m, n);
+    }
+  }
+}
+
 // Warp-collective: every lane of the warp calls it (row0, col0, M, N are the same for all of them).
 __device__ __forceinline__ void epilogue_row32(const Epilogue &e, const float (&v)[32], long long row0, int lane, long long col0, int M, int N,
                                                bool vec_ok, int mode, float *tr) {
-  const long long m = row0 + lane;
   if (col0 >= N) return;
   if (vec_ok && col0 + 32 <= N) {
     switch (mode) {
@@ -196,12 +218,8 @@ __device__ __forceinline__ void epilogue_row32(const Epilogue &e, const float (&
       case 2: epilogue_block32<false, false, true>(e, tr, v, lane, row0, col0, M); break;
       default: epilogue_block32<true, true, true>(e, tr, v, lane, row0, col0, M); break;
     }
-  } else if (m < M) {  // ragged right edge or unaligned arrays: one element at a time, the thread keeps its row
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const long long n = col0 + j;
-      if (n < N) e.C[c_row(e, m) + n] = epilogue_value(e, v[j], m, n);
-    }
+  } else {
+    epilogue_block32_rows(e, tr, v, lane, row0, col0, M, N);
   }
 }
 

@@ -170,15 +170,27 @@ __global__ void __launch_bounds__(256) lstm_bias_peephole_reduce_kernel(const fl
   }
 }
 
-__global__ void lstm_bias_peephole_finalize_kernel(const float *__restrict__ partial, int chunks, long long C, float *d_bias,
-                                                   float *d_peep, long long stride) {
-  const long long c = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  if (c >= C) return;
+// 32 cells per block, the chunks of a sum spread over 8 threads per cell
+__global__ void __launch_bounds__(256) lstm_bias_peephole_finalize_kernel(const float *__restrict__ partial, int chunks, long long C, float *d_bias,
+                                                                          float *d_peep, long long stride) {
+  __shared__ float sh[7][8][33];
+  const int cl = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const long long c = static_cast<long long>(blockIdx.x) * 32 + cl;
+#pragma unroll
+  for (int k = 0; k < 7; ++k) {
+    float t = 0.f;
+    if (c < C)
+      for (int ch = rl; ch < chunks; ch += 8) t += partial[(static_cast<long long>(k) * chunks + ch) * C + c];
+    sh[k][rl][cl] = t;
+  }
+  __syncthreads();
+  if (rl != 0 || c >= C) return;
   float t[7];
 #pragma unroll
   for (int k = 0; k < 7; ++k) {
     t[k] = 0.f;
-    for (int ch = 0; ch < chunks; ++ch) t[k] += partial[(static_cast<long long>(k) * chunks + ch) * C + c];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t[k] += sh[k][r][cl];
   }
   // atomics: with the reference's shifted bias base the output-gate slots alias the next layer's bias slots, which another
   // kernel of the same stream also accumulates into; stream order already serialises them, the atomics are belt and braces
@@ -704,7 +716,7 @@ int lstm_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float 
     ctx.begin(TC_RECURRENT);
     dim3 grid(static_cast<unsigned>((C + 31) / 32), chunks);
     lstm_bias_peephole_reduce_kernel<<<grid, 256, 0, ctx.stream>>>(D.dgates, D.cstate, rows, C, d == 0 ? B : -B, chunks, P->partial);
-    lstm_bias_peephole_finalize_kernel<<<static_cast<unsigned>((C + 255) / 256), 256, 0, ctx.stream>>>(P->partial, chunks, C, net->grads + D.b_base,
+    lstm_bias_peephole_finalize_kernel<<<static_cast<unsigned>((C + 31) / 32), 256, 0, ctx.stream>>>(P->partial, chunks, C, net->grads + D.b_base,
                                                                                                     gw + off.peep, P->stride);
     ctx.end(TC_RECURRENT, 2);
   }

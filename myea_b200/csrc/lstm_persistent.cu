@@ -57,7 +57,12 @@ template <int KIND> struct PsSmem {
   static constexpr int RECV_BYTES = (PsShape<KIND>::SPLIT - 1) * 128 * (BN / PsShape<KIND>::SPLIT) * 4;  // one slot per peer
   static constexpr int BAR_OFFSET = RECV_OFFSET + RECV_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;                // barriers, peepholes, slack to align the base
-  static constexpr int TMEM_COLS = 3 * BN <= 256 ? 256 : 512;          // main 0, main 1, cross
+  // Accumulators in tensor memory, BN columns each, filled one after the other: every one takes the products of
+  // ACC_KB K blocks (or more when the K slice is longer than MAX_ACC of them), hi*hi and cross terms alike.  The tensor
+  // core truncates when it adds into an accumulator, so a chain of adds is kept to 64 instructions where the slice
+  // allows; and the exchange warps read an accumulator while the tensor core fills the next one.
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int MAX_ACC = TMEM_COLS / BN, ACC_KB = 8;
   static_assert(TOTAL <= 227 * 1024, "shared memory of one SM");
   static_assert(STAGE_BYTES % 1024 == 0 && B_BYTES % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
 };
@@ -165,8 +170,8 @@ lstm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid
   float *recv = reinterpret_cast<float *>(smem + SM::RECV_OFFSET);  // [S - 1 peers][128 rows][W]: partial sums pushed by the peers
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + SM::BAR_OFFSET);
   uint64_t *empty_bar = full_bar + STAGES;
-  uint64_t *acc_full = empty_bar + STAGES;   // the step's MMAs of this CTA are complete
-  uint64_t *acc_empty = acc_full + 1;        // the 8 exchange warps have read tensor memory
+  uint64_t *acc_full = empty_bar + STAGES;   // [MAX_ACC] accumulator a of the step is complete
+  uint64_t *acc_empty = acc_full + SM::MAX_ACC;  // the 8 exchange warps have read tensor memory
   uint64_t *red_ready = acc_empty + 1;       // every exchange warp of every peer has pushed its partial sums for this CTA
   uint64_t *step_go = red_ready + 1;         // the producer has passed the step barrier
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(step_go + 1);
@@ -180,6 +185,8 @@ lstm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid
   const int m0 = tile_m * 128, n0 = tile_n * BN;
   const int kb0 = min(static_cast<int>(rank) * q.kb_per, q.num_kb), kb1 = min(kb0 + q.kb_per, q.num_kb);
   const int my_kb = kb1 - kb0;
+  const int acc_kb = max(SM::ACC_KB, (q.kb_per + SM::MAX_ACC - 1) / SM::MAX_ACC);  // K blocks per accumulator
+  const int nacc = (my_kb + acc_kb - 1) / acc_kb;                                    // accumulators this CTA fills per step
   unsigned int *counter = q.sync + tile_m;
   unsigned int *abort_word = q.sync + q.tiles_m;
   const unsigned int per_step = static_cast<unsigned int>(q.tiles_n * S);  // CTAs that complete a row of tiles
@@ -189,7 +196,7 @@ lstm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid
       ptx::mbar_init(&full_bar[s], 1);
       ptx::mbar_init(&empty_bar[s], 1);
     }
-    ptx::mbar_init(acc_full, 1);
+    for (int a = 0; a < SM::MAX_ACC; ++a) ptx::mbar_init(&acc_full[a], 1);
     ptx::mbar_init(acc_empty, 8);
     ptx::mbar_init(red_ready, static_cast<uint32_t>(8 * (S - 1)));
     ptx::mbar_init(step_go, 1);
@@ -251,11 +258,7 @@ lstm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid
           if (!ptx::mbar_wait_or_abort(acc_empty, static_cast<uint32_t>(s - 2) & 1u, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after();
         }
-        if (my_kb == 0) {  // an empty K slice (short K): nothing to add, the exchange warps take zeros
-          ptx::mbar_arrive_local(acc_full);
-          continue;
-        }
-        int step = 0;
+        int in_acc = 0, acc = 0;  // K blocks issued into the current accumulator, its index
         for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
           const int st = static_cast<int>(it % STAGES);
           const uint32_t ph = (it / STAGES) & 1u;
@@ -264,17 +267,20 @@ lstm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid
           const uint32_t base = ptx::smem_u32(smem + st * SM::STAGE_BYTES);
           const uint64_t a_hi = make_smem_desc(base), a_x = make_smem_desc(base + PS_TILE_BYTES);
           const uint64_t b_hi = make_smem_desc(base + 2 * PS_TILE_BYTES), b_x = make_smem_desc(base + 2 * PS_TILE_BYTES + SM::B_BYTES);
+          const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * BN);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k, ++step) {
+          for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t koff = static_cast<uint64_t>((k * UMMA_K * 4) >> 4);
-            // two main accumulators in turn: the tensor core truncates when it adds into an accumulator, so the chains
-            // of dominant products are kept short; the small cross terms have one of their own
-            ptx::mma_bf16(tmem_base + static_cast<uint32_t>(2 * BN), a_x + koff, b_x + koff, idesc_cross, step > 0 ? 1u : 0u);
-            ptx::mma_tf32(tmem_base + static_cast<uint32_t>((step & 1) * BN), a_hi + koff, b_hi + koff, idesc_main, step >= 2 ? 1u : 0u);
+            ptx::mma_bf16(t_acc, a_x + koff, b_x + koff, idesc_cross, (in_acc > 0 || k > 0) ? 1u : 0u);  // lo*hi + hi*lo
+            ptx::mma_tf32(t_acc, a_hi + koff, b_hi + koff, idesc_main, 1u);                                  // hi*hi
           }
           ptx::tc_commit(&empty_bar[st]);
+          if (++in_acc == acc_kb || kb + 1 == kb1) {
+            ptx::tc_commit(&acc_full[acc]);
+            ++acc;
+            in_acc = 0;
+          }
         }
-        if (ok) ptx::tc_commit(acc_full);
       }
       if (!ok) {
         atomicCAS(q.error_flag, 0, 402);
@@ -342,45 +348,40 @@ lstm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid
         if (ok && active) store_arrays(s - 1);
         pending = false;
       }
-      if (ok && !ptx::mbar_wait_or_abort(acc_full, static_cast<uint32_t>(s - 1) & 1u, abort_flag)) ok = false;
-      ptx::tc_fence_after();
-      float own[HW];
-      if (ok) {
-        // Partial sums of this CTA's K slice: for every CTA d of the cluster the columns of d's cells that belong to this
-        // thread's (row, half); the peers' shares are pushed into their receive slots, this CTA's own share stays here.
+      // Partial sums of this CTA's K slice: for every CTA d of the cluster the columns of d's cells that belong to this
+      // thread's (row, half), added up over the accumulators as the tensor core completes them (part[S - 1] is this
+      // CTA's own share, the others go to the peers in the order rank + 1, rank + 2, ...)
+      float part[S][HW];
+#pragma unroll
+      for (int dd = 0; dd < S; ++dd)
+#pragma unroll
+        for (int j = 0; j < HW; ++j) part[dd][j] = 0.f;
+      for (int a = 0; a < nacc && ok; ++a) {
+        if (!ptx::mbar_wait_or_abort(&acc_full[a], static_cast<uint32_t>(s - 1) & 1u, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after();
 #pragma unroll
         for (int dd = 1; dd <= S; ++dd) {
           const int d = (static_cast<int>(rank) + dd) % S;
-          float sum[HW];
-          if (my_kb > 0) {
-            uint32_t r0[HW], r1[HW], r2[HW];
-            const uint32_t t0 = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + static_cast<uint32_t>(d * W + half * HW);
-            if constexpr (HW == 32) {
-              ptx::tmem_ld_32x32(t0 + static_cast<uint32_t>(2 * BN), r0);
-              ptx::tmem_ld_32x32(t0, r1);
-              ptx::tmem_ld_32x32(t0 + static_cast<uint32_t>(BN), r2);
-            } else {
-              ptx::tmem_ld_32x8(t0 + static_cast<uint32_t>(2 * BN), r0);
-              ptx::tmem_ld_32x8(t0, r1);
-              ptx::tmem_ld_32x8(t0 + static_cast<uint32_t>(BN), r2);
-            }
-            ptx::tmem_ld_wait();
+          uint32_t r[HW];
+          const uint32_t t0 = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + static_cast<uint32_t>(a * BN + d * W + half * HW);
+          if constexpr (HW == 32) ptx::tmem_ld_32x32(t0, r);
+          else ptx::tmem_ld_32x8(t0, r);
+          ptx::tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < HW; ++j) sum[j] = (__uint_as_float(r0[j]) + __uint_as_float(r1[j])) + __uint_as_float(r2[j]);
-          } else {
+          for (int j = 0; j < HW; ++j) part[dd - 1][j] += __uint_as_float(r[j]);
+        }
+      }
+      if (ok) {
+        // the peers' shares are pushed into their receive slots, this CTA's own share stays in registers
 #pragma unroll
-            for (int j = 0; j < HW; ++j) sum[j] = 0.f;
-          }
-          if (dd < S) {
-            const int slot = static_cast<int>(rank) < d ? static_cast<int>(rank) : static_cast<int>(rank) - 1;
-            const uint32_t dst = ptx::map_to_cta(recv_addr + static_cast<uint32_t>((slot * 128 + row) * W * 4), static_cast<uint32_t>(d));
+        for (int dd = 1; dd < S; ++dd) {
+          const int d = (static_cast<int>(rank) + dd) % S;
+          const int slot = static_cast<int>(rank) < d ? static_cast<int>(rank) : static_cast<int>(rank) - 1;
+          const uint32_t dst = ptx::map_to_cta(recv_addr + static_cast<uint32_t>((slot * 128 + row) * W * 4), static_cast<uint32_t>(d));
 #pragma unroll
-            for (int i = 0; i < HW / 4; ++i)
-              ptx::st_cluster_f4(dst + (static_cast<uint32_t>((half * (HW / 4) + i) ^ swz) << 4), make_float4(sum[4 * i], sum[4 * i + 1], sum[4 * i + 2], sum[4 * i + 3]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < HW; ++j) own[j] = sum[j];
-          }
+          for (int i = 0; i < HW / 4; ++i)
+            ptx::st_cluster_f4(dst + (static_cast<uint32_t>((half * (HW / 4) + i) ^ swz) << 4),
+                               make_float4(part[dd - 1][4 * i], part[dd - 1][4 * i + 1], part[dd - 1][4 * i + 2], part[dd - 1][4 * i + 3]));
         }
         ptx::tc_fence_before();
         __syncwarp();
@@ -400,7 +401,7 @@ lstm_persistent_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid
         for (int j = 0; j < S; ++j) {
           if (j == static_cast<int>(rank)) {
 #pragma unroll
-            for (int i = 0; i < HW; ++i) rec[i] += own[i];
+            for (int i = 0; i < HW; ++i) rec[i] += part[S - 1][i];
           } else {
             const int slot = j < static_cast<int>(rank) ? j : j - 1;
             const float *src = recv + (slot * 128 + row) * W;
