@@ -1,12 +1,16 @@
 #!/usr/bin/env python
 """Throughput of one full training step (forward, output error, backward, derivative-weight accumulation, optimizer
 update) on the wide-MLP workload: 8 x FC 4096 + BatchNorm + ReLU + inverted dropout 0.5, FC 4096 -> 1024, MSE, Adam,
-global batch 4096, fp32 (3xTF32 tensor-core contractions), synthetic seeded data.
+GLOBAL batch 4096, fp32 (split-precision tensor-core contractions), synthetic seeded data.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c3|c4|c5]
+    python bench.py --gemm M N K [--steps K]          one contraction through the C ABI (error against float64 + timing)
 
-N > 1 is launched by torchrun, one rank per GPU; the global batch is split over the ranks (strong scaling), gradients
-are summed with NCCL and batch-norm statistics are synchronised so that the result equals the one-GPU step.
+N > 1 is launched by torchrun, one rank per GPU.  The global batch of the configuration is SHARDED over the ranks
+(strong scaling, as the configuration states it): every rank runs the step on 1/N of the rows, derivatives are summed
+with NCCL and batch-norm statistics are synchronised, so the result equals the one-GPU step.  The line also carries,
+under extra keys, the same step with the configuration's batch PER GPU (weak scaling), a correctness check of the
+data-parallel path (`dp_check`), and at N = 1 the other recurrent workload (`other_workloads`).
 Prints ONE JSON line.  `value` is measured with inputs resident in HBM; `e2e` goes through the host-buffer entry
 points (host -> device copy of inputs and targets and a device -> host read of the loss inside the timed region).
 `--impl reference` times the reference's own CPU/OpenMP implementation (compiled into oracle/_ref) on the host cores,
@@ -19,12 +23,14 @@ import os
 import subprocess
 import sys
 import threading
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 import numpy as np  # noqa: E402
+
+CLASS_NAMES = ["gemm", "split", "normalization", "elementwise", "optimizer", "recurrent", "comm", "other"]
+CPU_SAMPLE_ROWS = {"c2": 64, "c1": 128, "c3": 16, "c4": 64, "c5": 4}
 
 
 def _peaks():
@@ -84,15 +90,6 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_workload(name, world, global_batch=None):
-    from myea_b200 import workloads
-    # weak scaling: every GPU keeps the workload's own batch; --global-batch fixes the total instead (strong scaling)
-    wl = workloads.BUILDERS[name]()
-    if global_batch is not None:
-        wl = workloads.BUILDERS[name](batch=max(1, global_batch // world))
-    return wl, wl.B * world
-
-
 def cpu_reference_run(wl_name, steps, warmup, sample_batch, threads):
     """samples/s of the compiled reference on `sample_batch` rows of the workload"""
     from myea_b200 import workloads
@@ -110,172 +107,297 @@ def cpu_reference_run(wl_name, steps, warmup, sample_batch, threads):
 
 
 def run_reference(args):
+    from myea_b200 import workloads
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = min(os.cpu_count() or 1, 32)
-    sample = {"c2": 64, "c1": 128, "c3": 16, "c4": 64, "c5": 4}[args.workload]
+    sample = CPU_SAMPLE_ROWS[args.workload]
     steps = max(1, min(args.steps, 3))
     warm = 1 if args.warmup > 0 else 0
     r = cpu_reference_run(args.workload, steps, warm, sample, threads)
-    wl, gb = build_workload(args.workload, 1)
+    wl = workloads.BUILDERS[args.workload]()
     if r is None:
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libmyea_ref.so was not built (no reference checkout at build time)"}))
         return
     line = {"impl": "reference", "metric": "train samples/sec (fwd+bwd+update)", "value": r["value"], "unit": "samples/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl.name, "global_batch": gb, "sample_batch": sample},
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": wl.name, "global_batch": wl.B, "sample_batch": sample},
             "cpu_baseline": {"value": r["value"], "unit": "samples/s", "cores": r["cores"], "kind": "reference",
                              "sample": "%d rows of the workload per step, %d timed steps, reference OpenMP path" % (sample, steps)},
             "e2e": {"value": r["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
-def run_ours(args):
-    import torch
-    from myea_b200 import capi
-    from myea_b200.net import Net
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("--gpus %d needs torchrun with %d ranks" % (args.gpus, args.gpus))
-    torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    wl, global_batch = build_workload(args.workload, world, args.global_batch)
-    net = Net(wl.desc, wl.opt, device=local)
-    wl.materialize(net)
-    lib = net.lib
-    if world > 1:
-        uid = torch.zeros(128, dtype=torch.uint8)
-        if rank == 0:
-            buf = (C.c_uint8 * 128)()
-            rc = lib.myea_b200_comm_unique_id(buf)
-            if rc != 0:
-                raise RuntimeError("comm_unique_id failed")
-            uid = torch.tensor(list(buf), dtype=torch.uint8)
-        uid = uid.cuda()
-        dist.broadcast(uid, 0)
-        idb = (C.c_uint8 * 128)(*uid.cpu().tolist())
-        net._ck(lib.myea_b200_comm_init(net.h, world, rank, idb), "comm_init")
-    # this rank's shard of the global batch (rank r owns rows [r*B, (r+1)*B) of every time step)
-    Xg, Yg = wl.batch(rows=wl.B * world)
-    X = np.ascontiguousarray(Xg[:, rank * wl.B:(rank + 1) * wl.B])
-    Y = np.ascontiguousarray(Yg[:, rank * wl.B:(rank + 1) * wl.B])
-    Xh, Yh = torch.from_numpy(X).pin_memory(), torch.from_numpy(Y).pin_memory()
-    Xd, Yd = Xh.cuda(), Yh.cuda()
-    stream = torch.cuda.ExternalStream(int(lib.myea_b200_stream(net.h)))
-    h, B, opt = net.h, wl.B, C.byref(wl.opt)
-    N_train = global_batch
+class Job:
+    """one network on this rank's GPU for its shard of a global batch, joined to the other ranks when there are any"""
 
-    def step_device():
-        lib.myea_b200_forward_device(h, B, Xd.data_ptr(), 1)
-        lib.myea_b200_compute_error_device(h, B, Yd.data_ptr())
-        lib.myea_b200_backward(h, B)
-        lib.myea_b200_update_derivative_weight(h, B)
-        return lib.myea_b200_update_parameter(h, global_batch, N_train, opt)
+    def __init__(self, torch, dist, workload, per_gpu_batch, world, rank, local, scale=None, **kw):
+        from myea_b200 import workloads
+        from myea_b200.net import Net
+        self.torch, self.dist, self.world, self.rank = torch, dist, world, rank
+        build = workloads.BUILDERS[workload]
+        self.wl = build(batch=per_gpu_batch, **kw) if scale is None else build(scale=scale, batch=per_gpu_batch, **kw)
+        self.global_batch = per_gpu_batch * world
+        self.net = Net(self.wl.desc, self.wl.opt, device=local)
+        self.wl.materialize(self.net)
+        self.lib = self.net.lib
+        if world > 1:
+            uid = torch.zeros(128, dtype=torch.uint8)
+            if rank == 0:
+                buf = (C.c_uint8 * 128)()
+                if self.lib.myea_b200_comm_unique_id(buf) != 0:
+                    raise RuntimeError("comm_unique_id failed")
+                uid = torch.tensor(list(buf), dtype=torch.uint8)
+            uid = uid.cuda()
+            dist.broadcast(uid, 0)
+            idb = (C.c_uint8 * 128)(*uid.cpu().tolist())
+            self.net._ck(self.lib.myea_b200_comm_init(self.net.h, world, rank, idb), "comm_init")
+        # this rank's rows of the global batch (rank r owns rows [r*B, (r+1)*B) of every time step)
+        B = self.wl.B
+        Xg, Yg = self.wl.batch(rows=self.global_batch)
+        self.X = np.ascontiguousarray(Xg[:, rank * B:(rank + 1) * B])
+        self.Y = np.ascontiguousarray(Yg[:, rank * B:(rank + 1) * B])
+        self.Xg, self.Yg = (Xg, Yg) if rank == 0 else (None, None)
+        self.Xh, self.Yh = torch.from_numpy(self.X).pin_memory(), torch.from_numpy(self.Y).pin_memory()
+        self.Xd, self.Yd = self.Xh.cuda(), self.Yh.cuda()
+        self.stream = torch.cuda.ExternalStream(int(self.lib.myea_b200_stream(self.net.h)))
 
-    def step_host():
-        lib.myea_b200_reset_loss(h)
-        lib.myea_b200_forward(h, B, Xh.data_ptr(), 1)
-        lib.myea_b200_compute_error(h, B, Yh.data_ptr())
-        lib.myea_b200_backward(h, B)
-        lib.myea_b200_update_derivative_weight(h, B)
-        rc = lib.myea_b200_update_parameter(h, global_batch, N_train, opt)
-        s, n, a = C.c_double(), C.c_uint64(), C.c_double()
-        lib.myea_b200_get_loss(h, C.byref(s), C.byref(n), C.byref(a))  # device -> host read of the step's loss
+    def step_device(self):
+        lib, h, B, gb = self.lib, self.net.h, self.wl.B, self.global_batch
+        rc = lib.myea_b200_forward_device(h, B, self.Xd.data_ptr(), 1)
+        rc |= lib.myea_b200_compute_error_device(h, B, self.Yd.data_ptr())
+        rc |= lib.myea_b200_backward(h, B)
+        rc |= lib.myea_b200_update_derivative_weight(h, B)
+        rc |= lib.myea_b200_update_parameter(h, gb, gb, C.byref(self.wl.opt))
         return rc
 
-    def timed(fn, steps, warmup):
+    def step_host(self):
+        lib, h, B, gb = self.lib, self.net.h, self.wl.B, self.global_batch
+        rc = lib.myea_b200_reset_loss(h)
+        rc |= lib.myea_b200_forward(h, B, self.Xh.data_ptr(), 1)
+        rc |= lib.myea_b200_compute_error(h, B, self.Yh.data_ptr())
+        rc |= lib.myea_b200_backward(h, B)
+        rc |= lib.myea_b200_update_derivative_weight(h, B)
+        rc |= lib.myea_b200_update_parameter(h, gb, gb, C.byref(self.wl.opt))
+        s, n, a = C.c_double(), C.c_uint64(), C.c_double()
+        rc |= lib.myea_b200_get_loss(h, C.byref(s), C.byref(n), C.byref(a))  # device -> host read of the step's loss
+        return rc
+
+    def timed(self, fn, steps, warmup):
+        """(milliseconds for `steps` steps: device time on the library's stream, max over ranks; launches)"""
+        torch, dist, net = self.torch, self.dist, self.net
         for _ in range(warmup):
             if fn() != 0:
-                raise RuntimeError("step failed: " + lib.myea_b200_last_error(h).decode())
+                raise RuntimeError("step failed: " + self.lib.myea_b200_last_error(net.h).decode())
         net.synchronize()
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = net.launches()
-        e0.record(stream)
+        rc = 0
+        e0.record(self.stream)
         for _ in range(steps):
-            fn()
-        e1.record(stream)
+            rc |= fn()
+        e1.record(self.stream)
         e1.synchronize()
         torch.cuda.synchronize()
+        if rc != 0:   # a step that failed on the host side would otherwise count as a very fast one
+            raise RuntimeError("a timed step failed: " + self.lib.myea_b200_last_error(net.h).decode())
         ms = e0.elapsed_time(e1)
         if dist is not None:
             t = torch.tensor([ms], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dist.barrier()
             ms = float(t.item())
-        net.synchronize()
+        net.synchronize()   # raises when a kernel gave up a bounded wait
         return ms, net.launches() - l0
 
+    def classes(self, steps):
+        """per-class device time of `steps` steps (events around every launch: the steps run serialised)"""
+        net = self.net
+        net.profile(True)
+        net.profile_read(reset=True)
+        for _ in range(steps):
+            self.step_device()
+        net.synchronize()
+        cls_ms, cls_n, gemm_flops = net.profile_read(reset=True)
+        net.profile(False)
+        return cls_ms, gemm_flops
+
+    def close(self):
+        self.net.close()
+
+
+def dp_check(torch, dist, world, rank, local, timed_job):
+    """correctness of the data-parallel path, on every run with more than one rank:
+    (1) the parameter buffers of the timed job are identical on all ranks after the timed steps (bitwise: every rank
+        applied the same update to the same sums), (2) two steps of a small network sharded over the ranks equal the same
+        two steps on ONE rank with the whole batch, within the parity tolerance"""
+    from myea_b200 import capi
+    p = torch.from_numpy(timed_job.net.get(capi.BUF_PARAMETERS)).cuda()
+    hi, lo = p.clone(), p.clone()
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    spread = float((hi - lo).abs().max().item())
+    del p, hi, lo
+    small = Job(torch, dist, "c2", 64, world, rank, local, scale=1.0 / 16, hidden_layers=3)
+    for _ in range(2):
+        if small.step_host() != 0:
+            raise RuntimeError("dp_check step failed")
+    small.net.synchronize()
+    got = small.net.get(capi.BUF_PARAMETERS)
+    out = {"parameter_spread_across_ranks": spread}
+    if rank == 0:
+        from myea_b200 import workloads
+        from myea_b200.net import Net
+        wl = workloads.c2_wide_mlp(scale=1.0 / 16, batch=64 * world, hidden_layers=3)
+        one = Net(wl.desc, wl.opt, device=local)
+        wl.materialize(one)
+        for _ in range(2):
+            one.reset_loss(); one.forward(small.Xg); one.compute_error(small.Yg); one.backward(); one.update_derivative_weight(); one.update_parameter()
+        want = one.get(capi.BUF_PARAMETERS)
+        one.close()
+        out["sharded_vs_one_rank_rel_err"] = float(np.abs(got - want).max() / np.abs(want).max())
+        out["network"] = "C2 at 1/16 width, 3 hidden layers, global batch %d, 2 steps" % (64 * world)
+    small.close()
+    return out
+
+
+def run_ours(args):
+    import torch
+    from myea_b200 import workloads
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("--gpus %d needs torchrun with %d ranks" % (args.gpus, args.gpus))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    full = workloads.BUILDERS[args.workload]()
+    global_batch = args.global_batch or full.B
+    if global_batch % world != 0:
+        raise SystemExit("the global batch %d does not divide over %d ranks" % (global_batch, world))
+    kw = {"hidden_layers": args.hidden_layers} if args.hidden_layers else {}
+    job = Job(torch, dist, args.workload, global_batch // world, world, rank, local, **kw)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms_dev, launches = timed(step_device, args.steps, args.warmup)
+    ms_dev, launches = job.timed(job.step_device, args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
-    ms_e2e, _ = timed(step_host, args.steps, max(1, args.warmup // 2))
-    # kernel-class timing pass (CUDA events around every launch on the library's stream): the GEMM roofline figure
-    net.profile(True)
-    net.profile_read(reset=True)
-    for _ in range(max(1, min(args.steps, 3))):
-        step_device()
-    net.synchronize()
-    cls_ms, cls_n, gemm_flops = net.profile_read(reset=True)
-    net.profile(False)
+    ms_e2e, _ = job.timed(job.step_host, args.steps, max(1, args.warmup // 2))
+    cls_steps = max(1, min(args.steps, 3))
+    cls_ms, gemm_flops = job.classes(cls_steps)
+    check = dp_check(torch, dist, world, rank, local, job) if world > 1 else None
+    wl = job.wl
+    X_bytes, Y_bytes = int(job.X.nbytes), int(job.Y.nbytes)
+    job.close()
+    del job
+    weak = None
+    if world > 1 and not args.no_extra:
+        # the same step with the configuration's batch on EVERY GPU (weak scaling), for comparison
+        wjob = Job(torch, dist, args.workload, full.B, world, rank, local, **kw)
+        wms, _ = wjob.timed(wjob.step_device, args.steps, args.warmup)
+        weak = {"value": wjob.global_batch / (wms / args.steps / 1e3), "unit": "samples/s", "ms_per_step": wms / args.steps,
+                "global_batch": wjob.global_batch, "per_gpu_batch": full.B, "scaling": "weak"}
+        wjob.close()
+        del wjob
+    others = {}
+    if world == 1 and args.workload == "c2" and not args.no_extra:
+        # the recurrent configuration the throughput target also names, timed after the headline workload
+        for name, steps in (("c3", max(3, min(args.steps, 10))),):
+            oj = Job(torch, dist, name, workloads.BUILDERS[name]().B, 1, 0, local)
+            oms, ol = oj.timed(oj.step_device, steps, 3)
+            oe2e, _ = oj.timed(oj.step_host, steps, 1)
+            ocls, oflops = oj.classes(2)
+            others[name] = {"workload": oj.wl.name, "global_batch": oj.global_batch, "steps": steps, "ms_per_step": oms / steps,
+                            "value": oj.global_batch / (oms / steps / 1e3), "unit": "samples/s",
+                            "e2e": {"value": oj.global_batch / (oe2e / steps / 1e3), "unit": "samples/s"},
+                            "gpu_launches": int(ol), "step_tflops": oj.wl.flops_per_step / (oms / steps / 1e3) / 1e12,
+                            "kernel_classes_ms_per_step": {n: m / 2 for n, m in zip(CLASS_NAMES, ocls) if m > 0}}
+            oj.close()
+            del oj
     peaks = _peaks()
     if rank == 0:
         per_step = ms_dev / args.steps
         value = global_batch / (per_step / 1e3)
         e2e_value = global_batch / ((ms_e2e / args.steps) / 1e3)
         gemm_tflops = gemm_flops / (cls_ms[0] / 1e3) / 1e12 if cls_ms[0] > 0 else 0.0
-        peak = peaks["bf16_tflops_sustained"]
-        names = ["gemm", "split", "normalization", "elementwise", "optimizer", "recurrent", "comm", "other"]
+        peak, burst = peaks["bf16_tflops_sustained"], peaks["bf16_tflops"]
         line = {
             "metric": "train samples/sec (fwd+bwd+update)", "value": value, "unit": "samples/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True,
-            "scaling": "weak" if args.global_batch is None else "strong", "vs_baseline": None,
+            "scaling": "strong", "vs_baseline": None,
             "dtype": "f32 (split-precision tensor-core products: TF32 hi*hi + BF16 cross terms, fp32 accumulate)",
             "data": "synthetic",
             "config": {"workload": wl.name, "global_batch": global_batch, "per_gpu_batch": wl.B,
-                       "parallelism": "dp%d" % world, "l2": "per-step working set (> 6 GB) far exceeds the 126 MB L2"},
+                       "parallelism": "dp%d" % world, "l2": "per-step working set (> 6 GB at one GPU) far exceeds the 126 MB L2"},
             "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": int(X.nbytes + Y.nbytes) * world,
+            "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": (X_bytes + Y_bytes) * world,
                     "d2h_bytes_per_step": 24 * world},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "achieved": gemm_tflops, "peak": peak, "unit": "TFLOP/s",
                          "frac": gemm_tflops / peak if peak else None,
-                         # DRAM bytes of ONE launch of the dominant kernel on the 4096^3 contraction of this workload, from
-                         # the committed ncu capture (dram__bytes_read.sum + dram__bytes_write.sum); algorithmic 335 MB
+                         # DRAM bytes of ONE launch of the dominant kernel on the 4096^3 contraction of this workload
+                         # (dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture summarised under profiles/;
+                         # algorithmic: 335 MB)
                          "traffic": 704.7e6 if args.workload == "c2" else None,
+                         "traffic_source": "profiles/gemm3x_tf32_tcgen05_wide_4096x4096x4096.md" if args.workload == "c2" else None,
                          "kernel": "gemm3x_tf32_tcgen05_wide_kernel", "peak_source": peaks["source"] + " bf16 sustained",
                          # every fp32 product costs one TF32 and one BF16 K=16 instruction of equal duration: the
-                         # scheme's own ceiling is a quarter of the bf16 peak
+                         # scheme's own ceiling is a quarter of the bf16 peak (sustained: inside a step; burst: alone)
                          "scheme_ceiling": peak / 4.0, "frac_of_scheme_ceiling": gemm_tflops / (peak / 4.0),
+                         "scheme_ceiling_burst": burst / 4.0, "frac_of_scheme_ceiling_burst": gemm_tflops / (burst / 4.0),
                          "step_tflops": wl.flops_per_step * world / (per_step / 1e3) / 1e12},
-            "kernel_classes_ms_per_step": {n: m / max(1, min(args.steps, 3)) for n, m in zip(names, cls_ms) if m > 0},
+            "kernel_classes_ms_per_step": {n: m / cls_steps for n, m in zip(CLASS_NAMES, cls_ms) if m > 0},
         }
+        if check is not None:
+            line["dp_check"] = check
+        if weak is not None:
+            line["weak_scaling"] = weak
+        if others:
+            line["other_workloads"] = others
         if world == 1 and not args.no_cpu:
             try:
                 threads = min(os.cpu_count() or 1, 32)
-                sample = {"c2": 64, "c1": 128, "c3": 16, "c4": 64, "c5": 4}[args.workload]
-                r = cpu_reference_run(args.workload, 2, 1, sample, threads)
+                sample = CPU_SAMPLE_ROWS[args.workload]
+                r = cpu_reference_run(args.workload, 3, 1, sample, threads)
                 if r is not None:
                     line["cpu_baseline"] = {"value": r["value"], "unit": "samples/s", "cores": r["cores"], "kind": "reference",
-                                            "sample": "%d rows of the workload per step, 2 timed steps after 1 warm-up, reference OpenMP path" % sample}
+                                            "sample": "%d rows of the workload per step, 3 timed steps after 1 warm-up, reference OpenMP path" % sample}
             except Exception as exc:  # the baseline is reported, never required for the GPU number
                 line["cpu_baseline"] = {"value": None, "unit": "samples/s", "cores": 0, "kind": "reference", "sample": "failed: %s" % exc}
         print(json.dumps(line))
-    net.close()
     if dist is not None:
         dist.destroy_process_group()
+
+
+def run_gemm(args):
+    """one contraction C = A B^T through myea_b200_gemm_nt: error against a float64 product and, with --steps, timing"""
+    from myea_b200 import capi
+    M, N, K = args.gemm
+    lib = capi.load()
+    rng = np.random.default_rng(0)
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    B = rng.standard_normal((N, K), dtype=np.float32)
+    out = np.zeros((M, N), np.float32)
+    ms = C.c_float(0)
+    rc = lib.myea_b200_gemm_nt(0, args.engine, M, N, K, A.ctypes.data, B.ctypes.data, out.ctypes.data, 0, C.byref(ms), args.steps)
+    if rc != 0:
+        raise SystemExit("myea_b200_gemm_nt failed with status %d" % rc)
+    line = {"gemm": [M, N, K], "engine_flags": args.engine}
+    if M * N * K <= 2 ** 37:
+        want = A.astype(np.float64) @ B.astype(np.float64).T
+        line["max_error_over_max_abs"] = float(np.abs(out - want).max() / np.abs(want).max())
+    if args.steps > 0:
+        line["ms_per_contraction_with_operand_splits"] = ms.value
+        line["tflops"] = 2.0 * M * N * K / (ms.value * 1e-3) / 1e12
+    print(json.dumps(line))
 
 
 def main():
@@ -285,11 +407,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
-    ap.add_argument("--global-batch", type=int, default=None)
+    ap.add_argument("--global-batch", type=int, default=None, help="override the configuration's global batch")
+    ap.add_argument("--hidden-layers", type=int, default=None, help="c2 only: fewer hidden layers (small captures for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the weak-scaling and other-workload legs")
+    ap.add_argument("--gemm", type=int, nargs=3, metavar=("M", "N", "K"), default=None)
+    ap.add_argument("--engine", type=int, default=0, help="--gemm only: engine / tile flags of myea_b200_gemm_nt")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
-    if args.impl == "reference":
+    if args.gemm is not None:
+        run_gemm(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -288,7 +288,13 @@ int myea_b200_get_errors(myea_handle h, uint32_t layer, float *host, uint64_t co
 
 /* Merge_Derivatives_Parameters (Neural_Network__Merge.cpp:20-50) across GPUs: attach this handle to an NCCL
  * communicator of `world` ranks. `unique_id` is the 128-byte ncclUniqueId made by rank 0
- * (myea_b200_comm_unique_id) and carried to the other ranks by the caller. */
+ * (myea_b200_comm_unique_id) and carried to the other ranks by the caller.
+ * With a communicator every rank runs the step on its rows of the batch; update_derivative_weight hands each layer's
+ * derivatives to the communicator (reduce-scatter where the range divides evenly over the ranks and the update is
+ * element by element, else all-reduce), update_parameter updates this rank's slices and gathers the updated parameters,
+ * so that all ranks hold identical parameters afterwards.  The optimizer state (moments, previous deltas) of a slice
+ * lives on the rank that owns it: myea_b200_download of such a buffer gathers the slices first and is therefore
+ * COLLECTIVE - every rank has to make the call. */
 int myea_b200_comm_unique_id(uint8_t id_out[128]);
 int myea_b200_comm_init(myea_handle h, int world, int rank, const uint8_t unique_id[128]);
 

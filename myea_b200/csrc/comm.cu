@@ -1,9 +1,13 @@
 // Data-parallel plumbing: one handle per GPU, each on its shard of the batch, joined by an NCCL communicator.
 //
 // What is exchanged is exactly what the reference merges across its OpenMP threads: the per-thread derivative slices
-// summed by Merge_Derivatives_Parameters (Neural_Network__Merge.cpp:20-50) become an all-reduce(sum) of the flat
+// summed by Merge_Derivatives_Parameters (Neural_Network__Merge.cpp:20-50) become a sum over the ranks of the flat
 // derivative buffer, issued in per-layer buckets on a second stream as soon as a layer's weight derivative is complete so
-// that it overlaps the remaining layers; the per-thread partial sums of the batch-normalization statistics
+// that it overlaps the remaining layers.  A bucket whose size divides evenly is REDUCE-SCATTERED: every rank receives the
+// sum of its 1/world slice only, runs the optimizer on that slice (the update is element by element) and the updated
+// parameters are ALL-GATHERED - the same bytes on the wire as an all-reduce, 1/world of the optimizer's memory traffic
+// per rank.  Other buckets (and every bucket when a global-norm clip or the max-norm constraint needs whole rows) are
+// all-reduced and every rank updates all of them; the per-thread partial sums of the batch-normalization statistics
 // (Neural_Network__Forward_Pass__OpenMP.cpp:4591-4701, …Backward_Pass__OpenMP.cpp:1346-1709) become small all-reduces of
 // [2][H] column sums, so a sharded step computes the same statistics as the one-GPU step; the loss / accuracy
 // accumulators (Merge__Post__Training, Neural_Network__Merge.cpp:52-98) are summed when they are read.
@@ -12,6 +16,7 @@
 // NCCL is loaded at run time (dlopen) so that the library itself has no link-time dependency on it.
 #include "net.cuh"
 
+#include <utility>
 #include <vector>
 
 #include <dlfcn.h>
@@ -66,9 +71,17 @@ struct CommState {
   cudaEvent_t side_done = nullptr; // comm -> compute: the small sum started by comm_side_sum_begin has arrived
   bool pending = false;
   size_t reduced_weights = 0;      // how much of the weight range has been handed to the comm stream this step
-  struct Bucket { size_t offset = 0, n = 0; cudaEvent_t reduced = nullptr; };
+  struct Bucket {
+    size_t offset = 0, n = 0;
+    bool scattered = false;          // reduce-scattered: only [offset + rank * n / world, + n / world) holds the sum
+    cudaEvent_t reduced = nullptr;   // comm -> compute: the sum (or this rank's slice of it) has arrived
+    cudaEvent_t updated = nullptr;   // compute -> comm: the optimizer has updated this rank's slice of the parameters
+  };
   std::vector<Bucket> buckets;     // the ranges issued this step, each with the event that says its sum has arrived
   size_t used = 0;
+  bool scatter = false;            // this step's buckets may be reduce-scattered (set by update_derivative_weight's caller)
+  std::vector<std::pair<size_t, size_t>> last_scattered;  // (offset, n) of the buckets the last update handled in slices
+  cudaEvent_t gathered = nullptr;  // comm -> compute: every all-gather issued so far has completed
 };
 
 static int nccl_fail(myea_b200_net *net, ncclResult_t r, const char *what) {
@@ -106,16 +119,28 @@ int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n) {
   if (c == nullptr || n == 0) return MYEA_OK;
   NcclApi *api = nccl_api();
   if (cudaEventRecord(c->ready, net->ctx.stream) != cudaSuccess || cudaStreamWaitEvent(c->stream, c->ready, 0) != cudaSuccess) return MYEA_E_CUDA;
-  ncclResult_t r = api->AllReduce(net->grads + offset, net->grads + offset, n, ncclFloat, ncclSum, c->comm, c->stream);
-  if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllReduce (bucket)");
+  // a slice starts on a 16-byte boundary (the update kernel reads float4) and all slices are equal
+  const size_t w = static_cast<size_t>(c->world);
+  const bool scattered = c->scatter && (n % (4 * w)) == 0 && (offset % 4) == 0;
+  ncclResult_t r;
+  if (scattered) {
+    const size_t count = n / w;
+    r = api->ReduceScatter(net->grads + offset, net->grads + offset + static_cast<size_t>(c->rank) * count, count, ncclFloat, ncclSum, c->comm, c->stream);
+  } else {
+    r = api->AllReduce(net->grads + offset, net->grads + offset, n, ncclFloat, ncclSum, c->comm, c->stream);
+  }
+  if (r != ncclSuccess) return nccl_fail(net, r, scattered ? "ncclReduceScatter (bucket)" : "ncclAllReduce (bucket)");
   if (c->used == c->buckets.size()) {
     CommState::Bucket b;
-    if (cudaEventCreateWithFlags(&b.reduced, cudaEventDisableTiming) != cudaSuccess) return MYEA_E_CUDA;
+    if (cudaEventCreateWithFlags(&b.reduced, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&b.updated, cudaEventDisableTiming) != cudaSuccess)
+      return MYEA_E_CUDA;
     c->buckets.push_back(b);
   }
   CommState::Bucket &b = c->buckets[c->used++];
   b.offset = offset;
   b.n = n;
+  b.scattered = scattered;
   if (cudaEventRecord(b.reduced, c->stream) != cudaSuccess) return MYEA_E_CUDA;
   c->pending = true;
   net->ctx.launches += 1;
@@ -149,22 +174,103 @@ int comm_join(myea_b200_net *net) {
   if (cudaEventRecord(c->done, c->stream) != cudaSuccess || cudaStreamWaitEvent(net->ctx.stream, c->done, 0) != cudaSuccess) return MYEA_E_CUDA;
   c->pending = false;
   c->used = 0;
+  c->last_scattered.clear();  // every rank updates everything after a join
   return MYEA_OK;
 }
 
 // The ranges handed to the communicator this step, in the order their sums arrive.
 size_t comm_bucket_count(const myea_b200_net *net) { return net->comm != nullptr ? net->comm->used : 0; }
-// Makes the compute stream wait for bucket i only and says which range it covers.
-int comm_bucket_wait(myea_b200_net *net, size_t i, size_t *offset, size_t *n) {
+// Makes the compute stream wait for bucket i only and says which range it covers; for a reduce-scattered bucket
+// (slice_offset, slice_n) is the slice whose sum this rank holds (otherwise the whole bucket).
+int comm_bucket_wait(myea_b200_net *net, size_t i, size_t *offset, size_t *n, size_t *slice_offset, size_t *slice_n) {
   CommState *c = net->comm;
   if (c == nullptr || i >= c->used) return MYEA_E_INVALID;
-  if (cudaStreamWaitEvent(net->ctx.stream, c->buckets[i].reduced, 0) != cudaSuccess) return MYEA_E_CUDA;
-  *offset = c->buckets[i].offset;
-  *n = c->buckets[i].n;
+  const CommState::Bucket &b = c->buckets[i];
+  if (cudaStreamWaitEvent(net->ctx.stream, b.reduced, 0) != cudaSuccess) return MYEA_E_CUDA;
+  *offset = b.offset;
+  *n = b.n;
+  const size_t count = b.scattered ? b.n / static_cast<size_t>(c->world) : b.n;
+  *slice_offset = b.scattered ? b.offset + static_cast<size_t>(c->rank) * count : b.offset;
+  *slice_n = count;
+  return MYEA_OK;
+}
+// After the optimizer has updated this rank's slice of bucket i (queued on the compute stream): the slices of all ranks
+// are gathered into every rank's parameter buffer on the communication stream.  A bucket that was all-reduced needs
+// nothing.  The derivative slices of the OTHER ranks are cleared here (the optimizer clears its own).
+int comm_bucket_gather(myea_b200_net *net, size_t i) {
+  CommState *c = net->comm;
+  if (c == nullptr || i >= c->used) return MYEA_E_INVALID;
+  const CommState::Bucket &b = c->buckets[i];
+  if (!b.scattered) return MYEA_OK;
+  NcclApi *api = nccl_api();
+  const size_t count = b.n / static_cast<size_t>(c->world), mine = static_cast<size_t>(c->rank) * count;
+  if (mine > 0 && cudaMemsetAsync(net->grads + b.offset, 0, mine * sizeof(float), net->ctx.stream) != cudaSuccess) return MYEA_E_CUDA;
+  if (mine + count < b.n &&
+      cudaMemsetAsync(net->grads + b.offset + mine + count, 0, (b.n - mine - count) * sizeof(float), net->ctx.stream) != cudaSuccess)
+    return MYEA_E_CUDA;
+  if (cudaEventRecord(b.updated, net->ctx.stream) != cudaSuccess || cudaStreamWaitEvent(c->stream, b.updated, 0) != cudaSuccess) return MYEA_E_CUDA;
+  ncclResult_t r = api->AllGather(net->params + b.offset + mine, net->params + b.offset, count, ncclFloat, c->comm, c->stream);
+  if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllGather (bucket)");
+  net->ctx.launches += 1;
+  net->ctx.class_launches[TC_COMM] += 1;
+  return MYEA_OK;
+}
+// The update turned out to need whole derivative buffers (a clip or a max-norm constraint was switched on after the
+// buckets had been issued): the slices are gathered so that every rank holds every sum, as after an all-reduce.
+int comm_unscatter(myea_b200_net *net) {
+  CommState *c = net->comm;
+  if (c == nullptr) return MYEA_OK;
+  NcclApi *api = nccl_api();
+  for (size_t i = 0; i < c->used; ++i) {
+    CommState::Bucket &b = c->buckets[i];
+    if (!b.scattered) continue;
+    const size_t count = b.n / static_cast<size_t>(c->world), mine = static_cast<size_t>(c->rank) * count;
+    ncclResult_t r = api->AllGather(net->grads + b.offset + mine, net->grads + b.offset, count, ncclFloat, c->comm, c->stream);
+    if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllGather (derivative slices)");
+    if (cudaEventRecord(b.reduced, c->stream) != cudaSuccess) return MYEA_E_CUDA;
+    b.scattered = false;
+  }
+  c->pending = true;
+  return MYEA_OK;
+}
+// Makes the compute stream wait until every gather issued so far has landed.
+int comm_gather_join(myea_b200_net *net) {
+  CommState *c = net->comm;
+  if (c == nullptr) return MYEA_OK;
+  if (cudaEventRecord(c->gathered, c->stream) != cudaSuccess || cudaStreamWaitEvent(net->ctx.stream, c->gathered, 0) != cudaSuccess) return MYEA_E_CUDA;
+  return MYEA_OK;
+}
+// Whether the buckets issued from now on may be reduce-scattered (the caller knows if the update needs whole buffers).
+void comm_set_scatter(myea_b200_net *net, bool on) {
+  if (net->comm != nullptr) net->comm->scatter = on;
+}
+bool comm_any_scattered(const myea_b200_net *net) {
+  if (net->comm == nullptr) return false;
+  for (size_t i = 0; i < net->comm->used; ++i)
+    if (net->comm->buckets[i].scattered) return true;
+  return false;
+}
+// The optimizer state of a sharded update lives in slices: before a buffer of it is read back, every rank's slice of
+// every bucket that was scattered in the last step is gathered (collective: every rank has to ask).
+int comm_gather_state(myea_b200_net *net, float *buf) {
+  CommState *c = net->comm;
+  if (c == nullptr || buf == nullptr) return MYEA_OK;
+  NcclApi *api = nccl_api();
+  for (const auto &b : c->last_scattered) {
+    const size_t count = b.second / static_cast<size_t>(c->world), mine = static_cast<size_t>(c->rank) * count;
+    ncclResult_t r = api->AllGather(buf + b.first + mine, buf + b.first, count, ncclFloat, c->comm, net->ctx.stream);
+    if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllGather (optimizer state)");
+  }
   return MYEA_OK;
 }
 void comm_buckets_done(myea_b200_net *net) {
-  if (net->comm != nullptr) { net->comm->used = 0; net->comm->pending = false; }
+  CommState *c = net->comm;
+  if (c == nullptr) return;
+  c->last_scattered.clear();
+  for (size_t i = 0; i < c->used; ++i)
+    if (c->buckets[i].scattered) c->last_scattered.emplace_back(c->buckets[i].offset, c->buckets[i].n);
+  c->used = 0;
+  c->pending = false;
 }
 
 size_t &comm_reduced_weights(myea_b200_net *net) {
@@ -180,7 +286,11 @@ void comm_destroy(myea_b200_net *net) {
   if (net->comm->ready) cudaEventDestroy(net->comm->ready);
   if (net->comm->done) cudaEventDestroy(net->comm->done);
   if (net->comm->side_done) cudaEventDestroy(net->comm->side_done);
-  for (auto &b : net->comm->buckets) if (b.reduced) cudaEventDestroy(b.reduced);
+  for (auto &b : net->comm->buckets) {
+    if (b.reduced) cudaEventDestroy(b.reduced);
+    if (b.updated) cudaEventDestroy(b.updated);
+  }
+  if (net->comm->gathered) cudaEventDestroy(net->comm->gathered);
   if (net->comm->stream) cudaStreamDestroy(net->comm->stream);
   delete net->comm;
   net->comm = nullptr;
@@ -218,12 +328,14 @@ extern "C" int myea_b200_comm_init(myea_handle net, int world, int rank, const u
   if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->ready, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming) != cudaSuccess ||
-      cudaEventCreateWithFlags(&c->side_done, cudaEventDisableTiming) != cudaSuccess) {
+      cudaEventCreateWithFlags(&c->side_done, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&c->gathered, cudaEventDisableTiming) != cudaSuccess) {
     api->CommDestroy(c->comm);
     if (c->stream) cudaStreamDestroy(c->stream);
     if (c->ready) cudaEventDestroy(c->ready);
     if (c->done) cudaEventDestroy(c->done);
     if (c->side_done) cudaEventDestroy(c->side_done);
+    if (c->gathered) cudaEventDestroy(c->gathered);
     delete c;
     net->ctx.error = "stream / event creation failed";
     return MYEA_E_CUDA;

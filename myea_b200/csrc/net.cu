@@ -25,7 +25,13 @@ float *lstm_output_errors(LayerPlan &L);
 // residual.cu
 int residual_forward(myea_b200_net *net, int layer);
 size_t comm_bucket_count(const myea_b200_net *net);
-int comm_bucket_wait(myea_b200_net *net, size_t i, size_t *offset, size_t *n);
+int comm_bucket_wait(myea_b200_net *net, size_t i, size_t *offset, size_t *n, size_t *slice_offset, size_t *slice_n);
+int comm_bucket_gather(myea_b200_net *net, size_t i);
+int comm_gather_join(myea_b200_net *net);
+void comm_set_scatter(myea_b200_net *net, bool on);
+bool comm_any_scattered(const myea_b200_net *net);
+int comm_gather_state(myea_b200_net *net, float *buf);
+int comm_unscatter(myea_b200_net *net);
 void comm_buckets_done(myea_b200_net *net);
 int residual_backward(myea_b200_net *net, int layer);
 const float *residual_fc_input(myea_b200_net *net, int r, int k);
@@ -426,6 +432,9 @@ extern "C" int myea_b200_download(myea_handle net, int which, float *host, uint6
   float *src = select_buffer(net, which, &n);
   if (src == nullptr || offset > n || count > n - offset) return fail(net, MYEA_E_INVALID, "download: buffer selector or range out of bounds");
   CK(cudaSetDevice(net->ctx.device));
+  // under a sharded update every rank keeps the optimizer state of its slices only: reading such a buffer back gathers
+  // the slices first (collective: every rank has to make the call)
+  if (net->comm != nullptr && (src == net->m1 || src == net->m2 || src == net->m2hat || src == net->prev_delta)) RC(comm_gather_state(net, src));
   CK(cudaMemcpyAsync(host, src + offset, count * sizeof(float), cudaMemcpyDeviceToHost, net->ctx.stream));
   CK(cudaStreamSynchronize(net->ctx.stream));
   return MYEA_OK;
@@ -790,6 +799,9 @@ extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batc
   const long long rows = net->T * net->active_B;
   if (net->comm != nullptr && net->grads_reduced)
     return fail(net, MYEA_E_UNSUPPORTED, "with a communicator attached, call update_parameter after every update_derivative_weight (the derivative buckets of this step were already summed over the ranks)");
+  // Reduce-scatter instead of all-reduce where the update is element by element: not under a global-norm clip (the norm
+  // needs every element) or the max-norm constraint (whole rows), which the description announces
+  comm_set_scatter(net, net->comm != nullptr && net->sharded_update);
   // last layer first: its bucket is complete first, and its all-reduce overlaps the contractions of the layers below
   for (int l = static_cast<int>(net->layers.size()) - 1; l >= 1; --l) {
     LayerPlan &L = net->layers[l];
@@ -820,12 +832,16 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
   CK(cudaSetDevice(net->ctx.device));
   const size_t P = net->total_parameters;
   // Without a global-norm clip the update is element by element, so each derivative bucket can be applied as soon as
-  // ITS sum over the ranks has arrived, while the later (lower-layer) buckets are still on the wire.
-  bool by_bucket = net->comm != nullptr && net->grads_reduced && !opt->use_clip_gradient && opt->regularization__max_norm_constraints == 0.f &&
-                   comm_bucket_count(net) > 0 && (net->total_weights & 3) == 0;
+  // ITS sum over the ranks has arrived, while the later (lower-layer) buckets are still on the wire - and only on this
+  // rank's slice of it where the bucket was reduce-scattered.
+  const bool needs_whole = opt->use_clip_gradient || opt->regularization__max_norm_constraints != 0.f;
+  net->sharded_update = !needs_whole;  // what the NEXT step's buckets may assume
+  bool by_bucket = net->comm != nullptr && net->grads_reduced && !needs_whole && comm_bucket_count(net) > 0 && (net->total_weights & 3) == 0;
   for (const auto &L : net->layers)  // the update kernel reads float4: every bucket has to start on a 16-byte boundary
     if (L.type != MYEA_LAYER_RESIDUAL && (L.idx.first_connection_index & 3) != 0) by_bucket = false;
   if (net->comm != nullptr && !by_bucket) {
+    // slices that were reduce-scattered for an update that now wants whole buffers: gather them first
+    if (net->grads_reduced && comm_any_scattered(net)) RC(comm_unscatter(net));
     if (net->grads_reduced) RC(comm_join(net));            // buckets issued by update_derivative_weight
     else RC(comm_all_reduce_sum(net, net->grads, P));      // nothing was issued: reduce everything now
     net->grads_reduced = false;
@@ -898,13 +914,15 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
     const size_t count = comm_bucket_count(net);
     size_t covered = 0;
     for (size_t i = 0; i < count; ++i) {
-      size_t off = 0, n = 0;
-      RC(comm_bucket_wait(net, i, &off, &n));
+      size_t bucket_off = 0, n = 0, off = 0, slice = 0;
+      RC(comm_bucket_wait(net, i, &bucket_off, &n, &off, &slice));
       if ((off & 3) != 0) return fail(net, MYEA_E_INVALID, "derivative bucket does not start on a 16-byte boundary");
       RC(optimizer_update(net->ctx, o, net->params + off, net->grads + off, net->m1 + off, net->m2 + off, net->m2hat + off, net->prev_delta + off,
-                          net->mask_reg + off, n));
+                          net->mask_reg + off, slice));
+      RC(comm_bucket_gather(net, i));  // the other ranks' slices of the updated parameters (nothing for an all-reduced bucket)
       covered += n;
     }
+    RC(comm_gather_join(net));
     comm_buckets_done(net);
     net->grads_reduced = false;
     if (covered != P) return fail(net, MYEA_E_INVALID, "derivative buckets do not cover the parameter buffer");

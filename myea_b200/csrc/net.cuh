@@ -90,6 +90,7 @@ struct myea_b200_net {
   myea::CommState *comm = nullptr;
   myea::SumHook hook;            // cross-GPU sum of normalization column sums (world 1: unused)
   bool grads_reduced = false;    // this step's derivative buckets have already been handed to the communicator
+  bool sharded_update = true;    // the last update was element by element (no clip, no max-norm): buckets may be reduce-scattered
   double *d_loss_tmp = nullptr;  // [3] staging for the cross-GPU sum of the loss accumulators
   // dataset kept on the device for the epoch loop (epoch.cu): rows [example][T * width], the staged batch, the order
   float *ds_inputs = nullptr, *ds_outputs = nullptr, *ds_batch_inputs = nullptr, *ds_batch_outputs = nullptr;
