@@ -16,6 +16,7 @@
 // NCCL is loaded at run time (dlopen) so that the library itself has no link-time dependency on it.
 #include "net.cuh"
 
+#include <algorithm>
 #include <utility>
 #include <vector>
 
@@ -62,7 +63,85 @@ static NcclApi *nccl_api() {
   return api.lib != nullptr ? const_cast<NcclApi *>(&api) : nullptr;
 }
 
+// One-shot sum of a small vector over the ranks through peer-mapped memory (the batch-normalization column sums of a
+// sharded batch: 2 x H floats, 16 exchanges per step, each pure latency for a library all-reduce).  Every rank owns one
+// allocation that all ranks map (CUDA IPC): [2 parities][world slots][capacity] floats followed by
+// [2 parities][world][PEER_MAX_BLOCKS] arrival words.
+constexpr int PEER_MAX_BLOCKS = 64;
+constexpr int PEER_MAX_WORLD = 16;
+struct PeerSum {
+  bool ready = false;
+  float *local = nullptr;            // this rank's allocation
+  void *mapped[PEER_MAX_WORLD] = {}; // every rank's allocation in this process's address space ([rank] = local)
+  float **mapped_d = nullptr;        // the same table on the device
+  size_t capacity = 0;               // floats per slot
+  unsigned int epoch = 0;            // exchanges so far; the same on every rank
+};
+
+// Block b of every rank handles the same 1024 floats.  It stores its floats into slot `rank` of EVERY rank's buffer
+// (plain peer stores over NVLink), publishes them with one arrival word per peer, waits (bounded) for the arrival words of
+// all ranks in its own buffer and adds the slots in rank order - the same order on every rank, so all ranks end with
+// bitwise identical sums.  Two parities: exchange e + 2 can only start when every rank has finished e + 1, and a rank
+// enters e + 1 only after it has read the slots of e.
+__global__ void __launch_bounds__(256) peer_sum_kernel(float *__restrict__ data, int n, int rank, int world, float *const *__restrict__ bufs,
+                                                       size_t capacity, unsigned int epoch, int *error_flag) {
+  const int par = static_cast<int>(epoch & 1u);
+  const size_t slots = static_cast<size_t>(2) * world * capacity;  // floats before the arrival words
+  const int i = (static_cast<int>(blockIdx.x) * 256 + static_cast<int>(threadIdx.x)) * 4;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    if (i + k < n) v[k] = data[i + k];
+  if (i < n) {
+    for (int r = 0; r < world; ++r) {
+      float *dst = bufs[r] + (static_cast<size_t>(par) * world + rank) * capacity + i;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (i + k < n) dst[k] = v[k];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < world) {
+    const int r = static_cast<int>(threadIdx.x);
+    // tell rank r that this rank's floats of this block are in its buffer
+    unsigned int *theirs = reinterpret_cast<unsigned int *>(bufs[r] + slots) + (static_cast<size_t>(par) * world + rank) * PEER_MAX_BLOCKS + blockIdx.x;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+    // and wait until rank r's floats are in this rank's buffer; the bound is generous (ranks may reach their first
+    // exchange seconds apart) but it is a bound
+    const unsigned int *mine = reinterpret_cast<const unsigned int *>(bufs[rank] + slots) + (static_cast<size_t>(par) * world + r) * PEER_MAX_BLOCKS + blockIdx.x;
+    const long long t0 = clock64();
+    for (;;) {
+      unsigned int seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (static_cast<int>(seen - epoch) >= 0) break;
+      if (clock64() - t0 > (1ll << 36)) { failed = 1; break; }
+    }
+  }
+  __syncthreads();
+  if (failed) {
+    if (threadIdx.x == 0) atomicCAS(error_flag, 0, 501);
+    return;
+  }
+  if (i < n) {
+    float t[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      const volatile float *src = bufs[rank] + (static_cast<size_t>(par) * world + r) * capacity + i;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (i + k < n) t[k] += src[k];
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (i + k < n) data[i + k] = t[k];
+  }
+}
+
 struct CommState {
+  PeerSum peer;
   ncclComm_t comm = nullptr;
   int world = 1, rank = 0;
   cudaStream_t stream = nullptr;   // bucket all-reduces run here, beside the compute stream
@@ -94,11 +173,26 @@ static int nccl_fail(myea_b200_net *net, ncclResult_t r, const char *what) {
 
 int comm_world(const myea_b200_net *net) { return net->comm != nullptr ? net->comm->world : 1; }
 
+// the peer-memory exchange when it is set up and the vector fits, on `stream`
+static bool peer_sum(myea_b200_net *net, float *buf, size_t n, cudaStream_t stream) {
+  CommState *c = net->comm;
+  PeerSum &p = c->peer;
+  const int blocks = static_cast<int>((n + 1023) / 1024);
+  if (!p.ready || n > p.capacity || blocks > PEER_MAX_BLOCKS) return false;
+  ++p.epoch;
+  peer_sum_kernel<<<blocks, 256, 0, stream>>>(buf, static_cast<int>(n), c->rank, c->world, p.mapped_d, p.capacity, p.epoch, net->ctx.d_error_flag);
+  return true;
+}
+
 // in-place sum over ranks on the COMPUTE stream (small, latency-bound messages: normalization sums, loss counters)
 int comm_all_reduce_sum(myea_b200_net *net, float *buf, size_t n) {
   if (net->comm == nullptr || n == 0) return MYEA_OK;
   NcclApi *api = nccl_api();
   net->ctx.begin(TC_COMM);
+  if (peer_sum(net, buf, n, net->ctx.stream)) {
+    net->ctx.end(TC_COMM);
+    return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+  }
   ncclResult_t r = api->AllReduce(buf, buf, n, ncclFloat, ncclSum, net->comm->comm, net->ctx.stream);
   net->ctx.end(TC_COMM);
   return r == ncclSuccess ? MYEA_OK : nccl_fail(net, r, "ncclAllReduce");
@@ -154,8 +248,10 @@ int comm_side_sum_begin(myea_b200_net *net, float *buf, size_t n) {
   if (c == nullptr) return MYEA_E_INVALID;
   NcclApi *api = nccl_api();
   if (cudaEventRecord(c->ready, net->ctx.stream) != cudaSuccess || cudaStreamWaitEvent(c->stream, c->ready, 0) != cudaSuccess) return MYEA_E_CUDA;
-  ncclResult_t r = api->AllReduce(buf, buf, n, ncclFloat, ncclSum, c->comm, c->stream);
-  if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllReduce (side)");
+  if (!peer_sum(net, buf, n, c->stream)) {
+    ncclResult_t r = api->AllReduce(buf, buf, n, ncclFloat, ncclSum, c->comm, c->stream);
+    if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllReduce (side)");
+  }
   if (cudaEventRecord(c->side_done, c->stream) != cudaSuccess) return MYEA_E_CUDA;
   net->ctx.launches += 1;
   net->ctx.class_launches[TC_COMM] += 1;
@@ -278,10 +374,71 @@ size_t &comm_reduced_weights(myea_b200_net *net) {
   return net->comm != nullptr ? net->comm->reduced_weights : none;
 }
 
+// Sets the peer-memory exchange up: one allocation per rank, mapped by all ranks through CUDA IPC (the handles travel in
+// an all-gather).  Any failure leaves it off; the small sums then use the library's all-reduce.
+static void peer_setup(myea_b200_net *net) {
+  CommState *c = net->comm;
+  NcclApi *api = nccl_api();
+  PeerSum &p = c->peer;
+  if (c->world > PEER_MAX_WORLD) return;
+  long long widest = 0;
+  for (const auto &L : net->layers)
+    if (L.has_norm) widest = std::max(widest, L.n_out);
+  if (widest == 0) return;
+  p.capacity = static_cast<size_t>(2 * widest + 3) & ~static_cast<size_t>(3);
+  const size_t bytes = static_cast<size_t>(2) * c->world * p.capacity * sizeof(float) + static_cast<size_t>(2) * c->world * PEER_MAX_BLOCKS * sizeof(unsigned int);
+  unsigned char *stage = nullptr;
+  std::vector<cudaIpcMemHandle_t> handles(c->world);
+  bool ok = cudaMalloc(&p.local, bytes) == cudaSuccess && cudaMemset(p.local, 0, bytes) == cudaSuccess &&
+            cudaMalloc(&stage, c->world * sizeof(cudaIpcMemHandle_t)) == cudaSuccess;
+  cudaIpcMemHandle_t mine;
+  ok = ok && cudaIpcGetMemHandle(&mine, p.local) == cudaSuccess &&
+       cudaMemcpy(stage + c->rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice) == cudaSuccess;
+  // every rank takes part in the gather even when its own set-up failed (a zero handle then marks the failure)
+  if (!ok && stage != nullptr) cudaMemset(stage + c->rank * sizeof(mine), 0, sizeof(mine));
+  bool gathered = stage != nullptr &&
+                  api->AllGather(stage + c->rank * sizeof(mine), stage, sizeof(mine), ncclChar, c->comm, c->stream) == ncclSuccess &&
+                  cudaStreamSynchronize(c->stream) == cudaSuccess &&
+                  cudaMemcpy(handles.data(), stage, c->world * sizeof(mine), cudaMemcpyDeviceToHost) == cudaSuccess;
+  if (stage != nullptr) cudaFree(stage);
+  ok = ok && gathered;
+  const cudaIpcMemHandle_t zero = {};
+  for (int r = 0; ok && r < c->world; ++r)
+    if (memcmp(&handles[r], &zero, sizeof(zero)) == 0) ok = false;
+  for (int r = 0; ok && r < c->world; ++r) {
+    if (r == c->rank) { p.mapped[r] = p.local; continue; }
+    if (cudaIpcOpenMemHandle(&p.mapped[r], handles[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { p.mapped[r] = nullptr; ok = false; }
+  }
+  ok = ok && cudaMalloc(&p.mapped_d, c->world * sizeof(float *)) == cudaSuccess &&
+       cudaMemcpy(p.mapped_d, p.mapped, c->world * sizeof(float *), cudaMemcpyHostToDevice) == cudaSuccess;
+  cudaGetLastError();
+  // all ranks use it or none does: a rank that failed would otherwise wait for arrivals that never come
+  int *flag = nullptr;
+  int all = 0;
+  if (cudaMalloc(&flag, sizeof(int)) == cudaSuccess) {
+    const int v = ok ? 1 : 0;
+    cudaMemcpy(flag, &v, sizeof(int), cudaMemcpyHostToDevice);
+    if (api->AllReduce(flag, flag, 1, ncclInt, ncclMin, c->comm, c->stream) == ncclSuccess && cudaStreamSynchronize(c->stream) == cudaSuccess)
+      cudaMemcpy(&all, flag, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaFree(flag);
+  }
+  p.ready = ok && all == 1;
+}
+
+static void peer_teardown(CommState *c) {
+  PeerSum &p = c->peer;
+  for (int r = 0; r < c->world && r < PEER_MAX_WORLD; ++r)
+    if (r != c->rank && p.mapped[r] != nullptr) cudaIpcCloseMemHandle(p.mapped[r]);
+  if (p.mapped_d != nullptr) cudaFree(p.mapped_d);
+  if (p.local != nullptr) cudaFree(p.local);
+  p = PeerSum();
+}
+
 void comm_destroy(myea_b200_net *net) {
   if (net->comm == nullptr) return;
   NcclApi *api = nccl_api();
   if (net->comm->stream) cudaStreamSynchronize(net->comm->stream);
+  peer_teardown(net->comm);
   if (api && net->comm->comm) api->CommDestroy(net->comm->comm);
   if (net->comm->ready) cudaEventDestroy(net->comm->ready);
   if (net->comm->done) cudaEventDestroy(net->comm->done);
@@ -341,6 +498,7 @@ extern "C" int myea_b200_comm_init(myea_handle net, int world, int rank, const u
     return MYEA_E_CUDA;
   }
   net->comm = c;
+  peer_setup(net);  // optional: without it the small sums go through the library
   net->hook.world = world;
   net->hook.user = net;
   net->hook.all_reduce = [](void *user, float *buf, size_t n) { return comm_all_reduce_sum(static_cast<myea_b200_net *>(user), buf, n); };
@@ -348,3 +506,7 @@ extern "C" int myea_b200_comm_init(myea_handle net, int world, int rank, const u
   net->hook.end = [](void *user) { return comm_side_sum_end(static_cast<myea_b200_net *>(user)); };
   return MYEA_OK;
 }
+
+// Diagnostic (not part of the training interface): 1 when the small cross-rank sums of this handle go through the
+// peer-memory exchange kernel, 0 when they use the library's all-reduce.
+extern "C" int myea_b200_comm_peer_sums(myea_handle net) { return (net != nullptr && net->comm != nullptr && net->comm->peer.ready) ? 1 : 0; }
