@@ -130,6 +130,15 @@ struct Epilogue {
   long long ld_aux = 0;
   const float *col_scale = nullptr;  // pre = aux_pre * col_scale[n] + col_shift[n] when non-null (normalization folded in)
   const float *col_shift = nullptr;
+  // Column statistics of the result, emitted by the epilogue so that no separate pass has to re-read it (tensor-core
+  // kernels, 16-byte aligned arrays, N a multiple of 32): for every block of 32 output rows, col_stats[0][block][n] and
+  // col_stats[1][block][n] (pitch stats_blocks * N between the two) receive
+  //   stats_kind 1:  sum of the stored values, sum of their squares           (batch-normalization forward sums)
+  //   stats_kind 2:  sum of the stored values d, sum of d * (aux_pre - col_mean[n])   (its backward sums; needs deriv_af)
+  int stats_kind = 0;
+  float *col_stats = nullptr;
+  long long stats_blocks = 0;
+  const float *col_mean = nullptr;
   // seg_rows != 0: the output rows come in up to 4 segments of seg_rows rows; row m of the product is row
   // (m mod seg_rows) of the array that starts at C + seg_off[m / seg_rows] (the four gate matrices of an LSTM layer
   // inside the reference's per-block parameter layout: one contraction instead of four)
@@ -188,6 +197,19 @@ int gemm_prepare_shared(Context &ctx, const float *src, long long stride_r, long
                         Panels *as_rows, int role_cols, Panels *as_cols);
 // true when a contraction of this shape runs on the 256 x 256 kernel (the only one that takes MN-major operands)
 bool gemm_takes_mn_major(const Context &ctx, long long M, long long N);
+// The Panels of gemm_prepare_shared's layout in `mem` without writing them (for a producer kernel that writes them itself),
+// and what such a producer needs to know: where the three panels lie and which cross-term order each reading wants.
+// Only for R and C that are multiples of 8 (no padding rows or columns to clear).
+struct PanelSink {
+  float *hi = nullptr;            // [R][kp] TF32-rounded values
+  float *cross_k = nullptr;       // [R][kp] cross panel of the row reading (null: not wanted)
+  uint16_t *cross_mn = nullptr;   // [2 R][kp] bf16 cross panel of the column reading (null: not wanted)
+  long long kp = 0;
+  int role_k = 0, role_mn = 0;    // PANEL_ROLE_A / _B of the two readings
+};
+void shared_panel_layout(float *mem, long long R, long long C, int role_rows, Panels *as_rows, int role_cols, Panels *as_cols, PanelSink *sink);
+// whether the epilogue of a tensor-core contraction with this description can emit column statistics (stats_kind)
+bool epilogue_takes_stats(const Context &ctx, const Epilogue &e, long long N);
 // Launches split kernels + the tensor-core kernel (engine 0) or the FP32 FMA kernel (engine 1) on ctx.stream.
 int gemm_nt(Context &ctx, const Operand &A, const Operand &B, const Epilogue &epi, const GemmScratch &scratch);
 // Optional workspace that lets the 256 x 256 tensor-core kernel split the tiles of a partial last wave along K
@@ -227,15 +249,18 @@ struct OverlapWork {
 };
 
 // z [rows,H] -> batch statistics (training) or running statistics (inference) -> col_scale / col_shift
+// fused_chunks > 0: np.partial already holds the column sums of `fused_chunks` row blocks (written by the epilogue of the
+// contraction that produced z), no pass over z is made
 int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H, const NormParams &np, int training,
-                       const SumHook *hook = nullptr, const OverlapWork *meanwhile = nullptr);
+                       const SumHook *hook = nullptr, const OverlapWork *meanwhile = nullptr, int fused_chunks = 0);
 // out = dropout(f(z*col_scale+col_shift)) ; col_scale null = no normalization. mask: uint8[H] or null; keep_scale = 1/p for inverted dropout
+// sink (may be null): the result is also written as operand panels of the contraction that reads it next
 int activation_forward(Context &ctx, const float *z, float *out, long long rows, long long H, uint32_t af,
-                       const float *col_scale, const float *col_shift, const uint8_t *mask, float keep_scale);
+                       const float *col_scale, const float *col_shift, const uint8_t *mask, float keep_scale, const PanelSink *sink = nullptr);
 int softmax_forward(Context &ctx, const float *z, float *out, long long rows, long long H);
 // delta_af [rows,H] (error after the activation derivative) -> error before the normalization, plus d_gamma / d_beta
 int norm_backward(Context &ctx, const float *z, const float *delta_af, float *delta_out, long long rows, long long H,
-                  const NormParams &np, const SumHook *hook = nullptr);
+                  const NormParams &np, const SumHook *hook = nullptr, int fused_chunks = 0, const PanelSink *sink = nullptr);
 // delta = f'(pre,y) * (y - desired); loss / accuracy accumulators (double[2] + uint64) on the device
 int output_error(Context &ctx, const float *pre, const float *y, const float *desired, float *delta, long long rows,
                  long long H, uint32_t af, uint32_t loss, uint32_t accuracy, float accuracy_variance, double *d_acc,

@@ -118,7 +118,7 @@ __device__ __forceinline__ void derive4x4_any(uint32_t af, float4 (&x)[4], const
   }
 }
 
-template <bool ADD, bool DERIV, bool ACC>
+template <bool ADD, bool DERIV, bool ACC, int STATS = 0>
 __device__ __forceinline__ void epilogue_block32(const Epilogue &e, float *tr, const float (&v)[32], int lane, long long row0, long long col0, int M) {
   const int c4 = (lane & 7) * 4, rsub = lane >> 3;
   const long long n = col0 + c4;
@@ -150,6 +150,9 @@ __device__ __forceinline__ void epilogue_block32(const Epilogue &e, float *tr, c
       }
     }
   };
+  // column statistics of this 32 x 32 block: this lane's four columns over its eight rows first
+  float4 st0 = zero, st1 = zero;
+  const float4 mu = (STATS == 2 && e.col_mean != nullptr) ? ld4(e.col_mean + n) : zero;
   if (AHEAD) load_rows(0, 0, 2);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -179,7 +182,34 @@ __device__ __forceinline__ void epilogue_block32(const Epilogue &e, float *tr, c
     for (int i = 0; i < 4; ++i) {
       const long long m = row0 + h * 16 + rsub + 4 * i;
       if (ACC) { x[i].x += old[s0 + i].x; x[i].y += old[s0 + i].y; x[i].z += old[s0 + i].z; x[i].w += old[s0 + i].w; }
-      if (m < M) *reinterpret_cast<float4 *>(e.C + c_row(e, m) + n) = x[i];
+      if (m < M) {
+        *reinterpret_cast<float4 *>(e.C + c_row(e, m) + n) = x[i];
+        if (STATS == 1) {
+          st0.x += x[i].x; st0.y += x[i].y; st0.z += x[i].z; st0.w += x[i].w;
+          st1.x = fmaf(x[i].x, x[i].x, st1.x); st1.y = fmaf(x[i].y, x[i].y, st1.y); st1.z = fmaf(x[i].z, x[i].z, st1.z); st1.w = fmaf(x[i].w, x[i].w, st1.w);
+        }
+        if (STATS == 2) {
+          const float4 p = pre[s0 + i];  // the raw array the derivative was taken on (before the folded normalization)
+          st0.x += x[i].x; st0.y += x[i].y; st0.z += x[i].z; st0.w += x[i].w;
+          st1.x = fmaf(x[i].x, p.x - mu.x, st1.x); st1.y = fmaf(x[i].y, p.y - mu.y, st1.y); st1.z = fmaf(x[i].z, p.z - mu.z, st1.z); st1.w = fmaf(x[i].w, p.w - mu.w, st1.w);
+        }
+      }
+    }
+  }
+  if (STATS != 0) {
+    // the four lanes that share a column slot (lane, lane ^ 8, lane ^ 16, lane ^ 24) hold the block's 32 rows between them
+#pragma unroll
+    for (int o = 8; o <= 16; o <<= 1) {
+      st0.x += __shfl_xor_sync(0xffffffffu, st0.x, o); st0.y += __shfl_xor_sync(0xffffffffu, st0.y, o);
+      st0.z += __shfl_xor_sync(0xffffffffu, st0.z, o); st0.w += __shfl_xor_sync(0xffffffffu, st0.w, o);
+      st1.x += __shfl_xor_sync(0xffffffffu, st1.x, o); st1.y += __shfl_xor_sync(0xffffffffu, st1.y, o);
+      st1.z += __shfl_xor_sync(0xffffffffu, st1.z, o); st1.w += __shfl_xor_sync(0xffffffffu, st1.w, o);
+    }
+    const long long blk = row0 >> 5;
+    if (lane < 8 && blk < e.stats_blocks) {
+      float *dst = e.col_stats + blk * e.ldc + n;   // [block][N]: the result's pitch is N for the arrays that ask for this
+      *reinterpret_cast<float4 *>(dst) = st0;
+      *reinterpret_cast<float4 *>(dst + e.stats_blocks * e.ldc) = st1;
     }
   }
 }
@@ -213,8 +243,14 @@ __device__ __forceinline__ void epilogue_row32(const Epilogue &e, const float (&
   if (col0 >= N) return;
   if (vec_ok && col0 + 32 <= N) {
     switch (mode) {
-      case 0: epilogue_block32<false, false, false>(e, tr, v, lane, row0, col0, M); break;
-      case 1: epilogue_block32<false, true, false>(e, tr, v, lane, row0, col0, M); break;
+      case 0:
+        if (e.stats_kind == 1) epilogue_block32<false, false, false, 1>(e, tr, v, lane, row0, col0, M);
+        else epilogue_block32<false, false, false>(e, tr, v, lane, row0, col0, M);
+        break;
+      case 1:
+        if (e.stats_kind == 2) epilogue_block32<false, true, false, 2>(e, tr, v, lane, row0, col0, M);
+        else epilogue_block32<false, true, false>(e, tr, v, lane, row0, col0, M);
+        break;
       case 2: epilogue_block32<false, false, true>(e, tr, v, lane, row0, col0, M); break;
       default: epilogue_block32<true, true, true>(e, tr, v, lane, row0, col0, M); break;
     }
@@ -1099,9 +1135,7 @@ size_t shared_panel_floats(long long R, long long C) {
   return static_cast<size_t>(3 * r8 * pitch) + 64;  // hi, K-major cross, MN-major cross (2 * r8 rows of bf16)
 }
 
-int gemm_prepare_shared(Context &ctx, const float *src, long long stride_r, long long R, long long C, float *mem, int role_rows,
-                        Panels *as_rows, int role_cols, Panels *as_cols) {
-  if (src == nullptr || mem == nullptr || R <= 0 || C <= 0 || (reinterpret_cast<uintptr_t>(mem) & 255) != 0) return MYEA_E_INVALID;
+void shared_panel_layout(float *mem, long long R, long long C, int role_rows, Panels *as_rows, int role_cols, Panels *as_cols, PanelSink *sink) {
   const long long pitch = round_up(C, 64), r8 = round_up(R, 8);
   float *hi = mem, *cross_k = mem + r8 * pitch;
   uint16_t *cross_mn = reinterpret_cast<uint16_t *>(mem + 2 * r8 * pitch);
@@ -1115,6 +1149,31 @@ int gemm_prepare_shared(Context &ctx, const float *src, long long stride_r, long
     as_cols->hi = hi; as_cols->lo = reinterpret_cast<float *>(cross_mn); as_cols->rows = C; as_cols->k = R; as_cols->kp = pitch;
     as_cols->role = role_cols; as_cols->major = PANEL_MN;
   }
+  if (sink != nullptr) {
+    sink->hi = hi;
+    sink->cross_k = as_rows != nullptr ? cross_k : nullptr;
+    sink->cross_mn = as_cols != nullptr ? cross_mn : nullptr;
+    sink->kp = pitch;
+    sink->role_k = role_rows;
+    sink->role_mn = role_cols;
+  }
+}
+
+bool epilogue_takes_stats(const Context &ctx, const Epilogue &e, long long N) {
+  if (ctx.gemm_engine != 0 || (N & 31) != 0 || e.ldc != N || e.addend != nullptr || e.accumulate || e.seg_rows != 0) return false;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(e.C) | reinterpret_cast<uintptr_t>(e.bias) | reinterpret_cast<uintptr_t>(e.aux_pre) |
+                         reinterpret_cast<uintptr_t>(e.aux_y) | reinterpret_cast<uintptr_t>(e.col_scale) | reinterpret_cast<uintptr_t>(e.col_shift) |
+                         reinterpret_cast<uintptr_t>(e.col_stats) | reinterpret_cast<uintptr_t>(e.col_mean);
+  return (bits & 15) == 0 && ((e.ldc | e.ld_aux) & 3) == 0;
+}
+
+int gemm_prepare_shared(Context &ctx, const float *src, long long stride_r, long long R, long long C, float *mem, int role_rows,
+                        Panels *as_rows, int role_cols, Panels *as_cols) {
+  if (src == nullptr || mem == nullptr || R <= 0 || C <= 0 || (reinterpret_cast<uintptr_t>(mem) & 255) != 0) return MYEA_E_INVALID;
+  const long long pitch = round_up(C, 64), r8 = round_up(R, 8);
+  float *hi = mem, *cross_k = mem + r8 * pitch;
+  uint16_t *cross_mn = reinterpret_cast<uint16_t *>(mem + 2 * r8 * pitch);
+  shared_panel_layout(mem, R, C, role_rows, as_rows, role_cols, as_cols, nullptr);
   const int raw = ctx.gemm_engine == 1 ? 1 : 0;
   const long long total = r8 * ((C + 7) >> 3);
   int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));

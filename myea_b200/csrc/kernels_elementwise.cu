@@ -3,6 +3,7 @@
 // for the bias derivatives.  All of them stream [rows, H] row-major fp32 tensors with 128-bit accesses where the
 // shape allows and reduce over rows with per-thread partial sums, a shared-memory tree and a second small pass.
 #include "common.cuh"
+#include "panel_math.cuh"
 
 #include <algorithm>
 
@@ -150,16 +151,20 @@ __global__ void norm_stats_finalize_kernel(const float *__restrict__ partial, in
 }
 
 int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H, const NormParams &np, int training,
-                       const SumHook *hook, const OverlapWork *meanwhile) {
+                       const SumHook *hook, const OverlapWork *meanwhile, int fused_chunks) {
   ctx.begin(TC_NORM);
   int launches = 1;
   int chunks = 1;
   const float *sums = np.partial;
   long long rows_total = rows;
   if (training) {
-    chunks = pick_chunks(rows, H, (H % 4 == 0) ? 4 : 1, np.chunks);
-    launch_column_reduce<RK_SUM_SQ>(ctx, z, nullptr, nullptr, rows, H, chunks, np.partial);
-    ++launches;
+    if (fused_chunks > 0) {
+      chunks = fused_chunks;  // the contraction's epilogue has left the sums of every 32-row block in np.partial
+    } else {
+      chunks = pick_chunks(rows, H, (H % 4 == 0) ? 4 : 1, np.chunks);
+      launch_column_reduce<RK_SUM_SQ>(ctx, z, nullptr, nullptr, rows, H, chunks, np.partial);
+      ++launches;
+    }
     if (hook != nullptr && hook->world > 1) {
       // sharded batch: sum the column sums over the ranks, then every rank finalizes the same global statistics
       float *g = np.partial + 2ll * np.chunks * H + 3 * H;
@@ -265,6 +270,98 @@ __global__ void __launch_bounds__(256) activation_forward_cols_kernel(const floa
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Producers that also write their result as operand panels (see PanelSink): the contraction that reads the tensor next
+// then needs no split pass of its own.  A thread keeps EIGHT columns (one group of the cross panels) and walks rows.
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void write_panels8(const PanelSink &s, long long r, long long c, const float (&v)[8]) {
+  float h[8];
+  uint32_t x[8];
+  split_group(v, s.role_k, 0, h, x);
+  store8(s.hi + r * s.kp + c, h);
+  if (s.cross_k != nullptr) {
+    uint4 *px = reinterpret_cast<uint4 *>(s.cross_k + r * s.kp + c);
+    px[0] = make_uint4(x[0], x[1], x[2], x[3]);
+    px[1] = make_uint4(x[4], x[5], x[6], x[7]);
+  }
+  if (s.cross_mn != nullptr) {
+    // x[0..3] / x[4..7] are the packed lo and hi values of these 8 columns in the order of role_k; the column reading
+    // wants, per 8 source rows, 8 panel rows of lo and 8 of hi (role A) or hi then lo (role B)
+    const uint4 lo4 = s.role_k ? make_uint4(x[4], x[5], x[6], x[7]) : make_uint4(x[0], x[1], x[2], x[3]);
+    const uint4 hi4 = s.role_k ? make_uint4(x[0], x[1], x[2], x[3]) : make_uint4(x[4], x[5], x[6], x[7]);
+    const long long g16 = (r >> 3) * 16 + (r & 7);
+    const long long row_lo = g16 + (s.role_mn ? 8 : 0), row_hi = g16 + (s.role_mn ? 0 : 8);
+    *reinterpret_cast<uint4 *>(s.cross_mn + row_lo * s.kp + c) = lo4;
+    *reinterpret_cast<uint4 *>(s.cross_mn + row_hi * s.kp + c) = hi4;
+  }
+}
+
+template <uint32_t AF>
+__global__ void __launch_bounds__(256) activation_forward_panels_kernel(const float *__restrict__ z, float *__restrict__ out, long long rows,
+                                                                        long long H, const float *__restrict__ col_scale,
+                                                                        const float *__restrict__ col_shift, const uint8_t *__restrict__ mask,
+                                                                        float keep_scale, const PanelSink sink) {
+  const long long c = (blockIdx.x * 256ll + threadIdx.x) * 8;
+  if (c >= H) return;
+  const bool affine = col_scale != nullptr;
+  float cs[8], ch[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { cs[k] = affine ? col_scale[c + k] : 1.f; ch[k] = affine ? col_shift[c + k] : 0.f; }
+  const bool masked = mask != nullptr;
+  const unsigned long long keep = masked ? *reinterpret_cast<const unsigned long long *>(mask + c) : ~0ull;
+  const bool scale = masked || keep_scale != 1.0f;
+  for (long long r0 = blockIdx.y * 2ll; r0 < rows; r0 += gridDim.y * 2ll) {
+    float v[2][8];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+      if (r0 + u < rows) load8(v[u], z + (r0 + u) * H + c);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (r0 + u >= rows) break;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float y = af_fire(AF, affine ? v[u][k] * cs[k] + ch[k] : v[u][k]);
+        if (scale) y *= keep_scale;
+        if (((keep >> (8 * k)) & 0xFFull) == 0ull) y = 0.f;
+        v[u][k] = y;
+      }
+      store8(out + (r0 + u) * H + c, v[u]);
+      write_panels8(sink, r0 + u, c, v[u]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) norm_backward_apply_panels_kernel(const float *__restrict__ z, const float *__restrict__ delta,
+                                                                         float *__restrict__ out, long long rows, long long H,
+                                                                         const float *__restrict__ mean, const float *__restrict__ coef,
+                                                                         const PanelSink sink) {
+  const long long c = (blockIdx.x * 256ll + threadIdx.x) * 8;
+  if (c >= H) return;
+  float mu[8], k0[8], k1[8], k2[8];
+  load8(mu, mean + c); load8(k0, coef + c); load8(k1, coef + H + c); load8(k2, coef + 2 * H + c);
+  for (long long r0 = blockIdx.y * 2ll; r0 < rows; r0 += gridDim.y * 2ll) {
+    float t[2][8], u[2][8];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (r0 + i < rows) { load8(t[i], z + (r0 + i) * H + c); load8(u[i], delta + (r0 + i) * H + c); }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (r0 + i >= rows) break;
+      float d[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) d[k] = u[i][k] * k0[k] + (t[i][k] - mu[k]) * k1[k] + k2[k];
+      store8(out + (r0 + i) * H + c, d);
+      write_panels8(sink, r0 + i, c, d);
+    }
+  }
+}
+
+static dim3 column_walk_grid8(long long rows, long long H) {
+  const unsigned gx = static_cast<unsigned>((H / 8 + 255) / 256);
+  const long long walkers = std::max<long long>(1, (148 * 8) / gx);
+  return dim3(gx, static_cast<unsigned>(std::max<long long>(1, std::min<long long>((rows + 1) / 2, walkers))));
+}
+
 static dim3 column_walk_grid(long long rows, long long H) {
   const unsigned gx = static_cast<unsigned>((H / 4 + 255) / 256);
   const long long walkers = std::max<long long>(1, (148 * 8) / gx);
@@ -272,10 +369,27 @@ static dim3 column_walk_grid(long long rows, long long H) {
 }
 
 int activation_forward(Context &ctx, const float *z, float *out, long long rows, long long H, uint32_t af, const float *col_scale,
-                       const float *col_shift, const uint8_t *mask, float keep_scale) {
+                       const float *col_shift, const uint8_t *mask, float keep_scale, const PanelSink *sink) {
   ctx.begin(TC_ELEMENTWISE);
   const bool vec4 = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(z) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
                     ((reinterpret_cast<uintptr_t>(col_scale) & 15) == 0) && ((reinterpret_cast<uintptr_t>(col_shift) & 15) == 0);
+  if (sink != nullptr) {
+    if (!vec4 || (H & 7) != 0 || (rows & 7) != 0) return MYEA_E_INVALID;
+    const dim3 grid = column_walk_grid8(rows, H);
+#define MYEA_AF_CASE(A) case A: activation_forward_panels_kernel<A><<<grid, 256, 0, ctx.stream>>>(z, out, rows, H, col_scale, col_shift, mask, keep_scale, *sink); break
+    switch (af) {
+      MYEA_AF_CASE(MYEA_AF_TANH);
+      MYEA_AF_CASE(MYEA_AF_SIGMOID);
+      MYEA_AF_CASE(MYEA_AF_RELU);
+      MYEA_AF_CASE(MYEA_AF_LEAKY_RELU);
+      MYEA_AF_CASE(MYEA_AF_ELU);
+      MYEA_AF_CASE(MYEA_AF_SELU);
+      default: activation_forward_panels_kernel<MYEA_AF_LINEAR><<<grid, 256, 0, ctx.stream>>>(z, out, rows, H, col_scale, col_shift, mask, keep_scale, *sink); break;
+    }
+#undef MYEA_AF_CASE
+    ctx.end(TC_ELEMENTWISE);
+    return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+  }
   const long long total = rows * (vec4 ? H / 4 : H);
   const int blocks = static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, 148 * 16)));
   if (vec4) {
@@ -439,10 +553,10 @@ __global__ void __launch_bounds__(256) norm_backward_apply_cols_kernel(const flo
 }
 
 int norm_backward(Context &ctx, const float *z, const float *delta_af, float *delta_out, long long rows, long long H,
-                  const NormParams &np, const SumHook *hook) {
+                  const NormParams &np, const SumHook *hook, int fused_chunks, const PanelSink *sink) {
   ctx.begin(TC_NORM);
-  const int chunks = pick_chunks(rows, H, (H % 4 == 0) ? 4 : 1, np.chunks);
-  launch_column_reduce<RK_NORM_BWD>(ctx, z, delta_af, np.mean, rows, H, chunks, np.partial);
+  const int chunks = fused_chunks > 0 ? fused_chunks : pick_chunks(rows, H, (H % 4 == 0) ? 4 : 1, np.chunks);
+  if (fused_chunks <= 0) launch_column_reduce<RK_NORM_BWD>(ctx, z, delta_af, np.mean, rows, H, chunks, np.partial);
   float *coef = np.partial + 2ll * np.chunks * H;  // [3][H] behind the partial sums
   const float *global = nullptr;
   long long rows_total = rows;
@@ -460,7 +574,11 @@ int norm_backward(Context &ctx, const float *z, const float *delta_af, float *de
                     ((reinterpret_cast<uintptr_t>(delta_out) & 15) == 0);
   const long long total = rows * (vec4 ? H / 4 : H);
   const int blocks = static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, 148 * 16)));
-  if (vec4 && (reinterpret_cast<uintptr_t>(np.mean) & 15) == 0 && (reinterpret_cast<uintptr_t>(coef) & 15) == 0)
+  const bool cols_ok = vec4 && (reinterpret_cast<uintptr_t>(np.mean) & 15) == 0 && (reinterpret_cast<uintptr_t>(coef) & 15) == 0;
+  if (sink != nullptr && !(cols_ok && (H & 7) == 0 && (rows & 7) == 0)) return MYEA_E_INVALID;
+  if (sink != nullptr)
+    norm_backward_apply_panels_kernel<<<column_walk_grid8(rows, H), 256, 0, ctx.stream>>>(z, delta_af, delta_out, rows, H, np.mean, coef, *sink);
+  else if (cols_ok)
     norm_backward_apply_cols_kernel<<<column_walk_grid(rows, H), 256, 0, ctx.stream>>>(z, delta_af, delta_out, rows, H, np.mean, coef);
   else if (vec4)
     norm_backward_apply_kernel<4><<<blocks, 256, 0, ctx.stream>>>(z, delta_af, delta_out, rows, H, np.mean, coef);

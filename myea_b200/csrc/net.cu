@@ -287,7 +287,10 @@ static int allocate_buffers(myea_b200_net *net) {
     RC(dev_alloc(net, &net->norm_mean_avg, U));
     RC(dev_alloc(net, &net->norm_sigma_avg, U));
     RC(dev_alloc(net, &net->norm_stats, U * 6));
-    RC(dev_alloc(net, &net->norm_partial, static_cast<size_t>(2 * net->reduce_chunks + 5) * max_h));  // partial sums | 3 coefficients | 2 cross-GPU sums
+    // partial sums of up to norm_chunks row blocks (the contractions' epilogues emit one per 32 rows) | 3 coefficients |
+    // 2 cross-GPU sums
+    net->norm_chunks = static_cast<int>(std::max<long long>(net->reduce_chunks, (rows + 31) / 32));
+    RC(dev_alloc(net, &net->norm_partial, static_cast<size_t>(2 * net->norm_chunks + 5) * max_h));
     for (size_t l = 1; l < net->layers.size(); ++l) {
       LayerPlan &L = net->layers[l];
       if (!L.has_norm) continue;
@@ -311,7 +314,7 @@ static int allocate_buffers(myea_b200_net *net) {
       np.col_scale = net->norm_stats + 4 * U + o;
       np.col_shift = net->norm_stats + 5 * U + o;
       np.partial = net->norm_partial;
-      np.chunks = net->reduce_chunks;
+      np.chunks = net->norm_chunks;
     }
   }
   RC(dev_alloc(net, &net->reduce_partial, static_cast<size_t>(net->reduce_chunks) * max_h));
@@ -496,7 +499,12 @@ int fc_product_forward(myea_b200_net *net, LayerPlan &L, const float *input, lon
   if (fc_uses_shared_panels(net, L, rows)) {
     // while training, the same pass also writes the column readings the backward contractions will want
     const bool tr = net->training;
-    RC(gemm_prepare_shared(net->ctx, input, L.n_in, rows, L.n_in, L.in_panel_mem, PANEL_ROLE_A, &L.in_rows, PANEL_ROLE_B, tr ? &L.in_cols : nullptr));
+    if (L.in_ready_src == input && L.in_ready_rows == rows) {
+      // the kernel that produced `input` has written these panels already (fc_forward of the layer before)
+    } else {
+      RC(gemm_prepare_shared(net->ctx, input, L.n_in, rows, L.n_in, L.in_panel_mem, PANEL_ROLE_A, &L.in_rows, PANEL_ROLE_B, tr ? &L.in_cols : nullptr));
+    }
+    L.in_ready_src = nullptr;
     if (!L.w_prepared) RC(fc_prepare_weights(net, L));
     L.w_prepared = false;
     L.in_valid = L.w_valid = tr;
@@ -512,7 +520,8 @@ int fc_product_forward(myea_b200_net *net, LayerPlan &L, const float *input, lon
 
 int fc_product_backward(myea_b200_net *net, LayerPlan &N, long long rows, const Epilogue &e) {
   if (N.shared_panels && N.w_valid) {
-    RC(gemm_prepare_shared(net->ctx, N.errors, N.n_out, rows, N.n_out, N.d_panel_mem, PANEL_ROLE_A, &N.d_rows, PANEL_ROLE_A, &N.d_cols));
+    if (!N.d_valid)  // (the normalization backward of N may have written them already)
+      RC(gemm_prepare_shared(net->ctx, N.errors, N.n_out, rows, N.n_out, N.d_panel_mem, PANEL_ROLE_A, &N.d_rows, PANEL_ROLE_A, &N.d_cols));
     N.d_valid = true;
     return gemm_panels(net->ctx, N.d_rows, 0, rows, N.w_cols, 0, N.n_in, e);
   }
@@ -526,13 +535,38 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
   e.C = L.summations;
   e.ldc = L.n_out;
   e.bias = L.use_bias ? net->params + L.idx.first_bias_connection_index : nullptr;
+  // batch statistics: the contraction's epilogue leaves the column sums of every 32-row block behind, where it can
+  int fused_chunks = 0;
+  if (L.has_norm && net->training) {
+    Epilogue probe = e;
+    probe.stats_kind = 1;
+    probe.col_stats = L.norm.partial;
+    probe.stats_blocks = (rows + 31) / 32;
+    if (probe.stats_blocks <= L.norm.chunks && epilogue_takes_stats(net->ctx, probe, L.n_out)) {
+      e = probe;
+      fused_chunks = static_cast<int>(probe.stats_blocks);
+    }
+  }
   RC(fc_product_forward(net, L, input, rows, e));
+  const size_t li = static_cast<size_t>(&L - net->layers.data());
+  // the layer that reads this one's output from shared operand panels gets them from the activation kernel
+  PanelSink sink;
+  bool use_sink = false;
+  if (li + 1 < net->layers.size() && L.desc.type_activation_function != MYEA_AF_SOFTMAX && (rows & 7) == 0 && (L.n_out & 7) == 0 &&
+      net->ctx.gemm_engine == 0) {
+    LayerPlan &N = net->layers[li + 1];
+    if (N.type == MYEA_LAYER_FULLY_CONNECTED && N.input_layer == static_cast<int>(li) && fc_uses_shared_panels(net, N, rows)) {
+      shared_panel_layout(N.in_panel_mem, rows, N.n_in, PANEL_ROLE_A, &N.in_rows, PANEL_ROLE_B, net->training ? &N.in_cols : nullptr, &sink);
+      N.in_ready_src = L.values;
+      N.in_ready_rows = rows;
+      use_sink = true;
+    }
+  }
   const float *cs = nullptr, *ch = nullptr;
   if (L.has_norm) {
     // data-parallel ranks exchange the column sums here; the next layer's weight panels depend on nothing that is in
     // flight and are made while the sums travel
     struct Next { myea_b200_net *net; LayerPlan *layer; } next{net, nullptr};
-    const size_t li = static_cast<size_t>(&L - net->layers.data());
     if (li + 1 < net->layers.size()) {
       LayerPlan &N = net->layers[li + 1];
       if (N.type == MYEA_LAYER_FULLY_CONNECTED && !N.w_prepared && fc_uses_shared_panels(net, N, rows)) next.layer = &N;
@@ -540,7 +574,8 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
     OverlapWork work;
     work.arg = &next;
     work.run = [](void *arg) { Next *p = static_cast<Next *>(arg); return fc_prepare_weights(p->net, *p->layer); };
-    RC(norm_forward_stats(net->ctx, L.summations, rows, L.n_out, L.norm, net->training ? 1 : 0, &net->hook, next.layer != nullptr ? &work : nullptr));
+    RC(norm_forward_stats(net->ctx, L.summations, rows, L.n_out, L.norm, net->training ? 1 : 0, &net->hook, next.layer != nullptr ? &work : nullptr,
+                          fused_chunks));
     cs = L.norm.col_scale;
     ch = L.norm.col_shift;
   }
@@ -550,7 +585,11 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
   }
   const uint8_t *mask = (net->training && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
   const float scale = net->training ? (mask != nullptr ? L.keep_scale : 1.f) : L.infer_scale;
-  RC(activation_forward(net->ctx, L.summations, L.values, rows, L.n_out, L.desc.type_activation_function, cs, ch, mask, scale));
+  if (use_sink && ((reinterpret_cast<uintptr_t>(cs) | reinterpret_cast<uintptr_t>(ch)) & 15) != 0) {  // unaligned coefficients: the plain kernel, and the reader splits
+    use_sink = false;
+    net->layers[li + 1].in_ready_src = nullptr;
+  }
+  RC(activation_forward(net->ctx, L.summations, L.values, rows, L.n_out, L.desc.type_activation_function, cs, ch, mask, scale, use_sink ? &sink : nullptr));
   return MYEA_OK;
 }
 
@@ -581,7 +620,7 @@ static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cu
   net->active_B = static_cast<long long>(batch);
   const long long rows = net->T * net->active_B;
   const int n = static_cast<int>(net->layers.size());
-  for (auto &L : net->layers) L.w_prepared = false;
+  for (auto &L : net->layers) { L.w_prepared = false; L.in_ready_src = nullptr; }
   if (kind == cudaMemcpyHostToDevice) {
     // inputs from the host: copy them on the side stream (once everything already queued has finished with d_input)
     // and split every large layer's weights meanwhile - the copy takes longer than all those passes together
@@ -706,12 +745,32 @@ int fc_backward_from_fc(myea_b200_net *net, LayerPlan &L, const LayerPlan &next,
   Epilogue e;
   e.C = dst;
   e.ldc = next.n_in;
+  L.bwd_fused_chunks = 0;
   if (fuse_derivative) {
-    e.deriv_af = L.desc.type_activation_function;
-    e.aux_pre = L.summations;
-    e.aux_y = L.values;
+    const uint32_t af = L.desc.type_activation_function;
+    e.deriv_af = af;
+    // the derivative of tanh / sigmoid is a function of the output alone, that of ReLU of the pre-activation alone
+    // (Activation_Functions.hpp); an array the derivative does not read is not fetched
+    const bool wants_pre = !(af == MYEA_AF_TANH || af == MYEA_AF_SIGMOID), wants_y = !(af == MYEA_AF_RELU || af == MYEA_AF_LEAKY_RELU);
+    e.aux_pre = wants_pre ? L.summations : nullptr;
+    e.aux_y = wants_y ? L.values : nullptr;
     e.ld_aux = L.n_out;
-    if (L.has_norm) { e.col_scale = L.norm.col_scale; e.col_shift = L.norm.col_shift; }
+    if (L.has_norm) {
+      if (wants_pre) { e.col_scale = L.norm.col_scale; e.col_shift = L.norm.col_shift; }
+      // the sums of the normalization backward (error, error x centred summation) from the same epilogue
+      Epilogue probe = e;
+      probe.stats_kind = 2;
+      probe.aux_pre = L.summations;
+      probe.col_scale = L.norm.col_scale;
+      probe.col_shift = L.norm.col_shift;
+      probe.col_stats = L.norm.partial;
+      probe.col_mean = L.norm.mean;
+      probe.stats_blocks = (rows + 31) / 32;
+      if (next_errors == next.errors && probe.stats_blocks <= L.norm.chunks && epilogue_takes_stats(net->ctx, probe, L.n_out)) {
+        e = probe;
+        L.bwd_fused_chunks = static_cast<int>(probe.stats_blocks);
+      }
+    }
   }
   if (next_errors != next.errors) {  // (not the case today) an error array other than the layer's own: no shared panels
     Operand a{next_errors, rows, next.n_out, next.n_out, 1};
@@ -722,7 +781,16 @@ int fc_backward_from_fc(myea_b200_net *net, LayerPlan &L, const LayerPlan &next,
 }
 
 int fc_finish_backward(myea_b200_net *net, LayerPlan &L, long long rows) {
-  if (L.has_norm) return norm_backward(net->ctx, L.summations, L.deriv, L.errors, rows, L.n_out, L.norm, &net->hook);
+  if (!L.has_norm) return MYEA_OK;
+  // the layer's errors are read next by the error propagation below it (rows) and by its weight derivative (columns),
+  // both from shared operand panels: the kernel that writes the errors writes those panels as well
+  PanelSink sink;
+  const bool use_sink = L.shared_panels && L.in_valid && net->ctx.gemm_engine == 0 && (rows & 7) == 0 && (L.n_out & 7) == 0 &&
+                        gemm_takes_mn_major(net->ctx, rows, L.n_out) && gemm_takes_mn_major(net->ctx, rows, L.n_in);
+  if (use_sink) shared_panel_layout(L.d_panel_mem, rows, L.n_out, PANEL_ROLE_A, &L.d_rows, PANEL_ROLE_A, &L.d_cols, &sink);
+  RC(norm_backward(net->ctx, L.summations, L.deriv, L.errors, rows, L.n_out, L.norm, &net->hook, L.bwd_fused_chunks, use_sink ? &sink : nullptr));
+  L.bwd_fused_chunks = 0;
+  if (use_sink) L.d_valid = true;
   return MYEA_OK;
 }
 

@@ -46,6 +46,9 @@ struct LayerPlan {
   bool in_valid = false, w_valid = false, d_valid = false;
   bool w_prepared = false;  // the weight panels have already been made in this forward pass (hoisted under the input copy)
   const float *in_src = nullptr;  // the array the input panels were made from
+  const float *in_ready_src = nullptr;  // set by the producer of this layer's input when IT has written the input panels
+  long long in_ready_rows = 0;
+  int bwd_fused_chunks = 0;       // row blocks whose normalization-backward sums the error-propagation epilogue has emitted
 };
 
 // z = input * W^T of a fully connected layer and D = errors * W (error on the layer's inputs), from the layer's shared
@@ -77,6 +80,7 @@ struct myea_b200_net {
   float *norm_partial = nullptr;
   float *reduce_partial = nullptr;
   int reduce_chunks = 64;
+  int norm_chunks = 64;        // row blocks the normalization partial-sum workspace has room for
   float *d_input = nullptr;    // [T*B, inputs]
   float *d_desired = nullptr;  // [T*B, outputs]
   myea::GemmScratch scratch;

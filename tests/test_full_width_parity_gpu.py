@@ -201,7 +201,15 @@ def _check_case(name, wl, check_formula, truth="reference"):
     for l in range(len(wl.layers)):
         assert gpu.layer_index(l).as_tuple() == cpu.layer_index(l).as_tuple()
     # loss and counts
-    assert got["loss"][1] == want["loss"][1] and got["loss"][2] == want["loss"][2]
+    assert got["loss"][1] == want["loss"][1]
+    # accuracy hit count: exact, except for outputs that sit within 1e-4 of the hit threshold |y - t| = accuracy_variance
+    # (a quarter of a million outputs at these sizes: one of them within rounding distance of the threshold is expected)
+    borderline = 0
+    if wl.desc.type_accuracy_function == capi.ACC_DISTANCE:
+        var = wl.desc.accuracy_variance if wl.desc.accuracy_variance > 0 else 0.49
+        t0 = min(int(wl.desc.number_time_delays), wl.T) if wl.T > 1 else 0
+        borderline = int((np.abs(np.abs(want["output"][t0:].astype(np.float64) - Y[t0:]) - var) < 1e-4).sum())
+    assert abs(got["loss"][2] - want["loss"][2]) <= borderline, (got["loss"], want["loss"], borderline)
     assert abs(got["loss"][0] - want["loss"][0]) <= TOL * abs(want["loss"][0])
     record["loss_rel_err"] = abs(got["loss"][0] - want["loss"][0]) / abs(want["loss"][0])
     record["output_rel_err"] = rel_err(got["output"], want["output"])
