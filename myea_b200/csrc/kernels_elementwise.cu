@@ -102,28 +102,47 @@ static void launch_column_reduce(Context &ctx, const float *x, const float *y, c
 // The "variance" buffers of the reference hold the standard deviation sqrt(E[x^2] - mean^2 + eps); the running
 // averages are exponential averages of mean and standard deviation; r and d use the ALREADY UPDATED averages.
 // ---------------------------------------------------------------------------------------------------------
+// The two column sums of partial[2][chunks][H] for column j = blockIdx.x * 32 + (threadIdx.x & 31): blocks of 256
+// threads = 32 columns x 8 chunk lanes (the contractions' epilogues leave one chunk per 32 rows: 128 of them for a batch
+// of 4096, too many for one thread per column to walk alone).  Valid in the threads with threadIdx.x < 32.
+__device__ __forceinline__ void chunk_sums(const float *__restrict__ partial, int chunks, long long H, long long j, float &s, float &q) {
+  __shared__ float sh[2][8][33];
+  const int cl = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  float a = 0.f, b = 0.f;
+  if (j < H) {
+#pragma unroll 4
+    for (int c = rl; c < chunks; c += 8) { a += partial[(0ll * chunks + c) * H + j]; b += partial[(1ll * chunks + c) * H + j]; }
+  }
+  sh[0][rl][cl] = a;
+  sh[1][rl][cl] = b;
+  __syncthreads();
+  s = 0.f; q = 0.f;
+  if (rl == 0) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r) { s += sh[0][r][cl]; q += sh[1][r][cl]; }
+  }
+}
+
 // sums[2][H] = chunk sums of partial[2][chunks][H]: the message of the cross-GPU all-reduce
-__global__ void chunk_sum_kernel(const float *__restrict__ partial, int chunks, long long H, float *__restrict__ sums) {
-  const long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  if (j >= H) return;
-  float s = 0.f, q = 0.f;
-#pragma unroll 8
-  for (int c = 0; c < chunks; ++c) { s += partial[(0ll * chunks + c) * H + j]; q += partial[(1ll * chunks + c) * H + j]; }
+__global__ void __launch_bounds__(256) chunk_sum_kernel(const float *__restrict__ partial, int chunks, long long H, float *__restrict__ sums) {
+  const long long j = blockIdx.x * 32ll + (threadIdx.x & 31);
+  float s, q;
+  chunk_sums(partial, chunks, H, j, s, q);
+  if (threadIdx.x >= 32 || j >= H) return;
   sums[j] = s;
   sums[H + j] = q;
 }
 
 // `rows` is the batch the statistics are taken over: the global batch when the column sums were all-reduced (chunks == 1
 // then, partial = the reduced [2][H] sums).
-__global__ void norm_stats_finalize_kernel(const float *__restrict__ partial, int chunks, long long rows, long long H,
-                                           NormParams np, int training) {
-  const long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  if (j >= H) return;
+__global__ void __launch_bounds__(256) norm_stats_finalize_kernel(const float *__restrict__ partial, int chunks, long long rows, long long H,
+                                                                  NormParams np, int training) {
+  const long long j = blockIdx.x * 32ll + (threadIdx.x & 31);
+  float s = 0.f, q = 0.f;
+  if (training) chunk_sums(partial, chunks, H, j, s, q);
+  if (threadIdx.x >= 32 || j >= H) return;
   float mean, sigma, r = 1.f, d = 0.f;
   if (training) {
-    float s = 0.f, q = 0.f;
-  #pragma unroll 8
-  for (int c = 0; c < chunks; ++c) { s += partial[(0ll * chunks + c) * H + j]; q += partial[(1ll * chunks + c) * H + j]; }
     const float scale = 1.0f / static_cast<float>(rows);
     mean = s * scale;
     sigma = sqrtf(q * scale - mean * mean + np.epsilon);
@@ -168,7 +187,7 @@ int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H
     if (hook != nullptr && hook->world > 1) {
       // sharded batch: sum the column sums over the ranks, then every rank finalizes the same global statistics
       float *g = np.partial + 2ll * np.chunks * H + 3 * H;
-      chunk_sum_kernel<<<static_cast<unsigned>((H + 255) / 256), 256, 0, ctx.stream>>>(np.partial, chunks, H, g);
+      chunk_sum_kernel<<<static_cast<unsigned>((H + 31) / 32), 256, 0, ctx.stream>>>(np.partial, chunks, H, g);
       ctx.end(TC_NORM, launches + 1);
       if (hook->begin != nullptr && hook->end != nullptr && meanwhile != nullptr && meanwhile->run != nullptr && !ctx.profiling) {
         // the exchange is pure latency (a few KB): queue the caller's independent work beside it
@@ -186,7 +205,7 @@ int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H
       rows_total = rows * hook->world;
     }
   }
-  norm_stats_finalize_kernel<<<static_cast<unsigned>((H + 255) / 256), 256, 0, ctx.stream>>>(sums, chunks, rows_total, H, np, training);
+  norm_stats_finalize_kernel<<<static_cast<unsigned>((H + 31) / 32), 256, 0, ctx.stream>>>(sums, chunks, rows_total, H, np, training);
   ctx.end(TC_NORM, launches);
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
@@ -471,13 +490,12 @@ int softmax_forward(Context &ctx, const float *z, float *out, long long rows, lo
 // ---------------------------------------------------------------------------------------------------------
 // `global` (may be null): the column sums added over all ranks of a sharded batch; d_gamma / d_beta take the LOCAL sums
 // (the derivative buffers are summed over ranks later), d_mean / d_sigma and `rows` are those of the whole batch.
-__global__ void norm_backward_finalize_kernel(const float *__restrict__ partial, int chunks, const float *__restrict__ global,
-                                              long long rows, long long H, NormParams np, float *__restrict__ coef) {
-  const long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  if (j >= H) return;
-  float s1 = 0.f, s2 = 0.f;
-#pragma unroll 8
-  for (int c = 0; c < chunks; ++c) { s1 += partial[(0ll * chunks + c) * H + j]; s2 += partial[(1ll * chunks + c) * H + j]; }
+__global__ void __launch_bounds__(256) norm_backward_finalize_kernel(const float *__restrict__ partial, int chunks, const float *__restrict__ global,
+                                                                     long long rows, long long H, NormParams np, float *__restrict__ coef) {
+  const long long j = blockIdx.x * 32ll + (threadIdx.x & 31);
+  float s1, s2;
+  chunk_sums(partial, chunks, H, j, s1, s2);
+  if (threadIdx.x >= 32 || j >= H) return;
   const float sigma = np.sigma[j], r = np.r[j], d = np.d[j], g = np.gamma[j];
   const float k = r / sigma;
   np.d_beta[j] += s1;
@@ -562,14 +580,14 @@ int norm_backward(Context &ctx, const float *z, const float *delta_af, float *de
   long long rows_total = rows;
   if (hook != nullptr && hook->world > 1) {
     float *g = coef + 3 * H;
-    chunk_sum_kernel<<<static_cast<unsigned>((H + 255) / 256), 256, 0, ctx.stream>>>(np.partial, chunks, H, g);
+    chunk_sum_kernel<<<static_cast<unsigned>((H + 31) / 32), 256, 0, ctx.stream>>>(np.partial, chunks, H, g);
     ctx.end(TC_NORM, 2);
     if (hook->all_reduce(hook->user, g, static_cast<size_t>(2 * H)) != MYEA_OK) return MYEA_E_COMM;
     ctx.begin(TC_NORM);
     global = g;
     rows_total = rows * hook->world;
   }
-  norm_backward_finalize_kernel<<<static_cast<unsigned>((H + 255) / 256), 256, 0, ctx.stream>>>(np.partial, chunks, global, rows_total, H, np, coef);
+  norm_backward_finalize_kernel<<<static_cast<unsigned>((H + 31) / 32), 256, 0, ctx.stream>>>(np.partial, chunks, global, rows_total, H, np, coef);
   const bool vec4 = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(z) & 15) == 0) && ((reinterpret_cast<uintptr_t>(delta_af) & 15) == 0) &&
                     ((reinterpret_cast<uintptr_t>(delta_out) & 15) == 0);
   const long long total = rows * (vec4 ? H / 4 : H);
