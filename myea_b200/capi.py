@@ -91,10 +91,11 @@ def lstm(blocks, cells_per_block=1, bidirectional=False, dropout=DROP_NONE, p=(0
     return d
 
 
-def residual(block_depth, dropout=DROP_NONE, p=(0.0, 0.0, 0.0)):
+def residual(block_depth, dropout=DROP_NONE, p=(0.0, 0.0, 0.0), normalization=NORM_NONE):
     d = LayerDesc()
     d.type_layer = LAYER_RESIDUAL
     d.unit_parameters[0] = block_depth
+    d.type_normalization = normalization   # of the block's output, before ShakeDrop and the skip add
     d.use_layer_normalization_before_activation = 1
     d.type_dropout = dropout
     for i in range(3):

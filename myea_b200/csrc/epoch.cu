@@ -102,10 +102,10 @@ extern "C" int myea_b200_train_epoch(myea_handle net, const uint64_t *order, uin
   const uint64_t B = static_cast<uint64_t>(net->B);
   if (mini_batch_size == 0) return MYEA_E_INVALID;
   // Train_Batch_BP walks a mini-batch in sub-batches of the network's batch size, the last one shorter
-  // (Dataset.cpp:667-691); the last mini-batch of the epoch may be shorter as well.  Short batches need a feed-forward
-  // network (see myea_b200_forward).
-  if ((mini_batch_size % B != 0 || number_examples % mini_batch_size != 0) && (net->T != 1 || net->comm != nullptr)) {
-    net->ctx.error = "train_epoch: a recurrent (or multi-GPU) network needs a mini-batch that is a multiple of its batch size and divides the number of examples";
+  // (Dataset.cpp:667-691); the last mini-batch of the epoch may be shorter as well.  Ranks of a data-parallel job take
+  // full batches only (see myea_b200_forward).
+  if ((mini_batch_size % B != 0 || number_examples % mini_batch_size != 0) && net->comm != nullptr) {
+    net->ctx.error = "train_epoch: a multi-GPU network needs a mini-batch that is a multiple of its batch size and divides the number of examples";
     return MYEA_E_UNSUPPORTED;
   }
   // With a communicator the derivative buckets are summed over the ranks inside update_derivative_weight, so a
@@ -152,8 +152,8 @@ extern "C" int myea_b200_evaluate(myea_handle net, const uint64_t *order, uint64
   if (net == nullptr || number_examples == 0) return MYEA_E_INVALID;
   if (net->ds_examples == 0) { net->ctx.error = "no dataset on the device (myea_b200_dataset_set)"; return MYEA_E_INVALID; }
   const uint64_t B = static_cast<uint64_t>(net->B);
-  if (number_examples % B != 0 && (net->T != 1 || net->comm != nullptr)) {
-    net->ctx.error = "evaluate: a recurrent (or multi-GPU) network needs a number of examples that is a multiple of its batch size";
+  if (number_examples % B != 0 && net->comm != nullptr) {
+    net->ctx.error = "evaluate: a multi-GPU network needs a number of examples that is a multiple of its batch size";
     return MYEA_E_UNSUPPORTED;
   }
   if (cudaSetDevice(net->ctx.device) != cudaSuccess) return MYEA_E_CUDA;

@@ -600,8 +600,9 @@ int lstm_backward(myea_b200_net *net, LayerPlan &L) {
 }
 
 // error of the LSTM layer L propagated to the outputs of the layer feeding it: prev_deriv [T*B, n_in] = sum over
-// directions of dgates [T*B, 4C] * W_in [4C, n_in]
-int lstm_backward_to_input(myea_b200_net *net, LayerPlan &L, float *prev_deriv, const LayerPlan &prev) {
+// directions of dgates [T*B, 4C] * W_in [4C, n_in].  `finish` (optional) carries the activation derivative of a fully
+// connected layer below, applied by the epilogue of the last direction's contraction to the complete sum.
+int lstm_backward_to_input(myea_b200_net *net, LayerPlan &L, float *prev_deriv, const LayerPlan &prev, const Epilogue *finish) {
   LstmPlan *P = L.lstm;
   Context &ctx = net->ctx;
   const long long rows = net->T * net->B, C = P->C, n_in = P->n_in;
@@ -618,9 +619,11 @@ int lstm_backward_to_input(myea_b200_net *net, LayerPlan &L, float *prev_deriv, 
     LRC(gemm_prepare_into(ctx, Operand{w + off.z_in, n_in, C, 1, P->stride}, pwt, 0, 0));
     for (int g = 0; g < 3; ++g) LRC(gemm_prepare_into(ctx, Operand{w + off.in[g], n_in, C, 1, P->stride}, pwt, 0, (g + 1) * Cp));
     Epilogue e;
+    if (finish != nullptr && d == P->dirs - 1) e = *finish;
     e.C = prev_deriv;
     e.ldc = n_in;
-    e.accumulate = d > 0 ? 1 : 0;
+    if (d > 0 && finish != nullptr) { e.addend = prev_deriv; e.ld_addend = n_in; }  // the addend enters before the derivative
+    else e.accumulate = d > 0 ? 1 : 0;
     LRC(gemm_panels(ctx, pd, 0, rows, pwt, 0, n_in, e));
   }
   return MYEA_OK;

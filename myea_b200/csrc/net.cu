@@ -18,7 +18,7 @@ int lstm_create(myea_b200_net *net, LayerPlan &L);
 void lstm_destroy(LayerPlan &L);
 int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long n_in);
 int lstm_backward(myea_b200_net *net, LayerPlan &L);
-int lstm_backward_to_input(myea_b200_net *net, LayerPlan &L, float *prev_deriv, const LayerPlan &prev);
+int lstm_backward_to_input(myea_b200_net *net, LayerPlan &L, float *prev_deriv, const LayerPlan &prev, const Epilogue *finish = nullptr);
 int lstm_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float *input, long long n_in);
 int lstm_set_zoneout(myea_b200_net *net, LayerPlan &L, const uint8_t *state, const uint8_t *output, uint64_t count);
 float *lstm_output_errors(LayerPlan &L);
@@ -61,6 +61,15 @@ void comm_destroy(myea_b200_net *net);
 static int fail(myea_b200_net *net, int code, const char *msg) {
   net->ctx.error = msg;
   return code;
+}
+
+static bool layer_in_block(const myea_b200_net *net, int l, int *block_layer) {
+  for (int r = 1; r < static_cast<int>(net->layers.size()); ++r)
+    if (net->layers[r].type == MYEA_LAYER_RESIDUAL && l > r && l <= r + net->layers[r].block_depth) {
+      if (block_layer) *block_layer = r;
+      return true;
+    }
+  return false;
 }
 
 template <typename T>
@@ -117,7 +126,12 @@ int myea::build_index_map(myea_b200_net *net) {
       if (L.block_depth < 1 || l + L.block_depth >= n) return fail(net, MYEA_E_INVALID, "residual block runs past the output layer");
       for (int k = 1; k <= L.block_depth; ++k)
         if (net->layers[l + k].type != MYEA_LAYER_FULLY_CONNECTED) return fail(net, MYEA_E_UNSUPPORTED, "residual blocks of fully connected layers only");
-      L.n_out = net->layers[l + L.block_depth].n_out;
+      // the block output is as wide as the wider of the shortcut and the block's last layer (zero-padded identity); the
+      // shortcut is the layer before, or the residual layer of the block that ends there
+      uint32_t feeder = l - 1;
+      for (uint32_t q = 1; q < l; ++q)
+        if (net->layers[q].type == MYEA_LAYER_RESIDUAL && q + net->layers[q].block_depth == l - 1) feeder = q;
+      L.n_out = std::max(net->layers[feeder].n_out, net->layers[l + L.block_depth].n_out);
     }
   }
   // inputs: a layer reads the layer before it; the first layer of a residual block reads the layer before the
@@ -183,31 +197,29 @@ int myea::build_index_map(myea_b200_net *net) {
   for (uint32_t l = 1; l < n; ++l) net->any_norm = net->any_norm || d.layers[l].type_normalization != MYEA_NORM_NONE;
   net->total_norm_units = 0;
   if (net->any_norm) {
+    // units a layer normalizes (Prepare__Normalized__Layer / ..__Residual_Layer, Neural_Network__Layer_Normalization.cpp:43-154):
+    // its own outputs; inside a residual block its INPUT (the block runs normalization -> activation -> weights); for a
+    // residual layer the outputs of the block's last layer
     uint64_t units = 0;
     for (uint32_t l = 0; l < n; ++l) {
-      net->layers[l].norm_unit_offset = static_cast<long long>(units);
-      if (net->layers[l].type == MYEA_LAYER_LSTM) return fail(net, MYEA_E_UNSUPPORTED, "normalization in a network with LSTM layers is not built");
-      units += net->layers[l].n_out;
+      LayerPlan &L = net->layers[l];
+      L.norm_unit_offset = static_cast<long long>(units);
+      if (L.type == MYEA_LAYER_LSTM) return fail(net, MYEA_E_UNSUPPORTED, "normalization in a network with LSTM layers is not built");
+      long long own = L.n_out;
+      if (L.type == MYEA_LAYER_RESIDUAL) own = net->layers[l + L.block_depth].n_out;
+      else if (l > 0 && layer_in_block(net, static_cast<int>(l), nullptr)) own = L.n_in;
+      L.idx.number_units_norm = static_cast<uint64_t>(own);
+      units += static_cast<uint64_t>(own);
     }
     net->total_norm_units = units;
     for (uint32_t l = 0; l < n; ++l) {
       LayerPlan &L = net->layers[l];
       L.idx.scale_index = net->total_parameters + L.norm_unit_offset;
       L.idx.shift_index = net->total_parameters + units + L.norm_unit_offset;
-      L.idx.number_units_norm = L.n_out;
     }
     net->total_parameters += 2 * units;
   }
   return MYEA_OK;
-}
-
-static bool layer_in_block(const myea_b200_net *net, int l, int *block_layer) {
-  for (int r = 1; r < static_cast<int>(net->layers.size()); ++r)
-    if (net->layers[r].type == MYEA_LAYER_RESIDUAL && l > r && l <= r + net->layers[r].block_depth) {
-      if (block_layer) *block_layer = r;
-      return true;
-    }
-  return false;
 }
 
 static int allocate_buffers(myea_b200_net *net) {
@@ -273,6 +285,8 @@ static int allocate_buffers(myea_b200_net *net) {
       RC(dev_alloc(net, &L.values, rows * L.n_out));
       RC(dev_alloc(net, &L.deriv, rows * L.n_out));
       L.errors = L.deriv;
+      L.has_norm = L.desc.type_normalization != MYEA_NORM_NONE;  // normalization of the block's output before the skip add
+      if (L.has_norm) RC(dev_alloc(net, &L.summations, rows * L.n_out));
       if (L.desc.type_dropout == MYEA_DROPOUT_SHAKEDROP) {
         RC(dev_alloc(net, &L.shake_mask, net->B));
         RC(dev_alloc(net, &L.shake_alpha, net->B * L.n_out));
@@ -355,6 +369,8 @@ extern "C" int myea_b200_create(myea_handle *out, const myea_net_desc *desc, int
       cudaEventCreateWithFlags(&net->ev_input_free, cudaEventDisableTiming) != cudaSuccess)
     return fail(net, MYEA_E_CUDA, "cudaStreamCreate / cudaEventCreate failed");
   RC(myea::build_index_map(net));
+  net->full_pitch = net->T > 1;
+  for (const LayerPlan &L : net->layers) net->full_pitch = net->full_pitch || L.type == MYEA_LAYER_LSTM;
   RC(allocate_buffers(net));
   CK(cudaStreamSynchronize(net->ctx.stream));
   return MYEA_OK;
@@ -585,6 +601,16 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
   }
   const uint8_t *mask = (net->training && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
   const float scale = net->training ? (mask != nullptr ? L.keep_scale : 1.f) : L.infer_scale;
+  if (mask != nullptr && net->T > 1) {
+    // a recurrent network draws one mask per time step (mask[t][unit], Forward_Pass__Dropout__Bernoulli__Training__Loop,
+    // Neural_Network__Forward_Pass__Loop.cpp:4947-4970): one activation pass per step, each with its own mask row
+    if (use_sink) net->layers[li + 1].in_ready_src = nullptr;
+    const long long step_rows = rows / net->T;
+    for (long long t = 0; t < net->T; ++t)
+      RC(activation_forward(net->ctx, L.summations + t * step_rows * L.n_out, L.values + t * step_rows * L.n_out, step_rows, L.n_out,
+                            L.desc.type_activation_function, cs, ch, mask + t * L.n_out, scale, nullptr));
+    return MYEA_OK;
+  }
   if (use_sink && ((reinterpret_cast<uintptr_t>(cs) | reinterpret_cast<uintptr_t>(ch)) & 15) != 0) {  // unaligned coefficients: the plain kernel, and the reader splits
     use_sink = false;
     net->layers[li + 1].in_ready_src = nullptr;
@@ -596,15 +622,30 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
 }  // namespace myea
 
 // Forward_Pass(batch_size_received, ...) accepts any batch up to the allocated one (the last batch of
-// Dataset::Train_Batch_BP is smaller, Dataset.cpp:667-691).  Here: the full batch always; fewer rows for feed-forward
-// networks (one time step), whose buffers are plain [rows][units]; recurrent buffers are [T][B][units] with the
-// allocated B as pitch, so a recurrent network takes full batches only.
+// Dataset::Train_Batch_BP is smaller, Dataset.cpp:667-691).  A feed-forward network (one time step) keeps plain
+// [rows][units] buffers and simply runs fewer rows.  Recurrent buffers are [T][B][units] with the allocated B as the
+// pitch, as in the reference: a shorter batch fills the first rows of every time step, the rows behind them are
+// computed along as padding - zero inputs, zero output error, hence zero deltas and no share in any derivative - and
+// are not counted in the loss.
 static int batch_for_forward(myea_b200_net *net, uint64_t batch) {
   const long long b = static_cast<long long>(batch);
   if (b == net->B) return MYEA_OK;
   if (b < 1 || b > net->B) return fail(net, MYEA_E_INVALID, "batch must be between 1 and the batch size the network was created for");
-  if (net->T != 1) return fail(net, MYEA_E_UNSUPPORTED, "a recurrent network takes full batches only");
   if (net->comm != nullptr) return fail(net, MYEA_E_UNSUPPORTED, "with a communicator attached every rank takes full batches");
+  return MYEA_OK;
+}
+// rows the kernels of the step in flight run over, and the rows per time step among them
+static long long pitch_rows(const myea_b200_net *net) { return net->pitch(); }
+static long long step_rows_total(const myea_b200_net *net) { return net->T * pitch_rows(net); }
+// host or device block packed [T][active_B][units] -> [T][pitch][units], padding rows zeroed
+static int copy_batch_in(myea_b200_net *net, float *dst, const float *src, long long units, cudaMemcpyKind kind, cudaStream_t stream) {
+  const long long pitch = pitch_rows(net), b = net->active_B;
+  if (b == pitch) {
+    CK(cudaMemcpyAsync(dst, src, net->T * b * units * sizeof(float), kind, stream));
+    return MYEA_OK;
+  }
+  CK(cudaMemcpy2DAsync(dst, pitch * units * sizeof(float), src, b * units * sizeof(float), b * units * sizeof(float), net->T, kind, stream));
+  CK(cudaMemset2DAsync(dst + b * units, pitch * units * sizeof(float), 0, (pitch - b) * units * sizeof(float), net->T, stream));
   return MYEA_OK;
 }
 static int batch_in_flight(myea_b200_net *net, uint64_t batch) {
@@ -618,7 +659,7 @@ static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cu
   CK(cudaSetDevice(net->ctx.device));
   net->training = training != 0;
   net->active_B = static_cast<long long>(batch);
-  const long long rows = net->T * net->active_B;
+  const long long rows = step_rows_total(net);
   const int n = static_cast<int>(net->layers.size());
   for (auto &L : net->layers) { L.w_prepared = false; L.in_ready_src = nullptr; }
   if (kind == cudaMemcpyHostToDevice) {
@@ -626,7 +667,7 @@ static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cu
     // and split every large layer's weights meanwhile - the copy takes longer than all those passes together
     CK(cudaEventRecord(net->ev_input_free, net->ctx.stream));
     CK(cudaStreamWaitEvent(net->copy_stream, net->ev_input_free, 0));
-    CK(cudaMemcpyAsync(net->d_input, src, rows * net->layers[0].n_out * sizeof(float), kind, net->copy_stream));
+    RC(copy_batch_in(net, net->d_input, src, net->layers[0].n_out, kind, net->copy_stream));
     CK(cudaEventRecord(net->ev_input_ready, net->copy_stream));
     for (int l = 1; l < n; ++l) {
       LayerPlan &L = net->layers[l];
@@ -634,13 +675,12 @@ static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cu
     }
     CK(cudaStreamWaitEvent(net->ctx.stream, net->ev_input_ready, 0));
   } else {
-    CK(cudaMemcpyAsync(net->d_input, src, rows * net->layers[0].n_out * sizeof(float), kind, net->ctx.stream));
+    RC(copy_batch_in(net, net->d_input, src, net->layers[0].n_out, kind, net->ctx.stream));
   }
   for (int l = 1; l < n;) {
     LayerPlan &L = net->layers[l];
     const LayerPlan &in = net->layers[L.input_layer];
     if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
-      if (net->T > 1 && L.mask_bernoulli != nullptr) return fail(net, MYEA_E_UNSUPPORTED, "Bernoulli dropout on a recurrent network is not built");
       if (layer_in_block(net, l, nullptr)) return fail(net, MYEA_E_INVALID, "block layer outside its block");
       RC(fc_forward(net, L, in.values, rows));
       ++l;
@@ -670,27 +710,39 @@ static int compute_error_impl(myea_b200_net *net, uint64_t batch, const float *s
   RC(batch_in_flight(net, batch));
   CK(cudaSetDevice(net->ctx.device));
   LayerPlan &L = net->layers.back();
-  const long long rows = net->T * net->active_B;
+  const long long pitch = pitch_rows(net), rows = net->T * pitch;
   if (kind == cudaMemcpyHostToDevice) {
     // host targets: copy beside the forward pass still in flight on the main stream (the last use of d_desired by an
     // error kernel is behind ev_desired_free), and let the main stream wait for the copy only now
     CK(cudaStreamWaitEvent(net->copy_stream, net->ev_desired_free, 0));
-    CK(cudaMemcpyAsync(net->d_desired, src, rows * L.n_out * sizeof(float), kind, net->copy_stream));
+    RC(copy_batch_in(net, net->d_desired, src, L.n_out, kind, net->copy_stream));
     CK(cudaEventRecord(net->ev_desired_ready, net->copy_stream));
     CK(cudaStreamWaitEvent(net->ctx.stream, net->ev_desired_ready, 0));
   } else {
-    CK(cudaMemcpyAsync(net->d_desired, src, rows * L.n_out * sizeof(float), kind, net->ctx.stream));
+    RC(copy_batch_in(net, net->d_desired, src, L.n_out, kind, net->ctx.stream));
   }
   // Recurrent networks only score the steps t >= number_time_delays; earlier steps get a zero error
   // (RNN__Compute__Error, Neural_Network__Recurrent_Compute__Error__OpenMP.cpp:22-159).
   const long long t0 = net->T > 1 ? std::min<long long>(static_cast<long long>(net->desc.number_time_delays), net->T) : 0;
-  const long long skip = t0 * net->active_B;
-  if (skip > 0) RC(fill_zero(net->ctx, L.errors, skip * L.n_out));
-  if (rows > skip) {
-    const size_t off = static_cast<size_t>(skip) * L.n_out;
-    RC(output_error(net->ctx, L.summations + off, L.values + off, net->d_desired + off, L.errors + off, rows - skip, L.n_out,
-                    L.desc.type_activation_function, net->desc.type_loss_function, net->desc.type_accuracy_function,
-                    net->desc.accuracy_variance > 0.f ? net->desc.accuracy_variance : 0.49f, net->d_loss_acc, net->d_loss_count));
+  const float variance = net->desc.accuracy_variance > 0.f ? net->desc.accuracy_variance : 0.49f;
+  if (net->active_B == pitch) {
+    const long long skip = t0 * pitch;
+    if (skip > 0) RC(fill_zero(net->ctx, L.errors, skip * L.n_out));
+    if (rows > skip) {
+      const size_t off = static_cast<size_t>(skip) * L.n_out;
+      RC(output_error(net->ctx, L.summations + off, L.values + off, net->d_desired + off, L.errors + off, rows - skip, L.n_out,
+                      L.desc.type_activation_function, net->desc.type_loss_function, net->desc.type_accuracy_function, variance,
+                      net->d_loss_acc, net->d_loss_count));
+    }
+  } else {
+    // short batch of a recurrent network: every time step scores its first active_B rows, all other rows carry no error
+    RC(fill_zero(net->ctx, L.errors, rows * L.n_out));
+    for (long long t = t0; t < net->T; ++t) {
+      const size_t off = static_cast<size_t>(t * pitch) * L.n_out;
+      RC(output_error(net->ctx, L.summations + off, L.values + off, net->d_desired + off, L.errors + off, net->active_B, L.n_out,
+                      L.desc.type_activation_function, net->desc.type_loss_function, net->desc.type_accuracy_function, variance,
+                      net->d_loss_acc, net->d_loss_count));
+    }
   }
   CK(cudaEventRecord(net->ev_desired_free, net->ctx.stream));
   return MYEA_OK;
@@ -801,7 +853,7 @@ extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
   RC(batch_in_flight(net, batch));
   if (!net->training) return fail(net, MYEA_E_INVALID, "can not back propagate in inference mode");
   CK(cudaSetDevice(net->ctx.device));
-  const long long rows = net->T * net->active_B;
+  const long long rows = step_rows_total(net);
   const int n = static_cast<int>(net->layers.size());
   // `l` is a layer whose error is complete; send it to the layer feeding it, finish that layer, move down
   int l = n - 1;
@@ -816,8 +868,18 @@ extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
     if (p < 1) break;
     LayerPlan &P = net->layers[p];
     if (P.type == MYEA_LAYER_FULLY_CONNECTED) {
-      if (N.type != MYEA_LAYER_FULLY_CONNECTED) return fail(net, MYEA_E_UNSUPPORTED, "a fully connected hidden layer below an LSTM layer is not built");
-      RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, true));
+      if (N.type == MYEA_LAYER_FULLY_CONNECTED) {
+        RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, true));
+      } else {  // an LSTM layer above: its input contraction carries P's activation derivative in the epilogue
+        Epilogue fin;
+        const uint32_t af = P.desc.type_activation_function;
+        fin.deriv_af = af;
+        fin.aux_pre = (af == MYEA_AF_TANH || af == MYEA_AF_SIGMOID) ? nullptr : P.summations;
+        fin.aux_y = (af == MYEA_AF_RELU || af == MYEA_AF_LEAKY_RELU) ? nullptr : P.values;
+        fin.ld_aux = P.n_out;
+        P.bwd_fused_chunks = 0;
+        RC(lstm_backward_to_input(net, N, P.deriv, P, &fin));
+      }
       RC(fc_finish_backward(net, P, rows));
     } else if (P.type == MYEA_LAYER_LSTM) {
       float *dh = lstm_output_errors(P);
@@ -864,7 +926,7 @@ extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batc
   if (net == nullptr) return MYEA_E_INVALID;
   RC(batch_in_flight(net, batch));
   CK(cudaSetDevice(net->ctx.device));
-  const long long rows = net->T * net->active_B;
+  const long long rows = step_rows_total(net);
   if (net->comm != nullptr && net->grads_reduced)
     return fail(net, MYEA_E_UNSUPPORTED, "with a communicator attached, call update_parameter after every update_derivative_weight (the derivative buckets of this step were already summed over the ranks)");
   // Reduce-scatter instead of all-reduce where the update is element by element: not under a global-norm clip (the norm
@@ -1021,9 +1083,19 @@ extern "C" int myea_b200_clear_training_arrays(myea_handle net) {
 // ---------------------------------------------------------------------------------------------------------
 // Read-back helpers, synchronisation, profiling
 // ---------------------------------------------------------------------------------------------------------
-static int copy_out(myea_b200_net *net, const float *src, size_t have, float *host, uint64_t count) {
-  if (src == nullptr || count > have) return fail(net, MYEA_E_INVALID, "layer has no such buffer, or count too large");
-  CK(cudaMemcpyAsync(host, src, count * sizeof(float), cudaMemcpyDeviceToHost, net->ctx.stream));
+// rows of the step in flight, packed [T][active_B][units] for the caller (the device pitch is the allocated B when
+// the network is recurrent)
+static int copy_out(myea_b200_net *net, const float *src, long long units, float *host, uint64_t count) {
+  const long long pitch = pitch_rows(net), b = net->active_B;
+  if (src == nullptr || count > static_cast<uint64_t>(net->T * b * units)) return fail(net, MYEA_E_INVALID, "layer has no such buffer, or count too large");
+  if (b == pitch) {
+    CK(cudaMemcpyAsync(host, src, count * sizeof(float), cudaMemcpyDeviceToHost, net->ctx.stream));
+  } else {
+    const uint64_t per_step = static_cast<uint64_t>(b * units);
+    for (uint64_t t = 0; t * per_step < count; ++t)
+      CK(cudaMemcpyAsync(host + t * per_step, src + t * pitch * units, std::min<uint64_t>(per_step, count - t * per_step) * sizeof(float),
+                         cudaMemcpyDeviceToHost, net->ctx.stream));
+  }
   CK(cudaStreamSynchronize(net->ctx.stream));
   return MYEA_OK;
 }
@@ -1031,14 +1103,14 @@ static int copy_out(myea_b200_net *net, const float *src, size_t have, float *ho
 extern "C" int myea_b200_get_outputs(myea_handle net, uint32_t layer, float *host, uint64_t count) {
   if (net == nullptr || host == nullptr || layer >= net->layers.size()) return MYEA_E_INVALID;
   LayerPlan &L = net->layers[layer];
-  return copy_out(net, L.values, static_cast<size_t>(net->T * net->B * L.n_out), host, count);
+  return copy_out(net, L.values, L.n_out, host, count);
 }
 
 extern "C" int myea_b200_get_errors(myea_handle net, uint32_t layer, float *host, uint64_t count) {
   if (net == nullptr || host == nullptr || layer >= net->layers.size() || layer == 0) return MYEA_E_INVALID;
   LayerPlan &L = net->layers[layer];
   const float *src = L.type == MYEA_LAYER_LSTM ? lstm_output_errors(L) : L.errors;
-  return copy_out(net, src, static_cast<size_t>(net->T * net->B * L.n_out), host, count);
+  return copy_out(net, src, L.n_out, host, count);
 }
 
 extern "C" int myea_b200_synchronize(myea_handle net) {

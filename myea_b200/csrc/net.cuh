@@ -70,7 +70,9 @@ struct myea_b200_net {
   std::vector<myea::LayerPlan> layers;
   uint64_t total_parameters = 0, total_weights = 0, total_bias = 0, total_norm_units = 0;
   long long T = 1, B = 0;
-  long long active_B = 0;  // rows of the batch in flight: B, or fewer for the last batch of a feed-forward network
+  long long active_B = 0;  // samples of the batch in flight: B, or fewer for the last batch of an epoch
+  bool full_pitch = false; // recurrent (T > 1 or an LSTM layer): buffers keep the allocated B as the row pitch of a time step
+  long long pitch() const { return full_pitch ? B : active_B; }  // rows per time step the kernels of the step in flight run over
   bool any_norm = false;
   // flat buffers, [P] (norm averages: [total_norm_units])
   float *params = nullptr, *grads = nullptr, *m1 = nullptr, *m2 = nullptr, *m2hat = nullptr, *prev_delta = nullptr,

@@ -60,6 +60,45 @@ __global__ void __launch_bounds__(256) shakedrop_kernel(const float *__restrict_
   }
 }
 
+// The same with a block whose output is narrower or wider than its input (zero-padded identity,
+// Forward_Pass__Zero_Padded_Identity, Neural_Network__Forward_Pass__OpenMP.cpp:5158-5236): the result has
+// R = max(A, W) columns; the narrower of the two addends sits `pad` columns in.
+//   forward:  out[r, c] = x[r, c - oa] (inside [0, A)) + s[r, c - os] * (masked row ? coef[r, c - os] : 1) * scale (inside [0, W))
+__global__ void __launch_bounds__(256) shakedrop_pad_forward_kernel(const float *__restrict__ x, long long A, long long oa, const float *__restrict__ s,
+                                                                    long long W, long long os, float *__restrict__ out, long long R,
+                                                                    const uint8_t *__restrict__ mask, const float *__restrict__ coef, float scale,
+                                                                    long long rows) {
+  const long long total = rows * R;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / R, c = i - r * R;
+    float v = 0.f;
+    const long long ca = c - oa, cs = c - os;
+    if (cs >= 0 && cs < W) {
+      float t = s[r * W + cs];
+      if (mask != nullptr && mask[r] != 0) t *= coef[r * R + cs];
+      if (scale != 1.0f) t *= scale;
+      v = t;
+    }
+    if (ca >= 0 && ca < A) v = x[r * A + ca] + v;
+    out[i] = v;
+  }
+}
+//   backward (Backward_Pass__Residual, …Backward_Pass__OpenMP.cpp:1155-1215, then the ShakeDrop factor):
+//   out[r, c] = d[r, c + os] * (masked row ? coef[r, c] : 1)        for the W columns of the block's last layer
+__global__ void __launch_bounds__(256) shakedrop_pad_backward_kernel(const float *__restrict__ d, long long R, long long os, float *__restrict__ out,
+                                                                     long long W, const uint8_t *__restrict__ mask, const float *__restrict__ coef,
+                                                                     long long rows) {
+  const long long total = rows * W;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / W, c = i - r * W;
+    float v = d[r * R + c + os];
+    if (mask != nullptr && mask[r] != 0) v *= coef[r * R + c];
+    out[i] = v;
+  }
+}
+
 static int launch_shakedrop(Context &ctx, const float *x, const float *s, float *out, const uint8_t *mask, const float *coef, float scale,
                             long long rows, long long H) {
   ctx.begin(TC_ELEMENTWISE);
@@ -72,11 +111,12 @@ static int launch_shakedrop(Context &ctx, const float *x, const float *s, float 
   return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
+// columns the narrower addend of a zero-padded identity sits in (Assign__Post__Layer, Neural_Network__Compile.cpp:272-277)
+static long long residual_padding(long long A, long long W) { return ((A > W ? A - W : W - A) + 1) / 2; }
+
 int residual_check(myea_b200_net *net, int r) {
   LayerPlan &R = net->layers[r];
   if (net->T != 1) { net->ctx.error = "residual blocks in recurrent networks are not built"; return MYEA_E_UNSUPPORTED; }
-  if (R.desc.type_normalization != MYEA_NORM_NONE) { net->ctx.error = "normalization on the residual layer itself is not built"; return MYEA_E_UNSUPPORTED; }
-  if (R.n_in != R.n_out) { net->ctx.error = "zero-padded identity (block input and output of different widths) is not built"; return MYEA_E_UNSUPPORTED; }
   for (int k = 1; k <= R.block_depth; ++k) {
     const LayerPlan &L = net->layers[r + k];
     if (L.has_norm && (k == 1 || L.n_in != L.n_out)) { net->ctx.error = "normalization on the first layer of a block, or on a block layer whose input and output widths differ, is not built"; return MYEA_E_UNSUPPORTED; }
@@ -95,7 +135,7 @@ int residual_forward(myea_b200_net *net, int r) {
   LayerPlan &R = net->layers[r];
   RRC(residual_check(net, r));
   Context &ctx = net->ctx;
-  const long long rows = net->active_B;
+  const long long rows = net->pitch();
   const float *x = net->layers[R.input_layer].values;
   for (int k = 1; k <= R.block_depth; ++k) {
     LayerPlan &L = net->layers[r + k];
@@ -123,7 +163,23 @@ int residual_forward(myea_b200_net *net, int r) {
   const bool shake = R.desc.type_dropout == MYEA_DROPOUT_SHAKEDROP;
   const uint8_t *mask = (shake && net->training) ? R.shake_mask : nullptr;
   const float scale = (shake && !net->training) ? 1.0f - R.desc.dropout_values[0] : 1.0f;
-  return launch_shakedrop(ctx, x, last.summations, R.values, mask, R.shake_alpha, scale, rows, R.n_out);
+  // what the block adds to the shortcut: its last layer's output, normalized first when the residual layer itself
+  // carries a normalization (Forward_Pass__Residual, …Forward_Pass__OpenMP.cpp:3861-3998)
+  const float *s = last.summations;
+  const long long A = R.n_in, W = last.n_out;
+  if (R.has_norm) {
+    RRC(norm_forward_stats(ctx, last.summations, rows, W, R.norm, net->training ? 1 : 0, &net->hook));
+    RRC(activation_forward(ctx, last.summations, R.summations, rows, W, MYEA_AF_LINEAR, R.norm.col_scale, R.norm.col_shift, nullptr, 1.f));
+    s = R.summations;
+  }
+  if (A == W) return launch_shakedrop(ctx, x, s, R.values, mask, R.shake_alpha, scale, rows, R.n_out);
+  const long long pad = residual_padding(A, W);
+  ctx.begin(TC_ELEMENTWISE);
+  const long long total = rows * R.n_out;
+  const int blocks = static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, 148 * 16)));
+  shakedrop_pad_forward_kernel<<<blocks, 256, 0, ctx.stream>>>(x, A, A < W ? pad : 0, s, W, W < A ? pad : 0, R.values, R.n_out, mask, R.shake_alpha, scale, rows);
+  ctx.end(TC_ELEMENTWISE);
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
 }
 
 // R.deriv holds the error on the block's output.  Leaves every block layer's `errors` final and writes the complete
@@ -131,11 +187,27 @@ int residual_forward(myea_b200_net *net, int r) {
 int residual_backward(myea_b200_net *net, int r) {
   LayerPlan &R = net->layers[r];
   Context &ctx = net->ctx;
-  const long long rows = net->active_B;
+  const long long rows = net->pitch();
   LayerPlan &last = net->layers[r + R.block_depth];
   const bool shake = R.desc.type_dropout == MYEA_DROPOUT_SHAKEDROP;
-  // error on the last layer's output: the block error, times beta on the masked rows
-  RRC(launch_shakedrop(ctx, nullptr, R.deriv, last.errors, shake ? R.shake_mask : nullptr, R.shake_beta, 1.0f, rows, R.n_out));
+  // error on the last layer's output: the block error (its W columns out of the R of the block output), times beta on
+  // the masked rows, then through the residual layer's own normalization when it has one
+  // (Backward_Pass__Residual__Block, …Backward_Pass__OpenMP.cpp:351-452)
+  {
+    const long long A = R.n_in, W = last.n_out;
+    float *dst = R.has_norm ? R.summations : last.errors;  // R.summations: the normalized copy is not needed any more
+    if (A == W) {
+      RRC(launch_shakedrop(ctx, nullptr, R.deriv, dst, shake ? R.shake_mask : nullptr, R.shake_beta, 1.0f, rows, R.n_out));
+    } else {
+      ctx.begin(TC_ELEMENTWISE);
+      const long long total = rows * W;
+      const int blocks = static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, 148 * 16)));
+      shakedrop_pad_backward_kernel<<<blocks, 256, 0, ctx.stream>>>(R.deriv, R.n_out, W < A ? residual_padding(A, W) : 0, dst, W, shake ? R.shake_mask : nullptr,
+                                                                    R.shake_beta, rows);
+      ctx.end(TC_ELEMENTWISE);
+    }
+    if (R.has_norm) RRC(norm_backward(ctx, last.summations, dst, last.errors, rows, W, R.norm, &net->hook));
+  }
   for (int k = R.block_depth; k > 1; --k) {
     LayerPlan &L = net->layers[r + k];
     LayerPlan &below = net->layers[r + k - 1];
@@ -157,7 +229,8 @@ int residual_backward(myea_b200_net *net, int r) {
   Epilogue e;
   e.C = F.deriv;
   e.ldc = first.n_in;
-  e.addend = R.deriv;
+  // the skip connection: the A columns of the block error that lie over the shortcut
+  e.addend = R.deriv + (R.n_in < R.n_out ? residual_padding(R.n_in, R.n_out) : 0);
   e.ld_addend = R.n_out;
   if (F.type == MYEA_LAYER_FULLY_CONNECTED) {
     e.deriv_af = F.desc.type_activation_function;

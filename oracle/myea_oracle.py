@@ -87,9 +87,16 @@ def build_index_map(desc):
                      last_bias_connection_index=0, scale_index=0, shift_index=0, number_inputs=0, number_outputs=0,
                      block_stride=0, number_units_norm=0)
         Ls.append(L)
+    # a residual layer is as wide as the wider of its shortcut and its block's last layer (zero-padded identity,
+    # Assign__Post__Layers, Neural_Network__Compile.cpp:222-424); the shortcut is the layer before, or the residual layer
+    # of the block that ends there
     for l in range(1, n):
         if Ls[l].type == capi.LAYER_RESIDUAL:
-            Ls[l].n_out = Ls[l + Ls[l].depth].n_out
+            feeder = l - 1
+            for q in range(1, l):
+                if Ls[q].type == capi.LAYER_RESIDUAL and q + Ls[q].depth == l - 1:
+                    feeder = q
+            Ls[l].n_out = max(Ls[feeder].n_out, Ls[l + Ls[l].depth].n_out)
     for l in range(1, n):
         Ls[l].input_layer, Ls[l].n_in = l - 1, Ls[l - 1].n_out
     for l in range(1, n):
@@ -132,14 +139,21 @@ def build_index_map(desc):
     P = tw + tb
     units = 0
     if any(int(desc.layers[l].type_normalization) != capi.NORM_NONE for l in range(1, n)):
-        off = []
+        # units a layer normalizes (Prepare__Normalized__Layer / __Residual_Layer, Neural_Network__Layer_Normalization.cpp:43-154):
+        # its outputs; inside a residual block its input; for a residual layer the outputs of the block's last layer
+        off, own = [], []
+        in_block = set()
+        for l in range(1, n):
+            if Ls[l].type == capi.LAYER_RESIDUAL:
+                in_block.update(range(l + 1, l + Ls[l].depth + 1))
         for l in range(n):
             off.append(units)
-            units += Ls[l].n_out
+            own.append(Ls[l + Ls[l].depth].n_out if Ls[l].type == capi.LAYER_RESIDUAL else (Ls[l].n_in if l in in_block else Ls[l].n_out))
+            units += own[l]
         for l in range(n):
             Ls[l].idx["scale_index"] = P + off[l]
             Ls[l].idx["shift_index"] = P + units + off[l]
-            Ls[l].idx["number_units_norm"] = Ls[l].n_out
+            Ls[l].idx["number_units_norm"] = own[l]
             Ls[l].norm_off = off[l]
         P += 2 * units
     return Ls, P, tw, tb, units
@@ -227,7 +241,7 @@ class OracleNet:
         (Neural_Network__Forward_Pass__Loop.cpp:4673-4853); inference :4644-4671.  The 'variance' is the standard
         deviation sqrt(E[x^2]-mean^2+eps); r and d use the already updated running averages."""
         dt = self.dt
-        o, H = L.norm_off, L.n_out
+        o, H = L.norm_off, L.idx["number_units_norm"]
         gamma = self._p()[L.idx["scale_index"]:L.idx["scale_index"] + H]
         beta = self._p()[L.idx["shift_index"]:L.idx["shift_index"] + H]
         ma = self.buf[capi.BUF_NORM_MEAN_AVERAGE][o:o + H]
@@ -254,7 +268,7 @@ class OracleNet:
     def _norm_backward(self, L, z, delta):
         """Backward_Pass__Batch_Normalization / __Batch_Renormalization (Neural_Network__Backward_Pass__Loop.cpp:1380-1628)"""
         dt = self.dt
-        H, B = L.n_out, dt(z.shape[0] * self.world)
+        H, B = L.idx["number_units_norm"], dt(z.shape[0] * self.world)
         gamma = self._p()[L.idx["scale_index"]:L.idx["scale_index"] + H]
         self._g()[L.idx["scale_index"]:L.idx["scale_index"] + H] += (delta * L.xhat).sum(0, dtype=dt)
         self._g()[L.idx["shift_index"]:L.idx["shift_index"] + H] += delta.sum(0, dtype=dt)
@@ -287,7 +301,8 @@ class OracleNet:
         if drop in (capi.DROP_BERNOULLI, capi.DROP_BERNOULLI_INVERTED):
             p = dt(L.d.dropout_values[0])
             if self.training:
-                m = self.masks[l][0]
+                # one mask row per time step (…Forward_Pass__Loop.cpp:4947-4970); rows of y are time-major
+                m = np.repeat(np.asarray(self.masks[l]).reshape(-1, y.shape[1])[:max(1, y.shape[0] // self.active_B)], self.active_B, axis=0)
                 y = np.where(m, y * (dt(1) / p) if drop == capi.DROP_BERNOULLI_INVERTED else y, dt(0))
             elif drop == capi.DROP_BERNOULLI:
                 y = y * p

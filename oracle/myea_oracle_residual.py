@@ -11,7 +11,10 @@ Neural_Network_Library_Windows/Source_Files/Neural_Network/):
 
 The reference draws ShakeDrop's row mask and its forward (alpha ~ U(-1,1)) and backward (beta ~ U(0,1)) coefficients
 while it runs; here they are inputs (OracleNet.set_shakedrop), obtained for a parity test by replaying the reference's
-generators (oracle/ref_harness.cpp: ref_shakedrop_replay).  Equal block input / output widths only.
+generators (oracle/ref_harness.cpp: ref_shakedrop_replay).  A block narrower or wider than its shortcut: the result
+has max(A, W) columns and the narrower addend sits ((|A - W|) + 1) // 2 columns in (zero-padded identity).  A
+normalization on the residual layer itself normalizes the block's last summations before they are added
+(Forward_Pass__Residual :3861-3998 of the OpenMP twin, Backward_Pass__Residual__Block :351-452).
 """
 import numpy as np
 
@@ -37,7 +40,7 @@ def forward(net, r):
             if drop in (capi.DROP_BERNOULLI, capi.DROP_BERNOULLI_INVERTED):
                 p = dt(L.d.dropout_values[0])
                 if net.training:
-                    v = np.where(net.masks[r + k][0], v * (dt(1) / p) if drop == capi.DROP_BERNOULLI_INVERTED else v, dt(0))
+                    v = np.where(np.asarray(net.masks[r + k][0])[:v.shape[1]], v * (dt(1) / p) if drop == capi.DROP_BERNOULLI_INVERTED else v, dt(0))
                 elif drop == capi.DROP_BERNOULLI:
                     v = v * p
         L.dw_input = v
@@ -46,13 +49,23 @@ def forward(net, r):
         if not norm:
             s = s + net._p()[L.idx["first_bias_connection_index"]:L.idx["first_bias_connection_index"] + L.n_out]
         L.summations = s
+    last = net.layers[r + R.depth]
+    A, W = x.shape[1], last.n_out
+    if int(R.d.type_normalization) != capi.NORM_NONE:
+        R.z_block = s
+        s = net._norm_forward(R, s)
     if int(R.d.type_dropout) == capi.DROP_SHAKEDROP:
         if net.training:
             mask, alpha, _ = net.shake[r]
-            s = np.where(mask[:, None], s * alpha, s)
+            s = np.where(mask[:, None], s * np.asarray(alpha)[:, :W], s)
         else:
             s = s * (dt(1) - dt(R.d.dropout_values[0]))
-    R.values = (x + s).astype(dt)
+    out = np.zeros((x.shape[0], R.n_out), dt)
+    pad = (abs(A - W) + 1) // 2
+    oa, os_ = (pad if A < W else 0), (pad if W < A else 0)
+    out[:, os_:os_ + W] = s
+    out[:, oa:oa + A] = x + out[:, oa:oa + A]
+    R.values = out.astype(dt)
 
 
 def backward(net, r):
@@ -60,10 +73,16 @@ def backward(net, r):
     are final afterwards."""
     R = net.layers[r]
     d_r = R.errors
-    d = d_r
+    last = net.layers[r + R.depth]
+    A, W = net.layers[r + 1].n_in, last.n_out
+    pad = (abs(A - W) + 1) // 2
+    oa, os_ = (pad if A < W else 0), (pad if W < A else 0)
+    d = d_r[:, os_:os_ + W]
     if int(R.d.type_dropout) == capi.DROP_SHAKEDROP:
         mask, _, beta = net.shake[r]
-        d = np.where(mask[:, None], d * beta, d)
+        d = np.where(mask[:, None], d * np.asarray(beta)[:, :W], d)
+    if int(R.d.type_normalization) != capi.NORM_NONE:
+        d = net._norm_backward(R, R.z_block, d)
     for k in range(R.depth, 1, -1):
         L = net.layers[r + k]
         L.errors = d
@@ -76,7 +95,7 @@ def backward(net, r):
     if f < 1:
         return 0
     F = net.layers[f]
-    D = d_r + d @ net._fc_weights(first)
+    D = d_r[:, oa:oa + A] + d @ net._fc_weights(first)
     if F.type == capi.LAYER_FC:
         da = D * af_derive(int(F.d.type_activation_function), F.pre, F.values)
         F.errors = net._norm_backward(F, F.z, da) if int(F.d.type_normalization) != capi.NORM_NONE else da

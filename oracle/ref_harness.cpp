@@ -357,13 +357,16 @@ int ref_shakedrop_replay(void *h, uint64_t B, uint8_t *masks, float *alpha, floa
   MyEA::Random::Floating<T_> real;
   bern = nn.ptr_array_Class_Generator_Bernoulli_ShakeDrop[0];
   real = nn.ptr_array_Class_Generator_Real_ShakeDrop[0];
-  std::vector<size_t> blocks, widths, offsets;
+  // widths: pitch of a block's rows in alpha / beta (the residual layer's outputs); drawn: coefficients the reference
+  // draws per row = outputs of the block's LAST layer (narrower than the pitch under a zero-padded identity)
+  std::vector<size_t> blocks, widths, drawn, offsets;
   size_t off = 0;
   for (size_t l = 1; l < nn.total_layers; ++l) {
     Layer *L = nn.ptr_array_layers + l;
     if (L->type_layer == ENUM_TYPE_LAYER::TYPE_LAYER_RESIDUAL && L->type_dropout == ENUM_TYPE_LAYER_DROPOUT::TYPE_LAYER_DROPOUT_SHAKEDROP) {
       blocks.push_back(l);
       widths.push_back(*L->ptr_number_outputs);
+      drawn.push_back(*(L + L->block_depth)->ptr_number_outputs);
       offsets.push_back(off);
       off += B * *L->ptr_number_outputs;
     }
@@ -375,13 +378,13 @@ int ref_shakedrop_replay(void *h, uint64_t B, uint8_t *masks, float *alpha, floa
     for (size_t b = 0; b < B; ++b) {
       const bool m = bern();
       masks[k * B + b] = m ? 1 : 0;
-      for (size_t j = 0; j < widths[k]; ++j) alpha[offsets[k] + b * widths[k] + j] = m ? static_cast<float>(real()) : 1.0f;
+      for (size_t j = 0; j < widths[k]; ++j) alpha[offsets[k] + b * widths[k] + j] = (m && j < drawn[k]) ? static_cast<float>(real()) : 1.0f;
     }
   }
   for (size_t k = blocks.size(); k-- > 0;) {
     real.Range(0_T, 1_T);
     for (size_t b = 0; b < B; ++b)
-      for (size_t j = 0; j < widths[k]; ++j) beta[offsets[k] + b * widths[k] + j] = masks[k * B + b] ? static_cast<float>(real()) : 1.0f;
+      for (size_t j = 0; j < widths[k]; ++j) beta[offsets[k] + b * widths[k] + j] = (masks[k * B + b] && j < drawn[k]) ? static_cast<float>(real()) : 1.0f;
   }
   return static_cast<int>(blocks.size());
 }

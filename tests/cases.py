@@ -113,8 +113,29 @@ CASES_ORACLE_ONLY = {
 }
 
 
+
+
+def _lstm_fc_case(name, opt, T=4, B=6, n_in=7, below=10, H=8, above=6, out=5, drop_below=capi.DROP_BERNOULLI, drop_above=capi.DROP_BERNOULLI_INVERTED,
+                  delays=1, cells_per_block=1):
+    """fully connected hidden layers on both sides of an LSTM layer, each with its own per-time-step dropout mask"""
+    ls = [capi.fc(n_in), capi.fc(below, capi.AF_TANH, dropout=drop_below, p=(0.7, 0.0, 0.0)), capi.lstm(H, cells_per_block=cells_per_block),
+          capi.fc(above, capi.AF_RELU, dropout=drop_above, p=(0.8, 0.0, 0.0)), capi.fc(out, capi.AF_LINEAR)]
+    return workloads.Workload(name, capi.net(ls, B, T=T, loss=capi.LOSS_MSE, accuracy=capi.ACC_DISTANCE, time_delays=delays), opt, n_in, out, False, ls)
+
+
 def _res_wide():
     return _res_case("res_wide", capi.opt(capi.OPT_GD, gd_lr=0.001, momentum=0.9), B=136, n_in=40, H=144, out=7, blocks=2)
+
+
+CASES.update({
+    # recurrent networks with fully connected hidden layers around the LSTM layer and Bernoulli dropout drawn per time step
+    "lstm_between_fc_bernoulli": lambda: _lstm_fc_case("lstm_fc", capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9)),
+    # zero-padded identity: the block narrower / wider than its shortcut, and the residual layer's own normalization
+    "res_zero_pad_narrow_block": lambda: _res_case("res_np", capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9), H=14, block_width=9, blocks=1),
+    "res_zero_pad_wide_block": lambda: _res_case("res_wp", capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9), H=10, block_width=15, blocks=1),
+    "res_block_level_norm": lambda: _res_case("res_bn", capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9), norm=capi.NORM_NONE, af=capi.AF_TANH,
+                                              block_norm=capi.NORM_BN, blocks=2),
+})
 
 
 def _bilstm_case(name, opt, T=5, B=6, n_in=7, H=8, out=5, zoneout=None):
@@ -131,10 +152,14 @@ CASES_WITHOUT_REFERENCE = {
 }
 
 
-def _res_case(name, opt, B=10, n_in=9, H=12, out=5, blocks=2, p=0.5, norm=capi.NORM_BRN, af=capi.AF_ELU, shake=True, inner_drop=capi.DROP_NONE):
+def _res_case(name, opt, B=10, n_in=9, H=12, out=5, blocks=2, p=0.5, norm=capi.NORM_BRN, af=capi.AF_ELU, shake=True, inner_drop=capi.DROP_NONE,
+              block_width=None, block_norm=capi.NORM_NONE):
+    """block_width: width of the block's layers when it differs from the shortcut's H (zero-padded identity);
+    block_norm: normalization on the residual layer itself (the block's output before ShakeDrop and the skip add)"""
     ls = [capi.fc(n_in), capi.fc(H, af)]
+    W = block_width or H
     for _ in range(blocks):
-        ls += [capi.residual(2, capi.DROP_SHAKEDROP if shake else capi.DROP_NONE, (p, 0, 0)), capi.fc(H, af), capi.fc(H, af, norm, inner_drop, (0.7, 0, 0))]
+        ls += [capi.residual(2, capi.DROP_SHAKEDROP if shake else capi.DROP_NONE, (p, 0, 0), block_norm), capi.fc(W, af), capi.fc(W, af, norm, inner_drop, (0.7, 0, 0))]
     ls.append(capi.fc(out, capi.AF_SOFTMAX))
     return workloads.Workload(name, capi.net(ls, B, loss=capi.LOSS_CE, accuracy=capi.ACC_CE, r_max=3.0, d_max=5.0), opt, n_in, out, True, ls)
 

@@ -94,10 +94,11 @@ def test_epoch_with_device_drawn_masks_runs_and_is_repeatable():
     assert out[0][0] == out[1][0] and np.array_equal(out[0][1], out[1][1])
 
 
-@pytest.mark.parametrize("name", ["mlp_relu_gd", "c2_small"])
+@pytest.mark.parametrize("name", ["mlp_relu_gd", "c2_small", "lstm1_all_steps_adam", "lstm2_zoneout_clip"])
 def test_short_last_batches_match_the_reference(name):
-    """feed-forward networks: the last sub-batch of a mini-batch and the last mini-batch of the epoch may be shorter
-    than the allocated batch (Dataset::Train_Batch_BP, Dataset.cpp:667-691); BN statistics are then those of the short batch"""
+    """the last sub-batch of a mini-batch and the last mini-batch of the epoch may be shorter than the allocated batch
+    (Dataset::Train_Batch_BP, Dataset.cpp:667-691); BN statistics are then those of the short batch; recurrent
+    networks keep the allocated batch as the pitch of a time step"""
     wl = cases.CASES[name]()
     B = wl.B
     mini = B + B // 2                 # one full sub-batch + a half one
@@ -137,18 +138,17 @@ def test_short_last_batches_match_the_reference(name):
     gpu.close(); cpu.close()
 
 
-def test_requests_that_are_not_built_are_refused_not_mangled():
-    # a recurrent network takes full batches only
+def test_bad_requests_are_refused_not_mangled():
     wl = cases.CASES["lstm1_all_steps_adam"]()
     gpu = Net(wl.desc, wl.opt)
     wl.materialize(gpu)
     n = wl.B * 2 + 1
     X, Y = _dataset(wl, n)
     gpu.dataset_set(X.reshape(n, -1), Y.reshape(n, -1))
-    order = np.arange(n, dtype=np.uint64)
     loss, acc = C.c_double(), C.c_double()
-    assert gpu.lib.myea_b200_train_epoch(gpu.h, order.ctypes.data, n, wl.B, C.byref(wl.opt), 0, 0, C.byref(loss), C.byref(acc)) == -4
-    assert gpu.lib.myea_b200_evaluate(gpu.h, None, wl.B + 1, None, None, None, None) == -4
-    bad = np.array([0, n + 5] * wl.B, dtype=np.uint64)[:wl.B * 2]
+    bad = np.array([0, n + 5] * wl.B, dtype=np.uint64)[:wl.B * 2]      # an index past the dataset
     assert gpu.lib.myea_b200_train_epoch(gpu.h, bad.ctypes.data, bad.size, wl.B, C.byref(wl.opt), 0, 0, C.byref(loss), C.byref(acc)) == -1
+    assert gpu.lib.myea_b200_evaluate(gpu.h, None, n + 1, None, None, None, None) == -1      # more examples than the dataset holds
+    x = np.zeros((wl.desc.number_recurrent_depth, wl.B + 1, wl.n_in), np.float32)
+    assert gpu.lib.myea_b200_forward(gpu.h, wl.B + 1, x.ctypes.data, 1) == -1                # batch above the allocated one
     gpu.close()
