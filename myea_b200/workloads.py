@@ -67,6 +67,10 @@ class Workload:
                 stride = int(li.block_stride)
                 base = int(li.first_connection_index)
                 bound_in = math.sqrt(6.0 / (n_in + C))
+                if int(L.unit_parameters[1]) > 1:   # several cells per block: uniform values over the layer's whole range
+                    a, b = base, int(li.last_connection_index)
+                    p[a:b] = rng.uniform(-bound_in, bound_in, b - a)
+                    continue
                 for d in range(dirs):
                     blk = np.zeros((C, stride), np.float32)   # one row per block (1 cell per block)
                     # [W_z,in | W_z,rec | W_i,in W_f,in W_o,in | W_i,rec W_f,rec W_o,rec | p_i p_f p_o]
