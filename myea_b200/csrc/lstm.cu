@@ -6,7 +6,7 @@
 // (Neural_Network__Recurrent_Backward_Pass__OpenMP.cpp:1130-1604), error to the previous layer Backward_Pass__LSTM (:1024-1120),
 // Recurrent__Update_Derivative_Weight__LSTM + bias (Neural_Network__Recurrent_Update_Derivative_Weight__OpenMP.cpp:492-776).
 //
-// One cell per block (what every configuration uses).  Per step, with prev = the step before in the layer's direction:
+// One cell per block (what every shipped configuration uses; blocks of several cells: lstm_blocks.cu).  Per step, with prev = the step before in the layer's direction:
 //   z = tanh(Wz x + Rz h_prev + bz)          i = sig(Wi x + Ri h_prev + bi + pi*c_prev)
 //   f = sig(Wf x + Rf h_prev + bf + pf*c_prev)   c = z*i + f*c_prev        (first step: no recurrent terms, no f)
 //   o = sig(Wo x + Ro h_prev + bo + po*c)    h = tanh(c)*o
@@ -261,15 +261,16 @@ static int lalloc(myea_b200_net *net, T **p, size_t count) {
 
 int lstm_create(myea_b200_net *net, LayerPlan &L) {
   const long long cpb = std::max<long long>(1, static_cast<long long>(L.desc.unit_parameters[1]));
-  if (cpb != 1) { net->ctx.error = "LSTM blocks with more than one cell are not built"; return MYEA_E_UNSUPPORTED; }
   LstmPlan *P = new LstmPlan();
   L.lstm = P;
   P->dirs = L.desc.use_bidirectional ? 2 : 1;
   P->C = L.n_out / P->dirs;
+  P->cpb = cpb;
+  P->K = P->C / cpb;
   P->n_in = L.n_in;
   P->stride = static_cast<long long>(L.idx.block_stride);
-  if ((P->C & 3) != 0) { net->ctx.error = "LSTM width must be a multiple of 4"; return MYEA_E_UNSUPPORTED; }
   P->zoneout = L.desc.type_dropout == MYEA_DROPOUT_ZONEOUT;
+  if (cpb != 1) return lstm_blocks_create(net, L, P);
   const long long rows = net->T * net->B, C = P->C;
   // biases: the reference stores first_bias_connection_index already shifted by the number of cells and then reads
   // [bz | bi | bf | bo] from it, so bo overlaps the next layer's bias slots.  Reproduced for the unidirectional layer;
@@ -405,6 +406,7 @@ static int cell_blocks(long long total) { return static_cast<int>(std::max<long 
 // ---------------------------------------------------------------------------------------------------------
 int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long n_in) {
   LstmPlan *P = L.lstm;
+  if (P->cpb != 1) return lstm_blocks_forward(net, L, input, n_in);
   Context &ctx = net->ctx;
   const long long T = net->T, B = net->B, rows = T * B, C = P->C, ldh = L.n_out;
   const BlockOffsets off = block_offsets(n_in, C);
@@ -518,6 +520,7 @@ int lstm_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long
 // ---------------------------------------------------------------------------------------------------------
 int lstm_backward(myea_b200_net *net, LayerPlan &L) {
   LstmPlan *P = L.lstm;
+  if (P->cpb != 1) return lstm_blocks_backward(net, L);
   Context &ctx = net->ctx;
   const long long T = net->T, B = net->B, C = P->C, ldh = L.n_out, n_in = P->n_in;
   const long long Cp = (C + 7) & ~7ll;  // each gate's K segment starts on a group-of-8 boundary
@@ -604,6 +607,7 @@ int lstm_backward(myea_b200_net *net, LayerPlan &L) {
 // connected layer below, applied by the epilogue of the last direction's contraction to the complete sum.
 int lstm_backward_to_input(myea_b200_net *net, LayerPlan &L, float *prev_deriv, const LayerPlan &prev, const Epilogue *finish) {
   LstmPlan *P = L.lstm;
+  if (P->cpb != 1) return lstm_blocks_backward_to_input(net, L, prev_deriv, prev, finish);
   Context &ctx = net->ctx;
   const long long rows = net->T * net->B, C = P->C, n_in = P->n_in;
   if (prev.n_out != n_in) return MYEA_E_INVALID;
@@ -634,6 +638,7 @@ int lstm_backward_to_input(myea_b200_net *net, LayerPlan &L, float *prev_deriv, 
 // ---------------------------------------------------------------------------------------------------------
 int lstm_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float *input, long long n_in) {
   LstmPlan *P = L.lstm;
+  if (P->cpb != 1) return lstm_blocks_update_derivative_weight(net, L, input, n_in);
   Context &ctx = net->ctx;
   const long long T = net->T, B = net->B, rows = T * B, C = P->C, ldh = L.n_out;
   const BlockOffsets off = block_offsets(n_in, C);

@@ -38,7 +38,19 @@ struct LstmPlan {
   // batch rounded up to 128, so that one tensor map covers both
   Panels h_pan[2], dg_pan[2];
   LstmPersistent *persist = nullptr;
+  // blocks of several cells (lstm_blocks.cu): K blocks of cpb cells per direction, gate rows of G = C + 3K columns
+  // [z (C) | i (K) | f (K) | o (K)], weights gathered into dense matrices for the pass and their derivatives scattered back
+  long long K = 0, cpb = 1;
+  float *blk_w_in = nullptr, *blk_w_rec = nullptr, *blk_peep = nullptr;       // [G, in], [G, C], [3][C]
+  float *blk_dw_in = nullptr, *blk_dw_rec = nullptr, *blk_dpeep = nullptr;
+  float *blk_products = nullptr;                                               // [T*B, 3C]
 };
+
+int lstm_blocks_create(myea_b200_net *net, LayerPlan &L, LstmPlan *P);
+int lstm_blocks_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long n_in);
+int lstm_blocks_backward(myea_b200_net *net, LayerPlan &L);
+int lstm_blocks_backward_to_input(myea_b200_net *net, LayerPlan &L, float *prev_deriv, const LayerPlan &prev, const Epilogue *finish);
+int lstm_blocks_update_derivative_weight(myea_b200_net *net, LayerPlan &L, const float *input, long long n_in);
 
 
 // One launch that walks ALL remaining time steps of one layer and direction (lstm_persistent.cu): the recurrent

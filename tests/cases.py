@@ -115,6 +115,17 @@ CASES_ORACLE_ONLY = {
 
 
 
+def _lstm_blocks_case(name, opt, cpb, T=4, B=5, n_in=7, blocks=(4, 3), out=12, zoneout=0.3, delays=1):
+    """LSTM blocks of `cpb` cells each (the cells of a block share its gates); the output layer is at least as wide as
+    the last LSTM layer has cells, as the reference's shifted bias base requires"""
+    ls = [capi.fc(n_in)]
+    for i, k in enumerate(blocks):
+        z = zoneout if i == 0 else None
+        ls.append(capi.lstm(k, cells_per_block=cpb, dropout=capi.DROP_ZONEOUT if z else capi.DROP_NONE, p=(z or 0.0, z or 0.0, 0.0)))
+    ls.append(capi.fc(out, capi.AF_LINEAR))
+    return workloads.Workload(name, capi.net(ls, B, T=T, loss=capi.LOSS_MSE, accuracy=capi.ACC_DISTANCE, time_delays=delays), opt, n_in, out, False, ls)
+
+
 def _lstm_fc_case(name, opt, T=4, B=6, n_in=7, below=10, H=8, above=6, out=5, drop_below=capi.DROP_BERNOULLI, drop_above=capi.DROP_BERNOULLI_INVERTED,
                   delays=1, cells_per_block=1):
     """fully connected hidden layers on both sides of an LSTM layer, each with its own per-time-step dropout mask"""
@@ -128,6 +139,10 @@ def _res_wide():
 
 
 CASES.update({
+    # blocks of several cells, and a layer width that is no multiple of 4
+    "lstm_two_cells_per_block": lambda: _lstm_blocks_case("lstm_cpb2", capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9), 2),
+    "lstm_three_cells_per_block_adam": lambda: _lstm_blocks_case("lstm_cpb3", capi.opt(capi.OPT_ADAM), 3, blocks=(3, 2), delays=0),
+    "lstm_width_7": lambda: _lstm_case("lstm_w7", capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9), H=7, out=9, delays=1),
     # recurrent networks with fully connected hidden layers around the LSTM layer and Bernoulli dropout drawn per time step
     "lstm_between_fc_bernoulli": lambda: _lstm_fc_case("lstm_fc", capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9)),
     # zero-padded identity: the block narrower / wider than its shortcut, and the residual layer's own normalization
