@@ -40,14 +40,32 @@ extern "C" {
 #define MYEA_NETWORK_FEEDFORWARD 3u
 #define MYEA_NETWORK_RECURRENT 4u
 /* ENUM_TYPE_ACTIVATION_FUNCTION (Enum_Type_Activation_Functions.hpp:25) */
+#define MYEA_AF_COSINE 1u
+#define MYEA_AF_COSINE_SYMMETRIC 2u
 #define MYEA_AF_ELU 3u
+#define MYEA_AF_ELLIOT 4u
+#define MYEA_AF_ELLIOT_SYMMETRIC 5u
+#define MYEA_AF_GAUSSIAN 6u
+#define MYEA_AF_GAUSSIAN_STEPWISE 7u /* the reference's value is the constant 0 (Activation_Functions.hpp: AF_FIRE) */
+#define MYEA_AF_GAUSSIAN_SYMMETRIC 8u
+#define MYEA_AF_ISRU 9u
+#define MYEA_AF_ISRLU 10u
 #define MYEA_AF_LINEAR 11u
+#define MYEA_AF_LINEAR_PIECE 12u
+#define MYEA_AF_LINEAR_PIECE_SYMMETRIC 13u
 #define MYEA_AF_LEAKY_RELU 14u
+#define MYEA_AF_PARAMETRIC_RELU 15u /* fixed slope 0.01 in the reference (AF_PRELU_ALPHA) */
 #define MYEA_AF_RELU 16u
 #define MYEA_AF_SELU 17u
 #define MYEA_AF_SIGMOID 18u
+#define MYEA_AF_SINE 19u
+#define MYEA_AF_SIGMOID_STEPWISE 20u
+#define MYEA_AF_SINE_SYMMETRIC 21u
 #define MYEA_AF_SOFTMAX 22u
 #define MYEA_AF_TANH 23u
+#define MYEA_AF_TANH_STEPWISE 24u
+#define MYEA_AF_THRESHOLD 25u           /* no derivative in the reference (Activation_Function_Derive falls through */
+#define MYEA_AF_THRESHOLD_SYMMETRIC 26u /* to `return value`); the same factor is used here */
 /* ENUM_TYPE_LAYER_NORMALIZATION (Enum_Type_Layer_Normalization.hpp) */
 #define MYEA_NORM_NONE 0u
 #define MYEA_NORM_BATCH_NORMALIZATION 1u

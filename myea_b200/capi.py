@@ -15,6 +15,9 @@ MAX_LAYERS = 64
 LAYER_FC, LAYER_LSTM, LAYER_RESIDUAL = 4, 8, 10
 NET_FEEDFORWARD, NET_RECURRENT = 3, 4
 AF_ELU, AF_LINEAR, AF_LEAKY_RELU, AF_RELU, AF_SELU, AF_SIGMOID, AF_SOFTMAX, AF_TANH = 3, 11, 14, 16, 17, 18, 22, 23
+(AF_COSINE, AF_COSINE_SYMMETRIC, AF_ELLIOT, AF_ELLIOT_SYMMETRIC, AF_GAUSSIAN, AF_GAUSSIAN_STEPWISE, AF_GAUSSIAN_SYMMETRIC, AF_ISRU, AF_ISRLU,
+ AF_LINEAR_PIECE, AF_LINEAR_PIECE_SYMMETRIC, AF_PARAMETRIC_RELU, AF_SINE, AF_SIGMOID_STEPWISE, AF_SINE_SYMMETRIC, AF_TANH_STEPWISE, AF_THRESHOLD,
+ AF_THRESHOLD_SYMMETRIC) = 1, 2, 4, 5, 6, 7, 8, 9, 10, 12, 13, 15, 19, 20, 21, 24, 25, 26
 NORM_NONE, NORM_BN, NORM_BRN = 0, 1, 2
 MASK_BERNOULLI, MASK_ZONEOUT_STATE, MASK_ZONEOUT_OUTPUT, MASK_SHAKEDROP, MASK_SHAKEDROP_ALPHA, MASK_SHAKEDROP_BETA = range(6)
 DROP_NONE, DROP_BERNOULLI, DROP_BERNOULLI_INVERTED, DROP_SHAKEDROP, DROP_ZONEOUT = 0, 2, 3, 5, 7

@@ -52,10 +52,13 @@ std::string num(uint64_t v) { return std::to_string(v); }
 // Train.cpp:454-497), for the functions this library runs
 uint32_t activation_class(uint32_t af) {
   switch (af) {
-    case MYEA_AF_TANH: return 5u;                        // symmetric
-    case MYEA_AF_ELU: case MYEA_AF_LINEAR: case MYEA_AF_SIGMOID: return 1u;  // asymmetric
-    case MYEA_AF_LEAKY_RELU: case MYEA_AF_RELU: return 2u;  // rectifier
-    case MYEA_AF_SELU: return 3u;                        // self-normalization
+    case MYEA_AF_COSINE_SYMMETRIC: case MYEA_AF_ELLIOT_SYMMETRIC: case MYEA_AF_GAUSSIAN_SYMMETRIC: case MYEA_AF_LINEAR_PIECE_SYMMETRIC:
+    case MYEA_AF_SINE_SYMMETRIC: case MYEA_AF_TANH: case MYEA_AF_TANH_STEPWISE: case MYEA_AF_THRESHOLD_SYMMETRIC: return 5u;  // symmetric
+    case MYEA_AF_COSINE: case MYEA_AF_ELU: case MYEA_AF_ELLIOT: case MYEA_AF_GAUSSIAN: case MYEA_AF_GAUSSIAN_STEPWISE: case MYEA_AF_ISRU:
+    case MYEA_AF_ISRLU: case MYEA_AF_LINEAR: case MYEA_AF_LINEAR_PIECE: case MYEA_AF_SIGMOID: case MYEA_AF_SINE: case MYEA_AF_SIGMOID_STEPWISE:
+    case MYEA_AF_THRESHOLD: return 1u;                                                                                           // asymmetric
+    case MYEA_AF_LEAKY_RELU: case MYEA_AF_PARAMETRIC_RELU: case MYEA_AF_RELU: return 2u;                                          // rectifier
+    case MYEA_AF_SELU: return 3u;                                                                                                // self-normalization
     case MYEA_AF_SOFTMAX: return 4u;
     default: return 0u;
   }

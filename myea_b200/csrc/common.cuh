@@ -86,27 +86,92 @@ inline cudaError_t launch_dependent(const Context &ctx, void (*kernel)(KernelArg
 // tanh is 2/(1+e^-2z)-1 (Activation_Functions.hpp:45), sigmoid 1/(1+e^-z) (:40); the ELU derivative below zero is
 // alpha*y with y = e^z-1 (:93-94), not alpha*e^z; the softmax derivative is 1 (cross-entropy pairing).
 // ---------------------------------------------------------------------------------------------------------
+// piecewise-linear approximation through six points (v_k, r_k), constant lo / hi outside (AF_STEPWISE_real, :28-31)
+__host__ __device__ __forceinline__ float af_stepwise(float z, const float *v, const float *r, float lo, float hi) {
+  if (z < v[0]) return lo;
+  if (!(z < v[5])) return hi;
+  const int k = z < v[1] ? 0 : (z < v[2] ? 1 : (z < v[3] ? 2 : (z < v[4] ? 3 : 4)));
+  return (((r[k + 1] - r[k]) * (z - v[k])) / (v[k + 1] - v[k])) + r[k];
+}
+
 __host__ __device__ __forceinline__ float af_fire(uint32_t af, float z) {
   switch (af) {
     case MYEA_AF_TANH: return 2.0f / (1.0f + expf(-2.0f * z)) - 1.0f;
     case MYEA_AF_SIGMOID: return 1.0f / (1.0f + expf(-z));
     case MYEA_AF_RELU: return z < 0.0f ? 0.0f : z;
-    case MYEA_AF_LEAKY_RELU: return z < 0.0f ? 0.01f * z : z;
+    case MYEA_AF_LEAKY_RELU: case MYEA_AF_PARAMETRIC_RELU: return z < 0.0f ? 0.01f * z : z;
     case MYEA_AF_ELU: return z < 0.0f ? (expf(z) - 1.0f) : z;
     case MYEA_AF_SELU: return 1.0507009873554804934193349852946f * (z <= 0.0f ? 1.6732632423543772848170429916717f * expf(z) - 1.6732632423543772848170429916717f : z);
+    case MYEA_AF_LINEAR_PIECE: return z < 0.0f ? 0.0f : (z > 1.0f ? 1.0f : z);
+    case MYEA_AF_LINEAR_PIECE_SYMMETRIC: return z < -1.0f ? -1.0f : (z > 1.0f ? 1.0f : z);
+    case MYEA_AF_SIGMOID_STEPWISE: {
+      const float v[6] = {-2.64665246f, -1.47221947f, -0.549306154f, 0.549306154f, 1.47221935f, 2.64665294f};
+      const float r[6] = {0.00499999989f, 0.0500000007f, 0.25f, 0.75f, 0.949999988f, 0.995000005f};
+      return af_stepwise(z, v, r, 0.0f, 1.0f);
+    }
+    case MYEA_AF_TANH_STEPWISE: {
+      const float v[6] = {-2.64665294f, -1.47221935f, -0.549306154f, 0.549306154f, 1.47221935f, 2.64665294f};
+      const float r[6] = {-0.99000001f, -0.899999976f, -0.5f, 0.5f, 0.899999976f, 0.99000001f};
+      return af_stepwise(z, v, r, -1.0f, 1.0f);
+    }
+    case MYEA_AF_THRESHOLD: return z < 0.0f ? 0.0f : 1.0f;
+    case MYEA_AF_THRESHOLD_SYMMETRIC: return z < 0.0f ? -1.0f : 1.0f;
+    case MYEA_AF_GAUSSIAN: return expf(-z * z);
+    case MYEA_AF_GAUSSIAN_SYMMETRIC: return expf(-z * z) * 2.0f - 1.0f;
+    case MYEA_AF_GAUSSIAN_STEPWISE: return 0.0f;
+    case MYEA_AF_ELLIOT: return (z / 2.0f) / (1.0f + fabsf(z)) + 0.5f;
+    case MYEA_AF_ELLIOT_SYMMETRIC: return z / (1.0f + fabsf(z));
+    case MYEA_AF_SINE: return sinf(z) / 2.0f + 0.5f;
+    case MYEA_AF_SINE_SYMMETRIC: return sinf(z);
+    case MYEA_AF_COSINE: return cosf(z) / 2.0f + 0.5f;
+    case MYEA_AF_COSINE_SYMMETRIC: return cosf(z);
+    case MYEA_AF_ISRU: return z * (1.0f / sqrtf(1.0f + z * z));
+    case MYEA_AF_ISRLU: return z < 0.0f ? z * (1.0f / sqrtf(1.0f + z * z)) : z;
     default: return z;  // linear
   }
 }
 
+// Activation_Function_Derive (Neural_Network.cpp:3157-3199) at steepness 1.  The threshold functions and the stepwise
+// Gaussian are not in that switch: its default branch hands back the VALUE, and so does this one.  ISRU / ISRLU divide the
+// value by the summation; at a summation of exactly zero (0 / 0 in the reference) the limit 1 is used.
 __host__ __device__ __forceinline__ float af_derive(uint32_t af, float z, float y) {
   switch (af) {
-    case MYEA_AF_TANH: return 1.0f - y * y;
-    case MYEA_AF_SIGMOID: return y * (1.0f - y);
+    case MYEA_AF_TANH: case MYEA_AF_TANH_STEPWISE: return 1.0f - y * y;
+    case MYEA_AF_SIGMOID: case MYEA_AF_SIGMOID_STEPWISE: return y * (1.0f - y);
     case MYEA_AF_RELU: return z < 0.0f ? 0.0f : 1.0f;
-    case MYEA_AF_LEAKY_RELU: return z < 0.0f ? 0.01f : 1.0f;
+    case MYEA_AF_LEAKY_RELU: case MYEA_AF_PARAMETRIC_RELU: return z < 0.0f ? 0.01f : 1.0f;
     case MYEA_AF_ELU: return z < 0.0f ? y : 1.0f;
     case MYEA_AF_SELU: return 1.0507009873554804934193349852946f * (z <= 0.0f ? (y + 1.6732632423543772848170429916717f) : 1.0f);
-    default: return 1.0f;  // linear, softmax
+    case MYEA_AF_GAUSSIAN: return -2.0f * z * y;
+    case MYEA_AF_GAUSSIAN_SYMMETRIC: return -2.0f * z * (y + 1.0f);
+    case MYEA_AF_ELLIOT: { const float a = 1.0f + fabsf(z); return 1.0f / (2.0f * a * a); }
+    case MYEA_AF_ELLIOT_SYMMETRIC: { const float a = 1.0f + fabsf(z); return 1.0f / (a * a); }
+    case MYEA_AF_SINE: return cosf(z) / 2.0f;
+    case MYEA_AF_SINE_SYMMETRIC: return cosf(z);
+    case MYEA_AF_COSINE: return -sinf(z) / 2.0f;
+    case MYEA_AF_COSINE_SYMMETRIC: return -sinf(z);
+    case MYEA_AF_ISRU: { if (z == 0.0f) return 1.0f; const float q = y / z; return q * q * q; }
+    case MYEA_AF_ISRLU: { if (!(z < 0.0f)) return 1.0f; const float q = y / z; return q * q * q; }
+    case MYEA_AF_THRESHOLD: case MYEA_AF_THRESHOLD_SYMMETRIC: case MYEA_AF_GAUSSIAN_STEPWISE: return y;
+    default: return 1.0f;  // linear, linear piece (symmetric), softmax
+  }
+}
+
+// which arrays af_derive reads: the summation (pre-activation) and / or the value
+__host__ __device__ __forceinline__ bool af_derive_reads_summation(uint32_t af) {
+  switch (af) {
+    case MYEA_AF_TANH: case MYEA_AF_TANH_STEPWISE: case MYEA_AF_SIGMOID: case MYEA_AF_SIGMOID_STEPWISE: case MYEA_AF_THRESHOLD:
+    case MYEA_AF_THRESHOLD_SYMMETRIC: case MYEA_AF_GAUSSIAN_STEPWISE: case MYEA_AF_LINEAR: case MYEA_AF_LINEAR_PIECE:
+    case MYEA_AF_LINEAR_PIECE_SYMMETRIC: case MYEA_AF_SOFTMAX: return false;
+    default: return true;
+  }
+}
+__host__ __device__ __forceinline__ bool af_derive_reads_value(uint32_t af) {
+  switch (af) {
+    case MYEA_AF_RELU: case MYEA_AF_LEAKY_RELU: case MYEA_AF_PARAMETRIC_RELU: case MYEA_AF_ELLIOT: case MYEA_AF_ELLIOT_SYMMETRIC: case MYEA_AF_SINE:
+    case MYEA_AF_SINE_SYMMETRIC: case MYEA_AF_COSINE: case MYEA_AF_COSINE_SYMMETRIC: case MYEA_AF_LINEAR: case MYEA_AF_LINEAR_PIECE:
+    case MYEA_AF_LINEAR_PIECE_SYMMETRIC: case MYEA_AF_SOFTMAX: return false;
+    default: return true;
   }
 }
 
@@ -255,6 +320,7 @@ int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H
                        const SumHook *hook = nullptr, const OverlapWork *meanwhile = nullptr, int fused_chunks = 0);
 // out = dropout(f(z*col_scale+col_shift)) ; col_scale null = no normalization. mask: uint8[H] or null; keep_scale = 1/p for inverted dropout
 // sink (may be null): the result is also written as operand panels of the contraction that reads it next
+bool activation_writes_panels(uint32_t af);
 int activation_forward(Context &ctx, const float *z, float *out, long long rows, long long H, uint32_t af,
                        const float *col_scale, const float *col_shift, const uint8_t *mask, float keep_scale, const PanelSink *sink = nullptr);
 int softmax_forward(Context &ctx, const float *z, float *out, long long rows, long long H);

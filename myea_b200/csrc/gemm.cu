@@ -114,7 +114,16 @@ __device__ __forceinline__ void derive4x4_any(uint32_t af, float4 (&x)[4], const
     case MYEA_AF_LEAKY_RELU: derive4x4<MYEA_AF_LEAKY_RELU>(x, z, y); break;
     case MYEA_AF_ELU: derive4x4<MYEA_AF_ELU>(x, z, y); break;
     case MYEA_AF_SELU: derive4x4<MYEA_AF_SELU>(x, z, y); break;
-    default: break;  // linear, softmax: derivative 1
+    case MYEA_AF_LINEAR: case MYEA_AF_LINEAR_PIECE: case MYEA_AF_LINEAR_PIECE_SYMMETRIC: case MYEA_AF_SOFTMAX: break;  // derivative 1
+    default:  // the rarely used functions share one body that switches per element
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        x[i].x *= af_derive(af, z[i].x, y[i].x);
+        x[i].y *= af_derive(af, z[i].y, y[i].y);
+        x[i].z *= af_derive(af, z[i].z, y[i].z);
+        x[i].w *= af_derive(af, z[i].w, y[i].w);
+      }
+      break;
   }
 }
 

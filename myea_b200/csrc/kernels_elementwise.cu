@@ -387,6 +387,14 @@ static dim3 column_walk_grid(long long rows, long long H) {
   return dim3(gx, static_cast<unsigned>(std::max<long long>(1, std::min<long long>((rows + 3) / 4, walkers))));
 }
 
+// the functions whose kernel can also write the next contraction's operand panels
+bool activation_writes_panels(uint32_t af) {
+  switch (af) {
+    case MYEA_AF_TANH: case MYEA_AF_SIGMOID: case MYEA_AF_RELU: case MYEA_AF_LEAKY_RELU: case MYEA_AF_ELU: case MYEA_AF_SELU: case MYEA_AF_LINEAR: return true;
+    default: return false;
+  }
+}
+
 int activation_forward(Context &ctx, const float *z, float *out, long long rows, long long H, uint32_t af, const float *col_scale,
                        const float *col_shift, const uint8_t *mask, float keep_scale, const PanelSink *sink) {
   ctx.begin(TC_ELEMENTWISE);
@@ -403,7 +411,8 @@ int activation_forward(Context &ctx, const float *z, float *out, long long rows,
       MYEA_AF_CASE(MYEA_AF_LEAKY_RELU);
       MYEA_AF_CASE(MYEA_AF_ELU);
       MYEA_AF_CASE(MYEA_AF_SELU);
-      default: activation_forward_panels_kernel<MYEA_AF_LINEAR><<<grid, 256, 0, ctx.stream>>>(z, out, rows, H, col_scale, col_shift, mask, keep_scale, *sink); break;
+      case MYEA_AF_LINEAR: activation_forward_panels_kernel<MYEA_AF_LINEAR><<<grid, 256, 0, ctx.stream>>>(z, out, rows, H, col_scale, col_shift, mask, keep_scale, *sink); break;
+      default: return MYEA_E_INVALID;  // activation_writes_panels(af) is false: the caller asks for plain arrays
     }
 #undef MYEA_AF_CASE
     ctx.end(TC_ELEMENTWISE);

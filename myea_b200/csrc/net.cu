@@ -568,7 +568,7 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
   // the layer that reads this one's output from shared operand panels gets them from the activation kernel
   PanelSink sink;
   bool use_sink = false;
-  if (li + 1 < net->layers.size() && L.desc.type_activation_function != MYEA_AF_SOFTMAX && (rows & 7) == 0 && (L.n_out & 7) == 0 &&
+  if (li + 1 < net->layers.size() && activation_writes_panels(L.desc.type_activation_function) && (rows & 7) == 0 && (L.n_out & 7) == 0 &&
       net->ctx.gemm_engine == 0) {
     LayerPlan &N = net->layers[li + 1];
     if (N.type == MYEA_LAYER_FULLY_CONNECTED && N.input_layer == static_cast<int>(li) && fc_uses_shared_panels(net, N, rows)) {
@@ -803,7 +803,7 @@ int fc_backward_from_fc(myea_b200_net *net, LayerPlan &L, const LayerPlan &next,
     e.deriv_af = af;
     // the derivative of tanh / sigmoid is a function of the output alone, that of ReLU of the pre-activation alone
     // (Activation_Functions.hpp); an array the derivative does not read is not fetched
-    const bool wants_pre = !(af == MYEA_AF_TANH || af == MYEA_AF_SIGMOID), wants_y = !(af == MYEA_AF_RELU || af == MYEA_AF_LEAKY_RELU);
+    const bool wants_pre = af_derive_reads_summation(af), wants_y = af_derive_reads_value(af);
     e.aux_pre = wants_pre ? L.summations : nullptr;
     e.aux_y = wants_y ? L.values : nullptr;
     e.ld_aux = L.n_out;
@@ -874,8 +874,8 @@ extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
         Epilogue fin;
         const uint32_t af = P.desc.type_activation_function;
         fin.deriv_af = af;
-        fin.aux_pre = (af == MYEA_AF_TANH || af == MYEA_AF_SIGMOID) ? nullptr : P.summations;
-        fin.aux_y = (af == MYEA_AF_RELU || af == MYEA_AF_LEAKY_RELU) ? nullptr : P.values;
+        fin.aux_pre = af_derive_reads_summation(af) ? P.summations : nullptr;
+        fin.aux_y = af_derive_reads_value(af) ? P.values : nullptr;
         fin.ld_aux = P.n_out;
         P.bwd_fused_chunks = 0;
         RC(lstm_backward_to_input(net, N, P.deriv, P, &fin));

@@ -25,7 +25,26 @@ F = np.float32
 # ---------------------------------------------------------------------------------------------------------------
 # activation functions: Header_Files/Neural_Network/Activation_Functions.hpp:34-183, Neural_Network.cpp:3157-3204
 # ---------------------------------------------------------------------------------------------------------------
+_STEP_SIGMOID = ((-2.64665246, -1.47221947, -0.549306154, 0.549306154, 1.47221935, 2.64665294),
+                 (0.00499999989, 0.0500000007, 0.25, 0.75, 0.949999988, 0.995000005), 0.0, 1.0)
+_STEP_TANH = ((-2.64665294, -1.47221935, -0.549306154, 0.549306154, 1.47221935, 2.64665294),
+              (-0.99000001, -0.899999976, -0.5, 0.5, 0.899999976, 0.99000001), -1.0, 1.0)
+
+
+def _stepwise(z, table):
+    """AF_STEPWISE_real (Activation_Functions.hpp:28-31): linear between six points, constant outside"""
+    dt = z.dtype.type
+    v, r, lo, hi = table
+    v, r = [dt(np.float32(x)) for x in v], [dt(np.float32(x)) for x in r]
+    out = np.full_like(z, dt(hi))
+    for k in range(4, -1, -1):
+        seg = (((r[k + 1] - r[k]) * (z - v[k])) / (v[k + 1] - v[k])) + r[k]
+        out = np.where(z < v[k + 1], seg, out)
+    return np.where(z < v[0], dt(lo), out)
+
+
 def af_fire(af, z):
+    """AF_FIRE (Activation_Functions.hpp:124-196)"""
     dt = z.dtype.type
     if af == capi.AF_TANH:
         return dt(2) / (dt(1) + np.exp(dt(-2) * z)) - dt(1)
@@ -33,33 +52,91 @@ def af_fire(af, z):
         return dt(1) / (dt(1) + np.exp(-z))
     if af == capi.AF_RELU:
         return np.where(z < 0, dt(0), z)
-    if af == capi.AF_LEAKY_RELU:
+    if af in (capi.AF_LEAKY_RELU, capi.AF_PARAMETRIC_RELU):
         return np.where(z < 0, dt(0.01) * z, z)
     if af == capi.AF_ELU:
         return np.where(z < 0, np.exp(np.minimum(z, 0)) - dt(1), z)
     if af == capi.AF_SELU:
         a, s = dt(1.6732632423543772848170429916717), dt(1.0507009873554804934193349852946)
         return s * np.where(z <= 0, a * np.exp(np.minimum(z, 0)) - a, z)
+    if af == capi.AF_LINEAR_PIECE:
+        return np.where(z < 0, dt(0), np.where(z > 1, dt(1), z))
+    if af == capi.AF_LINEAR_PIECE_SYMMETRIC:
+        return np.where(z < -1, dt(-1), np.where(z > 1, dt(1), z))
+    if af == capi.AF_SIGMOID_STEPWISE:
+        return _stepwise(z, _STEP_SIGMOID)
+    if af == capi.AF_TANH_STEPWISE:
+        return _stepwise(z, _STEP_TANH)
+    if af == capi.AF_THRESHOLD:
+        return np.where(z < 0, dt(0), dt(1)).astype(z.dtype)
+    if af == capi.AF_THRESHOLD_SYMMETRIC:
+        return np.where(z < 0, dt(-1), dt(1)).astype(z.dtype)
+    if af == capi.AF_GAUSSIAN:
+        return np.exp(-z * z)
+    if af == capi.AF_GAUSSIAN_SYMMETRIC:
+        return np.exp(-z * z) * dt(2) - dt(1)
+    if af == capi.AF_GAUSSIAN_STEPWISE:
+        return np.zeros_like(z)
+    if af == capi.AF_ELLIOT:
+        return (z / dt(2)) / (dt(1) + np.abs(z)) + dt(0.5)
+    if af == capi.AF_ELLIOT_SYMMETRIC:
+        return z / (dt(1) + np.abs(z))
+    if af == capi.AF_SINE:
+        return np.sin(z) / dt(2) + dt(0.5)
+    if af == capi.AF_SINE_SYMMETRIC:
+        return np.sin(z)
+    if af == capi.AF_COSINE:
+        return np.cos(z) / dt(2) + dt(0.5)
+    if af == capi.AF_COSINE_SYMMETRIC:
+        return np.cos(z)
+    if af == capi.AF_ISRU:
+        return z * (dt(1) / np.sqrt(dt(1) + z * z))
+    if af == capi.AF_ISRLU:
+        return np.where(z < 0, z * (dt(1) / np.sqrt(dt(1) + z * z)), z)
     return z  # linear
 
 
 def af_derive(af, z, y):
+    """Activation_Function_Derive (Neural_Network.cpp:3157-3199), steepness 1; functions outside its switch get the value"""
     dt = y.dtype.type
     one = np.ones_like(y)
-    if af == capi.AF_TANH:
+    if af in (capi.AF_TANH, capi.AF_TANH_STEPWISE):
         return dt(1) - y * y
-    if af == capi.AF_SIGMOID:
+    if af in (capi.AF_SIGMOID, capi.AF_SIGMOID_STEPWISE):
         return y * (dt(1) - y)
     if af == capi.AF_RELU:
         return np.where(z < 0, dt(0), one)
-    if af == capi.AF_LEAKY_RELU:
+    if af in (capi.AF_LEAKY_RELU, capi.AF_PARAMETRIC_RELU):
         return np.where(z < 0, dt(0.01), one)
     if af == capi.AF_ELU:          # steepness * alpha * y below zero, y = e^z - 1 (not alpha * e^z)
         return np.where(z < 0, y, one)
     if af == capi.AF_SELU:
         a, s = dt(1.6732632423543772848170429916717), dt(1.0507009873554804934193349852946)
         return s * np.where(z <= 0, y + a, one)
-    return one  # linear, softmax
+    if af == capi.AF_GAUSSIAN:
+        return dt(-2) * z * y
+    if af == capi.AF_GAUSSIAN_SYMMETRIC:
+        return dt(-2) * z * (y + dt(1))
+    if af == capi.AF_ELLIOT:
+        return dt(1) / (dt(2) * (dt(1) + np.abs(z)) * (dt(1) + np.abs(z)))
+    if af == capi.AF_ELLIOT_SYMMETRIC:
+        return dt(1) / ((dt(1) + np.abs(z)) * (dt(1) + np.abs(z)))
+    if af == capi.AF_SINE:
+        return np.cos(z) / dt(2)
+    if af == capi.AF_SINE_SYMMETRIC:
+        return np.cos(z)
+    if af == capi.AF_COSINE:
+        return -np.sin(z) / dt(2)
+    if af == capi.AF_COSINE_SYMMETRIC:
+        return -np.sin(z)
+    if af in (capi.AF_ISRU, capi.AF_ISRLU):
+        zs = np.where(z == 0, dt(1), z)
+        q = np.where(z == 0, dt(1), y / zs)
+        cube = q * q * q
+        return cube if af == capi.AF_ISRU else np.where(z < 0, cube, one)
+    if af in (capi.AF_THRESHOLD, capi.AF_THRESHOLD_SYMMETRIC, capi.AF_GAUSSIAN_STEPWISE):
+        return y
+    return one  # linear, linear piece, softmax
 
 
 # ---------------------------------------------------------------------------------------------------------------

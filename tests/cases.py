@@ -115,6 +115,19 @@ CASES_ORACLE_ONLY = {
 
 
 
+# every activation function of the reference besides the ones the cases above already use (hidden layers of a small
+# network, one of them normalized so that the derivative sees the normalized summation; momentum descent)
+AF_NAMES = {capi.AF_COSINE: "cosine", capi.AF_COSINE_SYMMETRIC: "cosine_symmetric", capi.AF_ELLIOT: "elliot",
+            capi.AF_ELLIOT_SYMMETRIC: "elliot_symmetric", capi.AF_GAUSSIAN: "gaussian", capi.AF_GAUSSIAN_SYMMETRIC: "gaussian_symmetric",
+            capi.AF_ISRU: "isru", capi.AF_ISRLU: "isrlu", capi.AF_LINEAR_PIECE: "linear_piece",
+            capi.AF_LINEAR_PIECE_SYMMETRIC: "linear_piece_symmetric", capi.AF_PARAMETRIC_RELU: "parametric_relu", capi.AF_SINE: "sine",
+            capi.AF_SIGMOID_STEPWISE: "sigmoid_stepwise", capi.AF_SINE_SYMMETRIC: "sine_symmetric", capi.AF_TANH_STEPWISE: "tanh_stepwise",
+            capi.AF_LEAKY_RELU: "leaky_relu"}
+for _af, _n in AF_NAMES.items():
+    CASES["mlp_af_" + _n] = (lambda af=_af, n=_n: _mlp_variant("af_" + n, [16, 12], af, capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9), B=9, n_in=10,
+                                                            n_out=4, norm=capi.NORM_BN if af in (capi.AF_GAUSSIAN, capi.AF_ISRU, capi.AF_SINE) else capi.NORM_NONE))
+
+
 def _lstm_blocks_case(name, opt, cpb, T=4, B=5, n_in=7, blocks=(4, 3), out=12, zoneout=0.3, delays=1):
     """LSTM blocks of `cpb` cells each (the cells of a block share its gates); the output layer is at least as wide as
     the last LSTM layer has cells, as the reference's shifted bias base requires"""

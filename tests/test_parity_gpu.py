@@ -65,6 +65,22 @@ def test_step_matches_oracle(name):
     gpu.close(); cpu.close()
 
 
+@pytest.mark.parametrize("af", [capi.AF_THRESHOLD, capi.AF_THRESHOLD_SYMMETRIC, capi.AF_GAUSSIAN_STEPWISE])
+def test_activations_without_a_derivative_run_forward(af):
+    """the threshold functions and the stepwise Gaussian (a constant 0 in the reference) have no entry in the reference's
+    derivative switch; their forward values are checked against the restatement, inference mode"""
+    wl = cases._mlp_variant("af_%d" % af, [16, 12], af, capi.opt(capi.OPT_GD, gd_lr=0.01), B=9, n_in=10, n_out=4)
+    gpu, cpu = Net(wl.desc, wl.opt), myea_oracle.OracleNet(wl.desc, wl.opt)
+    X, _ = wl.batch()
+    for net in (gpu, cpu):
+        wl.materialize(net)
+        net.forward(X, training=False)
+    for l in range(1, len(wl.layers)):
+        a, b = np.asarray(gpu.outputs(l), np.float32).ravel(), np.asarray(cpu.outputs(l), np.float32).ravel()
+        assert (np.abs(a - b) > 1e-4).mean() < 0.02, l      # a summation within rounding of the threshold may land on either side
+    gpu.close()
+
+
 @pytest.mark.parametrize("name", sorted(cases.CASES_WITHOUT_REFERENCE))
 def test_step_matches_restatement_where_the_reference_cannot_serve(name):
     """bidirectional LSTM: checked against the numpy restatement (parity against the reference binary is unpinned here)"""
