@@ -146,6 +146,11 @@ typedef struct myea_opt_desc {
    * inside its own training loop the two are always equal at update time; a caller may pass them differently. */
   float rprop_increase_factor, rprop_decrease_factor, rprop_delta_min, rprop_delta_max, rprop_delta_zero;
   float loss_rprop, previous_loss_rprop;
+  /* Set__Regularization__L1 / __L2 (Data.hpp:2742-2743).  Accepted, kept in checkpoints, and WITHOUT effect on the step, as
+   * in the reference: Update_Parameter hands (batch, 0, total_weights) to routines that take (start, end, batch)
+   * (Neural_Network.cpp:4729-4741, 4832-4844 against Neural_Network__Regularization__L1.cpp:99-128, __L2.cpp alike), so
+   * their loops run from `batch` to 0 and never execute. */
+  float regularization__l1, regularization__l2;
 } myea_opt_desc;
 
 /* Where one layer's parameters sit in the flat [P] buffer: the index map that

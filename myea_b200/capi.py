@@ -55,7 +55,8 @@ class OptDesc(C.Structure):
                 ("use_clip_gradient", C.c_uint32), ("clip_gradient", C.c_float), ("epoch_time_step", C.c_float),
                 ("adam_gamma", C.c_float), ("regularization__max_norm_constraints", C.c_float),
                 ("rprop_increase_factor", C.c_float), ("rprop_decrease_factor", C.c_float), ("rprop_delta_min", C.c_float),
-                ("rprop_delta_max", C.c_float), ("rprop_delta_zero", C.c_float), ("loss_rprop", C.c_float), ("previous_loss_rprop", C.c_float)]
+                ("rprop_delta_max", C.c_float), ("rprop_delta_zero", C.c_float), ("loss_rprop", C.c_float), ("previous_loss_rprop", C.c_float),
+                ("regularization__l1", C.c_float), ("regularization__l2", C.c_float)]
 
 
 class LayerIndex(C.Structure):
@@ -129,7 +130,7 @@ def net(layers, batch, T=1, loss=LOSS_MSE, accuracy=ACC_NONE, time_delays=0, mom
 
 def opt(kind=OPT_ADAM, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, bias_correction=True, final_lr=0.1, gamma=1e-3,
         weight_decay=0.0, normalized_wd=True, clip=None, gd_lr=0.01, momentum=0.0, nesterov=False, epoch=1.0, nosadam_gamma=0.1,
-        max_norm=0.0, rprop=(0.0, 0.0, 0.0, 0.0, 0.0)):
+        max_norm=0.0, rprop=(0.0, 0.0, 0.0, 0.0, 0.0), l1=0.0, l2=0.0):
     """rprop: (increase factor, decrease factor, delta min, delta max, delta zero) of iRPROP+, 0 = class default"""
     o = OptDesc()
     o.type_optimizer_function = kind
@@ -146,6 +147,7 @@ def opt(kind=OPT_ADAM, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, bias_correctio
     o.epoch_time_step = epoch
     o.adam_gamma = nosadam_gamma
     o.regularization__max_norm_constraints = max_norm
+    o.regularization__l1, o.regularization__l2 = l1, l2
     (o.rprop_increase_factor, o.rprop_decrease_factor, o.rprop_delta_min, o.rprop_delta_max, o.rprop_delta_zero) = rprop
     return o
 

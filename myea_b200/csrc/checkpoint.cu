@@ -395,8 +395,8 @@ std::string format_general(const myea_net_desc &d, const myea_opt_desc &o) {
   close("TRAINING PARAMETERS");
   open("REGULARIZATION PARAMETERS");
   put("regularization__max_norm_constraints", real(o.regularization__max_norm_constraints));
-  put("regularization__l1", "0");
-  put("regularization__l2", "0");
+  put("regularization__l1", real(o.regularization__l1));
+  put("regularization__l2", real(o.regularization__l2));
   put("regularization__srip", "0");
   put("regularization__weight_decay", real(o.regularization__weight_decay));
   put("use_normalized_weight_decay", num(o.use_normalized_weight_decay ? 1 : 0));
@@ -775,7 +775,9 @@ int parse_general(const char *path, myea_net_desc &d, myea_opt_desc &o, std::str
     else if (k == "batch_renormalization_r_correction_maximum") d.batch_renormalization_r_correction_maximum = f;
     else if (k == "batch_renormalization_d_correction_maximum") d.batch_renormalization_d_correction_maximum = f;
     else if (k == "accuracy_variance") d.accuracy_variance = f;
-    else if ((k == "regularization__l1" || k == "regularization__l2" || k == "regularization__srip") && v != 0.0) {
+    else if (k == "regularization__l1") o.regularization__l1 = f;
+    else if (k == "regularization__l2") o.regularization__l2 = f;
+    else if (k == "regularization__srip" && v != 0.0) {
       error = k + " is set: that penalty is not built";
       return MYEA_E_UNSUPPORTED;
     } else if (k == "use_Warm_Restarts" && u != 0) {

@@ -350,6 +350,9 @@ int optimizer_update(Context &ctx, const OptLaunch &o, float *w, float *g, float
 // every row of w[rows][cols] whose Euclidean norm is >= max_norm is scaled to norm max_norm (Euclidean_Norm__Loop,
 // Neural_Network__Regularization__Max_Norm_Constraints.cpp:48-88)
 int row_max_norm(Context &ctx, float *w, long long rows, long long cols, float max_norm);
+// the same for the weight runs of `blocks` LSTM blocks whose first parameter is `first` (one direction has `cells` cells)
+int lstm_max_norm(Context &ctx, float *params, long long first, long long blocks, long long stride, long long n_in, long long cells,
+                  long long cells_per_block, float max_norm);
 // d_out[0] = sum g^2 (double)
 int sum_squares(Context &ctx, const float *g, size_t n, double *d_out);
 // clip_scale[0] = norm >= clip ? clip / norm : 1

@@ -1036,10 +1036,6 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
     default: return fail(net, MYEA_E_UNSUPPORTED, "optimizer not built (Adam, AMSGrad, NosAdam, AdaBound, AMSBound, gradient descent / momentum / Nesterov, iRPROP+)");
   }
   const float max_norm = opt->regularization__max_norm_constraints;
-  if (max_norm != 0.f) {
-    for (const auto &L : net->layers)
-      if (L.type == MYEA_LAYER_LSTM) return fail(net, MYEA_E_UNSUPPORTED, "max-norm constraints on LSTM blocks are not built");
-  }
   if (by_bucket) {
     const size_t count = comm_bucket_count(net);
     size_t covered = 0;
@@ -1063,6 +1059,12 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
     // Update_Weight_Regularization__Max_Norm_Constraints__Neurons (…Max_Norm_Constraints.cpp:147-165): one weight row per neuron
     for (const auto &L : net->layers)
       if (L.type == MYEA_LAYER_FULLY_CONNECTED) RC(row_max_norm(net->ctx, net->params + L.idx.first_connection_index, L.n_out, L.n_in, max_norm));
+    for (const auto &L : net->layers)
+      if (L.type == MYEA_LAYER_LSTM) {
+        const long long dirs = L.desc.use_bidirectional ? 2 : 1, cpb = std::max<long long>(1, static_cast<long long>(L.desc.unit_parameters[1]));
+        RC(lstm_max_norm(net->ctx, net->params, static_cast<long long>(L.idx.first_connection_index), static_cast<long long>(L.desc.unit_parameters[0]) * dirs,
+                         static_cast<long long>(L.idx.block_stride), L.n_in, L.n_out / dirs, cpb, max_norm));
+      }
   }
   return MYEA_OK;
 }

@@ -193,6 +193,51 @@ __global__ void __launch_bounds__(256) row_max_norm_kernel(float *__restrict__ w
   }
 }
 
+// LSTM blocks (Update_Weight_Regularization__Max_Norm_Constraints__LSTMs, …Max_Norm_Constraints.cpp:167-310): every run
+// of weights is a vector of its own - per cell the input and the recurrent weights of the cell input, per block those
+// of the three gates, and the three peephole runs.  One thread block per run: grid (blocks of the layer, 2 cpb + 9).
+// The reference tests `first_index > start` with start = 0: a run that begins at parameter 0 is passed over.
+__global__ void __launch_bounds__(256) lstm_max_norm_kernel(float *__restrict__ params, long long first, long long stride, long long I, long long C,
+                                                            long long cpb, float max_norm) {
+  __shared__ float sh[256];
+  const long long s = blockIdx.y, base = first + static_cast<long long>(blockIdx.x) * stride;
+  long long at, len;
+  if (s < 2 * cpb) {
+    at = base + (s >> 1) * (I + C) + ((s & 1) ? I : 0);
+    len = (s & 1) ? C : I;
+  } else {
+    const long long g = s - 2 * cpb, g0 = base + cpb * (I + C);
+    if (g < 3) { at = g0 + g * I; len = I; }
+    else if (g < 6) { at = g0 + 3 * I + (g - 3) * C; len = C; }
+    else { at = g0 + 3 * I + 3 * C + (g - 6) * cpb; len = cpb; }
+  }
+  if (at == 0) return;
+  float *v = params + at;
+  float acc = 0.f;
+  for (long long j = threadIdx.x; j < len; j += blockDim.x) acc = fmaf(v[j], v[j], acc);
+  sh[threadIdx.x] = acc;
+  __syncthreads();
+  for (int h = 128; h > 0; h >>= 1) {
+    if (threadIdx.x < h) sh[threadIdx.x] += sh[threadIdx.x + h];
+    __syncthreads();
+  }
+  const float norm = sqrtf(sh[0]);
+  if (norm >= max_norm) {
+    const float scale = max_norm / norm;
+    for (long long j = threadIdx.x; j < len; j += blockDim.x) v[j] *= scale;
+  }
+}
+
+int lstm_max_norm(Context &ctx, float *params, long long first, long long blocks, long long stride, long long n_in, long long cells,
+                  long long cells_per_block, float max_norm) {
+  if (blocks <= 0) return MYEA_OK;
+  ctx.begin(TC_OPTIMIZER);
+  lstm_max_norm_kernel<<<dim3(static_cast<unsigned>(blocks), static_cast<unsigned>(2 * cells_per_block + 9)), 256, 0, ctx.stream>>>(
+      params, first, stride, n_in, cells, cells_per_block, max_norm);
+  ctx.end(TC_OPTIMIZER);
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
 int row_max_norm(Context &ctx, float *w, long long rows, long long cols, float max_norm) {
   if (rows <= 0 || cols <= 0) return MYEA_OK;
   ctx.begin(TC_OPTIMIZER);

@@ -48,6 +48,10 @@ class Neural_Network {
   bool Set__Number_Time_Delays(size_t d) { desc_.number_time_delays = d; return d < desc_.number_recurrent_depth; }
   bool Set__Regularization__Weight_Decay(float v) { opt_.regularization__weight_decay = v; return v >= 0.f; }
   bool Set__Regularization__Max_Norm_Constraints(float v) { opt_.regularization__max_norm_constraints = v; return v >= 0.f; }
+  // range checks of Set__Regularization__L1 / __L2 (Neural_Network__Regularization__L1.cpp:24-46); the step ignores both
+  // penalties, as the reference's own does (see myea_opt_desc)
+  bool Set__Regularization__L1(float v) { if (v < 0.f || v > 1.f) return false; opt_.regularization__l1 = v; return true; }
+  bool Set__Regularization__L2(float v) { if (v < 0.f || v > 1.f) return false; opt_.regularization__l2 = v; return true; }
   void Set__Clip_Gradient(bool use) { opt_.use_clip_gradient = use ? 1u : 0u; }
   bool Set__Clip_Gradient(float v) { opt_.clip_gradient = v; return v > 0.f; }
   bool Set__Normalization_Momentum_Average(float v) { desc_.normalization_momentum_average = v; return v > 0.f && v <= 1.f; }

@@ -582,4 +582,29 @@ class OracleNet:
                 norms = np.sqrt((W * W).sum(axis=1, dtype=dt))
                 big = norms >= c
                 W[big] *= (c / norms[big])[:, None]
+            # LSTM blocks (…Max_Norm_Constraints.cpp:167-310): every run of weights is its own vector - per cell the input and
+            # the recurrent weights of the cell input, per block those of the three gates and the three peephole runs.  A
+            # run that starts at parameter 0 is passed over (`first_index > start_index` with start 0).
+            for L in self.layers[1:]:
+                if L.type != capi.LAYER_LSTM:
+                    continue
+                dirs = 2 if L.d.use_bidirectional else 1
+                cpb, K, I, S = max(1, int(L.d.unit_parameters[1])), int(L.d.unit_parameters[0]), L.n_in, L.idx["block_stride"]
+                C = K * cpb
+                p = self._p()
+                for k in range(dirs * K):
+                    base = L.idx["first_connection_index"] + k * S
+                    runs = []
+                    for j in range(cpb):
+                        runs += [(base + j * (I + C), I), (base + j * (I + C) + I, C)]
+                    g0 = base + cpb * (I + C)
+                    runs += [(g0 + g * I, I) for g in range(3)] + [(g0 + 3 * I + g * C, C) for g in range(3)]
+                    runs += [(g0 + 3 * I + 3 * C + g * cpb, cpb) for g in range(3)]
+                    for a, n in runs:
+                        if a == 0:
+                            continue
+                        v = p[a:a + n]
+                        norm = np.sqrt((v * v).sum(dtype=dt))
+                        if norm >= c:
+                            v *= c / norm
         g[:] = 0

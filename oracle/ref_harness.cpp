@@ -46,6 +46,8 @@ void apply_opt(Neural_Network &nn, const myea_opt_desc &o) {
   nn.epoch_time_step = o.epoch_time_step;
   if (o.adam_gamma > 0.f) nn.adam_gamma = o.adam_gamma;
   nn.Set__Regularization__Max_Norm_Constraints(o.regularization__max_norm_constraints);
+  nn.Set__Regularization__L1(o.regularization__l1);
+  nn.Set__Regularization__L2(o.regularization__l2);
   if (o.rprop_increase_factor > 0.f) nn.rprop_increase_factor = o.rprop_increase_factor;
   if (o.rprop_decrease_factor > 0.f) nn.rprop_decrease_factor = o.rprop_decrease_factor;
   if (o.rprop_delta_min > 0.f) nn.rprop_delta_min = o.rprop_delta_min;

@@ -156,6 +156,11 @@ CASES.update({
     "lstm_two_cells_per_block": lambda: _lstm_blocks_case("lstm_cpb2", capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9), 2),
     "lstm_three_cells_per_block_adam": lambda: _lstm_blocks_case("lstm_cpb3", capi.opt(capi.OPT_ADAM), 3, blocks=(3, 2), delays=0),
     "lstm_width_7": lambda: _lstm_case("lstm_w7", capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9), H=7, out=9, delays=1),
+    # max-norm constraint on LSTM weight runs (the run that starts at parameter 0 is passed over, as in the reference)
+    "lstm_max_norm": lambda: _lstm_case("lstm_mn", capi.opt(capi.OPT_GD, gd_lr=0.05, momentum=0.9, max_norm=0.6), layers=1, H=8, out=8, delays=0),
+    "lstm_two_cells_max_norm": lambda: _lstm_blocks_case("lstm_cpb2_mn", capi.opt(capi.OPT_GD, gd_lr=0.05, momentum=0.9, max_norm=0.5), 2),
+    # L1 / L2 penalties: accepted and without effect (the reference's call hands its arguments over in the wrong order)
+    "mlp_l1_l2_without_effect": lambda: _mlp_variant("l1l2", [14], capi.AF_TANH, capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9, l1=0.05, l2=0.05), B=8),
     # recurrent networks with fully connected hidden layers around the LSTM layer and Bernoulli dropout drawn per time step
     "lstm_between_fc_bernoulli": lambda: _lstm_fc_case("lstm_fc", capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9)),
     # zero-padded identity: the block narrower / wider than its shortcut, and the residual layer's own normalization
