@@ -32,7 +32,7 @@ def test_struct_layouts_match_header():
     # sizes implied by the header's field lists on an LP64 ABI
     assert C.sizeof(capi.LayerDesc) == 4 + 4 + 5 * 8 + 4 * 4 + 3 * 4 + 4
     assert C.sizeof(capi.NetDesc) == 4 + 4 + 8 * 3 + 4 * 2 + 4 * 5 + 4 + capi.MAX_LAYERS * C.sizeof(capi.LayerDesc)
-    assert C.sizeof(capi.OptDesc) == 25 * 4
+    assert C.sizeof(capi.OptDesc) == 27 * 4
     assert C.sizeof(capi.LayerIndex) == 10 * 8
 
 
@@ -41,7 +41,11 @@ def test_enumerators_match_header():
     for macro, value in (("MYEA_LAYER_FULLY_CONNECTED", capi.LAYER_FC), ("MYEA_LAYER_LSTM", capi.LAYER_LSTM),
                          ("MYEA_LAYER_RESIDUAL", capi.LAYER_RESIDUAL), ("MYEA_AF_TANH", capi.AF_TANH), ("MYEA_AF_RELU", capi.AF_RELU),
                          ("MYEA_AF_SOFTMAX", capi.AF_SOFTMAX), ("MYEA_OPT_ADAM", capi.OPT_ADAM), ("MYEA_OPT_AMSGRAD", capi.OPT_AMSGRAD),
-                         ("MYEA_OPT_ADABOUND", capi.OPT_ADABOUND), ("MYEA_OPT_NOSADAM", capi.OPT_NOSADAM), ("MYEA_OPT_IRPROP_PLUS", capi.OPT_IRPROP_PLUS), ("MYEA_LOSS_MSE", capi.LOSS_MSE), ("MYEA_DROPOUT_ZONEOUT", capi.DROP_ZONEOUT)):
+                         ("MYEA_OPT_ADABOUND", capi.OPT_ADABOUND), ("MYEA_OPT_NOSADAM", capi.OPT_NOSADAM), ("MYEA_OPT_IRPROP_PLUS", capi.OPT_IRPROP_PLUS), ("MYEA_LOSS_MSE", capi.LOSS_MSE), ("MYEA_DROPOUT_ZONEOUT", capi.DROP_ZONEOUT),
+                         ("MYEA_AF_COSINE", capi.AF_COSINE), ("MYEA_AF_ELLIOT_SYMMETRIC", capi.AF_ELLIOT_SYMMETRIC), ("MYEA_AF_GAUSSIAN_STEPWISE", capi.AF_GAUSSIAN_STEPWISE),
+                         ("MYEA_AF_ISRLU", capi.AF_ISRLU), ("MYEA_AF_LINEAR_PIECE_SYMMETRIC", capi.AF_LINEAR_PIECE_SYMMETRIC), ("MYEA_AF_PARAMETRIC_RELU", capi.AF_PARAMETRIC_RELU),
+                         ("MYEA_AF_SIGMOID_STEPWISE", capi.AF_SIGMOID_STEPWISE), ("MYEA_AF_SINE_SYMMETRIC", capi.AF_SINE_SYMMETRIC), ("MYEA_AF_TANH_STEPWISE", capi.AF_TANH_STEPWISE),
+                         ("MYEA_AF_THRESHOLD_SYMMETRIC", capi.AF_THRESHOLD_SYMMETRIC)):
         m = re.search(r"#define\s+%s\s+(\d+)u?" % macro, h)
         assert m and int(m.group(1)) == value, macro
 
