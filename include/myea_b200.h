@@ -174,8 +174,8 @@ typedef struct myea_b200_net *myea_handle;
 #define MYEA_BUF_SECOND_MOMENT 3  /* ptr_array_previous_biased_second_moment                            */
 #define MYEA_BUF_SECOND_MOMENT_HAT 4 /* ptr_array_previous_biased_second_moment_hat (AMSGrad)           */
 #define MYEA_BUF_MASK_REGULARIZED 5  /* ptr_array_mask_regularized_parameters                           */
-#define MYEA_BUF_NORM_MEAN_AVERAGE 6     /* normalized_batch_units.ptr_mean_average, all units          */
-#define MYEA_BUF_NORM_VARIANCE_AVERAGE 7 /* normalized_batch_units.ptr_variance_average, all units      */
+#define MYEA_BUF_NORM_MEAN_AVERAGE 6     /* normalized_batch_units.ptr_mean_average: units x time steps, [layer][T][units] */
+#define MYEA_BUF_NORM_VARIANCE_AVERAGE 7 /* normalized_batch_units.ptr_variance_average, same layout                       */
 #define MYEA_BUF_PREVIOUS_DELTA 8 /* ptr_array_previous_delta_parameters (GD momentum, iRPROP+)         */
 #define MYEA_BUF_PREVIOUS_DERIVATIVES 9 /* ptr_array_previous_derivatives_parameters (iRPROP+); shares the first-moment storage  */
 #define MYEA_BUF_PREVIOUS_STEPS 10      /* ptr_array_previous_steps (iRPROP+; 0 reads as rprop_delta_zero); shares the second-moment storage */
@@ -255,7 +255,9 @@ int myea_b200_evaluate(myea_handle h, const uint64_t *order, uint64_t number_exa
  *
  * The format / parse halves work on host arrays and need no GPU:
  * myea_b200_checkpoint_format_dimension / _format_general write the two files from a description, `parameters`
- *   [total_parameters] and the two average arrays [total_normalized_units] (null without normalization);
+ *   [total_parameters] and the two average arrays (null without normalization) of total_normalized_units x
+ *   number_recurrent_depth values: every time step keeps averages of its own, laid out layer after layer, each layer as
+ *   [time step][its units] (Allocate__Normalized_Unit, Neural_Network__Allocate.cpp:2643-2700);
  * myea_b200_checkpoint_parse reads them back: with `parameters` null it returns the description (batch_size filled
  *   in from the argument) and the two totals; with arrays of at least those sizes it fills them as well.
  *   `path_general` may be null (description fields that live in the `.net` file then stay 0 = class default).

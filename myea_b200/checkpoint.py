@@ -45,6 +45,7 @@ def parse(path_dimension, path_general=None, batch=1, arrays=True):
     if not arrays:
         return desc, opt, None, None, None
     params = np.zeros(P.value, np.float32)
-    mean, sigma = np.zeros(max(U.value, 1), np.float32), np.zeros(max(U.value, 1), np.float32)
-    call(params.ctypes.data, P.value, mean.ctypes.data, sigma.ctypes.data, U.value)
-    return desc, opt, params, mean[:U.value], sigma[:U.value]
+    n = U.value * max(1, int(desc.number_recurrent_depth))      # running averages: one set per time step, [layer][T][units]
+    mean, sigma = np.zeros(max(n, 1), np.float32), np.zeros(max(n, 1), np.float32)
+    call(params.ctypes.data, P.value, mean.ctypes.data, sigma.ctypes.data, n)
+    return desc, opt, params, mean[:n], sigma[:n]

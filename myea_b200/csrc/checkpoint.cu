@@ -165,7 +165,7 @@ struct Writer {
       line(10, "scale", real(params[L.idx.scale_index + u]));
       line(10, "shift", real(params[L.idx.shift_index + u]));
       for (uint64_t t = 0; t < T; ++t) {
-        const uint64_t at = static_cast<uint64_t>(L.norm_unit_offset) + u + units * t;
+        const uint64_t at = static_cast<uint64_t>(L.norm_unit_offset) * T + t * units + u;  // [layer][T][units]
         line(10, "mean_average[" + num(t) + "]", real(mean[at]));
         line(10, "variance_average[" + num(t) + "]", real(sigma[at]));
       }
@@ -456,11 +456,12 @@ extern "C" int myea_b200_save_dimension_parameters(myea_handle net, const char *
   HostPlan P;
   int rc = make_plan(&net->desc, P);
   if (rc != MYEA_OK) { net->ctx.error = P.error; return rc; }
-  std::vector<float> params(net->total_parameters + 1), mean(net->total_norm_units + 1), sigma(net->total_norm_units + 1);
+  const uint64_t averages = net->total_norm_units * static_cast<uint64_t>(net->T);  // one set per time step
+  std::vector<float> params(net->total_parameters + 1), mean(averages + 1), sigma(averages + 1);
   rc = myea_b200_download(net, MYEA_BUF_PARAMETERS, params.data(), 0, net->total_parameters);
-  if (rc == MYEA_OK && net->total_norm_units != 0) {
-    rc = myea_b200_download(net, MYEA_BUF_NORM_MEAN_AVERAGE, mean.data(), 0, net->total_norm_units);
-    if (rc == MYEA_OK) rc = myea_b200_download(net, MYEA_BUF_NORM_VARIANCE_AVERAGE, sigma.data(), 0, net->total_norm_units);
+  if (rc == MYEA_OK && averages != 0) {
+    rc = myea_b200_download(net, MYEA_BUF_NORM_MEAN_AVERAGE, mean.data(), 0, averages);
+    if (rc == MYEA_OK) rc = myea_b200_download(net, MYEA_BUF_NORM_VARIANCE_AVERAGE, sigma.data(), 0, averages);
   }
   if (rc != MYEA_OK) return rc;
   std::string text;
@@ -806,10 +807,11 @@ int place(const Parsed &in, uint64_t batch_size, HostPlan &P, float *params, flo
   std::fill(params, params + net.total_parameters, 0.f);
   for (uint64_t l = 0; l < net.layers.size() && net.any_norm; ++l) {  // units without a file entry: gamma 1, sigma 1 (Allocate__Normalized_Unit)
     const LayerPlan &L = net.layers[l];
-    for (uint64_t u = 0; u < L.idx.number_units_norm; ++u) {
-      params[L.idx.scale_index + u] = 1.f;
-      mean[L.norm_unit_offset + u] = 0.f;
-      sigma[L.norm_unit_offset + u] = 1.f;
+    const uint64_t T = static_cast<uint64_t>(net.T), units = L.idx.number_units_norm;
+    for (uint64_t u = 0; u < units; ++u) params[L.idx.scale_index + u] = 1.f;
+    for (uint64_t i = 0; i < units * T; ++i) {   // running averages: [layer][T][units]
+      mean[static_cast<uint64_t>(L.norm_unit_offset) * T + i] = 0.f;
+      sigma[static_cast<uint64_t>(L.norm_unit_offset) * T + i] = 1.f;
     }
   }
   for (const auto &w : in.weights) {
@@ -821,11 +823,14 @@ int place(const Parsed &in, uint64_t batch_size, HostPlan &P, float *params, flo
     const LayerPlan &L = net.layers[l];
     if (nv.scale.empty()) continue;
     if (nv.scale.size() != L.idx.number_units_norm) { error = "normalized units of a layer differ from its width"; return MYEA_E_INVALID; }
-    for (uint64_t u = 0; u < nv.scale.size(); ++u) {
+    const uint64_t T = static_cast<uint64_t>(net.T), units = nv.scale.size();
+    for (uint64_t u = 0; u < units; ++u) {
       params[L.idx.scale_index + u] = nv.scale[u];
       params[L.idx.shift_index + u] = nv.shift[u];
-      mean[L.norm_unit_offset + u] = nv.mean[u];    // time step 0: normalized layers exist in feed-forward networks only
-      sigma[L.norm_unit_offset + u] = nv.sigma[u];
+    }
+    for (uint64_t i = 0; i < units * T && i < nv.mean.size(); ++i) {   // the file's [t][unit] order is the arrays' order
+      mean[static_cast<uint64_t>(L.norm_unit_offset) * T + i] = nv.mean[i];
+      sigma[static_cast<uint64_t>(L.norm_unit_offset) * T + i] = nv.sigma[i];
     }
   }
   return MYEA_OK;
@@ -855,8 +860,9 @@ extern "C" int myea_b200_checkpoint_parse(const char *path_dimension, const char
   if (total_parameters) *total_parameters = in.total_parameters;
   if (total_normalized_units) *total_normalized_units = in.total_norm_units;
   const bool fill = parameters != nullptr;
+  const uint64_t averages = in.total_norm_units * std::max<uint64_t>(1, in.desc.number_recurrent_depth);
   if (fill && (parameters_capacity < in.total_parameters ||
-               (in.total_norm_units != 0 && (mean_average == nullptr || variance_average == nullptr || norm_capacity < in.total_norm_units)))) {
+               (averages != 0 && (mean_average == nullptr || variance_average == nullptr || norm_capacity < averages)))) {
     g_parse_error = "arrays too small for the file's parameters";
     return MYEA_E_INVALID;
   }
@@ -876,6 +882,7 @@ extern "C" int myea_b200_load(myea_handle *out, const char *path_dimension, cons
   uint64_t P = 0, U = 0;
   int rc = myea_b200_checkpoint_parse(path_dimension, path_general, batch_size, &desc, opt, nullptr, 0, nullptr, nullptr, 0, &P, &U);
   if (rc != MYEA_OK) return rc;
+  U *= std::max<uint64_t>(1, desc.number_recurrent_depth);  // running averages: one set per time step
   std::vector<float> params(P + 1), mean(U + 1), sigma(U + 1);
   rc = myea_b200_checkpoint_parse(path_dimension, path_general, batch_size, &desc, opt, params.data(), P, mean.data(), sigma.data(), U, nullptr, nullptr);
   if (rc != MYEA_OK) return rc;

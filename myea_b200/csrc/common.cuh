@@ -323,6 +323,9 @@ int norm_forward_stats(Context &ctx, const float *z, long long rows, long long H
 bool activation_writes_panels(uint32_t af);
 int activation_forward(Context &ctx, const float *z, float *out, long long rows, long long H, uint32_t af,
                        const float *col_scale, const float *col_shift, const uint8_t *mask, float keep_scale, const PanelSink *sink = nullptr);
+// in place: d *= f'(z * col_scale + col_shift, y) (col_scale null: the summation itself)
+int activation_backward(Context &ctx, float *d, const float *z, const float *y, long long rows, long long H, uint32_t af, const float *col_scale,
+                        const float *col_shift);
 int softmax_forward(Context &ctx, const float *z, float *out, long long rows, long long H);
 // delta_af [rows,H] (error after the activation derivative) -> error before the normalization, plus d_gamma / d_beta
 int norm_backward(Context &ctx, const float *z, const float *delta_af, float *delta_out, long long rows, long long H,

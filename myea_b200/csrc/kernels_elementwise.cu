@@ -479,6 +479,29 @@ __global__ void __launch_bounds__(128) softmax_forward_kernel(const float *__res
   for (long long j = threadIdx.x; j < H; j += blockDim.x) orow[j] *= inv;
 }
 
+// d[r][c] *= f'(z[r][c] * col_scale[c] + col_shift[c], y[r][c])   (Backward_Pass__FC__DF, Neural_Network__Backward_Pass__OpenMP.cpp:1225-1263)
+__global__ void __launch_bounds__(256) activation_backward_kernel(float *__restrict__ d, const float *__restrict__ z, const float *__restrict__ y,
+                                                                  long long rows, long long H, uint32_t af, const float *__restrict__ col_scale,
+                                                                  const float *__restrict__ col_shift) {
+  const long long total = rows * H;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long c = i % H;
+    const float pre = col_scale != nullptr ? fmaf(z[i], col_scale[c], col_shift[c]) : z[i];
+    d[i] *= af_derive(af, pre, y[i]);
+  }
+}
+
+int activation_backward(Context &ctx, float *d, const float *z, const float *y, long long rows, long long H, uint32_t af, const float *col_scale,
+                        const float *col_shift) {
+  if (rows <= 0 || H <= 0) return MYEA_OK;
+  ctx.begin(TC_ELEMENTWISE);
+  const int blocks = static_cast<int>(std::max<long long>(1, std::min<long long>((rows * H + 255) / 256, 148 * 16)));
+  activation_backward_kernel<<<blocks, 256, 0, ctx.stream>>>(d, z, y, rows, H, af, col_scale, col_shift);
+  ctx.end(TC_ELEMENTWISE);
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
 int softmax_forward(Context &ctx, const float *z, float *out, long long rows, long long H) {
   ctx.begin(TC_ELEMENTWISE);
   softmax_forward_kernel<<<static_cast<unsigned>(rows), 128, 0, ctx.stream>>>(z, out, H);

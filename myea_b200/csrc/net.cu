@@ -204,8 +204,13 @@ int myea::build_index_map(myea_b200_net *net) {
     for (uint32_t l = 0; l < n; ++l) {
       LayerPlan &L = net->layers[l];
       L.norm_unit_offset = static_cast<long long>(units);
-      if (L.type == MYEA_LAYER_LSTM) return fail(net, MYEA_E_UNSUPPORTED, "normalization in a network with LSTM layers is not built");
+      if (L.type == MYEA_LAYER_LSTM && d.layers[l].type_normalization != MYEA_NORM_NONE)
+        return fail(net, MYEA_E_UNSUPPORTED, "normalization of an LSTM layer's own gates and cell inputs is not built");
       long long own = L.n_out;
+      if (L.type == MYEA_LAYER_LSTM) {  // three per cell and six per block, counted although the layer does not normalize
+        const long long dirs = d.layers[l].use_bidirectional ? 2 : 1;
+        own = 3 * L.n_out + 6 * static_cast<long long>(d.layers[l].unit_parameters[0]) * dirs;
+      }
       if (L.type == MYEA_LAYER_RESIDUAL) own = net->layers[l + L.block_depth].n_out;
       else if (l > 0 && layer_in_block(net, static_cast<int>(l), nullptr)) own = L.n_in;
       L.idx.number_units_norm = static_cast<uint64_t>(own);
@@ -297,7 +302,9 @@ static int allocate_buffers(myea_b200_net *net) {
   net->layers[0].values = net->d_input;
   // normalization state
   if (net->any_norm) {
-    const size_t U = net->total_norm_units;
+    // every time step keeps statistics of its own (gamma and beta are shared): arrays of T * units values, one layer
+    // after the other, each layer as [T][its units] (Allocate__Normalized_Unit, Neural_Network__Allocate.cpp:2643-2700)
+    const size_t U = net->total_norm_units * static_cast<size_t>(net->T);
     RC(dev_alloc(net, &net->norm_mean_avg, U));
     RC(dev_alloc(net, &net->norm_sigma_avg, U));
     RC(dev_alloc(net, &net->norm_stats, U * 6));
@@ -318,7 +325,7 @@ static int allocate_buffers(myea_b200_net *net) {
       np.beta = net->params + L.idx.shift_index;
       np.d_gamma = net->grads + L.idx.scale_index;
       np.d_beta = net->grads + L.idx.shift_index;
-      const size_t o = L.norm_unit_offset;
+      const size_t o = static_cast<size_t>(L.norm_unit_offset) * static_cast<size_t>(net->T);  // time step 0 of this layer
       np.mean_avg = net->norm_mean_avg + o;
       np.sigma_avg = net->norm_sigma_avg + o;
       np.mean = net->norm_stats + 0 * U + o;
@@ -425,8 +432,8 @@ static float *select_buffer(myea_b200_net *net, int which, size_t *count) {
     case MYEA_BUF_SECOND_MOMENT_HAT: return net->m2hat;
     case MYEA_BUF_MASK_REGULARIZED: return net->mask_reg;
     case MYEA_BUF_PREVIOUS_DELTA: return net->prev_delta;
-    case MYEA_BUF_NORM_MEAN_AVERAGE: *count = net->total_norm_units; return net->norm_mean_avg;
-    case MYEA_BUF_NORM_VARIANCE_AVERAGE: *count = net->total_norm_units; return net->norm_sigma_avg;
+    case MYEA_BUF_NORM_MEAN_AVERAGE: *count = net->total_norm_units * static_cast<uint64_t>(net->T); return net->norm_mean_avg;
+    case MYEA_BUF_NORM_VARIANCE_AVERAGE: *count = net->total_norm_units * static_cast<uint64_t>(net->T); return net->norm_sigma_avg;
     default: *count = 0; return nullptr;
   }
 }
@@ -546,6 +553,14 @@ int fc_product_backward(myea_b200_net *net, LayerPlan &N, long long rows, const 
   return gemm_nt(net->ctx, a, b, e, net->scratch);
 }
 
+// the normalization state of time step t of a layer
+static NormParams norm_at_step(const LayerPlan &L, long long t) {
+  NormParams np = L.norm;
+  const long long o = t * static_cast<long long>(L.idx.number_units_norm);
+  np.mean += o; np.sigma += o; np.r += o; np.d += o; np.mean_avg += o; np.sigma_avg += o; np.col_scale += o; np.col_shift += o;
+  return np;
+}
+
 int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long rows) {
   Epilogue e;
   e.C = L.summations;
@@ -553,7 +568,8 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
   e.bias = L.use_bias ? net->params + L.idx.first_bias_connection_index : nullptr;
   // batch statistics: the contraction's epilogue leaves the column sums of every 32-row block behind, where it can
   int fused_chunks = 0;
-  if (L.has_norm && net->training) {
+  const bool timewise_norm = L.has_norm && net->T > 1;  // a recurrent network normalizes every time step by itself
+  if (L.has_norm && net->training && !timewise_norm) {
     Epilogue probe = e;
     probe.stats_kind = 1;
     probe.col_stats = L.norm.partial;
@@ -568,7 +584,7 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
   // the layer that reads this one's output from shared operand panels gets them from the activation kernel
   PanelSink sink;
   bool use_sink = false;
-  if (li + 1 < net->layers.size() && activation_writes_panels(L.desc.type_activation_function) && (rows & 7) == 0 && (L.n_out & 7) == 0 &&
+  if (li + 1 < net->layers.size() && !timewise_norm && activation_writes_panels(L.desc.type_activation_function) && (rows & 7) == 0 && (L.n_out & 7) == 0 &&
       net->ctx.gemm_engine == 0) {
     LayerPlan &N = net->layers[li + 1];
     if (N.type == MYEA_LAYER_FULLY_CONNECTED && N.input_layer == static_cast<int>(li) && fc_uses_shared_panels(net, N, rows)) {
@@ -577,6 +593,23 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
       N.in_ready_rows = rows;
       use_sink = true;
     }
+  }
+  if (timewise_norm) {
+    // statistics, running averages and coefficients of step t live at t * units behind those of step 0; the rows a short
+    // batch leaves unused take part in no sum (Forward_Pass__Batch_Normalization__Training__Loop(time_step, ...),
+    // Neural_Network__Forward_Pass__Loop.cpp:4673-4750)
+    if (L.desc.type_activation_function == MYEA_AF_SOFTMAX) return MYEA_E_UNSUPPORTED;
+    const long long pitch = rows / net->T;
+    const uint8_t *mask = (net->training && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
+    const float scale = net->training ? (mask != nullptr ? L.keep_scale : 1.f) : L.infer_scale;
+    for (long long t = 0; t < net->T; ++t) {
+      const NormParams np = norm_at_step(L, t);
+      const long long off = t * pitch * L.n_out;
+      RC(norm_forward_stats(net->ctx, L.summations + off, net->active_B, L.n_out, np, net->training ? 1 : 0, &net->hook, nullptr, 0));
+      RC(activation_forward(net->ctx, L.summations + off, L.values + off, pitch, L.n_out, L.desc.type_activation_function, np.col_scale, np.col_shift,
+                            mask != nullptr ? mask + t * L.n_out : nullptr, scale, nullptr));
+    }
+    return MYEA_OK;
   }
   const float *cs = nullptr, *ch = nullptr;
   if (L.has_norm) {
@@ -868,6 +901,25 @@ extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
     if (p < 1) break;
     LayerPlan &P = net->layers[p];
     if (P.type == MYEA_LAYER_FULLY_CONNECTED) {
+      if (P.has_norm && net->T > 1) {
+        // per-time-step normalization: the error over all rows first, then step by step the activation derivative on
+        // that step's normalized summations and the normalization backward with that step's statistics
+        if (N.type == MYEA_LAYER_FULLY_CONNECTED) RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, false));
+        else RC(lstm_backward_to_input(net, N, P.deriv, P, nullptr));
+        const long long pitch = rows / net->T;
+        for (long long t = 0; t < net->T; ++t) {
+          const NormParams np = norm_at_step(P, t);
+          const long long off = t * pitch * P.n_out;
+          RC(activation_backward(net->ctx, P.deriv + off, P.summations + off, P.values + off, net->active_B, P.n_out, P.desc.type_activation_function,
+                                 np.col_scale, np.col_shift));
+          RC(norm_backward(net->ctx, P.summations + off, P.deriv + off, P.errors + off, net->active_B, P.n_out, np, &net->hook, 0, nullptr));
+        }
+        if (net->active_B < pitch)  // rows a short batch leaves unused carry no error
+          CK(cudaMemset2DAsync(P.errors + net->active_B * P.n_out, pitch * P.n_out * sizeof(float), 0, (pitch - net->active_B) * P.n_out * sizeof(float),
+                               net->T, net->ctx.stream));
+        l = p;
+        continue;
+      }
       if (N.type == MYEA_LAYER_FULLY_CONNECTED) {
         RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, true));
       } else {  // an LSTM layer above: its input contraction carries P's activation derivative in the epilogue

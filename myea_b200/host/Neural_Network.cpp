@@ -89,8 +89,8 @@ bool Neural_Network::adopt_device(void) {
   index_.resize(total_layers);
   for (size_t l = 0; l < total_layers; ++l) myea_b200_layer_index(ptr_device_Neural_Network, static_cast<uint32_t>(l), &index_[l]);
   for (int k = 0; k < 6; ++k) host_[k].assign(P, 0.f);
-  host_[6].assign(U, 0.f);
-  host_[7].assign(U, 1.f);
+  host_[6].assign(U * number_recurrent_depth, 0.f);   // running averages: one set per time step
+  host_[7].assign(U * number_recurrent_depth, 1.f);
   ptr_array_parameters = host_[0].data();
   ptr_array_derivatives_parameters = host_[1].data();
   ptr_array_previous_biased_first_moment = host_[2].data();
@@ -116,8 +116,8 @@ bool Neural_Network::Copy__Parameters__Host_To_Device(void) {
   myea_handle h = ptr_device_Neural_Network;
   int rc = myea_b200_upload(h, MYEA_BUF_PARAMETERS, ptr_array_parameters, 0, total_parameters);
   if (rc == MYEA_OK) rc = myea_b200_upload(h, MYEA_BUF_MASK_REGULARIZED, ptr_array_mask_regularized_parameters, 0, total_parameters);
-  if (rc == MYEA_OK && total_normalized_units) rc = myea_b200_upload(h, MYEA_BUF_NORM_MEAN_AVERAGE, ptr_array_normalized_batch_units_means_averages, 0, total_normalized_units);
-  if (rc == MYEA_OK && total_normalized_units) rc = myea_b200_upload(h, MYEA_BUF_NORM_VARIANCE_AVERAGE, ptr_array_normalized_batch_units_variances_averages, 0, total_normalized_units);
+  if (rc == MYEA_OK && total_normalized_units) rc = myea_b200_upload(h, MYEA_BUF_NORM_MEAN_AVERAGE, ptr_array_normalized_batch_units_means_averages, 0, total_normalized_units * number_recurrent_depth);
+  if (rc == MYEA_OK && total_normalized_units) rc = myea_b200_upload(h, MYEA_BUF_NORM_VARIANCE_AVERAGE, ptr_array_normalized_batch_units_variances_averages, 0, total_normalized_units * number_recurrent_depth);
   return rc == MYEA_OK ? true : fail("Copy__Parameters__Host_To_Device", rc);
 }
 
@@ -145,8 +145,8 @@ bool Neural_Network::Copy__Optimizer_Paramaters__Device_To_Host(void) {
 bool Neural_Network::Copy__Batch_Normalization_Neurons__Device_To_Host(void) {
   if (!is_device_initialized || total_normalized_units == 0) return is_device_initialized;
   myea_handle h = ptr_device_Neural_Network;
-  int rc = myea_b200_download(h, MYEA_BUF_NORM_MEAN_AVERAGE, ptr_array_normalized_batch_units_means_averages, 0, total_normalized_units);
-  if (rc == MYEA_OK) rc = myea_b200_download(h, MYEA_BUF_NORM_VARIANCE_AVERAGE, ptr_array_normalized_batch_units_variances_averages, 0, total_normalized_units);
+  int rc = myea_b200_download(h, MYEA_BUF_NORM_MEAN_AVERAGE, ptr_array_normalized_batch_units_means_averages, 0, total_normalized_units * number_recurrent_depth);
+  if (rc == MYEA_OK) rc = myea_b200_download(h, MYEA_BUF_NORM_VARIANCE_AVERAGE, ptr_array_normalized_batch_units_variances_averages, 0, total_normalized_units * number_recurrent_depth);
   return rc == MYEA_OK ? true : fail("Copy__Batch_Normalization_Neurons__Device_To_Host", rc);
 }
 

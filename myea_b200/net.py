@@ -86,7 +86,7 @@ class Net:
         return li
 
     def _count(self, which):
-        return self.n_norm if which in (capi.BUF_NORM_MEAN_AVERAGE, capi.BUF_NORM_VARIANCE_AVERAGE) else self.P
+        return self.n_norm * self.T if which in (capi.BUF_NORM_MEAN_AVERAGE, capi.BUF_NORM_VARIANCE_AVERAGE) else self.P
 
     def get(self, which):
         out = np.empty(self._count(which), np.float32)

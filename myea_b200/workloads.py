@@ -93,8 +93,8 @@ class Workload:
         P, W, nb, nn = net.sizes()
         net.set(capi.BUF_PARAMETERS, self.parameters(net))
         if nn:
-            net.set(capi.BUF_NORM_MEAN_AVERAGE, np.zeros(nn * (self.T if hasattr(net, "threads") else 1), np.float32))
-            net.set(capi.BUF_NORM_VARIANCE_AVERAGE, np.ones(nn * (self.T if hasattr(net, "threads") else 1), np.float32))
+            net.set(capi.BUF_NORM_MEAN_AVERAGE, np.zeros(nn * self.T, np.float32))      # one set of averages per time step
+            net.set(capi.BUF_NORM_VARIANCE_AVERAGE, np.ones(nn * self.T, np.float32))
         if self.opt.regularization__weight_decay != 0.0:
             m = np.zeros(P, np.float32)
             m[:W] = 1.0   # weights 1, biases and gamma / beta 0 (Neural_Network__Indexing.cpp:50-76)

@@ -225,7 +225,10 @@ def build_index_map(desc):
                 in_block.update(range(l + 1, l + Ls[l].depth + 1))
         for l in range(n):
             off.append(units)
-            own.append(Ls[l + Ls[l].depth].n_out if Ls[l].type == capi.LAYER_RESIDUAL else (Ls[l].n_in if l in in_block else Ls[l].n_out))
+            if Ls[l].type == capi.LAYER_LSTM:   # three per cell and six per block, counted although the layer does not normalize
+                own.append(3 * Ls[l].n_out + 6 * int(Ls[l].d.unit_parameters[0]) * (2 if Ls[l].d.use_bidirectional else 1))
+            else:
+                own.append(Ls[l + Ls[l].depth].n_out if Ls[l].type == capi.LAYER_RESIDUAL else (Ls[l].n_in if l in in_block else Ls[l].n_out))
             units += own[l]
         for l in range(n):
             Ls[l].idx["scale_index"] = P + off[l]
@@ -244,8 +247,8 @@ class OracleNet:
         z = lambda k: np.zeros(k, dtype)
         self.buf = {capi.BUF_PARAMETERS: z(self.P), capi.BUF_DERIVATIVES: z(self.P), capi.BUF_FIRST_MOMENT: z(self.P),
                     capi.BUF_SECOND_MOMENT: z(self.P), capi.BUF_SECOND_MOMENT_HAT: z(self.P), capi.BUF_MASK_REGULARIZED: z(self.P),
-                    capi.BUF_PREVIOUS_DELTA: z(self.P), capi.BUF_NORM_MEAN_AVERAGE: z(self.n_norm),
-                    capi.BUF_NORM_VARIANCE_AVERAGE: np.ones(self.n_norm, dtype)}
+                    capi.BUF_PREVIOUS_DELTA: z(self.P), capi.BUF_NORM_MEAN_AVERAGE: z(self.n_norm * self.T),
+                    capi.BUF_NORM_VARIANCE_AVERAGE: np.ones(self.n_norm * self.T, dtype)}
         self.masks, self.zone, self.shake = {}, {}, {}
         # sharded batch: `allreduce(array) -> array summed over the ranks` and the number of ranks (tests/test_sharding_cpu.py)
         self.allreduce, self.world = None, 1
@@ -313,48 +316,67 @@ class OracleNet:
         i = L.idx
         return self._p()[i["first_connection_index"]:i["last_connection_index"]].reshape(L.n_out, L.n_in)
 
+    def _norm_steps(self, rows):
+        """row ranges of the time steps inside a [T * rows-per-step, H] array (one step for a feed-forward network)"""
+        T = self.T if rows % self.T == 0 and self.T > 1 else 1
+        n = rows // T
+        return [(t, slice(t * n, (t + 1) * n)) for t in range(T)]
+
     def _norm_forward(self, L, z):
         """Forward_Pass__Batch_Normalization__Training / __Batch_Renormalization__Training
         (Neural_Network__Forward_Pass__Loop.cpp:4673-4853); inference :4644-4671.  The 'variance' is the standard
-        deviation sqrt(E[x^2]-mean^2+eps); r and d use the already updated running averages."""
+        deviation sqrt(E[x^2]-mean^2+eps); r and d use the already updated running averages.  Every time step has
+        statistics and running averages of its own ([layer][T][units] arrays), gamma and beta are shared."""
         dt = self.dt
-        o, H = L.norm_off, L.idx["number_units_norm"]
+        H = L.idx["number_units_norm"]
         gamma = self._p()[L.idx["scale_index"]:L.idx["scale_index"] + H]
         beta = self._p()[L.idx["shift_index"]:L.idx["shift_index"] + H]
-        ma = self.buf[capi.BUF_NORM_MEAN_AVERAGE][o:o + H]
-        sa = self.buf[capi.BUF_NORM_VARIANCE_AVERAGE][o:o + H]
-        if self.training:
-            s1, s2 = z.sum(0, dtype=dt), (z * z).sum(0, dtype=dt)
-            if self.allreduce is not None:   # the statistics are those of the whole batch, whichever rank holds which rows
-                s1, s2 = self.allreduce(s1), self.allreduce(s2)
-            inv = dt(1) / dt(z.shape[0] * self.world)
-            mean = s1 * inv
-            sigma = np.sqrt(s2 * inv - mean * mean + self.eps)
-            ma += self.momentum * (mean - ma)
-            sa += self.momentum * (sigma - sa)
-            r, d = np.ones(H, dt), np.zeros(H, dt)
-            if int(L.d.type_normalization) == capi.NORM_BRN:
-                r = np.clip(sigma / sa, dt(1) / self.r_max, self.r_max)
-                d = np.clip((mean - ma) / sa, -self.d_max, self.d_max)
-            L.mean, L.sigma, L.r, L.dcorr = mean, sigma, r, d
-            L.xhat = (z - mean) / sigma * r + d
-        else:
-            L.xhat = (z - ma) / sa
+        L.xhat = np.zeros_like(z)
+        L.stats = {}
+        for t, rows in self._norm_steps(z.shape[0]):
+            o = L.norm_off * self.T + t * H
+            ma = self.buf[capi.BUF_NORM_MEAN_AVERAGE][o:o + H]
+            sa = self.buf[capi.BUF_NORM_VARIANCE_AVERAGE][o:o + H]
+            zt = z[rows]
+            if self.training:
+                s1, s2 = zt.sum(0, dtype=dt), (zt * zt).sum(0, dtype=dt)
+                if self.allreduce is not None:   # the statistics are those of the whole batch, whichever rank holds which rows
+                    s1, s2 = self.allreduce(s1), self.allreduce(s2)
+                inv = dt(1) / dt(zt.shape[0] * self.world)
+                mean = s1 * inv
+                sigma = np.sqrt(s2 * inv - mean * mean + self.eps)
+                ma += self.momentum * (mean - ma)
+                sa += self.momentum * (sigma - sa)
+                r, d = np.ones(H, dt), np.zeros(H, dt)
+                if int(L.d.type_normalization) == capi.NORM_BRN:
+                    r = np.clip(sigma / sa, dt(1) / self.r_max, self.r_max)
+                    d = np.clip((mean - ma) / sa, -self.d_max, self.d_max)
+                L.stats[t] = (mean, sigma, r, d)
+                L.xhat[rows] = (zt - mean) / sigma * r + d
+            else:
+                L.xhat[rows] = (zt - ma) / sa
         return gamma * L.xhat + beta
 
     def _norm_backward(self, L, z, delta):
-        """Backward_Pass__Batch_Normalization / __Batch_Renormalization (Neural_Network__Backward_Pass__Loop.cpp:1380-1628)"""
+        """Backward_Pass__Batch_Normalization / __Batch_Renormalization (Neural_Network__Backward_Pass__Loop.cpp:1380-1628),
+        time step by time step; the derivatives of gamma and beta add up over the steps"""
         dt = self.dt
-        H, B = L.idx["number_units_norm"], dt(z.shape[0] * self.world)
+        H = L.idx["number_units_norm"]
         gamma = self._p()[L.idx["scale_index"]:L.idx["scale_index"] + H]
         self._g()[L.idx["scale_index"]:L.idx["scale_index"] + H] += (delta * L.xhat).sum(0, dtype=dt)
         self._g()[L.idx["shift_index"]:L.idx["shift_index"] + H] += delta.sum(0, dtype=dt)
-        dh = delta * gamma
-        d_mean = (dh * (-L.r / L.sigma)).sum(0, dtype=dt)
-        d_sigma = (dh * (z - L.mean) * (-L.r / (L.sigma * L.sigma))).sum(0, dtype=dt)
-        if self.allreduce is not None:       # scale / shift derivatives stay local (summed with the other derivatives later)
-            d_mean, d_sigma = self.allreduce(d_mean), self.allreduce(d_sigma)
-        return dh * (L.r / L.sigma) + d_sigma * ((z - L.mean) / (B * L.sigma)) + d_mean * (dt(1) / B)
+        out = np.zeros_like(delta)
+        for t, rows in self._norm_steps(z.shape[0]):
+            mean, sigma, r, _ = L.stats[t]
+            zt = z[rows]
+            B = dt(zt.shape[0] * self.world)
+            dh = delta[rows] * gamma
+            d_mean = (dh * (-r / sigma)).sum(0, dtype=dt)
+            d_sigma = (dh * (zt - mean) * (-r / (sigma * sigma))).sum(0, dtype=dt)
+            if self.allreduce is not None:       # scale / shift derivatives stay local (summed with the other derivatives later)
+                d_mean, d_sigma = self.allreduce(d_mean), self.allreduce(d_sigma)
+            out[rows] = dh * (r / sigma) + d_sigma * ((zt - mean) / (B * sigma)) + d_mean * (dt(1) / B)
+        return out
 
     def _fc_forward(self, l, x):
         """Forward_Pass__FC (Neural_Network__Forward_Pass__Loop.cpp:350-790): weights, bias (only without

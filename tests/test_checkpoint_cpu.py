@@ -43,8 +43,8 @@ def _fixture(name):
 def _trained_state(name):
     g = np.load(os.path.join(GOLD, name + ".npz"))
     P, _, _, units = [int(v) for v in g["sizes"]]
-    mean = g["norm_mean_avg"][:units] if units else None
-    sigma = g["norm_sigma_avg"][:units] if units else None
+    mean = g["norm_mean_avg"] if units else None      # units x time steps values
+    sigma = g["norm_sigma_avg"] if units else None
     return g["param1"][:P], mean, sigma
 
 
@@ -188,11 +188,12 @@ def test_both_writers_agree_and_reference_loads_ours(name, tmp_path):
         params = net.get(capi.BUF_PARAMETERS).copy()
         units = net.sizes()[3]
         rng = np.random.default_rng(5)
+        averages = units * max(1, int(wl.desc.number_recurrent_depth))    # one set per time step
         if units:                                    # non-trivial running statistics in the reference object itself
-            net.set(capi.BUF_NORM_MEAN_AVERAGE, rng.standard_normal(units).astype(np.float32))
-            net.set(capi.BUF_NORM_VARIANCE_AVERAGE, (rng.random(units) + 0.5).astype(np.float32))
-        mean = net.get(capi.BUF_NORM_MEAN_AVERAGE)[:units].copy() if units else None
-        sigma = net.get(capi.BUF_NORM_VARIANCE_AVERAGE)[:units].copy() if units else None
+            net.set(capi.BUF_NORM_MEAN_AVERAGE, rng.standard_normal(averages).astype(np.float32))
+            net.set(capi.BUF_NORM_VARIANCE_AVERAGE, (rng.random(averages) + 0.5).astype(np.float32))
+        mean = net.get(capi.BUF_NORM_MEAN_AVERAGE)[:averages].copy() if units else None
+        sigma = net.get(capi.BUF_NORM_VARIANCE_AVERAGE)[:averages].copy() if units else None
         r_nn, r_net, m_nn, m_net = [tmp_path / f for f in ("r.nn", "r.net", "m.nn", "m.net")]
         net.save(r_nn, r_net)
         checkpoint.format_files(wl.desc, wl.opt, params, mean, sigma, m_nn, m_net)

@@ -83,7 +83,8 @@ def test_activations_without_a_derivative_run_forward(af):
 
 @pytest.mark.parametrize("name", sorted(cases.CASES_WITHOUT_REFERENCE))
 def test_step_matches_restatement_where_the_reference_cannot_serve(name):
-    """bidirectional LSTM: checked against the numpy restatement (parity against the reference binary is unpinned here)"""
+    """bidirectional LSTM, and normalized layers beside LSTM layers (the reference crashes while it builds such a network):
+    checked against the numpy restatement (parity against the reference binary is unpinned here)"""
     wl = cases.CASES_WITHOUT_REFERENCE[name]()
     gpu, cpu = Net(wl.desc, wl.opt), myea_oracle.OracleNet(wl.desc, wl.opt)
     out, want = cases.run_steps(gpu, wl), cases.run_steps(cpu, wl)
