@@ -100,10 +100,13 @@ CASES.update({
 
 
 # Larger shapes that reach the kernels only big layers use (256 x 256 tensor-core tiles, column-read operand panels,
-# 8-cells-per-thread LSTM steps).  Compared with the compiled reference on the GPU box, without a committed fixture
-# (the parameter vectors would be megabytes).  Momentum descent: an update that is linear in the derivatives (Adam-type
-# updates turn the rounding noise of near-zero derivatives into +-lr steps, and half a million parameters hold enough
-# of those to cross 1e-4 on the updated parameters although the derivatives agree to 1e-6).
+# 8-cells-per-thread and persistent LSTM steps).  Compared with the compiled reference on the GPU box, without a
+# committed fixture (the parameter vectors would be megabytes).  Momentum descent, an update that is linear in the
+# derivatives, so that the 1e-4 bound holds for every updated parameter.  Under Adam-type updates it does not, and the
+# numbers are (one step at the stated widths, tests/test_full_width_parity_gpu.py): derivatives agree to 1.3e-6 (C1),
+# 1.1e-5 (C2), 4.0e-6 (C3), 5.5e-6 (C4) of each tensor's largest, yet 1.5e-5 to 1.9e-4 of the UPDATED weights differ by
+# more than 1e-4 - all of them elements whose float64 derivative is below 1e-4 of the tensor's largest, where the first
+# Adam step lr * sign(g) is decided by rounding noise; that test arbitrates them with the reference's float64 build.
 CASES_ORACLE_ONLY = {
     "lstm_wide_nesterov": lambda: _lstm_case("lstm_wide", capi.opt(capi.OPT_GD, gd_lr=0.001, momentum=0.9, nesterov=True), T=4, B=16, n_in=136,
                                              H=192, layers=1, out=192),
