@@ -133,12 +133,14 @@ def run_reference(args):
 class Job:
     """one network on this rank's GPU for its shard of a global batch, joined to the other ranks when there are any"""
 
-    def __init__(self, torch, dist, workload, per_gpu_batch, world, rank, local, scale=None, **kw):
+    def __init__(self, torch, dist, workload, per_gpu_batch, world, rank, local, scale=None, opt=None, **kw):
         from myea_b200 import workloads
         from myea_b200.net import Net
         self.torch, self.dist, self.world, self.rank = torch, dist, world, rank
         build = workloads.BUILDERS[workload]
         self.wl = build(batch=per_gpu_batch, **kw) if scale is None else build(scale=scale, batch=per_gpu_batch, **kw)
+        if opt is not None:
+            self.wl.opt = opt
         self.global_batch = per_gpu_batch * world
         self.net = Net(self.wl.desc, self.wl.opt, device=local)
         self.wl.materialize(self.net)
@@ -235,7 +237,10 @@ def dp_check(torch, dist, world, rank, local, timed_job):
     """correctness of the data-parallel path, on every run with more than one rank:
     (1) the parameter buffers of the timed job are identical on all ranks after the timed steps (bitwise: every rank
         applied the same update to the same sums), (2) two steps of a small network sharded over the ranks equal the same
-        two steps on ONE rank with the whole batch, within the parity tolerance"""
+        two steps on ONE rank with the whole batch, within the parity tolerance.  The small network is updated by momentum
+        descent, which is linear in the derivatives: under Adam the first steps are lr * sign(g), and a derivative that is
+        zero up to the rounding of its sum takes either sign depending on the order of the sum (seen at 8 ranks: one
+        element of 0.4 million off by 2 * lr, everything else equal to 1e-6)"""
     from myea_b200 import capi
     p = torch.from_numpy(timed_job.net.get(capi.BUF_PARAMETERS)).cuda()
     hi, lo = p.clone(), p.clone()
@@ -243,7 +248,8 @@ def dp_check(torch, dist, world, rank, local, timed_job):
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     spread = float((hi - lo).abs().max().item())
     del p, hi, lo
-    small = Job(torch, dist, "c2", 64, world, rank, local, scale=1.0 / 16, hidden_layers=3)
+    linear = capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9)
+    small = Job(torch, dist, "c2", 64, world, rank, local, scale=1.0 / 16, opt=linear, hidden_layers=3)
     for _ in range(2):
         if small.step_host() != 0:
             raise RuntimeError("dp_check step failed")
@@ -256,6 +262,7 @@ def dp_check(torch, dist, world, rank, local, timed_job):
         from myea_b200 import workloads
         from myea_b200.net import Net
         wl = workloads.c2_wide_mlp(scale=1.0 / 16, batch=64 * world, hidden_layers=3)
+        wl.opt = linear
         one = Net(wl.desc, wl.opt, device=local)
         wl.materialize(one)
         for _ in range(2):
@@ -263,7 +270,7 @@ def dp_check(torch, dist, world, rank, local, timed_job):
         want = one.get(capi.BUF_PARAMETERS)
         one.close()
         out["sharded_vs_one_rank_rel_err"] = float(np.abs(got - want).max() / np.abs(want).max())
-        out["network"] = "C2 at 1/16 width, 3 hidden layers, global batch %d, 2 steps" % (64 * world)
+        out["network"] = "C2 at 1/16 width, 3 hidden layers, momentum descent, global batch %d, 2 steps" % (64 * world)
     small.close()
     return out
 
