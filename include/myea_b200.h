@@ -33,8 +33,10 @@ extern "C" {
 #define MYEA_E_COMM (-5)        /* NCCL failure                                   */
 
 /* ENUM_TYPE_LAYER (Enum_Type_Layer.hpp:25) */
+#define MYEA_LAYER_AVERAGE_POOLING 1u /* unit_parameters: kernel size, stride, padding, dilation, ceil mode (Compile.cpp:51-58) */
 #define MYEA_LAYER_FULLY_CONNECTED 4u
 #define MYEA_LAYER_LSTM 8u
+#define MYEA_LAYER_MAX_POOLING 9u     /* the same five values */
 #define MYEA_LAYER_RESIDUAL 10u
 /* ENUM_TYPE_NETWORKS (Enum_Type_Networks.hpp:25) */
 #define MYEA_NETWORK_FEEDFORWARD 3u

@@ -13,6 +13,7 @@ MAX_LAYERS = 64
 
 # enumerators (values of the reference's enums, see include/myea_b200.h)
 LAYER_FC, LAYER_LSTM, LAYER_RESIDUAL = 4, 8, 10
+LAYER_AVERAGE_POOLING, LAYER_MAX_POOLING = 1, 9
 NET_FEEDFORWARD, NET_RECURRENT = 3, 4
 AF_ELU, AF_LINEAR, AF_LEAKY_RELU, AF_RELU, AF_SELU, AF_SIGMOID, AF_SOFTMAX, AF_TANH = 3, 11, 14, 16, 17, 18, 22, 23
 (AF_COSINE, AF_COSINE_SYMMETRIC, AF_ELLIOT, AF_ELLIOT_SYMMETRIC, AF_GAUSSIAN, AF_GAUSSIAN_STEPWISE, AF_GAUSSIAN_SYMMETRIC, AF_ISRU, AF_ISRLU,
@@ -79,6 +80,15 @@ def fc(units, af=AF_LINEAR, norm=NORM_NONE, dropout=DROP_NONE, p=(0.0, 0.0, 0.0)
     d.type_dropout = dropout
     for i in range(3):
         d.dropout_values[i] = p[i]
+    return d
+
+
+def pooling(kind, kernel, stride, padding=0, dilation=1, ceil_mode=False):
+    """average (LAYER_AVERAGE_POOLING) or max (LAYER_MAX_POOLING) pooling over the units of the layer before"""
+    d = LayerDesc()
+    d.type_layer = kind
+    for i, v in enumerate((kernel, stride, padding, dilation, 1 if ceil_mode else 0)):
+        d.unit_parameters[i] = v
     return d
 
 

@@ -69,7 +69,7 @@ struct HostPlan {
   std::unique_ptr<myea_b200_net> net;
   std::vector<uint64_t> unit_base;  // first global unit number of each layer, in the numbering of its own unit kind
   std::vector<int> block_of;        // residual layer a layer sits in, or 0
-  uint64_t neurons = 0, cells = 0, blocks = 0, basics = 0, af_units = 0;
+  uint64_t neurons = 0, cells = 0, blocks = 0, basics = 0, basic_indices = 0, af_units = 0;
   std::vector<uint64_t> af_count;   // activation units each layer lists
   std::vector<int> reads;           // the layer whose units a layer's connections name
   std::string error;
@@ -113,8 +113,13 @@ int make_plan(const myea_net_desc *desc, HostPlan &P) {
         P.blocks += L.desc.unit_parameters[0];
         break;
       case MYEA_LAYER_RESIDUAL:
+      case MYEA_LAYER_AVERAGE_POOLING:   // Basic_unit, like the outputs of a residual block
         P.unit_base[l] = P.basics;
         P.basics += L.n_out;
+        break;
+      case MYEA_LAYER_MAX_POOLING:       // Basic_indice_unit
+        P.unit_base[l] = P.basic_indices;
+        P.basic_indices += L.n_out;
         break;
       default: P.error = "layer type not built"; return MYEA_E_UNSUPPORTED;
     }
@@ -126,7 +131,8 @@ int make_plan(const myea_net_desc *desc, HostPlan &P) {
 const char *connection_name(uint32_t type_layer) {
   switch (type_layer) {
     case MYEA_LAYER_LSTM: return "connected_to_cell";
-    case MYEA_LAYER_RESIDUAL: return "connected_to_basic";
+    case MYEA_LAYER_RESIDUAL: case MYEA_LAYER_AVERAGE_POOLING: return "connected_to_basic";
+    case MYEA_LAYER_MAX_POOLING: return "connected_to_basic_indice";
     default: return "connected_to_neuron";
   }
 }
@@ -268,7 +274,7 @@ int format_dimension(const HostPlan &P, const float *params, const float *mean, 
   w.line(0, "use_first_layer_as_input", "1");
   w.line(0, "use_last_layer_as_output", "1");
   w.line(0, "total_basic_units", num(P.basics));
-  w.line(0, "total_basic_indice_units", "0");
+  w.line(0, "total_basic_indice_units", num(P.basic_indices));
   w.line(0, "total_neuron_units", num(P.neurons));
   w.line(0, "total_AF_units", num(P.af_units));
   w.line(0, "total_AF_Ind_recurrent_units", "0");
@@ -307,6 +313,14 @@ int format_dimension(const HostPlan &P, const float *params, const float *mean, 
         w.sparsity_and_constraints();
         w.lstm_blocks(l);
         w.bias(L);
+        break;
+      case MYEA_LAYER_AVERAGE_POOLING:
+      case MYEA_LAYER_MAX_POOLING:   // (Save.cpp:305-311, 487-493; the ceil mode is not in the file)
+        w.line(4, "kernel_size", num(L.desc.unit_parameters[0]));
+        w.line(4, "stride", num(L.desc.unit_parameters[1]));
+        w.line(4, "padding", num(L.desc.unit_parameters[2]));
+        w.line(4, "dilation", num(L.desc.unit_parameters[3]));
+        w.line(4, L.type == MYEA_LAYER_MAX_POOLING ? "number_basic_indice_units" : "number_basic_units", num(L.n_out));
         break;
       case MYEA_LAYER_RESIDUAL: {
         const long long a = Ls[L.input_layer].n_out, b = Ls[l + L.block_depth].n_out;
@@ -678,7 +692,7 @@ int parse_dimension(const char *path, Parsed &out, std::string &error) {
        in.take_u64("total_bias", &out.total_bias);
   if (!ok) { error = in.error; return MYEA_E_INVALID; }
   if (layers < 2 || layers > MYEA_MAX_LAYERS || d.number_recurrent_depth == 0) { error = "layer count or recurrent depth out of range"; return MYEA_E_INVALID; }
-  if (totals[1] != 0 || totals[4] != 0) { error = "pooling and independently recurrent layers are not built"; return MYEA_E_UNSUPPORTED; }
+  if (totals[4] != 0) { error = "independently recurrent layers are not built"; return MYEA_E_UNSUPPORTED; }
   out.total_norm_units = totals[7];
   d.number_layers = static_cast<uint32_t>(layers);
   out.norm.assign(layers, NormValues());
@@ -690,6 +704,8 @@ int parse_dimension(const char *path, Parsed &out, std::string &error) {
   I.type_layer = static_cast<uint32_t>(u);
   ok = ok && in.take_u64("type_activation", &u) && parse_dropout(in, I, false) && in.take_u64("number_inputs", &I.unit_parameters[0]);
   I.use_layer_normalization_before_activation = 1;
+  std::vector<uint64_t> width(layers, 0);  // units of each layer as the file states them
+  width[0] = I.unit_parameters[0];
   for (uint64_t l = 1; ok && l + 1 < layers; ++l) {
     myea_layer_desc &L = d.layers[l];
     ok = in.take("Hidden", nullptr) && in.take_u64("type_layer", &u);
@@ -710,9 +726,23 @@ int parse_dimension(const char *path, Parsed &out, std::string &error) {
       case MYEA_LAYER_RESIDUAL:
         ok = in.take_u64("block_depth", &L.unit_parameters[0]) && in.take_u64("padding", &u) && parse_dropout(in, L, true) &&
              parse_normalization(in, L, out.norm[l], T, false) && in.take_u64("number_basic_units", &u);
+        width[l] = u;
         break;
+      case MYEA_LAYER_AVERAGE_POOLING:
+      case MYEA_LAYER_MAX_POOLING: {
+        ok = in.take_u64("kernel_size", &L.unit_parameters[0]) && in.take_u64("stride", &L.unit_parameters[1]) &&
+             in.take_u64("padding", &L.unit_parameters[2]) && in.take_u64("dilation", &L.unit_parameters[3]) &&
+             in.take_u64(L.type_layer == MYEA_LAYER_MAX_POOLING ? "number_basic_indice_units" : "number_basic_units", &u);
+        width[l] = u;
+        // the file does not carry the ceil mode: it is the mode under which the stated number of units comes out
+        L.unit_parameters[4] = 0;
+        if (ok && pooling_output_width(L, static_cast<long long>(width[l - 1])) != static_cast<long long>(u)) L.unit_parameters[4] = 1;
+        break;
+      }
       default: error = "layer type " + std::to_string(L.type_layer) + " is not built"; return MYEA_E_UNSUPPORTED;
     }
+    if (L.type_layer == MYEA_LAYER_FULLY_CONNECTED) width[l] = L.unit_parameters[0];
+    if (L.type_layer == MYEA_LAYER_LSTM) width[l] = L.unit_parameters[0] * std::max<uint64_t>(1, L.unit_parameters[1]);
   }
   myea_layer_desc &O = d.layers[layers - 1];
   ok = ok && in.take("Output", nullptr) && in.take_u64("type_layer", &u);

@@ -113,7 +113,15 @@ int myea::build_index_map(myea_b200_net *net) {
         break;
       }
       case MYEA_LAYER_RESIDUAL: L.block_depth = static_cast<int>(d.layers[l].unit_parameters[0]); break;
-      default: return fail(net, MYEA_E_UNSUPPORTED, "layer type not built (only fully connected, LSTM, residual)");
+      case MYEA_LAYER_AVERAGE_POOLING:
+      case MYEA_LAYER_MAX_POOLING:
+        // a window over the units of the layer before, which has to have a width of its own already
+        if (l == 0 || net->layers[l - 1].type == MYEA_LAYER_RESIDUAL) return fail(net, MYEA_E_UNSUPPORTED, "a pooling layer next to a residual block is not built");
+        if (d.layers[l].type_dropout != MYEA_DROPOUT_NONE || d.layers[l].type_normalization != MYEA_NORM_NONE)
+          return fail(net, MYEA_E_INVALID, "pooling layers take neither dropout nor normalization");
+        L.n_out = pooling_output_width(d.layers[l], net->layers[l - 1].n_out);
+        break;
+      default: return fail(net, MYEA_E_UNSUPPORTED, "layer type not built (fully connected, LSTM, residual, average / max pooling)");
     }
     if (L.type != MYEA_LAYER_RESIDUAL && L.n_out <= 0) return fail(net, MYEA_E_INVALID, "layer with zero units");
   }
@@ -134,6 +142,11 @@ int myea::build_index_map(myea_b200_net *net) {
       L.n_out = std::max(net->layers[feeder].n_out, net->layers[l + L.block_depth].n_out);
     }
   }
+  for (uint32_t l = 1; l < n; ++l) {
+    const uint32_t t = net->layers[l].type;
+    if ((t == MYEA_LAYER_AVERAGE_POOLING || t == MYEA_LAYER_MAX_POOLING) && layer_in_block(net, static_cast<int>(l) - 1, nullptr))
+      return fail(net, MYEA_E_UNSUPPORTED, "a pooling layer next to a residual block is not built");
+  }
   // inputs: a layer reads the layer before it; the first layer of a residual block reads the layer before the
   // residual layer, and the layer after a block reads the block's output (held by the residual layer)
   for (uint32_t l = 1; l < n; ++l) {
@@ -152,7 +165,8 @@ int myea::build_index_map(myea_b200_net *net) {
   uint64_t tw = 0;
   for (uint32_t l = 1; l < n; ++l) {
     LayerPlan &L = net->layers[l];
-    L.idx.number_inputs = L.type == MYEA_LAYER_RESIDUAL ? 0 : L.n_in;  // a residual layer has no connections of its own
+    const bool has_connections = L.type == MYEA_LAYER_FULLY_CONNECTED || L.type == MYEA_LAYER_LSTM;
+    L.idx.number_inputs = has_connections ? L.n_in : 0;  // residual and pooling layers have no connections of their own
     L.idx.number_outputs = L.n_out;
     if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
       L.idx.first_connection_index = tw;
@@ -212,6 +226,7 @@ int myea::build_index_map(myea_b200_net *net) {
         own = 3 * L.n_out + 6 * static_cast<long long>(d.layers[l].unit_parameters[0]) * dirs;
       }
       if (L.type == MYEA_LAYER_RESIDUAL) own = net->layers[l + L.block_depth].n_out;
+      if (L.type == MYEA_LAYER_AVERAGE_POOLING || L.type == MYEA_LAYER_MAX_POOLING) own = 0;  // Prepare__Normalized__Layer: none
       else if (l > 0 && layer_in_block(net, static_cast<int>(l), nullptr)) own = L.n_in;
       L.idx.number_units_norm = static_cast<uint64_t>(own);
       units += static_cast<uint64_t>(own);
@@ -286,6 +301,11 @@ static int allocate_buffers(myea_b200_net *net) {
       }
     } else if (L.type == MYEA_LAYER_LSTM) {
       RC(lstm_create(net, L));
+    } else if (L.type == MYEA_LAYER_AVERAGE_POOLING || L.type == MYEA_LAYER_MAX_POOLING) {
+      RC(dev_alloc(net, &L.values, rows * L.n_out));
+      RC(dev_alloc(net, &L.deriv, rows * L.n_out));
+      L.errors = L.deriv;  // no activation of its own: the error on its outputs is the error its backward pass spreads
+      if (L.type == MYEA_LAYER_MAX_POOLING) RC(dev_alloc(net, &L.pool_winner, rows * L.n_out));
     } else if (L.type == MYEA_LAYER_RESIDUAL) {
       RC(dev_alloc(net, &L.values, rows * L.n_out));
       RC(dev_alloc(net, &L.deriv, rows * L.n_out));
@@ -720,6 +740,9 @@ static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cu
     } else if (L.type == MYEA_LAYER_LSTM) {
       RC(lstm_forward(net, L, in.values, L.n_in));
       ++l;
+    } else if (L.type == MYEA_LAYER_AVERAGE_POOLING || L.type == MYEA_LAYER_MAX_POOLING) {
+      RC(pooling_forward(net, L, in.values, rows));
+      ++l;
     } else {  // residual block: consumes layers l+1 .. l+depth
       RC(residual_forward(net, l));
       l += L.block_depth + 1;
@@ -900,12 +923,18 @@ extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
     const int p = N.input_layer;
     if (p < 1) break;
     LayerPlan &P = net->layers[p];
+    const bool n_pool = N.type == MYEA_LAYER_AVERAGE_POOLING || N.type == MYEA_LAYER_MAX_POOLING;
+    // the error of N carried to the outputs of P, without P's activation derivative
+    auto send_plain = [&](float *dst) -> int {
+      if (N.type == MYEA_LAYER_FULLY_CONNECTED) return fc_backward_from_fc(net, P, N, N.errors, rows, dst, false);
+      if (n_pool) return pooling_backward(net, N, dst, rows);
+      return lstm_backward_to_input(net, N, dst, P, nullptr);
+    };
     if (P.type == MYEA_LAYER_FULLY_CONNECTED) {
       if (P.has_norm && net->T > 1) {
         // per-time-step normalization: the error over all rows first, then step by step the activation derivative on
         // that step's normalized summations and the normalization backward with that step's statistics
-        if (N.type == MYEA_LAYER_FULLY_CONNECTED) RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, false));
-        else RC(lstm_backward_to_input(net, N, P.deriv, P, nullptr));
+        RC(send_plain(P.deriv));
         const long long pitch = rows / net->T;
         for (long long t = 0; t < net->T; ++t) {
           const NormParams np = norm_at_step(P, t);
@@ -922,6 +951,11 @@ extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
       }
       if (N.type == MYEA_LAYER_FULLY_CONNECTED) {
         RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, true));
+      } else if (n_pool) {  // a pooling layer above: its backward pass has no epilogue to carry P's activation derivative
+        P.bwd_fused_chunks = 0;
+        RC(pooling_backward(net, N, P.deriv, rows));
+        RC(activation_backward(net->ctx, P.deriv, P.summations, P.values, rows, P.n_out, P.desc.type_activation_function,
+                               P.has_norm ? P.norm.col_scale : nullptr, P.has_norm ? P.norm.col_shift : nullptr));
       } else {  // an LSTM layer above: its input contraction carries P's activation derivative in the epilogue
         Epilogue fin;
         const uint32_t af = P.desc.type_activation_function;
@@ -934,12 +968,12 @@ extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
       }
       RC(fc_finish_backward(net, P, rows));
     } else if (P.type == MYEA_LAYER_LSTM) {
-      float *dh = lstm_output_errors(P);
-      if (N.type == MYEA_LAYER_FULLY_CONNECTED) RC(fc_backward_from_fc(net, P, N, N.errors, rows, dh, false));
-      else RC(lstm_backward_to_input(net, N, dh, P));
+      RC(send_plain(lstm_output_errors(P)));
       RC(lstm_backward(net, P));
+    } else if (P.type == MYEA_LAYER_AVERAGE_POOLING || P.type == MYEA_LAYER_MAX_POOLING) {
+      RC(send_plain(P.deriv));  // P.errors == P.deriv: nothing of its own to finish
     } else {  // residual block feeding N: its output has no activation of its own
-      if (N.type != MYEA_LAYER_FULLY_CONNECTED) return fail(net, MYEA_E_UNSUPPORTED, "a residual block below an LSTM layer is not built");
+      if (N.type != MYEA_LAYER_FULLY_CONNECTED) return fail(net, MYEA_E_UNSUPPORTED, "a residual block below an LSTM or pooling layer is not built");
       RC(fc_backward_from_fc(net, P, N, N.errors, rows, P.deriv, false));
     }
     l = p;

@@ -49,7 +49,13 @@ struct LayerPlan {
   const float *in_ready_src = nullptr;  // set by the producer of this layer's input when IT has written the input panels
   long long in_ready_rows = 0;
   int bwd_fused_chunks = 0;       // row blocks whose normalization-backward sums the error-propagation epilogue has emitted
+  int *pool_winner = nullptr;     // max pooling: [T*B, n_out] position (in the padded input) that gave each output
 };
+
+// pooling layers (pooling.cu)
+long long pooling_output_width(const myea_layer_desc &d, long long n_in);
+int pooling_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long rows);
+int pooling_backward(myea_b200_net *net, LayerPlan &L, float *d_input, long long rows);
 
 // z = input * W^T of a fully connected layer and D = errors * W (error on the layer's inputs), from the layer's shared
 // operand panels when it has them, else through gemm_nt; `e` carries destination and fused extras (net.cu)

@@ -15,6 +15,8 @@ Each routine cites the reference file:line it follows (paths relative to
 Neural_Network_Library_Windows/Source_Files/Neural_Network/).  Arithmetic is float32 unless `dtype=np.float64` is
 passed to OracleNet (tie-breaker / finite differences).  Same method set as oracle.ref.RefNet and myea_b200.net.Net.
 """
+import math
+
 import numpy as np
 
 from myea_b200 import capi
@@ -159,6 +161,13 @@ def build_index_map(desc):
             L.n_out = int(d.unit_parameters[0])
         elif L.type == capi.LAYER_LSTM:
             L.n_out = int(d.unit_parameters[0]) * max(1, int(d.unit_parameters[1])) * (2 if d.use_bidirectional else 1)
+        elif L.type in (capi.LAYER_AVERAGE_POOLING, capi.LAYER_MAX_POOLING):
+            # Assign__Post__Layer (Neural_Network__Compile.cpp:250-271): the average ignores the dilation, the maximum counts it
+            k, s_, p_, dil, ceil_mode = (int(d.unit_parameters[i]) for i in range(5))
+            n_prev = Ls[l - 1].n_out
+            span = n_prev + 2 * p_ - k if L.type == capi.LAYER_AVERAGE_POOLING else n_prev + 2 * p_ - dil * (k - 1) - 1
+            q = span / s_ + 1.0
+            L.n_out = int(math.ceil(q) if ceil_mode else math.floor(q))
         L.depth = int(d.unit_parameters[0]) if L.type == capi.LAYER_RESIDUAL else 0
         L.idx = dict(first_connection_index=0, last_connection_index=0, first_bias_connection_index=0,
                      last_bias_connection_index=0, scale_index=0, shift_index=0, number_inputs=0, number_outputs=0,
@@ -185,7 +194,7 @@ def build_index_map(desc):
     tw = 0
     for l in range(1, n):
         L = Ls[l]
-        L.idx["number_inputs"], L.idx["number_outputs"] = (0 if L.type == capi.LAYER_RESIDUAL else L.n_in), L.n_out
+        L.idx["number_inputs"], L.idx["number_outputs"] = (L.n_in if L.type in (capi.LAYER_FC, capi.LAYER_LSTM) else 0), L.n_out
         if L.type == capi.LAYER_FC:
             L.idx["first_connection_index"] = tw
             tw += L.n_out * L.n_in
@@ -225,7 +234,9 @@ def build_index_map(desc):
                 in_block.update(range(l + 1, l + Ls[l].depth + 1))
         for l in range(n):
             off.append(units)
-            if Ls[l].type == capi.LAYER_LSTM:   # three per cell and six per block, counted although the layer does not normalize
+            if Ls[l].type in (capi.LAYER_AVERAGE_POOLING, capi.LAYER_MAX_POOLING):
+                own.append(0)
+            elif Ls[l].type == capi.LAYER_LSTM:   # three per cell and six per block, counted although the layer does not normalize
                 own.append(3 * Ls[l].n_out + 6 * int(Ls[l].d.unit_parameters[0]) * (2 if Ls[l].d.use_bidirectional else 1))
             else:
                 own.append(Ls[l + Ls[l].depth].n_out if Ls[l].type == capi.LAYER_RESIDUAL else (Ls[l].n_in if l in in_block else Ls[l].n_out))
@@ -378,6 +389,59 @@ class OracleNet:
             out[rows] = dh * (r / sigma) + d_sigma * ((zt - mean) / (B * sigma)) + d_mean * (dt(1) / B)
         return out
 
+    def _pooling_windows(self, L):
+        """padded positions j * stride + k * dilation read by output j, and which of them fall inside the input"""
+        k, s_, p_, dil = (int(L.d.unit_parameters[i]) for i in range(4))
+        pos = np.arange(L.n_out)[:, None] * s_ + np.arange(k)[None, :] * dil      # [n_out, kernel]
+        inside = (pos >= p_) & (pos < L.n_in + p_)
+        return pos, inside, p_, k
+
+    def _pooling_forward(self, L, x):
+        """Forward_Pass__Average_Pooling__Loop / __Max_Pooling__Loop (Neural_Network__Forward_Pass__Loop.cpp:4537-4582,
+        :5069-5136): the average divides by the kernel size whatever falls outside the input; the maximum takes 0 for a
+        position outside and keeps the first of equal values"""
+        dt = self.dt
+        pos, inside, pad, k = self._pooling_windows(L)
+        idx = np.clip(pos - pad, 0, L.n_in - 1)
+        win = x[:, idx]                                                            # [rows, n_out, kernel]
+        if L.type == capi.LAYER_AVERAGE_POOLING:
+            out = np.zeros((x.shape[0], L.n_out), dt)
+            for kk in range(k):                                                    # summed in kernel order
+                out += np.where(inside[None, :, kk], win[:, :, kk], dt(0))
+            L.values = out * (dt(1) / dt(k))
+        else:
+            top = np.full((x.shape[0], L.n_out), -np.finfo(np.float32).max, dt)
+            best = np.zeros((x.shape[0], L.n_out), np.int64)
+            for kk in range(k):
+                v = np.where(inside[None, :, kk], win[:, :, kk], dt(0))
+                take = np.where(inside[None, :, kk], top < v, top < 0)
+                best = np.where(take, pos[None, :, kk], best)
+                top = np.where(take, v, top)
+            L.values, L.winner = top, best
+        L.pool_in = x.shape[1]
+        return L.values
+
+    def _pooling_backward(self, L):
+        """Backward_Pass__Average_Pooling__Loop / __Max_Pooling__Loop (Neural_Network__Backward_Pass__Loop.cpp:1004-1040,
+        :1139-1175): error on the layer's inputs"""
+        dt = self.dt
+        pos, inside, pad, k = self._pooling_windows(L)
+        d = L.errors
+        D = np.zeros((d.shape[0], L.n_in), dt)
+        if L.type == capi.LAYER_AVERAGE_POOLING:
+            share = d * (dt(1) / dt(k))
+            for j in range(L.n_out):
+                for kk in range(k):
+                    if inside[j, kk]:
+                        D[:, pos[j, kk] - pad] += share[:, j]
+        else:
+            rows = np.arange(d.shape[0])
+            for j in range(L.n_out):
+                w = L.winner[:, j]
+                ok = (w >= pad) & (w < L.n_in + pad)
+                np.add.at(D, (rows[ok], w[ok] - pad), d[ok, j])
+        return D
+
     def _fc_forward(self, l, x):
         """Forward_Pass__FC (Neural_Network__Forward_Pass__Loop.cpp:350-790): weights, bias (only without
         normalization), normalization, activation, dropout applied in place on the output (:4917-4990)."""
@@ -425,6 +489,9 @@ class OracleNet:
             elif L.type == capi.LAYER_LSTM:
                 from oracle import myea_oracle_lstm
                 myea_oracle_lstm.forward(self, l, x)
+                l += 1
+            elif L.type in (capi.LAYER_AVERAGE_POOLING, capi.LAYER_MAX_POOLING):
+                self._pooling_forward(L, x)
                 l += 1
             else:
                 from oracle import myea_oracle_residual
@@ -482,6 +549,8 @@ class OracleNet:
             Pl = self.layers[p]
             if N.type == capi.LAYER_FC:
                 D = N.errors @ self._fc_weights(N)
+            elif N.type in (capi.LAYER_AVERAGE_POOLING, capi.LAYER_MAX_POOLING):
+                D = self._pooling_backward(N)
             else:
                 from oracle import myea_oracle_lstm
                 D = myea_oracle_lstm.error_to_input(self, l)
