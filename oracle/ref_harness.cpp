@@ -149,6 +149,15 @@ void *ref_create(const myea_net_desc *d, const myea_opt_desc *opt, int threads) 
     }
   }
   if (!ok) { delete r; return nullptr; }
+  // The reference seeds its ShakeDrop generators from the clock (Neural_Network__Allocate.cpp:296, :314).  Seed them
+  // through their public Seed() instead, so that a test sees the same draws on every run (an activation kink that a
+  // particular draw happens to put within rounding distance of zero would otherwise fail one run in ten).
+  if (nn.ptr_array_Class_Generator_Bernoulli_ShakeDrop != nullptr && nn.ptr_array_Class_Generator_Real_ShakeDrop != nullptr) {
+    for (size_t g = 0; g < nn.number_threads; ++g) {
+      nn.ptr_array_Class_Generator_Bernoulli_ShakeDrop[g].Seed(5413u + static_cast<unsigned int>(g));
+      nn.ptr_array_Class_Generator_Real_ShakeDrop[g].Seed(7919u + static_cast<unsigned int>(g));
+    }
+  }
   r->n_inputs = nn.number_inputs;
   r->n_outputs = nn.number_outputs;
   nn.type_state_propagation = ENUM_TYPE_STATE_PROPAGATION::TYPE_STATE_PROPAGATION_TRAINING;
