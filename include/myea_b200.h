@@ -35,6 +35,8 @@ extern "C" {
 /* ENUM_TYPE_LAYER (Enum_Type_Layer.hpp:25) */
 #define MYEA_LAYER_AVERAGE_POOLING 1u /* unit_parameters: kernel size, stride, padding, dilation, ceil mode (Compile.cpp:51-58) */
 #define MYEA_LAYER_FULLY_CONNECTED 4u
+#define MYEA_LAYER_FC_INDEPENDENTLY_RECURRENT 5u /* a fully connected layer whose units also see their own previous output through
+                                                   one recurrent weight each (Ind-RNN; Prepare__Connections__FC_Ind_RNN) */
 #define MYEA_LAYER_LSTM 8u
 #define MYEA_LAYER_MAX_POOLING 9u     /* the same five values */
 #define MYEA_LAYER_RESIDUAL 10u
@@ -120,7 +122,10 @@ typedef struct myea_net_desc {
   float normalization_epsilon;   /* Data.hpp:2967                                                */
   float batch_renormalization_r_correction_maximum; /* Data.hpp:2746                             */
   float batch_renormalization_d_correction_maximum; /* Data.hpp:2747                             */
-  uint32_t reserved;
+  float clip_gradient; /* the class's clip_gradient member (Set__Clip_Gradient(T_), Data.hpp:2718) as far as it shapes the network:
+                          independently recurrent layers keep their recurrent weights inside +-(MAG / c)^(1/T) after every update,
+                          MAG = clip(clip_gradient, 2, 10), c = 0.9^(T/10) for symmetric activations and 1 otherwise
+                          (Compute__Regularization__Constraint_Recurrent_Weight__Default); 0 = the class default 1 */
   myea_layer_desc layers[MYEA_MAX_LAYERS];
 } myea_net_desc;
 

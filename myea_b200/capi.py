@@ -14,6 +14,7 @@ MAX_LAYERS = 64
 # enumerators (values of the reference's enums, see include/myea_b200.h)
 LAYER_FC, LAYER_LSTM, LAYER_RESIDUAL = 4, 8, 10
 LAYER_AVERAGE_POOLING, LAYER_MAX_POOLING = 1, 9
+LAYER_FC_IND_RNN = 5
 NET_FEEDFORWARD, NET_RECURRENT = 3, 4
 AF_ELU, AF_LINEAR, AF_LEAKY_RELU, AF_RELU, AF_SELU, AF_SIGMOID, AF_SOFTMAX, AF_TANH = 3, 11, 14, 16, 17, 18, 22, 23
 (AF_COSINE, AF_COSINE_SYMMETRIC, AF_ELLIOT, AF_ELLIOT_SYMMETRIC, AF_GAUSSIAN, AF_GAUSSIAN_STEPWISE, AF_GAUSSIAN_SYMMETRIC, AF_ISRU, AF_ISRLU,
@@ -43,7 +44,7 @@ class NetDesc(C.Structure):
                 ("type_accuracy_function", C.c_uint32), ("accuracy_variance", C.c_float),
                 ("normalization_momentum_average", C.c_float), ("normalization_epsilon", C.c_float),
                 ("batch_renormalization_r_correction_maximum", C.c_float),
-                ("batch_renormalization_d_correction_maximum", C.c_float), ("reserved", C.c_uint32),
+                ("batch_renormalization_d_correction_maximum", C.c_float), ("clip_gradient", C.c_float),
                 ("layers", LayerDesc * MAX_LAYERS)]
 
 
@@ -83,6 +84,13 @@ def fc(units, af=AF_LINEAR, norm=NORM_NONE, dropout=DROP_NONE, p=(0.0, 0.0, 0.0)
     return d
 
 
+def fc_ind_rnn(units, af=AF_RELU, norm=NORM_NONE, dropout=DROP_NONE, p=(0.0, 0.0, 0.0)):
+    """independently recurrent fully connected layer: y_t = f(W x_t + b + u * y_{t-1}), one recurrent weight per unit"""
+    d = fc(units, af, norm, dropout, p)
+    d.type_layer = LAYER_FC_IND_RNN
+    return d
+
+
 def pooling(kind, kernel, stride, padding=0, dilation=1, ceil_mode=False):
     """average (LAYER_AVERAGE_POOLING) or max (LAYER_MAX_POOLING) pooling over the units of the layer before"""
     d = LayerDesc()
@@ -118,12 +126,12 @@ def residual(block_depth, dropout=DROP_NONE, p=(0.0, 0.0, 0.0), normalization=NO
 
 
 def net(layers, batch, T=1, loss=LOSS_MSE, accuracy=ACC_NONE, time_delays=0, momentum=0.0, epsilon=0.0, r_max=0.0,
-        d_max=0.0):
+        d_max=0.0, clip_gradient=0.0):
     """Network descriptor. momentum/epsilon/r_max/d_max of 0 keep the reference defaults
     (0.999, 1e-5, 1, 0: Data.hpp:2966-2969)."""
     d = NetDesc()
     d.number_layers = len(layers)
-    d.type_network = NET_RECURRENT if T > 1 or any(l.type_layer == LAYER_LSTM for l in layers) else NET_FEEDFORWARD
+    d.type_network = NET_RECURRENT if T > 1 or any(l.type_layer in (LAYER_LSTM, LAYER_FC_IND_RNN) for l in layers) else NET_FEEDFORWARD
     d.number_recurrent_depth = T
     d.number_time_delays = time_delays
     d.batch_size = batch
@@ -133,6 +141,7 @@ def net(layers, batch, T=1, loss=LOSS_MSE, accuracy=ACC_NONE, time_delays=0, mom
     d.normalization_epsilon = epsilon
     d.batch_renormalization_r_correction_maximum = r_max
     d.batch_renormalization_d_correction_maximum = d_max
+    d.clip_gradient = clip_gradient   # only shapes the recurrent-weight bounds of independently recurrent layers; 0 = class default 1
     for i, l in enumerate(layers):
         d.layers[i] = l
     return d

@@ -69,8 +69,9 @@ struct HostPlan {
   std::unique_ptr<myea_b200_net> net;
   std::vector<uint64_t> unit_base;  // first global unit number of each layer, in the numbering of its own unit kind
   std::vector<int> block_of;        // residual layer a layer sits in, or 0
-  uint64_t neurons = 0, cells = 0, blocks = 0, basics = 0, basic_indices = 0, af_units = 0;
+  uint64_t neurons = 0, cells = 0, blocks = 0, basics = 0, basic_indices = 0, af_units = 0, af_ind_units = 0;
   std::vector<uint64_t> af_count;   // activation units each layer lists
+  std::vector<uint64_t> ind_base;   // first global AF_Ind_recurrent unit number of an independently recurrent layer
   std::vector<int> reads;           // the layer whose units a layer's connections name
   std::string error;
 };
@@ -101,8 +102,14 @@ int make_plan(const myea_net_desc *desc, HostPlan &P) {
     if (L.desc.use_bidirectional) { P.error = "bidirectional layers have no usable definition in the reference's files"; return MYEA_E_UNSUPPORTED; }
     switch (L.type) {
       case MYEA_LAYER_FULLY_CONNECTED:
-        P.unit_base[l] = P.neurons;
+        P.unit_base[l] = P.neurons;   // its readers name neuron units, also when the layer is independently recurrent (Save.cpp:731-738)
         P.neurons += L.n_out;
+        if (L.ind_rnn) {  // it lists AF_Ind_recurrent units instead of plain activation units
+          P.ind_base.resize(n, 0);
+          P.ind_base[l] = P.af_ind_units;
+          P.af_ind_units += L.n_out;
+          break;
+        }
         if (P.block_of[l] == 0) P.af_count[l] = L.n_out;
         else P.af_count[l] = (static_cast<int>(l) == P.block_of[l] + 1) ? 0 : L.n_in;
         P.af_units += P.af_count[l];
@@ -178,10 +185,16 @@ struct Writer {
     }
   }
 
-  void sparsity_and_constraints() {
+  void sparsity_and_constraints(const LayerPlan *L = nullptr) {
     line(4, "use_tied_parameter", "0");
     line(4, "k_sparsity", "0");
     line(4, "alpha_sparsity", "1");
+    if (L != nullptr && L->ind_rnn) {  // the default bound of the layer's recurrent weights
+      const float b = ind_rnn_weight_bound(net().desc.clip_gradient, L->desc.type_activation_function, net().T);
+      line(4, "constraint_recurrent_weight_lower_bound", real(-b));
+      line(4, "constraint_recurrent_weight_upper_bound", real(b));
+      return;
+    }
     line(4, "constraint_recurrent_weight_lower_bound", "0");
     line(4, "constraint_recurrent_weight_upper_bound", "0");
   }
@@ -210,6 +223,20 @@ struct Writer {
       line(6, "AF[" + num(i) + "]", "");
       line(8, "activation_steepness", "1");
       line(8, "activation_function", num(L.desc.type_activation_function));
+    }
+  }
+
+  // Information__Layer__AF_Ind_Recurrent (Save.cpp:844-863): activation and the self connection of every unit
+  void ind_recurrent_units(size_t l) {
+    const LayerPlan &L = net().layers[l];
+    line(4, "number_AF_Ind_recurrent_units", num(L.n_out));
+    const uint64_t first = L.idx.first_connection_index + static_cast<uint64_t>(L.n_out) * L.n_in;
+    for (long long i = 0; i < L.n_out; ++i) {
+      line(6, "AF_Ind_R[" + num(i) + "]", "");
+      line(8, "activation_steepness", "1");
+      line(8, "activation_function", num(L.desc.type_activation_function));
+      line(8, "connected_to_AF_Ind_R", num(P.ind_base[l] + i));
+      line(8, "weight[" + num(first + i) + "]", real(params[first + i]));
     }
   }
 
@@ -277,7 +304,7 @@ int format_dimension(const HostPlan &P, const float *params, const float *mean, 
   w.line(0, "total_basic_indice_units", num(P.basic_indices));
   w.line(0, "total_neuron_units", num(P.neurons));
   w.line(0, "total_AF_units", num(P.af_units));
-  w.line(0, "total_AF_Ind_recurrent_units", "0");
+  w.line(0, "total_AF_Ind_recurrent_units", num(P.af_ind_units));
   w.line(0, "total_block_units", num(P.blocks));
   w.line(0, "total_cell_units", num(P.cells));
   w.line(0, "total_normalized_units", num(net.total_norm_units));
@@ -294,16 +321,17 @@ int format_dimension(const HostPlan &P, const float *params, const float *mean, 
   for (size_t l = 1; l + 1 < n; ++l) {
     const LayerPlan &L = Ls[l];
     w.line(2, "Hidden layer " + num(l) + ":", "");
-    w.line(4, "type_layer", num(L.type));
+    w.line(4, "type_layer", num(L.desc.type_layer));
     w.line(4, "use_bidirectional", "0");
     switch (L.type) {
       case MYEA_LAYER_FULLY_CONNECTED:
         w.line(4, "type_activation", num(activation_class(L.desc.type_activation_function)));
         w.dropout(L, true);
         w.normalization(L);
-        w.sparsity_and_constraints();
+        w.sparsity_and_constraints(&L);
         w.neurons(l, "number_neuron_units");
-        w.activation_units(l);
+        if (L.ind_rnn) w.ind_recurrent_units(l);
+        else w.activation_units(l);
         w.bias(L);
         break;
       case MYEA_LAYER_LSTM:
@@ -606,11 +634,13 @@ bool parse_normalization(Lines &in, myea_layer_desc &L, NormValues &nv, uint64_t
   return true;
 }
 
-bool skip_sparsity_and_constraints(Lines &in) {
-  float f;
+bool skip_sparsity_and_constraints(Lines &in, float *upper_bound = nullptr) {
+  float f, hi = 0.f;
   uint64_t u;
-  return in.take_u64("use_tied_parameter", &u) && in.take_u64("k_sparsity", &u) && in.take_real("alpha_sparsity", &f) &&
-         in.take_real("constraint_recurrent_weight_lower_bound", &f) && in.take_real("constraint_recurrent_weight_upper_bound", &f);
+  const bool ok = in.take_u64("use_tied_parameter", &u) && in.take_u64("k_sparsity", &u) && in.take_real("alpha_sparsity", &f) &&
+                  in.take_real("constraint_recurrent_weight_lower_bound", &f) && in.take_real("constraint_recurrent_weight_upper_bound", &hi);
+  if (upper_bound != nullptr) *upper_bound = hi;
+  return ok;
 }
 
 bool parse_connections(Lines &in, uint64_t count, Parsed &out) {
@@ -644,6 +674,22 @@ bool parse_activation_units(Lines &in, myea_layer_desc &L, uint64_t *count) {
     if (steep != 1.f) return in.fail("activation steepness other than 1 is not built");
     if (i == 0) L.type_activation_function = static_cast<uint32_t>(af);
     else if (L.type_activation_function != af) return in.fail("a layer mixing activation functions is not built");
+  }
+  return true;
+}
+
+bool parse_ind_recurrent_units(Lines &in, myea_layer_desc &L, Parsed &out) {
+  uint64_t n = 0, af = 0, unit = 0, idx = 0;
+  float steep = 1.f, v = 0.f;
+  if (!in.take_u64("number_AF_Ind_recurrent_units", &n)) return false;
+  for (uint64_t i = 0; i < n; ++i) {
+    if (!in.take("AF_Ind_R", nullptr, true) || !in.take_real("activation_steepness", &steep) || !in.take_u64("activation_function", &af) ||
+        !in.take_u64("connected_to_AF_Ind_R", &unit) || !in.take_weight(&idx, &v))
+      return false;
+    if (steep != 1.f) return in.fail("activation steepness other than 1 is not built");
+    if (i == 0) L.type_activation_function = static_cast<uint32_t>(af);
+    else if (L.type_activation_function != af) return in.fail("a layer mixing activation functions is not built");
+    out.weights.emplace_back(idx, v);
   }
   return true;
 }
@@ -692,7 +738,6 @@ int parse_dimension(const char *path, Parsed &out, std::string &error) {
        in.take_u64("total_bias", &out.total_bias);
   if (!ok) { error = in.error; return MYEA_E_INVALID; }
   if (layers < 2 || layers > MYEA_MAX_LAYERS || d.number_recurrent_depth == 0) { error = "layer count or recurrent depth out of range"; return MYEA_E_INVALID; }
-  if (totals[4] != 0) { error = "independently recurrent layers are not built"; return MYEA_E_UNSUPPORTED; }
   out.total_norm_units = totals[7];
   d.number_layers = static_cast<uint32_t>(layers);
   out.norm.assign(layers, NormValues());
@@ -719,6 +764,19 @@ int parse_dimension(const char *path, Parsed &out, std::string &error) {
              skip_sparsity_and_constraints(in) && parse_neurons(in, "number_neuron_units", L, out) &&
              parse_activation_units(in, L, &out.af_units[l]) && parse_bias(in, out);
         break;
+      case MYEA_LAYER_FC_INDEPENDENTLY_RECURRENT: {
+        float bound = 0.f;
+        ok = in.take_u64("type_activation", &u) && parse_dropout(in, L, true) && parse_normalization(in, L, out.norm[l], T, true) &&
+             skip_sparsity_and_constraints(in, &bound) && parse_neurons(in, "number_neuron_units", L, out) &&
+             parse_ind_recurrent_units(in, L, out) && parse_bias(in, out);
+        out.af_units[l] = L.unit_parameters[0];  // (not the first layer of a block)
+        // the bound is the default one for some clip_gradient between 2 and 10: recover that value (0 = the class default)
+        if (ok && bound > 0.f && fabsf(bound - ind_rnn_weight_bound(0.f, L.type_activation_function, static_cast<long long>(T))) > 1e-6f * bound) {
+          const float c = ind_rnn_weight_bound(0.f, L.type_activation_function, static_cast<long long>(T));
+          d.clip_gradient = 2.f * powf(bound / c, static_cast<float>(T));  // bound = (MAG / k)^(1/T), c = (2 / k)^(1/T)
+        }
+        break;
+      }
       case MYEA_LAYER_LSTM:
         ok = in.take_u64("type_activation", &u) && parse_dropout(in, L, true) && parse_normalization(in, L, out.norm[l], T, false) &&
              skip_sparsity_and_constraints(in) && parse_lstm(in, L, out) && parse_bias(in, out);
@@ -741,7 +799,7 @@ int parse_dimension(const char *path, Parsed &out, std::string &error) {
       }
       default: error = "layer type " + std::to_string(L.type_layer) + " is not built"; return MYEA_E_UNSUPPORTED;
     }
-    if (L.type_layer == MYEA_LAYER_FULLY_CONNECTED) width[l] = L.unit_parameters[0];
+    if (L.type_layer == MYEA_LAYER_FULLY_CONNECTED || L.type_layer == MYEA_LAYER_FC_INDEPENDENTLY_RECURRENT) width[l] = L.unit_parameters[0];
     if (L.type_layer == MYEA_LAYER_LSTM) width[l] = L.unit_parameters[0] * std::max<uint64_t>(1, L.unit_parameters[1]);
   }
   myea_layer_desc &O = d.layers[layers - 1];

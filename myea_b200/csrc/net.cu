@@ -103,6 +103,12 @@ int myea::build_index_map(myea_b200_net *net) {
     L.type = d.layers[l].type_layer;
     memset(&L.idx, 0, sizeof(L.idx));
     switch (L.type) {
+      case MYEA_LAYER_FC_INDEPENDENTLY_RECURRENT:  // a fully connected layer with one recurrent weight per unit on top
+        L.type = MYEA_LAYER_FULLY_CONNECTED;
+        L.ind_rnn = true;
+        L.n_out = static_cast<long long>(d.layers[l].unit_parameters[0]);
+        if (l == 0 || l + 1 == n) return fail(net, MYEA_E_INVALID, "an independently recurrent layer is a hidden layer");
+        break;
       case MYEA_LAYER_FULLY_CONNECTED: L.n_out = static_cast<long long>(d.layers[l].unit_parameters[0]); break;
       case MYEA_LAYER_LSTM: {
         const long long blocks = static_cast<long long>(d.layers[l].unit_parameters[0]);
@@ -133,7 +139,8 @@ int myea::build_index_map(myea_b200_net *net) {
     if (L.type == MYEA_LAYER_RESIDUAL) {
       if (L.block_depth < 1 || l + L.block_depth >= n) return fail(net, MYEA_E_INVALID, "residual block runs past the output layer");
       for (int k = 1; k <= L.block_depth; ++k)
-        if (net->layers[l + k].type != MYEA_LAYER_FULLY_CONNECTED) return fail(net, MYEA_E_UNSUPPORTED, "residual blocks of fully connected layers only");
+        if (net->layers[l + k].type != MYEA_LAYER_FULLY_CONNECTED || net->layers[l + k].ind_rnn)
+          return fail(net, MYEA_E_UNSUPPORTED, "residual blocks of fully connected layers only");
       // the block output is as wide as the wider of the shortcut and the block's last layer (zero-padded identity); the
       // shortcut is the layer before, or the residual layer of the block that ends there
       uint32_t feeder = l - 1;
@@ -171,6 +178,7 @@ int myea::build_index_map(myea_b200_net *net) {
     if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
       L.idx.first_connection_index = tw;
       tw += static_cast<uint64_t>(L.n_out) * L.n_in;
+      if (L.ind_rnn) tw += static_cast<uint64_t>(L.n_out);  // the units' self connections (Prepare__Connections__FC_Ind_RNN)
       L.idx.last_connection_index = tw;
     } else if (L.type == MYEA_LAYER_LSTM) {
       const uint64_t blocks = L.desc.unit_parameters[0] << (L.desc.use_bidirectional ? 1 : 0);
@@ -275,6 +283,7 @@ static int allocate_buffers(myea_b200_net *net) {
       // a layer inside a residual block keeps its normalized / activated INPUT in `values` and `deriv`
       const long long wide = layer_in_block(net, static_cast<int>(l), nullptr) ? std::max(L.n_out, L.n_in) : L.n_out;
       RC(dev_alloc(net, &L.summations, rows * L.n_out));
+      if (L.ind_rnn) RC(dev_alloc(net, &L.pre_af, rows * L.n_out));
       RC(dev_alloc(net, &L.values, rows * wide));
       RC(dev_alloc(net, &L.deriv, rows * wide));
       if (L.has_norm) RC(dev_alloc(net, &L.errors, rows * L.n_out));
@@ -588,7 +597,7 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
   e.bias = L.use_bias ? net->params + L.idx.first_bias_connection_index : nullptr;
   // batch statistics: the contraction's epilogue leaves the column sums of every 32-row block behind, where it can
   int fused_chunks = 0;
-  const bool timewise_norm = L.has_norm && net->T > 1;  // a recurrent network normalizes every time step by itself
+  const bool timewise_norm = (L.has_norm && net->T > 1) || L.ind_rnn;  // a recurrent network normalizes every time step by itself
   if (L.has_norm && net->training && !timewise_norm) {
     Epilogue probe = e;
     probe.stats_kind = 1;
@@ -613,6 +622,27 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
       N.in_ready_rows = rows;
       use_sink = true;
     }
+  }
+  if (L.ind_rnn) {
+    // the recurrence runs step by step on the summations of all steps (one contraction above): per step the statistics of
+    // a normalized layer, then pre = z' + u * y_prev and the activation
+    if (L.desc.type_activation_function == MYEA_AF_SOFTMAX) return MYEA_E_UNSUPPORTED;
+    const long long pitch = rows / net->T;
+    const uint8_t *mask = (net->training && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
+    const float scale = net->training ? (mask != nullptr ? L.keep_scale : 1.f) : L.infer_scale;
+    const float *u = net->params + L.idx.first_connection_index + static_cast<uint64_t>(L.n_out) * L.n_in;
+    for (long long t = 0; t < net->T; ++t) {
+      const long long off = t * pitch * L.n_out;
+      const float *cs = nullptr, *ch = nullptr;
+      if (L.has_norm) {
+        const NormParams np = norm_at_step(L, t);
+        RC(norm_forward_stats(net->ctx, L.summations + off, net->active_B, L.n_out, np, net->training ? 1 : 0, &net->hook, nullptr, 0));
+        cs = np.col_scale; ch = np.col_shift;
+      }
+      RC(ind_rnn_forward_step(net->ctx, L.summations + off, t > 0 ? L.values + off - pitch * L.n_out : nullptr, u, L.pre_af + off, L.values + off, pitch,
+                              L.n_out, L.desc.type_activation_function, cs, ch, mask != nullptr ? mask + t * L.n_out : nullptr, scale));
+    }
+    return MYEA_OK;
   }
   if (timewise_norm) {
     // statistics, running averages and coefficients of step t live at t * units behind those of step 0; the rows a short
@@ -931,6 +961,30 @@ extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
       return lstm_backward_to_input(net, N, dst, P, nullptr);
     };
     if (P.type == MYEA_LAYER_FULLY_CONNECTED) {
+      if (P.ind_rnn) {
+        // the error over all rows first, then backwards through time dAF_t = f'(pre_t) * (D_t + u * dAF_{t+1}), in place, and
+        // the normalization backward of each step behind it
+        RC(send_plain(P.deriv));
+        const long long pitch = rows / net->T;
+        const float *u = net->params + P.idx.first_connection_index + static_cast<uint64_t>(P.n_out) * P.n_in;
+        for (long long t = net->T - 1; t >= 0; --t) {
+          const long long off = t * pitch * P.n_out;
+          RC(ind_rnn_backward_step(net->ctx, P.deriv + off, t + 1 < net->T ? P.deriv + off + pitch * P.n_out : nullptr, u, P.pre_af + off, P.values + off,
+                                   pitch, P.n_out, P.desc.type_activation_function));
+        }
+        if (P.has_norm) {
+          for (long long t = 0; t < net->T; ++t) {
+            const NormParams np = norm_at_step(P, t);
+            const long long off = t * pitch * P.n_out;
+            RC(norm_backward(net->ctx, P.summations + off, P.deriv + off, P.errors + off, net->active_B, P.n_out, np, &net->hook, 0, nullptr));
+          }
+          if (net->active_B < pitch)
+            CK(cudaMemset2DAsync(P.errors + net->active_B * P.n_out, pitch * P.n_out * sizeof(float), 0, (pitch - net->active_B) * P.n_out * sizeof(float),
+                                 net->T, net->ctx.stream));
+        }
+        l = p;
+        continue;
+      }
       if (P.has_norm && net->T > 1) {
         // per-time-step normalization: the error over all rows first, then step by step the activation derivative on
         // that step's normalized summations and the normalization backward with that step's statistics
@@ -1026,10 +1080,18 @@ extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batc
       int blk = 0;
       if (layer_in_block(net, l, &blk)) input = residual_fc_input(net, blk, l - blk);  // normalized / activated copy kept by the block
       RC(fc_update_derivative_weight(net, L, input, rows));
+      if (L.ind_rnn && net->T > 1) {
+        // recurrent weights: dAF of step t with the output of step t - 1 (the pre-activation buffer is free by now and
+        // holds the products)
+        const long long pitch = rows / net->T;
+        RC(ind_rnn_recurrent_derivative(net->ctx, L.deriv, L.values, (net->T - 1) * pitch, L.n_out, pitch, L.pre_af,
+                                        net->grads + L.idx.first_connection_index + static_cast<uint64_t>(L.n_out) * L.n_in, net->reduce_partial,
+                                        net->reduce_chunks));
+      }
     } else if (L.type == MYEA_LAYER_LSTM) {
       RC(lstm_update_derivative_weight(net, L, net->layers[L.input_layer].values, L.n_in));
     }
-    if (net->comm != nullptr && L.type != MYEA_LAYER_RESIDUAL)
+    if (net->comm != nullptr && L.idx.last_connection_index > L.idx.first_connection_index)
       RC(comm_reduce_bucket_async(net, L.idx.first_connection_index, L.idx.last_connection_index - L.idx.first_connection_index));
   }
   if (net->comm != nullptr) {  // biases and normalization scales / shifts: one last bucket behind the weights
@@ -1141,6 +1203,11 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
   } else {
     RC(optimizer_update(net->ctx, o, net->params, net->grads, net->m1, net->m2, net->m2hat, net->prev_delta, net->mask_reg, P));
   }
+  // independently recurrent layers keep their recurrent weights inside their bound (Update_Parameter: Use__Regularization__Constraint_Recurrent_Weight)
+  for (const auto &L : net->layers)
+    if (L.ind_rnn)
+      RC(ind_rnn_clamp(net->ctx, net->params + L.idx.first_connection_index + static_cast<uint64_t>(L.n_out) * L.n_in, L.n_out,
+                       ind_rnn_weight_bound(net->desc.clip_gradient, L.desc.type_activation_function, net->T)));
   if (max_norm != 0.f) {
     // Update_Weight_Regularization__Max_Norm_Constraints__Neurons (…Max_Norm_Constraints.cpp:147-165): one weight row per neuron
     for (const auto &L : net->layers)

@@ -50,7 +50,21 @@ struct LayerPlan {
   long long in_ready_rows = 0;
   int bwd_fused_chunks = 0;       // row blocks whose normalization-backward sums the error-propagation epilogue has emitted
   int *pool_winner = nullptr;     // max pooling: [T*B, n_out] position (in the padded input) that gave each output
+  // independently recurrent fully connected layer (type FULLY_CONNECTED here, ind_rnn set): n_out recurrent weights
+  // behind the layer's n_out * n_in weights; pre_af = summation (normalized) + u * previous output, what the activation sees
+  bool ind_rnn = false;
+  float *pre_af = nullptr;        // [T*B, n_out]
 };
+
+// independently recurrent layers (ind_rnn.cu)
+int ind_rnn_forward_step(Context &ctx, const float *z, const float *y_prev, const float *u, float *pre, float *y, long long rows, long long H, uint32_t af,
+                         const float *col_scale, const float *col_shift, const uint8_t *mask, float keep_scale);
+int ind_rnn_backward_step(Context &ctx, float *d, const float *d_next, const float *u, const float *pre, const float *y, long long rows, long long H,
+                          uint32_t af);
+float ind_rnn_weight_bound(float clip_gradient, uint32_t type_activation_function, long long T);
+int ind_rnn_clamp(Context &ctx, float *w, long long n, float bound);
+int ind_rnn_recurrent_derivative(Context &ctx, const float *d, const float *y, long long rows, long long H, long long shift, float *scratch, float *du,
+                                 float *partial, int chunks);
 
 // pooling layers (pooling.cu)
 long long pooling_output_width(const myea_layer_desc &d, long long n_in);

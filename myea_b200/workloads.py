@@ -56,11 +56,13 @@ class Workload:
             L = self.layers[l]
             li = net.layer_index(l)
             n_in, n_out = int(li.number_inputs), int(li.number_outputs)
-            if L.type_layer == capi.LAYER_FC:
+            if L.type_layer in (capi.LAYER_FC, capi.LAYER_FC_IND_RNN):
                 gain = {capi.AF_TANH: 5.0 / 3.0, capi.AF_RELU: math.sqrt(2.0)}.get(L.type_activation_function, 1.0)
                 bound = gain * math.sqrt(6.0 / (n_in + n_out))
                 a, b = int(li.first_connection_index), int(li.last_connection_index)
                 p[a:b] = rng.uniform(-bound, bound, b - a)
+                if L.type_layer == capi.LAYER_FC_IND_RNN:     # the units' recurrent weights close the layer's range
+                    p[b - n_out:b] = rng.uniform(0.2, 0.9, n_out)
             elif L.type_layer == capi.LAYER_LSTM:
                 dirs = 2 if L.use_bidirectional else 1
                 C = n_out // dirs

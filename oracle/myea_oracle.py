@@ -49,9 +49,11 @@ def af_fire(af, z):
     """AF_FIRE (Activation_Functions.hpp:124-196)"""
     dt = z.dtype.type
     if af == capi.AF_TANH:
-        return dt(2) / (dt(1) + np.exp(dt(-2) * z)) - dt(1)
+        with np.errstate(over="ignore"):      # e^(+big) = inf gives the limit -1, as in the reference's float arithmetic
+            return dt(2) / (dt(1) + np.exp(dt(-2) * z)) - dt(1)
     if af == capi.AF_SIGMOID:
-        return dt(1) / (dt(1) + np.exp(-z))
+        with np.errstate(over="ignore"):
+            return dt(1) / (dt(1) + np.exp(-z))
     if af == capi.AF_RELU:
         return np.where(z < 0, dt(0), z)
     if af in (capi.AF_LEAKY_RELU, capi.AF_PARAMETRIC_RELU):
@@ -157,6 +159,9 @@ def build_index_map(desc):
         L = _Layer()
         L.d, L.type = d, int(d.type_layer)
         L.n_out = 0
+        L.ind_rnn = L.type == capi.LAYER_FC_IND_RNN   # a fully connected layer plus one recurrent weight per unit
+        if L.ind_rnn:
+            L.type = capi.LAYER_FC
         if L.type == capi.LAYER_FC:
             L.n_out = int(d.unit_parameters[0])
         elif L.type == capi.LAYER_LSTM:
@@ -198,6 +203,8 @@ def build_index_map(desc):
         if L.type == capi.LAYER_FC:
             L.idx["first_connection_index"] = tw
             tw += L.n_out * L.n_in
+            if L.ind_rnn:
+                tw += L.n_out       # the units' self connections (Prepare__Connections__FC_Ind_RNN, …Prepare_Connections.cpp:45-78)
             L.idx["last_connection_index"] = tw
         elif L.type == capi.LAYER_LSTM:
             dirs = 2 if L.d.use_bidirectional else 1
@@ -325,7 +332,7 @@ class OracleNet:
     # ---- fully connected layer ---------------------------------------------------------------------------------
     def _fc_weights(self, L):
         i = L.idx
-        return self._p()[i["first_connection_index"]:i["last_connection_index"]].reshape(L.n_out, L.n_in)
+        return self._p()[i["first_connection_index"]:i["first_connection_index"] + L.n_out * L.n_in].reshape(L.n_out, L.n_in)
 
     def _norm_steps(self, rows):
         """row ranges of the time steps inside a [T * rows-per-step, H] array (one step for a feed-forward network)"""
@@ -388,6 +395,57 @@ class OracleNet:
                 d_mean, d_sigma = self.allreduce(d_mean), self.allreduce(d_sigma)
             out[rows] = dh * (r / sigma) + d_sigma * ((zt - mean) / (B * sigma)) + d_mean * (dt(1) / B)
         return out
+
+    def _dropout(self, l, y):
+        """Bernoulli / inverted Bernoulli dropout of layer l on rows y of ONE time step `self._t` (mask row per step)"""
+        L = self.layers[l]
+        dt = self.dt
+        drop = int(L.d.type_dropout)
+        if drop in (capi.DROP_BERNOULLI, capi.DROP_BERNOULLI_INVERTED):
+            p = dt(L.d.dropout_values[0])
+            if self.training:
+                m = np.asarray(self.masks[l]).reshape(-1, y.shape[1])[self._t]
+                y = np.where(m, y * (dt(1) / p) if drop == capi.DROP_BERNOULLI_INVERTED else y, dt(0))
+            elif drop == capi.DROP_BERNOULLI:
+                y = y * p
+        return y
+
+    def _ind_rnn_forward(self, l, pre):
+        """Forward_Pass__FC_Ind_RNN__Loop (Neural_Network__Recurrent_Forward_Pass__Loop.cpp:813-860): per time step
+        pre_t = z'_t + u * y_{t-1}, y_t = f(pre_t), dropout in place on y_t (what the next step then sees)"""
+        L = self.layers[l]
+        dt = self.dt
+        i = L.idx
+        u = self._p()[i["first_connection_index"] + L.n_out * L.n_in:i["last_connection_index"]]
+        af = int(L.d.type_activation_function)
+        n = pre.shape[0] // self.T
+        L.pre = np.array(pre, dt)
+        y = np.zeros_like(L.pre)
+        for t in range(self.T):
+            rows = slice(t * n, (t + 1) * n)
+            if t > 0:
+                L.pre[rows] = L.pre[rows] + u * y[(t - 1) * n:t * n]
+            self._t = t
+            y[rows] = self._dropout(l, af_fire(af, L.pre[rows]))
+        L.values = y.astype(dt)
+        return L.values
+
+    def _ind_rnn_backward(self, L, D):
+        """Backward_Pass__FC__DF_Ind_RNN__Loop (Neural_Network__Backward_Pass__Loop.cpp:1296-1372):
+        dAF_t = D_t * f' + u * f' * dAF_{t+1}, backwards in time"""
+        dt = self.dt
+        i = L.idx
+        u = self._p()[i["first_connection_index"] + L.n_out * L.n_in:i["last_connection_index"]]
+        f = af_derive(int(L.d.type_activation_function), L.pre, L.values)
+        n = D.shape[0] // self.T
+        dAF = np.zeros_like(D)
+        for t in range(self.T - 1, -1, -1):
+            rows = slice(t * n, (t + 1) * n)
+            dAF[rows] = D[rows] * f[rows]
+            if t + 1 < self.T:
+                dAF[rows] = dAF[rows] + u * f[rows] * dAF[(t + 1) * n:(t + 2) * n]
+        L.dAF = dAF.astype(dt)
+        return L.dAF
 
     def _pooling_windows(self, L):
         """padded positions j * stride + k * dilation read by output j, and which of them fall inside the input"""
@@ -453,6 +511,8 @@ class OracleNet:
             z = z + self._p()[L.idx["first_bias_connection_index"]:L.idx["first_bias_connection_index"] + L.n_out]
         L.z = z
         pre = self._norm_forward(L, z) if norm else z
+        if L.ind_rnn:
+            return self._ind_rnn_forward(l, pre)
         L.pre = pre
         af = int(L.d.type_activation_function)
         if af == capi.AF_SOFTMAX:
@@ -555,7 +615,7 @@ class OracleNet:
                 from oracle import myea_oracle_lstm
                 D = myea_oracle_lstm.error_to_input(self, l)
             if Pl.type == capi.LAYER_FC:
-                da = D * af_derive(int(Pl.d.type_activation_function), Pl.pre, Pl.values)
+                da = self._ind_rnn_backward(Pl, D) if Pl.ind_rnn else D * af_derive(int(Pl.d.type_activation_function), Pl.pre, Pl.values)
                 Pl.errors = self._norm_backward(Pl, Pl.z, da) if int(Pl.d.type_normalization) != capi.NORM_NONE else da
             elif Pl.type == capi.LAYER_LSTM:
                 from oracle import myea_oracle_lstm
@@ -575,7 +635,10 @@ class OracleNet:
                 if x is None:
                     x = self.layers[L.input_layer].values
                 i = L.idx
-                self._g()[i["first_connection_index"]:i["last_connection_index"]] += (L.errors.T @ x).ravel()
+                self._g()[i["first_connection_index"]:i["first_connection_index"] + L.n_out * L.n_in] += (L.errors.T @ x).ravel()
+                if L.ind_rnn and self.T > 1:   # Update_Derivative_Weight__FC_Ind_RNN: dAF of step t with the output of step t - 1
+                    n = L.values.shape[0] // self.T
+                    self._g()[i["first_connection_index"] + L.n_out * L.n_in:i["last_connection_index"]] += (L.dAF[n:] * L.values[:-n]).sum(0, dtype=self.dt)
                 if int(L.d.type_normalization) == capi.NORM_NONE:
                     self._g()[i["first_bias_connection_index"]:i["first_bias_connection_index"] + L.n_out] += L.errors.sum(0, dtype=self.dt)
             elif L.type == capi.LAYER_LSTM:
@@ -664,6 +727,19 @@ class OracleNet:
                     w -= mom * prev - lr * g + decay
                 else:
                     w -= prev + decay
+        # independently recurrent layers: recurrent weights kept inside +-(MAG / k)^(1/T) (…Constraint_Recurrent_Weight.cpp:43-80,
+        # :317-334), MAG = clip(clip_gradient, 2, 10), k = 0.9^(T/10) for symmetric activation functions, else 1
+        for L in self.layers[1:]:
+            if getattr(L, "ind_rnn", False):
+                cg = float(self.desc.clip_gradient) or 1.0
+                mag = np.float32(min(max(cg, 2.0), 10.0))
+                sym = int(L.d.type_activation_function) in (capi.AF_COSINE_SYMMETRIC, capi.AF_ELLIOT_SYMMETRIC, capi.AF_GAUSSIAN_SYMMETRIC,
+                                                            capi.AF_LINEAR_PIECE_SYMMETRIC, capi.AF_SINE_SYMMETRIC, capi.AF_TANH, capi.AF_TANH_STEPWISE,
+                                                            capi.AF_THRESHOLD_SYMMETRIC)
+                t = np.float32(self.T)
+                b = np.power(mag / np.power(np.float32(0.9), t / np.float32(10)), np.float32(1) / t) if sym else np.power(mag, np.float32(1) / t)
+                a0 = L.idx["first_connection_index"] + L.n_out * L.n_in
+                np.clip(w[a0:L.idx["last_connection_index"]], -dt(b), dt(b), out=w[a0:L.idx["last_connection_index"]])
         c = dt(o.regularization__max_norm_constraints)
         if c != 0:   # …Max_Norm_Constraints.cpp:147-165 + Euclidean_Norm__Loop :48-88: one weight row per neuron of every FC layer
             for L in self.layers[1:]:

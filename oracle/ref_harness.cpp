@@ -96,7 +96,7 @@ void *ref_create(const myea_net_desc *d, const myea_opt_desc *opt, int threads) 
   if (d->number_recurrent_depth > 1) nn.Set__Number_Time_Delays(d->number_time_delays);
   for (uint32_t i = 1; i < d->number_layers; ++i) {
     const myea_layer_desc &L = d->layers[i];
-    if (L.type_layer == MYEA_LAYER_FULLY_CONNECTED && L.type_activation_function != 0)
+    if ((L.type_layer == MYEA_LAYER_FULLY_CONNECTED || L.type_layer == MYEA_LAYER_FC_INDEPENDENTLY_RECURRENT) && L.type_activation_function != 0)
       nn.Set__Layer_Activation_Function(i, static_cast<ENUM_TYPE_ACTIVATION_FUNCTION>(L.type_activation_function));
   }
   nn.Set__Loss_Function(static_cast<ENUM_TYPE_LOSS_FUNCTIONS>(d->type_loss_function));
@@ -198,7 +198,8 @@ int ref_layer_index(void *h, uint32_t layer, myea_layer_index *out) {
     Block_unit *b = L->ptr_array_block_units;
     out->block_stride = b->last_index_connection - b->first_index_connection;
     out->number_inputs = b->last_index_feedforward_connection_input_gate - b->first_index_feedforward_connection_input_gate;
-  } else if (layer > 0 && L->type_layer == ENUM_TYPE_LAYER::TYPE_LAYER_FULLY_CONNECTED) {
+  } else if (layer > 0 && (L->type_layer == ENUM_TYPE_LAYER::TYPE_LAYER_FULLY_CONNECTED ||
+                           L->type_layer == ENUM_TYPE_LAYER::TYPE_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT)) {
     out->number_inputs = *L->ptr_array_neuron_units->ptr_number_connections;
   }
   if (nn.total_normalized_units != 0 && L->ptr_array_normalized_units != nullptr) {

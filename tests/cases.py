@@ -155,6 +155,25 @@ CASES.update({
 })
 
 
+def _ind_rnn_case(name, af, norm=capi.NORM_NONE, dropout=capi.DROP_NONE, T=4, stacked=False, lr=0.01):
+    """independently recurrent fully connected layers (Ind-RNN): y_t = f(W x_t + b + u * y_{t-1})"""
+    ls = [capi.fc(7), capi.fc_ind_rnn(9, af, norm=norm, dropout=dropout, p=(0.8, 0.0, 0.0))]
+    if stacked:
+        ls.append(capi.fc_ind_rnn(8, af))
+    ls += [capi.fc(6, capi.AF_TANH), capi.fc(5, capi.AF_LINEAR)]
+    return workloads.Workload(name, capi.net(ls, 6, T=T, loss=capi.LOSS_MSE, accuracy=capi.ACC_DISTANCE, time_delays=1, **({"momentum": 0.9} if norm else {})),
+                              capi.opt(capi.OPT_GD, gd_lr=lr, momentum=0.9), 7, 5, False, ls)
+
+
+CASES.update({
+    "ind_rnn_relu": lambda: _ind_rnn_case("indrnn", capi.AF_RELU),
+    "ind_rnn_tanh_stacked_dropout": lambda: _ind_rnn_case("indrnn2", capi.AF_TANH, dropout=capi.DROP_BERNOULLI_INVERTED, stacked=True),
+    "ind_rnn_batch_norm": lambda: _ind_rnn_case("indrnn_bn", capi.AF_TANH, norm=capi.NORM_BN),
+    # a large step pushes recurrent weights against their bound +-2^(1/T) (the layer's weight constraint)
+    "ind_rnn_relu_weights_at_bound": lambda: _ind_rnn_case("indrnn_clip", capi.AF_RELU, T=3, lr=1.5),
+})
+
+
 def _lstm_blocks_case(name, opt, cpb, T=4, B=5, n_in=7, blocks=(4, 3), out=12, zoneout=0.3, delays=1):
     """LSTM blocks of `cpb` cells each (the cells of a block share its gates); the output layer is at least as wide as
     the last LSTM layer has cells, as the reference's shifted bias base requires"""
