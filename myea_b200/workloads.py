@@ -137,10 +137,10 @@ def _mlp_flops(widths, B):
     return f
 
 
-def c1_mlp(scale=1.0):
+def c1_mlp(scale=1.0, batch=None):
     """config 1: MLP 64-256-256-10, tanh / softmax, cross-entropy, batch 128, Adam"""
     w = [_s(64, scale), _s(256, scale), _s(256, scale), 10]
-    B = _s(128, scale)
+    B = batch or _s(128, scale)
     layers = [capi.fc(w[0]), capi.fc(w[1], capi.AF_TANH), capi.fc(w[2], capi.AF_TANH), capi.fc(w[3], capi.AF_SOFTMAX)]
     wl = Workload("C1 MLP 64-256-256-10", capi.net(layers, B, loss=capi.LOSS_CE, accuracy=capi.ACC_CE), capi.opt(capi.OPT_ADAM),
                   w[0], w[3], True, layers)
