@@ -41,6 +41,7 @@ extern "C" {
 #define MYEA_LAYER_MAX_POOLING 9u     /* the same five values */
 #define MYEA_LAYER_RESIDUAL 10u
 /* ENUM_TYPE_NETWORKS (Enum_Type_Networks.hpp:25) */
+#define MYEA_NETWORK_AUTOENCODER 1u
 #define MYEA_NETWORK_FEEDFORWARD 3u
 #define MYEA_NETWORK_RECURRENT 4u
 /* ENUM_TYPE_ACTIVATION_FUNCTION (Enum_Type_Activation_Functions.hpp:25) */
@@ -287,6 +288,14 @@ const char *myea_b200_checkpoint_last_error(void);
  * (Neural_Network__Forward_Pass__OpenMP.cpp:5021-5056, Neural_Network__Backward_Pass__OpenMP.cpp:1009-1042). */
 int myea_b200_set_shakedrop(myea_handle h, uint32_t layer, const uint8_t *mask, const float *alpha, const float *beta,
                             uint64_t batch);
+
+/* bool Set__Pre_Training_Level(size_t) (Neural_Network__Indexing.cpp:20-51): 0 = the whole network (default); k >= 1 = the step
+ * functions train hidden layer k and its mirror image, layer number_layers - k, as one autoencoder pair: layers before k
+ * encode in inference behaviour, the decoded layer reads the coded layer's output and is compared with what the coded
+ * layer read (at level 1: the targets passed to compute_error, normally the inputs).  The decoded layer's answer is
+ * read with myea_b200_get_outputs(h, number_layers - k, ...).  Feed-forward networks of plain fully connected layers,
+ * no normalization on the two layers of the pair, no communicator. */
+int myea_b200_set_pre_training_level(myea_handle h, uint64_t level);
 
 /* void Forward_Pass(size_t B, T_ const *const *X, …) (Data.hpp:2896). X is the packed [T][B][inputs] block the
  * host class gathers from the reference's row pointers; host memory. training: type_state_propagation (Data.hpp:3048).

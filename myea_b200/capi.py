@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(HERE, "libmyea_b200.so")
 MAX_LAYERS = 64
 
 # enumerators (values of the reference's enums, see include/myea_b200.h)
+NET_AUTOENCODER = 1
 LAYER_FC, LAYER_LSTM, LAYER_RESIDUAL = 4, 8, 10
 LAYER_AVERAGE_POOLING, LAYER_MAX_POOLING = 1, 9
 LAYER_FC_IND_RNN = 5
@@ -176,6 +177,7 @@ _LIB = None
 _PROTOS = {
     "myea_b200_create": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(NetDesc), C.c_int]),
     "myea_b200_destroy": (None, [C.c_void_p]),
+    "myea_b200_set_pre_training_level": (C.c_int, [C.c_void_p, C.c_uint64]),
     "myea_b200_last_error": (C.c_char_p, [C.c_void_p]),
     "myea_b200_sizes": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_uint64)] * 4),
     "myea_b200_layer_index": (C.c_int, [C.c_void_p, C.c_uint32, C.POINTER(LayerIndex)]),

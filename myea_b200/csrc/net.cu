@@ -591,6 +591,10 @@ static NormParams norm_at_step(const LayerPlan &L, long long t) {
 }
 
 int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long rows) {
+  // normalization with batch statistics / dropout with masks: as the network's state says, unless a pre-training pass
+  // runs this layer in another role (LayerPlan::mode_norm, mode_drop)
+  const bool norm_train = L.mode_norm < 0 ? net->training : L.mode_norm != 0;
+  const bool drop_train = L.mode_drop < 0 ? net->training : L.mode_drop != 0;
   Epilogue e;
   e.C = L.summations;
   e.ldc = L.n_out;
@@ -598,7 +602,7 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
   // batch statistics: the contraction's epilogue leaves the column sums of every 32-row block behind, where it can
   int fused_chunks = 0;
   const bool timewise_norm = (L.has_norm && net->T > 1) || L.ind_rnn;  // a recurrent network normalizes every time step by itself
-  if (L.has_norm && net->training && !timewise_norm) {
+  if (L.has_norm && norm_train && !timewise_norm) {
     Epilogue probe = e;
     probe.stats_kind = 1;
     probe.col_stats = L.norm.partial;
@@ -628,15 +632,15 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
     // a normalized layer, then pre = z' + u * y_prev and the activation
     if (L.desc.type_activation_function == MYEA_AF_SOFTMAX) return MYEA_E_UNSUPPORTED;
     const long long pitch = rows / net->T;
-    const uint8_t *mask = (net->training && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
-    const float scale = net->training ? (mask != nullptr ? L.keep_scale : 1.f) : L.infer_scale;
+    const uint8_t *mask = (drop_train && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
+    const float scale = drop_train ? (mask != nullptr ? L.keep_scale : 1.f) : L.infer_scale;
     const float *u = net->params + L.idx.first_connection_index + static_cast<uint64_t>(L.n_out) * L.n_in;
     for (long long t = 0; t < net->T; ++t) {
       const long long off = t * pitch * L.n_out;
       const float *cs = nullptr, *ch = nullptr;
       if (L.has_norm) {
         const NormParams np = norm_at_step(L, t);
-        RC(norm_forward_stats(net->ctx, L.summations + off, net->active_B, L.n_out, np, net->training ? 1 : 0, &net->hook, nullptr, 0));
+        RC(norm_forward_stats(net->ctx, L.summations + off, net->active_B, L.n_out, np, norm_train ? 1 : 0, &net->hook, nullptr, 0));
         cs = np.col_scale; ch = np.col_shift;
       }
       RC(ind_rnn_forward_step(net->ctx, L.summations + off, t > 0 ? L.values + off - pitch * L.n_out : nullptr, u, L.pre_af + off, L.values + off, pitch,
@@ -650,12 +654,12 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
     // Neural_Network__Forward_Pass__Loop.cpp:4673-4750)
     if (L.desc.type_activation_function == MYEA_AF_SOFTMAX) return MYEA_E_UNSUPPORTED;
     const long long pitch = rows / net->T;
-    const uint8_t *mask = (net->training && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
-    const float scale = net->training ? (mask != nullptr ? L.keep_scale : 1.f) : L.infer_scale;
+    const uint8_t *mask = (drop_train && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
+    const float scale = drop_train ? (mask != nullptr ? L.keep_scale : 1.f) : L.infer_scale;
     for (long long t = 0; t < net->T; ++t) {
       const NormParams np = norm_at_step(L, t);
       const long long off = t * pitch * L.n_out;
-      RC(norm_forward_stats(net->ctx, L.summations + off, net->active_B, L.n_out, np, net->training ? 1 : 0, &net->hook, nullptr, 0));
+      RC(norm_forward_stats(net->ctx, L.summations + off, net->active_B, L.n_out, np, norm_train ? 1 : 0, &net->hook, nullptr, 0));
       RC(activation_forward(net->ctx, L.summations + off, L.values + off, pitch, L.n_out, L.desc.type_activation_function, np.col_scale, np.col_shift,
                             mask != nullptr ? mask + t * L.n_out : nullptr, scale, nullptr));
     }
@@ -673,7 +677,7 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
     OverlapWork work;
     work.arg = &next;
     work.run = [](void *arg) { Next *p = static_cast<Next *>(arg); return fc_prepare_weights(p->net, *p->layer); };
-    RC(norm_forward_stats(net->ctx, L.summations, rows, L.n_out, L.norm, net->training ? 1 : 0, &net->hook, next.layer != nullptr ? &work : nullptr,
+    RC(norm_forward_stats(net->ctx, L.summations, rows, L.n_out, L.norm, norm_train ? 1 : 0, &net->hook, next.layer != nullptr ? &work : nullptr,
                           fused_chunks));
     cs = L.norm.col_scale;
     ch = L.norm.col_shift;
@@ -682,8 +686,8 @@ int fc_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long r
     if (L.has_norm) return MYEA_E_UNSUPPORTED;
     return softmax_forward(net->ctx, L.summations, L.values, rows, L.n_out);
   }
-  const uint8_t *mask = (net->training && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
-  const float scale = net->training ? (mask != nullptr ? L.keep_scale : 1.f) : L.infer_scale;
+  const uint8_t *mask = (drop_train && L.mask_bernoulli != nullptr) ? L.mask_bernoulli : nullptr;
+  const float scale = drop_train ? (mask != nullptr ? L.keep_scale : 1.f) : L.infer_scale;
   if (mask != nullptr && net->T > 1) {
     // a recurrent network draws one mask per time step (mask[t][unit], Forward_Pass__Dropout__Bernoulli__Training__Loop,
     // Neural_Network__Forward_Pass__Loop.cpp:4947-4970): one activation pass per step, each with its own mask row
@@ -736,6 +740,64 @@ static int batch_in_flight(myea_b200_net *net, uint64_t batch) {
   return MYEA_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Autoencoder pre-training (Set__Pre_Training_Level, Neural_Network__Indexing.cpp:20-51): at level k >= 1 only hidden
+// layer k (the "coded" layer) and its mirror image, layer n - k (the "decoded" layer), are trained: the layers before k
+// encode the input in inference behaviour (the one feeding layer k with its training dropout), layer k and layer n - k
+// run in training behaviour with dropout reduced to its inference scaling, the decoded layer reads the coded layer's
+// output, and its output is compared with what the coded layer read (the targets of the call at level 1)
+// (FF__Forward_Pass_Batch__Pre_Training, …Forward_Pass__Loop.cpp:205-326; FF__Compute__Error :120;
+// FF__Backward_Pass_Batch__Pre_Training, …Backward_Pass__Loop.cpp:211-296; FF__Update_Derivative_Weight_Batch__Pre_Training,
+// …Update_Derivative_Weight__Loop.cpp:135-182).
+// ---------------------------------------------------------------------------------------------------------
+static int pre_training_layers(myea_b200_net *net, int *coded, int *decoded) {
+  const int n = static_cast<int>(net->layers.size()), k = static_cast<int>(net->pre_training_level);
+  *coded = k;
+  *decoded = n - k;
+  return MYEA_OK;
+}
+
+extern "C" int myea_b200_set_pre_training_level(myea_handle net, uint64_t level) {
+  if (net == nullptr) return MYEA_E_INVALID;
+  const uint64_t n = net->layers.size();
+  if (level == 0) { net->pre_training_level = 0; return MYEA_OK; }
+  if (n < 3 || level > (n - 3) / 2 + 1) return fail(net, MYEA_E_INVALID, "pre-training level above the number of layer pairs");
+  if (net->T != 1 || net->comm != nullptr) return fail(net, MYEA_E_UNSUPPORTED, "pre-training of recurrent or data-parallel networks is not built");
+  const LayerPlan &K = net->layers[level], &D = net->layers[n - level];
+  for (uint64_t l = 1; l <= level; ++l)
+    if (net->layers[l].type != MYEA_LAYER_FULLY_CONNECTED || net->layers[l].ind_rnn || layer_in_block(net, static_cast<int>(l), nullptr))
+      return fail(net, MYEA_E_UNSUPPORTED, "pre-training is built for plain fully connected layers");
+  if (D.type != MYEA_LAYER_FULLY_CONNECTED || D.ind_rnn || layer_in_block(net, static_cast<int>(n - level), nullptr))
+    return fail(net, MYEA_E_UNSUPPORTED, "pre-training is built for plain fully connected layers");
+  if (D.n_in != K.n_out || D.n_out != K.n_in) return fail(net, MYEA_E_INVALID, "the decoded layer is not the mirror image of the coded layer");
+  if (K.has_norm || D.has_norm) return fail(net, MYEA_E_UNSUPPORTED, "normalization on the coded or decoded layer is not built");
+  if (D.desc.type_activation_function == MYEA_AF_SOFTMAX && n - level != n - 1) return fail(net, MYEA_E_INVALID, "softmax on a hidden layer");
+  net->pre_training_level = static_cast<uint32_t>(level);
+  return MYEA_OK;
+}
+
+static int forward_pre_training(myea_b200_net *net, long long rows) {
+  int k = 0, dl = 0;
+  RC(pre_training_layers(net, &k, &dl));
+  for (int l = 1; l < k; ++l) {  // encode: inference behaviour; the layer feeding the coded layer keeps its training dropout
+    LayerPlan &L = net->layers[l];
+    L.mode_norm = 0;
+    L.mode_drop = (l == k - 1 && net->training) ? 1 : 0;
+    const int rc = fc_forward(net, L, net->layers[L.input_layer].values, rows);
+    L.mode_norm = L.mode_drop = -1;
+    RC(rc);
+  }
+  LayerPlan &K = net->layers[k], &D = net->layers[dl];
+  K.mode_drop = 0;  // (coded dropout is a flag this library does not carry: the layer scales as at inference)
+  int rc = fc_forward(net, K, net->layers[K.input_layer].values, rows);
+  K.mode_drop = -1;
+  RC(rc);
+  D.mode_drop = 0;
+  rc = fc_forward(net, D, K.values, rows);
+  D.mode_drop = -1;
+  return rc;
+}
+
 static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cudaMemcpyKind kind, int training) {
   if (net == nullptr || src == nullptr) return MYEA_E_INVALID;
   RC(batch_for_forward(net, batch));
@@ -760,6 +822,7 @@ static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cu
   } else {
     RC(copy_batch_in(net, net->d_input, src, net->layers[0].n_out, kind, net->ctx.stream));
   }
+  if (net->pre_training_level != 0) return forward_pre_training(net, rows);
   for (int l = 1; l < n;) {
     LayerPlan &L = net->layers[l];
     const LayerPlan &in = net->layers[L.input_layer];
@@ -795,6 +858,24 @@ static int compute_error_impl(myea_b200_net *net, uint64_t batch, const float *s
   if (net == nullptr || src == nullptr) return MYEA_E_INVALID;
   RC(batch_in_flight(net, batch));
   CK(cudaSetDevice(net->ctx.device));
+  if (net->pre_training_level != 0) {
+    // the decoded layer answers as the output layer; above level 1 it is compared with what the coded layer read
+    int k = 0, dl = 0;
+    RC(pre_training_layers(net, &k, &dl));
+    LayerPlan &D = net->layers[dl];
+    const long long rows = step_rows_total(net);
+    const float *desired = net->layers[k - 1].values;
+    if (k <= 1) {
+      CK(cudaStreamWaitEvent(net->ctx.stream, net->ev_desired_free, 0));
+      CK(cudaMemcpyAsync(net->d_desired, src, rows * D.n_out * sizeof(float), kind, net->ctx.stream));
+      desired = net->d_desired;
+    }
+    RC(output_error(net->ctx, D.summations, D.values, desired, D.errors, rows, D.n_out, D.desc.type_activation_function, net->desc.type_loss_function,
+                    net->desc.type_accuracy_function, net->desc.accuracy_variance > 0.f ? net->desc.accuracy_variance : 0.49f, net->d_loss_acc,
+                    net->d_loss_count));
+    CK(cudaEventRecord(net->ev_desired_free, net->ctx.stream));
+    return MYEA_OK;
+  }
   LayerPlan &L = net->layers.back();
   const long long pitch = pitch_rows(net), rows = net->T * pitch;
   if (kind == cudaMemcpyHostToDevice) {
@@ -941,6 +1022,13 @@ extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
   CK(cudaSetDevice(net->ctx.device));
   const long long rows = step_rows_total(net);
   const int n = static_cast<int>(net->layers.size());
+  if (net->pre_training_level != 0) {  // the decoded layer's error reaches the coded layer and stops there
+    int k = 0, dl = 0;
+    RC(pre_training_layers(net, &k, &dl));
+    LayerPlan &K = net->layers[k], &D = net->layers[dl];
+    RC(fc_backward_from_fc(net, K, D, D.errors, rows, K.deriv, true));
+    return fc_finish_backward(net, K, rows);
+  }
   // `l` is a layer whose error is complete; send it to the layer feeding it, finish that layer, move down
   int l = n - 1;
   while (l >= 1) {
@@ -1072,6 +1160,13 @@ extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batc
   // Reduce-scatter instead of all-reduce where the update is element by element: not under a global-norm clip (the norm
   // needs every element) or the max-norm constraint (whole rows), which the description announces
   comm_set_scatter(net, net->comm != nullptr && net->sharded_update);
+  if (net->pre_training_level != 0) {  // the two layers of the pair only
+    int k = 0, dl = 0;
+    RC(pre_training_layers(net, &k, &dl));
+    LayerPlan &K = net->layers[k], &D = net->layers[dl];
+    RC(fc_update_derivative_weight(net, D, K.values, rows));
+    return fc_update_derivative_weight(net, K, net->layers[K.input_layer].values, rows);
+  }
   // last layer first: its bucket is complete first, and its all-reduce overlaps the contractions of the layers below
   for (int l = static_cast<int>(net->layers.size()) - 1; l >= 1; --l) {
     LayerPlan &L = net->layers[l];

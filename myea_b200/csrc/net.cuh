@@ -52,6 +52,9 @@ struct LayerPlan {
   int *pool_winner = nullptr;     // max pooling: [T*B, n_out] position (in the padded input) that gave each output
   // independently recurrent fully connected layer (type FULLY_CONNECTED here, ind_rnn set): n_out recurrent weights
   // behind the layer's n_out * n_in weights; pre_af = summation (normalized) + u * previous output, what the activation sees
+  // roles of an autoencoder pre-training pass: -1 = as the network's state says, 0 = inference behaviour (running
+  // statistics / dropout scaling), 1 = training behaviour (batch statistics / dropout masks)
+  int mode_norm = -1, mode_drop = -1;
   bool ind_rnn = false;
   float *pre_af = nullptr;        // [T*B, n_out]
 };
@@ -113,6 +116,7 @@ struct myea_b200_net {
   float optimizer_time_step = 0.f;
   float nosadam_previous_beta2 = 0.f;  // adam_previous_beta2 (Data.hpp:2953)
   bool training = true;
+  uint32_t pre_training_level = 0;  // 0: the whole network; k >= 1: hidden layer k and its mirror image are trained as an autoencoder
   myea::CommState *comm = nullptr;
   myea::SumHook hook;            // cross-GPU sum of normalization column sums (world 1: unused)
   bool grads_reduced = false;    // this step's derivative buckets have already been handed to the communicator

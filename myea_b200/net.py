@@ -106,6 +106,10 @@ class Net:
         o = np.ascontiguousarray(output, dtype=np.uint8).ravel()
         self._ck(self.lib.myea_b200_set_mask_zoneout(self.h, layer, s.ctypes.data, o.ctypes.data, s.size), "set_mask_zoneout")
 
+    def set_pre_training_level(self, level):
+        """0 = the whole network; k >= 1 = train hidden layer k and its mirror image as one autoencoder pair"""
+        self._ck(self.lib.myea_b200_set_pre_training_level(self.h, int(level)), "set_pre_training_level")
+
     def set_shakedrop(self, layer, mask, alpha, beta):
         m = np.ascontiguousarray(mask, dtype=np.uint8).ravel()
         a, b = _f32(alpha), _f32(beta)

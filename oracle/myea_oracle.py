@@ -521,9 +521,10 @@ class OracleNet:
         else:
             y = af_fire(af, pre)
         drop = int(L.d.type_dropout)
+        drop_training = self.training if getattr(self, "_drop_training", None) is None else self._drop_training
         if drop in (capi.DROP_BERNOULLI, capi.DROP_BERNOULLI_INVERTED):
             p = dt(L.d.dropout_values[0])
-            if self.training:
+            if drop_training:
                 # one mask row per time step (…Forward_Pass__Loop.cpp:4947-4970); rows of y are time-major
                 m = np.repeat(np.asarray(self.masks[l]).reshape(-1, y.shape[1])[:max(1, y.shape[0] // self.active_B)], self.active_B, axis=0)
                 y = np.where(m, y * (dt(1) / p) if drop == capi.DROP_BERNOULLI_INVERTED else y, dt(0))
@@ -533,12 +534,36 @@ class OracleNet:
         return L.values
 
     # ---- step functions ------------------------------------------------------------------------------------------
+    def set_pre_training_level(self, level):
+        """Set__Pre_Training_Level (Neural_Network__Indexing.cpp:20-51): 0 = the whole network, k >= 1 = hidden layer k and its
+        mirror image n - k are trained as one autoencoder pair"""
+        self.pre_training_level = int(level)
+
+    def _forward_pre_training(self):
+        """FF__Forward_Pass_Batch__Pre_Training__Loop (Neural_Network__Forward_Pass__Loop.cpp:205-326): layers before the
+        coded one in inference behaviour (Forward_Pass__Encode__FC :794-1018; the layer feeding the coded layer keeps its
+        training dropout), the coded layer (:1020-1479) and the decoded layer (:1481-) in training behaviour with dropout
+        reduced to its inference scaling; the decoded layer reads the coded layer's output"""
+        k, n = self.pre_training_level, len(self.layers)
+        state = self.training
+        for l in range(1, k):
+            self.training = False
+            self._drop_training = state and l == k - 1
+            self._fc_forward(l, self.layers[self.layers[l].input_layer].values)
+        self.training = state
+        self._drop_training = False
+        self._fc_forward(k, self.layers[self.layers[k].input_layer].values)
+        self._fc_forward(n - k, self.layers[k].values)
+        self._drop_training = None
+
     def forward(self, X, training=True, batch=None):
         self.training = training
         self.active_B = int(batch or self.B)   # Forward_Pass(batch_size_received, ...): any batch up to the allocated one (T = 1)
         X = np.asarray(X, self.dt).reshape(self.T * self.active_B, -1)
         self.layers[0].values = X
         n = len(self.layers)
+        if getattr(self, "pre_training_level", 0):
+            return self._forward_pre_training()
         l = 1
         while l < n:
             L = self.layers[l]
@@ -564,6 +589,11 @@ class OracleNet:
         before number_time_delays are not scored and get zero error."""
         dt = self.dt
         L = self.layers[-1]
+        k = getattr(self, "pre_training_level", 0)
+        if k:   # the decoded layer answers; above level 1 it is compared with what the coded layer read (FF__Compute__Error :120)
+            L = self.layers[len(self.layers) - k]
+            if k > 1:
+                Y = self.layers[k - 1].values
         Y = np.asarray(Y, dt).reshape(self.T * getattr(self, "active_B", self.B), -1)
         t0 = min(int(self.desc.number_time_delays), self.T) if self.T > 1 else 0
         skip = t0 * getattr(self, "active_B", self.B)
@@ -596,6 +626,11 @@ class OracleNet:
         """FF__Backward_Pass_Batch (Neural_Network__Backward_Pass__Loop.cpp:80-209): error to the previous layer
         (:1079-1114), activation derivative (:1259-1294), normalization backward."""
         n = len(self.layers)
+        k = getattr(self, "pre_training_level", 0)
+        if k:   # FF__Backward_Pass_Batch__Pre_Training__Loop (…Backward_Pass__Loop.cpp:211-296): decoded -> coded layer, no further
+            K, D = self.layers[k], self.layers[n - k]
+            K.errors = (D.errors @ self._fc_weights(D)) * af_derive(int(K.d.type_activation_function), K.pre, K.values)
+            return
         l = n - 1
         while l >= 1:
             N = self.layers[l]
@@ -628,11 +663,15 @@ class OracleNet:
     def update_derivative_weight(self):
         """Update_Derivative_Weight__FC + bias (Neural_Network__Update_Derivative_Weight__Loop.cpp): sums over the batch,
         never divided by the batch size."""
-        for l in range(1, len(self.layers)):
+        k = getattr(self, "pre_training_level", 0)
+        trained = (k, len(self.layers) - k) if k else range(1, len(self.layers))
+        for l in trained:
             L = self.layers[l]
             if L.type == capi.LAYER_FC:
                 x = getattr(L, "dw_input", None)
-                if x is None:
+                if k and l == len(self.layers) - k:   # the decoded layer read the coded layer's output
+                    x = self.layers[k].values
+                elif x is None:
                     x = self.layers[L.input_layer].values
                 i = L.idx
                 self._g()[i["first_connection_index"]:i["first_connection_index"] + L.n_out * L.n_in] += (L.errors.T @ x).ravel()

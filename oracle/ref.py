@@ -37,6 +37,7 @@ def _lib(double=False):
         lib.ref_buffer.restype = C.POINTER(scalar)
         lib.ref_buffer.argtypes = [C.c_void_p, C.c_int]
         lib.ref_set_mask_bernoulli.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64]
+        lib.ref_set_pre_training_level.argtypes = [C.c_void_p, C.c_uint64]
         lib.ref_set_mask_zoneout.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint64]
         lib.ref_set_training.argtypes = [C.c_void_p, C.c_int]
         lib.ref_load_batch.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]
@@ -192,6 +193,10 @@ class RefNet:
         if self.lib.ref_get_errors(self.h, layer, self.B, out.ctypes.data) != 0:
             raise RuntimeError("layer %d has no error buffer" % layer)
         return out
+
+    def set_pre_training_level(self, level):
+        if self.lib.ref_set_pre_training_level(self.h, int(level)) != 0:
+            raise RuntimeError("Set__Pre_Training_Level(%d) failed" % level)
 
     def next_shakedrop(self):
         """{residual layer: (mask[B], alpha[B, width], beta[B, width])} the reference will draw in its NEXT training step"""

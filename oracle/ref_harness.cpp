@@ -167,6 +167,12 @@ void *ref_create(const myea_net_desc *d, const myea_opt_desc *opt, int threads) 
 
 void ref_destroy(void *h) { delete static_cast<RefNet *>(h); }
 
+// Set__Pre_Training_Level (Neural_Network__Indexing.cpp:20-51): 0 = the whole network, k >= 1 = train the k-th layer pair
+// of an autoencoder (hidden layer k and its mirror image)
+int ref_set_pre_training_level(void *h, uint64_t level) {
+  return static_cast<RefNet *>(h)->nn.Set__Pre_Training_Level(level) ? 0 : -1;
+}
+
 // bytes of the reference's scalar type in this build: 4 (float) or 8 (COMPILE_DOUBLE); buffers, outputs and errors
 // cross this interface in that type, inputs and targets always arrive as float
 int ref_scalar_bytes(void) { return static_cast<int>(sizeof(T_)); }

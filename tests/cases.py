@@ -155,6 +155,39 @@ CASES.update({
 })
 
 
+def autoencoder_case(dropout=capi.DROP_NONE):
+    """a five-layer autoencoder 10-7-4-7-10 for the pre-training passes (levels 1 and 2), optional dropout on the first
+    hidden layer (the one that feeds the coded layer at level 2)"""
+    ls = [capi.fc(10), capi.fc(7, capi.AF_TANH, dropout=dropout, p=(0.8, 0.0, 0.0)), capi.fc(4, capi.AF_TANH), capi.fc(7, capi.AF_ELU),
+          capi.fc(10, capi.AF_LINEAR)]
+    d = capi.net(ls, 8, loss=capi.LOSS_MSE, accuracy=capi.ACC_DISTANCE)
+    d.type_network = capi.NET_AUTOENCODER
+    return workloads.Workload("autoencoder", d, capi.opt(capi.OPT_GD, gd_lr=0.05, momentum=0.9), 10, 10, False, ls)
+
+
+def run_pre_training(net, wl, levels=(1, 2, 0), steps=2):
+    """the training sequence at every pre-training level in turn (targets = inputs): derivatives, loss, the answering
+    layer's outputs and the updated parameters of every step"""
+    X, _ = wl.batch()
+    wl.materialize(net)
+    n = len(wl.layers)
+    out = {}
+    for level in levels:
+        net.set_pre_training_level(level)
+        for it in range(steps):
+            net.reset_loss()
+            net.forward(X); net.compute_error(X); net.backward(); net.update_derivative_weight()
+            key = "level%d_step%d_" % (level, it)
+            out[key + "grad"] = net.get(capi.BUF_DERIVATIVES)
+            s_, n_, a_ = net.loss()
+            out[key + "loss"] = [s_, float(n_), a_]
+            out[key + "output"] = net.outputs(n - level if level else n - 1)
+            net.update_parameter()
+            out[key + "param"] = net.get(capi.BUF_PARAMETERS)
+    net.set_pre_training_level(0)
+    return out
+
+
 def _ind_rnn_case(name, af, norm=capi.NORM_NONE, dropout=capi.DROP_NONE, T=4, stacked=False, lr=0.01):
     """independently recurrent fully connected layers (Ind-RNN): y_t = f(W x_t + b + u * y_{t-1})"""
     ls = [capi.fc(7), capi.fc_ind_rnn(9, af, norm=norm, dropout=dropout, p=(0.8, 0.0, 0.0))]

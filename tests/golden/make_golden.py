@@ -2,6 +2,7 @@
 oracle/build_ref.sh from the reference checkout) on every case of tests/cases.py.  Run from the repository root:
 
     python tests/golden/make_golden.py [case ...]
+    python tests/golden/make_golden.py --pre-training      (the autoencoder pre-training fixtures)
 
 The fixtures hold the reference's derivatives, losses, updated parameters, first moments, running normalization
 statistics, last-layer outputs, index map and sizes in float32 / float64 / int64; inputs are regenerated from seeds by
@@ -26,7 +27,25 @@ def input_checksum(wl, net):
     return np.array([float(np.abs(X).sum(dtype=np.float64)), float(np.abs(Y).sum(dtype=np.float64)), float(np.abs(p).sum(dtype=np.float64))])
 
 
+PRE_TRAINING = {"autoencoder_pre_training": cases.capi.DROP_NONE, "autoencoder_pre_training_dropout": cases.capi.DROP_BERNOULLI_INVERTED}
+
+
+def pre_training():
+    """tests/golden/autoencoder_pre_training*.npz: the pre-training levels 1, 2 and the whole network, two steps each"""
+    for name, drop in PRE_TRAINING.items():
+        wl = cases.autoencoder_case(drop)
+        net = ref.RefNet(wl.desc, wl.opt, threads=1)
+        out = cases.run_pre_training(net, wl)
+        net.close()
+        arrays = {k: np.asarray(v, np.float64 if k.endswith("loss") else np.float32) for k, v in out.items()}
+        path = os.path.join(ROOT, "tests", "golden", name + ".npz")
+        np.savez_compressed(path, **arrays)
+        print("%-32s %6.1f KiB" % (name, os.path.getsize(path) / 1024.0))
+
+
 def main():
+    if sys.argv[1:] == ["--pre-training"]:
+        return pre_training()
     names = sys.argv[1:] or sorted(cases.CASES)
     for name in names:
         wl = cases.CASES[name]()

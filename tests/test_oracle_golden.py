@@ -41,6 +41,21 @@ def test_oracle_matches_golden(name, golden_dir):
         assert rel_err(out["norm_sigma_avg"], gold["norm_sigma_avg"]) < TOL
 
 
+@pytest.mark.parametrize("name,dropout", [("autoencoder_pre_training", cases.capi.DROP_NONE),
+                                          ("autoencoder_pre_training_dropout", cases.capi.DROP_BERNOULLI_INVERTED)])
+def test_oracle_pre_training_matches_golden(name, dropout, golden_dir):
+    """autoencoder pre-training: levels 1 and 2, then the whole network, against the reference's vectors"""
+    gold = _load(golden_dir, name)
+    wl = cases.autoencoder_case(dropout)
+    out = cases.run_pre_training(myea_oracle.OracleNet(wl.desc, wl.opt), wl)
+    assert sorted(out) == sorted(gold.files)
+    for k in gold.files:
+        if k.endswith("loss"):
+            assert abs(out[k][0] - gold[k][0]) <= 1e-4 * abs(gold[k][0]) + 1e-6 and out[k][1] == gold[k][1] and out[k][2] == gold[k][2], k
+        else:
+            assert rel_err(out[k], gold[k]) < TOL, k
+
+
 @pytest.mark.parametrize("name", sorted(cases.CASES))
 def test_golden_inputs_unchanged(name, golden_dir):
     """the seeded inputs the fixtures were generated from are still what the workload builders produce"""

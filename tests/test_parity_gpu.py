@@ -81,6 +81,22 @@ def test_activations_without_a_derivative_run_forward(af):
     gpu.close()
 
 
+@pytest.mark.parametrize("dropout", [capi.DROP_NONE, capi.DROP_BERNOULLI_INVERTED, capi.DROP_BERNOULLI])
+def test_autoencoder_pre_training_matches_the_reference(dropout):
+    """Set__Pre_Training_Level 1, 2 and back to 0 on a 10-7-4-7-10 autoencoder, two steps each: derivatives, losses, the
+    answering layer's outputs and the updated parameters against the compiled reference (the restatement without it)"""
+    wl = cases.autoencoder_case(dropout)
+    gpu, cpu = Net(wl.desc, wl.opt), _oracle(wl)
+    out, want = cases.run_pre_training(gpu, wl), cases.run_pre_training(cpu, wl)
+    assert gpu.launches() > 0
+    for k in want:
+        if k.endswith("loss"):
+            assert abs(out[k][0] - want[k][0]) <= 1e-4 * abs(want[k][0]) + 1e-6 and out[k][1] == want[k][1] and out[k][2] == want[k][2], k
+        else:
+            assert rel_err(out[k], want[k]) < TOL, (k, rel_err(out[k], want[k]))
+    gpu.close(); cpu.close()
+
+
 @pytest.mark.parametrize("name", sorted(cases.CASES_WITHOUT_REFERENCE))
 def test_step_matches_restatement_where_the_reference_cannot_serve(name):
     """bidirectional LSTM, and normalized layers beside LSTM layers (the reference crashes while it builds such a network):
