@@ -58,6 +58,14 @@ class Neural_Network {
   bool Set__Normalization_Epsilon(float v) { desc_.normalization_epsilon = v; return v > 0.f; }
   bool Set__Batch_Renormalization_r_Correction_Maximum(float v) { desc_.batch_renormalization_r_correction_maximum = v; return v >= 1.f; }
   bool Set__Batch_Renormalization_d_Correction_Maximum(float v) { desc_.batch_renormalization_d_correction_maximum = v; return v >= 0.f; }
+  // autoencoder pre-training (Neural_Network__Indexing.cpp:20-51): 0 = the whole network; needs the device network
+  bool Set__Pre_Training_Level(size_t pre_training_level) {
+    if (!is_device_initialized) return fail("Set__Pre_Training_Level", MYEA_E_INVALID);
+    int const rc = myea_b200_set_pre_training_level(ptr_device_Neural_Network, pre_training_level);
+    if (rc == MYEA_OK) this->pre_training_level = pre_training_level;
+    return rc == MYEA_OK ? true : fail("Set__Pre_Training_Level", rc);
+  }
+  size_t pre_training_level = 0;
   bool Update__Batch_Size(size_t desired_batch_size, bool force_update = false);
   void Clear_Training_Arrays(void);
 
