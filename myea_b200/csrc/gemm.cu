@@ -648,6 +648,17 @@ struct WideSegments {
     if (u < u_end) {
       const int ts = u / num_chunks;
       c0 = u - ts * num_chunks;
+      if (c0 + (u_end - u) > num_chunks) {
+        // The run crosses into the next tile (a run is shorter than a tile, so it touches two at most): the head of
+        // the next tile goes first and the end of this tile after it.  Every cluster then walks K upwards from chunk 0
+        // at the same time as the clusters on the neighbouring tiles, which read the same operand panels, and the
+        // panels are fetched from DRAM once instead of once per tile.
+        tile = dp_tiles + ts + 1;
+        c0 = 0;
+        c1 = u_end - (ts + 1) * num_chunks;
+        u_end = (ts + 1) * num_chunks;
+        return true;
+      }
       c1 = min(num_chunks, c0 + (u_end - u));
       tile = dp_tiles + ts;
       u += c1 - c0;

@@ -64,7 +64,7 @@ def test_every_tile_shape(tile, shape):
     assert _gemm(*shape, engine=tile) < 2e-5
 
 
-@pytest.mark.parametrize("shape", [(300, 520, 4096), (1024, 512, 2048), (2048, 1024, 1024), (640, 896, 8200)])
+@pytest.mark.parametrize("shape", [(300, 520, 4096), (1024, 512, 2048), (2048, 1024, 1024), (640, 896, 8200), (2048, 2048, 8192)])
 def test_tiles_split_along_k_are_exact_and_repeatable(shape):
     """fewer tiles than SM pairs: the 256 x 256 kernel cuts the K chunks of the tiles into equal runs (stream-K); the
     partial sums are added in a fixed order, so two runs agree bit for bit"""
