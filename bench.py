@@ -257,7 +257,8 @@ def dp_check(torch, dist, world, rank, local, timed_job):
     got = small.net.get(capi.BUF_PARAMETERS)
     out = {"parameter_spread_across_ranks": spread,
            # whether the batch-norm column sums travel through the library's own peer-memory exchange kernel (1) or NCCL (0)
-           "peer_memory_sums": int(C.CDLL(capi.LIB_PATH).myea_b200_comm_peer_sums(timed_job.net.h))}
+           "peer_memory_sums": int(C.CDLL(capi.LIB_PATH).myea_b200_comm_peer_sums(timed_job.net.h)),
+           "peer_memory_copies": int(C.CDLL(capi.LIB_PATH).myea_b200_comm_peer_copies(timed_job.net.h))}
     if rank == 0:
         from myea_b200 import workloads
         from myea_b200.net import Net

@@ -333,7 +333,9 @@ int myea_b200_get_errors(myea_handle h, uint32_t layer, float *host, uint64_t co
  * With a communicator every rank runs the step on its rows of the batch; update_derivative_weight hands each layer's
  * derivatives to the communicator (reduce-scatter where the range divides evenly over the ranks and the update is
  * element by element, else all-reduce), update_parameter updates this rank's slices and gathers the updated parameters,
- * so that all ranks hold identical parameters afterwards.  The optimizer state (moments, previous deltas) of a slice
+ * so that all ranks hold identical parameters afterwards (where the ranks can map each other's memory, slices and
+ * updated parameters travel as peer copies with arrival words instead of library collectives; a forward pass waits
+ * for a layer's parameters only where it reads them).  The optimizer state (moments, previous deltas) of a slice
  * lives on the rank that owns it: myea_b200_download of such a buffer gathers the slices first and is therefore
  * COLLECTIVE - every rank has to make the call. */
 int myea_b200_comm_unique_id(uint8_t id_out[128]);

@@ -140,8 +140,73 @@ __global__ void __launch_bounds__(256) peer_sum_kernel(float *__restrict__ data,
   }
 }
 
+// Derivative buckets and updated parameters over peer memory, moved by the copy engines.  The library's reduce-scatter
+// and all-gather run as kernels; beside the persistent contraction kernels, which hold every SM, those kernels start
+// late and push contraction CTAs off their SMs, so neither side gets the overlap.  Copies between peer-mapped buffers
+// need no SM at all.  Per bucket of n floats and rank r (count = n / world):
+//   sum:    every rank copies, for each peer p, its derivative slice p into p's staging area (slot of the sender),
+//           then sets p's arrival word; rank p waits for world - 1 words and adds the slots to its own slice in rank order
+//           (the same order on every rank's slice, whoever arrives first);
+//   gather: after the update every rank copies its parameter slice into every peer's parameter buffer and sets the
+//           peers' arrival words; a reader of the parameters waits for the words of the buckets it reads.
+// The staging area of a bucket is the bucket's own index range in a buffer as long as the parameter buffer; words carry
+// the step number, so nothing is ever reset.  A rank cannot run ahead by a step: its next push of a bucket comes after
+// its forward pass has waited for every peer's gather of that bucket, which the peer issues after it has added the slots.
+constexpr int PEER_MAX_BUCKETS = 256;
+struct PeerCopy {
+  bool ready = false;
+  float *stage = nullptr;                      // [total_parameters] receive area for derivative slices
+  unsigned int *flags = nullptr;               // [2 kinds][PEER_MAX_BUCKETS][PEER_MAX_WORLD] arrival words
+  void *params[PEER_MAX_WORLD] = {};           // every rank's parameter buffer, staging area and words in this address space
+  void *stages[PEER_MAX_WORLD] = {};
+  void *words[PEER_MAX_WORLD] = {};
+  unsigned int **words_d = nullptr;            // `words` on the device
+  unsigned int epoch = 0;                      // steps that issued buckets so far; the same on every rank
+};
+__host__ __device__ inline size_t peer_word(int kind, size_t bucket, int source) {
+  return (static_cast<size_t>(kind) * PEER_MAX_BUCKETS + bucket) * PEER_MAX_WORLD + static_cast<size_t>(source);
+}
+
+// tells every peer that this rank's copies of (kind, bucket) are in its memory (same stream as the copies, behind them)
+__global__ void peer_signal_kernel(unsigned int *const *__restrict__ words, int kind, size_t bucket, int rank, int world, unsigned int epoch) {
+  const int r = static_cast<int>(threadIdx.x);
+  if (r >= world || r == rank) return;
+  __threadfence_system();
+  unsigned int *theirs = words[r] + peer_word(kind, bucket, rank);
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+}
+// waits (bounded) until every peer's copies of (kind, bucket) of step `epoch` are in this rank's memory
+__global__ void peer_wait_kernel(const unsigned int *__restrict__ mine, int kind, size_t bucket, int rank, int world, unsigned int epoch, int *error_flag) {
+  const int r = static_cast<int>(threadIdx.x);
+  if (r >= world || r == rank) return;
+  const unsigned int *word = mine + peer_word(kind, bucket, r);
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned int seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(word) : "memory");
+    if (static_cast<int>(seen - epoch) >= 0) return;
+    if (clock64() - t0 > (1ll << 36)) {
+      atomicCAS(error_flag, 0, 502 + kind);
+      return;
+    }
+    __nanosleep(200);
+  }
+}
+// slice[i] = sum over ranks in rank order of (r == rank ? slice[i] : slot of r), float4 at a time
+__global__ void __launch_bounds__(256) peer_slices_sum_kernel(float4 *__restrict__ slice, const float4 *__restrict__ slots, size_t count4, int rank, int world) {
+  for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < count4; i += static_cast<size_t>(gridDim.x) * 256) {
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4 v = r == rank ? slice[i] : __ldcs(slots + static_cast<size_t>(r < rank ? r : r - 1) * count4 + i);
+      t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+    }
+    slice[i] = t;
+  }
+}
+
 struct CommState {
   PeerSum peer;
+  PeerCopy copy;
   ncclComm_t comm = nullptr;
   int world = 1, rank = 0;
   cudaStream_t stream = nullptr;   // bucket all-reduces run here, beside the compute stream
@@ -155,12 +220,17 @@ struct CommState {
     bool scattered = false;          // reduce-scattered: only [offset + rank * n / world, + n / world) holds the sum
     cudaEvent_t reduced = nullptr;   // comm -> compute: the sum (or this rank's slice of it) has arrived
     cudaEvent_t updated = nullptr;   // compute -> comm: the optimizer has updated this rank's slice of the parameters
+    cudaEvent_t gathered = nullptr;  // comm -> compute: every rank's slice of the updated parameters has landed
+    bool gather_open = false;        // the gather was issued and the compute stream has not been told to wait for it yet
+    bool by_copies = false;          // moved by peer copies and arrival words instead of the library's collectives
+    size_t index = 0;                // position in this step's issue order (names the arrival words)
+    unsigned int epoch = 0;          // the step whose words it waits for
   };
   std::vector<Bucket> buckets;     // the ranges issued this step, each with the event that says its sum has arrived
   size_t used = 0;
   bool scatter = false;            // this step's buckets may be reduce-scattered (set by update_derivative_weight's caller)
   std::vector<std::pair<size_t, size_t>> last_scattered;  // (offset, n) of the buckets the last update handled in slices
-  cudaEvent_t gathered = nullptr;  // comm -> compute: every all-gather issued so far has completed
+  bool gathers_open = false;       // some bucket's gather_open is set
 };
 
 static int nccl_fail(myea_b200_net *net, ncclResult_t r, const char *what) {
@@ -206,18 +276,33 @@ int comm_all_reduce_sum_f64(myea_b200_net *net, double *buf, size_t n) {
   return r == ncclSuccess ? MYEA_OK : nccl_fail(net, r, "ncclAllReduce");
 }
 
+int comm_gather_join(myea_b200_net *net);
+
 // Hands the derivative range [offset, offset + n) to the communication stream: it is summed over ranks while the compute
 // stream carries on with the next layer.  Every rank issues the same buckets in the same order.
 int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n) {
   CommState *c = net->comm;
   if (c == nullptr || n == 0) return MYEA_OK;
   NcclApi *api = nccl_api();
+  if (comm_gather_join(net) != MYEA_OK) return MYEA_E_CUDA;  // the bucket records are about to be reused
   if (cudaEventRecord(c->ready, net->ctx.stream) != cudaSuccess || cudaStreamWaitEvent(c->stream, c->ready, 0) != cudaSuccess) return MYEA_E_CUDA;
   // a slice starts on a 16-byte boundary (the update kernel reads float4) and all slices are equal
   const size_t w = static_cast<size_t>(c->world);
   const bool scattered = c->scatter && (n % (4 * w)) == 0 && (offset % 4) == 0;
-  ncclResult_t r;
-  if (scattered) {
+  if (c->used == 0) ++c->copy.epoch;
+  const bool by_copies = scattered && c->copy.ready && c->used < static_cast<size_t>(PEER_MAX_BUCKETS);
+  ncclResult_t r = ncclSuccess;
+  if (by_copies) {
+    const size_t count = n / w;
+    for (int p = 0; p < c->world; ++p) {
+      if (p == c->rank) continue;
+      float *dst = static_cast<float *>(c->copy.stages[p]) + offset + static_cast<size_t>(c->rank < p ? c->rank : c->rank - 1) * count;
+      if (cudaMemcpyAsync(dst, net->grads + offset + static_cast<size_t>(p) * count, count * sizeof(float), cudaMemcpyDeviceToDevice, c->stream) != cudaSuccess)
+        return MYEA_E_CUDA;
+    }
+    peer_signal_kernel<<<1, 32, 0, c->stream>>>(c->copy.words_d, 0, c->used, c->rank, c->world, c->copy.epoch);
+    if (cudaGetLastError() != cudaSuccess) return MYEA_E_CUDA;
+  } else if (scattered) {
     const size_t count = n / w;
     r = api->ReduceScatter(net->grads + offset, net->grads + offset + static_cast<size_t>(c->rank) * count, count, ncclFloat, ncclSum, c->comm, c->stream);
   } else {
@@ -227,7 +312,8 @@ int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n) {
   if (c->used == c->buckets.size()) {
     CommState::Bucket b;
     if (cudaEventCreateWithFlags(&b.reduced, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&b.updated, cudaEventDisableTiming) != cudaSuccess)
+        cudaEventCreateWithFlags(&b.updated, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&b.gathered, cudaEventDisableTiming) != cudaSuccess)
       return MYEA_E_CUDA;
     c->buckets.push_back(b);
   }
@@ -235,6 +321,9 @@ int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n) {
   b.offset = offset;
   b.n = n;
   b.scattered = scattered;
+  b.by_copies = by_copies;
+  b.index = c->used - 1;
+  b.epoch = c->copy.epoch;
   if (cudaEventRecord(b.reduced, c->stream) != cudaSuccess) return MYEA_E_CUDA;
   c->pending = true;
   net->ctx.launches += 1;
@@ -274,6 +363,20 @@ int comm_join(myea_b200_net *net) {
   return MYEA_OK;
 }
 
+// A bucket that travelled by peer copies: once every peer's slot has arrived, this rank's slice becomes the sum.
+static int add_peer_slots(myea_b200_net *net, const CommState::Bucket &b) {
+  CommState *c = net->comm;
+  const size_t count = b.n / static_cast<size_t>(c->world), count4 = count / 4;
+  net->ctx.begin(TC_COMM);
+  peer_wait_kernel<<<1, 32, 0, net->ctx.stream>>>(c->copy.flags, 0, b.index, c->rank, c->world, b.epoch, net->ctx.d_error_flag);
+  const unsigned blocks = static_cast<unsigned>(std::max<size_t>(1, std::min<size_t>((count4 + 255) / 256, 148 * 8)));
+  peer_slices_sum_kernel<<<blocks, 256, 0, net->ctx.stream>>>(reinterpret_cast<float4 *>(net->grads + b.offset + static_cast<size_t>(c->rank) * count),
+                                                              reinterpret_cast<const float4 *>(c->copy.stage + b.offset), count4, c->rank, c->world);
+  net->ctx.end(TC_COMM);
+  net->ctx.launches += 2;
+  return cudaGetLastError() == cudaSuccess ? MYEA_OK : MYEA_E_CUDA;
+}
+
 // The ranges handed to the communicator this step, in the order their sums arrive.
 size_t comm_bucket_count(const myea_b200_net *net) { return net->comm != nullptr ? net->comm->used : 0; }
 // Makes the compute stream wait for bucket i only and says which range it covers; for a reduce-scattered bucket
@@ -282,21 +385,23 @@ int comm_bucket_wait(myea_b200_net *net, size_t i, size_t *offset, size_t *n, si
   CommState *c = net->comm;
   if (c == nullptr || i >= c->used) return MYEA_E_INVALID;
   const CommState::Bucket &b = c->buckets[i];
-  if (cudaStreamWaitEvent(net->ctx.stream, b.reduced, 0) != cudaSuccess) return MYEA_E_CUDA;
+  if (cudaStreamWaitEvent(net->ctx.stream, b.reduced, 0) != cudaSuccess) return MYEA_E_CUDA;  // by copies: this rank's slices have left
   *offset = b.offset;
   *n = b.n;
   const size_t count = b.scattered ? b.n / static_cast<size_t>(c->world) : b.n;
+  if (b.by_copies && add_peer_slots(net, b) != MYEA_OK) return MYEA_E_CUDA;
   *slice_offset = b.scattered ? b.offset + static_cast<size_t>(c->rank) * count : b.offset;
   *slice_n = count;
   return MYEA_OK;
 }
 // After the optimizer has updated this rank's slice of bucket i (queued on the compute stream): the slices of all ranks
 // are gathered into every rank's parameter buffer on the communication stream.  A bucket that was all-reduced needs
-// nothing.  The derivative slices of the OTHER ranks are cleared here (the optimizer clears its own).
+// nothing.  The derivative slices of the OTHER ranks are cleared here (the optimizer clears its own).  Nobody waits for
+// the gather here: whoever reads the parameters next asks with comm_wait_gathers (one range) or comm_gather_join (all).
 int comm_bucket_gather(myea_b200_net *net, size_t i) {
   CommState *c = net->comm;
   if (c == nullptr || i >= c->used) return MYEA_E_INVALID;
-  const CommState::Bucket &b = c->buckets[i];
+  CommState::Bucket &b = c->buckets[i];
   if (!b.scattered) return MYEA_OK;
   NcclApi *api = nccl_api();
   const size_t count = b.n / static_cast<size_t>(c->world), mine = static_cast<size_t>(c->rank) * count;
@@ -305,8 +410,22 @@ int comm_bucket_gather(myea_b200_net *net, size_t i) {
       cudaMemsetAsync(net->grads + b.offset + mine + count, 0, (b.n - mine - count) * sizeof(float), net->ctx.stream) != cudaSuccess)
     return MYEA_E_CUDA;
   if (cudaEventRecord(b.updated, net->ctx.stream) != cudaSuccess || cudaStreamWaitEvent(c->stream, b.updated, 0) != cudaSuccess) return MYEA_E_CUDA;
-  ncclResult_t r = api->AllGather(net->params + b.offset + mine, net->params + b.offset, count, ncclFloat, c->comm, c->stream);
-  if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllGather (bucket)");
+  if (b.by_copies) {
+    for (int p = 0; p < c->world; ++p) {
+      if (p == c->rank) continue;
+      if (cudaMemcpyAsync(static_cast<float *>(c->copy.params[p]) + b.offset + mine, net->params + b.offset + mine, count * sizeof(float),
+                          cudaMemcpyDeviceToDevice, c->stream) != cudaSuccess)
+        return MYEA_E_CUDA;
+    }
+    peer_signal_kernel<<<1, 32, 0, c->stream>>>(c->copy.words_d, 1, b.index, c->rank, c->world, b.epoch);
+    if (cudaGetLastError() != cudaSuccess) return MYEA_E_CUDA;
+  } else {
+    ncclResult_t r = api->AllGather(net->params + b.offset + mine, net->params + b.offset, count, ncclFloat, c->comm, c->stream);
+    if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllGather (bucket)");
+  }
+  if (cudaEventRecord(b.gathered, c->stream) != cudaSuccess) return MYEA_E_CUDA;
+  b.gather_open = true;
+  c->gathers_open = true;
   net->ctx.launches += 1;
   net->ctx.class_launches[TC_COMM] += 1;
   return MYEA_OK;
@@ -321,6 +440,12 @@ int comm_unscatter(myea_b200_net *net) {
     CommState::Bucket &b = c->buckets[i];
     if (!b.scattered) continue;
     const size_t count = b.n / static_cast<size_t>(c->world), mine = static_cast<size_t>(c->rank) * count;
+    if (b.by_copies) {  // the slots are added on the compute stream first
+      if (cudaStreamWaitEvent(net->ctx.stream, b.reduced, 0) != cudaSuccess || add_peer_slots(net, b) != MYEA_OK ||
+          cudaEventRecord(c->ready, net->ctx.stream) != cudaSuccess || cudaStreamWaitEvent(c->stream, c->ready, 0) != cudaSuccess)
+        return MYEA_E_CUDA;
+      b.by_copies = false;
+    }
     ncclResult_t r = api->AllGather(net->grads + b.offset + mine, net->grads + b.offset, count, ncclFloat, c->comm, c->stream);
     if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllGather (derivative slices)");
     if (cudaEventRecord(b.reduced, c->stream) != cudaSuccess) return MYEA_E_CUDA;
@@ -329,11 +454,45 @@ int comm_unscatter(myea_b200_net *net) {
   c->pending = true;
   return MYEA_OK;
 }
+// the compute stream waits until every rank's slice of the bucket's updated parameters is in this rank's buffer
+static int gather_wait(myea_b200_net *net, const CommState::Bucket &b) {
+  CommState *c = net->comm;
+  if (cudaStreamWaitEvent(net->ctx.stream, b.gathered, 0) != cudaSuccess) return MYEA_E_CUDA;  // by copies: this rank's slice has left
+  if (b.by_copies) {
+    peer_wait_kernel<<<1, 32, 0, net->ctx.stream>>>(c->copy.flags, 1, b.index, c->rank, c->world, b.epoch, net->ctx.d_error_flag);
+    if (cudaGetLastError() != cudaSuccess) return MYEA_E_CUDA;
+    net->ctx.launches += 1;
+  }
+  return MYEA_OK;
+}
+// Makes the compute stream wait for the gathers of the buckets that overlap the parameter range [offset, offset + n):
+// the forward pass asks layer by layer, so the gathers of the upper layers travel while the lower layers compute.
+int comm_wait_gathers(myea_b200_net *net, size_t offset, size_t n) {
+  CommState *c = net->comm;
+  if (c == nullptr || !c->gathers_open) return MYEA_OK;
+  bool any = false;
+  for (auto &b : c->buckets) {
+    if (!b.gather_open) continue;
+    if (b.offset < offset + n && offset < b.offset + b.n) {
+      if (gather_wait(net, b) != MYEA_OK) return MYEA_E_CUDA;
+      b.gather_open = false;
+    } else {
+      any = true;
+    }
+  }
+  c->gathers_open = any;
+  return MYEA_OK;
+}
 // Makes the compute stream wait until every gather issued so far has landed.
 int comm_gather_join(myea_b200_net *net) {
   CommState *c = net->comm;
-  if (c == nullptr) return MYEA_OK;
-  if (cudaEventRecord(c->gathered, c->stream) != cudaSuccess || cudaStreamWaitEvent(net->ctx.stream, c->gathered, 0) != cudaSuccess) return MYEA_E_CUDA;
+  if (c == nullptr || !c->gathers_open) return MYEA_OK;
+  for (auto &b : c->buckets) {
+    if (!b.gather_open) continue;
+    if (gather_wait(net, b) != MYEA_OK) return MYEA_E_CUDA;
+    b.gather_open = false;
+  }
+  c->gathers_open = false;
   return MYEA_OK;
 }
 // Whether the buckets issued from now on may be reduce-scattered (the caller knows if the update needs whole buffers).
@@ -374,45 +533,36 @@ size_t &comm_reduced_weights(myea_b200_net *net) {
   return net->comm != nullptr ? net->comm->reduced_weights : none;
 }
 
-// Sets the peer-memory exchange up: one allocation per rank, mapped by all ranks through CUDA IPC (the handles travel in
-// an all-gather).  Any failure leaves it off; the small sums then use the library's all-reduce.
-static void peer_setup(myea_b200_net *net) {
-  CommState *c = net->comm;
+// Maps one allocation of every rank into this process (CUDA IPC; the handles travel in an all-gather).  Every rank takes
+// part in the gather even when its own side failed (a zero handle marks the failure); false when anything failed on
+// this rank.
+static bool ipc_map_all(CommState *c, void *local, bool local_ok, void **mapped) {
   NcclApi *api = nccl_api();
-  PeerSum &p = c->peer;
-  if (c->world > PEER_MAX_WORLD) return;
-  long long widest = 0;
-  for (const auto &L : net->layers)
-    if (L.has_norm) widest = std::max(widest, L.n_out);
-  if (widest == 0) return;
-  p.capacity = static_cast<size_t>(2 * widest + 3) & ~static_cast<size_t>(3);
-  const size_t bytes = static_cast<size_t>(2) * c->world * p.capacity * sizeof(float) + static_cast<size_t>(2) * c->world * PEER_MAX_BLOCKS * sizeof(unsigned int);
   unsigned char *stage = nullptr;
   std::vector<cudaIpcMemHandle_t> handles(c->world);
-  bool ok = cudaMalloc(&p.local, bytes) == cudaSuccess && cudaMemset(p.local, 0, bytes) == cudaSuccess &&
-            cudaMalloc(&stage, c->world * sizeof(cudaIpcMemHandle_t)) == cudaSuccess;
-  cudaIpcMemHandle_t mine;
-  ok = ok && cudaIpcGetMemHandle(&mine, p.local) == cudaSuccess &&
-       cudaMemcpy(stage + c->rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice) == cudaSuccess;
-  // every rank takes part in the gather even when its own set-up failed (a zero handle then marks the failure)
-  if (!ok && stage != nullptr) cudaMemset(stage + c->rank * sizeof(mine), 0, sizeof(mine));
-  bool gathered = stage != nullptr &&
-                  api->AllGather(stage + c->rank * sizeof(mine), stage, sizeof(mine), ncclChar, c->comm, c->stream) == ncclSuccess &&
-                  cudaStreamSynchronize(c->stream) == cudaSuccess &&
-                  cudaMemcpy(handles.data(), stage, c->world * sizeof(mine), cudaMemcpyDeviceToHost) == cudaSuccess;
+  cudaIpcMemHandle_t mine = {};
+  bool ok = local_ok && local != nullptr && cudaIpcGetMemHandle(&mine, local) == cudaSuccess;
+  if (!ok) memset(&mine, 0, sizeof(mine));
+  const bool staged = cudaMalloc(&stage, c->world * sizeof(mine)) == cudaSuccess &&
+                      cudaMemcpy(stage + c->rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice) == cudaSuccess;
+  const bool gathered = staged && api->AllGather(stage + c->rank * sizeof(mine), stage, sizeof(mine), ncclChar, c->comm, c->stream) == ncclSuccess &&
+                        cudaStreamSynchronize(c->stream) == cudaSuccess &&
+                        cudaMemcpy(handles.data(), stage, c->world * sizeof(mine), cudaMemcpyDeviceToHost) == cudaSuccess;
   if (stage != nullptr) cudaFree(stage);
   ok = ok && gathered;
   const cudaIpcMemHandle_t zero = {};
   for (int r = 0; ok && r < c->world; ++r)
     if (memcmp(&handles[r], &zero, sizeof(zero)) == 0) ok = false;
   for (int r = 0; ok && r < c->world; ++r) {
-    if (r == c->rank) { p.mapped[r] = p.local; continue; }
-    if (cudaIpcOpenMemHandle(&p.mapped[r], handles[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { p.mapped[r] = nullptr; ok = false; }
+    if (r == c->rank) { mapped[r] = local; continue; }
+    if (cudaIpcOpenMemHandle(&mapped[r], handles[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { mapped[r] = nullptr; ok = false; }
   }
-  ok = ok && cudaMalloc(&p.mapped_d, c->world * sizeof(float *)) == cudaSuccess &&
-       cudaMemcpy(p.mapped_d, p.mapped, c->world * sizeof(float *), cudaMemcpyHostToDevice) == cudaSuccess;
   cudaGetLastError();
-  // all ranks use it or none does: a rank that failed would otherwise wait for arrivals that never come
+  return ok;
+}
+// all ranks use a peer-memory path or none does: a rank that failed would otherwise wait for arrivals that never come
+static bool all_ranks_agree(CommState *c, bool ok) {
+  NcclApi *api = nccl_api();
   int *flag = nullptr;
   int all = 0;
   if (cudaMalloc(&flag, sizeof(int)) == cudaSuccess) {
@@ -422,22 +572,77 @@ static void peer_setup(myea_b200_net *net) {
       cudaMemcpy(&all, flag, sizeof(int), cudaMemcpyDeviceToHost);
     cudaFree(flag);
   }
-  p.ready = ok && all == 1;
+  cudaGetLastError();
+  return ok && all == 1;
+}
+
+// Sets the peer-memory paths up.  Any failure leaves a path off; the library's collectives then do its work.
+static void peer_setup(myea_b200_net *net) {
+  CommState *c = net->comm;
+  if (c->world > PEER_MAX_WORLD) return;
+  {  // the small sums of the normalization layers: [2 parities][world slots][capacity] floats + arrival words
+    PeerSum &p = c->peer;
+    long long widest = 0;
+    for (const auto &L : net->layers)
+      if (L.has_norm) widest = std::max(widest, L.n_out);
+    p.capacity = static_cast<size_t>(2 * std::max<long long>(widest, 1) + 3) & ~static_cast<size_t>(3);
+    const size_t bytes = static_cast<size_t>(2) * c->world * p.capacity * sizeof(float) + static_cast<size_t>(2) * c->world * PEER_MAX_BLOCKS * sizeof(unsigned int);
+    bool ok = cudaMalloc(&p.local, bytes) == cudaSuccess && cudaMemset(p.local, 0, bytes) == cudaSuccess;
+    ok = ipc_map_all(c, p.local, ok, p.mapped);
+    ok = ok && cudaMalloc(&p.mapped_d, c->world * sizeof(float *)) == cudaSuccess &&
+         cudaMemcpy(p.mapped_d, p.mapped, c->world * sizeof(float *), cudaMemcpyHostToDevice) == cudaSuccess;
+    p.ready = all_ranks_agree(c, ok);
+  }
+  {  // derivative buckets and updated parameters by peer copies
+    PeerCopy &q = c->copy;
+    const size_t floats = net->total_parameters + 4;
+    const size_t words = static_cast<size_t>(2) * PEER_MAX_BUCKETS * PEER_MAX_WORLD;
+    bool ok = cudaMalloc(&q.stage, floats * sizeof(float)) == cudaSuccess && cudaMalloc(&q.flags, words * sizeof(unsigned int)) == cudaSuccess &&
+              cudaMemset(q.flags, 0, words * sizeof(unsigned int)) == cudaSuccess && cudaDeviceSynchronize() == cudaSuccess;
+    const bool a = ipc_map_all(c, net->params, ok, q.params);
+    const bool b = ipc_map_all(c, q.stage, ok, q.stages);
+    const bool d = ipc_map_all(c, q.flags, ok, q.words);
+    ok = ok && a && b && d;
+    ok = ok && cudaMalloc(&q.words_d, c->world * sizeof(unsigned int *)) == cudaSuccess &&
+         cudaMemcpy(q.words_d, q.words, c->world * sizeof(unsigned int *), cudaMemcpyHostToDevice) == cudaSuccess;
+    q.ready = all_ranks_agree(c, ok);
+  }
+  cudaGetLastError();
 }
 
 static void peer_teardown(CommState *c) {
   PeerSum &p = c->peer;
-  for (int r = 0; r < c->world && r < PEER_MAX_WORLD; ++r)
-    if (r != c->rank && p.mapped[r] != nullptr) cudaIpcCloseMemHandle(p.mapped[r]);
+  PeerCopy &q = c->copy;
+  for (int r = 0; r < c->world && r < PEER_MAX_WORLD; ++r) {
+    if (r == c->rank) continue;
+    if (p.mapped[r] != nullptr) cudaIpcCloseMemHandle(p.mapped[r]);
+    if (q.params[r] != nullptr) cudaIpcCloseMemHandle(q.params[r]);
+    if (q.stages[r] != nullptr) cudaIpcCloseMemHandle(q.stages[r]);
+    if (q.words[r] != nullptr) cudaIpcCloseMemHandle(q.words[r]);
+  }
   if (p.mapped_d != nullptr) cudaFree(p.mapped_d);
   if (p.local != nullptr) cudaFree(p.local);
+  if (q.words_d != nullptr) cudaFree(q.words_d);
+  if (q.stage != nullptr) cudaFree(q.stage);
+  if (q.flags != nullptr) cudaFree(q.flags);
   p = PeerSum();
+  q = PeerCopy();
 }
 
 void comm_destroy(myea_b200_net *net) {
   if (net->comm == nullptr) return;
   NcclApi *api = nccl_api();
+  // Peers may still be copying into this rank's buffers: slices of a step whose update was never asked for, parameters
+  // of the last update.  Their arrival words are waited for (bounded) before anything is unmapped or freed.
+  CommState *c = net->comm;
+  for (size_t i = 0; i < c->used; ++i) {
+    const CommState::Bucket &b = c->buckets[i];
+    if (b.by_copies) peer_wait_kernel<<<1, 32, 0, net->ctx.stream>>>(c->copy.flags, 0, b.index, c->rank, c->world, b.epoch, net->ctx.d_error_flag);
+  }
+  comm_gather_join(net);
+  if (net->ctx.stream) cudaStreamSynchronize(net->ctx.stream);
   if (net->comm->stream) cudaStreamSynchronize(net->comm->stream);
+  cudaGetLastError();
   peer_teardown(net->comm);
   if (api && net->comm->comm) api->CommDestroy(net->comm->comm);
   if (net->comm->ready) cudaEventDestroy(net->comm->ready);
@@ -446,8 +651,8 @@ void comm_destroy(myea_b200_net *net) {
   for (auto &b : net->comm->buckets) {
     if (b.reduced) cudaEventDestroy(b.reduced);
     if (b.updated) cudaEventDestroy(b.updated);
+    if (b.gathered) cudaEventDestroy(b.gathered);
   }
-  if (net->comm->gathered) cudaEventDestroy(net->comm->gathered);
   if (net->comm->stream) cudaStreamDestroy(net->comm->stream);
   delete net->comm;
   net->comm = nullptr;
@@ -485,14 +690,12 @@ extern "C" int myea_b200_comm_init(myea_handle net, int world, int rank, const u
   if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->ready, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming) != cudaSuccess ||
-      cudaEventCreateWithFlags(&c->side_done, cudaEventDisableTiming) != cudaSuccess ||
-      cudaEventCreateWithFlags(&c->gathered, cudaEventDisableTiming) != cudaSuccess) {
+      cudaEventCreateWithFlags(&c->side_done, cudaEventDisableTiming) != cudaSuccess) {
     api->CommDestroy(c->comm);
     if (c->stream) cudaStreamDestroy(c->stream);
     if (c->ready) cudaEventDestroy(c->ready);
     if (c->done) cudaEventDestroy(c->done);
     if (c->side_done) cudaEventDestroy(c->side_done);
-    if (c->gathered) cudaEventDestroy(c->gathered);
     delete c;
     net->ctx.error = "stream / event creation failed";
     return MYEA_E_CUDA;
@@ -510,3 +713,5 @@ extern "C" int myea_b200_comm_init(myea_handle net, int world, int rank, const u
 // Diagnostic (not part of the training interface): 1 when the small cross-rank sums of this handle go through the
 // peer-memory exchange kernel, 0 when they use the library's all-reduce.
 extern "C" int myea_b200_comm_peer_sums(myea_handle net) { return (net != nullptr && net->comm != nullptr && net->comm->peer.ready) ? 1 : 0; }
+// 1 when derivative buckets and updated parameters travel by peer copies, 0 when the library's collectives move them
+extern "C" int myea_b200_comm_peer_copies(myea_handle net) { return (net != nullptr && net->comm != nullptr && net->comm->copy.ready) ? 1 : 0; }

@@ -28,6 +28,7 @@ size_t comm_bucket_count(const myea_b200_net *net);
 int comm_bucket_wait(myea_b200_net *net, size_t i, size_t *offset, size_t *n, size_t *slice_offset, size_t *slice_n);
 int comm_bucket_gather(myea_b200_net *net, size_t i);
 int comm_gather_join(myea_b200_net *net);
+int comm_wait_gathers(myea_b200_net *net, size_t offset, size_t n);
 void comm_set_scatter(myea_b200_net *net, bool on);
 bool comm_any_scattered(const myea_b200_net *net);
 int comm_gather_state(myea_b200_net *net, float *buf);
@@ -473,6 +474,7 @@ extern "C" int myea_b200_upload(myea_handle net, int which, const float *host, u
   float *dst = select_buffer(net, which, &n);
   if (dst == nullptr || offset > n || count > n - offset) return fail(net, MYEA_E_INVALID, "upload: buffer selector or range out of bounds");
   CK(cudaSetDevice(net->ctx.device));
+  RC(comm_gather_join(net));
   CK(cudaMemcpyAsync(dst + offset, host, count * sizeof(float), cudaMemcpyHostToDevice, net->ctx.stream));
   CK(cudaStreamSynchronize(net->ctx.stream));
   if (dst == net->params) {
@@ -489,6 +491,7 @@ extern "C" int myea_b200_download(myea_handle net, int which, float *host, uint6
   CK(cudaSetDevice(net->ctx.device));
   // under a sharded update every rank keeps the optimizer state of its slices only: reading such a buffer back gathers
   // the slices first (collective: every rank has to make the call)
+  RC(comm_gather_join(net));
   if (net->comm != nullptr && (src == net->m1 || src == net->m2 || src == net->m2hat || src == net->prev_delta)) RC(comm_gather_state(net, src));
   CK(cudaMemcpyAsync(host, src + offset, count * sizeof(float), cudaMemcpyDeviceToHost, net->ctx.stream));
   CK(cudaStreamSynchronize(net->ctx.stream));
@@ -540,6 +543,7 @@ static bool fc_uses_shared_panels(const myea_b200_net *net, const LayerPlan &L, 
 // while the inputs are still on their way (see forward_impl).
 static int fc_prepare_weights(myea_b200_net *net, LayerPlan &L) {
   const bool tr = net->training;
+  RC(comm_wait_gathers(net, L.idx.first_connection_index, L.idx.last_connection_index - L.idx.first_connection_index));
   RC(gemm_prepare_shared(net->ctx, net->params + L.idx.first_connection_index, L.n_in, L.n_out, L.n_in, L.w_panel_mem, PANEL_ROLE_B, &L.w_rows,
                          PANEL_ROLE_B, tr ? &L.w_cols : nullptr));
   L.w_prepared = true;
@@ -548,6 +552,8 @@ static int fc_prepare_weights(myea_b200_net *net, LayerPlan &L) {
 
 int fc_product_forward(myea_b200_net *net, LayerPlan &L, const float *input, long long rows, const Epilogue &e) {
   const float *w = net->params + L.idx.first_connection_index;
+  // the other ranks' slices of this layer's updated weights (a sharded update gathers them layer by layer)
+  RC(comm_wait_gathers(net, L.idx.first_connection_index, L.idx.last_connection_index - L.idx.first_connection_index));
   if (fc_uses_shared_panels(net, L, rows)) {
     // while training, the same pass also writes the column readings the backward contractions will want
     const bool tr = net->training;
@@ -807,6 +813,10 @@ static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cu
   const long long rows = step_rows_total(net);
   const int n = static_cast<int>(net->layers.size());
   for (auto &L : net->layers) { L.w_prepared = false; L.in_ready_src = nullptr; }
+  // After a sharded update the gathers of the updated parameters may still be travelling.  Biases and normalization
+  // parameters are waited for here, every fully connected layer's weights where the layer first reads them, and
+  // everything that is left before any other kind of layer.
+  RC(comm_wait_gathers(net, net->total_weights, net->total_parameters - net->total_weights));
   if (kind == cudaMemcpyHostToDevice) {
     // inputs from the host: copy them on the side stream (once everything already queued has finished with d_input)
     // and split every large layer's weights meanwhile - the copy takes longer than all those passes together
@@ -822,10 +832,14 @@ static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cu
   } else {
     RC(copy_batch_in(net, net->d_input, src, net->layers[0].n_out, kind, net->ctx.stream));
   }
-  if (net->pre_training_level != 0) return forward_pre_training(net, rows);
+  if (net->pre_training_level != 0) {
+    RC(comm_gather_join(net));
+    return forward_pre_training(net, rows);
+  }
   for (int l = 1; l < n;) {
     LayerPlan &L = net->layers[l];
     const LayerPlan &in = net->layers[L.input_layer];
+    if (L.type != MYEA_LAYER_FULLY_CONNECTED || L.ind_rnn) RC(comm_gather_join(net));
     if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
       if (layer_in_block(net, l, nullptr)) return fail(net, MYEA_E_INVALID, "block layer outside its block");
       RC(fc_forward(net, L, in.values, rows));
@@ -841,7 +855,7 @@ static int forward_impl(myea_b200_net *net, uint64_t batch, const float *src, cu
       l += L.block_depth + 1;
     }
   }
-  return MYEA_OK;
+  return comm_gather_join(net);
 }
 
 extern "C" int myea_b200_forward(myea_handle net, uint64_t batch, const float *inputs, int training) {
@@ -1020,6 +1034,7 @@ extern "C" int myea_b200_backward(myea_handle net, uint64_t batch) {
   RC(batch_in_flight(net, batch));
   if (!net->training) return fail(net, MYEA_E_INVALID, "can not back propagate in inference mode");
   CK(cudaSetDevice(net->ctx.device));
+  RC(comm_gather_join(net));
   const long long rows = step_rows_total(net);
   const int n = static_cast<int>(net->layers.size());
   if (net->pre_training_level != 0) {  // the decoded layer's error reaches the coded layer and stops there
@@ -1167,8 +1182,13 @@ extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batc
     RC(fc_update_derivative_weight(net, D, K.values, rows));
     return fc_update_derivative_weight(net, K, net->layers[K.input_layer].values, rows);
   }
-  // last layer first: its bucket is complete first, and its all-reduce overlaps the contractions of the layers below
-  for (int l = static_cast<int>(net->layers.size()) - 1; l >= 1; --l) {
+  // Every layer's error is known by now, so the order is free.  One GPU: last layer first.  Data parallel: FIRST layer
+  // first - its bucket is then the first to be summed, updated and gathered, and the next forward pass, which waits
+  // for each layer's gather only where it reads that layer, finds the lower layers' parameters in place while the
+  // upper layers' are still travelling.
+  const int n_layers = static_cast<int>(net->layers.size());
+  for (int step = 1; step < n_layers; ++step) {
+    const int l = net->comm != nullptr ? step : n_layers - step;
     LayerPlan &L = net->layers[l];
     if (L.type == MYEA_LAYER_FULLY_CONNECTED) {
       const float *input = net->layers[L.input_layer].values;
@@ -1203,6 +1223,7 @@ extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batc
 extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint64_t training_size, const myea_opt_desc *opt) {
   if (net == nullptr || opt == nullptr || training_size == 0) return MYEA_E_INVALID;
   CK(cudaSetDevice(net->ctx.device));
+  RC(comm_gather_join(net));
   const size_t P = net->total_parameters;
   // Without a global-norm clip the update is element by element, so each derivative bucket can be applied as soon as
   // ITS sum over the ranks has arrived, while the later (lower-layer) buckets are still on the wire - and only on this
@@ -1282,7 +1303,10 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
   if (by_bucket) {
     const size_t count = comm_bucket_count(net);
     size_t covered = 0;
-    for (size_t i = 0; i < count; ++i) {
+    // the bucket of the biases and normalization parameters was issued last but is gathered first: the next forward
+    // pass reads it before anything else
+    for (size_t k = 0; k < count; ++k) {
+      const size_t i = k == 0 ? count - 1 : k - 1;
       size_t bucket_off = 0, n = 0, off = 0, slice = 0;
       RC(comm_bucket_wait(net, i, &bucket_off, &n, &off, &slice));
       if ((off & 3) != 0) return fail(net, MYEA_E_INVALID, "derivative bucket does not start on a 16-byte boundary");
@@ -1291,8 +1315,7 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
       RC(comm_bucket_gather(net, i));  // the other ranks' slices of the updated parameters (nothing for an all-reduced bucket)
       covered += n;
     }
-    RC(comm_gather_join(net));
-    comm_buckets_done(net);
+    comm_buckets_done(net);  // the gathers stay open: the next reader of the parameters waits for them
     net->grads_reduced = false;
     if (covered != P) return fail(net, MYEA_E_INVALID, "derivative buckets do not cover the parameter buffer");
   } else {
@@ -1367,6 +1390,7 @@ extern "C" int myea_b200_synchronize(myea_handle net) {
   if (net == nullptr) return MYEA_E_INVALID;
   CK(cudaSetDevice(net->ctx.device));
   int flag = 0;
+  RC(comm_gather_join(net));
   CK(cudaMemcpyAsync(&flag, net->ctx.d_error_flag, sizeof(int), cudaMemcpyDeviceToHost, net->ctx.stream));
   CK(cudaStreamSynchronize(net->ctx.stream));
   if (flag != 0) {
