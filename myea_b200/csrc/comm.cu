@@ -168,9 +168,12 @@ __host__ __device__ inline size_t peer_word(int kind, size_t bucket, int source)
 }
 
 // tells every peer that this rank's copies of (kind, bucket) are in its memory (same stream as the copies, behind them)
-__global__ void peer_signal_kernel(unsigned int *const *__restrict__ words, int kind, size_t bucket, int rank, int world, unsigned int epoch) {
+// (which: 0 every peer, 1 / 2 the peers an odd / even number of ranks ahead - the two halves travel on two streams)
+__global__ void peer_signal_kernel(unsigned int *const *__restrict__ words, int kind, size_t bucket, int rank, int world, unsigned int epoch, int which) {
   const int r = static_cast<int>(threadIdx.x);
   if (r >= world || r == rank) return;
+  const int ahead = (r - rank + world) % world;
+  if ((which == 1 && (ahead & 1) == 0) || (which == 2 && (ahead & 1) == 1)) return;
   __threadfence_system();
   unsigned int *theirs = words[r] + peer_word(kind, bucket, rank);
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
@@ -210,6 +213,10 @@ struct CommState {
   ncclComm_t comm = nullptr;
   int world = 1, rank = 0;
   cudaStream_t stream = nullptr;   // bucket all-reduces run here, beside the compute stream
+  cudaStream_t stream_aux = nullptr;    // peer copies: the peers an even number of ranks ahead (a second copy engine)
+  cudaStream_t stream_small = nullptr;  // peer copies of small buckets (biases), so that they do not queue behind the large ones
+  cudaStream_t stream_gather = nullptr, stream_gather_aux = nullptr;  // updated parameters: not behind the last derivative slices
+  cudaEvent_t aux_done = nullptr;
   cudaEvent_t ready = nullptr;     // compute -> comm: the bucket is complete
   cudaEvent_t done = nullptr;      // comm -> compute: every bucket issued so far is reduced
   cudaEvent_t side_done = nullptr; // comm -> compute: the small sum started by comm_side_sum_begin has arrived
@@ -278,6 +285,41 @@ int comm_all_reduce_sum_f64(myea_b200_net *net, double *buf, size_t n) {
 
 int comm_gather_join(myea_b200_net *net);
 
+// Peer copies of one bucket: kind 0 sends peer p this rank's derivative slice p (into the sender's slot of p's staging
+// area), kind 1 sends every peer this rank's slice of the updated parameters.  The copies start once `producer` (recorded
+// on the compute stream) has passed; `finished` is recorded when all of them have left.  Rank r starts with rank r + 1, so
+// at any moment every rank receives from one sender per stream.
+static int peer_push(myea_b200_net *net, int kind, size_t index, unsigned int epoch, size_t offset, size_t count, cudaEvent_t producer,
+                     cudaEvent_t finished) {
+  CommState *c = net->comm;
+  const int w = c->world;
+  const bool small = count * sizeof(float) * static_cast<size_t>(w - 1) < (static_cast<size_t>(4) << 20);
+  cudaStream_t main = small ? c->stream_small : (kind == 0 ? c->stream : c->stream_gather);
+  cudaStream_t aux = (small || w < 4) ? nullptr : (kind == 0 ? c->stream_aux : c->stream_gather_aux);
+  if (cudaStreamWaitEvent(main, producer, 0) != cudaSuccess) return MYEA_E_CUDA;
+  if (aux != nullptr && cudaStreamWaitEvent(aux, producer, 0) != cudaSuccess) return MYEA_E_CUDA;
+  for (int k = 1; k < w; ++k) {
+    const int p = (c->rank + k) % w;
+    const float *src;
+    float *dst;
+    if (kind == 0) {
+      src = net->grads + offset + static_cast<size_t>(p) * count;
+      dst = static_cast<float *>(c->copy.stages[p]) + offset + static_cast<size_t>(c->rank < p ? c->rank : c->rank - 1) * count;
+    } else {
+      src = net->params + offset + static_cast<size_t>(c->rank) * count;
+      dst = static_cast<float *>(c->copy.params[p]) + offset + static_cast<size_t>(c->rank) * count;
+    }
+    if (cudaMemcpyAsync(dst, src, count * sizeof(float), cudaMemcpyDeviceToDevice, (aux != nullptr && (k & 1) == 0) ? aux : main) != cudaSuccess) return MYEA_E_CUDA;
+  }
+  peer_signal_kernel<<<1, 32, 0, main>>>(c->copy.words_d, kind, index, c->rank, w, epoch, aux != nullptr ? 1 : 0);
+  if (aux != nullptr) {
+    peer_signal_kernel<<<1, 32, 0, aux>>>(c->copy.words_d, kind, index, c->rank, w, epoch, 2);
+    if (cudaEventRecord(c->aux_done, aux) != cudaSuccess || cudaStreamWaitEvent(main, c->aux_done, 0) != cudaSuccess) return MYEA_E_CUDA;
+  }
+  if (cudaGetLastError() != cudaSuccess || cudaEventRecord(finished, main) != cudaSuccess) return MYEA_E_CUDA;
+  return MYEA_OK;
+}
+
 // Hands the derivative range [offset, offset + n) to the communication stream: it is summed over ranks while the compute
 // stream carries on with the next layer.  Every rank issues the same buckets in the same order.
 int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n) {
@@ -285,30 +327,12 @@ int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n) {
   if (c == nullptr || n == 0) return MYEA_OK;
   NcclApi *api = nccl_api();
   if (comm_gather_join(net) != MYEA_OK) return MYEA_E_CUDA;  // the bucket records are about to be reused
-  if (cudaEventRecord(c->ready, net->ctx.stream) != cudaSuccess || cudaStreamWaitEvent(c->stream, c->ready, 0) != cudaSuccess) return MYEA_E_CUDA;
   // a slice starts on a 16-byte boundary (the update kernel reads float4) and all slices are equal
   const size_t w = static_cast<size_t>(c->world);
   const bool scattered = c->scatter && (n % (4 * w)) == 0 && (offset % 4) == 0;
   if (c->used == 0) ++c->copy.epoch;
   const bool by_copies = scattered && c->copy.ready && c->used < static_cast<size_t>(PEER_MAX_BUCKETS);
   ncclResult_t r = ncclSuccess;
-  if (by_copies) {
-    const size_t count = n / w;
-    for (int p = 0; p < c->world; ++p) {
-      if (p == c->rank) continue;
-      float *dst = static_cast<float *>(c->copy.stages[p]) + offset + static_cast<size_t>(c->rank < p ? c->rank : c->rank - 1) * count;
-      if (cudaMemcpyAsync(dst, net->grads + offset + static_cast<size_t>(p) * count, count * sizeof(float), cudaMemcpyDeviceToDevice, c->stream) != cudaSuccess)
-        return MYEA_E_CUDA;
-    }
-    peer_signal_kernel<<<1, 32, 0, c->stream>>>(c->copy.words_d, 0, c->used, c->rank, c->world, c->copy.epoch);
-    if (cudaGetLastError() != cudaSuccess) return MYEA_E_CUDA;
-  } else if (scattered) {
-    const size_t count = n / w;
-    r = api->ReduceScatter(net->grads + offset, net->grads + offset + static_cast<size_t>(c->rank) * count, count, ncclFloat, ncclSum, c->comm, c->stream);
-  } else {
-    r = api->AllReduce(net->grads + offset, net->grads + offset, n, ncclFloat, ncclSum, c->comm, c->stream);
-  }
-  if (r != ncclSuccess) return nccl_fail(net, r, scattered ? "ncclReduceScatter (bucket)" : "ncclAllReduce (bucket)");
   if (c->used == c->buckets.size()) {
     CommState::Bucket b;
     if (cudaEventCreateWithFlags(&b.reduced, cudaEventDisableTiming) != cudaSuccess ||
@@ -317,6 +341,18 @@ int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n) {
       return MYEA_E_CUDA;
     c->buckets.push_back(b);
   }
+  if (cudaEventRecord(c->ready, net->ctx.stream) != cudaSuccess) return MYEA_E_CUDA;
+  if (by_copies) {
+    if (peer_push(net, 0, c->used, c->copy.epoch, offset, n / w, c->ready, c->buckets[c->used].reduced) != MYEA_OK) return MYEA_E_CUDA;
+  } else if (cudaStreamWaitEvent(c->stream, c->ready, 0) != cudaSuccess) {
+    return MYEA_E_CUDA;
+  } else if (scattered) {
+    const size_t count = n / w;
+    r = api->ReduceScatter(net->grads + offset, net->grads + offset + static_cast<size_t>(c->rank) * count, count, ncclFloat, ncclSum, c->comm, c->stream);
+  } else {
+    r = api->AllReduce(net->grads + offset, net->grads + offset, n, ncclFloat, ncclSum, c->comm, c->stream);
+  }
+  if (r != ncclSuccess) return nccl_fail(net, r, scattered ? "ncclReduceScatter (bucket)" : "ncclAllReduce (bucket)");
   CommState::Bucket &b = c->buckets[c->used++];
   b.offset = offset;
   b.n = n;
@@ -324,7 +360,7 @@ int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n) {
   b.by_copies = by_copies;
   b.index = c->used - 1;
   b.epoch = c->copy.epoch;
-  if (cudaEventRecord(b.reduced, c->stream) != cudaSuccess) return MYEA_E_CUDA;
+  if (!by_copies && cudaEventRecord(b.reduced, c->stream) != cudaSuccess) return MYEA_E_CUDA;
   c->pending = true;
   net->ctx.launches += 1;
   net->ctx.class_launches[TC_COMM] += 1;
@@ -356,6 +392,8 @@ int comm_side_sum_end(myea_b200_net *net) {
 int comm_join(myea_b200_net *net) {
   CommState *c = net->comm;
   if (c == nullptr || !c->pending) return MYEA_OK;
+  for (size_t i = 0; i < c->used; ++i)  // (buckets may have travelled on several streams)
+    if (cudaStreamWaitEvent(net->ctx.stream, c->buckets[i].reduced, 0) != cudaSuccess) return MYEA_E_CUDA;
   if (cudaEventRecord(c->done, c->stream) != cudaSuccess || cudaStreamWaitEvent(net->ctx.stream, c->done, 0) != cudaSuccess) return MYEA_E_CUDA;
   c->pending = false;
   c->used = 0;
@@ -409,21 +447,15 @@ int comm_bucket_gather(myea_b200_net *net, size_t i) {
   if (mine + count < b.n &&
       cudaMemsetAsync(net->grads + b.offset + mine + count, 0, (b.n - mine - count) * sizeof(float), net->ctx.stream) != cudaSuccess)
     return MYEA_E_CUDA;
-  if (cudaEventRecord(b.updated, net->ctx.stream) != cudaSuccess || cudaStreamWaitEvent(c->stream, b.updated, 0) != cudaSuccess) return MYEA_E_CUDA;
+  if (cudaEventRecord(b.updated, net->ctx.stream) != cudaSuccess) return MYEA_E_CUDA;
   if (b.by_copies) {
-    for (int p = 0; p < c->world; ++p) {
-      if (p == c->rank) continue;
-      if (cudaMemcpyAsync(static_cast<float *>(c->copy.params[p]) + b.offset + mine, net->params + b.offset + mine, count * sizeof(float),
-                          cudaMemcpyDeviceToDevice, c->stream) != cudaSuccess)
-        return MYEA_E_CUDA;
-    }
-    peer_signal_kernel<<<1, 32, 0, c->stream>>>(c->copy.words_d, 1, b.index, c->rank, c->world, b.epoch);
-    if (cudaGetLastError() != cudaSuccess) return MYEA_E_CUDA;
+    if (peer_push(net, 1, b.index, b.epoch, b.offset, count, b.updated, b.gathered) != MYEA_OK) return MYEA_E_CUDA;
   } else {
+    if (cudaStreamWaitEvent(c->stream, b.updated, 0) != cudaSuccess) return MYEA_E_CUDA;
     ncclResult_t r = api->AllGather(net->params + b.offset + mine, net->params + b.offset, count, ncclFloat, c->comm, c->stream);
     if (r != ncclSuccess) return nccl_fail(net, r, "ncclAllGather (bucket)");
+    if (cudaEventRecord(b.gathered, c->stream) != cudaSuccess) return MYEA_E_CUDA;
   }
-  if (cudaEventRecord(b.gathered, c->stream) != cudaSuccess) return MYEA_E_CUDA;
   b.gather_open = true;
   c->gathers_open = true;
   net->ctx.launches += 1;
@@ -641,7 +673,8 @@ void comm_destroy(myea_b200_net *net) {
   }
   comm_gather_join(net);
   if (net->ctx.stream) cudaStreamSynchronize(net->ctx.stream);
-  if (net->comm->stream) cudaStreamSynchronize(net->comm->stream);
+  for (cudaStream_t st : {net->comm->stream, net->comm->stream_aux, net->comm->stream_small, net->comm->stream_gather, net->comm->stream_gather_aux})
+    if (st) cudaStreamSynchronize(st);
   cudaGetLastError();
   peer_teardown(net->comm);
   if (api && net->comm->comm) api->CommDestroy(net->comm->comm);
@@ -653,7 +686,9 @@ void comm_destroy(myea_b200_net *net) {
     if (b.updated) cudaEventDestroy(b.updated);
     if (b.gathered) cudaEventDestroy(b.gathered);
   }
-  if (net->comm->stream) cudaStreamDestroy(net->comm->stream);
+  for (cudaStream_t st : {net->comm->stream, net->comm->stream_aux, net->comm->stream_small, net->comm->stream_gather, net->comm->stream_gather_aux})
+    if (st) cudaStreamDestroy(st);
+  if (net->comm->aux_done) cudaEventDestroy(net->comm->aux_done);
   delete net->comm;
   net->comm = nullptr;
 }
@@ -688,11 +723,21 @@ extern "C" int myea_b200_comm_init(myea_handle net, int world, int rank, const u
   ncclResult_t r = api->CommInitRank(&c->comm, world, id, rank);
   if (r != ncclSuccess) { delete c; return nccl_fail(net, r, "ncclCommInitRank"); }
   if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&c->stream_aux, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&c->stream_small, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&c->stream_gather, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&c->stream_gather_aux, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&c->aux_done, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->ready, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->side_done, cudaEventDisableTiming) != cudaSuccess) {
     api->CommDestroy(c->comm);
     if (c->stream) cudaStreamDestroy(c->stream);
+    if (c->stream_aux) cudaStreamDestroy(c->stream_aux);
+    if (c->stream_small) cudaStreamDestroy(c->stream_small);
+    if (c->stream_gather) cudaStreamDestroy(c->stream_gather);
+    if (c->stream_gather_aux) cudaStreamDestroy(c->stream_gather_aux);
+    if (c->aux_done) cudaEventDestroy(c->aux_done);
     if (c->ready) cudaEventDestroy(c->ready);
     if (c->done) cudaEventDestroy(c->done);
     if (c->side_done) cudaEventDestroy(c->side_done);
