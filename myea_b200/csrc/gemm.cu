@@ -67,7 +67,6 @@ __device__ __forceinline__ float epilogue_value(const Epilogue &e, float acc, lo
   return v;
 }
 
-
 __device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
 
 // The vector path of the epilogue needs 16-byte aligned bases and pitches that are multiples of four floats.
@@ -238,10 +237,27 @@ __device__ __forceinline__ void epilogue_block32_rows(const Epilogue &e, float *
       for (int j = 0; j < 8; ++j) *reinterpret_cast<float4 *>(dst + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     }
     __syncwarp();
+    if (e.accumulate && e.bias == nullptr && e.addend == nullptr && e.deriv_af == 0u) {
+      // C += product and nothing else (weight derivatives): the 16 old row segments are requested together - one after
+      // the other, their latency (rows of an LSTM layer's weight derivatives lie a whole block apart) is what the
+      // epilogue of a tile takes
+      float old[16];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const long long m = row0 + h * 16 + r;
+        old[r] = (m < M && n < N) ? e.C[c_row(e, m) + n] : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const long long m = row0 + h * 16 + r;
+        if (m < M && n < N) e.C[c_row(e, m) + n] = tr[r * TR_PITCH + lane] + old[r];
+      }
+    } else {
 #pragma unroll 4
-    for (int r = 0; r < 16; ++r) {
-      const long long m = row0 + h * 16 + r;
-      if (m < M && n < N) e.C[c_row(e, m) + n] = epilogue_value(e, tr[r * TR_PITCH + lane], m, n);
+      for (int r = 0; r < 16; ++r) {
+        const long long m = row0 + h * 16 + r;
+        if (m < M && n < N) e.C[c_row(e, m) + n] = epilogue_value(e, tr[r * TR_PITCH + lane], m, n);
+      }
     }
   }
 }
