@@ -6,7 +6,7 @@
 // that it overlaps the remaining layers.  A bucket whose size divides evenly is REDUCE-SCATTERED: every rank receives the
 // sum of its 1/world slice only, runs the optimizer on that slice (the update is element by element) and the updated
 // parameters are ALL-GATHERED - the same bytes on the wire as an all-reduce, 1/world of the optimizer's memory traffic
-// per rank.  Other buckets (and every bucket when a global-norm clip or the max-norm constraint needs whole rows) are
+// per rank.  Other buckets (and every bucket when the max-norm constraint needs whole rows) are
 // all-reduced and every rank updates all of them; the per-thread partial sums of the batch-normalization statistics
 // (Neural_Network__Forward_Pass__OpenMP.cpp:4591-4701, …Backward_Pass__OpenMP.cpp:1346-1709) become small all-reduces of
 // [2][H] column sums, so a sharded step computes the same statistics as the one-GPU step; the loss / accuracy
@@ -249,6 +249,7 @@ static int nccl_fail(myea_b200_net *net, ncclResult_t r, const char *what) {
 }
 
 int comm_world(const myea_b200_net *net) { return net->comm != nullptr ? net->comm->world : 1; }
+int comm_rank(const myea_b200_net *net) { return net->comm != nullptr ? net->comm->rank : 0; }
 
 // the peer-memory exchange when it is set up and the vector fits, on `stream`
 static bool peer_sum(myea_b200_net *net, float *buf, size_t n, cudaStream_t stream) {

@@ -357,7 +357,7 @@ int row_max_norm(Context &ctx, float *w, long long rows, long long cols, float m
 int lstm_max_norm(Context &ctx, float *params, long long first, long long blocks, long long stride, long long n_in, long long cells,
                   long long cells_per_block, float max_norm);
 // d_out[0] = sum g^2 (double)
-int sum_squares(Context &ctx, const float *g, size_t n, double *d_out);
+int sum_squares(Context &ctx, const float *g, size_t n, double *d_out, bool accumulate = false);  // d_out (+)= sum of g^2
 // clip_scale[0] = norm >= clip ? clip / norm : 1
 int clip_scale_from_norm(Context &ctx, const double *d_sumsq, float clip, float *d_scale);
 

@@ -42,6 +42,7 @@ int comm_all_reduce_sum_f64(myea_b200_net *net, double *buf, size_t n);
 int comm_reduce_bucket_async(myea_b200_net *net, size_t offset, size_t n);
 int comm_join(myea_b200_net *net);
 int comm_world(const myea_b200_net *net);
+int comm_rank(const myea_b200_net *net);
 void comm_destroy(myea_b200_net *net);
 }  // namespace myea
 
@@ -1172,8 +1173,8 @@ extern "C" int myea_b200_update_derivative_weight(myea_handle net, uint64_t batc
   const long long rows = step_rows_total(net);
   if (net->comm != nullptr && net->grads_reduced)
     return fail(net, MYEA_E_UNSUPPORTED, "with a communicator attached, call update_parameter after every update_derivative_weight (the derivative buckets of this step were already summed over the ranks)");
-  // Reduce-scatter instead of all-reduce where the update is element by element: not under a global-norm clip (the norm
-  // needs every element) or the max-norm constraint (whole rows), which the description announces
+  // Reduce-scatter instead of all-reduce where the update works on slices: not under the max-norm constraint (whole
+  // rows), which the last update's description announced
   comm_set_scatter(net, net->comm != nullptr && net->sharded_update);
   if (net->pre_training_level != 0) {  // the two layers of the pair only
     int k = 0, dl = 0;
@@ -1225,10 +1226,11 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
   CK(cudaSetDevice(net->ctx.device));
   RC(comm_gather_join(net));
   const size_t P = net->total_parameters;
-  // Without a global-norm clip the update is element by element, so each derivative bucket can be applied as soon as
-  // ITS sum over the ranks has arrived, while the later (lower-layer) buckets are still on the wire - and only on this
-  // rank's slice of it where the bucket was reduce-scattered.
-  const bool needs_whole = opt->use_clip_gradient || opt->regularization__max_norm_constraints != 0.f;
+  // The update is element by element, so each derivative bucket can be applied as soon as ITS sum over the ranks has
+  // arrived, while the later buckets are still on the wire - and only on this rank's slice of it where the bucket was
+  // reduce-scattered.  A global-norm clip works on slices too (every rank squares what it holds and the sums are added
+  // over the ranks) but has to see every bucket before the first update; the max-norm constraint needs whole rows.
+  const bool needs_whole = opt->regularization__max_norm_constraints != 0.f;
   net->sharded_update = !needs_whole;  // what the NEXT step's buckets may assume
   bool by_bucket = net->comm != nullptr && net->grads_reduced && !needs_whole && comm_bucket_count(net) > 0 && (net->total_weights & 3) == 0;
   for (const auto &L : net->layers)  // the update kernel reads float4: every bucket has to start on a 16-byte boundary
@@ -1243,8 +1245,25 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
   for (auto &L : net->layers) L.w_valid = false;  // the weights change below
   OptLaunch o;
   o.type = opt->type_optimizer_function;
+  struct ReadyBucket { size_t i, n, off, slice; };
+  std::vector<ReadyBucket> ready;  // buckets whose sums were waited for ahead of the update loop (clip only)
   if (opt->use_clip_gradient) {
-    RC(sum_squares(net->ctx, net->grads, P, net->d_sumsq));
+    if (by_bucket) {
+      // the norm needs every bucket's sum before the first update: a reduce-scattered bucket contributes this rank's
+      // slice, an all-reduced one (every rank holds all of it) is counted by rank 0 alone
+      CK(cudaMemsetAsync(net->d_sumsq, 0, sizeof(double), net->ctx.stream));
+      const size_t count = comm_bucket_count(net);
+      for (size_t k = 0; k < count; ++k) {
+        ReadyBucket b{k == 0 ? count - 1 : k - 1, 0, 0, 0};
+        size_t bucket_off = 0;
+        RC(comm_bucket_wait(net, b.i, &bucket_off, &b.n, &b.off, &b.slice));
+        if (b.slice != b.n || comm_rank(net) == 0) RC(sum_squares(net->ctx, net->grads + b.off, b.slice, net->d_sumsq, true));
+        ready.push_back(b);
+      }
+      RC(comm_all_reduce_sum_f64(net, net->d_sumsq, 1));
+    } else {
+      RC(sum_squares(net->ctx, net->grads, P, net->d_sumsq));
+    }
     RC(clip_scale_from_norm(net->ctx, net->d_sumsq, opt->clip_gradient, net->d_clip_scale));
     o.clip_scale = net->d_clip_scale;
   }
@@ -1306,9 +1325,10 @@ extern "C" int myea_b200_update_parameter(myea_handle net, uint64_t batch, uint6
     // the bucket of the biases and normalization parameters was issued last but is gathered first: the next forward
     // pass reads it before anything else
     for (size_t k = 0; k < count; ++k) {
-      const size_t i = k == 0 ? count - 1 : k - 1;
+      size_t i = k == 0 ? count - 1 : k - 1;
       size_t bucket_off = 0, n = 0, off = 0, slice = 0;
-      RC(comm_bucket_wait(net, i, &bucket_off, &n, &off, &slice));
+      if (!ready.empty()) { i = ready[k].i; n = ready[k].n; off = ready[k].off; slice = ready[k].slice; }
+      else RC(comm_bucket_wait(net, i, &bucket_off, &n, &off, &slice));
       if ((off & 3) != 0) return fail(net, MYEA_E_INVALID, "derivative bucket does not start on a 16-byte boundary");
       RC(optimizer_update(net->ctx, o, net->params + off, net->grads + off, net->m1 + off, net->m2 + off, net->m2hat + off, net->prev_delta + off,
                           net->mask_reg + off, slice));

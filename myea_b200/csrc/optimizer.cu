@@ -154,9 +154,9 @@ __global__ void __launch_bounds__(256) sum_squares_kernel(const float *__restric
   }
 }
 
-int sum_squares(Context &ctx, const float *g, size_t n, double *d_out) {
+int sum_squares(Context &ctx, const float *g, size_t n, double *d_out, bool accumulate) {
   ctx.begin(TC_OPTIMIZER);
-  cudaMemsetAsync(d_out, 0, sizeof(double), ctx.stream);
+  if (!accumulate) cudaMemsetAsync(d_out, 0, sizeof(double), ctx.stream);
   const int blocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(((n >> 2) + 255) / 256, 148 * 8)));
   sum_squares_kernel<<<blocks, 256, 0, ctx.stream>>>(g, n, d_out);
   ctx.end(TC_OPTIMIZER);

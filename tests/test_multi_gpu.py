@@ -17,7 +17,7 @@ def _gpus():
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("name", ["c2_small", "c3_small", "c1_small"])
+@pytest.mark.parametrize("name", ["c2_small", "c3_small", "c1_small", "lstm2_zoneout_clip", "mlp_bernoulli_amsbound_clip"])
 def test_two_gpus_equal_one_process(name):
     if _gpus() < 2:
         pytest.skip("needs 2 GPUs")
