@@ -53,7 +53,7 @@ def _worker(rank, world, port, name, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("name", ["c2_small", "c1_small"])
+@pytest.mark.parametrize("name", ["c2_small", "c1_small", "mlp_bernoulli_amsbound_clip", "lstm2_zoneout_clip"])
 def test_two_ranks_equal_one_process(name, tmp_path):
     wl = cases.CASES[name]()
     if wl.B % 2:
