@@ -68,6 +68,9 @@ static NcclApi *nccl_api() {
 // allocation that all ranks map (CUDA IPC): [2 parities][world slots][capacity] floats followed by
 // [2 parities][world][PEER_MAX_BLOCKS] arrival words.
 constexpr int PEER_MAX_BLOCKS = 64;
+// how long a rank waits for a peer's arrival word before it gives up and flags the handle: about two minutes of SM
+// clocks - ranks may reach an exchange far apart (the first step, a rank that loads data), but it is a bound
+constexpr long long PEER_WAIT_CYCLES = 1ll << 38;
 constexpr int PEER_MAX_WORLD = 16;
 struct PeerSum {
   bool ready = false;
@@ -118,7 +121,7 @@ __global__ void __launch_bounds__(256) peer_sum_kernel(float *__restrict__ data,
       unsigned int seen;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
       if (static_cast<int>(seen - epoch) >= 0) break;
-      if (clock64() - t0 > (1ll << 36)) { failed = 1; break; }
+      if (clock64() - t0 > PEER_WAIT_CYCLES) { failed = 1; break; }
     }
   }
   __syncthreads();
@@ -188,7 +191,7 @@ __global__ void peer_wait_kernel(const unsigned int *__restrict__ mine, int kind
     unsigned int seen;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(word) : "memory");
     if (static_cast<int>(seen - epoch) >= 0) return;
-    if (clock64() - t0 > (1ll << 36)) {
+    if (clock64() - t0 > PEER_WAIT_CYCLES) {
       atomicCAS(error_flag, 0, 502 + kind);
       return;
     }
