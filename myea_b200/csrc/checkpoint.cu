@@ -773,7 +773,17 @@ int parse_dimension(const char *path, Parsed &out, std::string &error) {
         // the bound is the default one for some clip_gradient between 2 and 10: recover that value (0 = the class default)
         if (ok && bound > 0.f && fabsf(bound - ind_rnn_weight_bound(0.f, L.type_activation_function, static_cast<long long>(T))) > 1e-6f * bound) {
           const float c = ind_rnn_weight_bound(0.f, L.type_activation_function, static_cast<long long>(T));
-          d.clip_gradient = 2.f * powf(bound / c, static_cast<float>(T));  // bound = (MAG / k)^(1/T), c = (2 / k)^(1/T)
+          const float guess = 2.f * powf(bound / c, static_cast<float>(T));  // bound = (MAG / k)^(1/T), c = (2 / k)^(1/T)
+          // the power and its root do not invert each other to the last bit: take the neighbour of the guess that gives
+          // this very bound back, so that a file written from the parsed description equals the file that was read
+          d.clip_gradient = guess;
+          float up = guess, down = guess;
+          for (int step = 0; step < 64; ++step) {
+            if (ind_rnn_weight_bound(up, L.type_activation_function, static_cast<long long>(T)) == bound) { d.clip_gradient = up; break; }
+            if (ind_rnn_weight_bound(down, L.type_activation_function, static_cast<long long>(T)) == bound) { d.clip_gradient = down; break; }
+            up = nextafterf(up, INFINITY);
+            down = nextafterf(down, -INFINITY);
+          }
         }
         break;
       }
@@ -944,6 +954,12 @@ extern "C" int myea_b200_checkpoint_parse(const char *path_dimension, const char
   if (path_general != nullptr) {
     rc = parse_general(path_general, in.desc, o, g_parse_error);
     if (rc != MYEA_OK) return rc;
+    // the general file states clip_gradient itself; where the bounds of the independently recurrent layers are the
+    // default ones for that value, it replaces the value recovered from a bound
+    if (in.desc.clip_gradient != 0.f && o.clip_gradient > 0.f) {
+      const float from_bound = std::min(std::max(in.desc.clip_gradient, 2.f), 10.f), stated = std::min(std::max(o.clip_gradient, 2.f), 10.f);
+      if (fabsf(from_bound - stated) <= 1e-4f * stated) in.desc.clip_gradient = o.clip_gradient;
+    }
   }
   if (total_parameters) *total_parameters = in.total_parameters;
   if (total_normalized_units) *total_normalized_units = in.total_norm_units;
