@@ -15,7 +15,9 @@ ACTIVATIONS = [getattr(capi, n) for n in dir(capi) if n.startswith("AF_") and n 
 OPTIMIZERS = [capi.OPT_ADAM, capi.OPT_AMSGRAD, capi.OPT_ADABOUND, capi.OPT_AMSBOUND, capi.OPT_GD, capi.OPT_NOSADAM, capi.OPT_IRPROP_PLUS]
 
 
-def _random_network(seed):
+def _random_network(seed, activations=None, optimizers=None, batch=None):
+    """(descriptor, optimizer settings, layer list) of a seeded random feed-forward network"""
+    activations, optimizers = activations or ACTIVATIONS, optimizers or OPTIMIZERS
     rng = np.random.default_rng(seed)
     width = lambda: int(rng.integers(3, 25))
     layers = [capi.fc(width())]
@@ -23,7 +25,7 @@ def _random_network(seed):
     norm_of_net = int(rng.choice([capi.NORM_BN, capi.NORM_BRN]))   # the reference refuses both kinds in one network
     for _ in range(int(rng.integers(2, 6))):
         kind = rng.choice(["fc", "fc", "fc", "pool", "block"])
-        af = int(rng.choice(ACTIVATIONS))
+        af = int(rng.choice(activations))
         norm = int(rng.choice([capi.NORM_NONE, norm_of_net]))
         drop = int(rng.choice([capi.DROP_NONE, capi.DROP_BERNOULLI, capi.DROP_BERNOULLI_INVERTED]))
         p = (float(np.float32(rng.uniform(0.3, 0.9))), 0.0, 0.0) if drop != capi.DROP_NONE else (0.0, 0.0, 0.0)
@@ -46,9 +48,9 @@ def _random_network(seed):
             prev = layers[-1].unit_parameters[0]
     softmax = rng.random() < 0.5
     layers.append(capi.fc(width(), capi.AF_SOFTMAX if softmax else capi.AF_LINEAR))
-    desc = capi.net(layers, batch=int(rng.integers(2, 9)), loss=capi.LOSS_CE if softmax else capi.LOSS_MSE,
+    desc = capi.net(layers, batch=batch or int(rng.integers(2, 9)), loss=capi.LOSS_CE if softmax else capi.LOSS_MSE,
                     accuracy=capi.ACC_CE if softmax else capi.ACC_DISTANCE)
-    kind = int(rng.choice(OPTIMIZERS))
+    kind = int(rng.choice(optimizers))
     opt = capi.opt(kind, lr=float(np.float32(rng.uniform(1e-4, 1e-2))), weight_decay=float(np.float32(rng.choice([0.0, 1e-4]))),
                    clip=float(np.float32(rng.uniform(0.5, 2.0))) if rng.random() < 0.3 else None,
                    momentum=float(np.float32(rng.choice([0.0, 0.9]))), nesterov=bool(rng.random() < 0.3))

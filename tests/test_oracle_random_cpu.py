@@ -1,0 +1,64 @@
+"""The numpy restatement against the compiled reference on seeded random feed-forward architectures (CPU only): random
+depth and widths, sigmoidal activation functions, batch normalization / renormalization, Bernoulli and inverted dropout,
+average / max pooling, residual blocks of equal and unequal width with and without ShakeDrop (the reference's draws
+replayed), gradient descent with and without momentum / Nesterov / clip / weight decay; two training steps.
+
+What is compared: derivatives, updated parameters, the last layer's outputs, running averages, loss.  Bars: every
+network within 5e-3 of max|reference| (tiny batch deviations of normalized units amplify fp32 rounding: a chain of
+saturating layers leaves a unit almost constant over the 24 rows, and sigma^2 + epsilon then carries a per-cent error
+on either side), and at least 85 % of the networks within 5e-5.  A difference in meaning - a wrong formula, a wrong
+index - shows as an error of order one.  Optimizers that take the SIGN of a derivative (Adam-type first steps, iRPROP+)
+and activation functions with kinks are left to the pinned cases: on random networks a derivative that is zero on one
+side and 1e-12 on the other decides a whole step."""
+import numpy as np
+import pytest
+
+import cases
+from conftest import rel_err
+from myea_b200 import capi, workloads
+from oracle import myea_oracle, ref
+from test_checkpoint_random_cpu import _random_network
+
+pytestmark = pytest.mark.skipif(not ref.available(), reason="compiled reference (oracle/_ref) not present")
+
+SMOOTH = [capi.AF_TANH, capi.AF_SIGMOID, capi.AF_ELLIOT, capi.AF_ELLIOT_SYMMETRIC, capi.AF_GAUSSIAN, capi.AF_GAUSSIAN_SYMMETRIC, capi.AF_ISRU,
+          capi.AF_ISRLU]
+SEEDS = range(48)
+
+
+def _errors(seed):
+    desc, opt, layers = _random_network(seed, activations=SMOOTH, optimizers=[capi.OPT_GD], batch=24)
+    n_in, n_out = int(layers[0].unit_parameters[0]), int(layers[-1].unit_parameters[0])
+    one_hot = layers[-1].type_activation_function == capi.AF_SOFTMAX
+
+    def workload():
+        w = workloads.Workload("random%d" % seed, desc, opt, n_in, n_out, one_hot, layers)
+        w.seed = seed
+        return w
+
+    net = ref.RefNet(desc, opt, threads=1)
+    try:
+        want = cases.run_steps(net, workload(), steps=2)
+    finally:
+        net.close()
+    got = cases.run_steps(myea_oracle.OracleNet(desc, opt), workload(), steps=2, shake=want["shake"])
+    assert got["index_map"] == want["index_map"] and got["sizes"] == want["sizes"]
+    for it in (0, 1):
+        assert got["loss%d" % it][1] == want["loss%d" % it][1]              # how many values were scored
+    keys = [k for k in ("grad0", "param0", "grad1", "param1", "output_last", "norm_mean_avg", "norm_sigma_avg", "m") if k in want]
+    return max(rel_err(got[k], want[k]) for k in keys)
+
+
+@pytest.fixture(scope="module")
+def errors():
+    return {seed: _errors(seed) for seed in SEEDS}
+
+
+def test_every_random_network_within_the_conditioning_bar(errors):
+    worst = max(errors, key=errors.get)
+    assert errors[worst] < 5e-3, "seed %d: %.2e" % (worst, errors[worst])
+
+
+def test_most_random_networks_at_rounding_level(errors):
+    tight = sum(e < 5e-5 for e in errors.values())
+    assert tight >= 0.85 * len(errors), sorted(errors.items(), key=lambda kv: -kv[1])[:8]
