@@ -62,3 +62,53 @@ def test_every_random_network_within_the_conditioning_bar(errors):
 def test_most_random_networks_at_rounding_level(errors):
     tight = sum(e < 5e-5 for e in errors.values())
     assert tight >= 0.85 * len(errors), sorted(errors.items(), key=lambda kv: -kv[1])[:8]
+
+
+def random_recurrent_case(seed):
+    """(descriptor, optimizer settings, layers) of a seeded random recurrent network for a numerics comparison: the
+    layer list of the checkpoint test's generator (LSTM layers of 1 - 3 cells per block with and without zoneout,
+    independently recurrent layers, fully connected layers), sigmoidal activation functions, gradient descent with or
+    without momentum and clip, a batch of 6 sequences of 2 - 5 time steps"""
+    from test_checkpoint_random_cpu import _random_recurrent_network
+    desc, opt = _random_recurrent_network(seed)
+    layers = [desc.layers[l] for l in range(desc.number_layers)]
+    for L in layers:
+        if L.type_layer == capi.LAYER_FC and L.type_activation_function != capi.AF_LINEAR:
+            L.type_activation_function = [capi.AF_TANH, capi.AF_SIGMOID, capi.AF_ELLIOT_SYMMETRIC, capi.AF_ISRU][seed % 4]
+        if L.type_layer == capi.LAYER_FC_IND_RNN:
+            L.type_activation_function = capi.AF_TANH
+    opt = capi.opt(capi.OPT_GD, gd_lr=0.01, momentum=0.9 if seed % 2 else 0.0, clip=opt.clip_gradient if opt.use_clip_gradient else None)
+    desc = capi.net(layers, batch=6, T=int(desc.number_recurrent_depth), loss=capi.LOSS_MSE, accuracy=capi.ACC_DISTANCE,
+                    time_delays=int(desc.number_time_delays), clip_gradient=float(desc.clip_gradient))
+    return desc, opt, layers
+
+
+def recurrent_errors(seed, make_net):
+    desc, opt, layers = random_recurrent_case(seed)
+    n_in, n_out = int(layers[0].unit_parameters[0]), int(layers[-1].unit_parameters[0])
+
+    def workload():
+        w = workloads.Workload("recurrent%d" % seed, desc, opt, n_in, n_out, False, layers)
+        w.seed = seed
+        return w
+
+    net = ref.RefNet(desc, opt, threads=1)
+    try:
+        want = cases.run_steps(net, workload(), steps=2)
+    finally:
+        net.close()
+    other = make_net(desc, opt)
+    try:
+        got = cases.run_steps(other, workload(), steps=2)
+    finally:
+        if hasattr(other, "close"):
+            other.close()
+    assert got["index_map"] == want["index_map"] and list(got["sizes"]) == list(want["sizes"])
+    for it in (0, 1):
+        assert got["loss%d" % it][1] == want["loss%d" % it][1]
+    return max(rel_err(got[k], want[k]) for k in ("grad0", "param0", "grad1", "param1", "output_last", "m"))
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_recurrent_network(seed):
+    assert recurrent_errors(seed, myea_oracle.OracleNet) < 2e-5

@@ -61,3 +61,11 @@ def test_every_random_network_within_the_conditioning_bar(errors):
 def test_most_random_networks_within_the_parity_tolerance(errors):
     tight = sum(e < 1e-4 for e in errors.values())
     assert tight >= 0.80 * len(errors), sorted(errors.items(), key=lambda kv: -kv[1])[:8]
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_recurrent_network(seed):
+    """LSTM layers of 1 - 3 cells per block with and without zoneout, independently recurrent layers and fully connected
+    layers between them, 2 - 5 time steps: within the 1e-4 parity tolerance of the compiled reference"""
+    from test_oracle_random_cpu import recurrent_errors
+    assert recurrent_errors(seed, Net) < 1e-4
