@@ -112,3 +112,52 @@ def recurrent_errors(seed, make_net):
 @pytest.mark.parametrize("seed", range(40))
 def test_random_recurrent_network(seed):
     assert recurrent_errors(seed, myea_oracle.OracleNet) < 2e-5
+
+
+def random_autoencoder_case(seed):
+    """(workload, coded layers on the way in) of a seeded random autoencoder: 3, 5 or 7 layers of units with mirrored
+    widths, sigmoidal activation functions (and ELU, Gaussian), no / Bernoulli / inverted dropout on the encoding side"""
+    rng = np.random.default_rng(900 + seed)
+    smooth = [capi.AF_TANH, capi.AF_SIGMOID, capi.AF_ELLIOT_SYMMETRIC, capi.AF_ISRU, capi.AF_ELU, capi.AF_GAUSSIAN]
+    depth = int(rng.integers(1, 4))
+    widths = [int(rng.integers(6, 16))]
+    for _ in range(depth):
+        widths.append(int(rng.integers(3, widths[-1] + 1)))
+    full = widths + widths[-2::-1]
+    layers = [capi.fc(full[0])]
+    for i, w in enumerate(full[1:-1], 1):
+        drop = int(rng.choice([capi.DROP_NONE, capi.DROP_BERNOULLI, capi.DROP_BERNOULLI_INVERTED])) if i <= depth else capi.DROP_NONE
+        layers.append(capi.fc(w, int(rng.choice(smooth)), dropout=drop, p=(float(np.float32(rng.uniform(0.5, 0.9))), 0.0, 0.0) if drop else (0.0, 0.0, 0.0)))
+    layers.append(capi.fc(full[-1], capi.AF_LINEAR))
+    desc = capi.net(layers, int(rng.integers(4, 12)), loss=capi.LOSS_MSE, accuracy=capi.ACC_DISTANCE)
+    desc.type_network = capi.NET_AUTOENCODER
+    wl = workloads.Workload("autoencoder%d" % seed, desc, capi.opt(capi.OPT_GD, gd_lr=0.05, momentum=0.9 if seed % 2 else 0.0), full[0], full[-1], False, layers)
+    wl.seed = seed
+    return wl, depth
+
+
+def autoencoder_errors(seed, make_net):
+    """every pre-training level of the network in turn, then the whole network (level 0), two steps each"""
+    wl, depth = random_autoencoder_case(seed)
+    levels = tuple(range(1, depth + 1)) + (0,)
+    net = ref.RefNet(wl.desc, wl.opt, threads=1)
+    try:
+        want = cases.run_pre_training(net, wl, levels=levels)
+    finally:
+        net.close()
+    wl, _ = random_autoencoder_case(seed)
+    other = make_net(wl.desc, wl.opt)
+    try:
+        got = cases.run_pre_training(other, wl, levels=levels)
+    finally:
+        if hasattr(other, "close"):
+            other.close()
+    for k in want:
+        if k.endswith("loss"):
+            assert got[k][1] == want[k][1], k
+    return max(rel_err(got[k], want[k]) for k in want if not k.endswith("loss"))
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_autoencoder_pre_training(seed):
+    assert autoencoder_errors(seed, myea_oracle.OracleNet) < 2e-5

@@ -69,3 +69,10 @@ def test_random_recurrent_network(seed):
     layers between them, 2 - 5 time steps: within the 1e-4 parity tolerance of the compiled reference"""
     from test_oracle_random_cpu import recurrent_errors
     assert recurrent_errors(seed, Net) < 1e-4
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_autoencoder_pre_training(seed):
+    """autoencoders of 3, 5 or 7 layers with mirrored widths: every pre-training level in turn, then the whole network"""
+    from test_oracle_random_cpu import autoencoder_errors
+    assert autoencoder_errors(seed, Net) < 1e-4
