@@ -1019,7 +1019,12 @@ int fc_finish_backward(myea_b200_net *net, LayerPlan &L, long long rows) {
   // the layer's errors are read next by the error propagation below it (rows) and by its weight derivative (columns),
   // both from shared operand panels: the kernel that writes the errors writes those panels as well
   PanelSink sink;
-  const bool use_sink = L.shared_panels && L.in_valid && net->ctx.gemm_engine == 0 && (rows & 7) == 0 && (L.n_out & 7) == 0 &&
+  // (the panel-writing kernel reads the layer's statistics eight columns at a time: they lie behind those of the
+  // normalized layers before this one, whose unit counts need not be multiples of four - then the plain kernel runs and
+  // the readers of the errors split them themselves, as the forward pass does with unaligned coefficients)
+  const uintptr_t stat_bits = reinterpret_cast<uintptr_t>(L.norm.mean) | reinterpret_cast<uintptr_t>(L.norm.partial) |
+                              reinterpret_cast<uintptr_t>(L.summations) | reinterpret_cast<uintptr_t>(L.deriv) | reinterpret_cast<uintptr_t>(L.errors);
+  const bool use_sink = L.shared_panels && L.in_valid && net->ctx.gemm_engine == 0 && (rows & 7) == 0 && (L.n_out & 7) == 0 && (stat_bits & 15) == 0 &&
                         gemm_takes_mn_major(net->ctx, rows, L.n_out) && gemm_takes_mn_major(net->ctx, rows, L.n_in);
   if (use_sink) shared_panel_layout(L.d_panel_mem, rows, L.n_out, PANEL_ROLE_A, &L.d_rows, PANEL_ROLE_A, &L.d_cols, &sink);
   RC(norm_backward(net->ctx, L.summations, L.deriv, L.errors, rows, L.n_out, L.norm, &net->hook, L.bwd_fused_chunks, use_sink ? &sink : nullptr));

@@ -15,11 +15,12 @@ ACTIVATIONS = [getattr(capi, n) for n in dir(capi) if n.startswith("AF_") and n 
 OPTIMIZERS = [capi.OPT_ADAM, capi.OPT_AMSGRAD, capi.OPT_ADABOUND, capi.OPT_AMSBOUND, capi.OPT_GD, capi.OPT_NOSADAM, capi.OPT_IRPROP_PLUS]
 
 
-def _random_network(seed, activations=None, optimizers=None, batch=None):
-    """(descriptor, optimizer settings, layer list) of a seeded random feed-forward network"""
+def _random_network(seed, activations=None, optimizers=None, batch=None, widths=None):
+    """(descriptor, optimizer settings, layer list) of a seeded random feed-forward network; `widths`: the layer widths
+    to draw from (default: 3 .. 24)"""
     activations, optimizers = activations or ACTIVATIONS, optimizers or OPTIMIZERS
     rng = np.random.default_rng(seed)
-    width = lambda: int(rng.integers(3, 25))
+    width = (lambda: int(rng.choice(widths))) if widths else (lambda: int(rng.integers(3, 25)))
     layers = [capi.fc(width())]
     prev = layers[0].unit_parameters[0]
     norm_of_net = int(rng.choice([capi.NORM_BN, capi.NORM_BRN]))   # the reference refuses both kinds in one network

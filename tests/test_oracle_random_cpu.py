@@ -161,3 +161,44 @@ def autoencoder_errors(seed, make_net):
 @pytest.mark.parametrize("seed", range(40))
 def test_random_autoencoder_pre_training(seed):
     assert autoencoder_errors(seed, myea_oracle.OracleNet) < 2e-5
+
+
+WIDE = [136, 200, 257, 264, 300, 384]
+
+
+def wide_errors(seed, make_net):
+    """the feed-forward generator at layer widths of 136 - 384 units and batches of 136 - 200 rows: sizes at which the
+    CUDA path takes its CTA-pair and 256 x 256 contraction kernels, shared operand panels and the kernels that write
+    panels while they produce; widths that are no multiple of 8 take the plain paths.  (One reference thread: the
+    harness replays the reference's ShakeDrop draws from the generator of thread 0.)"""
+    desc, opt, layers = _random_network(seed, activations=SMOOTH, optimizers=[capi.OPT_GD], batch=[136, 160, 200][seed % 3], widths=WIDE)
+    opt.learning_rate = 1e-4     # derivatives are sums over the rows
+    n_in, n_out = int(layers[0].unit_parameters[0]), int(layers[-1].unit_parameters[0])
+    one_hot = layers[-1].type_activation_function == capi.AF_SOFTMAX
+
+    def workload():
+        w = workloads.Workload("wide%d" % seed, desc, opt, n_in, n_out, one_hot, layers)
+        w.seed = seed
+        return w
+
+    net = ref.RefNet(desc, opt, threads=1)
+    try:
+        want = cases.run_steps(net, workload(), steps=2)
+    finally:
+        net.close()
+    other = make_net(desc, opt)
+    try:
+        got = cases.run_steps(other, workload(), steps=2, shake=want["shake"])
+    finally:
+        if hasattr(other, "close"):
+            other.close()
+    assert got["index_map"] == want["index_map"] and list(got["sizes"]) == list(want["sizes"])
+    for it in (0, 1):
+        assert got["loss%d" % it][1] == want["loss%d" % it][1]
+    keys = [k for k in ("grad0", "param0", "grad1", "param1", "output_last", "norm_mean_avg", "norm_sigma_avg", "m") if k in want]
+    return max(rel_err(got[k], want[k]) for k in keys)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_wide_network(seed):
+    assert wide_errors(seed, myea_oracle.OracleNet) < 1e-4

@@ -76,3 +76,13 @@ def test_random_autoencoder_pre_training(seed):
     """autoencoders of 3, 5 or 7 layers with mirrored widths: every pre-training level in turn, then the whole network"""
     from test_oracle_random_cpu import autoencoder_errors
     assert autoencoder_errors(seed, Net) < 1e-4
+
+
+def test_random_wide_networks():
+    """layer widths of 136 - 384 units, batches of 136 - 200 rows (CTA-pair and 256 x 256 contraction kernels, shared
+    operand panels, producers that write panels; widths that are no multiple of 8 on the plain paths)"""
+    from test_oracle_random_cpu import wide_errors
+    errors = {seed: wide_errors(seed, Net) for seed in range(24)}
+    print(sorted(errors.items(), key=lambda kv: -kv[1]))
+    worst = max(errors, key=errors.get)
+    assert errors[worst] < 1e-4, "seed %d: %.2e" % (worst, errors[worst])
