@@ -199,7 +199,9 @@ class RefNet:
             raise RuntimeError("Set__Pre_Training_Level(%d) failed" % level)
 
     def next_shakedrop(self):
-        """{residual layer: (mask[B], alpha[B, width], beta[B, width])} the reference will draw in its NEXT training step"""
+        """{residual layer: (mask[B], alpha[B, width], beta[B, width])} the reference will draw in its NEXT training step.
+        Copies of the generators of thread 0 are replayed: an object that is to be compared row by row with another
+        implementation is created with threads=1 (with more threads every thread draws for its own rows)."""
         layers = [l for l in range(1, int(self.desc.number_layers))
                   if self.desc.layers[l].type_layer == capi.LAYER_RESIDUAL and self.desc.layers[l].type_dropout == capi.DROP_SHAKEDROP]
         if not layers:
